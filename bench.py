@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""Benchmark of the autograd-backward hot path: ResNet-50 training step (forward +
+backward, data-parallel gradient all-reduce at N > 1) on synthetic inputs.
+
+    python bench.py --gpus N --steps K --warmup W            # this library, B200
+    python bench.py --impl reference --steps K --warmup W     # CPU stand-in of the reference
+
+One JSON line on stdout (rank 0).  `value` = images/s over all ranks with inputs
+resident in HBM; `e2e` = the same step with the host->device copy of each batch from
+pinned memory and the device->host read of the loss inside the timed region;
+`roofline` = the operator with the largest share of device time, timed with CUDA events
+around its launches inside the timed steps; `cpu_baseline` = the CPU stand-in
+(torch-CPU, same operator sequence) on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from collections import defaultdict
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "resnet50_fwd_bwd_images_per_sec"
+UNIT = "images/s"
+WORKLOAD = "resnet50_train_step_224x224x3_fp32"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+# ------------------------------------------------------------------ CPU arm
+def cpu_sample(batch: int, steps: int, warmup: int, budget_s: float, seed: int = 1234):
+    """Times the CPU stand-in on `batch` images per step; stops early once budget_s is spent."""
+    import torch
+
+    from oracle import cpu_workloads
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    params = _resnet50_params_cpu(g)
+    x = torch.randn(batch, 3, 224, 224, generator=g)
+    t = torch.randint(0, 1000, (batch,), generator=g)
+    for _ in range(warmup):
+        cpu_workloads.resnet50_step(params, x, t)
+    done, t0 = 0, time.perf_counter()
+    while done < steps:
+        cpu_workloads.resnet50_step(params, x, t)
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": batch * done / dt, "unit": UNIT, "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"{done} steps of {batch} images (torch-CPU oneDNN stand-in, fp32), "
+                      f"{dt:.1f} s"}, dt / done * 1e3, done
+
+
+def _resnet50_params_cpu(gen):
+    """Same shapes and initialisers as flashlight_b200.workloads.resnet50, built on the CPU."""
+    import math
+
+    import torch
+
+    ps = []
+
+    def conv(i, o, k):
+        bound = math.sqrt(3.0 / (k * k * i))
+        ps.append((torch.rand(o, i, k, k, generator=gen) * 2 - 1) * bound)
+        ps.append(torch.rand(o, generator=gen))
+        ps.append(torch.zeros(o))
+
+    conv(3, 64, 7)
+    in_c = 64
+    for i, nb in enumerate((3, 4, 6, 3)):
+        planes = 64 * 2 ** i
+        for j in range(nb):
+            stride = (1 if i == 0 else 2) if j == 0 else 1
+            conv(in_c, planes, 1)
+            conv(planes, planes, 3)
+            conv(planes, planes * 4, 1)
+            if in_c != planes * 4 or stride > 1:
+                conv(in_c, planes * 4, 1)
+            in_c = planes * 4
+    ps.append((torch.rand(in_c, 1000, generator=gen) * 2 - 1) * math.sqrt(3.0 / in_c))
+    ps.append((torch.rand(1000, generator=gen) * 2 - 1) * math.sqrt(1.0 / in_c))
+    return ps
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    batch = args.cpu_batch
+    base, ms, done = cpu_sample(batch, args.steps, min(args.warmup, 1), budget_s=150.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT,
+        "n_gpus": args.gpus, "steps": done, "warmup": min(args.warmup, 1), "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "batch_per_step": batch,
+                   "note": "the reference's oneDNN CPU backend cannot be built in this image; "
+                           "this arm times the torch-CPU stand-in (same oneDNN generation) on a "
+                           "bounded sample of the workload"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------- GPU arm
+class ClockSampler:
+    """nvidia-smi samples of this GPU's clocks while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
+                 str(self.index), "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL,
+                text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+class OpTimer:
+    """CUDA-event brackets around every operator call of the extension / function layer."""
+
+    def __init__(self, torch):
+        self.torch = torch
+        self.enabled = False
+        self.records = []  # (name, start, end, flops, bytes)
+
+    def wrap(self, name, fn, work):
+        def timed(*a, **k):
+            if not self.enabled:
+                return fn(*a, **k)
+            s = self.torch.cuda.Event(enable_timing=True)
+            e = self.torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = fn(*a, **k)
+            e.record()
+            fl, by = work(out, *a, **k)
+            self.records.append((name, s, e, fl, by))
+            return out
+        return timed
+
+    def summary(self):
+        agg = defaultdict(lambda: [0, 0.0, 0.0, 0.0])
+        for name, s, e, fl, by in self.records:
+            a = agg[name]
+            a[0] += 1
+            a[1] += s.elapsed_time(e)
+            a[2] += fl
+            a[3] += by
+        return {k: {"calls": v[0], "ms": v[1], "flops": v[2], "bytes": v[3]} for k, v in agg.items()}
+
+
+def _numel_bytes(*ts):
+    return float(sum(t.numel() * t.element_size() for t in ts if t is not None))
+
+
+def install_timers(timer: OpTimer, ext, F):
+    def conv_flops(y, w):
+        # 2 * M * N * K of the implicit GEMM: outputs x (Cin/g * kH * kW)
+        return 2.0 * y.numel() * w.shape[1] * w.shape[2] * w.shape[3]
+
+    ext.conv2d = timer.wrap("conv2d", ext.conv2d,
+                            lambda out, x, w, b, *a, **k: (conv_flops(out, w), _numel_bytes(x, w, out)))
+    ext.conv2dBackwardData = timer.wrap(
+        "conv2dBackwardData", ext.conv2dBackwardData,
+        lambda out, gy, x, w, *a, **k: (conv_flops(gy, w), _numel_bytes(gy, w, out)))
+    ext.conv2dBackwardFilterBias = timer.wrap(
+        "conv2dBackwardFilterBias", ext.conv2dBackwardFilterBias,
+        lambda out, gy, x, w, *a, **k: (conv_flops(gy, w), _numel_bytes(gy, x, w)))
+    ext.batchnorm = timer.wrap("batchnorm", ext.batchnorm,
+                               lambda out, x, *a, **k: (0.0, 2 * _numel_bytes(x)))
+    ext.batchnormBackward = timer.wrap("batchnormBackward", ext.batchnormBackward,
+                                       lambda out, gy, sm, sv, x, *a, **k: (0.0, 3 * _numel_bytes(x)))
+    ext.pool2d = timer.wrap("pool2d", ext.pool2d, lambda out, x, *a, **k: (0.0, _numel_bytes(x, out)))
+    ext.pool2dBackward = timer.wrap("pool2dBackward", ext.pool2dBackward,
+                                    lambda out, gy, x, *a, **k: (0.0, 2 * _numel_bytes(x) + _numel_bytes(gy)))
+    F.relu = timer.wrap("relu", F.relu, lambda out, x: (0.0, 2 * _numel_bytes(x)))
+    F.relu_backward = timer.wrap("relu_backward", F.relu_backward,
+                                 lambda out, x, gy: (0.0, 3 * _numel_bytes(x)))
+    F.add = timer.wrap("add", F.add, lambda out, a, b, **k: (0.0, 3 * _numel_bytes(a)))
+    F.linear = timer.wrap("linear", F.linear,
+                          lambda out, x, w, b=None, **k: (2.0 * out.numel() * w.shape[0],
+                                                          _numel_bytes(x, w, out)))
+    F.linear_backward = timer.wrap(
+        "linear_backward", F.linear_backward,
+        lambda out, x, w, gy, *a, **k: (4.0 * gy.numel() * w.shape[0], _numel_bytes(x, w, gy) * 2))
+
+
+TENSOR_OPS = {"conv2d", "conv2dBackwardData", "conv2dBackwardFilterBias", "linear", "linear_backward"}
+
+
+def run_gpu_arm(args) -> None:
+    import torch
+
+    from flashlight_b200 import _lib as L
+    from flashlight_b200 import autograd as A
+    from flashlight_b200 import distributed as D
+    from flashlight_b200 import functions as F
+    from flashlight_b200 import workloads
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device — this library has no CPU path")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        D.distributedInit("nccl")
+    dev = torch.device("cuda", local)
+
+    math_mode = L.MATH_TF32 if args.math == "tf32" else L.MATH_STRICT_F32
+    A.set_math_mode(math_mode)
+    model = workloads.resnet50(seed=1234, device=dev)
+    reducer = None
+    if world > 1:
+        D.allReduceParameters(model)
+        reducer = D.BucketReducer(model.parameters(), 1.0 / world, args.bucket_mb << 20)
+        D.distributeModuleGrads(model, reducer)
+
+    B = args.batch
+    g = torch.Generator().manual_seed(1000 + rank)
+    x_host = torch.randn(B, 3, 224, 224, generator=g).pin_memory()
+    t_host = torch.randint(0, 1000, (B,), generator=g, dtype=torch.int32).pin_memory()
+    x_dev, t_dev = x_host.to(dev), t_host.to(dev)
+
+    timer = OpTimer(torch)
+    install_timers(timer, A.extension(), F)
+
+    def step(x, t):
+        model.zeroGrad()
+        loss = model.loss(x, t)
+        loss.backward()
+        if reducer is not None:
+            reducer.finalize()
+        return loss
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            torch.distributed.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(x_dev, t_dev)
+    barrier()
+
+    # ---- timed region 1: inputs resident in HBM
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = L.kernel_launches()
+    timer.enabled = True
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        loss = step(x_dev, t_dev)
+    e1.record()
+    barrier()
+    timer.enabled = False
+    launches = L.kernel_launches() - launches0
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- timed region 2: end to end (pinned host batch -> device, loss -> host)
+    for _ in range(1):
+        xb = x_host.to(dev, non_blocking=True)
+        tb = t_host.to(dev, non_blocking=True)
+        step(xb, tb).tensor.item()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    last = 0.0
+    for _ in range(args.steps):
+        xb = x_host.to(dev, non_blocking=True)
+        tb = t_host.to(dev, non_blocking=True)
+        last = step(xb, tb).tensor.item()
+    f1.record()
+    barrier()
+    ms_e2e = f0.elapsed_time(f1)
+
+    if world > 1:
+        tt = torch.tensor([ms_total, ms_e2e], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
+        ms_total, ms_e2e = float(tt[0]), float(tt[1])
+    if rank != 0:
+        return
+
+    images = world * B * args.steps
+    value = images / (ms_total * 1e-3)
+    e2e_value = images / (ms_e2e * 1e-3)
+    peaks = measured_peaks()
+    ops = timer.summary()
+    total_op_ms = sum(v["ms"] for v in ops.values()) or 1.0
+    top = max(ops, key=lambda k: ops[k]["ms"])
+    tv = ops[top]
+    if top in TENSOR_OPS:
+        achieved = tv["flops"] / (tv["ms"] * 1e-3) / 1e12
+        # TF32 has half the tensor rate of bf16; the measured bf16 cuBLAS figure is the only
+        # driver-measured tensor number, so the TF32 peak is taken as half of it.
+        peak = peaks["bf16_tflops_sustained"] / 2
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": None,
+                "peak_source": f"{peaks['source']} bf16 sustained / 2 (tf32 rate)"}
+    else:
+        achieved = tv["bytes"] / (tv["ms"] * 1e-3) / 1e9
+        peak = peaks["hbm_gbs"]
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": None, "peak_source": peaks["source"]}
+    roof["kernel"] = top
+    roof["share_of_step"] = tv["ms"] / total_op_ms
+    per_op = {}
+    for k, v in sorted(ops.items(), key=lambda kv: -kv[1]["ms"]):
+        per_op[k] = {"calls_per_step": v["calls"] / args.steps, "ms_per_step": v["ms"] / args.steps,
+                     "share": v["ms"] / total_op_ms,
+                     "tflops": v["flops"] / (v["ms"] * 1e-3) / 1e12 if v["flops"] else None,
+                     "gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9}
+
+    cpu_base = None
+    if world == 1 and not args.no_cpu_baseline:
+        cpu_base, _, _ = cpu_sample(args.cpu_batch, 3, 1, budget_s=25.0)
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None,
+        "dtype": "tf32" if math_mode == L.MATH_TF32 else "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "batch_per_gpu": B, "global_batch": B * world,
+                   "parallelism": f"dp{world}", "math_mode": args.math,
+                   "l2": "inputs and activations larger than L2 (no flush needed)",
+                   "step": "zeroGrad + forward + loss + backward" +
+                           (" + bucketed NCCL all-reduce" if world > 1 else "")},
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": int(x_host.numel() * 4 + t_host.numel() * 4),
+                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
+        "gpu_launches": int(launches),
+        "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base, "per_op": per_op,
+        "loss": last,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
+    ap.add_argument("--math", default=os.environ.get("FLB200_MATH", "tf32"), choices=["tf32", "strict"])
+    ap.add_argument("--bucket-mb", type=int, default=32)
+    ap.add_argument("--cpu-batch", type=int, default=32)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

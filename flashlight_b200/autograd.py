@@ -1,0 +1,306 @@
+"""A minimal restatement of Flashlight's autograd tape, just enough to drive the
+five benchmark workloads through the B200 kernels the way fl::Variable does.
+
+Variable mirrors flashlight/fl/autograd/Variable.cpp:185-294 (shared grad,
+addGrad accumulation, reverse-topological backward, grad hooks fired once the
+gradient of a leaf is complete).  The differentiable functions mirror the ones in
+flashlight/fl/autograd/Functions.cpp that sit on the backward hot path; each
+builds its result with flb200 kernels and registers a gradFunc closure that calls
+the matching backward kernels.  This file holds no arithmetic of its own.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from . import _lib as L
+from . import functions as F
+from .extension import AutogradPayload, B200AutogradExtension, RNNGradData
+
+_ext: Optional[B200AutogradExtension] = None
+
+
+def extension() -> B200AutogradExtension:
+    """The process-wide extension instance (created lazily, once, like
+    TensorBackend::getExtension, flashlight/fl/tensor/TensorBackend.h:283-300)."""
+    global _ext
+    if _ext is None:
+        _ext = B200AutogradExtension()
+    return _ext
+
+
+def set_math_mode(mode: int) -> None:
+    extension().math_mode = mode
+
+
+class Variable:
+    def __init__(self, tensor: torch.Tensor, calc_grad: bool = False,
+                 inputs: Sequence["Variable"] = (), grad_func: Optional[Callable] = None):
+        self.tensor = tensor
+        self.inputs: List[Variable] = list(inputs)
+        self.grad_func = grad_func
+        self.calc_grad = calc_grad or any(i.calc_grad for i in self.inputs)
+        self.grad: Optional[torch.Tensor] = None
+        self._grad_owned = False
+        self.grad_hook: Optional[Callable[["Variable"], None]] = None
+
+    # Variable::isCalcGrad / addGrad (Variable.cpp:185-211)
+    def isCalcGrad(self) -> bool:
+        return self.calc_grad
+
+    def addGrad(self, g: torch.Tensor) -> None:
+        if not self.calc_grad:
+            return
+        if g.shape != self.tensor.shape:
+            raise ValueError(f"addGrad: given gradient has dimensions not equal to this Variable's "
+                             f"dimensions: {tuple(g.shape)} vs {tuple(self.tensor.shape)}")
+        if self.grad is None:
+            self.grad, self._grad_owned = g, False
+        elif self._grad_owned:
+            F.add(self.grad, g, out=self.grad)
+        else:  # the first gradient may be shared with another Variable: never write into it
+            self.grad, self._grad_owned = F.add(self.grad, g), True
+
+    def zeroGrad(self) -> None:
+        self.grad, self._grad_owned = None, False
+
+    def registerGradHook(self, hook: Callable[["Variable"], None]) -> None:
+        self.grad_hook = hook
+
+    # Variable::backward / build (Variable.cpp:248-294): iterative topological sort
+    def backward(self, grad: Optional[torch.Tensor] = None, retain_graph: bool = False) -> None:
+        if grad is None:
+            grad = torch.ones_like(self.tensor)
+        self.addGrad(grad)
+        order: List[Variable] = []
+        seen = set()
+        stack = [(self, False)]
+        while stack:
+            node, done = stack.pop()
+            if done:
+                order.append(node)
+                continue
+            if id(node) in seen or not node.calc_grad:
+                continue
+            seen.add(id(node))
+            stack.append((node, True))
+            for inp in node.inputs:
+                if id(inp) not in seen:
+                    stack.append((inp, False))
+        for node in reversed(order):
+            if node.grad_func is not None and node.grad is not None:
+                node.grad_func(node.inputs, node.grad)
+            if node.grad_hook is not None and node.grad is not None:
+                node.grad_hook(node)
+            if not retain_graph and node.grad_func is not None:
+                node.grad_func = None
+                node.inputs = []
+                node.grad = None
+
+
+# ------------------------------------------------------------------ functions
+def conv2d(x: Variable, w: Variable, b: Optional[Variable], sx=1, sy=1, px=0, py=0, dx=1, dy=1,
+           groups=1) -> Variable:
+    """fl::conv2d (Functions.cpp:1327-1452)."""
+    ext = extension()
+    args = (sx, sy, px, py, dx, dy, groups)
+    payload = AutogradPayload()
+    bt = b.tensor if b is not None else None
+    y = ext.conv2d(x.tensor, w.tensor, bt, *args, payload)
+    xt, wt = x.tensor, w.tensor
+
+    def grad_func(inputs, gy):
+        if inputs[0].isCalcGrad():
+            inputs[0].addGrad(ext.conv2dBackwardData(gy, xt, wt, *args, None, payload))
+        need_b = b is not None and inputs[2].isCalcGrad()
+        if inputs[1].isCalcGrad() or need_b:
+            gw, gb = ext.conv2dBackwardFilterBias(gy, xt, wt, bt if need_b else None, *args, None,
+                                                  None, payload)
+            if inputs[1].isCalcGrad():
+                inputs[1].addGrad(gw)
+            if need_b:
+                inputs[2].addGrad(gb.reshape(bt.shape))
+
+    return Variable(y, False, [x, w] + ([b] if b is not None else []), grad_func)
+
+
+def pool2d(x: Variable, wx, wy, sx, sy, px, py, mode=L.POOL_MAX) -> Variable:
+    """fl::pool2d (Functions.cpp:1459-1496)."""
+    ext = extension()
+    payload = AutogradPayload()
+    y = ext.pool2d(x.tensor, wx, wy, sx, sy, px, py, mode, payload)
+    xt = x.tensor
+
+    def grad_func(inputs, gy):
+        inputs[0].addGrad(ext.pool2dBackward(gy, xt, y, wx, wy, sx, sy, px, py, mode, payload))
+
+    return Variable(y, False, [x], grad_func)
+
+
+def batchnorm(x: Variable, weight: Optional[Variable], bias: Optional[Variable],
+              running_mean: Optional[torch.Tensor], running_var: Optional[torch.Tensor],
+              axes: Sequence[int], train: bool, momentum: float, epsilon: float) -> Variable:
+    """fl::batchnorm (Functions.cpp:1498-1565)."""
+    ext = extension()
+    wt = weight.tensor if weight is not None else None
+    bt = bias.tensor if bias is not None else None
+    y, save_mean, save_var = ext.batchnorm(x.tensor, wt, bt, running_mean, running_var, axes, train,
+                                           momentum, epsilon, None)
+    xt = x.tensor
+    ins = [x] + ([weight] if weight is not None else []) + ([bias] if bias is not None else [])
+
+    def grad_func(inputs, gy):
+        gx, gw, gb = ext.batchnormBackward(gy, save_mean, save_var, xt, wt, axes, train, epsilon, None)
+        inputs[0].addGrad(gx)
+        k = 1
+        if weight is not None:
+            inputs[k].addGrad(gw.reshape(wt.shape)); k += 1
+        if bias is not None:
+            inputs[k].addGrad(gb.reshape(bt.shape))
+
+    return Variable(y, False, ins, grad_func)
+
+
+def rnn(x: Variable, hx: Optional[Variable], cx: Optional[Variable], w: Variable, hidden: int,
+        layers: int, mode: int, bidirectional: bool, dropout: float = 0.0):
+    """fl::rnn (Functions.cpp:1606-1705): three outputs sharing one gradient computation."""
+    ext = extension()
+    payload = AutogradPayload()
+    hxt = hx.tensor if hx is not None else None
+    cxt = cx.tensor if cx is not None else None
+    y, hy, cy = ext.rnn(x.tensor, hxt, cxt, w.tensor, hidden, layers, mode, bidirectional, dropout,
+                        payload)
+    grad_data = RNNGradData()
+    xt, wt = x.tensor, w.tensor
+    ins = [x, w] + ([hx] if hx is not None else []) + ([cx] if cx is not None else [])
+
+    def dummy_grad(inputs, _g):
+        dx, dhx, dcx, dw = ext.rnnBackward(xt, hxt, cxt, wt, grad_data, y, layers, hidden, mode,
+                                           bidirectional, dropout, payload)
+        inputs[0].addGrad(dx)
+        inputs[1].addGrad(dw.reshape(wt.shape))
+        k = 2
+        if hx is not None:
+            inputs[k].addGrad(dhx); k += 1
+        if cx is not None and dcx is not None:
+            inputs[k].addGrad(dcx)
+
+    dummy = Variable(torch.empty(0, device=xt.device), False, ins, dummy_grad)
+
+    def stash(name):
+        def f(inputs, g):
+            setattr(grad_data, name, g)
+            if inputs[0].grad is None:
+                inputs[0].grad = g.new_empty(0)  # marks the shared node as reached
+        return f
+
+    out_y = Variable(y, False, [dummy], stash("dy"))
+    out_h = Variable(hy, False, [dummy], stash("dhy"))
+    out_c = Variable(cy, False, [dummy], stash("dcy")) if cy is not None else None
+    return out_y, out_h, out_c
+
+
+def linear(x: Variable, w: Variable, b: Optional[Variable]) -> Variable:
+    """fl::linear (Functions.cpp:1255-1309)."""
+    mode = extension().math_mode
+    bt = b.tensor if b is not None else None
+    y = F.linear(x.tensor, w.tensor, bt, math_mode=mode)
+    xt, wt = x.tensor, w.tensor
+
+    def grad_func(inputs, gy):
+        need_b = b is not None and inputs[2].isCalcGrad()
+        gx, gw, gb = F.linear_backward(xt, wt, gy, need_b, inputs[0].isCalcGrad(),
+                                       inputs[1].isCalcGrad(), math_mode=mode)
+        if gx is not None:
+            inputs[0].addGrad(gx)
+        if gw is not None:
+            inputs[1].addGrad(gw)
+        if need_b:
+            inputs[2].addGrad(gb.reshape(bt.shape))
+
+    return Variable(y, False, [x, w] + ([b] if b is not None else []), grad_func)
+
+
+def _unary(x: Variable, fwd, bwd, save_output: bool) -> Variable:
+    y = fwd(x.tensor)
+    saved = y if save_output else x.tensor
+
+    def grad_func(inputs, gy):
+        inputs[0].addGrad(bwd(saved, gy))
+
+    return Variable(y, False, [x], grad_func)
+
+
+def relu(x: Variable) -> Variable:
+    # The mask (x > 0) equals (y > 0), so the output is the saved tensor and the input can be freed.
+    return _unary(x, F.relu, F.relu_backward, True)
+
+
+def gelu(x: Variable) -> Variable:
+    return _unary(x, F.gelu, F.gelu_backward, False)
+
+
+def tanh(x: Variable) -> Variable:
+    return _unary(x, F.tanh, F.tanh_backward, True)
+
+
+def dropout(x: Variable, p: float, mask: torch.Tensor) -> Variable:
+    """fl::dropout with the Bernoulli mask supplied as data (Functions.cpp:1777-1785)."""
+    y = F.dropout_apply(x.tensor, mask, p)
+
+    def grad_func(inputs, gy):
+        inputs[0].addGrad(F.dropout_apply(gy, mask, p))
+
+    return Variable(y, False, [x], grad_func)
+
+
+def add(a: Variable, b: Variable) -> Variable:
+    """operator+ (Functions.cpp:114-123): both inputs receive the same gradient tensor."""
+    y = F.add(a.tensor, b.tensor)
+
+    def grad_func(inputs, gy):
+        inputs[0].addGrad(gy)
+        inputs[1].addGrad(gy)
+
+    return Variable(y, False, [a, b], grad_func)
+
+
+def view(x: Variable, shape) -> Variable:
+    """moddims (Functions.cpp:969-1019): same bytes, new extents (torch order)."""
+    old = x.tensor.shape
+
+    def grad_func(inputs, gy):
+        inputs[0].addGrad(gy.reshape(old))
+
+    return Variable(x.tensor.reshape(shape), False, [x], grad_func)
+
+
+def log_softmax(x: Variable) -> Variable:
+    return _unary(x, F.log_softmax, F.log_softmax_backward, True)
+
+
+def categorical_cross_entropy(logp: Variable, targets: torch.Tensor, reduction=L.REDUCE_MEAN,
+                              ignore_index=-1, validate=False) -> Variable:
+    """fl::categoricalCrossEntropy (Functions.cpp:1078-1154)."""
+    loss, state = F.categorical_cross_entropy(logp.tensor, targets, reduction, ignore_index)
+    if validate:
+        F.check_targets(state)
+    like, classes = logp.tensor, logp.tensor.shape[-1]
+
+    def grad_func(inputs, gl):
+        inputs[0].addGrad(F.categorical_cross_entropy_backward(gl, state, classes, like))
+
+    return Variable(loss, False, [logp], grad_func)
+
+
+def log_softmax_cross_entropy(x: Variable, targets: torch.Tensor, reduction=L.REDUCE_MEAN,
+                              ignore_index=-1) -> Variable:
+    """categoricalCrossEntropy(logSoftmax(x)) with the fused gradient kernel."""
+    y = F.log_softmax(x.tensor)
+    loss, state = F.categorical_cross_entropy(y, targets, reduction, ignore_index)
+
+    def grad_func(inputs, gl):
+        inputs[0].addGrad(F.log_softmax_cross_entropy_backward(y, gl, state))
+
+    return Variable(loss, False, [x], grad_func)

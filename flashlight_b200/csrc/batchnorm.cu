@@ -1,0 +1,413 @@
+// batchnorm / LayerNorm forward and backward, convolution bias gradient, bias
+// tile-add.  Stands behind fl::AutogradExtension::batchnorm and
+// ::batchnormBackward (flashlight/fl/autograd/tensor/AutogradExtension.h:82-94,
+// 155-164); geometry rule from
+// flashlight/fl/autograd/tensor/backend/cudnn/BatchNorm.cpp:22-75 (identical to
+// backend/onednn/BatchNorm.cpp:40-71).  fl::LayerNorm runs through the same
+// entry points (flashlight/fl/nn/modules/LayerNorm.cpp:88-97).
+//
+// Forward (training):  pass 1 shifted sums -> finalize (double) -> pass 2 apply.
+// Backward:            pass 1 (sum dy, sum dy*(x-mean)) -> finalize -> pass 2.
+// Algorithmic bytes per element: forward 8 (+4 for the second read when the
+// slab does not stay in L2), backward 12 (+8 likewise).
+#include "channel_ops.cuh"
+
+namespace flb200 {
+namespace {
+
+// ------------------------------------------------------------ functors
+struct SumF {
+  struct K {};
+  __device__ K channel(long long) const { return K{}; }
+  __device__ void accumulate(const K&, float a, float, float& s0, float&) const { s0 += a; }
+};
+
+// Sums of (x - shift) and (x - shift)^2 with shift = the channel's first
+// element: keeps E[d^2] - E[d]^2 well conditioned when |mean| >> std.
+struct StatsF {
+  const float* x_first;   // base of the tensor (fp32 view used only for the shift)
+  long long inner;        // stride between channels in elements
+  int dtype;
+  struct K { float shift; };
+  __device__ K channel(long long c) const {
+    float v;
+    if (dtype == FLB200_F32) v = x_first[c * inner];
+    else if (dtype == FLB200_F16) v = __half2float(reinterpret_cast<const __half*>(x_first)[c * inner]);
+    else v = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x_first)[c * inner]);
+    if (!(fabsf(v) < 3.0e38f)) v = 0.f;  // inf/NaN shift would poison finite data
+    return K{v};
+  }
+  __device__ void accumulate(const K& k, float a, float, float& s0, float& s1) const {
+    const float d = a - k.shift;
+    s0 += d;
+    s1 += d * d;
+  }
+};
+
+struct BnBwdReduceF {  // a = x, b = dy
+  const float* mean;
+  struct K { float mean; };
+  __device__ K channel(long long c) const { return K{mean[c]}; }
+  __device__ void accumulate(const K& k, float a, float b, float& s0, float& s1) const {
+    s0 += b;
+    s1 += b * (a - k.mean);
+  }
+};
+
+struct BnFwdApplyF {  // y = (x - mean) * scale + shift
+  const float* mean;
+  const float* scale;  // invstd * gamma
+  const float* shift;  // beta
+  struct K { float mean, scale, shift; };
+  __device__ K channel(long long c) const { return K{mean[c], scale[c], shift ? shift[c] : 0.f}; }
+  __device__ float apply(const K& k, float a, float) const {
+    return (a - k.mean) * k.scale + k.shift;
+  }
+};
+
+struct BnBwdApplyF {  // a = x, b = dy: dx = k1 * (dy - mb - (x - mean) * k4)
+  const float4* coef;  // (mean, k1, mean_dbeta, k4)
+  struct K { float mean, k1, mb, k4; };
+  __device__ K channel(long long c) const {
+    const float4 v = coef[c];
+    return K{v.x, v.y, v.z, v.w};
+  }
+  __device__ float apply(const K& k, float a, float b) const {
+    return k.k1 * (b - k.mb - (a - k.mean) * k.k4);
+  }
+};
+
+struct BiasAddF {
+  const float* bias;
+  struct K { float b; };
+  __device__ K channel(long long c) const { return K{bias[c]}; }
+  __device__ float apply(const K& k, float a, float) const { return a + k.b; }
+};
+
+// ----------------------------------------------------- finalize kernels
+__global__ void sum_finalize_kernel(const float2* __restrict__ partial, int splits,
+                                    long long channels, float* __restrict__ out) {
+  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  double s = 0.0;
+  for (int i = 0; i < splits; ++i) s += (double)partial[c * splits + i].x;
+  out[c] = (float)s;
+}
+
+// Turns the shifted sums into mean / inverse std, updates the running stats and
+// prepares the per-channel scale (invstd * gamma) for the apply pass.
+__global__ void bn_stats_finalize_kernel(const float2* __restrict__ partial, int splits,
+                                         long long channels, double count,
+                                         const void* __restrict__ x, long long inner, int dtype,
+                                         const float* __restrict__ weight, double eps,
+                                         double momentum, float* __restrict__ running_mean,
+                                         float* __restrict__ running_var,
+                                         float* __restrict__ save_mean,
+                                         float* __restrict__ save_invstd,
+                                         float* __restrict__ scale) {
+  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  StatsF sf{reinterpret_cast<const float*>(x), inner, dtype};
+  const double shift = (double)sf.channel(c).shift;
+  double s0 = 0.0, s1 = 0.0;
+  for (int i = 0; i < splits; ++i) {
+    const float2 p = partial[c * splits + i];
+    s0 += (double)p.x;
+    s1 += (double)p.y;
+  }
+  const double md = s0 / count;
+  double var = s1 / count - md * md;
+  if (var < 0.0) var = 0.0;
+  const double mean = md + shift;
+  const double invstd = 1.0 / sqrt(var + eps);
+  save_mean[c] = (float)mean;
+  save_invstd[c] = (float)invstd;
+  scale[c] = (float)(invstd * (weight ? (double)weight[c] : 1.0));
+  if (running_mean) running_mean[c] = (float)((1.0 - momentum) * running_mean[c] + momentum * mean);
+  if (running_var) {
+    const double unbiased = count > 1.0 ? var * count / (count - 1.0) : var;
+    running_var[c] = (float)((1.0 - momentum) * running_var[c] + momentum * unbiased);
+  }
+}
+
+__global__ void bn_infer_prepare_kernel(long long channels, const float* __restrict__ weight,
+                                        const float* __restrict__ running_var, double eps,
+                                        float* __restrict__ scale) {
+  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const double invstd = 1.0 / sqrt((double)running_var[c] + eps);
+  scale[c] = (float)(invstd * (weight ? (double)weight[c] : 1.0));
+}
+
+__global__ void bn_bwd_finalize_kernel(const float2* __restrict__ partial, int splits,
+                                       long long channels, double count,
+                                       const float* __restrict__ weight,
+                                       const float* __restrict__ save_mean,
+                                       const float* __restrict__ save_invstd,
+                                       float* __restrict__ grad_weight,
+                                       float* __restrict__ grad_bias,
+                                       float4* __restrict__ coef) {
+  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  double s0 = 0.0, s1 = 0.0;
+  for (int i = 0; i < splits; ++i) {
+    const float2 p = partial[c * splits + i];
+    s0 += (double)p.x;
+    s1 += (double)p.y;
+  }
+  const double invstd = (double)save_invstd[c];
+  const double gamma = weight ? (double)weight[c] : 1.0;
+  grad_bias[c] = (float)s0;
+  grad_weight[c] = (float)(s1 * invstd);
+  coef[c] = make_float4(save_mean[c], (float)(gamma * invstd), (float)(s0 / count),
+                        (float)(invstd * invstd * s1 / count));
+}
+
+// ------------------------------------------------------------ launchers
+template <typename T, int NIN, typename F>
+int launch_reduce(const char* name, const void* a, const void* b, float2* partial,
+                  long long outer, long long channels, long long inner, F f, int* splits_out,
+                  cudaStream_t st) {
+  if (inner == 1) {
+    const int splits = column_splits(outer, channels);
+    const long long rps = (outer + splits - 1) / splits;
+    dim3 grid((unsigned)((channels + 31) / 32), (unsigned)splits);
+    column_reduce_kernel<T, NIN, F><<<grid, 256, 0, st>>>(
+        static_cast<const T*>(a), static_cast<const T*>(b), partial, outer, channels, splits, rps,
+        f);
+    FLB200_AFTER_LAUNCH(name);
+    *splits_out = splits;
+    return FLB200_OK;
+  }
+  const ChannelGeo g = make_channel_geo(outer, channels, inner);
+  const bool vec = inner % Vec16<T>::N == 0 && aligned16(a) && (NIN == 1 || aligned16(b));
+  dim3 grid((unsigned)channels, (unsigned)g.splits);
+  if (vec)
+    channel_reduce_kernel<T, NIN, true, F><<<grid, kChanThreads, 0, st>>>(
+        static_cast<const T*>(a), static_cast<const T*>(b), partial, g, f);
+  else
+    channel_reduce_kernel<T, NIN, false, F><<<grid, kChanThreads, 0, st>>>(
+        static_cast<const T*>(a), static_cast<const T*>(b), partial, g, f);
+  FLB200_AFTER_LAUNCH(name);
+  *splits_out = g.splits;
+  return FLB200_OK;
+}
+
+template <typename T, int NIN, typename F>
+int launch_apply(const char* name, const void* a, const void* b, void* out, long long outer,
+                 long long channels, long long inner, F f, cudaStream_t st) {
+  if (inner == 1) {
+    const int grid = grid_for(outer * channels, 256 * 4);
+    column_apply_kernel<T, NIN, F><<<grid, 256, 0, st>>>(
+        static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), outer, channels,
+        f);
+    FLB200_AFTER_LAUNCH(name);
+    return FLB200_OK;
+  }
+  const ChannelGeo g = make_channel_geo(outer, channels, inner);
+  const bool vec = inner % Vec16<T>::N == 0 && aligned16(a) && aligned16(out) &&
+                   (NIN == 1 || aligned16(b));
+  dim3 grid((unsigned)channels, (unsigned)g.splits);
+  if (vec)
+    channel_apply_kernel<T, NIN, true, F><<<grid, kChanThreads, 0, st>>>(
+        static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), g, f);
+  else
+    channel_apply_kernel<T, NIN, false, F><<<grid, kChanThreads, 0, st>>>(
+        static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), g, f);
+  FLB200_AFTER_LAUNCH(name);
+  return FLB200_OK;
+}
+
+#define FLB200_DISPATCH_DTYPE(dtype, name, CALL)                                   \
+  switch (dtype) {                                                                 \
+    case FLB200_F32: { using T = float; CALL; } break;                             \
+    case FLB200_F16: { using T = __half; CALL; } break;                            \
+    case FLB200_BF16: { using T = __nv_bfloat16; CALL; } break;                    \
+    default: return fail(FLB200_UNSUPPORTED, "%s: unknown dtype %d", name, dtype); \
+  }
+
+int check_geo(const char* name, long long outer, long long channels, long long inner) {
+  FLB200_REQUIRE(outer >= 1 && channels >= 1 && inner >= 1, "%s: empty geometry", name);
+  FLB200_REQUIRE(channels < 0x7fffffffLL, "%s: too many channels", name);
+  return FLB200_OK;
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+}  // namespace flb200
+
+using namespace flb200;
+
+extern "C" {
+
+size_t flb200_channel_sum_workspace_bytes(int64_t outer, int64_t channels, int64_t inner) {
+  if (outer < 1 || channels < 1 || inner < 1) return 0;
+  return channel_partial_bytes(outer, channels, inner);
+}
+
+int flb200_channel_sum(const void* in, float* out, int64_t outer, int64_t channels, int64_t inner,
+                       int dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  if (int st = check_geo("channel_sum", outer, channels, inner)) return st;
+  FLB200_REQUIRE(in && out, "channel_sum: null pointer");
+  if (workspace_bytes < channel_partial_bytes(outer, channels, inner) || !workspace)
+    return fail(FLB200_WORKSPACE_TOO_SMALL, "channel_sum: workspace %zu < %zu", workspace_bytes,
+                channel_partial_bytes(outer, channels, inner));
+  cudaStream_t st = as_stream(stream);
+  float2* partial = static_cast<float2*>(workspace);
+  int splits = 0;
+  int rc = FLB200_OK;
+  FLB200_DISPATCH_DTYPE(dtype, "channel_sum",
+                        rc = (launch_reduce<T, 1>("channel_sum", in, nullptr, partial, outer,
+                                                  channels, inner, SumF{}, &splits, st)));
+  if (rc) return rc;
+  sum_finalize_kernel<<<(unsigned)((channels + 127) / 128), 128, 0, st>>>(partial, splits, channels,
+                                                                        out);
+  FLB200_AFTER_LAUNCH("channel_sum_finalize");
+  return FLB200_OK;
+}
+
+int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t outer,
+                            int64_t channels, int64_t inner, int dtype, void* stream) {
+  if (int st = check_geo("channel_bias_add", outer, channels, inner)) return st;
+  FLB200_REQUIRE(x && bias && y, "channel_bias_add: null pointer");
+  int rc = FLB200_OK;
+  FLB200_DISPATCH_DTYPE(dtype, "channel_bias_add",
+                        rc = (launch_apply<T, 1>("channel_bias_add", x, nullptr, y, outer, channels,
+                                                 inner, BiasAddF{bias}, as_stream(stream))));
+  return rc;
+}
+
+int flb200_batchnorm_geometry(const int64_t* shape, int ndim, const int32_t* axes, int naxes,
+                              flb200_batchnorm_desc* out) {
+  FLB200_REQUIRE(shape && axes && out, "batchnorm_geometry: null pointer");
+  FLB200_REQUIRE(ndim >= 1 && ndim <= 8 && naxes >= 1 && naxes <= ndim,
+                 "batchnorm_geometry: bad rank (ndim %d, naxes %d)", ndim, naxes);
+  int min_axis = axes[0], max_axis = axes[0];
+  int64_t nfeatures = 1, elements = 1;
+  for (int i = 0; i < ndim; ++i) {
+    FLB200_REQUIRE(shape[i] >= 1, "batchnorm_geometry: empty dimension %d", i);
+    elements *= shape[i];
+  }
+  for (int i = 0; i < naxes; ++i) {
+    // "batchnorm - passed axes ... exceeds the number of dimensions of the input"
+    FLB200_REQUIRE(axes[i] >= 0 && axes[i] <= ndim - 1,
+                   "batchnorm - passed axes (axis value %d) exceeds the number of dimensions of "
+                   "the input (%d)",
+                   axes[i], ndim);
+    for (int j = 0; j < i; ++j)
+      FLB200_REQUIRE(axes[j] != axes[i], "batchnorm_geometry: duplicate axis %d", axes[i]);
+    nfeatures *= shape[axes[i]];
+    if (axes[i] < min_axis) min_axis = axes[i];
+    if (axes[i] > max_axis) max_axis = axes[i];
+  }
+  FLB200_REQUIRE(naxes == max_axis - min_axis + 1, "axis array should be continuous");
+  if (min_axis == 0) {  // per-activation
+    out->outer = elements / nfeatures;
+    out->channels = nfeatures;
+    out->inner = 1;
+  } else {
+    int64_t batch = 1;
+    for (int i = max_axis + 1; i < ndim; ++i) batch *= shape[i];
+    out->outer = batch;
+    out->channels = nfeatures;
+    out->inner = elements / (nfeatures * batch);
+  }
+  out->dtype = FLB200_F32;
+  return FLB200_OK;
+}
+
+// Workspace layout: [partials][scale: C floats][coef: C float4]
+size_t flb200_batchnorm_workspace_bytes(const flb200_batchnorm_desc* d) {
+  if (!d || d->outer < 1 || d->channels < 1 || d->inner < 1) return 0;
+  return align_up(channel_partial_bytes(d->outer, d->channels, d->inner), 256) +
+         align_up((size_t)d->channels * sizeof(float), 256) +
+         align_up((size_t)d->channels * sizeof(float4), 256);
+}
+
+int flb200_batchnorm_forward(const flb200_batchnorm_desc* d, const void* x, const float* weight,
+                             const float* bias, float* running_mean, float* running_var,
+                             float* save_mean, float* save_invstd, int train, double momentum,
+                             double epsilon, void* y, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  FLB200_REQUIRE(d, "batchnorm_forward: null descriptor");
+  if (int st = check_geo("batchnorm_forward", d->outer, d->channels, d->inner)) return st;
+  FLB200_REQUIRE(x && y, "batchnorm_forward: null tensor");
+  const size_t need = flb200_batchnorm_workspace_bytes(d);
+  if (!workspace || workspace_bytes < need)
+    return fail(FLB200_WORKSPACE_TOO_SMALL, "batchnorm_forward: workspace %zu < %zu",
+                workspace_bytes, need);
+  cudaStream_t st = as_stream(stream);
+  const long long C = d->channels;
+  char* ws = static_cast<char*>(workspace);
+  float2* partial = reinterpret_cast<float2*>(ws);
+  float* scale =
+      reinterpret_cast<float*>(ws + align_up(channel_partial_bytes(d->outer, C, d->inner), 256));
+  const unsigned fin_grid = (unsigned)((C + 127) / 128);
+  int rc = FLB200_OK;
+  const float* mean_ptr;
+  if (train) {
+    FLB200_REQUIRE(save_mean && save_invstd, "batchnorm_forward: training needs save_mean/save_invstd");
+    int splits = 0;
+    StatsF sf{static_cast<const float*>(x), d->inner, d->dtype};
+    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_forward",
+                          rc = (launch_reduce<T, 1>("batchnorm_stats", x, nullptr, partial,
+                                                    d->outer, C, d->inner, sf, &splits, st)));
+    if (rc) return rc;
+    bn_stats_finalize_kernel<<<fin_grid, 128, 0, st>>>(
+        partial, splits, C, (double)d->outer * (double)d->inner, x, d->inner, d->dtype, weight,
+        epsilon, momentum, running_mean, running_var, save_mean, save_invstd, scale);
+    FLB200_AFTER_LAUNCH("batchnorm_stats_finalize");
+    mean_ptr = save_mean;
+  } else {
+    FLB200_REQUIRE(running_mean && running_var,
+                   "batchnorm_forward: inference needs running_mean/running_var");
+    bn_infer_prepare_kernel<<<fin_grid, 128, 0, st>>>(C, weight, running_var, epsilon, scale);
+    FLB200_AFTER_LAUNCH("batchnorm_infer_prepare");
+    mean_ptr = running_mean;
+  }
+  BnFwdApplyF af{mean_ptr, scale, bias};
+  FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_forward",
+                        rc = (launch_apply<T, 1>("batchnorm_apply", x, nullptr, y, d->outer, C,
+                                                 d->inner, af, st)));
+  return rc;
+}
+
+int flb200_batchnorm_backward(const flb200_batchnorm_desc* d, const void* grad_y, const void* x,
+                              const float* weight, const float* save_mean,
+                              const float* save_invstd, void* grad_x, float* grad_weight,
+                              float* grad_bias, void* workspace, size_t workspace_bytes,
+                              void* stream) {
+  FLB200_REQUIRE(d, "batchnorm_backward: null descriptor");
+  if (int st = check_geo("batchnorm_backward", d->outer, d->channels, d->inner)) return st;
+  FLB200_REQUIRE(grad_y && x && save_mean && save_invstd && grad_x && grad_weight && grad_bias,
+                 "batchnorm_backward: null tensor");
+  const size_t need = flb200_batchnorm_workspace_bytes(d);
+  if (!workspace || workspace_bytes < need)
+    return fail(FLB200_WORKSPACE_TOO_SMALL, "batchnorm_backward: workspace %zu < %zu",
+                workspace_bytes, need);
+  cudaStream_t st = as_stream(stream);
+  const long long C = d->channels;
+  char* ws = static_cast<char*>(workspace);
+  float2* partial = reinterpret_cast<float2*>(ws);
+  size_t off = align_up(channel_partial_bytes(d->outer, C, d->inner), 256);
+  off += align_up((size_t)C * sizeof(float), 256);
+  float4* coef = reinterpret_cast<float4*>(ws + off);
+  int rc = FLB200_OK, splits = 0;
+  BnBwdReduceF rf{save_mean};
+  FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_backward",
+                        rc = (launch_reduce<T, 2>("batchnorm_backward_reduce", x, grad_y, partial,
+                                                  d->outer, C, d->inner, rf, &splits, st)));
+  if (rc) return rc;
+  bn_bwd_finalize_kernel<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(
+      partial, splits, C, (double)d->outer * (double)d->inner, weight, save_mean, save_invstd,
+      grad_weight, grad_bias, coef);
+  FLB200_AFTER_LAUNCH("batchnorm_backward_finalize");
+  BnBwdApplyF af{coef};
+  FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_backward",
+                        rc = (launch_apply<T, 2>("batchnorm_backward_apply", x, grad_y, grad_x,
+                                                 d->outer, C, d->inner, af, st)));
+  return rc;
+}
+
+}  // extern "C"

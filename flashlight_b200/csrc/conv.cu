@@ -1,0 +1,339 @@
+// conv2d forward, backward-data and backward-filter(+bias) as implicit GEMMs
+// over fl's native layout: x [N][C][H][W], w [Cout][C/groups][kH][kW],
+// y [N][Cout][Ho][Wo] (row-major views of fl's column-major tensors; the byte
+// buffers are identical, cf. flashlight/fl/autograd/tensor/backend/onednn/Conv2D.cpp:171-178).
+// Stands behind fl::AutogradExtension::conv2d / ::conv2dBackwardData /
+// ::conv2dBackwardFilterBias (flashlight/fl/autograd/tensor/AutogradExtension.h:58-69,
+// 110-138).  Cross-correlation, stride (sx,sy), symmetric zero padding (px,py),
+// dilation (dx,dy), groups.
+//
+// GEMM views (per group):
+//   forward   M = Cout/g, N = batch*Ho*Wo, K = (C/g)*kH*kW
+//   bwd data  M = C/g,    N = batch*H*W,   K = (Cout/g)*kH*kW
+//   bwd filt  M = Cout/g, N = (C/g)*kH*kW, K = batch*Ho*Wo   (split-K)
+// STRICT mode: the fp32-FMA kernel of simt_gemm.cuh with im2col loaders below.
+// TF32 mode: shapes covered by the tensor-core kernels go to tc_conv, the rest
+// fall through to the fp32 kernel.
+#include "simt_gemm.cuh"
+#include "tc_conv.cuh"
+
+namespace flb200 {
+
+int make_conv_geo(const char* name, const flb200_conv2d_desc* d, ConvGeo* g) {
+  FLB200_REQUIRE(d, "%s: null descriptor", name);
+  FLB200_REQUIRE(d->W >= 1 && d->H >= 1 && d->C >= 1 && d->N >= 1, "%s: empty input", name);
+  FLB200_REQUIRE(d->kW >= 1 && d->kH >= 1 && d->Cout >= 1, "%s: empty filter", name);
+  FLB200_REQUIRE(d->sx >= 1 && d->sy >= 1 && d->dx >= 1 && d->dy >= 1 && d->px >= 0 && d->py >= 0,
+                 "%s: bad stride/dilation/padding", name);
+  FLB200_REQUIRE(d->groups >= 1 && d->C % d->groups == 0 && d->Cout % d->groups == 0,
+                 "%s: channels (%d in, %d out) not divisible by groups (%d)", name, d->C, d->Cout,
+                 d->groups);
+  FLB200_REQUIRE(d->dtype == FLB200_F32, "%s: only f32 is built (dtype %d)", name, d->dtype);
+  FLB200_REQUIRE(d->math_mode == FLB200_MATH_STRICT_F32 || d->math_mode == FLB200_MATH_TF32,
+                 "%s: unknown math mode %d", name, d->math_mode);
+  const int ekw = 1 + (d->kW - 1) * d->dx, ekh = 1 + (d->kH - 1) * d->dy;
+  FLB200_REQUIRE(d->W + 2 * d->px >= ekw && d->H + 2 * d->py >= ekh,
+                 "%s: filter larger than padded input", name);
+  g->W = d->W; g->H = d->H; g->C = d->C; g->N = d->N;
+  g->kW = d->kW; g->kH = d->kH; g->Cout = d->Cout;
+  g->sx = d->sx; g->sy = d->sy; g->px = d->px; g->py = d->py; g->dx = d->dx; g->dy = d->dy;
+  g->groups = d->groups;
+  g->Wo = 1 + (d->W + 2 * d->px - ekw) / d->sx;
+  g->Ho = 1 + (d->H + 2 * d->py - ekh) / d->sy;
+  g->Cg = d->C / d->groups;
+  g->Coutg = d->Cout / d->groups;
+  g->HW = d->H * d->W;
+  g->HoWo = g->Ho * g->Wo;
+  g->RS = d->kH * d->kW;
+  return FLB200_OK;
+}
+
+namespace {
+
+// ------------------------------------------------------------- forward
+// B(k=(ci,r,s), n=(img,p,q)) = x[img][g*Cg+ci][p*sy-py+r*dy][q*sx-px+s*dx]
+struct FpropB {
+  static constexpr bool kAlongK = false;
+  const float* x;
+  ConvGeo g;
+  long long n_total;
+  struct Row { long long base; int h0, w0; };
+  struct Kk { int off, dh, dw; };
+  __device__ Row row(int n, int z) const {
+    if (n >= n_total) return Row{-1, 0, 0};
+    const int img = n / g.HoWo, pq = n - img * g.HoWo;
+    const int p = pq / g.Wo, q = pq - p * g.Wo;
+    return Row{((long long)img * g.C + (long long)z * g.Cg) * g.HW, p * g.sy - g.py,
+               q * g.sx - g.px};
+  }
+  __device__ Kk kk(long long k, int) const {
+    const int ki = (int)k;
+    const int ci = ki / g.RS, rs = ki - ci * g.RS;
+    const int r = rs / g.kW, s = rs - r * g.kW;
+    return Kk{ci * g.HW, r * g.dy, s * g.dx};
+  }
+  __device__ float load(const Row& r, const Kk& k) const {
+    const int h = r.h0 + k.dh, w = r.w0 + k.dw;
+    if (r.base < 0 || h < 0 || h >= g.H || w < 0 || w >= g.W) return 0.f;
+    return x[r.base + k.off + h * g.W + w];
+  }
+};
+
+struct FpropEpilogue {
+  float* y;
+  const float* bias;
+  ConvGeo g;
+  struct Row { long long off; float b; };
+  struct Col { long long off; };
+  __device__ Row row(int m, int z) const {
+    const int co = z * g.Coutg + m;
+    return Row{(long long)co * g.HoWo, bias ? bias[co] : 0.f};
+  }
+  __device__ Col col(int n, int) const {
+    const int img = n / g.HoWo, pq = n - img * g.HoWo;
+    return Col{(long long)img * g.Cout * g.HoWo + pq};
+  }
+  __device__ void store(const Row& r, const Col& c, float acc) const {
+    y[r.off + c.off] = acc + r.b;
+  }
+};
+
+// ------------------------------------------------------- backward data
+// A(m=ci, k=(co,r,s)) = w[g*Coutg+co][ci][r][s]
+struct DgradA {
+  static constexpr bool kAlongK = true;
+  const float* w;
+  ConvGeo g;
+  struct Row { long long off; };
+  struct Kk { long long off; };
+  __device__ Row row(int m, int z) const {
+    if (m >= g.Cg) return Row{-1};
+    return Row{(long long)m * g.RS + (long long)z * g.Coutg * g.Cg * g.RS};
+  }
+  __device__ Kk kk(long long k, int) const {
+    const int ki = (int)k;
+    const int co = ki / g.RS, rs = ki - co * g.RS;
+    return Kk{(long long)co * g.Cg * g.RS + rs};
+  }
+  __device__ float load(const Row& r, const Kk& k) const {
+    return r.off >= 0 ? w[r.off + k.off] : 0.f;
+  }
+};
+
+// B(k=(co,r,s), n=(img,h,w)) = gy[img][g*Coutg+co][p][q] with p*sy = h+py-r*dy, q*sx = w+px-s*dx
+struct DgradB {
+  static constexpr bool kAlongK = false;
+  const float* gy;
+  ConvGeo g;
+  long long n_total;
+  struct Row { long long base; int hh, ww; };
+  struct Kk { int off, dh, dw; };
+  __device__ Row row(int n, int z) const {
+    if (n >= n_total) return Row{-1, 0, 0};
+    const int img = n / g.HW, hw = n - img * g.HW;
+    const int h = hw / g.W, w = hw - h * g.W;
+    return Row{((long long)img * g.Cout + (long long)z * g.Coutg) * g.HoWo, h + g.py, w + g.px};
+  }
+  __device__ Kk kk(long long k, int) const {
+    const int ki = (int)k;
+    const int co = ki / g.RS, rs = ki - co * g.RS;
+    const int r = rs / g.kW, s = rs - r * g.kW;
+    return Kk{co * g.HoWo, r * g.dy, s * g.dx};
+  }
+  __device__ float load(const Row& r, const Kk& k) const {
+    const int th = r.hh - k.dh, tw = r.ww - k.dw;
+    if (r.base < 0 || th < 0 || tw < 0) return 0.f;
+    int p = th, q = tw;
+    if (g.sy != 1) { p = th / g.sy; if (p * g.sy != th) return 0.f; }
+    if (g.sx != 1) { q = tw / g.sx; if (q * g.sx != tw) return 0.f; }
+    if (p >= g.Ho || q >= g.Wo) return 0.f;
+    return gy[r.base + k.off + p * g.Wo + q];
+  }
+};
+
+struct DgradEpilogue {
+  float* gx;
+  ConvGeo g;
+  struct Row { long long off; };
+  struct Col { long long off; };
+  __device__ Row row(int m, int z) const { return Row{((long long)z * g.Cg + m) * g.HW}; }
+  __device__ Col col(int n, int) const {
+    const int img = n / g.HW, hw = n - img * g.HW;
+    return Col{(long long)img * g.C * g.HW + hw};
+  }
+  __device__ void store(const Row& r, const Col& c, float acc) const { gx[r.off + c.off] = acc; }
+};
+
+// ----------------------------------------------------- backward filter
+// A(m=co, k=(img,p,q)) = gy[img][g*Coutg+co][p][q]
+struct WgradA {
+  static constexpr bool kAlongK = true;
+  const float* gy;
+  ConvGeo g;
+  struct Row { long long off; };
+  struct Kk { long long off; };
+  __device__ Row row(int m, int z) const {
+    if (m >= g.Coutg) return Row{-1};
+    return Row{((long long)z * g.Coutg + m) * g.HoWo};
+  }
+  __device__ Kk kk(long long k, int) const {
+    const long long img = k / g.HoWo;
+    const int pq = (int)(k - img * g.HoWo);
+    return Kk{img * g.Cout * g.HoWo + pq};
+  }
+  __device__ float load(const Row& r, const Kk& k) const {
+    return r.off >= 0 ? gy[r.off + k.off] : 0.f;
+  }
+};
+
+// B(k=(img,p,q), n=(ci,r,s)) = x[img][g*Cg+ci][p*sy-py+r*dy][q*sx-px+s*dx]
+struct WgradB {
+  static constexpr bool kAlongK = true;
+  const float* x;
+  ConvGeo g;
+  int n_total;
+  struct Row { long long off; int dh, dw; };
+  struct Kk { long long base; int h0, w0; };
+  __device__ Row row(int n, int z) const {
+    if (n >= n_total) return Row{-1, 0, 0};
+    const int ci = n / g.RS, rs = n - ci * g.RS;
+    const int r = rs / g.kW, s = rs - r * g.kW;
+    return Row{((long long)z * g.Cg + ci) * g.HW, r * g.dy - g.py, s * g.dx - g.px};
+  }
+  __device__ Kk kk(long long k, int) const {
+    const long long img = k / g.HoWo;
+    const int pq = (int)(k - img * g.HoWo);
+    const int p = pq / g.Wo, q = pq - p * g.Wo;
+    return Kk{img * g.C * g.HW, p * g.sy, q * g.sx};
+  }
+  __device__ float load(const Row& r, const Kk& k) const {
+    const int h = k.h0 + r.dh, w = k.w0 + r.dw;
+    if (r.off < 0 || h < 0 || h >= g.H || w < 0 || w >= g.W) return 0.f;
+    return x[k.base + r.off + h * g.W + w];
+  }
+};
+
+struct WgradEpilogue {
+  float* gw;
+  ConvGeo g;
+  struct Row { long long off; };
+  struct Col { long long off; };
+  __device__ Row row(int m, int z) const {
+    return Row{((long long)z * g.Coutg + m) * ((long long)g.Cg * g.RS)};
+  }
+  __device__ Col col(int n, int) const { return Col{(long long)n}; }
+  __device__ void store(const Row& r, const Col& c, float acc) const { gw[r.off + c.off] = acc; }
+};
+
+inline size_t max_sz(size_t a, size_t b) { return a > b ? a : b; }
+
+}  // namespace
+}  // namespace flb200
+
+using namespace flb200;
+
+extern "C" {
+
+int flb200_conv2d_output_dims(const flb200_conv2d_desc* d, int32_t* Wo, int32_t* Ho) {
+  ConvGeo g;
+  if (int st = make_conv_geo("conv2d_output_dims", d, &g)) return st;
+  if (Wo) *Wo = g.Wo;
+  if (Ho) *Ho = g.Ho;
+  return FLB200_OK;
+}
+
+size_t flb200_conv2d_workspace_bytes(const flb200_conv2d_desc* d, int which) {
+  ConvGeo g;
+  if (make_conv_geo("conv2d_workspace_bytes", d, &g)) return 0;
+  size_t need = 0;
+  if (which == 0) {
+    need = plan_simt(g.Coutg, (long long)g.N * g.HoWo, (long long)g.Cg * g.RS, g.groups)
+               .workspace_bytes;
+  } else if (which == 1) {
+    need = plan_simt(g.Cg, (long long)g.N * g.HW, (long long)g.Coutg * g.RS, g.groups)
+               .workspace_bytes;
+  } else {
+    need = plan_simt(g.Coutg, (long long)g.Cg * g.RS, (long long)g.N * g.HoWo, g.groups)
+               .workspace_bytes;
+    need = max_sz(need, flb200_channel_sum_workspace_bytes(g.N, g.Cout, g.HoWo));
+  }
+  if (d->math_mode == FLB200_MATH_TF32) need = max_sz(need, tc_conv_workspace_bytes(g, which));
+  return need;
+}
+
+int flb200_conv2d_forward(const flb200_conv2d_desc* d, const void* x, const void* w,
+                          const void* bias, void* y, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  ConvGeo g;
+  if (int st = make_conv_geo("conv2d_forward", d, &g)) return st;
+  FLB200_REQUIRE(x && w && y, "conv2d_forward: null tensor");
+  cudaStream_t st = as_stream(stream);
+  const float* xf = static_cast<const float*>(x);
+  const float* wf = static_cast<const float*>(w);
+  const float* bf = static_cast<const float*>(bias);
+  float* yf = static_cast<float*>(y);
+  if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 0, workspace_bytes))
+    return tc_conv_forward(g, xf, wf, bf, yf, workspace, workspace_bytes, st);
+  const long long n_total = (long long)g.N * g.HoWo;
+  FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_forward: too many output pixels");
+  const long long K = (long long)g.Cg * g.RS;
+  StridedLoader<true> al{wf, K, 1, (long long)g.Coutg * K, g.Coutg};
+  FpropB bl{xf, g, n_total};
+  FpropEpilogue ep{yf, bf, g};
+  return launch_simt_gemm("conv2d_forward", al, bl, ep, g.Coutg, n_total, K, g.groups, workspace,
+                          workspace_bytes, st);
+}
+
+int flb200_conv2d_backward_data(const flb200_conv2d_desc* d, const void* grad_y, const void* w,
+                                void* grad_x, void* workspace, size_t workspace_bytes,
+                                void* stream) {
+  ConvGeo g;
+  if (int st = make_conv_geo("conv2d_backward_data", d, &g)) return st;
+  FLB200_REQUIRE(grad_y && w && grad_x, "conv2d_backward_data: null tensor");
+  cudaStream_t st = as_stream(stream);
+  const float* gyf = static_cast<const float*>(grad_y);
+  const float* wf = static_cast<const float*>(w);
+  float* gxf = static_cast<float*>(grad_x);
+  if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 1, workspace_bytes))
+    return tc_conv_backward_data(g, gyf, wf, gxf, workspace, workspace_bytes, st);
+  const long long n_total = (long long)g.N * g.HW;
+  FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_backward_data: too many input pixels");
+  DgradA al{wf, g};
+  DgradB bl{gyf, g, n_total};
+  DgradEpilogue ep{gxf, g};
+  return launch_simt_gemm("conv2d_backward_data", al, bl, ep, g.Cg, n_total,
+                          (long long)g.Coutg * g.RS, g.groups, workspace, workspace_bytes, st);
+}
+
+int flb200_conv2d_backward_filter_bias(const flb200_conv2d_desc* d, const void* grad_y,
+                                       const void* x, void* grad_w, void* grad_bias,
+                                       void* workspace, size_t workspace_bytes, void* stream) {
+  ConvGeo g;
+  if (int st = make_conv_geo("conv2d_backward_filter_bias", d, &g)) return st;
+  FLB200_REQUIRE(grad_y && x && grad_w, "conv2d_backward_filter_bias: null tensor");
+  cudaStream_t st = as_stream(stream);
+  const float* gyf = static_cast<const float*>(grad_y);
+  const float* xf = static_cast<const float*>(x);
+  float* gwf = static_cast<float*>(grad_w);
+  int rc;
+  if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 2, workspace_bytes)) {
+    rc = tc_conv_backward_filter(g, gyf, xf, gwf, workspace, workspace_bytes, st);
+  } else {
+    const int n_total = g.Cg * g.RS;
+    WgradA al{gyf, g};
+    WgradB bl{xf, g, n_total};
+    WgradEpilogue ep{gwf, g};
+    rc = launch_simt_gemm("conv2d_backward_filter", al, bl, ep, g.Coutg, n_total,
+                          (long long)g.N * g.HoWo, g.groups, workspace, workspace_bytes, st);
+  }
+  if (rc) return rc;
+  if (grad_bias) {
+    // db[co] = sum over batch and output pixels of dy — one pass over dy
+    // (flashlight/fl/autograd/tensor/backend/cudnn/Conv2D.cpp:737).
+    return flb200_channel_sum(grad_y, static_cast<float*>(grad_bias), g.N, g.Cout, g.HoWo,
+                              FLB200_F32, workspace, workspace_bytes, stream);
+  }
+  return FLB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,237 @@
+// pool2d forward / backward (max, average with and without padding in the
+// divisor).  Stands behind fl::AutogradExtension::pool2d / ::pool2dBackward
+// (flashlight/fl/autograd/tensor/AutogradExtension.h:71-80, 141-152); output
+// extent as flashlight/fl/autograd/tensor/backend/onednn/Pool2D.cpp:100-102.
+//
+// Layout: x [N][C][H][W] row-major (fl [W,H,C,N]).  Forward: one thread per
+// output element, lanes along Wo.  Backward is a GATHER: one thread per input
+// element adds up the windows that selected it, so there are no atomics and the
+// result does not depend on scheduling.  The forward pass leaves one byte per
+// output element (the selected window position) for backward; without it the
+// selection is recomputed from x.
+// Algorithmic bytes: forward 4*(N_in + N_out); backward 4*(2*N_in + N_out).
+#include "common.cuh"
+
+#include <cfloat>
+
+namespace flb200 {
+namespace {
+
+struct PoolGeo {
+  int W, H, Wo, Ho;
+  int wx, wy, sx, sy, px, py;
+  int mode;
+  long long planes;  // N * C
+};
+
+// Selected window position (ky*wx + kx) and value of window (p, q) of one plane.
+// First in-bounds element wins ties; a NaN takes over and later NaNs keep moving
+// the selection, as in the CPU stand-in this library is checked against.
+template <typename T>
+__device__ __forceinline__ int window_argmax(const T* __restrict__ plane, const PoolGeo& g, int p,
+                                             int q, float* best_out) {
+  const int h0 = p * g.sy - g.py, w0 = q * g.sx - g.px;
+  float best = -INFINITY;
+  int arg = 255;
+  for (int ky = 0; ky < g.wy; ++ky) {
+    const int h = h0 + ky;
+    if (h < 0 || h >= g.H) continue;
+    for (int kx = 0; kx < g.wx; ++kx) {
+      const int w = w0 + kx;
+      if (w < 0 || w >= g.W) continue;
+      const float v = Num<T>::to_f(plane[(long long)h * g.W + w]);
+      if (arg == 255 || v > best || v != v) {
+        best = v;
+        arg = ky * g.wx + kx;
+      }
+    }
+  }
+  *best_out = best;
+  return arg;
+}
+
+__device__ __forceinline__ float window_divisor(const PoolGeo& g, int p, int q) {
+  if (g.mode == FLB200_POOL_AVG_INCLUDE_PAD) return (float)(g.wx * g.wy);
+  const int h0 = p * g.sy - g.py, w0 = q * g.sx - g.px;
+  const int h1 = min(h0 + g.wy, g.H), w1 = min(w0 + g.wx, g.W);
+  const int cnt = (h1 - max(h0, 0)) * (w1 - max(w0, 0));
+  return (float)max(cnt, 1);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pool_forward_kernel(const T* __restrict__ x,
+                                                           T* __restrict__ y,
+                                                           uint8_t* __restrict__ argmax,
+                                                           PoolGeo g) {
+  const long long out_plane = (long long)g.Ho * g.Wo;
+  const long long total = g.planes * out_plane;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const long long plane = t / out_plane;
+    const int r = (int)(t - plane * out_plane);
+    const int p = r / g.Wo, q = r - p * g.Wo;
+    const T* xp = x + plane * (long long)g.H * g.W;
+    if (g.mode == FLB200_POOL_MAX) {
+      float best;
+      const int arg = window_argmax(xp, g, p, q, &best);
+      y[t] = Num<T>::from_f(best);
+      if (argmax) argmax[t] = (uint8_t)arg;
+    } else {
+      const int h0 = p * g.sy - g.py, w0 = q * g.sx - g.px;
+      float acc = 0.f;
+      for (int ky = 0; ky < g.wy; ++ky) {
+        const int h = h0 + ky;
+        if (h < 0 || h >= g.H) continue;
+        for (int kx = 0; kx < g.wx; ++kx) {
+          const int w = w0 + kx;
+          if (w < 0 || w >= g.W) continue;
+          acc += Num<T>::to_f(xp[(long long)h * g.W + w]);
+        }
+      }
+      y[t] = Num<T>::from_f(acc / window_divisor(g, p, q));
+    }
+  }
+}
+
+__device__ __forceinline__ int ceil_div_pos(int a, int b) {  // ceil(a / b) for b > 0, any a
+  return a >= 0 ? (a + b - 1) / b : -((-a) / b);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) pool_backward_kernel(const T* __restrict__ dy,
+                                                            const T* __restrict__ x,
+                                                            const uint8_t* __restrict__ argmax,
+                                                            T* __restrict__ dx, PoolGeo g) {
+  const long long in_plane = (long long)g.H * g.W;
+  const long long out_plane = (long long)g.Ho * g.Wo;
+  const long long total = g.planes * in_plane;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const long long plane = t / in_plane;
+    const int r = (int)(t - plane * in_plane);
+    const int h = r / g.W, w = r - h * g.W;
+    // windows p with p*sy - py <= h <= p*sy - py + wy - 1
+    const int p_lo = max(ceil_div_pos(h + g.py - g.wy + 1, g.sy), 0);
+    const int p_hi = min((h + g.py) / g.sy, g.Ho - 1);
+    const int q_lo = max(ceil_div_pos(w + g.px - g.wx + 1, g.sx), 0);
+    const int q_hi = min((w + g.px) / g.sx, g.Wo - 1);
+    const T* dyp = dy + plane * out_plane;
+    float acc = 0.f;
+    for (int p = p_lo; p <= p_hi; ++p) {
+      for (int q = q_lo; q <= q_hi; ++q) {
+        const long long o = (long long)p * g.Wo + q;
+        if (g.mode == FLB200_POOL_MAX) {
+          const int mine = (h + g.py - p * g.sy) * g.wx + (w + g.px - q * g.sx);
+          int sel;
+          if (argmax) {
+            sel = argmax[plane * out_plane + o];
+          } else {
+            float unused;
+            sel = window_argmax(x + plane * in_plane, g, p, q, &unused);
+          }
+          if (sel == mine) acc += Num<T>::to_f(dyp[o]);
+        } else {
+          acc += Num<T>::to_f(dyp[o]) / window_divisor(g, p, q);
+        }
+      }
+    }
+    dx[t] = Num<T>::from_f(acc);
+  }
+}
+
+int make_geo(const char* name, const flb200_pool2d_desc* d, PoolGeo* g) {
+  FLB200_REQUIRE(d, "%s: null descriptor", name);
+  FLB200_REQUIRE(d->W >= 1 && d->H >= 1 && d->C >= 1 && d->N >= 1, "%s: empty input", name);
+  FLB200_REQUIRE(d->wx >= 1 && d->wy >= 1 && d->sx >= 1 && d->sy >= 1 && d->px >= 0 && d->py >= 0,
+                 "%s: bad window/stride/padding", name);
+  FLB200_REQUIRE(d->wx * d->wy <= 255, "%s: window larger than 255 elements", name);
+  FLB200_REQUIRE(d->mode >= FLB200_POOL_MAX && d->mode <= FLB200_POOL_AVG_EXCLUDE_PAD,
+                 "%s: unknown pooling mode %d", name, d->mode);
+  FLB200_REQUIRE(d->W + 2 * d->px >= d->wx && d->H + 2 * d->py >= d->wy,
+                 "%s: window larger than padded input", name);
+  g->W = d->W; g->H = d->H;
+  g->Wo = 1 + (d->W + 2 * d->px - d->wx) / d->sx;
+  g->Ho = 1 + (d->H + 2 * d->py - d->wy) / d->sy;
+  g->wx = d->wx; g->wy = d->wy; g->sx = d->sx; g->sy = d->sy; g->px = d->px; g->py = d->py;
+  g->mode = d->mode;
+  g->planes = (long long)d->C * d->N;
+  return FLB200_OK;
+}
+
+}  // namespace
+}  // namespace flb200
+
+using namespace flb200;
+
+extern "C" {
+
+int flb200_pool2d_output_dims(const flb200_pool2d_desc* d, int32_t* Wo, int32_t* Ho) {
+  PoolGeo g;
+  if (int st = make_geo("pool2d_output_dims", d, &g)) return st;
+  if (Wo) *Wo = g.Wo;
+  if (Ho) *Ho = g.Ho;
+  return FLB200_OK;
+}
+
+int flb200_pool2d_forward(const flb200_pool2d_desc* d, const void* x, void* y, uint8_t* argmax,
+                          void* stream) {
+  PoolGeo g;
+  if (int st = make_geo("pool2d_forward", d, &g)) return st;
+  FLB200_REQUIRE(x && y, "pool2d_forward: null tensor");
+  const long long total = g.planes * g.Ho * g.Wo;
+  const int grid = grid_for(total, 256);
+  cudaStream_t st = as_stream(stream);
+  switch (d->dtype) {
+    case FLB200_F32:
+      pool_forward_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x),
+                                                       static_cast<float*>(y), argmax, g);
+      break;
+    case FLB200_F16:
+      pool_forward_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(x),
+                                                        static_cast<__half*>(y), argmax, g);
+      break;
+    case FLB200_BF16:
+      pool_forward_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), argmax, g);
+      break;
+    default:
+      return fail(FLB200_UNSUPPORTED, "pool2d_forward: unknown dtype %d", d->dtype);
+  }
+  FLB200_AFTER_LAUNCH("pool2d_forward");
+  return FLB200_OK;
+}
+
+int flb200_pool2d_backward(const flb200_pool2d_desc* d, const void* grad_y, const void* x,
+                           const uint8_t* argmax, void* grad_x, void* stream) {
+  PoolGeo g;
+  if (int st = make_geo("pool2d_backward", d, &g)) return st;
+  FLB200_REQUIRE(grad_y && grad_x, "pool2d_backward: null tensor");
+  FLB200_REQUIRE(d->mode != FLB200_POOL_MAX || argmax || x,
+                 "pool2d_backward: max pooling needs the argmax payload or the input");
+  const long long total = g.planes * g.H * g.W;
+  const int grid = grid_for(total, 256);
+  cudaStream_t st = as_stream(stream);
+  switch (d->dtype) {
+    case FLB200_F32:
+      pool_backward_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(grad_y),
+                                                        static_cast<const float*>(x), argmax,
+                                                        static_cast<float*>(grad_x), g);
+      break;
+    case FLB200_F16:
+      pool_backward_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(grad_y),
+                                                         static_cast<const __half*>(x), argmax,
+                                                         static_cast<__half*>(grad_x), g);
+      break;
+    case FLB200_BF16:
+      pool_backward_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+          static_cast<const __nv_bfloat16*>(grad_y), static_cast<const __nv_bfloat16*>(x), argmax,
+          static_cast<__nv_bfloat16*>(grad_x), g);
+      break;
+    default:
+      return fail(FLB200_UNSUPPORTED, "pool2d_backward: unknown dtype %d", d->dtype);
+  }
+  FLB200_AFTER_LAUNCH("pool2d_backward");
+  return FLB200_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,28 @@
+// Convolution geometry shared by the fp32 and the tensor-core paths, and the
+// interface of the tcgen05 implicit-GEMM convolution used by TF32 mode.
+#pragma once
+#include "common.cuh"
+
+namespace flb200 {
+
+struct ConvGeo {
+  int W, H, C, N;
+  int kW, kH, Cout;
+  int sx, sy, px, py, dx, dy, groups;
+  int Wo, Ho, Cg, Coutg;
+  int HW, HoWo, RS;
+};
+
+int make_conv_geo(const char* name, const flb200_conv2d_desc* d, ConvGeo* g);
+
+// which: 0 forward, 1 backward-data, 2 backward-filter.
+bool tc_conv_supported(const ConvGeo& g, int which, size_t workspace_bytes);
+size_t tc_conv_workspace_bytes(const ConvGeo& g, int which);
+int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias, float* y,
+                    void* ws, size_t ws_bytes, cudaStream_t st);
+int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx, void* ws,
+                          size_t ws_bytes, cudaStream_t st);
+int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw, void* ws,
+                            size_t ws_bytes, cudaStream_t st);
+
+}  // namespace flb200

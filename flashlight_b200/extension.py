@@ -1,0 +1,295 @@
+"""Host-side mirror of fl::AutogradExtension over the flb200 C ABI.
+
+`B200AutogradExtension` has the nine operator methods of the reference
+interface (flashlight/fl/autograd/tensor/AutogradExtension.h:46-180) with the
+same names, argument order and argument meaning; the C++ class of the same
+name (csrc/fl/B200AutogradExtension.cpp) is the one a Flashlight build links.
+This Python class exists so that the parity tests and the benchmark drive the
+very same C entry points from device buffers that torch owns.
+
+Tensor convention: a torch CUDA tensor of shape (d_{k-1}, ..., d_0), contiguous,
+stands for the fl tensor [d_0, ..., d_{k-1}] — fl is column-major, so the bytes
+are identical.  An image batch fl [W,H,C,N] is torch (N,C,H,W); `axes` and every
+other dimension index are fl indices (0 = fastest).  An absent (empty) fl tensor
+is None.  Out-parameters of the reference (saveMean, saveVar) are returned.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib as L
+
+_DTYPES = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
+
+
+def dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise ValueError(f"dtype {t.dtype} is not supported by the B200 autograd extension") from None
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("the B200 autograd extension needs device (CUDA) tensors")
+    if not t.is_contiguous():
+        # fl::DevicePtr also refuses non-contiguous tensors (flashlight/fl/common/DevicePtr.cpp:16-33)
+        raise ValueError("can't get device pointer of non-contiguous tensor")
+    return t.data_ptr()
+
+
+def stream_handle() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def workspace(nbytes: int, like: torch.Tensor) -> Optional[torch.Tensor]:
+    if nbytes <= 0:
+        return None
+    return torch.empty(int(nbytes), dtype=torch.uint8, device=like.device)
+
+
+class AutogradPayload:
+    """detail::AutogradPayload: a nullable slot that forward fills and backward reads."""
+
+    def __init__(self):
+        self.data = None
+
+
+@dataclass
+class RNNGradData:
+    """detail::RNNGradData (flashlight/fl/autograd/tensor/AutogradOps.h:356-360)."""
+    dy: Optional[torch.Tensor] = None
+    dhy: Optional[torch.Tensor] = None
+    dcy: Optional[torch.Tensor] = None
+
+
+@dataclass
+class _PoolPayload:
+    argmax: torch.Tensor
+
+
+@dataclass
+class _RnnPayload:
+    reserve: torch.Tensor
+
+
+def _shape4(t: torch.Tensor):
+    """torch (.., N, C, H, W) with missing leading dims = 1 -> (W, H, C, N)."""
+    if t.dim() > 4:
+        raise ValueError("expected at most 4 dimensions")
+    s = (1,) * (4 - t.dim()) + tuple(t.shape)
+    return s[3], s[2], s[1], s[0]
+
+
+def default_math_mode() -> int:
+    """FLB200_TF32=1 selects the tensor-core (TF32) kernels, FLB200_TF32=0 strict fp32."""
+    return L.MATH_TF32 if os.environ.get("FLB200_TF32", "0") not in ("0", "", "false") else L.MATH_STRICT_F32
+
+
+class B200AutogradExtension:
+    """sm_100a implementation of the Flashlight autograd extension interface."""
+
+    def __init__(self, math_mode: Optional[int] = None):
+        self.math_mode = default_math_mode() if math_mode is None else math_mode
+
+    # ------------------------------------------------------------ registry
+    def isDataTypeSupported(self, dtype) -> bool:
+        """TensorExtension::isDataTypeSupported (flashlight/fl/tensor/TensorExtension.h:34)."""
+        return dtype in _DTYPES
+
+    def createBenchmarkOptions(self):
+        """Base-class default: no dynamic benchmark (AutogradExtension.h:53-55)."""
+        return None
+
+    # --------------------------------------------------------------- conv2d
+    def _conv_desc(self, input, weights, sx, sy, px, py, dx, dy, groups) -> L.Conv2dDesc:
+        if input.dtype != torch.float32 or weights.dtype != torch.float32:
+            raise ValueError("conv2d: only f32 tensors are supported")
+        W, H, Cin, N = _shape4(input)
+        kW, kH, Cg, Cout = _shape4(weights)
+        if Cg * groups != Cin:
+            raise ValueError(
+                f"conv2d: weight has {Cg} input channels per group x {groups} groups, input has {Cin}")
+        return L.Conv2dDesc(W, H, Cin, N, kW, kH, Cout, sx, sy, px, py, dx, dy, groups, L.F32,
+                            self.math_mode)
+
+    def conv2d(self, input, weights, bias, sx, sy, px, py, dx, dy, groups, payload=None):
+        d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups)
+        wo, ho = L.i32(), L.i32()
+        L.check(L.lib.flb200_conv2d_output_dims(C.byref(d), C.byref(wo), C.byref(ho)))
+        out = torch.empty((d.N, d.Cout, ho.value, wo.value), dtype=input.dtype, device=input.device)
+        if bias is not None and bias.numel() != d.Cout:
+            raise ValueError("conv2d: bias must have one element per output channel")
+        nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 0)
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_conv2d_forward(C.byref(d), ptr(input), ptr(weights), ptr(bias), ptr(out),
+                                            ptr(ws), nbytes, stream_handle()))
+        return out
+
+    def conv2dBackwardData(self, gradOutput, input, weight, sx, sy, px, py, dx, dy, groups,
+                           dataGradBenchmark=None, payload=None):
+        d = self._conv_desc(input, weight, sx, sy, px, py, dx, dy, groups)
+        grad_in = torch.empty_like(input)
+        nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 1)
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_conv2d_backward_data(C.byref(d), ptr(gradOutput), ptr(weight),
+                                                  ptr(grad_in), ptr(ws), nbytes, stream_handle()))
+        return grad_in
+
+    def conv2dBackwardFilterBias(self, gradOutput, input, weights, bias, sx, sy, px, py, dx, dy,
+                                 groups, filterBench=None, biasBench=None, autogradPayload=None):
+        d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups)
+        grad_w = torch.empty_like(weights)
+        grad_b = torch.empty_like(bias) if bias is not None else None
+        nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 2)
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_conv2d_backward_filter_bias(
+            C.byref(d), ptr(gradOutput), ptr(input), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes,
+            stream_handle()))
+        return grad_w, grad_b
+
+    # --------------------------------------------------------------- pool2d
+    @staticmethod
+    def _pool_desc(input, wx, wy, sx, sy, px, py, mode) -> L.Pool2dDesc:
+        W, H, Cc, N = _shape4(input)
+        return L.Pool2dDesc(W, H, Cc, N, wx, wy, sx, sy, px, py, int(mode), dtype_code(input))
+
+    def pool2d(self, input, wx, wy, sx, sy, px, py, mode, payload=None):
+        d = self._pool_desc(input, wx, wy, sx, sy, px, py, mode)
+        wo, ho = L.i32(), L.i32()
+        L.check(L.lib.flb200_pool2d_output_dims(C.byref(d), C.byref(wo), C.byref(ho)))
+        out = torch.empty((d.N, d.C, ho.value, wo.value), dtype=input.dtype, device=input.device)
+        argmax = None
+        if payload is not None and int(mode) == L.POOL_MAX:
+            argmax = torch.empty(out.shape, dtype=torch.uint8, device=input.device)
+            payload.data = _PoolPayload(argmax)
+        L.check(L.lib.flb200_pool2d_forward(C.byref(d), ptr(input), ptr(out), ptr(argmax),
+                                            stream_handle()))
+        return out
+
+    def pool2dBackward(self, gradOutput, input, poolOutput, wx, wy, sx, sy, px, py, mode,
+                       payload=None):
+        d = self._pool_desc(input, wx, wy, sx, sy, px, py, mode)
+        argmax = payload.data.argmax if payload is not None and payload.data is not None else None
+        grad_in = torch.empty_like(input)
+        L.check(L.lib.flb200_pool2d_backward(C.byref(d), ptr(gradOutput), ptr(input), ptr(argmax),
+                                             ptr(grad_in), stream_handle()))
+        return grad_in
+
+    # ------------------------------------------------------------ batchnorm
+    @staticmethod
+    def _bn_desc(input, axes: Sequence[int]) -> L.BatchnormDesc:
+        fl_shape = tuple(reversed(input.shape))
+        shape = (L.i64 * len(fl_shape))(*fl_shape)
+        ax = (L.i32 * len(axes))(*axes)
+        d = L.BatchnormDesc()
+        L.check(L.lib.flb200_batchnorm_geometry(shape, len(fl_shape), ax, len(axes), C.byref(d)))
+        d.dtype = dtype_code(input)
+        return d
+
+    def batchnorm(self, input, weight, bias, runningMean, runningVar, axes, train, momentum,
+                  epsilon, payload=None):
+        """Returns (output, saveMean, saveVar).  saveVar holds 1/sqrt(var + eps).
+        runningMean / runningVar are updated in place when given."""
+        d = self._bn_desc(input, axes)
+        for t in (weight, bias, runningMean, runningVar):
+            if t is not None and t.dtype != torch.float32:
+                raise ValueError("fl::batchnorm: non-input tensors must be of type f32")
+        if weight is not None and weight.numel() != d.channels:
+            raise ValueError("[BatchNorm] Invalid shape for weight.")
+        if bias is not None and bias.numel() != d.channels:
+            raise ValueError("[BatchNorm] Invalid shape for bias.")
+        out = torch.empty_like(input)
+        save_mean = save_var = None
+        if train:
+            save_mean = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+            save_var = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_batchnorm_forward(
+            C.byref(d), ptr(input), ptr(weight), ptr(bias), ptr(runningMean), ptr(runningVar),
+            ptr(save_mean), ptr(save_var), 1 if train else 0, float(momentum), float(epsilon),
+            ptr(out), ptr(ws), nbytes, stream_handle()))
+        return out, save_mean, save_var
+
+    def batchnormBackward(self, gradOutput, saveMean, saveVar, input, weight, axes, train, epsilon,
+                          payload=None):
+        if not train:
+            # cudnn/BatchNorm.cpp:196-199
+            raise RuntimeError("can't compute batchnorm grad when train was not specified")
+        d = self._bn_desc(input, axes)
+        grad_in = torch.empty_like(input)
+        grad_w = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        grad_b = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_batchnorm_backward(
+            C.byref(d), ptr(gradOutput), ptr(input), ptr(weight), ptr(saveMean), ptr(saveVar),
+            ptr(grad_in), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes, stream_handle()))
+        return grad_in, grad_w, grad_b
+
+    # ------------------------------------------------------------------ rnn
+    def _rnn_desc(self, input, hiddenSize, numLayers, mode, bidirectional) -> L.RnnDesc:
+        if input.dtype != torch.float32:
+            raise ValueError("rnn: only f32 tensors are supported")
+        if input.dim() != 3:
+            raise ValueError("rnn: input must be [inputSize, batch, seqLen]")
+        T, B, I = input.shape
+        return L.RnnDesc(I, hiddenSize, numLayers, B, T, int(mode), 1 if bidirectional else 0, L.F32,
+                         self.math_mode)
+
+    def rnn(self, input, hiddenState, cellState, weights, hiddenSize, numLayers, mode,
+            bidirectional, dropout, payload=None):
+        """Returns (y, hy, cy); cy is None unless mode is LSTM."""
+        if dropout != 0.0:
+            raise NotImplementedError("rnn: inter-layer dropout is not built")
+        d = self._rnn_desc(input, hiddenSize, numLayers, mode, bidirectional)
+        nparams = L.lib.flb200_rnn_num_params(C.byref(d))
+        if weights.numel() != nparams:
+            raise ValueError(f"rnn: weights has {weights.numel()} elements, expected {nparams}")
+        dirs = 2 if bidirectional else 1
+        T, B, _ = input.shape
+        dev = input.device
+        y = torch.empty((T, B, hiddenSize * dirs), dtype=torch.float32, device=dev)
+        hy = torch.empty((numLayers * dirs, B, hiddenSize), dtype=torch.float32, device=dev)
+        cy = torch.empty_like(hy) if int(mode) == L.RNN_LSTM else None
+        reserve = None
+        rbytes = 0
+        if payload is not None:
+            rbytes = L.lib.flb200_rnn_reserve_bytes(C.byref(d))
+            reserve = workspace(rbytes, input)
+            payload.data = _RnnPayload(reserve)
+        wbytes = L.lib.flb200_rnn_workspace_bytes(C.byref(d), 0 if reserve is not None else 2)
+        ws = workspace(wbytes, input)
+        L.check(L.lib.flb200_rnn_forward(
+            C.byref(d), ptr(input), ptr(hiddenState), ptr(cellState), ptr(weights), ptr(y), ptr(hy),
+            ptr(cy), ptr(reserve), rbytes, ptr(ws), wbytes, stream_handle()))
+        return y, hy, cy
+
+    def rnnBackward(self, input, hiddenState, cellState, weights, gradData: RNNGradData, output,
+                    numLayers, hiddenSize, mode, bidirectional, dropProb, payload=None):
+        """Returns (dx, dhx, dcx, dw)."""
+        if payload is None or payload.data is None:
+            raise ValueError("B200AutogradExtension::rnnBackward given null detail::AutogradPayload")
+        d = self._rnn_desc(input, hiddenSize, numLayers, mode, bidirectional)
+        reserve = payload.data.reserve
+        dx = torch.empty_like(input)
+        dirs = 2 if bidirectional else 1
+        B = input.shape[1]
+        dhx = torch.empty((numLayers * dirs, B, hiddenSize), dtype=torch.float32, device=input.device)
+        dcx = torch.empty_like(dhx) if int(mode) == L.RNN_LSTM else None
+        dw = torch.empty_like(weights)
+        wbytes = L.lib.flb200_rnn_workspace_bytes(C.byref(d), 1)
+        ws = workspace(wbytes, input)
+        L.check(L.lib.flb200_rnn_backward(
+            C.byref(d), ptr(input), ptr(hiddenState), ptr(cellState), ptr(weights), ptr(output),
+            ptr(gradData.dy), ptr(gradData.dhy), ptr(gradData.dcy), ptr(dx), ptr(dhx), ptr(dcx),
+            ptr(dw), ptr(reserve), reserve.numel(), ptr(ws), wbytes, stream_handle()))
+        return dx, dhx, dcx, dw

@@ -1,0 +1,239 @@
+"""Fused forward / gradient kernels for the tensor-op chains of Flashlight's
+autograd functions that are NOT behind fl::AutogradExtension
+(flashlight/fl/autograd/Functions.cpp): relu, gelu, tanh, dropout, linear,
+logSoftmax, categoricalCrossEntropy, bias tile/sumAs and gradient accumulation.
+
+Tensor convention as in extension.py: torch shape = reversed fl shape, None for
+an absent tensor.  Every function launches flb200 kernels through the C ABI on
+torch's current stream; nothing is computed by torch itself.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+from .extension import dtype_code, ptr, stream_handle, workspace, default_math_mode
+
+
+def _unary(fn, x):
+    out = torch.empty_like(x)
+    L.check(fn(ptr(x), ptr(out), x.numel(), dtype_code(x), stream_handle()))
+    return out
+
+
+def _binary(fn, a, b):
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("operands must have the same shape and dtype")
+    out = torch.empty_like(a)
+    L.check(fn(ptr(a), ptr(b), ptr(out), a.numel(), dtype_code(a), stream_handle()))
+    return out
+
+
+def relu(x):
+    """fl::relu = max(x, 0) (Functions.cpp:1787-1789)."""
+    return _unary(L.lib.flb200_relu_forward, x)
+
+
+def relu_backward(x, grad_y):
+    """(x > 0) * dy (Functions.cpp:329-338).  Passing the output y instead of x gives the same mask."""
+    return _binary(L.lib.flb200_relu_backward, x, grad_y)
+
+
+def gelu(x):
+    """fl::gelu, tanh form (Functions.cpp:1791-1796)."""
+    return _unary(L.lib.flb200_gelu_forward, x)
+
+
+def gelu_backward(x, grad_y):
+    return _binary(L.lib.flb200_gelu_backward, x, grad_y)
+
+
+def tanh(x):
+    return _unary(L.lib.flb200_tanh_forward, x)
+
+
+def tanh_backward(y, grad_y):
+    """(1 - y^2) * dy from the saved output (Functions.cpp:454-463)."""
+    return _binary(L.lib.flb200_tanh_backward, y, grad_y)
+
+
+def dropout_apply(x, mask, p: float):
+    """x * mask / (1 - p): forward with x, gradient with dy (Functions.cpp:1777-1785)."""
+    if x.shape != mask.shape or x.dtype != mask.dtype:
+        raise ValueError("mask must match the tensor's shape and dtype")
+    out = torch.empty_like(x)
+    L.check(L.lib.flb200_dropout_apply(ptr(x), ptr(mask), ptr(out), 1.0 / (1.0 - p), x.numel(),
+                                       dtype_code(x), stream_handle()))
+    return out
+
+
+def add(a, b, out=None):
+    """Gradient fan-in accumulation of Variable::addGrad (Variable.cpp:205-211)."""
+    if a.shape != b.shape or a.dtype != b.dtype:
+        raise ValueError("operands must have the same shape and dtype")
+    if out is None:
+        out = torch.empty_like(a)
+    L.check(L.lib.flb200_add(ptr(a), ptr(b), ptr(out), a.numel(), dtype_code(a), stream_handle()))
+    return out
+
+
+def channel_sum(x, outer: int, channels: int, inner: int):
+    """out[c] = sum_{o,i} x[o][c][i] (conv bias gradient; detail::sumAs onto a bias)."""
+    if x.numel() != outer * channels * inner:
+        raise ValueError("channel_sum: geometry does not match the tensor")
+    out = torch.empty(channels, dtype=torch.float32, device=x.device)
+    nbytes = L.lib.flb200_channel_sum_workspace_bytes(outer, channels, inner)
+    ws = workspace(nbytes, x)
+    L.check(L.lib.flb200_channel_sum(ptr(x), ptr(out), outer, channels, inner, dtype_code(x), ptr(ws),
+                                     nbytes, stream_handle()))
+    return out
+
+
+def channel_bias_add(x, bias, outer: int, channels: int, inner: int, out=None):
+    if out is None:
+        out = torch.empty_like(x)
+    L.check(L.lib.flb200_channel_bias_add(ptr(x), ptr(bias), ptr(out), outer, channels, inner,
+                                          dtype_code(x), stream_handle()))
+    return out
+
+
+# ------------------------------------------------------------------ linear
+def _linear_dims(weight, x):
+    I = x.shape[-1]
+    cols = x.numel() // I
+    O, I_w = weight.shape[1], weight.shape[0]  # fl weight [O, I] is torch (I, O)
+    if I_w != I:
+        raise ValueError(f"linear: weight expects {I_w} input features, input has {I}")
+    return O, I, cols
+
+
+def linear(x, weight, bias=None, math_mode: Optional[int] = None):
+    """fl::linear forward (Functions.cpp:1255-1275): fl weight [O,I] (torch (I,O)), x fl [I,...]."""
+    mode = default_math_mode() if math_mode is None else math_mode
+    O, I, cols = _linear_dims(weight, x)
+    y = torch.empty(tuple(x.shape[:-1]) + (O,), dtype=x.dtype, device=x.device)
+    nbytes = L.lib.flb200_linear_workspace_bytes(O, I, cols, 0)
+    ws = workspace(nbytes, x)
+    L.check(L.lib.flb200_linear_forward(O, I, cols, ptr(weight), ptr(x), ptr(bias), ptr(y), mode,
+                                        ptr(ws), nbytes, stream_handle()))
+    return y
+
+
+def linear_backward(x, weight, grad_y, has_bias: bool, need_input_grad=True, need_weight_grad=True,
+                    math_mode: Optional[int] = None):
+    """The linear gradFunc (Functions.cpp:1277-1305): returns (grad_x, grad_weight, grad_bias)."""
+    mode = default_math_mode() if math_mode is None else math_mode
+    O, I, cols = _linear_dims(weight, x)
+    gx = gw = gb = None
+    if has_bias:
+        gb = channel_sum(grad_y, cols, O, 1)
+    if need_input_grad:
+        gx = torch.empty_like(x)
+        nbytes = L.lib.flb200_linear_workspace_bytes(O, I, cols, 1)
+        ws = workspace(nbytes, x)
+        L.check(L.lib.flb200_linear_backward_input(O, I, cols, ptr(weight), ptr(grad_y), ptr(gx),
+                                                   mode, ptr(ws), nbytes, stream_handle()))
+    if need_weight_grad:
+        gw = torch.empty_like(weight)
+        nbytes = L.lib.flb200_linear_workspace_bytes(O, I, cols, 2)
+        ws = workspace(nbytes, x)
+        L.check(L.lib.flb200_linear_backward_weight(O, I, cols, ptr(grad_y), ptr(x), ptr(gw), mode,
+                                                    ptr(ws), nbytes, stream_handle()))
+    return gx, gw, gb
+
+
+def matmul(a, b, c=None, *, m, n, k, a_strides, b_strides, c_strides=None, batch=1,
+           batch_strides=(0, 0, 0), alpha=1.0, beta=0.0, math_mode: Optional[int] = None):
+    """C[m,n] = alpha * A(m,k) B(k,n) + beta * C on strided row-major views (flb200_matmul)."""
+    mode = default_math_mode() if math_mode is None else math_mode
+    if c is None:
+        c = torch.empty((batch, m, n) if batch > 1 else (m, n), dtype=a.dtype, device=a.device)
+        c_strides = (n, 1)
+        batch_strides = (batch_strides[0], batch_strides[1], m * n)
+    d = L.MatmulDesc(m, n, k, batch, a_strides[0], a_strides[1], batch_strides[0], b_strides[0],
+                     b_strides[1], batch_strides[1], c_strides[0], c_strides[1], batch_strides[2],
+                     alpha, beta, L.F32, mode)
+    nbytes = L.lib.flb200_matmul_workspace_bytes(C.byref(d))
+    ws = workspace(nbytes, a)
+    L.check(L.lib.flb200_matmul(C.byref(d), ptr(a), ptr(b), ptr(c), ptr(ws), nbytes, stream_handle()))
+    return c
+
+
+# --------------------------------------------------- logSoftmax and CE loss
+def _cx(x):
+    Cc = x.shape[-1]
+    return Cc, x.numel() // Cc
+
+
+def log_softmax(x):
+    """fl::logSoftmax(input, 0) (Functions.cpp:1044-1060): over fl dim 0 = torch's last dim."""
+    Cc, X = _cx(x)
+    y = torch.empty_like(x)
+    L.check(L.lib.flb200_log_softmax_forward(ptr(x), ptr(y), Cc, X, dtype_code(x), stream_handle()))
+    return y
+
+
+def log_softmax_backward(y, grad_y):
+    Cc, X = _cx(y)
+    gx = torch.empty_like(y)
+    L.check(L.lib.flb200_log_softmax_backward(ptr(y), ptr(grad_y), ptr(gx), Cc, X, dtype_code(y),
+                                              stream_handle()))
+    return gx
+
+
+class CrossEntropyState:
+    """What the categoricalCrossEntropy gradFunc captures: targets, kept-target count, mode."""
+
+    def __init__(self, targets, count, reduction, ignore_index):
+        self.targets, self.count, self.reduction, self.ignore_index = (
+            targets, count, reduction, ignore_index)
+
+
+def categorical_cross_entropy(logp, targets, reduction: int = L.REDUCE_MEAN, ignore_index: int = -1):
+    """fl::categoricalCrossEntropy (Functions.cpp:1078-1154).  Returns (loss, state).
+    Raises ValueError when a target lies outside [0, C) and is not ignore_index."""
+    Cc, X = _cx(logp)
+    if targets.numel() != X:
+        raise ValueError("dimension mismatch in categorical cross entropy")
+    if targets.dtype != torch.int32:
+        targets = targets.to(torch.int32)
+    dev = logp.device
+    loss = torch.empty(X if reduction == L.REDUCE_NONE else 1, dtype=torch.float32, device=dev)
+    meta = torch.zeros(2, dtype=torch.int32, device=dev)  # [count, bad-target flag]
+    nbytes = L.lib.flb200_cce_workspace_bytes(X)
+    ws = workspace(nbytes, logp)
+    L.check(L.lib.flb200_cce_forward(ptr(logp), ptr(targets), ptr(loss), meta.data_ptr(),
+                                     meta.data_ptr() + 4, Cc, X, reduction, ignore_index,
+                                     dtype_code(logp), ptr(ws), nbytes, stream_handle()))
+    state = CrossEntropyState(targets, meta, reduction, ignore_index)
+    return loss, state
+
+
+def check_targets(state: CrossEntropyState) -> None:
+    """Host-side read of the bad-target flag (one synchronising copy); the
+    reference performs the same check eagerly (Functions.cpp:1100-1107)."""
+    if int(state.count[1].item()) != 0:
+        raise ValueError("target contains elements out of valid range [0, num_categories) "
+                         "in categorical cross entropy")
+
+
+def categorical_cross_entropy_backward(grad_loss, state: CrossEntropyState, C_classes: int, like):
+    X = state.targets.numel()
+    gx = torch.empty_like(like)
+    L.check(L.lib.flb200_cce_backward(ptr(grad_loss), ptr(state.targets), state.count.data_ptr(),
+                                      ptr(gx), C_classes, X, state.reduction, state.ignore_index,
+                                      dtype_code(like), stream_handle()))
+    return gx
+
+
+def log_softmax_cross_entropy_backward(y, grad_loss, state: CrossEntropyState):
+    """Gradient of categoricalCrossEntropy(logSoftmax(x)) w.r.t. x in one pass."""
+    Cc, X = _cx(y)
+    gx = torch.empty_like(y)
+    L.check(L.lib.flb200_log_softmax_cce_backward(
+        ptr(y), ptr(grad_loss), ptr(state.targets), state.count.data_ptr(), ptr(gx), Cc, X,
+        state.reduction, state.ignore_index, dtype_code(y), stream_handle()))
+    return gx

@@ -1,0 +1,186 @@
+"""The synthetic benchmark workloads: the reference's model definitions restated
+operator for operator over the B200 kernels (nn.py / autograd.py).
+
+  mnist_convnet   README MNIST convnet (reference README.md quick-start model)
+  resnet50        flashlight/pkg/vision/models/Resnet.cpp:67-121, 161-172, 210-230
+  conv_asr        12 x (Conv2D k=13x1 SAME, LayerNorm{0,1,2}, ReLU) + Linear + CE
+                  (flashlight/pkg/runtime/common/SequentialBuilder.cpp:215-226, 332-350)
+  bilstm          fl::RNN(80, 1024, 3, LSTM, bidirectional) + MSE
+
+Each builder returns a model whose `loss(inputs, targets)` builds the tape and
+returns the scalar loss Variable; `loss(...).backward()` is the measured step.
+"""
+from __future__ import annotations
+
+import math
+from typing import List
+
+import torch
+
+from . import _lib as L
+from . import autograd as A
+from . import functions as F
+from . import nn
+from .autograd import Variable
+
+
+class Bottleneck(nn.Module):
+    """ResNetBottleneckBlock (Resnet.cpp:67-121): 1x1, 3x3 (carries the stride), 1x1 x4,
+    BatchNorm after each, ReLU after the first two and after the residual add."""
+
+    def __init__(self, in_c, planes, stride, gen, device):
+        super().__init__()
+        out_c = planes * 4
+        mk = lambda i, o, k, s: nn.Conv2D(i, o, k, k, s, s, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device)
+        self.c1, self.b1 = mk(in_c, planes, 1, 1), nn.BatchNorm(2, planes, gen=gen, device=device)
+        self.c2, self.b2 = mk(planes, planes, 3, stride), nn.BatchNorm(2, planes, gen=gen, device=device)
+        self.c3, self.b3 = mk(planes, out_c, 1, 1), nn.BatchNorm(2, out_c, gen=gen, device=device)
+        self.children = [self.c1, self.b1, self.c2, self.b2, self.c3, self.b3]
+        self.down = None
+        if in_c != out_c or stride > 1:
+            self.down = nn.Sequential(mk(in_c, out_c, 1, stride),
+                                      nn.BatchNorm(2, out_c, gen=gen, device=device))
+            self.children.append(self.down)
+
+    def forward(self, x):
+        out = A.relu(self.b1(self.c1(x)))
+        out = A.relu(self.b2(self.c2(out)))
+        out = self.b3(self.c3(out))
+        shortcut = self.down(x) if self.down is not None else x
+        return A.relu(A.add(out, shortcut))
+
+
+class ClassifierModel(nn.Module):
+    """A trunk that ends in class scores [classes, batch]; loss = mean CE of logSoftmax."""
+
+    def __init__(self, trunk: nn.Module, fused_loss: bool = True):
+        super().__init__()
+        self.trunk = trunk
+        self.children = [trunk]
+        self.fused_loss = fused_loss
+
+    def forward(self, x: Variable) -> Variable:
+        return self.trunk(x)
+
+    def loss(self, x: torch.Tensor, targets: torch.Tensor) -> Variable:
+        scores = self.forward(Variable(x, False))
+        if self.fused_loss:
+            return A.log_softmax_cross_entropy(scores, targets)
+        return A.categorical_cross_entropy(A.log_softmax(scores), targets)
+
+
+def resnet50(seed: int = 1234, device: str = "cuda", blocks=(3, 4, 6, 3), classes: int = 1000,
+             width: int = 64) -> ClassifierModel:
+    """resnet50() of Resnet.cpp:210-230; `blocks` / `width` only shrink it for tests."""
+    gen = torch.Generator().manual_seed(seed)
+    m = nn.Sequential()
+    m.add(nn.Conv2D(3, width, 7, 7, 2, 2, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device))
+    m.add(nn.BatchNorm(2, width, gen=gen, device=device))
+    m.add(nn.ReLU())
+    m.add(nn.Pool2D(3, 3, 2, 2, nn.SAME, nn.SAME, L.POOL_MAX))
+    in_c = width
+    for i, nb in enumerate(blocks):
+        planes = width * (2 ** i)
+        for j in range(nb):
+            m.add(Bottleneck(in_c, planes, (1 if i == 0 else 2) if j == 0 else 1, gen, device))
+            in_c = planes * 4
+    m.add(nn.Pool2D(7, 7, 1, 1, 0, 0, L.POOL_AVG_EXCLUDE_PAD))
+    m.add(nn.View((-1, in_c)))
+    m.add(nn.Linear(in_c, classes, True, gen, device))
+    return ClassifierModel(m)
+
+
+def mnist_convnet(seed: int = 1234, device: str = "cuda") -> ClassifierModel:
+    """Conv 1->32 5x5 SAME, ReLU, MaxPool 2x2/2, Conv 32->64 5x5 SAME, ReLU, MaxPool 2x2/2,
+    View 3136, Linear 3136->1024, ReLU, Dropout(0.5), Linear 1024->10, LogSoftmax."""
+    gen = torch.Generator().manual_seed(seed)
+    m = nn.Sequential(
+        nn.Conv2D(1, 32, 5, 5, 1, 1, nn.SAME, nn.SAME, 1, 1, True, 1, gen, device), nn.ReLU(),
+        nn.Pool2D(2, 2, 2, 2, 0, 0, L.POOL_MAX),
+        nn.Conv2D(32, 64, 5, 5, 1, 1, nn.SAME, nn.SAME, 1, 1, True, 1, gen, device), nn.ReLU(),
+        nn.Pool2D(2, 2, 2, 2, 0, 0, L.POOL_MAX),
+        nn.View((-1, 7 * 7 * 64)),
+        nn.Linear(7 * 7 * 64, 1024, True, gen, device), nn.ReLU(), nn.Dropout(0.5, gen),
+        nn.Linear(1024, 10, True, gen, device))
+    return ClassifierModel(m, fused_loss=False)
+
+
+class ConvAsr(nn.Module):
+    """Input fl [T,1,feat,B]; 12 x (Conv2D kW=13 kH=1 SAME + bias, LayerNorm over fl axes
+    {0,1,2}, ReLU); then per-frame Linear channels->classes and frame-wise cross entropy."""
+
+    def __init__(self, feat=80, channels=1024, layers=12, classes=30, kw=13, seed=1234, device="cuda"):
+        super().__init__()
+        gen = torch.Generator().manual_seed(seed)
+        self.convs = [nn.Conv2D(feat if i == 0 else channels, channels, kw, 1, 1, 1, nn.SAME, 0, 1, 1,
+                                True, 1, gen, device) for i in range(layers)]
+        self.ln = nn.LayerNorm([0, 1, 2], 4)
+        self.head = nn.Linear(channels, classes, True, gen, device)
+        self.children = self.convs + [self.head]
+        self.channels, self.classes = channels, classes
+
+    def loss(self, x: torch.Tensor, targets: torch.Tensor) -> Variable:
+        h = Variable(x, False)  # torch (B, feat, 1, T)
+        for conv in self.convs:
+            h = A.relu(self.ln(conv(h)))
+        B, Cc, _, T = h.tensor.shape
+        # frames as columns: fl reorder to [C, T, B]; done with a torch permute copy, which is
+        # data movement outside the measured operators' arithmetic
+        ht = Variable(h.tensor.permute(0, 3, 2, 1).contiguous().reshape(B * T, Cc), False)
+        hv = _ReorderBridge.apply(h, ht)
+        scores = self.head(hv)
+        return A.log_softmax_cross_entropy(scores, targets)
+
+
+class _ReorderBridge:
+    """fl::reorder between the conv stack and the per-frame Linear (Functions.cpp:513-535):
+    forward and gradient are pure permutations of the same values."""
+
+    @staticmethod
+    def apply(src: Variable, dst: Variable) -> Variable:
+        B, Cc, _, T = src.tensor.shape
+
+        def grad_func(inputs, gy):
+            g = gy.reshape(B, T, 1, Cc).permute(0, 3, 2, 1).contiguous()
+            inputs[0].addGrad(g)
+
+        return Variable(dst.tensor, False, [src], grad_func)
+
+
+class BiLstm(nn.Module):
+    """fl::RNN(80, 1024, 3, LSTM, bidirectional=true) + MSE against a dense target."""
+
+    def __init__(self, input_size=80, hidden=1024, layers=3, seed=1234, device="cuda"):
+        super().__init__()
+        gen = torch.Generator().manual_seed(seed)
+        d = L.RnnDesc(input_size, hidden, layers, 1, 1, L.RNN_LSTM, 1, L.F32, 0)
+        import ctypes as C
+        n = int(L.lib.flb200_rnn_num_params(C.byref(d)))
+        bound = 1.0 / math.sqrt(hidden)  # flashlight/fl/nn/modules/RNN.cpp:58-65
+        w = ((torch.rand(n, generator=gen, dtype=torch.float32) * 2 - 1) * bound).to(device)
+        self.params = [Variable(w, True)]
+        self.hidden, self.layers = hidden, layers
+
+    def loss(self, x: torch.Tensor, target: torch.Tensor) -> Variable:
+        y, _, _ = A.rnn(Variable(x, False), None, None, self.params[0], self.hidden, self.layers,
+                        L.RNN_LSTM, True)
+        return mse(y, target)
+
+
+def mse(y: Variable, target: torch.Tensor) -> Variable:
+    """fl::MeanSquaredError (flashlight/fl/nn/modules/Loss.cpp:17-31): mean over all elements of
+    (y - t)^2; gradient 2 (y - t) / n.  Built from flb200 kernels: add with a negated target,
+    then the scalar reduction through channel_sum."""
+    n = y.tensor.numel()
+    diff = F.add(y.tensor, -target)  # negation of the constant target is input preparation
+    sq = F.dropout_apply(diff, diff, 0.0)  # diff * diff * 1
+    total = F.channel_sum(sq.reshape(-1), n, 1, 1)
+
+    def grad_func(inputs, gl):
+        # d/dy = 2 (y - t) / n * gl ; gl is a device scalar of ones in the benchmark
+        scale = torch.full_like(diff, 2.0 / n)
+        g = F.dropout_apply(diff, scale, 0.0)
+        inputs[0].addGrad(F.dropout_apply(g, gl.expand_as(g).contiguous(), 0.0))
+
+    loss = Variable(total / n, False, [y], grad_func)
+    return loss

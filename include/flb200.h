@@ -1,0 +1,302 @@
+/*
+ * flb200 — C ABI of the B200 (sm_100a) autograd-backward kernel library.
+ *
+ * Every entry point takes raw DEVICE pointers, extents in Flashlight order
+ * (column-major: dim 0 is the fastest; an fl tensor [W,H,C,N] is the same bytes
+ * as a row-major NCHW array) and a CUDA stream (passed as void* so that this
+ * header needs no CUDA include).  Every entry point returns an int status
+ * (FLB200_OK == 0) and never throws, exits or allocates device memory: scratch
+ * is passed in by the caller, sized by the matching *_workspace_bytes query.
+ * The last error text of the calling thread is kept in flb200_last_error().
+ *
+ * Each declaration names the Flashlight interface it stands behind
+ * (path within the flashlight project : line).
+ */
+#ifndef FLB200_H_
+#define FLB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- status */
+enum {
+  FLB200_OK = 0,
+  FLB200_INVALID_ARG = 1,     /* maps to std::invalid_argument on the C++ side */
+  FLB200_UNSUPPORTED = 2,     /* dtype / mode not built */
+  FLB200_LAUNCH_FAILURE = 3,  /* a CUDA call returned an error */
+  FLB200_TIMEOUT = 4,         /* a bounded device-side wait ran out */
+  FLB200_WORKSPACE_TOO_SMALL = 5
+};
+
+/* fl::dtype subset (flashlight/fl/tensor/Types.h:17-30) + bf16 */
+enum { FLB200_F32 = 0, FLB200_F16 = 1, FLB200_BF16 = 2 };
+
+/* fl::PoolingMode (flashlight/fl/autograd/tensor/AutogradOps.h) */
+enum { FLB200_POOL_MAX = 0, FLB200_POOL_AVG_INCLUDE_PAD = 1, FLB200_POOL_AVG_EXCLUDE_PAD = 2 };
+
+/* fl::RnnMode (flashlight/fl/autograd/tensor/AutogradOps.h) */
+enum { FLB200_RNN_RELU = 0, FLB200_RNN_TANH = 1, FLB200_RNN_LSTM = 2, FLB200_RNN_GRU = 3 };
+
+/* Arithmetic mode of the dense contractions; the counterpart of
+ * fl::KernelMode {F32, F32_ALLOW_CONVERSION, F16} (flashlight/fl/common/Defines.h:100).
+ * STRICT = fp32 FMA everywhere (meets 1e-4 parity); TF32 = tcgen05 kind::tf32
+ * with fp32 accumulation in tensor memory where a tensor-core kernel exists for
+ * the shape, fp32 FMA otherwise. */
+enum { FLB200_MATH_STRICT_F32 = 0, FLB200_MATH_TF32 = 1 };
+
+/* fl::ReduceMode (flashlight/fl/autograd/Functions.h) */
+enum { FLB200_REDUCE_NONE = 0, FLB200_REDUCE_MEAN = 1, FLB200_REDUCE_SUM = 2 };
+
+int flb200_abi_version(void);
+const char* flb200_status_string(int status);
+const char* flb200_last_error(void);
+/* Number of kernels this library has launched from the calling process so far. */
+long long flb200_kernel_launches(void);
+/* 1 when the library was built with the tcgen05 kernels and the current device is sm_100. */
+int flb200_has_tensor_core_path(void);
+
+/* ------------------------------------------------- conv2d (a3, a4, a8) */
+/* Geometry of one fl::conv2d call.  x [W,H,C,N], w [kW,kH,C/groups,Cout],
+ * bias [1,1,Cout,1] or absent, y [Wo,Ho,Cout,N] with
+ * Wo = 1 + (W + 2 px - (1 + (kW-1) dx)) / sx  (same for H)
+ * — flashlight/fl/autograd/tensor/backend/onednn/Conv2D.cpp:179-188. */
+typedef struct flb200_conv2d_desc {
+  int32_t W, H, C, N;
+  int32_t kW, kH, Cout;
+  int32_t sx, sy, px, py, dx, dy, groups;
+  int32_t dtype;      /* FLB200_F32 only */
+  int32_t math_mode;  /* FLB200_MATH_* */
+} flb200_conv2d_desc;
+
+int flb200_conv2d_output_dims(const flb200_conv2d_desc* d, int32_t* Wo, int32_t* Ho);
+
+/* which: 0 forward, 1 backward-data, 2 backward-filter(+bias) */
+size_t flb200_conv2d_workspace_bytes(const flb200_conv2d_desc* d, int which);
+
+/* fl::AutogradExtension::conv2d — flashlight/fl/autograd/tensor/AutogradExtension.h:58-69.
+ * bias may be NULL. */
+int flb200_conv2d_forward(const flb200_conv2d_desc* d, const void* x, const void* w,
+                          const void* bias, void* y, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
+/* fl::AutogradExtension::conv2dBackwardData — AutogradExtension.h:110-122.
+ * grad_x [W,H,C,N] is fully overwritten. */
+int flb200_conv2d_backward_data(const flb200_conv2d_desc* d, const void* grad_y,
+                                const void* w, void* grad_x, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
+/* fl::AutogradExtension::conv2dBackwardFilterBias — AutogradExtension.h:124-138.
+ * grad_w [kW,kH,C/groups,Cout] is fully overwritten; grad_bias [Cout] may be
+ * NULL (the reference skips it when bias is empty:
+ * flashlight/fl/autograd/tensor/backend/cudnn/Conv2D.cpp:753). */
+int flb200_conv2d_backward_filter_bias(const flb200_conv2d_desc* d, const void* grad_y,
+                                       const void* x, void* grad_w, void* grad_bias,
+                                       void* workspace, size_t workspace_bytes,
+                                       void* stream);
+
+/* ------------------------------------------------------- pool2d (a5, a8) */
+typedef struct flb200_pool2d_desc {
+  int32_t W, H, C, N;
+  int32_t wx, wy, sx, sy, px, py;
+  int32_t mode;   /* FLB200_POOL_* */
+  int32_t dtype;  /* FLB200_F32 */
+} flb200_pool2d_desc;
+
+/* Wo = 1 + (W + 2 px - wx) / sx — flashlight/fl/autograd/tensor/backend/onednn/Pool2D.cpp:100-102 */
+int flb200_pool2d_output_dims(const flb200_pool2d_desc* d, int32_t* Wo, int32_t* Ho);
+
+/* fl::AutogradExtension::pool2d — AutogradExtension.h:71-80.
+ * argmax (optional, MAX mode only): one byte per output element holding the
+ * window position ky*wx+kx of the selected input; this is the payload that
+ * backward consumes (the oneDNN backend keeps a workspace the same way:
+ * backend/onednn/Pool2D.cpp:71-76).  Ties go to the first in-bounds element in
+ * scan order (ky outer, kx inner); NaN propagates. */
+int flb200_pool2d_forward(const flb200_pool2d_desc* d, const void* x, void* y,
+                          uint8_t* argmax, void* stream);
+
+/* fl::AutogradExtension::pool2dBackward — AutogradExtension.h:141-152.
+ * argmax may be NULL: the selection is then recomputed from x (the cuDNN
+ * backend also works from x and y: backend/cudnn/Pool2D.cpp:73-122). x may be
+ * NULL when argmax is given or mode is an average. */
+int flb200_pool2d_backward(const flb200_pool2d_desc* d, const void* grad_y,
+                           const void* x, const uint8_t* argmax, void* grad_x,
+                           void* stream);
+
+/* ---------------------------------------------------- batchnorm (a6, a8) */
+/* Geometry after fl's axes rule (backend/cudnn/BatchNorm.cpp:22-75): the input
+ * is [outer][channels][inner] row-major; statistics are per channel over
+ * outer*inner elements.  Per-activation mode (min axis 0) is inner == 1. */
+typedef struct flb200_batchnorm_desc {
+  int64_t outer, channels, inner;
+  int32_t dtype;  /* FLB200_F32 */
+} flb200_batchnorm_desc;
+
+/* Turns (shape, axes) into the descriptor; returns FLB200_INVALID_ARG for axes
+ * that are out of range or not contiguous, like the reference. */
+int flb200_batchnorm_geometry(const int64_t* shape, int ndim, const int32_t* axes,
+                              int naxes, flb200_batchnorm_desc* out);
+
+size_t flb200_batchnorm_workspace_bytes(const flb200_batchnorm_desc* d);
+
+/* fl::AutogradExtension::batchnorm — AutogradExtension.h:82-94.
+ * train != 0: batch statistics; save_mean[c] = mean, save_invstd[c] =
+ * 1/sqrt(biased var + eps) (what cuDNN's saveVar slot holds); running stats
+ * (optional) updated as r = (1-momentum) r + momentum * batch (unbiased var).
+ * train == 0: normalises with running_mean / running_var.
+ * weight / bias may be NULL (ones / zeros). */
+int flb200_batchnorm_forward(const flb200_batchnorm_desc* d, const void* x,
+                             const float* weight, const float* bias,
+                             float* running_mean, float* running_var,
+                             float* save_mean, float* save_invstd, int train,
+                             double momentum, double epsilon, void* y,
+                             void* workspace, size_t workspace_bytes, void* stream);
+
+/* fl::AutogradExtension::batchnormBackward — AutogradExtension.h:155-164.
+ * Always writes grad_x, grad_weight, grad_bias. */
+int flb200_batchnorm_backward(const flb200_batchnorm_desc* d, const void* grad_y,
+                              const void* x, const float* weight,
+                              const float* save_mean, const float* save_invstd,
+                              void* grad_x, float* grad_weight, float* grad_bias,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
+/* --------------------------------------------------------- matmul (a9) */
+/* C[m,n] = alpha * sum_k A(m,k) B(k,n) + beta * C[m,n] on ROW-MAJOR views with
+ * explicit element strides, so that every fl::matmul / matmulTN / matmulNT
+ * (flashlight/fl/autograd/Functions.cpp:827-946; TensorBackend::matmul,
+ * flashlight/fl/tensor/TensorBackend.h:213-217) is one call.  batch > 1 walks
+ * the batch strides (0 = broadcast). */
+typedef struct flb200_matmul_desc {
+  int64_t m, n, k, batch;
+  int64_t a_row, a_col, a_batch; /* A(i,kk) at a[i*a_row + kk*a_col + b*a_batch] */
+  int64_t b_row, b_col, b_batch; /* B(kk,j) at b[kk*b_row + j*b_col + b*b_batch] */
+  int64_t c_row, c_col, c_batch;
+  float alpha, beta;
+  int32_t dtype;      /* FLB200_F32 */
+  int32_t math_mode;  /* FLB200_MATH_* */
+} flb200_matmul_desc;
+
+size_t flb200_matmul_workspace_bytes(const flb200_matmul_desc* d);
+int flb200_matmul(const flb200_matmul_desc* d, const void* a, const void* b, void* c,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* fl::linear gradFunc pieces (Functions.cpp:1255-1309) on fl-layout buffers:
+ * weight [O,I], x [I,cols], y / grad_y [O,cols] (all column-major).  which:
+ * 0 forward, 1 backward-input, 2 backward-weight.  workspace may be NULL (the
+ * contraction then runs without split-K). */
+size_t flb200_linear_workspace_bytes(int64_t O, int64_t I, int64_t cols, int which);
+int flb200_linear_forward(int64_t O, int64_t I, int64_t cols, const void* weight,
+                          const void* x, const void* bias, void* y, int math_mode,
+                          void* workspace, size_t workspace_bytes, void* stream);
+int flb200_linear_backward_input(int64_t O, int64_t I, int64_t cols, const void* weight,
+                                 const void* grad_y, void* grad_x, int math_mode,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+int flb200_linear_backward_weight(int64_t O, int64_t I, int64_t cols, const void* grad_y,
+                                  const void* x, void* grad_w, int math_mode,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------- bandwidth-bound gradFuncs (a10-a12) */
+/* out[c] = sum over outer, inner of in[o][c][i]  — conv bias gradient
+ * (backend/cudnn/Conv2D.cpp:737) with (N, Cout, Ho*Wo), and detail::sumAs for a
+ * linear bias (Functions.cpp:44-58, 1285-1289) with (cols, O, 1). */
+size_t flb200_channel_sum_workspace_bytes(int64_t outer, int64_t channels, int64_t inner);
+int flb200_channel_sum(const void* in, float* out, int64_t outer, int64_t channels,
+                       int64_t inner, int dtype, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* y[o][c][i] = x[o][c][i] + bias[c] (tile + add, Functions.cpp:1270-1275). In place allowed. */
+int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t outer,
+                            int64_t channels, int64_t inner, int dtype, void* stream);
+
+/* relu = max(x, 0) (Functions.cpp:1787-1789); gradient (x > 0) * dy (Functions.cpp:329-338). */
+int flb200_relu_forward(const void* x, void* y, int64_t n, int dtype, void* stream);
+int flb200_relu_backward(const void* x, const void* grad_y, void* grad_x, int64_t n,
+                         int dtype, void* stream);
+/* gelu, tanh form with 0.7978845608 and 0.044715 (Functions.cpp:1791-1796). */
+int flb200_gelu_forward(const void* x, void* y, int64_t n, int dtype, void* stream);
+int flb200_gelu_backward(const void* x, const void* grad_y, void* grad_x, int64_t n,
+                         int dtype, void* stream);
+/* tanh: gradient (1 - y^2) * dy from the saved OUTPUT (Functions.cpp:454-463). */
+int flb200_tanh_forward(const void* x, void* y, int64_t n, int dtype, void* stream);
+int flb200_tanh_backward(const void* y, const void* grad_y, void* grad_x, int64_t n,
+                         int dtype, void* stream);
+/* dropout: out = in * mask * scale, scale = 1/(1-p); the same call serves the
+ * forward (in = x) and the gradient (in = dy) (Functions.cpp:1777-1785). mask
+ * holds 0/1 in the tensor's dtype, as the reference materialises it. */
+int flb200_dropout_apply(const void* in, const void* mask, void* out, float scale,
+                         int64_t n, int dtype, void* stream);
+/* out = a + b: Variable::addGrad fan-in accumulation (flashlight/fl/autograd/Variable.cpp:205-211). In place allowed. */
+int flb200_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
+
+/* logSoftmax over fl dim 0: x, y [C, X] column-major (Functions.cpp:1044-1070). */
+int flb200_log_softmax_forward(const void* x, void* y, int64_t C, int64_t X, int dtype,
+                               void* stream);
+/* grad_x = grad_y - exp(y) * sum_c grad_y (Functions.cpp:1062-1067). */
+int flb200_log_softmax_backward(const void* y, const void* grad_y, void* grad_x, int64_t C,
+                                int64_t X, int dtype, void* stream);
+
+/* categoricalCrossEntropy (Functions.cpp:1078-1154): logp [C,X], targets int32 [X].
+ * loss: [X] for NONE, [1] otherwise; count_out (optional) receives the number
+ * of targets != ignore_index (the MEAN denominator).  A target outside [0,C)
+ * that is not ignore_index makes bad_target_flag (device int, optional) nonzero
+ * and contributes 0 — the host side turns that into std::invalid_argument. */
+size_t flb200_cce_workspace_bytes(int64_t X);
+int flb200_cce_forward(const void* logp, const int32_t* targets, float* loss,
+                       int32_t* count_out, int32_t* bad_target_flag, int64_t C, int64_t X,
+                       int reduction, int ignore_index, int dtype, void* workspace,
+                       size_t workspace_bytes, void* stream);
+/* grad_logp [C,X] is fully written: -(g) at the target row, 0 elsewhere, where
+ * g = grad_loss[x] (NONE), grad_loss[0]/count (MEAN), grad_loss[0] (SUM);
+ * count is read from the device int written by the forward call. */
+int flb200_cce_backward(const float* grad_loss, const int32_t* targets,
+                        const int32_t* count, void* grad_logp, int64_t C, int64_t X,
+                        int reduction, int ignore_index, int dtype, void* stream);
+/* logSoftmax + categoricalCrossEntropy gradient in one pass:
+ * grad_x = (exp(y) - onehot) * g   (the chain of the two gradFuncs above). */
+int flb200_log_softmax_cce_backward(const void* y, const float* grad_loss,
+                                    const int32_t* targets, const int32_t* count,
+                                    void* grad_x, int64_t C, int64_t X, int reduction,
+                                    int ignore_index, int dtype, void* stream);
+
+/* ----------------------------------------------------------- rnn (a7, a8) */
+/* x [I,B,T], y [H*dirs,B,T], hx/cx/hy/cy [H,B,L*dirs]; w flat in the cuDNN
+ * order the reference uses (flashlight/fl/nn/Utils.cpp:45-84;
+ * backend/onednn/RNN.cpp:66-158): for every pseudo-layer (layer-major, forward
+ * direction then reverse) W_ih [G*H, In] and W_hh [G*H, H] row-major; then for
+ * every pseudo-layer b_ih [G*H], b_hh [G*H].  Gate order LSTM i,f,g,o; GRU
+ * r,z,n with the reset gate applied after the recurrent product. */
+typedef struct flb200_rnn_desc {
+  int32_t input_size, hidden_size, num_layers, batch, seq_len;
+  int32_t mode;           /* FLB200_RNN_* */
+  int32_t bidirectional;  /* 0 / 1 */
+  int32_t dtype;          /* FLB200_F32 */
+  int32_t math_mode;
+} flb200_rnn_desc;
+
+int64_t flb200_rnn_num_params(const flb200_rnn_desc* d);
+/* reserve space written by forward and read by backward (the payload). */
+size_t flb200_rnn_reserve_bytes(const flb200_rnn_desc* d);
+size_t flb200_rnn_workspace_bytes(const flb200_rnn_desc* d, int backward);
+
+/* fl::AutogradExtension::rnn — AutogradExtension.h:96-106. hx, cx may be NULL (zeros);
+ * hy, cy may be NULL; reserve may be NULL for inference. */
+int flb200_rnn_forward(const flb200_rnn_desc* d, const void* x, const void* hx,
+                       const void* cx, const void* w, void* y, void* hy, void* cy,
+                       void* reserve, size_t reserve_bytes, void* workspace,
+                       size_t workspace_bytes, void* stream);
+/* fl::AutogradExtension::rnnBackward — AutogradExtension.h:167-179. grad_y, grad_hy,
+ * grad_cy may be NULL (zeros: backend/cudnn/RNN.cpp:269-272); grad_hx / grad_cx may be NULL. */
+int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
+                        const void* cx, const void* w, const void* y,
+                        const void* grad_y, const void* grad_hy, const void* grad_cy,
+                        void* grad_x, void* grad_hx, void* grad_cx, void* grad_w,
+                        const void* reserve, size_t reserve_bytes, void* workspace,
+                        size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLB200_H_ */

@@ -1,0 +1,389 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle on seeded inputs.
+Strict-fp32 mode: relative error (tests/parity.py) <= 1e-4 against the fp64 oracle."""
+import pytest
+import torch
+
+from oracle import flref as R
+from tests.parity import STRICT_TOL, assert_close, randint, randn, rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def fx():
+    from flashlight_b200 import functions
+    return functions
+
+
+@pytest.fixture(scope="module")
+def ext():
+    from flashlight_b200 import _lib as L
+    from flashlight_b200.extension import B200AutogradExtension
+    return B200AutogradExtension(math_mode=L.MATH_STRICT_F32)
+
+
+def dev(t):
+    return None if t is None else t.cuda()
+
+
+def f64(t):
+    return None if t is None else t.double()
+
+
+# ------------------------------------------------------------------ eltwise
+@pytest.mark.parametrize("n", [1, 7, 4096, 1000003])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.float16, 2e-3),
+                                       (torch.bfloat16, 1.6e-2)])
+def test_eltwise_gradfuncs(fx, n, dtype, tol):
+    x = randn(n, seed=1, dtype=dtype)
+    gy = randn(n, seed=2, dtype=dtype)
+    xd, gd = x.cuda(), gy.cuda()
+    x64, g64 = x.double(), gy.double()
+    assert_close(fx.relu(xd), R.relu(x64), tol, "relu")
+    assert_close(fx.relu_backward(xd, gd), R.relu_backward(x64, g64), tol, "relu_backward")
+    assert_close(fx.gelu(xd), R.gelu(x64), tol, "gelu")
+    assert_close(fx.gelu_backward(xd, gd), R.gelu_backward(x64, g64), tol, "gelu_backward")
+    y = torch.tanh(x64).to(dtype)
+    assert_close(fx.tanh(xd), torch.tanh(x64), tol, "tanh")
+    assert_close(fx.tanh_backward(y.cuda(), gd), R.tanh_backward(y.double(), g64), tol, "tanh_backward")
+    mask = (randn(n, seed=3) > 0).to(dtype)
+    assert_close(fx.dropout_apply(gd, mask.cuda(), 0.5), R.dropout_apply(g64, mask.double(), 0.5),
+                 tol, "dropout")
+    assert_close(fx.add(xd, gd), x64 + g64, tol, "add")
+
+
+def test_eltwise_unaligned_pointers_and_inplace(fx):
+    base = randn(10001, seed=4).cuda()
+    gbase = randn(10001, seed=5).cuda()
+    x, g = base[1:], gbase[1:]  # 4-byte aligned only: takes the scalar kernels
+    want = R.relu_backward(x.cpu().double(), g.cpu().double())
+    assert_close(fx.relu_backward(x, g), want, 1e-6, "unaligned inputs")
+    out = torch.empty(10001, device="cuda")[1:]
+    from flashlight_b200 import _lib as L
+    L.check(L.lib.flb200_relu_backward(x.data_ptr(), g.data_ptr(), out.data_ptr(), x.numel(), L.F32,
+                                       torch.cuda.current_stream().cuda_stream))
+    assert_close(out, want, 1e-6, "unaligned pointers")
+    a = randn(5000, seed=6).cuda()
+    b = randn(5000, seed=7).cuda()
+    want = a.cpu().double() + b.cpu().double()
+    fx.add(a, b, out=a)
+    assert_close(a, want, 1e-6, "in-place add")
+
+
+def test_relu_propagates_nan_and_handles_negative_zero(fx):
+    x = torch.tensor([float("nan"), -0.0, 0.0, -1.0, 2.0], device="cuda")
+    y = fx.relu(x).cpu()
+    assert torch.isnan(y[0]) and y[1] == 0 and y[2] == 0 and y[3] == 0 and y[4] == 2
+    g = fx.relu_backward(x, torch.ones_like(x)).cpu()
+    assert g.tolist() == [0.0, 0.0, 0.0, 0.0, 1.0]
+
+
+# -------------------------------------------------- channel sum / bias add
+GEOS = [(8, 64, 3136), (4, 16, 49), (1, 16, 102400), (1000, 30, 1), (7, 33, 1), (3, 5, 7),
+        (2, 3, 1026), (16, 2048, 49), (1, 300, 768), (5000, 1, 1), (1, 1, 5)]
+
+
+@pytest.mark.parametrize("geo", GEOS)
+def test_channel_sum_and_bias_add(fx, geo):
+    outer, ch, inner = geo
+    x = randn(outer, ch, inner, seed=8)
+    want = x.double().sum(dim=(0, 2))
+    assert_close(fx.channel_sum(x.cuda(), outer, ch, inner), want, STRICT_TOL, f"channel_sum {geo}")
+    b = randn(ch, seed=9)
+    got = fx.channel_bias_add(x.cuda(), b.cuda(), outer, ch, inner)
+    assert_close(got, x.double() + b.double()[None, :, None], 1e-6, f"bias_add {geo}")
+
+
+# ---------------------------------------------------------------- batchnorm
+BN_CASES = [
+    # torch shape, fl axes
+    ((8, 64, 28, 28), [2]),        # ResNet-style spatial
+    ((4, 256, 7, 7), [2]),         # inner = 49 (not a multiple of 4)
+    ((3, 5, 6, 7), [2]),           # tiny, ragged
+    ((2, 384, 768), [1, 2]),       # LayerNorm over fl axis 0 (transformer)
+    ((4, 64, 1, 3000), [3]),       # fl [T,1,C,B] 'LN 0 1 2' -> axes {3}: few long channels
+    ((16, 6, 5, 7), [0, 1, 2]),    # per-activation
+    ((6, 4, 5, 3), [0, 1, 2, 3]),  # everything is a feature, outer = 1
+    ((64, 10), [1]),               # fl [10, 64]: axis 1 -> 64 channels... of inner 10
+]
+
+
+@pytest.mark.parametrize("shape,axes", BN_CASES)
+@pytest.mark.parametrize("affine", [True, False])
+def test_batchnorm_forward_backward(ext, shape, axes, affine):
+    x = randn(*shape, seed=10) * 1.7 + 0.4
+    outer, ch, inner = R.batchnorm_geometry(tuple(reversed(shape)), axes)
+    w = (randn(ch, seed=11).abs() + 0.5) if affine else None
+    b = randn(ch, seed=12) if affine else None
+    rm, rv = randn(ch, seed=13) * 0.1, randn(ch, seed=14).abs() + 0.5
+    rm_d, rv_d = rm.cuda(), rv.cuda()
+    y, sm, sv = ext.batchnorm(x.cuda(), dev(w), dev(b), rm_d, rv_d, axes, True, 0.1, 1e-5)
+    wy, wm, wi, wrm, wrv = R.batchnorm(x.double(), f64(w), f64(b), rm.double(), rv.double(), axes,
+                                       True, 0.1, 1e-5)
+    assert_close(y, wy, STRICT_TOL, "bn y")
+    assert_close(sm, wm, STRICT_TOL, "bn save_mean")
+    assert_close(sv, wi, STRICT_TOL, "bn save_invstd")
+    assert_close(rm_d, wrm, STRICT_TOL, "bn running_mean")
+    if outer * inner > 1:
+        assert_close(rv_d, wrv, STRICT_TOL, "bn running_var")
+    gy = randn(*shape, seed=15)
+    dx, dg, db = ext.batchnormBackward(gy.cuda(), sm, sv, x.cuda(), dev(w), axes, True, 1e-5)
+    wdx, wdg, wdb = R.batchnorm_backward(gy.double(), x.double(), f64(w), axes, 1e-5)
+    assert_close(dx, wdx, STRICT_TOL, "bn dx")
+    assert_close(dg, wdg, STRICT_TOL, "bn dgamma")
+    assert_close(db, wdb, STRICT_TOL, "bn dbeta")
+    # inference path with the running statistics
+    yi, _, _ = ext.batchnorm(x.cuda(), dev(w), dev(b), rm.cuda(), rv.cuda(), axes, False, 0.0, 1e-5)
+    wyi, *_ = R.batchnorm(x.double(), f64(w), f64(b), rm.double(), rv.double(), axes, False, 0.0, 1e-5)
+    assert_close(yi, wyi, STRICT_TOL, "bn inference")
+
+
+def test_batchnorm_large_mean_is_well_conditioned(ext):
+    x = randn(8, 32, 14, 14, seed=16) * 0.05 + 100.0
+    y, sm, sv = ext.batchnorm(x.cuda(), None, None, None, None, [2], True, 0.0, 1e-5)
+    wy, wm, wi, _, _ = R.batchnorm(x.double(), None, None, None, None, [2], True, 0.0, 1e-5)
+    assert_close(sm, wm, 1e-6, "mean")
+    assert_close(sv, wi, 1e-3, "invstd")
+    assert_close(y, wy, 2e-3, "y")
+
+
+def test_batchnorm_errors(ext):
+    x = randn(2, 3, 4, 5, seed=1).cuda()
+    with pytest.raises(ValueError):
+        ext.batchnorm(x, None, None, None, None, [0, 2], True, 0.0, 1e-5)
+    with pytest.raises(ValueError):
+        ext.batchnorm(x, torch.ones(7, device="cuda"), None, None, None, [2], True, 0.0, 1e-5)
+    with pytest.raises(RuntimeError):
+        ext.batchnormBackward(x, None, None, x, None, [2], False, 1e-5)
+
+
+# ------------------------------------------------------------------- pool2d
+POOL_GEOS = [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1), (3, 2, 1, 2, 1, 0), (7, 7, 1, 1, 0, 0),
+             (2, 2, 1, 1, 0, 0)]
+
+
+@pytest.mark.parametrize("mode", [R.POOL_MAX, R.POOL_AVG_INCLUDE_PAD, R.POOL_AVG_EXCLUDE_PAD])
+@pytest.mark.parametrize("geo", POOL_GEOS)
+@pytest.mark.parametrize("with_payload", [True, False])
+def test_pool2d(ext, mode, geo, with_payload):
+    from flashlight_b200.extension import AutogradPayload
+    wx, wy, sx, sy, px, py = geo
+    x = randn(3, 5, 14, 13, seed=17)
+    payload = AutogradPayload() if with_payload else None
+    y = ext.pool2d(x.cuda(), wx, wy, sx, sy, px, py, mode, payload)
+    want = R.pool2d(x.double(), wx, wy, sx, sy, px, py, mode)
+    assert tuple(y.shape) == tuple(want.shape)
+    assert_close(y, want, 1e-6, "pool forward")
+    gy = randn(*want.shape, seed=18)
+    gx = ext.pool2dBackward(gy.cuda(), x.cuda(), y, wx, wy, sx, sy, px, py, mode, payload)
+    wgx = R.pool2d_backward(gy.double(), x.double(), wx, wy, sx, sy, px, py, mode)
+    assert_close(gx, wgx, 1e-5, "pool backward")
+    if mode == R.POOL_MAX and with_payload:
+        _, arg = R.pool2d_naive(x.numpy(), wx, wy, sx, sy, px, py, mode)
+        assert torch.equal(payload.data.argmax.cpu(), torch.from_numpy(arg))
+
+
+@pytest.mark.parametrize("geo", [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1)])
+def test_max_pool_ties_after_relu(ext, geo):
+    """Half the activations are exactly zero after ReLU: ties must resolve like the oracle."""
+    from flashlight_b200.extension import AutogradPayload
+    wx, wy, sx, sy, px, py = geo
+    x = torch.clamp_min(randn(2, 4, 12, 12, seed=19) - 0.8, 0)
+    x[0, 0] = 0
+    gy = randn(*R.pool2d(x, wx, wy, sx, sy, px, py, R.POOL_MAX).shape, seed=20)
+    want = R.pool2d_backward(gy.double(), x.double(), wx, wy, sx, sy, px, py, R.POOL_MAX)
+    for payload in (AutogradPayload(), None):
+        y = ext.pool2d(x.cuda(), wx, wy, sx, sy, px, py, R.POOL_MAX, payload)
+        gx = ext.pool2dBackward(gy.cuda(), x.cuda(), y, wx, wy, sx, sy, px, py, R.POOL_MAX, payload)
+        assert torch.equal(gx.cpu().double(), want)
+
+
+# ------------------------------------------------------------------- conv2d
+CONV_CASES = [
+    # N, C, H, W, Cout, kH, kW, sx, sy, px, py, dx, dy, groups
+    (7, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 1, 1, 1),    # shape of AutogradConv2DTest.cpp:21-74
+    (2, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 1, 1, 2),    # groups (AutogradConv2DTest.cpp:137-162)
+    (2, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 2, 1, 1),    # dilation dx=2 (AutogradConv2DTest.cpp:164-213)
+    (4, 1, 28, 28, 32, 5, 5, 1, 1, 2, 2, 1, 1, 1),  # MNIST conv1
+    (4, 32, 14, 14, 64, 5, 5, 1, 1, 2, 2, 1, 1, 1),  # MNIST conv2
+    (2, 3, 32, 32, 64, 7, 7, 2, 2, 3, 3, 1, 1, 1),  # ResNet stem (reduced image)
+    (2, 64, 14, 14, 256, 1, 1, 1, 1, 0, 0, 1, 1, 1),  # bottleneck expand
+    (2, 256, 14, 14, 64, 1, 1, 1, 1, 0, 0, 1, 1, 1),  # bottleneck reduce
+    (2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1),  # bottleneck 3x3
+    (2, 128, 14, 14, 128, 3, 3, 2, 2, 1, 1, 1, 1, 1),  # stride-2 3x3
+    (2, 256, 14, 14, 512, 1, 1, 2, 2, 0, 0, 1, 1, 1),  # stride-2 1x1 downsample
+    (2, 512, 7, 7, 2048, 1, 1, 1, 1, 0, 0, 1, 1, 1),  # 7x7 plane (49 pixels)
+    (2, 80, 1, 100, 96, 1, 13, 1, 1, 6, 0, 1, 1, 1),  # conv-ASR time convolution (kW=13, kH=1)
+    (1, 5, 6, 7, 3, 2, 3, 3, 2, 0, 1, 1, 2, 1),      # ragged everything
+]
+
+
+@pytest.mark.parametrize("case", CONV_CASES)
+def test_conv2d_strict(ext, case):
+    N, Cin, H, W, Cout, kH, kW, sx, sy, px, py, dx, dy, groups = case
+    x = randn(N, Cin, H, W, seed=21)
+    w = randn(Cout, Cin // groups, kH, kW, seed=22) * (1.0 / (Cin // groups * kH * kW) ** 0.5)
+    b = randn(Cout, seed=23)
+    args = (sx, sy, px, py, dx, dy, groups)
+    y = ext.conv2d(x.cuda(), w.cuda(), b.cuda(), *args)
+    want = R.conv2d(x.double(), w.double(), b.double(), *args)
+    assert tuple(y.shape) == tuple(want.shape)
+    assert_close(y, want, STRICT_TOL, "conv forward")
+    y_nb = ext.conv2d(x.cuda(), w.cuda(), None, *args)
+    assert_close(y_nb, R.conv2d(x.double(), w.double(), None, *args), STRICT_TOL, "conv forward, no bias")
+    gy = randn(*want.shape, seed=24)
+    gx = ext.conv2dBackwardData(gy.cuda(), x.cuda(), w.cuda(), *args)
+    assert_close(gx, R.conv2d_backward_data(gy.double(), x.shape, w.double(), *args), STRICT_TOL,
+                 "conv backward data")
+    gw, gb = ext.conv2dBackwardFilterBias(gy.cuda(), x.cuda(), w.cuda(), b.cuda(), *args)
+    wgw, wgb = R.conv2d_backward_filter_bias(gy.double(), x.double(), w.shape, True, *args)
+    assert_close(gw, wgw, STRICT_TOL, "conv backward filter")
+    assert_close(gb, wgb, STRICT_TOL, "conv backward bias")
+    gw2, gb2 = ext.conv2dBackwardFilterBias(gy.cuda(), x.cuda(), w.cuda(), None, *args)
+    assert gb2 is None
+    assert torch.equal(gw2, gw), "filter gradient must not depend on the bias argument (deterministic)"
+
+
+def test_conv2d_backward_filter_split_k_is_deterministic(ext):
+    """Large K (batch * pixels) takes the split-K path; two runs must agree bit for bit."""
+    x = randn(16, 16, 28, 28, seed=25)
+    gy = randn(16, 32, 28, 28, seed=26)
+    w = randn(32, 16, 3, 3, seed=27)
+    args = (1, 1, 1, 1, 1, 1, 1)
+    a, _ = ext.conv2dBackwardFilterBias(gy.cuda(), x.cuda(), w.cuda(), None, *args)
+    b, _ = ext.conv2dBackwardFilterBias(gy.cuda(), x.cuda(), w.cuda(), None, *args)
+    assert torch.equal(a, b)
+    wgw, _ = R.conv2d_backward_filter_bias(gy.double(), x.double(), w.shape, False, *args)
+    assert_close(a, wgw, STRICT_TOL, "split-K filter gradient")
+
+
+# ------------------------------------------------------------------- linear
+@pytest.mark.parametrize("dims", [(10, 1024, 64), (1024, 3136, 64), (30, 1024, 200), (1000, 2048, 16),
+                                  (7, 5, 3), (768, 768, 96), (130, 70, 257)])
+def test_linear(fx, dims):
+    from flashlight_b200 import _lib as L
+    O, I, cols = dims
+    x = randn(cols, I, seed=28)
+    w = randn(I, O, seed=29) * (1.0 / I ** 0.5)
+    b = randn(O, seed=30)
+    y = fx.linear(x.cuda(), w.cuda(), b.cuda(), math_mode=L.MATH_STRICT_F32)
+    assert_close(y, R.linear(x.double(), w.double(), b.double()), STRICT_TOL, "linear forward")
+    gy = randn(cols, O, seed=31)
+    gx, gw, gb = fx.linear_backward(x.cuda(), w.cuda(), gy.cuda(), True, math_mode=L.MATH_STRICT_F32)
+    wx, ww, wb = R.linear_backward(x.double(), w.double(), gy.double(), True)
+    assert_close(gx, wx, STRICT_TOL, "linear dx")
+    assert_close(gw, ww, STRICT_TOL, "linear dW")
+    assert_close(gb, wb, STRICT_TOL, "linear db")
+
+
+def test_matmul_strided_batched_alpha_beta(fx):
+    from flashlight_b200 import _lib as L
+    a = randn(3, 37, 53, seed=32)   # batch, m, k
+    b = randn(3, 29, 53, seed=33)   # batch, n, k  (B read transposed)
+    c0 = randn(3, 37, 29, seed=34)
+    c = c0.clone().cuda()
+    fx.matmul(a.cuda(), b.cuda(), c, m=37, n=29, k=53, a_strides=(53, 1), b_strides=(1, 53),
+              c_strides=(29, 1), batch=3, batch_strides=(37 * 53, 29 * 53, 37 * 29), alpha=0.5,
+              beta=2.0, math_mode=L.MATH_STRICT_F32)
+    want = 0.5 * a.double() @ b.double().transpose(1, 2) + 2.0 * c0.double()
+    assert_close(c, want, STRICT_TOL, "matmul")
+
+
+# ------------------------------------------------------- logSoftmax and CE
+@pytest.mark.parametrize("C_,X", [(10, 64), (30, 1000), (1000, 37), (32000, 9), (1, 5), (1025, 3)])
+def test_log_softmax_and_cross_entropy(fx, C_, X):
+    x = randn(X, C_, seed=35) * 3
+    y = fx.log_softmax(x.cuda())
+    wy = R.log_softmax(x.double())
+    assert_close(y, wy, STRICT_TOL, "logSoftmax")
+    gy = randn(X, C_, seed=36)
+    assert_close(fx.log_softmax_backward(y, gy.cuda()), R.log_softmax_backward(wy, gy.double()),
+                 STRICT_TOL, "logSoftmax backward")
+    t = randint(0, C_, X, seed=37)
+    if X > 2:
+        t[1] = -1  # ignored
+    for red in (R.REDUCE_NONE, R.REDUCE_MEAN, R.REDUCE_SUM):
+        loss, state = fx.categorical_cross_entropy(y, t.cuda(), red, -1)
+        fx.check_targets(state)
+        wl, denom = R.categorical_cross_entropy(wy, t, red, -1)
+        assert_close(loss, wl, STRICT_TOL, f"CE loss red={red}")
+        assert int(state.count[0].item()) == denom
+        gl = randn(*wl.shape, seed=38).abs() + 0.1
+        g = fx.categorical_cross_entropy_backward(gl.cuda(), state, C_, y)
+        wg = R.categorical_cross_entropy_backward(gl.double(), wy.shape, t, red, -1, torch.float64)
+        assert_close(g, wg, 1e-6, f"CE backward red={red}")
+        fused = fx.log_softmax_cross_entropy_backward(y, gl.cuda(), state)
+        assert_close(fused, R.log_softmax_backward(wy, wg), STRICT_TOL, f"fused backward red={red}")
+
+
+def test_cross_entropy_rejects_out_of_range_target(fx):
+    y = fx.log_softmax(randn(4, 5, seed=39).cuda())
+    t = torch.tensor([0, 1, 5, 2], dtype=torch.int32).cuda()
+    _, state = fx.categorical_cross_entropy(y, t)
+    with pytest.raises(ValueError, match="out of valid range"):
+        fx.check_targets(state)
+
+
+# ---------------------------------------------------------------------- rnn
+RNN_CASES = [
+    # I, H, L, B, T, bidirectional
+    (2, 2, 2, 2, 3, True),     # flashlight/fl/test/autograd/AutogradRnnTest.cpp:24-157
+    (4, 3, 2, 5, 6, False),    # flashlight/fl/test/nn/ModuleTest.cpp:436-480
+    (5, 16, 2, 3, 7, True),
+    (80, 64, 3, 4, 9, True),   # the biLSTM workload, scaled down
+]
+
+
+@pytest.mark.parametrize("mode", [R.RNN_RELU, R.RNN_TANH, R.RNN_LSTM, R.RNN_GRU])
+@pytest.mark.parametrize("case", RNN_CASES)
+@pytest.mark.parametrize("with_state", [False, True])
+def test_rnn_forward_backward(ext, mode, case, with_state):
+    from flashlight_b200.extension import AutogradPayload, RNNGradData
+    I, H, L_, B, T, bi = case
+    dirs = 2 if bi else 1
+    n = R.rnn_num_params(I, H, L_, mode, bi)
+    w = randn(n, seed=40) * (1.0 / H ** 0.5)
+    x = randn(T, B, I, seed=41)
+    hx = randn(L_ * dirs, B, H, seed=42) * 0.5 if with_state else None
+    cx = randn(L_ * dirs, B, H, seed=43) * 0.5 if (with_state and mode == R.RNN_LSTM) else None
+    payload = AutogradPayload()
+    y, hy, cy = ext.rnn(x.cuda(), dev(hx), dev(cx), w.cuda(), H, L_, mode, bi, 0.0, payload)
+    wy, why, wcy = R.rnn(x.double(), f64(hx), f64(cx), w.double(), H, L_, mode, bi)
+    assert_close(y, wy, STRICT_TOL, "rnn y")
+    assert_close(hy, why, STRICT_TOL, "rnn hy")
+    if mode == R.RNN_LSTM:
+        assert_close(cy, wcy, STRICT_TOL, "rnn cy")
+    gy = randn(T, B, H * dirs, seed=44)
+    ghy = randn(L_ * dirs, B, H, seed=45) if with_state else None
+    gcy = randn(L_ * dirs, B, H, seed=46) if (with_state and mode == R.RNN_LSTM) else None
+    dx, dhx, dcx, dw = ext.rnnBackward(x.cuda(), dev(hx), dev(cx), w.cuda(),
+                                       RNNGradData(dev(gy), dev(ghy), dev(gcy)), y, L_, H, mode, bi,
+                                       0.0, payload)
+    wdx, wdhx, wdcx, wdw = R.rnn_backward(x.double(), f64(hx), f64(cx), w.double(), H, L_, mode, bi,
+                                          gy.double(), f64(ghy), f64(gcy))
+    assert_close(dx, wdx, STRICT_TOL, "rnn dx")
+    assert_close(dw, wdw, STRICT_TOL, "rnn dw")
+    if with_state:
+        assert_close(dhx, wdhx, STRICT_TOL, "rnn dhx")
+        if mode == R.RNN_LSTM:
+            assert_close(dcx, wdcx, STRICT_TOL, "rnn dcx")
+
+
+def test_rnn_backward_without_output_gradient(ext):
+    """dy absent counts as zeros (backend/cudnn/RNN.cpp:269-272): only dhy drives the gradient."""
+    from flashlight_b200.extension import AutogradPayload, RNNGradData
+    I, H, L_, B, T = 3, 4, 1, 2, 4
+    w = randn(R.rnn_num_params(I, H, L_, R.RNN_LSTM, False), seed=47) * 0.5
+    x = randn(T, B, I, seed=48)
+    payload = AutogradPayload()
+    y, hy, cy = ext.rnn(x.cuda(), None, None, w.cuda(), H, L_, R.RNN_LSTM, False, 0.0, payload)
+    ghy = randn(L_, B, H, seed=49)
+    dx, _, _, dw = ext.rnnBackward(x.cuda(), None, None, w.cuda(), RNNGradData(None, ghy.cuda(), None),
+                                   y, L_, H, R.RNN_LSTM, False, 0.0, payload)
+    wdx, _, _, wdw = R.rnn_backward(x.double(), None, None, w.double(), H, L_, R.RNN_LSTM, False, None,
+                                    ghy.double(), None)
+    assert_close(dx, wdx, STRICT_TOL, "dx")
+    assert_close(dw, wdw, STRICT_TOL, "dw")
+    with pytest.raises(ValueError):
+        ext.rnnBackward(x.cuda(), None, None, w.cuda(), RNNGradData(), y, L_, H, R.RNN_LSTM, False, 0.0,
+                        None)
