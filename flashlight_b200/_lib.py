@@ -58,6 +58,8 @@ SIGNATURES = {
     "flb200_last_error": (C.c_char_p, []),
     "flb200_kernel_launches": (C.c_longlong, []),
     "flb200_has_tensor_core_path": (C.c_int, []),
+    "flb200_tc_kernel_launches": (C.c_longlong, []),
+    "flb200_tc_poll_status": (C.c_int, [vp]),
     "flb200_conv2d_output_dims": (C.c_int, [P(Conv2dDesc), P(i32), P(i32)]),
     "flb200_conv2d_workspace_bytes": (sz, [P(Conv2dDesc), C.c_int]),
     "flb200_conv2d_forward": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, vp]),

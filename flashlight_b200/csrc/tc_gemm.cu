@@ -1,16 +1,320 @@
-// Placeholder translation unit for the tcgen05 contraction: reports "not covered"
-// for every shape, so TF32 mode currently runs the fp32 kernel.
+// Host side of the tcgen05 contraction: turns a strided matmul description into
+// TMA tensor maps + operand plans, picks the tile width and the split-K factor,
+// and launches tc_gemm_kernel (tc_core.cuh).  Used by flb200_matmul / the linear
+// gradients in TF32 mode, by the convolution paths in tc_conv.cu and by rnn.cu.
 #include "tc_gemm.cuh"
 
+#include <mutex>
+
+#include "tc_core.cuh"
+
 namespace flb200 {
-bool tc_gemm_supported(const flb200_matmul_desc*, const void*, const void*, const void*) {
-  return false;
+namespace tc {
+
+// ------------------------------------------------------- driver entry point
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    (void)cudaGetLastError();
+  });
+  return fn;
 }
-size_t tc_gemm_workspace_bytes(const flb200_matmul_desc*) { return 0; }
-int tc_gemm_run(const flb200_matmul_desc*, const void*, const void*, void*, void*, size_t,
-                cudaStream_t) {
-  return fail(FLB200_UNSUPPORTED, "tc_gemm: not built");
+
+// fp32 tensor map; dims[0] is the contiguous dimension, strides_bytes[i] belongs to
+// dims[i+1], box[0] must be 32 elements (128 bytes).  K-major operand tiles use the
+// 128-byte swizzle of 16-byte chunks, MN-major ones the swizzle of 32-byte chunks.
+int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box, bool mn_major) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return fail(FLB200_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
+  cuuint64_t gd[5];
+  cuuint64_t gs[4];
+  cuuint32_t bx[5], es[5];
+  for (int i = 0; i < rank; ++i) {
+    gd[i] = dims[i];
+    bx[i] = box[i];
+    es[i] = 1;
+    if (i > 0) gs[i - 1] = strides_bytes[i - 1];
+  }
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base),
+                  gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(FLB200_INVALID_ARG, "cuTensorMapEncodeTiled failed with code %d (rank %d)", (int)r,
+                rank);
+  return FLB200_OK;
 }
+
+std::atomic<long long> g_tc_launches{0};
+
+// ------------------------------------------------------------ status flag
+__device__ int g_tc_status = 0;
+
+static int* status_ptr() {
+  // one address per device, looked up with that device current
+  static int* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!ptrs[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_tc_status) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    ptrs[dev] = static_cast<int*>(p);
+  }
+  return ptrs[dev];
+}
+
+// ---------------------------------------------------------------- launch
+template <int BN, int STAGES>
+static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const KernelArgs& args,
+                      dim3 grid, cudaStream_t st) {
+  using SL = SmemLayout<BN, STAGES>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_gemm_kernel<BN, STAGES>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SL::kTotal));
+    configured[dev] = true;
+  }
+  tc_gemm_kernel<BN, STAGES><<<grid, kThreads, SL::kTotal, st>>>(ma, mb, args);
+  FLB200_AFTER_LAUNCH("tc_gemm");
+  g_tc_launches.fetch_add(1, std::memory_order_relaxed);
+  return FLB200_OK;
+}
+
+int pick_bn(long long N) {
+  if (N <= 32) return 32;
+  if (N <= 64) return 64;
+  return 128;
+}
+
+Launch plan_launch(long long M, long long N, long long k_iters, long long Z) {
+  Launch L;
+  L.bn = pick_bn(N);
+  const long long tiles = ((M + kBM - 1) / kBM) * ((N + L.bn - 1) / L.bn) * Z;
+  const long long target = 2LL * device_info().sm_count;
+  long long splits = 1;
+  if (tiles < target && k_iters >= 16) {
+    splits = (target + tiles - 1) / tiles;
+    const long long max_by_k = k_iters / 8;  // at least 8 stage iterations (256 k) per split
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 256) splits = 256;
+    if (Z * splits > 65535) splits = 65535 / Z;
+    if (splits < 1) splits = 1;
+  }
+  long long ips = (k_iters + splits - 1) / splits;
+  if (ips < 1) ips = 1;
+  splits = (k_iters + ips - 1) / ips;
+  if (splits < 1) splits = 1;
+  L.splits = (int)splits;
+  L.iters_per_split = (int)ips;
+  L.workspace_bytes = splits > 1 ? (size_t)(Z * splits * M * N) * sizeof(float) : 0;
+  return L;
+}
+
+int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, const OperandPlan& pb,
+        const EpiloguePlan& ep, long long M, long long N, long long k_iters, long long Z, void* ws,
+        size_t ws_bytes, cudaStream_t st) {
+  Launch L = plan_launch(M, N, k_iters, Z);
+  if (L.splits > 1 && (!ws || ws_bytes < L.workspace_bytes)) {
+    L.splits = 1;
+    L.iters_per_split = (int)k_iters;
+  }
+  KernelArgs args;
+  args.a = pa;
+  args.b = pb;
+  args.ep = ep;
+  args.M = (int)M;
+  args.N = (int)N;
+  args.k_iters = (int)k_iters;
+  args.splits = L.splits;
+  args.iters_per_split = L.iters_per_split;
+  args.partial = static_cast<float*>(ws);
+  args.status = status_ptr();
+  dim3 grid((unsigned)((N + L.bn - 1) / L.bn), (unsigned)((M + kBM - 1) / kBM),
+            (unsigned)(Z * L.splits));
+  FLB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "tc_gemm: grid out of range");
+  int rc;
+  if (L.bn == 32) rc = launch_one<32, 4>(ma, mb, args, grid, st);
+  else if (L.bn == 64) rc = launch_one<64, 4>(ma, mb, args, grid, st);
+  else rc = launch_one<128, 3>(ma, mb, args, grid, st);
+  if (rc) return rc;
+  if (L.splits > 1) {
+    const int rgrid = grid_for(M * N * Z, 256);
+    tc_splitk_reduce_kernel<<<rgrid, 256, 0, st>>>(args.partial, ep, (int)M, (int)N, (int)Z,
+                                                   L.splits);
+    FLB200_AFTER_LAUNCH("tc_splitk_reduce");
+  }
+  return FLB200_OK;
+}
+
+}  // namespace tc
+
+// ----------------------------------------------------- strided matmul entry
+namespace {
+
+struct Side {
+  bool ok, mn_major;
+  long long ld;  // stride (elements) of the non-contiguous dimension
+};
+
+// op(r, k) at base[r*row + k*col]: decide the major and the leading dimension.
+Side classify(long long row, long long col, long long rows, long long K) {
+  Side s{false, false, 0};
+  if (col == 1 && (row % 4 == 0 || rows == 1) && row >= 1) {
+    s = Side{true, false, rows == 1 ? (K + 3) / 4 * 4 : row};
+  } else if (row == 1 && (col % 4 == 0 || K == 1) && col >= 1) {
+    s = Side{true, true, K == 1 ? (rows + 3) / 4 * 4 : col};
+  }
+  return s;
+}
+
+struct Prepared {
+  bool ok = false;
+  bool swap = false;
+  Side a, b;
+};
+
+Prepared prepare(const flb200_matmul_desc* d, const void* a, const void* b, const void* c) {
+  Prepared p;
+  if (d->dtype != FLB200_F32 || d->m < 1 || d->n < 1 || d->k < 1) return p;
+  if (!aligned16(a) || !aligned16(b) || !c) return p;
+  if (d->batch > 1 && (d->a_batch % 4 != 0 || d->b_batch % 4 != 0)) return p;
+  // too little work to pay for a tensor-core launch: leave it to the fp32 kernel
+  if ((double)d->m * (double)d->n * (double)d->k < 262144.0) return p;
+  p.a = classify(d->a_row, d->a_col, d->m, d->k);
+  // B(k, n): "row" of the operand is n with stride b_col; k stride is b_row
+  p.b = classify(d->b_col, d->b_row, d->n, d->k);
+  if (!p.a.ok || !p.b.ok) return p;
+  p.swap = d->m < 64 && d->n > d->m;  // put the long extent on the 128-row side of the MMA
+  p.ok = true;
+  return p;
+}
+
+// Tensor map + plan of one operand: rows x K matrix (+ batch).
+int build_operand(const Side& s, const void* base, long long rows, long long K, long long batch,
+                  long long batch_stride, int tile_rows, CUtensorMap* map, tc::OperandPlan* plan) {
+  uint64_t dims[3], strides[2];
+  uint32_t box[3];
+  *plan = tc::OperandPlan{};
+  plan->k_inner = 0;
+  plan->k2_dim = -1;
+  if (s.mn_major) {
+    dims[0] = (uint64_t)rows; dims[1] = (uint64_t)K;
+    box[0] = 32; box[1] = tc::kBK;
+    plan->mn_major = 1; plan->mn_dim = 0; plan->k_dim = 1;
+  } else {
+    dims[0] = (uint64_t)K; dims[1] = (uint64_t)rows;
+    box[0] = tc::kBK; box[1] = (uint32_t)tile_rows;
+    plan->mn_major = 0; plan->mn_dim = 1; plan->k_dim = 0;
+  }
+  strides[0] = (uint64_t)s.ld * 4;
+  int rank = 2;
+  plan->z_dim = -1;
+  if (batch > 1) {
+    dims[2] = (uint64_t)batch;
+    strides[1] = (uint64_t)batch_stride * 4;
+    box[2] = 1;
+    rank = 3;
+    plan->z_dim = 2;
+  }
+  plan->rank = rank;
+  return tc::make_tensor_map(map, base, rank, dims, strides, box, s.mn_major);
+}
+
+}  // namespace
+
+bool tc_gemm_supported(const flb200_matmul_desc* d, const void* a, const void* b, const void* c) {
+  if (device_info().cc_major != 10) return false;
+  if (!tc::encode_tiled_fn()) return false;
+  return prepare(d, a, b, c).ok;
+}
+
+size_t tc_gemm_workspace_bytes(const flb200_matmul_desc* d) {
+  if (!d || d->m < 1 || d->n < 1 || d->k < 1) return 0;
+  const long long k_iters = (d->k + tc::kBK - 1) / tc::kBK;
+  // the swapped orientation has the same M*N; take the larger split count of both
+  const size_t w1 = tc::plan_launch(d->m, d->n, k_iters, d->batch).workspace_bytes;
+  const size_t w2 = tc::plan_launch(d->n, d->m, k_iters, d->batch).workspace_bytes;
+  return w1 > w2 ? w1 : w2;
+}
+
+int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void* c, void* ws,
+                size_t ws_bytes, cudaStream_t st) {
+  const Prepared p = prepare(d, a, b, c);
+  if (!p.ok) return fail(FLB200_UNSUPPORTED, "tc_gemm: layout not covered");
+  const long long k_iters = (d->k + tc::kBK - 1) / tc::kBK;
+  CUtensorMap ma, mb;
+  tc::OperandPlan pa, pb;
+  tc::EpiloguePlan ep{};
+  ep.out = static_cast<float*>(c);
+  ep.alpha = d->alpha;
+  ep.beta = d->beta;
+  ep.z_stride = d->c_batch;
+  long long M, N;
+  if (!p.swap) {
+    M = d->m; N = d->n;
+    const int bn = tc::pick_bn(N);
+    if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch, tc::kBM, &ma, &pa)) return rc;
+    if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch, bn, &mb, &pb)) return rc;
+    ep.m_stride = d->c_row;
+    ep.n_stride = d->c_col;
+  } else {
+    // C^T = B^T A^T: the kernel's rows are the caller's columns
+    M = d->n; N = d->m;
+    const int bn = tc::pick_bn(N);
+    if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch, tc::kBM, &ma, &pa)) return rc;
+    if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch, bn, &mb, &pb)) return rc;
+    ep.m_stride = d->c_col;
+    ep.n_stride = d->c_row;
+  }
+  return tc::run(ma, mb, pa, pb, ep, M, N, k_iters, d->batch, ws, ws_bytes, st);
+}
+
 }  // namespace flb200
 
-extern "C" int flb200_has_tensor_core_path(void) { return 0; }
+extern "C" {
+
+int flb200_has_tensor_core_path(void) {
+  return flb200::device_info().cc_major == 10 && flb200::tc::encode_tiled_fn() != nullptr ? 1 : 0;
+}
+
+long long flb200_tc_kernel_launches(void) {
+  return flb200::tc::g_tc_launches.load(std::memory_order_relaxed);
+}
+
+// Reads (and clears) the device flag that a bounded wait inside a tensor-core kernel raises when
+// it runs out.  Synchronises the stream.  Returns FLB200_TIMEOUT if the flag was set.
+int flb200_tc_poll_status(void* stream) {
+  using namespace flb200;
+  int* p = tc::status_ptr();
+  if (!p) return FLB200_OK;
+  int v = 0;
+  cudaStream_t st = as_stream(stream);
+  FLB200_CUDA_CHECK(cudaMemcpyAsync(&v, p, sizeof(int), cudaMemcpyDeviceToHost, st));
+  FLB200_CUDA_CHECK(cudaStreamSynchronize(st));
+  if (v != 0) {
+    FLB200_CUDA_CHECK(cudaMemsetAsync(p, 0, sizeof(int), st));
+    return fail(FLB200_TIMEOUT, "a tensor-core kernel gave up waiting (stage %d)", v);
+  }
+  return FLB200_OK;
+}
+
+}  // extern "C"

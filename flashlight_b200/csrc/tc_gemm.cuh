@@ -1,5 +1,9 @@
-// Interface of the tcgen05 (tensor-core) contraction used by TF32 mode.
+// Host interface of the tcgen05 (tensor-core) TF32 contraction: the plan structs that
+// describe how operands are fetched by TMA and how the accumulator is stored, and the
+// entry points used by matmul, the convolution paths and the RNN.
 #pragma once
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace flb200 {
@@ -10,4 +14,64 @@ size_t tc_gemm_workspace_bytes(const flb200_matmul_desc* d);
 int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void* c, void* ws,
                 size_t ws_bytes, cudaStream_t st);
 
+namespace tc {
+
+constexpr int kBM = 128;  // rows of one output tile (UMMA M)
+constexpr int kBK = 32;   // fp32 elements per pipeline stage along K (= 128 bytes)
+
+// How one operand's TMA coordinates advance.  coord[d] for dimension d of the
+// tensor map is  base[d] + mn * (d == mn_dim) + k_lo * (d == k_dim)
+//                + k_hi * (d == k2_dim) + z * (d == z_dim)
+// where k = k_hi * k_inner + k_lo walks the contraction (k_lo in elements).
+struct OperandPlan {
+  int rank;      // tensor-map rank, 2..4
+  int mn_major;  // 1: m (or n) is the contiguous dimension
+  int mn_dim, k_dim, k2_dim, z_dim;  // -1 = unused
+  int k_inner;   // stage iterations per k2 step (ceil(extent of k_dim / kBK)); 0 = single level
+  int base[4];
+};
+
+struct EpiloguePlan {
+  float* out;
+  // offset(m) = (m / m_div) * m_outer + (m % m_div) * m_stride   (m_div == 0: m * m_stride)
+  long long m_stride, m_outer, n_stride, n_outer, z_stride;
+  int m_div, n_div;
+  const float* bias_m;  // added per row (may be null)
+  const float* bias_n;  // added per column (may be null)
+  float alpha, beta;
+};
+
+struct KernelArgs {
+  OperandPlan a, b;
+  EpiloguePlan ep;
+  int M, N;
+  int k_iters;          // total stage iterations over the whole contraction
+  int splits;           // gridDim.z = batch * splits
+  int iters_per_split;
+  float* partial;       // split-K scratch: [z*splits + s][M][N]
+  int* status;          // device flag raised on a bounded-wait timeout
+};
+
+struct Launch {
+  int bn, splits, iters_per_split;
+  size_t workspace_bytes;
+};
+
+int pick_bn(long long N);
+// Tile width, split-K factor and scratch size for an M x N output over k_iters stages, Z batches.
+Launch plan_launch(long long M, long long N, long long k_iters, long long Z);
+
+// fp32 tensor map; dims[0] is the contiguous dimension, strides_bytes[i] belongs to
+// dims[i+1]; box[0] must be 32 elements.  mn_major selects the 32-byte-chunk swizzle that
+// TF32 operands with a contiguous m / n index need.
+int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                    const uint64_t* strides_bytes, const uint32_t* box, bool mn_major);
+
+// Launches the contraction (and the split-K reduction when the plan splits K).  Without
+// enough scratch the contraction runs unsplit.
+int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, const OperandPlan& pb,
+        const EpiloguePlan& ep, long long M, long long N, long long k_iters, long long Z, void* ws,
+        size_t ws_bytes, cudaStream_t st);
+
+}  // namespace tc
 }  // namespace flb200

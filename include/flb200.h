@@ -56,8 +56,15 @@ const char* flb200_status_string(int status);
 const char* flb200_last_error(void);
 /* Number of kernels this library has launched from the calling process so far. */
 long long flb200_kernel_launches(void);
-/* 1 when the library was built with the tcgen05 kernels and the current device is sm_100. */
+/* 1 when the tcgen05 kernels can run: the current device is sm_100 and the driver exports
+ * cuTensorMapEncodeTiled. */
 int flb200_has_tensor_core_path(void);
+/* Number of tcgen05 contraction kernels launched so far (subset of flb200_kernel_launches). */
+long long flb200_tc_kernel_launches(void);
+/* Every wait inside a tensor-core kernel is bounded; one that runs out raises a device flag
+ * and the kernel drains and returns.  This call synchronises the stream, reads and clears
+ * the flag and returns FLB200_TIMEOUT if it was set. */
+int flb200_tc_poll_status(void* stream);
 
 /* ------------------------------------------------- conv2d (a3, a4, a8) */
 /* Geometry of one fl::conv2d call.  x [W,H,C,N], w [kW,kH,C/groups,Cout],

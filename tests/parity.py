@@ -39,3 +39,27 @@ def randn(*shape, seed=0, dtype=torch.float32):
 def randint(lo, hi, *shape, seed=0):
     g = torch.Generator().manual_seed(seed)
     return torch.randint(lo, hi, shape, generator=g, dtype=torch.int32)
+
+
+# TF32 mode: operands are read with a 10-bit mantissa, so single products carry ~1e-3
+# relative error and entries that are small through cancellation cannot be matched
+# element-wise; the bound is on the error relative to the tensor's largest magnitude.
+TF32_SCALED_TOL = 2e-3
+
+
+def scaled_err(got, want) -> float:
+    """max_i |got_i - want_i| / max_i |want_i|."""
+    g = torch.as_tensor(got).detach().double().cpu().reshape(-1)
+    w = torch.as_tensor(want).detach().double().cpu().reshape(-1)
+    assert g.shape == w.shape, (g.shape, w.shape)
+    if w.numel() == 0:
+        return 0.0
+    if not bool(torch.isfinite(g).all()):
+        return float("inf")
+    scale = float(w.abs().max()) or 1.0
+    return float((g - w).abs().max()) / scale
+
+
+def assert_close_scaled(got, want, tol, what=""):
+    e = scaled_err(got, want)
+    assert e <= tol, f"{what}: error relative to the tensor scale {e:.3e} > {tol:.1e}"

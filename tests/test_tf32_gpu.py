@@ -1,0 +1,119 @@
+"""TF32 (tcgen05 tensor-core) mode against the fp64 oracle.  Bound: relative error
+relative to the tensor scale (tests/parity.py scaled_err) <= 2e-3 — fp32 operands are read with a 10-bit mantissa (2^-11 relative
+rounding each) and accumulated in fp32; strict mode keeps the 1e-4 bound."""
+import pytest
+import torch
+
+from oracle import flref as R
+from tests.parity import TF32_SCALED_TOL, assert_close, assert_close_scaled, randn
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def L():
+    from flashlight_b200 import _lib
+    if not _lib.lib.flb200_has_tensor_core_path():
+        pytest.fail("tensor-core path unavailable on this device: TF32 mode cannot be tested")
+    return _lib
+
+
+@pytest.fixture(scope="module")
+def fx():
+    from flashlight_b200 import functions
+    return functions
+
+
+def tc_delta(L, fn):
+    before = L.lib.flb200_tc_kernel_launches()
+    out = fn()
+    torch.cuda.synchronize()
+    L.check(L.lib.flb200_tc_poll_status(torch.cuda.current_stream().cuda_stream))
+    return out, L.lib.flb200_tc_kernel_launches() - before
+
+
+# (m, n, k): full tiles, ragged tiles, K tails, skinny shapes that take the swapped orientation
+MNK = [(128, 128, 32), (128, 128, 256), (256, 384, 512), (200, 136, 100), (129, 65, 33),
+       (1000, 64, 72), (32, 4096, 1024), (4096, 32, 1024), (512, 520, 4100), (64, 64, 8192)]
+
+
+@pytest.mark.parametrize("mnk", MNK)
+@pytest.mark.parametrize("a_mn_major", [False, True])
+@pytest.mark.parametrize("b_mn_major", [False, True])
+def test_matmul_tf32_all_majors(L, fx, mnk, a_mn_major, b_mn_major):
+    m, n, k = mnk
+    pad = lambda v: (v + 3) // 4 * 4  # leading dimensions must be multiples of 16 bytes
+    if a_mn_major:
+        a_store = randn(k, pad(m), seed=1)          # A(i,kk) at kk*ld + i
+        a_view, a_str = a_store[:, :m].t(), (1, pad(m))
+    else:
+        a_store = randn(m, pad(k), seed=1)          # A(i,kk) at i*ld + kk
+        a_view, a_str = a_store[:, :k], (pad(k), 1)
+    if b_mn_major:
+        b_store = randn(k, pad(n), seed=2)          # B(kk,j) at kk*ld + j
+        b_view, b_str = b_store[:, :n], (pad(n), 1)
+    else:
+        b_store = randn(n, pad(k), seed=2)          # B(kk,j) at j*ld + kk
+        b_view, b_str = b_store[:, :k].t(), (1, pad(k))
+    want = a_view.double() @ b_view.double()
+    c, launched = tc_delta(L, lambda: fx.matmul(a_store.cuda(), b_store.cuda(), m=m, n=n, k=k,
+                                                a_strides=a_str, b_strides=b_str,
+                                                math_mode=L.MATH_TF32))
+    assert launched >= 1, "TF32 matmul did not run on the tensor-core kernel"
+    assert_close_scaled(c, want, TF32_SCALED_TOL, f"matmul {mnk} a_mn={a_mn_major} b_mn={b_mn_major}")
+
+
+def test_matmul_tf32_batched_alpha_beta(L, fx):
+    a = randn(3, 160, 96, seed=3)
+    b = randn(3, 96, 200, seed=4)
+    c0 = randn(3, 160, 200, seed=5)
+    c = c0.clone().cuda()
+    _, launched = tc_delta(L, lambda: fx.matmul(
+        a.cuda(), b.cuda(), c, m=160, n=200, k=96, a_strides=(96, 1), b_strides=(200, 1),
+        c_strides=(200, 1), batch=3, batch_strides=(160 * 96, 96 * 200, 160 * 200), alpha=0.5,
+        beta=2.0, math_mode=L.MATH_TF32))
+    assert launched >= 1
+    assert_close_scaled(c, 0.5 * a.double() @ b.double() + 2.0 * c0.double(), TF32_SCALED_TOL, "batched matmul")
+
+
+def test_matmul_tf32_unaligned_layout_falls_back_to_fp32_kernel(L, fx):
+    """A leading dimension that is not a multiple of 16 bytes cannot be described to TMA: the
+    call still succeeds (fp32 kernel) and meets the strict bound."""
+    a = randn(70, 33, seed=6)
+    b = randn(33, 50, seed=7)
+    c, launched = tc_delta(L, lambda: fx.matmul(a.cuda(), b.cuda(), m=70, n=50, k=33,
+                                                a_strides=(33, 1), b_strides=(50, 1),
+                                                math_mode=L.MATH_TF32))
+    assert launched == 0
+    assert_close(c, a.double() @ b.double(), 1e-4, "fallback matmul")
+
+
+@pytest.mark.parametrize("dims", [(1024, 3136, 64), (1000, 2048, 256), (768, 3072, 512),
+                                  (32000, 768, 128), (30, 1024, 2000)])
+def test_linear_tf32(L, fx, dims):
+    O, I, cols = dims
+    x = randn(cols, I, seed=8)
+    w = randn(I, O, seed=9) * (1.0 / I ** 0.5)
+    b = randn(O, seed=10)
+    y, launched = tc_delta(L, lambda: fx.linear(x.cuda(), w.cuda(), b.cuda(), math_mode=L.MATH_TF32))
+    assert_close_scaled(y, R.linear(x.double(), w.double(), b.double()), TF32_SCALED_TOL, "linear forward")
+    gy = randn(cols, O, seed=11)
+    (gx, gw, gb), launched2 = tc_delta(L, lambda: fx.linear_backward(
+        x.cuda(), w.cuda(), gy.cuda(), True, math_mode=L.MATH_TF32))
+    wx, ww, wb = R.linear_backward(x.double(), w.double(), gy.double(), True)
+    assert_close_scaled(gx, wx, TF32_SCALED_TOL, "linear dx")
+    assert_close_scaled(gw, ww, TF32_SCALED_TOL, "linear dW")
+    assert_close(gb, wb, 1e-4, "linear db")
+    if O % 4 == 0 and I % 4 == 0:
+        assert launched >= 1 and launched2 >= 2
+
+
+def test_split_k_is_deterministic_tf32(L, fx):
+    a = randn(128, 16384, seed=12)
+    b = randn(16384, 128, seed=13)
+    run = lambda: fx.matmul(a.cuda(), b.cuda(), m=128, n=128, k=16384, a_strides=(16384, 1),
+                            b_strides=(128, 1), math_mode=L.MATH_TF32)
+    c1, _ = tc_delta(L, run)
+    c2, _ = tc_delta(L, run)
+    assert torch.equal(c1, c2)
+    assert_close_scaled(c1, a.double() @ b.double(), TF32_SCALED_TOL, "split-K matmul")
