@@ -175,7 +175,7 @@ __device__ __forceinline__ void operand_coords(const OperandPlan& p, int mn, int
   }
   c[p.mn_dim] += mn;
   c[p.k_dim] += k_lo * kBK;
-  if (p.k2_dim >= 0) c[p.k2_dim] += k_hi;
+  if (p.k2_dim >= 0) c[p.k2_dim] += k_hi * p.k2_scale;
   if (p.z_dim >= 0) c[p.z_dim] += z;
 }
 
@@ -313,6 +313,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                                        : epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) +
                                              (long long)z * ep.z_stride;
     const float bm = (!to_partial && ep.bias_m && m < args.M) ? ep.bias_m[m] : 0.f;
+    // padding rows of a padded pixel axis are computed but never stored
+    const bool row_live =
+        m < args.M && (to_partial || ep.m_valid == 0 || ep.m_div == 0 || (m % ep.m_div) < ep.m_valid);
     if (ok) {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -324,7 +327,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0.f;
         }
-        if (m < args.M) {
+        if (row_live) {
           if (to_partial) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
@@ -368,6 +371,7 @@ tc_splitk_reduce_kernel(const float* __restrict__ partial, EpiloguePlan ep, int 
     const int z = (int)(i / mn);
     const long long r = i - (long long)z * mn;
     const int m = (int)(r / N), n = (int)(r - (long long)m * N);
+    if (ep.m_valid != 0 && ep.m_div != 0 && (m % ep.m_div) >= ep.m_valid) continue;
     float s = 0.f;
     for (int sp = 0; sp < splits; ++sp) s += partial[((long long)z * splits + sp) * mn + r];
     float* dst = ep.out + epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) +

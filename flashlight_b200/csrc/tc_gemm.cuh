@@ -21,21 +21,24 @@ constexpr int kBK = 32;   // fp32 elements per pipeline stage along K (= 128 byt
 
 // How one operand's TMA coordinates advance.  coord[d] for dimension d of the
 // tensor map is  base[d] + mn * (d == mn_dim) + k_lo * (d == k_dim)
-//                + k_hi * (d == k2_dim) + z * (d == z_dim)
-// where k = k_hi * k_inner + k_lo walks the contraction (k_lo in elements).
+//                + k_hi * k2_scale * (d == k2_dim) + z * (d == z_dim)
+// where k = k_hi * k_inner + k_lo walks the contraction (k_lo in elements).  k2_dim may
+// equal k_dim (a flat pixel axis made of images of k2_scale pixels each).
 struct OperandPlan {
   int rank;      // tensor-map rank, 2..4
   int mn_major;  // 1: m (or n) is the contiguous dimension
   int mn_dim, k_dim, k2_dim, z_dim;  // -1 = unused
   int k_inner;   // stage iterations per k2 step (ceil(extent of k_dim / kBK)); 0 = single level
+  int k2_scale;  // coordinate step per k_hi
   int base[4];
 };
 
 struct EpiloguePlan {
   float* out;
-  // offset(m) = (m / m_div) * m_outer + (m % m_div) * m_stride   (m_div == 0: m * m_stride)
+  // offset(m) = (m / m_div) * m_outer + (m % m_div) * m_stride   (m_div == 0: m * m_stride);
+  // rows with (m % m_div) >= m_valid are padding and are not stored (m_valid == 0: all valid)
   long long m_stride, m_outer, n_stride, n_outer, z_stride;
-  int m_div, n_div;
+  int m_div, n_div, m_valid;
   const float* bias_m;  // added per row (may be null)
   const float* bias_n;  // added per column (may be null)
   float alpha, beta;

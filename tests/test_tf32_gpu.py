@@ -117,3 +117,73 @@ def test_split_k_is_deterministic_tf32(L, fx):
     c2, _ = tc_delta(L, run)
     assert torch.equal(c1, c2)
     assert_close_scaled(c1, a.double() @ b.double(), TF32_SCALED_TOL, "split-K matmul")
+
+
+# ------------------------------------------------------------- convolution
+# N, C, H, W, Cout, kH, kW, sx, sy, px, py, dx, dy, groups, expect tensor-core kernel
+TF32_CONV_CASES = [
+    (2, 64, 16, 16, 256, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),    # direct 1x1, expand
+    (3, 256, 14, 14, 64, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),    # direct 1x1, reduce, 196 pixels
+    (2, 128, 28, 28, 128, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),   # direct 1x1
+    (4, 512, 7, 7, 128, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),     # 1x1 on 49-pixel planes: general route
+    (2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1, True),     # 3x3
+    (2, 128, 14, 14, 128, 3, 3, 2, 2, 1, 1, 1, 1, 1, True),   # 3x3 stride 2
+    (2, 256, 14, 14, 512, 1, 1, 2, 2, 0, 0, 1, 1, 1, True),   # 1x1 stride 2 downsample
+    (2, 3, 32, 32, 64, 7, 7, 2, 2, 3, 3, 1, 1, 1, True),      # stem: K = 147 (padded filter rows)
+    (4, 1, 28, 28, 32, 5, 5, 1, 1, 2, 2, 1, 1, 1, True),      # MNIST conv1: K = 25
+    (2, 80, 1, 100, 96, 1, 13, 1, 1, 6, 0, 1, 1, 1, True),    # conv-ASR time convolution
+    (7, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 1, 1, 1, True),        # reference test shape, ragged pixels
+    (2, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 2, 1, 1, True),        # dilation
+    (2, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 1, 1, 2, False),       # groups: fp32 kernel
+]
+
+
+@pytest.mark.parametrize("case", TF32_CONV_CASES)
+def test_conv2d_tf32(L, case):
+    from flashlight_b200.extension import B200AutogradExtension
+    N, Cin, H, W, Cout, kH, kW, sx, sy, px, py, dx, dy, groups, expect_tc = case
+    ext = B200AutogradExtension(math_mode=L.MATH_TF32)
+    x = randn(N, Cin, H, W, seed=21)
+    w = randn(Cout, Cin // groups, kH, kW, seed=22) * (1.0 / (Cin // groups * kH * kW) ** 0.5)
+    b = randn(Cout, seed=23)
+    args = (sx, sy, px, py, dx, dy, groups)
+    y, n1 = tc_delta(L, lambda: ext.conv2d(x.cuda(), w.cuda(), b.cuda(), *args))
+    want = R.conv2d(x.double(), w.double(), b.double(), *args)
+    assert tuple(y.shape) == tuple(want.shape)
+    assert_close_scaled(y, want, TF32_SCALED_TOL, "conv forward")
+    gy = randn(*want.shape, seed=24)
+    gx, n2 = tc_delta(L, lambda: ext.conv2dBackwardData(gy.cuda(), x.cuda(), w.cuda(), *args))
+    assert_close_scaled(gx, R.conv2d_backward_data(gy.double(), x.shape, w.double(), *args),
+                        TF32_SCALED_TOL, "conv backward data")
+    (gw, gb), n3 = tc_delta(L, lambda: ext.conv2dBackwardFilterBias(gy.cuda(), x.cuda(), w.cuda(),
+                                                                    b.cuda(), *args))
+    wgw, wgb = R.conv2d_backward_filter_bias(gy.double(), x.double(), w.shape, True, *args)
+    assert_close_scaled(gw, wgw, TF32_SCALED_TOL, "conv backward filter")
+    assert_close(gb, wgb, 1e-4, "conv backward bias")
+    if expect_tc:
+        assert n1 >= 1 and n2 >= 1 and n3 >= 1, (n1, n2, n3)
+    else:
+        assert n1 == 0 and n2 == 0 and n3 == 0
+
+
+def test_rnn_tf32(L):
+    """The recurrent and input GEMMs of the RNN run on the tensor-core kernel in TF32 mode."""
+    from flashlight_b200.extension import AutogradPayload, B200AutogradExtension, RNNGradData
+    ext = B200AutogradExtension(math_mode=L.MATH_TF32)
+    I, H, L_, B, T = 80, 128, 2, 32, 6
+    n = R.rnn_num_params(I, H, L_, R.RNN_LSTM, True)
+    w = randn(n, seed=40) * (0.5 / H ** 0.5)
+    x = randn(T, B, I, seed=41)
+    payload = AutogradPayload()
+    (y, hy, cy), launched = tc_delta(L, lambda: ext.rnn(x.cuda(), None, None, w.cuda(), H, L_,
+                                                         R.RNN_LSTM, True, 0.0, payload))
+    wy, why, wcy = R.rnn(x.double(), None, None, w.double(), H, L_, R.RNN_LSTM, True)
+    assert launched >= 1
+    assert_close_scaled(y, wy, 5e-3, "rnn y (tf32)")
+    gy = randn(T, B, 2 * H, seed=44)
+    dx, _, _, dw = ext.rnnBackward(x.cuda(), None, None, w.cuda(), RNNGradData(gy.cuda(), None, None),
+                                   y, L_, H, R.RNN_LSTM, True, 0.0, payload)
+    wdx, _, _, wdw = R.rnn_backward(x.double(), None, None, w.double(), H, L_, R.RNN_LSTM, True,
+                                    gy.double(), None, None)
+    assert_close_scaled(dx, wdx, 5e-3, "rnn dx (tf32)")
+    assert_close_scaled(dw, wdw, 5e-3, "rnn dw (tf32)")
