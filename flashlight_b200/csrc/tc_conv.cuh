@@ -25,4 +25,15 @@ int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, flo
 int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw, void* ws,
                             size_t ws_bytes, cudaStream_t st);
 
+// Channels-last implicit-GEMM route (tc_conv_patch.cu): no im2col matrix, one NHWC copy of the
+// activation operand per pass.
+bool patch_conv_supported(const ConvGeo& g);
+size_t patch_conv_workspace_bytes(const ConvGeo& g, int which);
+int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
+                       float* y, void* ws, size_t ws_bytes, cudaStream_t st);
+int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx,
+                             void* ws, size_t ws_bytes, cudaStream_t st);
+int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
+                               void* ws, size_t ws_bytes, cudaStream_t st);
+
 }  // namespace flb200

@@ -1,0 +1,381 @@
+// Host side of the channels-last implicit-GEMM convolution (policies in tc_patch.cuh):
+// NCHW -> NHWC copies of the activations, filter repacking, TMA tensor maps, tap tables.
+//
+// Scratch traffic per pass: one transposed copy of the activation operand (8 bytes per
+// element) and a repacked filter; there is no im2col matrix.
+#include "tc_conv.cuh"
+#include "tc_patch.cuh"
+
+namespace flb200 {
+namespace {
+
+inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+inline int up4(int v) { return (v + 3) / 4 * 4; }
+
+// dst[n][hw][cp] = src[n][c][hw] for c < C, 0 for the padding channels C <= c < cp.
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_kernel(const float* __restrict__ src, float* __restrict__ dst, int C, int cp,
+                    int HW) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int hw0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const long long n = blockIdx.z;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = c0 + ty + 8 * i, hw = hw0 + tx;
+    tile[ty + 8 * i][tx] = (c < C && hw < HW) ? src[(n * C + c) * HW + hw] : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int hw = hw0 + ty + 8 * i, c = c0 + tx;
+    if (hw < HW && c < cp) dst[(n * HW + hw) * cp + c] = tile[tx][ty + 8 * i];
+  }
+}
+
+int to_nhwc(const float* src, float* dst, int N, int C, int cp, int HW, cudaStream_t st) {
+  dim3 grid((unsigned)((HW + 31) / 32), (unsigned)((cp + 31) / 32), (unsigned)N);
+  FLB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "nchw_to_nhwc: extent out of range");
+  nchw_to_nhwc_kernel<<<grid, 256, 0, st>>>(src, dst, C, cp, HW);
+  FLB200_AFTER_LAUNCH("nchw_to_nhwc");
+  return FLB200_OK;
+}
+
+// Filter w[co][ci][tap] repacked to out[tap][rows][kp] with (rows, k) = (co, ci) for the
+// forward pass and (ci, co) for backward-data; k >= its extent is zero.
+__global__ void pack_filter_kernel(const float* __restrict__ w, float* __restrict__ out, int Cout,
+                                   int C, int RS, int rows, int kext, int kp, int rows_are_co) {
+  const long long total = (long long)RS * rows * kp;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+       t += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(t % kp);
+    const long long r2 = t / kp;
+    const int row = (int)(r2 % rows), tap = (int)(r2 / rows);
+    float v = 0.f;
+    if (k < kext) {
+      const int co = rows_are_co ? row : k, ci = rows_are_co ? k : row;
+      v = w[((long long)co * C + ci) * RS + tap];
+    }
+    out[t] = v;
+  }
+}
+
+// gw[co][ci][tap] = sum over splits of partial[split][tap][co][ci]
+__global__ void wgrad_reduce_kernel(const float* __restrict__ partial, float* __restrict__ gw,
+                                    int Cout, int C, int RS, int splits) {
+  const long long per_split = (long long)RS * Cout * C;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < per_split;
+       t += (long long)gridDim.x * blockDim.x) {
+    const int ci = (int)(t % C);
+    const long long r2 = t / C;
+    const int co = (int)(r2 % Cout), tap = (int)(r2 / Cout);
+    float s = 0.f;
+    for (int sp = 0; sp < splits; ++sp) s += partial[(long long)sp * per_split + t];
+    gw[((long long)co * C + ci) * RS + tap] = s;
+  }
+}
+
+struct Patch { int QW, PH, NB, qw_shift, ph_shift; };
+int log2i(int v) { int s = 0; while ((1 << s) < v) ++s; return s; }
+// 128-row patch for the forward / backward-data passes.
+Patch pick_patch(int Wq, int Hq) {
+  Patch p;
+  p.QW = 8;
+  while (p.QW < Wq && p.QW < 128) p.QW *= 2;
+  p.PH = 128 / p.QW;
+  p.NB = 1;
+  int ph_needed = 1;
+  while (ph_needed < Hq) ph_needed *= 2;
+  if (p.PH > ph_needed) { p.NB = p.PH / ph_needed; p.PH = ph_needed; }
+  p.qw_shift = log2i(p.QW);
+  p.ph_shift = log2i(p.PH);
+  return p;
+}
+// 32-pixel patch (the K extent of one stage) for the backward-filter pass.
+void pick_k_patch(int Wq, int Hq, int* QW, int* PH) {
+  int q = 4;
+  while (q < Wq && q < 32) q *= 2;
+  int ph = 32 / q;
+  (void)Hq;
+  *QW = q;
+  *PH = ph;
+}
+
+// 4-D NHWC map [c, w, h, n] of a tensor with cp channels per pixel.
+int nhwc_map(CUtensorMap* m, const float* base, int C, int cp, int W, int H, int N, int box_w,
+             int box_h, int box_n, int sx, int sy, int mode) {
+  const uint64_t dims[4] = {(uint64_t)C, (uint64_t)W, (uint64_t)H, (uint64_t)N};
+  const uint64_t strides[3] = {(uint64_t)cp * 4, (uint64_t)W * cp * 4, (uint64_t)H * W * cp * 4};
+  const uint32_t box[4] = {32, (uint32_t)(box_w * sx), (uint32_t)(box_h * sy), (uint32_t)box_n};
+  const uint32_t es[4] = {1, (uint32_t)sx, (uint32_t)sy, 1};
+  return tc::make_tensor_map(m, base, 4, dims, strides, box, mode, es);
+}
+
+// Packed filter map [k, rows, taps].
+int filter_map(CUtensorMap* m, const float* base, int kext, int kp, int rows, int taps, int bn) {
+  const uint64_t dims[3] = {(uint64_t)kext, (uint64_t)rows, (uint64_t)taps};
+  const uint64_t strides[2] = {(uint64_t)kp * 4, (uint64_t)rows * kp * 4};
+  const uint32_t box[3] = {32, (uint32_t)bn, 1};
+  return tc::make_tensor_map(m, base, 3, dims, strides, box, tc::kMapKMajor);
+}
+
+template <int BN>
+int launch_patch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
+                 tc::PatchConvProblem<BN>& p, cudaStream_t st) {
+  p.tiles_n = (p.n_out + BN - 1) / BN;
+  const long long tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b * p.tiles_n;
+  FLB200_REQUIRE(tiles < 0x7fffffffLL, "patch conv: too many tiles");
+  return tc::launch_problem<tc::PatchConvProblem<BN>, BN>("tc_patch_conv", ma, mb, mc, p, tiles,
+                                                         st);
+}
+
+// Fills the parts of the problem that do not depend on BN and launches with the BN that fits
+// the number of output channels.
+struct PatchArgs {
+  Patch patch;
+  int pix_w, pix_h, images, n_out, cchunks, ntaps, a_w_mul, a_h_mul;
+  tc::TapTable taps;
+  float* out;
+  const float* bias;
+  int out_H, out_W, out_C, oh_mul, oh_add, ow_mul, ow_add;
+};
+template <int BN>
+int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
+              const PatchArgs& a, cudaStream_t st) {
+  tc::PatchConvProblem<BN> p;
+  p.a_mn_major = 0; p.b_mn_major = 0;
+  p.QW = a.patch.QW; p.PH = a.patch.PH; p.NB = a.patch.NB;
+  p.qw_shift = a.patch.qw_shift; p.ph_shift = a.patch.ph_shift;
+  p.tiles_q = (a.pix_w + p.QW - 1) / p.QW;
+  p.tiles_p = (a.pix_h + p.PH - 1) / p.PH;
+  p.tiles_b = (a.images + p.NB - 1) / p.NB;
+  p.pix_w = a.pix_w; p.pix_h = a.pix_h; p.images = a.images; p.n_out = a.n_out;
+  p.cchunks = a.cchunks; p.ntaps = a.ntaps; p.a_w_mul = a.a_w_mul; p.a_h_mul = a.a_h_mul;
+  p.taps = a.taps;
+  p.out = a.out; p.bias = a.bias;
+  p.out_H = a.out_H; p.out_W = a.out_W; p.out_C = a.out_C;
+  p.oh_mul = a.oh_mul; p.oh_add = a.oh_add; p.ow_mul = a.ow_mul; p.ow_add = a.ow_add;
+  p.tma_store = mc ? 1 : 0;
+  return launch_patch<BN>(ma, mb, mc, p, st);
+}
+int run_patch_any(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
+                  const PatchArgs& a, cudaStream_t st) {
+  if (bn == 32) return run_patch<32>(ma, mb, mc, a, st);
+  if (bn == 64) return run_patch<64>(ma, mb, mc, a, st);
+  return run_patch<128>(ma, mb, mc, a, st);
+}
+
+// Output map [w, h, c, n] for TMA stores of a patch: only when rows of the plane are
+// 16-byte multiples and the patch rows tile the warp's 32 accumulator rows.
+bool out_store_map(CUtensorMap* m, float* out, int W, int H, int C, int N, const Patch& p) {
+  if (W % 4 != 0 || !aligned16(out)) return false;
+  const uint64_t dims[4] = {(uint64_t)W, (uint64_t)H, (uint64_t)C, (uint64_t)N};
+  const uint64_t strides[3] = {(uint64_t)W * 4, (uint64_t)H * W * 4, (uint64_t)C * H * W * 4};
+  const uint32_t box[4] = {(uint32_t)(p.QW < 32 ? p.QW : 32), (uint32_t)(p.QW < 32 ? 32 / p.QW : 1),
+                           32, 1};
+  if (p.QW < 32 && p.PH < 32 / p.QW) return false;  // a warp would span two images
+  return tc::make_tensor_map(m, out, 4, dims, strides, box, tc::kMapStaging) == FLB200_OK;
+}
+
+struct WgradPlan { int QW, PH, tiles_q, tiles_p, k_iters, splits, ips, bn; size_t partial_bytes; };
+WgradPlan plan_wgrad(const ConvGeo& g) {
+  WgradPlan w;
+  pick_k_patch(g.Wo, g.Ho, &w.QW, &w.PH);
+  w.tiles_q = (g.Wo + w.QW - 1) / w.QW;
+  w.tiles_p = (g.Ho + w.PH - 1) / w.PH;
+  w.k_iters = g.N * w.tiles_p * w.tiles_q;
+  w.bn = tc::pick_bn(g.C);
+  const long long out_tiles = (long long)((g.Cout + tc::kBM - 1) / tc::kBM) *
+                              ((g.C + w.bn - 1) / w.bn) * g.RS;
+  const long long target = 2LL * device_info().sm_count;
+  long long splits = (target + out_tiles - 1) / out_tiles;
+  const long long max_by_k = w.k_iters / 16 > 0 ? w.k_iters / 16 : 1;
+  if (splits > max_by_k) splits = max_by_k;
+  if (splits < 1) splits = 1;
+  long long ips = (w.k_iters + splits - 1) / splits;
+  splits = (w.k_iters + ips - 1) / ips;
+  w.splits = (int)splits;
+  w.ips = (int)ips;
+  w.partial_bytes = (size_t)splits * g.RS * g.Cout * g.C * 4;
+  return w;
+}
+
+template <int BN>
+int run_wgrad(const CUtensorMap& ma, const CUtensorMap& mb, const ConvGeo& g, const WgradPlan& w,
+              const tc::TapTable& taps, float* partial, cudaStream_t st) {
+  tc::PatchWgradProblem<BN> p;
+  p.a_mn_major = 1; p.b_mn_major = 1;
+  p.QW = w.QW; p.PH = w.PH; p.tiles_q = w.tiles_q; p.tiles_p = w.tiles_p; p.images = g.N;
+  p.M = g.Cout; p.N = g.C;
+  p.tiles_m = (g.Cout + tc::kBM - 1) / tc::kBM;
+  p.tiles_n = (g.C + BN - 1) / BN;
+  p.ntaps = g.RS; p.splits = w.splits; p.iters_per_split = w.ips; p.k_iters = w.k_iters;
+  p.b_w_mul = g.sx; p.b_h_mul = g.sy;
+  p.taps = taps;
+  p.partial = partial;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * p.ntaps * p.splits;
+  return tc::launch_problem<tc::PatchWgradProblem<BN>, BN>("tc_patch_wgrad", ma, mb, nullptr, p,
+                                                          tiles, st);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- interface
+bool patch_conv_supported(const ConvGeo& g) {
+  // small channel counts would waste most of each 32-wide K chunk: those stay on the gather route
+  return g.groups == 1 && g.RS <= tc::kMaxTaps && g.C >= 16 && g.Cout >= 16 &&
+         g.sx <= 2 && g.sy <= 2 && g.N <= 65535;
+}
+
+size_t patch_conv_workspace_bytes(const ConvGeo& g, int which) {
+  const int cp = up4(g.C), cop = up4(g.Cout);
+  if (which == 0)
+    return up256((size_t)g.N * g.HW * cp * 4) + up256((size_t)g.RS * g.Cout * cp * 4);
+  if (which == 1)
+    return up256((size_t)g.N * g.HoWo * cop * 4) + up256((size_t)g.RS * g.C * cop * 4);
+  return up256((size_t)g.N * g.HW * cp * 4) + up256((size_t)g.N * g.HoWo * cop * 4) +
+         up256(plan_wgrad(g).partial_bytes);
+}
+
+int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
+                       float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+  (void)ws_bytes;
+  const int cp = up4(g.C);
+  char* base = static_cast<char*>(ws);
+  float* xt = reinterpret_cast<float*>(base);
+  float* wp = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HW * cp * 4));
+  if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
+  pack_filter_kernel<<<grid_for((long long)g.RS * g.Cout * cp, 256), 256, 0, st>>>(
+      w, wp, g.Cout, g.C, g.RS, g.Cout, g.C, cp, 1);
+  FLB200_AFTER_LAUNCH("pack_filter");
+  PatchArgs a{};
+  a.patch = pick_patch(g.Wo, g.Ho);
+  a.pix_w = g.Wo; a.pix_h = g.Ho; a.images = g.N; a.n_out = g.Cout;
+  a.cchunks = (g.C + tc::kBK - 1) / tc::kBK;
+  a.ntaps = g.RS;
+  a.a_w_mul = g.sx; a.a_h_mul = g.sy;
+  for (int r = 0; r < g.kH; ++r)
+    for (int s = 0; s < g.kW; ++s) {
+      const int t = r * g.kW + s;
+      a.taps.dw[t] = (short)(s * g.dx - g.px);
+      a.taps.dh[t] = (short)(r * g.dy - g.py);
+      a.taps.wtap[t] = (short)t;
+    }
+  a.out = y; a.bias = bias;
+  a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
+  a.oh_mul = 1; a.ow_mul = 1;
+  const int bn = tc::pick_bn(g.Cout);
+  CUtensorMap ma, mb, mc;
+  if (int rc = nhwc_map(&ma, xt, g.C, cp, g.W, g.H, g.N, a.patch.QW, a.patch.PH, a.patch.NB, g.sx,
+                        g.sy, tc::kMapKMajor))
+    return rc;
+  if (int rc = filter_map(&mb, wp, g.C, cp, g.Cout, g.RS, bn)) return rc;
+  const bool tma_out = out_store_map(&mc, y, g.Wo, g.Ho, g.Cout, g.N, a.patch);
+  return run_patch_any(bn, ma, mb, tma_out ? &mc : nullptr, a, st);
+}
+
+int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx,
+                             void* ws, size_t ws_bytes, cudaStream_t st) {
+  (void)ws_bytes;
+  const int cop = up4(g.Cout);
+  char* base = static_cast<char*>(ws);
+  float* gyt = reinterpret_cast<float*>(base);
+  float* wd = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HoWo * cop * 4));
+  if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+  pack_filter_kernel<<<grid_for((long long)g.RS * g.C * cop, 256), 256, 0, st>>>(
+      w, wd, g.Cout, g.C, g.RS, g.C, g.Cout, cop, 0);
+  FLB200_AFTER_LAUNCH("pack_filter");
+  const int bn = tc::pick_bn(g.C);
+  CUtensorMap mb;
+  if (int rc = filter_map(&mb, wd, g.Cout, cop, g.C, g.RS, bn)) return rc;
+  // One launch per parity class (a, b) of the input pixel: h = p*sy + a, w = q*sx + b.  Only
+  // the taps with (a + py - r*dy) divisible by sy reach that class.
+  // Classes that no tap reaches keep a zero gradient: clear dx first if there is one.
+  bool any_empty = false;
+  for (int ca = 0; ca < g.sy; ++ca)
+    for (int cb = 0; cb < g.sx; ++cb) {
+      bool hit_h = false, hit_w = false;
+      for (int r = 0; r < g.kH; ++r) hit_h = hit_h || ((ca + g.py - r * g.dy) % g.sy == 0);
+      for (int s = 0; s < g.kW; ++s) hit_w = hit_w || ((cb + g.px - s * g.dx) % g.sx == 0);
+      any_empty = any_empty || !(hit_h && hit_w);
+    }
+  if (any_empty) FLB200_CUDA_CHECK(cudaMemsetAsync(gx, 0, (size_t)g.N * g.C * g.HW * 4, st));
+  for (int ca = 0; ca < g.sy; ++ca)
+    for (int cb = 0; cb < g.sx; ++cb) {
+      PatchArgs a{};
+      a.pix_h = (g.H - ca + g.sy - 1) / g.sy;
+      a.pix_w = (g.W - cb + g.sx - 1) / g.sx;
+      if (a.pix_h <= 0 || a.pix_w <= 0) continue;
+      int nt = 0;
+      for (int r = 0; r < g.kH; ++r) {
+        const int th = ca + g.py - r * g.dy;
+        if (th % g.sy != 0) continue;
+        for (int s = 0; s < g.kW; ++s) {
+          const int tw = cb + g.px - s * g.dx;
+          if (tw % g.sx != 0) continue;
+          a.taps.dh[nt] = (short)(th / g.sy);
+          a.taps.dw[nt] = (short)(tw / g.sx);
+          a.taps.wtap[nt] = (short)(r * g.kW + s);
+          ++nt;
+        }
+      }
+      if (nt == 0) continue;  // no tap reaches this class: it stays zero
+      a.patch = pick_patch(a.pix_w, a.pix_h);
+      a.images = g.N; a.n_out = g.C;
+      a.cchunks = (g.Cout + tc::kBK - 1) / tc::kBK;
+      a.ntaps = nt;
+      a.a_w_mul = 1; a.a_h_mul = 1;
+      a.out = gx; a.bias = nullptr;
+      a.out_H = g.H; a.out_W = g.W; a.out_C = g.C;
+      a.oh_mul = g.sy; a.oh_add = ca; a.ow_mul = g.sx; a.ow_add = cb;
+      CUtensorMap ma, mc;
+      if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, a.patch.QW, a.patch.PH,
+                            a.patch.NB, 1, 1, tc::kMapKMajor))
+        return rc;
+      const bool tma_out = g.sx == 1 && g.sy == 1 &&
+                           out_store_map(&mc, gx, g.W, g.H, g.C, g.N, a.patch);
+      if (int rc = run_patch_any(bn, ma, mb, tma_out ? &mc : nullptr, a, st)) return rc;
+    }
+  return FLB200_OK;
+}
+
+int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
+                               void* ws, size_t ws_bytes, cudaStream_t st) {
+  (void)ws_bytes;
+  const int cp = up4(g.C), cop = up4(g.Cout);
+  const WgradPlan wp = plan_wgrad(g);
+  char* base = static_cast<char*>(ws);
+  float* xt = reinterpret_cast<float*>(base);
+  size_t off = up256((size_t)g.N * g.HW * cp * 4);
+  float* gyt = reinterpret_cast<float*>(base + off);
+  off += up256((size_t)g.N * g.HoWo * cop * 4);
+  float* partial = reinterpret_cast<float*>(base + off);
+  if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
+  if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+  tc::TapTable taps{};
+  for (int r = 0; r < g.kH; ++r)
+    for (int s = 0; s < g.kW; ++s) {
+      const int t = r * g.kW + s;
+      taps.dw[t] = (short)(s * g.dx - g.px);
+      taps.dh[t] = (short)(r * g.dy - g.py);
+      taps.wtap[t] = (short)t;
+    }
+  CUtensorMap ma, mb;
+  if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH, 1, 1, 1,
+                        tc::kMapMnMajor))
+    return rc;
+  if (int rc = nhwc_map(&mb, xt, g.C, cp, g.W, g.H, g.N, wp.QW, wp.PH, 1, g.sx, g.sy,
+                        tc::kMapMnMajor))
+    return rc;
+  int rc;
+  if (wp.bn == 32) rc = run_wgrad<32>(ma, mb, g, wp, taps, partial, st);
+  else if (wp.bn == 64) rc = run_wgrad<64>(ma, mb, g, wp, taps, partial, st);
+  else rc = run_wgrad<128>(ma, mb, g, wp, taps, partial, st);
+  if (rc) return rc;
+  wgrad_reduce_kernel<<<grid_for((long long)g.RS * g.Cout * g.C, 256), 256, 0, st>>>(
+      partial, gw, g.Cout, g.C, g.RS, wp.splits);
+  FLB200_AFTER_LAUNCH("wgrad_reduce");
+  return FLB200_OK;
+}
+
+}  // namespace flb200

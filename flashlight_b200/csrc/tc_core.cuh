@@ -67,6 +67,28 @@ __device__ __forceinline__ void fence_barrier_init() {
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// TMA store of a 3-D box from shared memory (bulk-group completion); elements outside the
+// tensor are clipped by the hardware.  c[0] is the contiguous coordinate (16-byte rule applies).
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, const void* src, int c0,
+                                             int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(
+          reinterpret_cast<uint64_t>(map)),
+      "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Waits until at most N of this thread's bulk groups still READ their shared-memory source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ void tma_load(const CUtensorMap* map, uint64_t* bar, void* dst,
                                          int rank, const int* c) {
   const uint32_t d = smem_u32(dst), b = smem_u32(bar);
@@ -201,185 +223,6 @@ __device__ __forceinline__ long long epi_off(int idx, int div, long long stride,
   if (div == 0) return (long long)idx * stride;
   const int hi = idx / div;
   return (long long)hi * outer + (long long)(idx - hi * div) * stride;
-}
-
-template <int BN, int STAGES>
-struct SmemLayout {
-  static constexpr int kABytes = kBM * kBK * 4;  // 16 KB
-  static constexpr int kBBytes = BN * kBK * 4;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kTileBytes = STAGES * kStageBytes;
-  static constexpr int kBarBytes = 256;
-  static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // + slack to align to 1024
-};
-
-template <int BN, int STAGES>
-__global__ void __launch_bounds__(kThreads)
-tc_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               const KernelArgs args) {
-  using SL = SmemLayout<BN, STAGES>;
-  extern __shared__ char smem_raw[];
-  char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                        ~static_cast<uintptr_t>(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + SL::kTileBytes);
-  uint64_t* empty_bar = full_bar + STAGES;
-  uint64_t* tmem_full_bar = empty_bar + STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full_bar + 1);
-  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * kBM, n0 = blockIdx.x * BN;
-  const int z = blockIdx.z / args.splits, split = blockIdx.z - z * args.splits;
-  const int it0 = split * args.iters_per_split;
-  int it1 = it0 + args.iters_per_split;
-  if (it1 > args.k_iters) it1 = args.k_iters;
-  const int n_iters = it1 > it0 ? it1 - it0 : 0;
-  constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&empty_bar[s], 1);
-    }
-    mbar_init(tmem_full_bar, 1);
-    *failed = 0;
-    fence_barrier_init();
-  }
-  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      for (int i = 0; i < n_iters; ++i) {
-        const int s = i % STAGES;
-        const uint32_t round = i / STAGES;
-        if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
-          *failed = 1;
-          break;
-        }
-        char* a_dst = tiles + s * SL::kStageBytes;
-        char* b_dst = a_dst + SL::kABytes;
-        mbar_expect_tx(&full_bar[s], SL::kStageBytes);
-        load_operand<kBM>(&map_a, args.a, &full_bar[s], a_dst, m0, it0 + i, z);
-        load_operand<BN>(&map_b, args.b, &full_bar[s], b_dst, n0, it0 + i, z);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_tf32(BN, args.a.mn_major, args.b.mn_major);
-      bool ok = true;
-      for (int i = 0; i < n_iters && ok; ++i) {
-        const int s = i % STAGES;
-        const uint32_t round = i / STAGES;
-        if (!mbar_wait(&full_bar[s], round & 1)) {
-          *failed = 2;
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t a_addr = smem_u32(tiles + s * SL::kStageBytes);
-        const uint32_t b_addr = a_addr + SL::kABytes;
-#pragma unroll
-        for (int k = 0; k < kBK / kUmmaK; ++k) {
-          // K-major: step 8 elements = 32 bytes inside the swizzled row;
-          // MN-major: step 8 k-rows = one 1024-byte atom inside each box.
-          const uint64_t ad = args.a.mn_major
-                                  ? umma_desc(a_addr + k * 1024, kBK * 128, 512, 1)
-                                  : umma_desc(a_addr + k * 32, 16, 1024, 2);
-          const uint64_t bd = args.b.mn_major
-                                  ? umma_desc(b_addr + k * 1024, kBK * 128, 512, 1)
-                                  : umma_desc(b_addr + k * 32, 16, 1024, 2);
-          umma_tf32(tmem_base, ad, bd, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
-      }
-      umma_commit(tmem_full_bar);    // accumulator complete (or nothing was issued)
-    }
-  } else {
-    // epilogue warps 2..5 own TMEM lanes 32*(warp % 4) .. +31
-    const int lane_base = (warp & 3) * 32;
-    const int m = m0 + lane_base + lane;
-    bool ok = mbar_wait(tmem_full_bar, 0);
-    if (!ok) *failed = 3;
-    tc_fence_after();
-    ok = ok && (*failed == 0);
-    const EpiloguePlan& ep = args.ep;
-    const bool to_partial = args.splits > 1;
-    float* out = to_partial ? args.partial + ((long long)blockIdx.z * args.M) * args.N : ep.out;
-    const long long m_off = to_partial ? (long long)m * args.N
-                                       : epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) +
-                                             (long long)z * ep.z_stride;
-    const float bm = (!to_partial && ep.bias_m && m < args.M) ? ep.bias_m[m] : 0.f;
-    // padding rows of a padded pixel axis are computed but never stored
-    const bool row_live =
-        m < args.M && (to_partial || ep.m_valid == 0 || ep.m_div == 0 || (m % ep.m_div) < ep.m_valid);
-    if (ok) {
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (n0 + c0 >= args.N) break;  // uniform across the warp
-        float v[32];
-        if (n_iters > 0) {
-          tmem_ld32(tmem_base + ((uint32_t)lane_base << 16) + (uint32_t)c0, v);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0.f;
-        }
-        if (row_live) {
-          if (to_partial) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = n0 + c0 + j;
-              if (n < args.N) out[m_off + n] = v[j];
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = n0 + c0 + j;
-              if (n < args.N) {
-                float* dst = out + m_off + epi_off(n, ep.n_div, ep.n_stride, ep.n_outer);
-                float r = ep.alpha * v[j] + bm + (ep.bias_n ? ep.bias_n[n] : 0.f);
-                if (ep.beta != 0.f) r += ep.beta * *dst;
-                *dst = r;
-              }
-            }
-          }
-        }
-      }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (threadIdx.x == 0 && *failed != 0 && args.status) atomicExch(args.status, *failed);
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
-  }
-}
-
-// Sums split-K partial tiles in split order, then applies the epilogue.
-__global__ void __launch_bounds__(256)
-tc_splitk_reduce_kernel(const float* __restrict__ partial, EpiloguePlan ep, int M, int N, int Z,
-                        int splits) {
-  const long long mn = (long long)M * N;
-  const long long total = mn * Z;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const int z = (int)(i / mn);
-    const long long r = i - (long long)z * mn;
-    const int m = (int)(r / N), n = (int)(r - (long long)m * N);
-    if (ep.m_valid != 0 && ep.m_div != 0 && (m % ep.m_div) >= ep.m_valid) continue;
-    float s = 0.f;
-    for (int sp = 0; sp < splits; ++sp) s += partial[((long long)z * splits + sp) * mn + r];
-    float* dst = ep.out + epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) +
-                 epi_off(n, ep.n_div, ep.n_stride, ep.n_outer) + (long long)z * ep.z_stride;
-    float v = ep.alpha * s + (ep.bias_m ? ep.bias_m[m] : 0.f) + (ep.bias_n ? ep.bias_n[n] : 0.f);
-    if (ep.beta != 0.f) v += ep.beta * *dst;
-    *dst = v;
-  }
 }
 
 }  // namespace tc

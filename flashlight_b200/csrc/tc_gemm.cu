@@ -6,7 +6,7 @@
 
 #include <mutex>
 
-#include "tc_core.cuh"
+#include "tc_kernel.cuh"
 
 namespace flb200 {
 namespace tc {
@@ -36,7 +36,8 @@ static EncodeTiledFn encode_tiled_fn() {
 // dims[i+1], box[0] must be 32 elements (128 bytes).  K-major operand tiles use the
 // 128-byte swizzle of 16-byte chunks, MN-major ones the swizzle of 32-byte chunks.
 int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                    const uint64_t* strides_bytes, const uint32_t* box, bool mn_major) {
+                    const uint64_t* strides_bytes, const uint32_t* box, int mode,
+                    const uint32_t* elem_strides) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(FLB200_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
   cuuint64_t gd[5];
@@ -45,12 +46,14 @@ int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t
   for (int i = 0; i < rank; ++i) {
     gd[i] = dims[i];
     bx[i] = box[i];
-    es[i] = 1;
+    es[i] = elem_strides ? elem_strides[i] : 1;
     if (i > 0) gs[i - 1] = strides_bytes[i - 1];
   }
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base),
                   gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                  mode == kMapStaging ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                      : (mode == kMapMnMajor ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                             : CU_TENSOR_MAP_SWIZZLE_128B),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(FLB200_INVALID_ARG, "cuTensorMapEncodeTiled failed with code %d (rank %d)", (int)r,
@@ -59,11 +62,12 @@ int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t
 }
 
 std::atomic<long long> g_tc_launches{0};
+void count_tc_launch() { g_tc_launches.fetch_add(1, std::memory_order_relaxed); }
 
 // ------------------------------------------------------------ status flag
 __device__ int g_tc_status = 0;
 
-static int* status_ptr() {
+int* status_ptr() {
   // one address per device, looked up with that device current
   static int* ptrs[64] = {nullptr};
   int dev = 0;
@@ -80,23 +84,46 @@ static int* status_ptr() {
 }
 
 // ---------------------------------------------------------------- launch
-template <int BN, int STAGES>
-static int launch_one(const CUtensorMap& ma, const CUtensorMap& mb, const KernelArgs& args,
-                      dim3 grid, cudaStream_t st) {
-  using SL = SmemLayout<BN, STAGES>;
-  static bool configured[64] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_gemm_kernel<BN, STAGES>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           SL::kTotal));
-    configured[dev] = true;
+// Sums split-K partial tiles in split order, then applies the epilogue.
+static __global__ void __launch_bounds__(256)
+tc_splitk_reduce_kernel(const float* __restrict__ partial, EpiloguePlan ep, int M, int N, int Z,
+                        int splits) {
+  const long long mn = (long long)M * N;
+  const long long total = mn * Z;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const int z = (int)(i / mn);
+    const long long r = i - (long long)z * mn;
+    const int m = (int)(r / N), n = (int)(r - (long long)m * N);
+    if (ep.m_valid != 0 && ep.m_div != 0 && (m % ep.m_div) >= ep.m_valid) continue;
+    float s = 0.f;
+    for (int sp = 0; sp < splits; ++sp) s += partial[((long long)z * splits + sp) * mn + r];
+    float* dst = ep.out + epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) +
+                 epi_off(n, ep.n_div, ep.n_stride, ep.n_outer) + (long long)z * ep.z_stride;
+    float v = ep.alpha * s + (ep.bias_m ? ep.bias_m[m] : 0.f) + (ep.bias_n ? ep.bias_n[n] : 0.f);
+    if (ep.beta != 0.f) v += ep.beta * *dst;
+    *dst = v;
   }
-  tc_gemm_kernel<BN, STAGES><<<grid, kThreads, SL::kTotal, st>>>(ma, mb, args);
-  FLB200_AFTER_LAUNCH("tc_gemm");
-  g_tc_launches.fetch_add(1, std::memory_order_relaxed);
-  return FLB200_OK;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
+                       const OperandPlan& pa, const OperandPlan& pb, const EpiloguePlan& ep,
+                       long long M, long long N, long long k_iters, long long Z, const Launch& L,
+                       float* partial, cudaStream_t st) {
+  GemmProblem<BN> p;
+  p.tma_store = mc ? 1 : 0;
+  p.a = pa; p.b = pb; p.ep = ep;
+  p.a_mn_major = pa.mn_major; p.b_mn_major = pb.mn_major;
+  p.M = (int)M; p.N = (int)N; p.k_iters = (int)k_iters;
+  p.splits = L.splits; p.iters_per_split = L.iters_per_split;
+  p.tiles_m = (int)((M + kBM - 1) / kBM);
+  p.tiles_n = (int)((N + BN - 1) / BN);
+  p.Z = (int)Z;
+  p.partial = partial;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * Z * L.splits;
+  FLB200_REQUIRE(tiles < 0x7fffffffLL, "tc_gemm: too many tiles");
+  return launch_problem<GemmProblem<BN>, BN>("tc_gemm", ma, mb, mc, p, tiles, st);
 }
 
 int pick_bn(long long N) {
@@ -116,7 +143,6 @@ Launch plan_launch(long long M, long long N, long long k_iters, long long Z) {
     const long long max_by_k = k_iters / 8;  // at least 8 stage iterations (256 k) per split
     if (splits > max_by_k) splits = max_by_k;
     if (splits > 256) splits = 256;
-    if (Z * splits > 65535) splits = 65535 / Z;
     if (splits < 1) splits = 1;
   }
   long long ips = (k_iters + splits - 1) / splits;
@@ -137,29 +163,29 @@ int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, con
     L.splits = 1;
     L.iters_per_split = (int)k_iters;
   }
-  KernelArgs args;
-  args.a = pa;
-  args.b = pb;
-  args.ep = ep;
-  args.M = (int)M;
-  args.N = (int)N;
-  args.k_iters = (int)k_iters;
-  args.splits = L.splits;
-  args.iters_per_split = L.iters_per_split;
-  args.partial = static_cast<float*>(ws);
-  args.status = status_ptr();
-  dim3 grid((unsigned)((N + L.bn - 1) / L.bn), (unsigned)((M + kBM - 1) / kBM),
-            (unsigned)(Z * L.splits));
-  FLB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "tc_gemm: grid out of range");
+  float* partial = static_cast<float*>(ws);
+  // Outputs whose row index m is contiguous ([z][n][m], e.g. NCHW pixels) leave through TMA
+  // stores of 32x32 staging tiles; everything else is stored from registers.
+  CUtensorMap mc_storage;
+  const CUtensorMap* mc = nullptr;
+  if (L.splits == 1 && ep.m_stride == 1 && ep.m_div == 0 && ep.n_div == 0 && ep.beta == 0.f &&
+      ep.alpha == 1.f && ep.bias_m == nullptr && ep.n_stride % 4 == 0 && ep.n_stride >= M &&
+      (Z == 1 || ep.z_stride % 4 == 0) && aligned16(ep.out)) {
+    const uint64_t dims[3] = {(uint64_t)M, (uint64_t)N, (uint64_t)Z};
+    const uint64_t zs = Z == 1 ? (uint64_t)ep.n_stride * (uint64_t)N : (uint64_t)ep.z_stride;
+    const uint64_t strides[2] = {(uint64_t)ep.n_stride * 4, zs * 4};
+    const uint32_t box[3] = {32, 32, 1};
+    if (make_tensor_map(&mc_storage, ep.out, 3, dims, strides, box, kMapStaging) == FLB200_OK)
+      mc = &mc_storage;
+  }
   int rc;
-  if (L.bn == 32) rc = launch_one<32, 4>(ma, mb, args, grid, st);
-  else if (L.bn == 64) rc = launch_one<64, 4>(ma, mb, args, grid, st);
-  else rc = launch_one<128, 3>(ma, mb, args, grid, st);
+  if (L.bn == 32) rc = launch_gemm<32>(ma, mb, mc, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
+  else if (L.bn == 64) rc = launch_gemm<64>(ma, mb, mc, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
+  else rc = launch_gemm<128>(ma, mb, mc, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
   if (rc) return rc;
   if (L.splits > 1) {
     const int rgrid = grid_for(M * N * Z, 256);
-    tc_splitk_reduce_kernel<<<rgrid, 256, 0, st>>>(args.partial, ep, (int)M, (int)N, (int)Z,
-                                                   L.splits);
+    tc_splitk_reduce_kernel<<<rgrid, 256, 0, st>>>(partial, ep, (int)M, (int)N, (int)Z, L.splits);
     FLB200_AFTER_LAUNCH("tc_splitk_reduce");
   }
   return FLB200_OK;
@@ -236,7 +262,8 @@ int build_operand(const Side& s, const void* base, long long rows, long long K, 
     plan->z_dim = 2;
   }
   plan->rank = rank;
-  return tc::make_tensor_map(map, base, rank, dims, strides, box, s.mn_major);
+  return tc::make_tensor_map(map, base, rank, dims, strides, box,
+                             s.mn_major ? tc::kMapMnMajor : tc::kMapKMajor);
 }
 
 }  // namespace

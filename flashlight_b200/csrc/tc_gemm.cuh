@@ -44,17 +44,6 @@ struct EpiloguePlan {
   float alpha, beta;
 };
 
-struct KernelArgs {
-  OperandPlan a, b;
-  EpiloguePlan ep;
-  int M, N;
-  int k_iters;          // total stage iterations over the whole contraction
-  int splits;           // gridDim.z = batch * splits
-  int iters_per_split;
-  float* partial;       // split-K scratch: [z*splits + s][M][N]
-  int* status;          // device flag raised on a bounded-wait timeout
-};
-
 struct Launch {
   int bn, splits, iters_per_split;
   size_t workspace_bytes;
@@ -65,10 +54,19 @@ int pick_bn(long long N);
 Launch plan_launch(long long M, long long N, long long k_iters, long long Z);
 
 // fp32 tensor map; dims[0] is the contiguous dimension, strides_bytes[i] belongs to
-// dims[i+1]; box[0] must be 32 elements.  mn_major selects the 32-byte-chunk swizzle that
-// TF32 operands with a contiguous m / n index need.
+// dims[i+1]; box[0] must be 32 elements.  mode: K-major operand tile (128-byte swizzle of
+// 16-byte chunks), MN-major operand tile (TF32 operands with a contiguous m / n index need
+// the swizzle of 32-byte chunks), or an unswizzled staging tile for TMA stores.
+// elem_strides (optional) samples every s-th element of a dimension; the box extent of that
+// dimension is then given in source elements (count * s).
+enum { kMapKMajor = 0, kMapMnMajor = 1, kMapStaging = 2 };
 int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                    const uint64_t* strides_bytes, const uint32_t* box, bool mn_major);
+                    const uint64_t* strides_bytes, const uint32_t* box, int mode,
+                    const uint32_t* elem_strides = nullptr);
+
+// Address of the device flag that bounded waits raise (per device), and the launch counter.
+int* status_ptr();
+void count_tc_launch();
 
 // Launches the contraction (and the split-K reduction when the plan splits K).  Without
 // enough scratch the contraction runs unsplit.

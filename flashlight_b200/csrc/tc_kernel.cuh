@@ -1,0 +1,345 @@
+// Persistent tcgen05 contraction kernel for sm_100a and the "problem" policies that feed it.
+//
+//   D = sum_k A(m,k) * B(k,n),  fp32 operands read as TF32, fp32 accumulation in TMEM.
+//
+// One CTA per SM walks a static list of 128 x BN output tiles:
+//   warp 0   : TMA producer — one lane issues cp.async.bulk.tensor loads (never multicast)
+//              into a STAGES-deep ring of 128-byte-swizzled shared-memory tiles and runs
+//              ahead into the next output tile while the current one drains
+//   warp 1   : allocates TMEM (2 accumulators of BN columns); one lane issues tcgen05.mma
+//              for each ready stage and tcgen05.commit to free the stage / publish the tile
+//   warps 2-5: epilogue — tcgen05.ld the finished accumulator (32 lanes each) and write it
+//              out while the MMA warp already fills the other accumulator.  Outputs whose
+//              row index is contiguous in memory go through a per-warp staging tile in
+//              shared memory and a TMA store (the hardware clips ragged edges); the rest
+//              are stored from registers.
+// Hand-offs: full/empty mbarriers per stage, full/empty mbarriers per accumulator.
+// Every wait is bounded by a clock budget; a wait that runs out raises a flag, all roles
+// drain and the CTA frees its TMEM and returns (the host then reports FLB200_TIMEOUT).
+//
+// A problem policy P tells the skeleton what a tile is:
+//   int  a_mn_major, b_mn_major;
+//   struct Tile;                                   // decoded tile coordinates
+//   __device__ int  num_tiles() const;
+//   __device__ void decode(int tile, Tile&) const;
+//   __device__ int  k_begin(const Tile&) const;  __device__ int k_end(const Tile&) const;
+//   __device__ void load(const CUtensorMap* a, const CUtensorMap* b, const Tile&, int k,
+//                        uint64_t* bar, char* a_dst, char* b_dst) const;   // expect_tx + TMA
+//   __device__ bool chunk_live(const Tile&, int c0) const;                 // warp-uniform
+//   __device__ void store(const Tile&, const EpiCtx&, int c0, const float* v) const;  // 32 cols
+#pragma once
+#include "tc_core.cuh"
+
+namespace flb200 {
+namespace tc {
+
+constexpr int kStageTileBytes = 32 * 32 * 4;       // one staging tile: 32 columns x 32 rows
+constexpr int kStagingBytes = 4 * 2 * kStageTileBytes;  // 4 epilogue warps x 2 buffers
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kABytes = kBM * kBK * 4;  // 16 KB
+  static constexpr int kBBytes = BN * kBK * 4;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTileBytes = STAGES * kStageBytes;
+  static constexpr int kBarBytes = 512;
+  static constexpr int kTotal = kTileBytes + kStagingBytes + kBarBytes + 1024;  // + align slack
+};
+
+constexpr int stages_for(int bn) { return bn >= 128 ? 5 : 7; }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// What an epilogue thread knows about itself.
+struct EpiCtx {
+  const CUtensorMap* map_c;  // output tensor map (TMA-store problems only)
+  float* staging;            // this warp's two 32x32 staging tiles
+  int row;                   // accumulator row (TMEM lane) 0..127 owned by this thread
+  int lane;                  // lane in the warp; row = 32 * quarter + lane
+  uint32_t chunk_parity;     // alternates per stored chunk: selects the staging buffer
+};
+
+template <class P, int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads)
+tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                     const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ CUtensorMap map_c, const P prob, int* status) {
+  using SL = SmemLayout<BN, STAGES>;
+  extern __shared__ char smem_raw[];
+  char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                        ~static_cast<uintptr_t>(1023));
+  char* staging = tiles + SL::kTileBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;   // [2] accumulator ready for the epilogue
+  uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained, MMA may overwrite
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  const int n_tiles = prob.num_tiles();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 4);  // one arrival per epilogue warp
+    }
+    *failed = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      typename P::Tile t;
+      for (int tile = blockIdx.x; tile < n_tiles && *failed == 0; tile += gridDim.x) {
+        prob.decode(tile, t);
+        const int k1 = prob.k_end(t);
+        for (int k = prob.k_begin(t); k < k1; ++k, ++it) {
+          const uint32_t s = it % STAGES, round = it / STAGES;
+          if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+            *failed = 1;
+            break;
+          }
+          char* a_dst = tiles + s * SL::kStageBytes;
+          prob.load(&map_a, &map_b, t, k, &full_bar[s], a_dst, a_dst + SL::kABytes);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_tf32(BN, prob.a_mn_major, prob.b_mn_major);
+      uint32_t it = 0, nt = 0;
+      typename P::Tile t;
+      for (int tile = blockIdx.x; tile < n_tiles && *failed == 0; tile += gridDim.x, ++nt) {
+        prob.decode(tile, t);
+        const uint32_t acc = nt & 1, around = nt >> 1;
+        if (around > 0 && !mbar_wait(&tempty_bar[acc], (around - 1) & 1)) {
+          *failed = 4;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        const int k0 = prob.k_begin(t), k1 = prob.k_end(t);
+        for (int k = k0; k < k1; ++k, ++it) {
+          const uint32_t s = it % STAGES, round = it / STAGES;
+          if (!mbar_wait(&full_bar[s], round & 1)) {
+            *failed = 2;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * SL::kStageBytes);
+          const uint32_t b_addr = a_addr + SL::kABytes;
+#pragma unroll
+          for (int j = 0; j < kBK / kUmmaK; ++j) {
+            // K-major: step 8 elements = 32 bytes inside the swizzled row;
+            // MN-major: step 8 k-rows = 1024 bytes inside each box.
+            const uint64_t ad = prob.a_mn_major
+                                    ? umma_desc(a_addr + j * 1024, kBK * 128, 512, 1)
+                                    : umma_desc(a_addr + j * 32, 16, 1024, 2);
+            const uint64_t bd = prob.b_mn_major
+                                    ? umma_desc(b_addr + j * 1024, kBK * 128, 512, 1)
+                                    : umma_desc(b_addr + j * 32, 16, 1024, 2);
+            umma_tf32(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+        }
+        umma_commit(&tfull_bar[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // epilogue warps 2..5 own TMEM lanes 32*(warp % 4) .. +31
+    const int quarter = warp & 3;
+    EpiCtx ctx;
+    ctx.map_c = &map_c;
+    ctx.staging = reinterpret_cast<float*>(staging + quarter * 2 * kStageTileBytes);
+    ctx.row = quarter * 32 + lane;
+    ctx.lane = lane;
+    ctx.chunk_parity = 0;
+    uint32_t nt = 0;
+    typename P::Tile t;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++nt) {
+      prob.decode(tile, t);
+      const uint32_t acc = nt & 1, around = nt >> 1;
+      if (*failed != 0) break;
+      if (!mbar_wait(&tfull_bar[acc], around & 1)) {
+        *failed = 3;
+        break;
+      }
+      tc_fence_after();
+      if (*failed != 0) break;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (!prob.chunk_live(t, c0)) break;  // uniform across the warp
+        float v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
+        prob.store(t, ctx, c0, v);
+        ctx.chunk_parity ^= 1u;
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+    }
+    // staging tiles must stay intact until the TMA stores that read them are done
+    if (lane == 0) bulk_wait<0>();
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *failed != 0 && status) atomicExch(status, *failed);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------ plain GEMM
+// Tiles ordered split-fastest, then n, then m, then batch, so that CTAs running
+// together share the (large) A tile through L2.
+template <int BN>
+struct GemmProblem {
+  OperandPlan a, b;
+  EpiloguePlan ep;
+  int a_mn_major, b_mn_major;
+  int M, N, k_iters, splits, iters_per_split;
+  int tiles_m, tiles_n, Z;
+  int tma_store;   // 1: output is [z][n][m] with m contiguous, written through map_c
+  float* partial;  // split-K scratch [z*splits + s][M][N]
+
+  struct Tile { int m0, n0, z, split, k0, k1; };
+
+  __device__ __forceinline__ int num_tiles() const { return tiles_m * tiles_n * Z * splits; }
+  __device__ __forceinline__ void decode(int tile, Tile& t) const {
+    int r = tile;
+    t.split = r % splits; r /= splits;
+    t.n0 = (r % tiles_n) * BN; r /= tiles_n;
+    t.m0 = (r % tiles_m) * kBM; r /= tiles_m;
+    t.z = r;
+    t.k0 = t.split * iters_per_split;
+    t.k1 = min(t.k0 + iters_per_split, k_iters);
+  }
+  __device__ __forceinline__ int k_begin(const Tile& t) const { return t.k0; }
+  __device__ __forceinline__ int k_end(const Tile& t) const { return t.k1; }
+  __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
+                                       const Tile& t, int k, uint64_t* bar, char* a_dst,
+                                       char* b_dst) const {
+    mbar_expect_tx(bar, (kBM + BN) * kBK * 4);
+    load_operand<kBM>(ma, a, bar, a_dst, t.m0, k, t.z);
+    load_operand<BN>(mb, b, bar, b_dst, t.n0, k, t.z);
+  }
+  __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
+    return t.n0 + c0 < N;
+  }
+
+  __device__ __forceinline__ void store(const Tile& t, const EpiCtx& ctx, int c0,
+                                        const float* v) const {
+    const int m = t.m0 + ctx.row;
+    const int nb = t.n0 + c0;
+    if (tma_store) {
+      // staging tile [32 columns][32 rows]: lanes write consecutive floats of one column
+      float* buf = ctx.staging + ctx.chunk_parity * (kStageTileBytes / 4);
+      if (ctx.lane == 0) bulk_wait_read<1>();  // the store that used this buffer has read it
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float r = v[j];
+        if (ep.bias_n && nb + j < N) r += ep.bias_n[nb + j];
+        buf[j * 32 + ctx.lane] = r;
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (ctx.lane == 0 && t.m0 + (ctx.row & ~31) < M) {  // a box past the last row has nothing to write
+        tma_store_3d(ctx.map_c, buf, t.m0 + (ctx.row & ~31), nb, t.z);
+        bulk_commit();
+      }
+      return;
+    }
+    if (m >= M) return;
+    if (splits > 1) {
+      float* dst = partial + ((long long)(t.z * splits + t.split) * M + m) * N + nb;
+      if (nb + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (nb + j < N) dst[j] = v[j];
+      }
+      return;
+    }
+    if (ep.m_valid != 0 && ep.m_div != 0 && (m % ep.m_div) >= ep.m_valid) return;
+    const long long m_off =
+        epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) + (long long)t.z * ep.z_stride;
+    const float bm = ep.bias_m ? ep.bias_m[m] : 0.f;
+    const bool simple = ep.beta == 0.f && ep.n_div == 0 && ep.bias_n == nullptr;
+    if (simple && nb + 32 <= N) {
+      float* dst = ep.out + m_off + (long long)nb * ep.n_stride;
+      if (ep.n_stride == 1 && ((m_off + nb) & 3) == 0 &&
+          (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) =
+              make_float4(ep.alpha * v[j] + bm, ep.alpha * v[j + 1] + bm,
+                          ep.alpha * v[j + 2] + bm, ep.alpha * v[j + 3] + bm);
+      } else {
+        const long long ns = ep.n_stride;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j * ns] = ep.alpha * v[j] + bm;
+      }
+      return;
+    }
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const int n = nb + j;
+      if (n < N) {
+        float* dst = ep.out + m_off + epi_off(n, ep.n_div, ep.n_stride, ep.n_outer);
+        float r = ep.alpha * v[j] + bm + (ep.bias_n ? ep.bias_n[n] : 0.f);
+        if (ep.beta != 0.f) r += ep.beta * *dst;
+        *dst = r;
+      }
+    }
+  }
+};
+
+// ------------------------------------------------------------- host launch
+// Launches the persistent kernel for problem P: one CTA per SM (fewer when there are fewer
+// tiles).  mc may be null when the problem never stores through TMA.
+template <class P, int BN>
+int launch_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& mb,
+                   const CUtensorMap* mc, const P& prob, long long tiles, cudaStream_t st) {
+  constexpr int STAGES = stages_for(BN);
+  using SL = SmemLayout<BN, STAGES>;
+  if (tiles <= 0) return FLB200_OK;
+  static bool configured[64] = {false};
+  int dev = 0;
+  FLB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_persistent_kernel<P, BN, STAGES>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SL::kTotal));
+    configured[dev] = true;
+  }
+  const long long sms = device_info().sm_count;
+  const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
+  tc_persistent_kernel<P, BN, STAGES><<<grid, kThreads, SL::kTotal, st>>>(
+      ma, mb, mc ? *mc : ma, prob, status_ptr());
+  FLB200_AFTER_LAUNCH(name);
+  count_tc_launch();
+  return FLB200_OK;
+}
+
+}  // namespace tc
+}  // namespace flb200

@@ -1,0 +1,195 @@
+// Problem policies that turn the persistent tcgen05 kernel (tc_kernel.cuh) into implicit-GEMM
+// convolutions over a channels-last (NHWC) copy of the activations.
+//
+// Why channels-last: a filter tap shifts the window by whole pixels.  In NCHW the shifted
+// pixel is the contiguous index, which breaks TMA's 16-byte start rule; in NHWC the shift
+// lands on the w / h coordinates of the tensor map (any value, negative = zero padding for
+// free) and the contiguous coordinate is the channel, always a multiple of 32 here.
+//
+//  PatchConvProblem  (forward, and backward-data with transposed taps)
+//     rows  m = output pixels of a rectangular patch  NB images x PH rows x QW columns = 128
+//     cols  n = output channels
+//     k     = taps x 32-channel chunks:  A = one TMA box [32 c][QW][PH][NB] of the source at
+//             the tap's offset (element strides implement the convolution stride),
+//             B = packed filter [tap][n][c] (K-major)
+//     out   = NCHW, optionally strided (the parity classes of a strided backward-data)
+//
+//  PatchWgradProblem (backward-filter), one GEMM per tap:
+//     rows  m = output channels (A = dy in NHWC, MN-major boxes [32 co][32 pixels])
+//     cols  n = input channels  (B = x in NHWC at the tap's offset, MN-major)
+//     k     = 32-pixel patches (QW x PH) of every image; split over CTAs, partial sums are
+//             reduced in a fixed order by a second kernel.
+#pragma once
+#include "tc_kernel.cuh"
+
+namespace flb200 {
+namespace tc {
+
+constexpr int kMaxTaps = 64;
+
+struct TapTable {
+  short dw[kMaxTaps];   // added to the w coordinate of the A / B box
+  short dh[kMaxTaps];   // added to the h coordinate
+  short wtap[kMaxTaps]; // index of the tap in the packed filter / in the output
+};
+
+template <int BN>
+struct PatchConvProblem {
+  int a_mn_major, b_mn_major;  // 0, 0
+  // patch geometry (all powers of two, NB * PH * QW == 128)
+  int QW, PH, NB, qw_shift, ph_shift;
+  int tiles_q, tiles_p, tiles_b, tiles_n;
+  int pix_w, pix_h, images;  // extent of the pixel grid the rows walk over
+  int n_out;                 // number of output channels (columns)
+  // K loop
+  int cchunks, ntaps;
+  int a_w_mul, a_h_mul;      // A box origin = (q0 * a_w_mul + dw, p0 * a_h_mul + dh)
+  TapTable taps;
+  // output: out[img][co][oh][ow], oh = p * oh_mul + oh_add, ow = q * ow_mul + ow_add
+  float* out;
+  const float* bias;
+  int out_H, out_W, out_C;
+  int oh_mul, oh_add, ow_mul, ow_add;
+  int tma_store;  // 1: out is written through a 4-D TMA store map [w, h, c, n] (unit multipliers)
+
+  struct Tile { int q0, p0, b0, n0; };
+
+  __device__ __forceinline__ int num_tiles() const { return tiles_q * tiles_p * tiles_b * tiles_n; }
+  __device__ __forceinline__ void decode(int tile, Tile& t) const {
+    int r = tile;
+    t.n0 = (r % tiles_n) * BN; r /= tiles_n;
+    t.q0 = (r % tiles_q) * QW; r /= tiles_q;
+    t.p0 = (r % tiles_p) * PH; r /= tiles_p;
+    t.b0 = r * NB;
+  }
+  __device__ __forceinline__ int k_begin(const Tile&) const { return 0; }
+  __device__ __forceinline__ int k_end(const Tile&) const { return ntaps * cchunks; }
+  __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
+                                       const Tile& t, int k, uint64_t* bar, char* a_dst,
+                                       char* b_dst) const {
+    const int tap = k / cchunks, cc = k - tap * cchunks;
+    mbar_expect_tx(bar, (kBM + BN) * kBK * 4);  // NB*PH*QW == 128 rows of 128 bytes + B tile
+    int ca[4] = {cc * kBK, t.q0 * a_w_mul + taps.dw[tap], t.p0 * a_h_mul + taps.dh[tap], t.b0};
+    tma_load(ma, bar, a_dst, 4, ca);
+    int cb[4] = {cc * kBK, t.n0, taps.wtap[tap], 0};
+    tma_load(mb, bar, b_dst, 3, cb);
+  }
+  __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
+    return t.n0 + c0 < n_out;
+  }
+  __device__ __forceinline__ void store(const Tile& t, const EpiCtx& ctx, int c0,
+                                        const float* v) const {
+    const int nb = t.n0 + c0;
+    // row -> (image, p, q) inside the patch
+    const int qw = ctx.row & (QW - 1);
+    const int ph = (ctx.row >> qw_shift) & (PH - 1);
+    const int bi = ctx.row >> (qw_shift + ph_shift);
+    if (tma_store) {
+      float* buf = ctx.staging + ctx.chunk_parity * (kStageTileBytes / 4);
+      if (ctx.lane == 0) bulk_wait_read<1>();
+      __syncwarp();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        float r = v[j];
+        if (bias && nb + j < n_out) r += bias[nb + j];
+        buf[j * 32 + ctx.lane] = r;
+      }
+      fence_proxy_async();
+      __syncwarp();
+      // the warp's 32 rows are 32/QW full patch rows (QW <= 32) or a 32-wide piece of one row
+      const int row0 = ctx.row & ~31;
+      const int q_w = QW >= 32 ? t.q0 + (row0 & (QW - 1)) : t.q0;
+      const int p_w = t.p0 + ((row0 >> qw_shift) & (PH - 1));
+      const int b_w = t.b0 + (row0 >> (qw_shift + ph_shift));
+      if (ctx.lane == 0 && q_w < pix_w && p_w < pix_h && b_w < images) {
+        asm volatile(
+            "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
+                "l"(reinterpret_cast<uint64_t>(ctx.map_c)),
+            "r"(smem_u32(buf)), "r"(q_w), "r"(p_w), "r"(nb), "r"(b_w)
+            : "memory");
+        bulk_commit();
+      }
+      return;
+    }
+    const int q = t.q0 + qw, p = t.p0 + ph, img = t.b0 + bi;
+    if (q >= pix_w || p >= pix_h || img >= images) return;
+    const long long plane = (long long)out_H * out_W;
+    float* dst = out + ((long long)img * out_C + nb) * plane +
+                 (long long)(p * oh_mul + oh_add) * out_W + (q * ow_mul + ow_add);
+    if (nb + 32 <= n_out) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) dst[j * plane] = v[j] + (bias ? bias[nb + j] : 0.f);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < n_out) dst[j * plane] = v[j] + (bias ? bias[nb + j] : 0.f);
+    }
+  }
+};
+
+template <int BN>
+struct PatchWgradProblem {
+  int a_mn_major, b_mn_major;  // 1, 1
+  int QW, PH;                  // 32-pixel patch: QW * PH == 32
+  int tiles_q, tiles_p, images;
+  int tiles_m, tiles_n, M, N;  // M = output channels, N = input channels
+  int ntaps, splits, iters_per_split, k_iters;  // k_iters = images * tiles_p * tiles_q
+  int b_w_mul, b_h_mul;        // B box origin = (q0 * b_w_mul + dw, p0 * b_h_mul + dh)
+  TapTable taps;
+  float* partial;              // [split][tap][M][N]
+
+  struct Tile { int m0, n0, tap, split, k0, k1; };
+
+  __device__ __forceinline__ int num_tiles() const { return tiles_m * tiles_n * ntaps * splits; }
+  __device__ __forceinline__ void decode(int tile, Tile& t) const {
+    int r = tile;
+    t.split = r % splits; r /= splits;
+    t.n0 = (r % tiles_n) * BN; r /= tiles_n;
+    t.m0 = (r % tiles_m) * kBM; r /= tiles_m;
+    t.tap = r;
+    t.k0 = t.split * iters_per_split;
+    t.k1 = min(t.k0 + iters_per_split, k_iters);
+  }
+  __device__ __forceinline__ int k_begin(const Tile& t) const { return t.k0; }
+  __device__ __forceinline__ int k_end(const Tile& t) const { return t.k1; }
+  __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
+                                       const Tile& t, int k, uint64_t* bar, char* a_dst,
+                                       char* b_dst) const {
+    int r = k;
+    const int q0 = (r % tiles_q) * QW; r /= tiles_q;
+    const int p0 = (r % tiles_p) * PH; r /= tiles_p;
+    const int img = r;
+    mbar_expect_tx(bar, (kBM + BN) * kBK * 4);
+#pragma unroll
+    for (int j = 0; j < kBM / 32; ++j) {
+      int c[4] = {t.m0 + 32 * j, q0, p0, img};
+      tma_load(ma, bar, a_dst + j * (kBK * 128), 4, c);
+    }
+    const int bw = q0 * b_w_mul + taps.dw[t.tap], bh = p0 * b_h_mul + taps.dh[t.tap];
+#pragma unroll
+    for (int j = 0; j < BN / 32; ++j) {
+      int c[4] = {t.n0 + 32 * j, bw, bh, img};
+      tma_load(mb, bar, b_dst + j * (kBK * 128), 4, c);
+    }
+  }
+  __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const { return t.n0 + c0 < N; }
+  __device__ __forceinline__ void store(const Tile& t, const EpiCtx& ctx, int c0,
+                                        const float* v) const {
+    const int m = t.m0 + ctx.row;
+    if (m >= M) return;
+    const int nb = t.n0 + c0;
+    float* dst = partial + (((long long)t.split * ntaps + t.tap) * M + m) * N + nb;
+    if (nb + 32 <= N && (N & 3) == 0) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 4)
+        *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (nb + j < N) dst[j] = v[j];
+    }
+  }
+};
+
+}  // namespace tc
+}  // namespace flb200
