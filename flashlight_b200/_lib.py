@@ -82,6 +82,7 @@ SIGNATURES = {
     "flb200_linear_backward_weight": (C.c_int, [i64, i64, i64, vp, vp, vp, C.c_int, vp, sz, vp]),
     "flb200_channel_sum_workspace_bytes": (sz, [i64, i64, i64]),
     "flb200_channel_sum": (C.c_int, [vp, vp, i64, i64, i64, C.c_int, vp, sz, vp]),
+    "flb200_channel_sum_static_scratch": (C.c_int, [vp, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_channel_bias_add": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_relu_forward": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "flb200_relu_backward": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),

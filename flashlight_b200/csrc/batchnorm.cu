@@ -267,6 +267,42 @@ int flb200_channel_sum(const void* in, float* out, int64_t outer, int64_t channe
   return FLB200_OK;
 }
 
+// ---- channel sum for callers that cannot hand over scratch memory ------------------------
+// The partial sums of flb200_channel_sum normally live in scratch the caller allocates.  Some
+// callers have no way to get device memory at the moment of the call: code that runs inside a
+// host framework's memory-manager callback (re-entering the allocator there would deadlock or
+// recurse), an out-of-memory handler, or a plugin host that handed out its whole device budget at
+// start-up and forbids cudaMalloc afterwards.  For them the partials go into this fixed array,
+// which every GPU that loads the library holds from load until the process exits.
+constexpr size_t kStaticScratchBytes = 1u << 20;  // 1 MiB
+static __device__ __align__(256) unsigned char g_channel_sum_scratch[kStaticScratchBytes];
+
+int flb200_channel_sum_static_scratch(const void* in, float* out, int64_t outer, int64_t channels,
+                                      int64_t inner, int dtype, void* stream) {
+  if (int st = check_geo("channel_sum_static_scratch", outer, channels, inner)) return st;
+  const size_t need = channel_partial_bytes(outer, channels, inner);
+  if (need > kStaticScratchBytes)
+    return fail(FLB200_INVALID_ARG,
+                "channel_sum_static_scratch: this shape needs %zu bytes of partial sums, the "
+                "built-in scratch holds %zu; use flb200_channel_sum with caller scratch",
+                need, (size_t)kStaticScratchBytes);
+  // In host code the array's name is only a handle; the device address has to be looked up,
+  // once per device, with that device current.  This happens on the first call per device.
+  static void* device_addr[64] = {nullptr};
+  int dev = 0;
+  FLB200_CUDA_CHECK(cudaGetDevice(&dev));
+  FLB200_REQUIRE(dev >= 0 && dev < 64, "channel_sum_static_scratch: device ordinal %d out of range",
+                 dev);
+  if (!device_addr[dev]) {
+    void* p = nullptr;
+    FLB200_CUDA_CHECK(cudaGetSymbolAddress(&p, g_channel_sum_scratch));
+    device_addr[dev] = p;
+  }
+  // Every partial is written before it is read, so stale contents of earlier calls do no harm.
+  return flb200_channel_sum(in, out, outer, channels, inner, dtype, device_addr[dev],
+                            kStaticScratchBytes, stream);
+}
+
 int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t outer,
                             int64_t channels, int64_t inner, int dtype, void* stream) {
   if (int st = check_geo("channel_bias_add", outer, channels, inner)) return st;

@@ -214,6 +214,18 @@ int flb200_channel_sum(const void* in, float* out, int64_t outer, int64_t channe
                        int64_t inner, int dtype, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* flb200_channel_sum for callers that cannot allocate device memory at the time of the call
+ * (code running inside a framework's memory-manager callback or out-of-memory handler, hosts
+ * that hand out their whole device budget at start-up).  It has no counterpart in the reference.
+ * The partial sums live in a 1 MiB array built into the library (held by every GPU that loads
+ * it, until the process exits); shapes that need more are refused with FLB200_INVALID_ARG — use
+ * flb200_channel_sum with your own scratch for those.  Calls neither cudaMalloc nor cudaFree.
+ * The first call on a device looks up the array's device address; make that first call before
+ * any stream capture begins.  All calls share the one array: two calls that may overlap on the
+ * GPU (different streams, no ordering between them) race and give wrong sums. */
+int flb200_channel_sum_static_scratch(const void* in, float* out, int64_t outer,
+                                      int64_t channels, int64_t inner, int dtype, void* stream);
+
 /* y[o][c][i] = x[o][c][i] + bias[c] (tile + add, Functions.cpp:1270-1275). In place allowed. */
 int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t outer,
                             int64_t channels, int64_t inner, int dtype, void* stream);
