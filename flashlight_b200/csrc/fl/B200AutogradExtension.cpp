@@ -1,0 +1,461 @@
+/*
+ * Host code of B200AutogradExtension: fl::Tensor in, C ABI call, fl::Tensor out.
+ * The structure of each method follows what the cuDNN backend does around its library calls
+ * (flashlight/fl/autograd/tensor/backend/cudnn/Conv2D.cpp:242-357, Pool2D.cpp:17-122,
+ * BatchNorm.cpp:79-265, RNN.cpp:60-373) with the library call replaced by flb200_*.
+ */
+#include "B200AutogradExtension.h"
+
+#include <algorithm>
+#include <cstdlib>
+#include <stdexcept>
+#include <string>
+
+#include "flashlight/fl/common/DevicePtr.h"
+#include "flashlight/fl/tensor/Compute.h"
+#include "flashlight/fl/tensor/TensorBase.h"
+#include "flb200.h"
+
+namespace fl {
+namespace {
+
+// FLB200_INVALID_ARG is a caller error (std::invalid_argument, like cudnnCheckErr for bad
+// parameters: flashlight/fl/autograd/tensor/backend/cudnn/CudnnUtils.cpp:88-99); the rest are
+// run-time failures.
+void check(int status, const char* where) {
+  if (status == FLB200_OK) {
+    return;
+  }
+  const std::string msg = std::string(where) + ": " + flb200_status_string(status) + " - " +
+      flb200_last_error();
+  if (status == FLB200_INVALID_ARG) {
+    throw std::invalid_argument(msg);
+  }
+  throw std::runtime_error(msg);
+}
+
+long long dimOr1(const Tensor& t, int i) {
+  return t.ndim() > i ? t.dim(i) : 1;
+}
+
+void requireF32(const Tensor& t, const char* what) {
+  if (!t.isEmpty() && t.type() != fl::dtype::f32) {
+    throw std::invalid_argument(std::string(what) + ": the B200 extension needs f32 tensors");
+  }
+}
+
+Tensor scratch(size_t bytes) {
+  return Tensor({static_cast<long long>(std::max<size_t>(bytes, 1))}, fl::dtype::b8);
+}
+
+struct PoolPayload : detail::AutogradPayloadData {
+  Tensor argmax; // one byte per output element: selected window position
+};
+
+struct RnnPayload : detail::AutogradPayloadData {
+  Tensor reserve;
+};
+
+flb200_conv2d_desc convDesc(
+    const Tensor& input,
+    const Tensor& weights,
+    int sx, int sy, int px, int py, int dx, int dy, int groups, int mathMode) {
+  flb200_conv2d_desc d;
+  d.W = static_cast<int>(dimOr1(input, 0));
+  d.H = static_cast<int>(dimOr1(input, 1));
+  d.C = static_cast<int>(dimOr1(input, 2));
+  d.N = static_cast<int>(dimOr1(input, 3));
+  d.kW = static_cast<int>(dimOr1(weights, 0));
+  d.kH = static_cast<int>(dimOr1(weights, 1));
+  d.Cout = static_cast<int>(dimOr1(weights, 3));
+  d.sx = sx; d.sy = sy; d.px = px; d.py = py; d.dx = dx; d.dy = dy; d.groups = groups;
+  d.dtype = FLB200_F32;
+  d.math_mode = mathMode;
+  if (dimOr1(weights, 2) * groups != d.C) {
+    throw std::invalid_argument("conv2d: weight channels x groups do not match the input");
+  }
+  return d;
+}
+
+flb200_pool2d_desc poolDesc(
+    const Tensor& input, int wx, int wy, int sx, int sy, int px, int py, PoolingMode mode) {
+  flb200_pool2d_desc d;
+  d.W = static_cast<int>(dimOr1(input, 0));
+  d.H = static_cast<int>(dimOr1(input, 1));
+  d.C = static_cast<int>(dimOr1(input, 2));
+  d.N = static_cast<int>(dimOr1(input, 3));
+  d.wx = wx; d.wy = wy; d.sx = sx; d.sy = sy; d.px = px; d.py = py;
+  d.mode = static_cast<int>(mode);
+  d.dtype = FLB200_F32;
+  return d;
+}
+
+flb200_batchnorm_desc bnDesc(const Tensor& input, const std::vector<int>& axes) {
+  std::vector<int64_t> shape(input.ndim());
+  for (int i = 0; i < input.ndim(); ++i) {
+    shape[i] = input.dim(i);
+  }
+  std::vector<int32_t> ax(axes.begin(), axes.end());
+  flb200_batchnorm_desc d;
+  check(
+      flb200_batchnorm_geometry(
+          shape.data(), input.ndim(), ax.data(), static_cast<int>(ax.size()), &d),
+      "batchnorm");
+  return d;
+}
+
+flb200_rnn_desc rnnDesc(
+    const Tensor& input, int hiddenSize, int numLayers, RnnMode mode, bool bidirectional,
+    int mathMode) {
+  flb200_rnn_desc d;
+  d.input_size = static_cast<int>(dimOr1(input, 0));
+  d.batch = static_cast<int>(dimOr1(input, 1));
+  d.seq_len = static_cast<int>(dimOr1(input, 2));
+  d.hidden_size = hiddenSize;
+  d.num_layers = numLayers;
+  d.mode = static_cast<int>(mode);
+  d.bidirectional = bidirectional ? 1 : 0;
+  d.dtype = FLB200_F32;
+  d.math_mode = mathMode;
+  return d;
+}
+
+void* ptrOrNull(const Tensor& t, DevicePtr& holder) {
+  if (t.isEmpty()) {
+    return nullptr;
+  }
+  holder = DevicePtr(t);
+  return holder.get();
+}
+
+} // namespace
+
+B200AutogradExtension::B200AutogradExtension() : mathMode_(FLB200_MATH_STRICT_F32) {
+  const char* env = std::getenv("FLB200_TF32");
+  if (env && env[0] != '\0' && env[0] != '0') {
+    mathMode_ = FLB200_MATH_TF32;
+  }
+}
+
+const CUDAStream& B200AutogradExtension::stream() {
+  if (!stream_) {
+    stream_ = CUDAStream::createManaged();
+  }
+  return *stream_;
+}
+
+bool B200AutogradExtension::isDataTypeSupported(const fl::dtype& dtype) const {
+  return dtype == fl::dtype::f32;
+}
+
+/**************************** conv2d ****************************/
+Tensor B200AutogradExtension::conv2d(
+    const Tensor& input, const Tensor& weights, const Tensor& bias, const int sx, const int sy,
+    const int px, const int py, const int dx, const int dy, const int groups,
+    std::shared_ptr<detail::AutogradPayload>) {
+  requireF32(input, "conv2d");
+  requireF32(weights, "conv2d");
+  requireF32(bias, "conv2d");
+  const auto d = convDesc(input, weights, sx, sy, px, py, dx, dy, groups, mathMode_);
+  int32_t wo = 0, ho = 0;
+  check(flb200_conv2d_output_dims(&d, &wo, &ho), "conv2d");
+  auto output = Tensor({wo, ho, d.Cout, d.N}, input.type());
+  const size_t wsBytes = flb200_conv2d_workspace_bytes(&d, 0);
+  auto ws = scratch(wsBytes);
+  {
+    DevicePtr inPtr(input), wtPtr(weights), outPtr(output), wsPtr(ws), bsPtr;
+    void* bs = ptrOrNull(bias, bsPtr);
+    const auto& st = stream();
+    relativeSync(st, {input, weights, bias, output, ws});
+    check(
+        flb200_conv2d_forward(
+            &d, inPtr.get(), wtPtr.get(), bs, outPtr.get(), wsPtr.get(), wsBytes, st.handle()),
+        "conv2d");
+    relativeSync({output}, st);
+  }
+  return output;
+}
+
+Tensor B200AutogradExtension::conv2dBackwardData(
+    const Tensor& gradOutput, const Tensor& input, const Tensor& weight, const int sx,
+    const int sy, const int px, const int py, const int dx, const int dy, const int groups,
+    std::shared_ptr<DynamicBenchmark>, std::shared_ptr<detail::AutogradPayload>) {
+  requireF32(gradOutput, "conv2dBackwardData");
+  const auto d = convDesc(input, weight, sx, sy, px, py, dx, dy, groups, mathMode_);
+  auto gradInput = Tensor(input.shape(), input.type());
+  const size_t wsBytes = flb200_conv2d_workspace_bytes(&d, 1);
+  auto ws = scratch(wsBytes);
+  {
+    DevicePtr goPtr(gradOutput), wtPtr(weight), giPtr(gradInput), wsPtr(ws);
+    const auto& st = stream();
+    relativeSync(st, {gradOutput, weight, gradInput, ws});
+    check(
+        flb200_conv2d_backward_data(
+            &d, goPtr.get(), wtPtr.get(), giPtr.get(), wsPtr.get(), wsBytes, st.handle()),
+        "conv2dBackwardData");
+    relativeSync({gradInput}, st);
+  }
+  return gradInput;
+}
+
+std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
+    const Tensor& gradOutput, const Tensor& input, const Tensor& weights, const Tensor& bias,
+    const int sx, const int sy, const int px, const int py, const int dx, const int dy,
+    const int groups, std::shared_ptr<DynamicBenchmark>, std::shared_ptr<DynamicBenchmark>,
+    std::shared_ptr<detail::AutogradPayload>) {
+  requireF32(gradOutput, "conv2dBackwardFilterBias");
+  const auto d = convDesc(input, weights, sx, sy, px, py, dx, dy, groups, mathMode_);
+  auto gradWeights = Tensor(weights.shape(), weights.type());
+  // the bias gradient is skipped when there is no bias (cudnn/Conv2D.cpp:753)
+  Tensor gradBias;
+  if (!bias.isEmpty()) {
+    gradBias = Tensor(bias.shape(), bias.type());
+  }
+  const size_t wsBytes = flb200_conv2d_workspace_bytes(&d, 2);
+  auto ws = scratch(wsBytes);
+  {
+    DevicePtr goPtr(gradOutput), inPtr(input), gwPtr(gradWeights), wsPtr(ws), gbPtr;
+    void* gb = ptrOrNull(gradBias, gbPtr);
+    const auto& st = stream();
+    relativeSync(st, {gradOutput, input, gradWeights, gradBias, ws});
+    check(
+        flb200_conv2d_backward_filter_bias(
+            &d, goPtr.get(), inPtr.get(), gwPtr.get(), gb, wsPtr.get(), wsBytes, st.handle()),
+        "conv2dBackwardFilterBias");
+    relativeSync({gradWeights, gradBias}, st);
+  }
+  return {gradWeights, gradBias};
+}
+
+/**************************** pool2d ****************************/
+Tensor B200AutogradExtension::pool2d(
+    const Tensor& input, const int wx, const int wy, const int sx, const int sy, const int px,
+    const int py, const PoolingMode mode, std::shared_ptr<detail::AutogradPayload> payload) {
+  requireF32(input, "pool2d");
+  const auto d = poolDesc(input, wx, wy, sx, sy, px, py, mode);
+  int32_t wo = 0, ho = 0;
+  check(flb200_pool2d_output_dims(&d, &wo, &ho), "pool2d");
+  auto output = Tensor({wo, ho, d.C, d.N}, input.type());
+  Tensor argmax;
+  if (payload && mode == PoolingMode::MAX) {
+    argmax = Tensor({wo, ho, d.C, d.N}, fl::dtype::u8);
+    auto data = std::make_shared<PoolPayload>();
+    data->argmax = argmax;
+    payload->data = data;
+  }
+  {
+    DevicePtr inPtr(input), outPtr(output), amPtr;
+    void* am = ptrOrNull(argmax, amPtr);
+    const auto& st = stream();
+    relativeSync(st, {input, output, argmax});
+    check(
+        flb200_pool2d_forward(
+            &d, inPtr.get(), outPtr.get(), static_cast<uint8_t*>(am), st.handle()),
+        "pool2d");
+    relativeSync({output, argmax}, st);
+  }
+  return output;
+}
+
+Tensor B200AutogradExtension::pool2dBackward(
+    const Tensor& gradOutput, const Tensor& input, const Tensor& /* poolOutput */, const int wx,
+    const int wy, const int sx, const int sy, const int px, const int py, const PoolingMode mode,
+    std::shared_ptr<detail::AutogradPayload> payload) {
+  requireF32(gradOutput, "pool2dBackward");
+  const auto d = poolDesc(input, wx, wy, sx, sy, px, py, mode);
+  auto gradInput = Tensor(input.shape(), input.type());
+  Tensor argmax;
+  if (payload && payload->data) {
+    argmax = std::static_pointer_cast<PoolPayload>(payload->data)->argmax;
+  }
+  {
+    DevicePtr goPtr(gradOutput), inPtr(input), giPtr(gradInput), amPtr;
+    void* am = ptrOrNull(argmax, amPtr);
+    const auto& st = stream();
+    relativeSync(st, {gradOutput, input, gradInput, argmax});
+    check(
+        flb200_pool2d_backward(
+            &d, goPtr.get(), inPtr.get(), static_cast<const uint8_t*>(am), giPtr.get(),
+            st.handle()),
+        "pool2dBackward");
+    relativeSync({gradInput}, st);
+  }
+  return gradInput;
+}
+
+/**************************** batchnorm ****************************/
+Tensor B200AutogradExtension::batchnorm(
+    Tensor& saveMean, Tensor& saveVar, const Tensor& input, const Tensor& weight,
+    const Tensor& bias, Tensor& runningMean, Tensor& runningVar, const std::vector<int>& axes,
+    const bool train, const double momentum, const double epsilon,
+    std::shared_ptr<detail::AutogradPayload>) {
+  requireF32(input, "batchnorm");
+  requireF32(weight, "batchnorm");
+  requireF32(bias, "batchnorm");
+  auto d = bnDesc(input, axes);
+  const long long features = d.channels;
+  if (!weight.isEmpty() && weight.elements() != features) {
+    throw std::invalid_argument("[BatchNorm] Invalid shape for weight.");
+  }
+  if (!bias.isEmpty() && bias.elements() != features) {
+    throw std::invalid_argument("[BatchNorm] Invalid shape for bias.");
+  }
+  auto output = Tensor(input.shape(), input.type());
+  if (train) {
+    saveMean = Tensor({features}, fl::dtype::f32);
+    saveVar = Tensor({features}, fl::dtype::f32);
+  }
+  const size_t wsBytes = flb200_batchnorm_workspace_bytes(&d);
+  auto ws = scratch(wsBytes);
+  {
+    DevicePtr inPtr(input), outPtr(output), wsPtr(ws), wtPtr, bsPtr, rmPtr, rvPtr, smPtr, svPtr;
+    const auto& st = stream();
+    relativeSync(st, {input, output, weight, bias, runningMean, runningVar, saveMean, saveVar, ws});
+    check(
+        flb200_batchnorm_forward(
+            &d, inPtr.get(), static_cast<const float*>(ptrOrNull(weight, wtPtr)),
+            static_cast<const float*>(ptrOrNull(bias, bsPtr)),
+            static_cast<float*>(ptrOrNull(runningMean, rmPtr)),
+            static_cast<float*>(ptrOrNull(runningVar, rvPtr)),
+            static_cast<float*>(ptrOrNull(saveMean, smPtr)),
+            static_cast<float*>(ptrOrNull(saveVar, svPtr)), train ? 1 : 0, momentum, epsilon,
+            outPtr.get(), wsPtr.get(), wsBytes, st.handle()),
+        "batchnorm");
+    relativeSync({output, runningMean, runningVar, saveMean, saveVar}, st);
+  }
+  return output;
+}
+
+std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::batchnormBackward(
+    const Tensor& gradOutput, const Tensor& saveMean, const Tensor& saveVar, const Tensor& input,
+    const Tensor& weight, const std::vector<int>& axes, const bool train, const float /* eps */,
+    std::shared_ptr<detail::AutogradPayload>) {
+  if (!train) {
+    throw std::logic_error("can't compute batchnorm grad when train was not specified");
+  }
+  requireF32(gradOutput, "batchnormBackward");
+  auto d = bnDesc(input, axes);
+  const long long features = d.channels;
+  auto gradIn = Tensor(input.shape(), input.type());
+  auto gradWt = Tensor({features}, fl::dtype::f32);
+  auto gradBs = Tensor({features}, fl::dtype::f32);
+  const size_t wsBytes = flb200_batchnorm_workspace_bytes(&d);
+  auto ws = scratch(wsBytes);
+  {
+    DevicePtr goPtr(gradOutput), inPtr(input), smPtr(saveMean), svPtr(saveVar), giPtr(gradIn),
+        gwPtr(gradWt), gbPtr(gradBs), wsPtr(ws), wtPtr;
+    const auto& st = stream();
+    relativeSync(st, {gradOutput, input, weight, saveMean, saveVar, gradIn, gradWt, gradBs, ws});
+    check(
+        flb200_batchnorm_backward(
+            &d, goPtr.get(), inPtr.get(), static_cast<const float*>(ptrOrNull(weight, wtPtr)),
+            static_cast<const float*>(smPtr.get()), static_cast<const float*>(svPtr.get()),
+            giPtr.get(), static_cast<float*>(gwPtr.get()), static_cast<float*>(gbPtr.get()),
+            wsPtr.get(), wsBytes, st.handle()),
+        "batchnormBackward");
+    relativeSync({gradIn, gradWt, gradBs}, st);
+  }
+  return std::make_tuple(gradIn, gradWt, gradBs);
+}
+
+/**************************** rnn ****************************/
+std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::rnn(
+    const Tensor& input, const Tensor& hiddenState, const Tensor& cellState,
+    const Tensor& weights, const int hiddenSize, const int numLayers, const RnnMode mode,
+    const bool bidirectional, const float dropout,
+    std::shared_ptr<detail::AutogradPayload> payload) {
+  if (dropout != 0.f) {
+    throw std::invalid_argument("rnn: inter-layer dropout is not built in the B200 extension");
+  }
+  requireF32(input, "rnn");
+  requireF32(weights, "rnn");
+  const auto d = rnnDesc(input, hiddenSize, numLayers, mode, bidirectional, mathMode_);
+  if (weights.elements() != flb200_rnn_num_params(&d)) {
+    throw std::invalid_argument("rnn: invalid weights tensor size");
+  }
+  const auto x = input.asContiguousTensor();
+  const auto hx = hiddenState.isEmpty() ? hiddenState : hiddenState.asContiguousTensor();
+  const auto cx = cellState.isEmpty() ? cellState : cellState.asContiguousTensor();
+  const auto w = weights.asContiguousTensor();
+  const int dirs = bidirectional ? 2 : 1;
+  auto y = Tensor({hiddenSize * dirs, d.batch, d.seq_len}, input.type());
+  auto hy = Tensor({hiddenSize, d.batch, numLayers * dirs}, input.type());
+  Tensor cy;
+  if (mode == RnnMode::LSTM) {
+    cy = Tensor({hiddenSize, d.batch, numLayers * dirs}, input.type());
+  }
+  Tensor reserve;
+  size_t reserveBytes = 0;
+  if (payload) {
+    reserveBytes = flb200_rnn_reserve_bytes(&d);
+    reserve = scratch(reserveBytes);
+    auto data = std::make_shared<RnnPayload>();
+    data->reserve = reserve;
+    payload->data = data;
+  }
+  const size_t wsBytes = flb200_rnn_workspace_bytes(&d, payload ? 0 : 2);
+  auto ws = scratch(wsBytes);
+  {
+    DevicePtr xPtr(x), wPtr(w), yPtr(y), hyPtr(hy), wsPtr(ws), hxPtr, cxPtr, cyPtr, rsPtr;
+    const auto& st = stream();
+    relativeSync(st, {x, hx, cx, w, y, hy, cy, reserve, ws});
+    check(
+        flb200_rnn_forward(
+            &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(), yPtr.get(),
+            hyPtr.get(), ptrOrNull(cy, cyPtr), ptrOrNull(reserve, rsPtr), reserveBytes,
+            wsPtr.get(), wsBytes, st.handle()),
+        "rnn");
+    relativeSync({y, hy, cy, reserve}, st);
+  }
+  return std::make_tuple(y, hy, cy);
+}
+
+std::tuple<Tensor, Tensor, Tensor, Tensor> B200AutogradExtension::rnnBackward(
+    const Tensor& input, const Tensor& hiddenState, const Tensor& cellState,
+    const Tensor& weights, const std::shared_ptr<detail::RNNGradData> gradData,
+    const Tensor& output, const int numLayers, const int hiddenSize, const RnnMode mode,
+    const bool bidirectional, const float /* dropProb */,
+    std::shared_ptr<detail::AutogradPayload> payload) {
+  if (!payload || !payload->data) {
+    throw std::invalid_argument(
+        "B200AutogradExtension::rnnBackward given null detail::AutogradPayload");
+  }
+  const auto d = rnnDesc(input, hiddenSize, numLayers, mode, bidirectional, mathMode_);
+  auto reserve = std::static_pointer_cast<RnnPayload>(payload->data)->reserve;
+  const auto x = input.asContiguousTensor();
+  const auto hx = hiddenState.isEmpty() ? hiddenState : hiddenState.asContiguousTensor();
+  const auto cx = cellState.isEmpty() ? cellState : cellState.asContiguousTensor();
+  const auto w = weights.asContiguousTensor();
+  const auto y = output.asContiguousTensor();
+  // absent output gradients count as zeros (cudnn/RNN.cpp:269-272)
+  const Tensor dy = gradData ? gradData->dy : Tensor();
+  const Tensor dhy = gradData ? gradData->dhy : Tensor();
+  const Tensor dcy = gradData ? gradData->dcy : Tensor();
+  auto dx = Tensor(input.shape(), input.type());
+  const int dirs = bidirectional ? 2 : 1;
+  auto dhx = Tensor({hiddenSize, d.batch, numLayers * dirs}, input.type());
+  Tensor dcx;
+  if (mode == RnnMode::LSTM) {
+    dcx = Tensor({hiddenSize, d.batch, numLayers * dirs}, input.type());
+  }
+  auto dw = Tensor(weights.shape(), weights.type());
+  const size_t wsBytes = flb200_rnn_workspace_bytes(&d, 1);
+  auto ws = scratch(wsBytes);
+  {
+    DevicePtr xPtr(x), wPtr(w), yPtr(y), dxPtr(dx), dhxPtr(dhx), dwPtr(dw), rsPtr(reserve),
+        wsPtr(ws), hxPtr, cxPtr, dyPtr, dhyPtr, dcyPtr, dcxPtr;
+    const auto& st = stream();
+    relativeSync(st, {x, hx, cx, w, y, dy, dhy, dcy, dx, dhx, dcx, dw, reserve, ws});
+    check(
+        flb200_rnn_backward(
+            &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(), yPtr.get(),
+            ptrOrNull(dy, dyPtr), ptrOrNull(dhy, dhyPtr), ptrOrNull(dcy, dcyPtr), dxPtr.get(),
+            dhxPtr.get(), ptrOrNull(dcx, dcxPtr), dwPtr.get(), rsPtr.get(),
+            static_cast<size_t>(reserve.elements()), wsPtr.get(), wsBytes, st.handle()),
+        "rnnBackward");
+    relativeSync({dx, dhx, dcx, dw}, st);
+  }
+  return std::make_tuple(dx, dhx, dcx, dw);
+}
+
+} // namespace fl

@@ -106,3 +106,16 @@ def test_null_and_bad_arguments_return_status_not_crash():
     assert b"unknown reduction" in L.lib.flb200_last_error()
     md = L.MatmulDesc(4, 4, 4, 1, 4, 1, 0, 4, 1, 0, 4, 1, 0, 1.0, 0.0, L.F16, 0)
     assert L.lib.flb200_matmul(C.byref(md), None, None, None, None, 0, None) == L.INVALID_ARG
+
+
+def test_cpp_extension_compiles_against_reference_headers(reference_root):
+    """B200AutogradExtension overrides every pure virtual of fl::AutogradExtension with the exact
+    reference signatures: compiling it against the reference headers is the proof."""
+    import subprocess
+    import sys
+    script = (Path(__file__).resolve().parent.parent / "flashlight_b200" / "csrc" / "fl" /
+              "check_against_reference.py")
+    res = subprocess.run([sys.executable, str(script), str(reference_root)], capture_output=True,
+                         text=True)
+    assert res.returncode == 0, res.stderr
+    assert "compiles against the reference headers" in res.stdout
