@@ -3,6 +3,8 @@
 //
 // Scratch traffic per pass: one transposed copy of the activation operand (8 bytes per
 // element) and a repacked filter; there is no im2col matrix.
+#include <cstdlib>
+
 #include "tc_conv.cuh"
 #include "tc_patch.cuh"
 
@@ -120,13 +122,12 @@ int filter_map(CUtensorMap* m, const float* base, int kext, int kp, int rows, in
 }
 
 template <int BN>
-int launch_patch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
-                 tc::PatchConvProblem<BN>& p, cudaStream_t st) {
+int launch_patch(const CUtensorMap& ma, const CUtensorMap& mb, tc::PatchConvProblem<BN>& p,
+                 cudaStream_t st) {
   p.tiles_n = (p.n_out + BN - 1) / BN;
   const long long tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b * p.tiles_n;
   FLB200_REQUIRE(tiles < 0x7fffffffLL, "patch conv: too many tiles");
-  return tc::launch_problem<tc::PatchConvProblem<BN>, BN>("tc_patch_conv", ma, mb, mc, p, tiles,
-                                                         st);
+  return tc::launch_problem<tc::PatchConvProblem<BN>, BN>("tc_patch_conv", ma, mb, p, tiles, st);
 }
 
 // Fills the parts of the problem that do not depend on BN and launches with the BN that fits
@@ -134,14 +135,13 @@ int launch_patch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap
 struct PatchArgs {
   Patch patch;
   int pix_w, pix_h, images, n_out, cchunks, ntaps, a_w_mul, a_h_mul;
-  tc::TapTable taps;
+  tc::TapGrid taps;
   float* out;
   const float* bias;
   int out_H, out_W, out_C, oh_mul, oh_add, ow_mul, ow_add;
 };
 template <int BN>
-int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
-              const PatchArgs& a, cudaStream_t st) {
+int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, cudaStream_t st) {
   tc::PatchConvProblem<BN> p;
   p.a_mn_major = 0; p.b_mn_major = 0;
   p.QW = a.patch.QW; p.PH = a.patch.PH; p.NB = a.patch.NB;
@@ -155,26 +155,14 @@ int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* m
   p.out = a.out; p.bias = a.bias;
   p.out_H = a.out_H; p.out_W = a.out_W; p.out_C = a.out_C;
   p.oh_mul = a.oh_mul; p.oh_add = a.oh_add; p.ow_mul = a.ow_mul; p.ow_add = a.ow_add;
-  p.tma_store = mc ? 1 : 0;
-  return launch_patch<BN>(ma, mb, mc, p, st);
+  return launch_patch<BN>(ma, mb, p, st);
 }
-int run_patch_any(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
-                  const PatchArgs& a, cudaStream_t st) {
-  if (bn == 32) return run_patch<32>(ma, mb, mc, a, st);
-  if (bn == 64) return run_patch<64>(ma, mb, mc, a, st);
-  return run_patch<128>(ma, mb, mc, a, st);
-}
-
-// Output map [w, h, c, n] for TMA stores of a patch: only when rows of the plane are
-// 16-byte multiples and the patch rows tile the warp's 32 accumulator rows.
-bool out_store_map(CUtensorMap* m, float* out, int W, int H, int C, int N, const Patch& p) {
-  if (W % 4 != 0 || !aligned16(out)) return false;
-  const uint64_t dims[4] = {(uint64_t)W, (uint64_t)H, (uint64_t)C, (uint64_t)N};
-  const uint64_t strides[3] = {(uint64_t)W * 4, (uint64_t)H * W * 4, (uint64_t)C * H * W * 4};
-  const uint32_t box[4] = {(uint32_t)(p.QW < 32 ? p.QW : 32), (uint32_t)(p.QW < 32 ? 32 / p.QW : 1),
-                           32, 1};
-  if (p.QW < 32 && p.PH < 32 / p.QW) return false;  // a warp would span two images
-  return tc::make_tensor_map(m, out, 4, dims, strides, box, tc::kMapStaging) == FLB200_OK;
+int run_patch_any(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a,
+                  cudaStream_t st) {
+  if (bn == 32) return run_patch<32>(ma, mb, a, st);
+  if (bn == 64) return run_patch<64>(ma, mb, a, st);
+  if (bn == 128) return run_patch<128>(ma, mb, a, st);
+  return run_patch<256>(ma, mb, a, st);
 }
 
 struct WgradPlan { int QW, PH, tiles_q, tiles_p, k_iters, splits, ips, bn; size_t partial_bytes; };
@@ -202,7 +190,7 @@ WgradPlan plan_wgrad(const ConvGeo& g) {
 
 template <int BN>
 int run_wgrad(const CUtensorMap& ma, const CUtensorMap& mb, const ConvGeo& g, const WgradPlan& w,
-              const tc::TapTable& taps, float* partial, cudaStream_t st) {
+              float* partial, cudaStream_t st) {
   tc::PatchWgradProblem<BN> p;
   p.a_mn_major = 1; p.b_mn_major = 1;
   p.QW = w.QW; p.PH = w.PH; p.tiles_q = w.tiles_q; p.tiles_p = w.tiles_p; p.images = g.N;
@@ -211,11 +199,11 @@ int run_wgrad(const CUtensorMap& ma, const CUtensorMap& mb, const ConvGeo& g, co
   p.tiles_n = (g.C + BN - 1) / BN;
   p.ntaps = g.RS; p.splits = w.splits; p.iters_per_split = w.ips; p.k_iters = w.k_iters;
   p.b_w_mul = g.sx; p.b_h_mul = g.sy;
-  p.taps = taps;
+  p.kW = g.kW; p.dil_x = g.dx; p.dil_y = g.dy; p.pad_x = g.px; p.pad_y = g.py;
   p.partial = partial;
   const long long tiles = (long long)p.tiles_m * p.tiles_n * p.ntaps * p.splits;
-  return tc::launch_problem<tc::PatchWgradProblem<BN>, BN>("tc_patch_wgrad", ma, mb, nullptr, p,
-                                                          tiles, st);
+  return tc::launch_problem<tc::PatchWgradProblem<BN>, BN>("tc_patch_wgrad", ma, mb, p, tiles,
+                                                          st);
 }
 
 }  // namespace
@@ -223,7 +211,7 @@ int run_wgrad(const CUtensorMap& ma, const CUtensorMap& mb, const ConvGeo& g, co
 // ---------------------------------------------------------------- interface
 bool patch_conv_supported(const ConvGeo& g) {
   // small channel counts would waste most of each 32-wide K chunk: those stay on the gather route
-  return g.groups == 1 && g.RS <= tc::kMaxTaps && g.C >= 16 && g.Cout >= 16 &&
+  return g.groups == 1 && g.RS <= 64 && g.C >= 16 && g.Cout >= 16 &&
          g.sx <= 2 && g.sy <= 2 && g.N <= 65535;
 }
 
@@ -254,24 +242,17 @@ int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const f
   a.cchunks = (g.C + tc::kBK - 1) / tc::kBK;
   a.ntaps = g.RS;
   a.a_w_mul = g.sx; a.a_h_mul = g.sy;
-  for (int r = 0; r < g.kH; ++r)
-    for (int s = 0; s < g.kW; ++s) {
-      const int t = r * g.kW + s;
-      a.taps.dw[t] = (short)(s * g.dx - g.px);
-      a.taps.dh[t] = (short)(r * g.dy - g.py);
-      a.taps.wtap[t] = (short)t;
-    }
+  a.taps = tc::TapGrid{g.kH, g.kW, -g.py, g.dy, -g.px, g.dx, 0, 1, 0, 1, g.kW};
   a.out = y; a.bias = bias;
   a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
   a.oh_mul = 1; a.ow_mul = 1;
   const int bn = tc::pick_bn(g.Cout);
-  CUtensorMap ma, mb, mc;
+  CUtensorMap ma, mb;
   if (int rc = nhwc_map(&ma, xt, g.C, cp, g.W, g.H, g.N, a.patch.QW, a.patch.PH, a.patch.NB, g.sx,
                         g.sy, tc::kMapKMajor))
     return rc;
   if (int rc = filter_map(&mb, wp, g.C, cp, g.Cout, g.RS, bn)) return rc;
-  const bool tma_out = out_store_map(&mc, y, g.Wo, g.Ho, g.Cout, g.N, a.patch);
-  return run_patch_any(bn, ma, mb, tma_out ? &mc : nullptr, a, st);
+  return run_patch_any(bn, ma, mb, a, st);
 }
 
 int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx,
@@ -290,51 +271,56 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
   if (int rc = filter_map(&mb, wd, g.Cout, cop, g.C, g.RS, bn)) return rc;
   // One launch per parity class (a, b) of the input pixel: h = p*sy + a, w = q*sx + b.  Only
   // the taps with (a + py - r*dy) divisible by sy reach that class.
-  // Classes that no tap reaches keep a zero gradient: clear dx first if there is one.
+  // One launch per parity class (a, b) of the input pixel: h = p*sy + a, w = q*sx + b.  Only
+  // the taps with (a + py - r*dy) divisible by sy reach that class; they form an arithmetic
+  // progression in r (and likewise in s).  Classes that no tap reaches keep a zero gradient.
+  struct Prog { int first, step, count, off0, off_step; };
+  auto progression = [](int cls, int pad, int dil, int stride, int kext) {
+    Prog pr{0, 1, 0, 0, 0};
+    int first = -1, second = -1;
+    for (int r = 0; r < kext; ++r)
+      if ((cls + pad - r * dil) % stride == 0) {
+        if (first < 0) first = r;
+        else if (second < 0) second = r;
+        ++pr.count;
+      }
+    if (pr.count == 0) return pr;
+    pr.first = first;
+    pr.step = second >= 0 ? second - first : 1;
+    pr.off0 = (cls + pad - first * dil) / stride;
+    pr.off_step = -(pr.step * dil) / stride;
+    return pr;
+  };
   bool any_empty = false;
   for (int ca = 0; ca < g.sy; ++ca)
-    for (int cb = 0; cb < g.sx; ++cb) {
-      bool hit_h = false, hit_w = false;
-      for (int r = 0; r < g.kH; ++r) hit_h = hit_h || ((ca + g.py - r * g.dy) % g.sy == 0);
-      for (int s = 0; s < g.kW; ++s) hit_w = hit_w || ((cb + g.px - s * g.dx) % g.sx == 0);
-      any_empty = any_empty || !(hit_h && hit_w);
-    }
+    for (int cb = 0; cb < g.sx; ++cb)
+      any_empty = any_empty || progression(ca, g.py, g.dy, g.sy, g.kH).count == 0 ||
+                  progression(cb, g.px, g.dx, g.sx, g.kW).count == 0;
   if (any_empty) FLB200_CUDA_CHECK(cudaMemsetAsync(gx, 0, (size_t)g.N * g.C * g.HW * 4, st));
   for (int ca = 0; ca < g.sy; ++ca)
     for (int cb = 0; cb < g.sx; ++cb) {
+      const Prog ph = progression(ca, g.py, g.dy, g.sy, g.kH);
+      const Prog pw = progression(cb, g.px, g.dx, g.sx, g.kW);
+      if (ph.count == 0 || pw.count == 0) continue;
       PatchArgs a{};
       a.pix_h = (g.H - ca + g.sy - 1) / g.sy;
       a.pix_w = (g.W - cb + g.sx - 1) / g.sx;
       if (a.pix_h <= 0 || a.pix_w <= 0) continue;
-      int nt = 0;
-      for (int r = 0; r < g.kH; ++r) {
-        const int th = ca + g.py - r * g.dy;
-        if (th % g.sy != 0) continue;
-        for (int s = 0; s < g.kW; ++s) {
-          const int tw = cb + g.px - s * g.dx;
-          if (tw % g.sx != 0) continue;
-          a.taps.dh[nt] = (short)(th / g.sy);
-          a.taps.dw[nt] = (short)(tw / g.sx);
-          a.taps.wtap[nt] = (short)(r * g.kW + s);
-          ++nt;
-        }
-      }
-      if (nt == 0) continue;  // no tap reaches this class: it stays zero
+      a.taps = tc::TapGrid{ph.count, pw.count, ph.off0, ph.off_step, pw.off0, pw.off_step,
+                           ph.first, ph.step, pw.first, pw.step, g.kW};
       a.patch = pick_patch(a.pix_w, a.pix_h);
       a.images = g.N; a.n_out = g.C;
       a.cchunks = (g.Cout + tc::kBK - 1) / tc::kBK;
-      a.ntaps = nt;
+      a.ntaps = ph.count * pw.count;
       a.a_w_mul = 1; a.a_h_mul = 1;
       a.out = gx; a.bias = nullptr;
       a.out_H = g.H; a.out_W = g.W; a.out_C = g.C;
       a.oh_mul = g.sy; a.oh_add = ca; a.ow_mul = g.sx; a.ow_add = cb;
-      CUtensorMap ma, mc;
+      CUtensorMap ma;
       if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, a.patch.QW, a.patch.PH,
                             a.patch.NB, 1, 1, tc::kMapKMajor))
         return rc;
-      const bool tma_out = g.sx == 1 && g.sy == 1 &&
-                           out_store_map(&mc, gx, g.W, g.H, g.C, g.N, a.patch);
-      if (int rc = run_patch_any(bn, ma, mb, tma_out ? &mc : nullptr, a, st)) return rc;
+      if (int rc = run_patch_any(bn, ma, mb, a, st)) return rc;
     }
   return FLB200_OK;
 }
@@ -352,14 +338,6 @@ int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x
   float* partial = reinterpret_cast<float*>(base + off);
   if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
   if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
-  tc::TapTable taps{};
-  for (int r = 0; r < g.kH; ++r)
-    for (int s = 0; s < g.kW; ++s) {
-      const int t = r * g.kW + s;
-      taps.dw[t] = (short)(s * g.dx - g.px);
-      taps.dh[t] = (short)(r * g.dy - g.py);
-      taps.wtap[t] = (short)t;
-    }
   CUtensorMap ma, mb;
   if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH, 1, 1, 1,
                         tc::kMapMnMajor))
@@ -368,9 +346,10 @@ int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x
                         tc::kMapMnMajor))
     return rc;
   int rc;
-  if (wp.bn == 32) rc = run_wgrad<32>(ma, mb, g, wp, taps, partial, st);
-  else if (wp.bn == 64) rc = run_wgrad<64>(ma, mb, g, wp, taps, partial, st);
-  else rc = run_wgrad<128>(ma, mb, g, wp, taps, partial, st);
+  if (wp.bn == 32) rc = run_wgrad<32>(ma, mb, g, wp, partial, st);
+  else if (wp.bn == 64) rc = run_wgrad<64>(ma, mb, g, wp, partial, st);
+  else if (wp.bn == 128) rc = run_wgrad<128>(ma, mb, g, wp, partial, st);
+  else rc = run_wgrad<256>(ma, mb, g, wp, partial, st);
   if (rc) return rc;
   wgrad_reduce_kernel<<<grid_for((long long)g.RS * g.Cout * g.C, 256), 256, 0, st>>>(
       partial, gw, g.Cout, g.C, g.RS, wp.splits);

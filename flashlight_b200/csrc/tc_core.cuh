@@ -186,34 +186,32 @@ __host__ __device__ inline uint32_t umma_idesc_tf32(int n, int a_mn_major, int b
          ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
 }
 
-__device__ __forceinline__ void operand_coords(const OperandPlan& p, int mn, int k_iter, int z,
-                                               int* c) {
+// Coordinates of one operand box: every term is a multiply-add with per-dimension
+// multipliers prepared on the host (zero where a term does not apply), so that the single
+// producer thread needs no divisions, no branches and no indexed local arrays per stage.
+__device__ __forceinline__ void operand_coords(const OperandCoords& p, int mn, int k_lo, int k_hi,
+                                               int z, int* c) {
 #pragma unroll
-  for (int d = 0; d < 4; ++d) c[d] = p.base[d];
-  int k_hi = 0, k_lo = k_iter;
-  if (p.k_inner > 0) {
-    k_hi = k_iter / p.k_inner;
-    k_lo = k_iter - k_hi * p.k_inner;
-  }
-  c[p.mn_dim] += mn;
-  c[p.k_dim] += k_lo * kBK;
-  if (p.k2_dim >= 0) c[p.k2_dim] += k_hi * p.k2_scale;
-  if (p.z_dim >= 0) c[p.z_dim] += z;
+  for (int d = 0; d < 4; ++d)
+    c[d] = p.base[d] + mn * p.mn_mul[d] + k_lo * p.k_mul[d] + k_hi * p.k2_mul[d] + z * p.z_mul[d];
 }
 
 // Issues the TMA loads of one operand tile (ROWS = 128 for A, BN for B) into `dst`.
 template <int ROWS>
-__device__ __forceinline__ void load_operand(const CUtensorMap* map, const OperandPlan& p,
-                                             uint64_t* bar, char* dst, int mn0, int k_iter, int z) {
+__device__ __forceinline__ void load_operand(const CUtensorMap* map, const OperandCoords& p,
+                                             uint64_t* bar, char* dst, int mn0, int k_lo, int k_hi,
+                                             int z) {
   int c[4];
+  operand_coords(p, mn0, k_lo, k_hi, z, c);
   if (p.mn_major) {
 #pragma unroll
     for (int j = 0; j < ROWS / 32; ++j) {
-      operand_coords(p, mn0 + 32 * j, k_iter, z, c);
-      tma_load(map, bar, dst + j * (kBK * 128), p.rank, c);
+      int cj[4];
+#pragma unroll
+      for (int d = 0; d < 4; ++d) cj[d] = c[d] + 32 * j * p.mn_mul[d];
+      tma_load(map, bar, dst + j * (kBK * 128), p.rank, cj);
     }
   } else {
-    operand_coords(p, mn0, k_iter, z, c);
     tma_load(map, bar, dst, p.rank, c);
   }
 }

@@ -4,6 +4,7 @@
 // gradients in TF32 mode, by the convolution paths in tc_conv.cu and by rnn.cu.
 #include "tc_gemm.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 #include "tc_kernel.cuh"
@@ -107,13 +108,12 @@ tc_splitk_reduce_kernel(const float* __restrict__ partial, EpiloguePlan ep, int 
 }
 
 template <int BN>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap* mc,
-                       const OperandPlan& pa, const OperandPlan& pb, const EpiloguePlan& ep,
-                       long long M, long long N, long long k_iters, long long Z, const Launch& L,
-                       float* partial, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa,
+                       const OperandPlan& pb, const EpiloguePlan& ep, long long M, long long N,
+                       long long k_iters, long long Z, const Launch& L, float* partial,
+                       cudaStream_t st) {
   GemmProblem<BN> p;
-  p.tma_store = mc ? 1 : 0;
-  p.a = pa; p.b = pb; p.ep = ep;
+  p.a = make_coords(pa); p.b = make_coords(pb); p.ep = ep;
   p.a_mn_major = pa.mn_major; p.b_mn_major = pb.mn_major;
   p.M = (int)M; p.N = (int)N; p.k_iters = (int)k_iters;
   p.splits = L.splits; p.iters_per_split = L.iters_per_split;
@@ -123,13 +123,16 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const CUten
   p.partial = partial;
   const long long tiles = (long long)p.tiles_m * p.tiles_n * Z * L.splits;
   FLB200_REQUIRE(tiles < 0x7fffffffLL, "tc_gemm: too many tiles");
-  return launch_problem<GemmProblem<BN>, BN>("tc_gemm", ma, mb, mc, p, tiles, st);
+  return launch_problem<GemmProblem<BN>, BN>("tc_gemm", ma, mb, p, tiles, st);
 }
 
+// Wider tiles re-read the 128-row operand less often (the contraction is fed from L2):
+// 256 columns as soon as there are enough of them to fill most of such a tile.
 int pick_bn(long long N) {
   if (N <= 32) return 32;
   if (N <= 64) return 64;
-  return 128;
+  if (N < 192) return 128;
+  return 256;
 }
 
 Launch plan_launch(long long M, long long N, long long k_iters, long long Z) {
@@ -164,24 +167,11 @@ int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, con
     L.iters_per_split = (int)k_iters;
   }
   float* partial = static_cast<float*>(ws);
-  // Outputs whose row index m is contiguous ([z][n][m], e.g. NCHW pixels) leave through TMA
-  // stores of 32x32 staging tiles; everything else is stored from registers.
-  CUtensorMap mc_storage;
-  const CUtensorMap* mc = nullptr;
-  if (L.splits == 1 && ep.m_stride == 1 && ep.m_div == 0 && ep.n_div == 0 && ep.beta == 0.f &&
-      ep.alpha == 1.f && ep.bias_m == nullptr && ep.n_stride % 4 == 0 && ep.n_stride >= M &&
-      (Z == 1 || ep.z_stride % 4 == 0) && aligned16(ep.out)) {
-    const uint64_t dims[3] = {(uint64_t)M, (uint64_t)N, (uint64_t)Z};
-    const uint64_t zs = Z == 1 ? (uint64_t)ep.n_stride * (uint64_t)N : (uint64_t)ep.z_stride;
-    const uint64_t strides[2] = {(uint64_t)ep.n_stride * 4, zs * 4};
-    const uint32_t box[3] = {32, 32, 1};
-    if (make_tensor_map(&mc_storage, ep.out, 3, dims, strides, box, kMapStaging) == FLB200_OK)
-      mc = &mc_storage;
-  }
   int rc;
-  if (L.bn == 32) rc = launch_gemm<32>(ma, mb, mc, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
-  else if (L.bn == 64) rc = launch_gemm<64>(ma, mb, mc, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
-  else rc = launch_gemm<128>(ma, mb, mc, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
+  if (L.bn == 32) rc = launch_gemm<32>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
+  else if (L.bn == 64) rc = launch_gemm<64>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
+  else if (L.bn == 128) rc = launch_gemm<128>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
+  else rc = launch_gemm<256>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
   if (rc) return rc;
   if (L.splits > 1) {
     const int rgrid = grid_for(M * N * Z, 256);

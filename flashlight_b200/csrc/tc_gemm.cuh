@@ -33,6 +33,25 @@ struct OperandPlan {
   int base[4];
 };
 
+// The same plan flattened for the device: per-dimension multipliers of the tile offset, the
+// two levels of the k walk and the batch index.
+struct OperandCoords {
+  int rank, mn_major, k_inner;
+  int base[4], mn_mul[4], k_mul[4], k2_mul[4], z_mul[4];
+};
+inline OperandCoords make_coords(const OperandPlan& p) {
+  OperandCoords c{};
+  c.rank = p.rank; c.mn_major = p.mn_major; c.k_inner = p.k_inner;
+  for (int d = 0; d < 4; ++d) {
+    c.base[d] = p.base[d];
+    c.mn_mul[d] = d == p.mn_dim ? 1 : 0;
+    c.k_mul[d] = d == p.k_dim ? kBK : 0;
+    c.k2_mul[d] = d == p.k2_dim ? p.k2_scale : 0;
+    c.z_mul[d] = d == p.z_dim ? 1 : 0;
+  }
+  return c;
+}
+
 struct EpiloguePlan {
   float* out;
   // offset(m) = (m / m_div) * m_outer + (m % m_div) * m_stride   (m_div == 0: m * m_stride);

@@ -5,36 +5,34 @@
 // One CTA per SM walks a static list of 128 x BN output tiles:
 //   warp 0   : TMA producer — one lane issues cp.async.bulk.tensor loads (never multicast)
 //              into a STAGES-deep ring of 128-byte-swizzled shared-memory tiles and runs
-//              ahead into the next output tile while the current one drains
+//              ahead into the next output tile while the current one drains.  Its per-stage
+//              work is a handful of multiply-adds: coordinates advance incrementally.
 //   warp 1   : allocates TMEM (2 accumulators of BN columns); one lane issues tcgen05.mma
 //              for each ready stage and tcgen05.commit to free the stage / publish the tile
-//   warps 2-5: epilogue — tcgen05.ld the finished accumulator (32 lanes each) and write it
-//              out while the MMA warp already fills the other accumulator.  Outputs whose
-//              row index is contiguous in memory go through a per-warp staging tile in
-//              shared memory and a TMA store (the hardware clips ragged edges); the rest
-//              are stored from registers.
+//   warps 2-5: epilogue — tcgen05.ld the finished accumulator (32 lanes each) and store it
+//              from registers (coalesced 128-byte rows when the row index is contiguous in
+//              memory, 16-byte vectors when the column index is) while the MMA warp already
+//              fills the other accumulator
 // Hand-offs: full/empty mbarriers per stage, full/empty mbarriers per accumulator.
 // Every wait is bounded by a clock budget; a wait that runs out raises a flag, all roles
 // drain and the CTA frees its TMEM and returns (the host then reports FLB200_TIMEOUT).
 //
 // A problem policy P tells the skeleton what a tile is:
 //   int  a_mn_major, b_mn_major;
-//   struct Tile;                                   // decoded tile coordinates
+//   struct Tile;  struct LoadState;
 //   __device__ int  num_tiles() const;
 //   __device__ void decode(int tile, Tile&) const;
 //   __device__ int  k_begin(const Tile&) const;  __device__ int k_end(const Tile&) const;
-//   __device__ void load(const CUtensorMap* a, const CUtensorMap* b, const Tile&, int k,
-//                        uint64_t* bar, char* a_dst, char* b_dst) const;   // expect_tx + TMA
-//   __device__ bool chunk_live(const Tile&, int c0) const;                 // warp-uniform
-//   __device__ void store(const Tile&, const EpiCtx&, int c0, const float* v) const;  // 32 cols
+//   __device__ void load_begin(const Tile&, LoadState&) const;     // once per tile
+//   __device__ void load(const CUtensorMap* a, const CUtensorMap* b, const Tile&, LoadState&,
+//                        uint64_t* bar, char* a_dst, char* b_dst) const;  // one stage, advances
+//   __device__ bool chunk_live(const Tile&, int c0) const;                // warp-uniform
+//   __device__ void store(const Tile&, int row, int c0, const float* v) const;  // 32 columns
 #pragma once
 #include "tc_core.cuh"
 
 namespace flb200 {
 namespace tc {
-
-constexpr int kStageTileBytes = 32 * 32 * 4;       // one staging tile: 32 columns x 32 rows
-constexpr int kStagingBytes = 4 * 2 * kStageTileBytes;  // 4 epilogue warps x 2 buffers
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -43,35 +41,25 @@ struct SmemLayout {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTileBytes = STAGES * kStageBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int kTotal = kTileBytes + kStagingBytes + kBarBytes + 1024;  // + align slack
+  static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // + slack to align to 1024
 };
 
-constexpr int stages_for(int bn) { return bn >= 128 ? 5 : 7; }
+// ~200 KB of tiles per CTA
+constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : (bn >= 64 ? 8 : 10)); }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// What an epilogue thread knows about itself.
-struct EpiCtx {
-  const CUtensorMap* map_c;  // output tensor map (TMA-store problems only)
-  float* staging;            // this warp's two 32x32 staging tiles
-  int row;                   // accumulator row (TMEM lane) 0..127 owned by this thread
-  int lane;                  // lane in the warp; row = 32 * quarter + lane
-  uint32_t chunk_parity;     // alternates per stored chunk: selects the staging buffer
-};
-
 template <class P, int BN, int STAGES>
 __global__ void __launch_bounds__(kThreads)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
-                     const __grid_constant__ CUtensorMap map_b,
-                     const __grid_constant__ CUtensorMap map_c, const P prob, int* status) {
+                     const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
   using SL = SmemLayout<BN, STAGES>;
   extern __shared__ char smem_raw[];
   char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                         ~static_cast<uintptr_t>(1023));
-  char* staging = tiles + SL::kTileBytes;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + kStagingBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + SL::kTileBytes);
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;   // [2] accumulator ready for the epilogue
   uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained, MMA may overwrite
@@ -102,26 +90,28 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t s = 0, round = 0;
       typename P::Tile t;
+      typename P::LoadState ls;
       for (int tile = blockIdx.x; tile < n_tiles && *failed == 0; tile += gridDim.x) {
         prob.decode(tile, t);
+        prob.load_begin(t, ls);
         const int k1 = prob.k_end(t);
-        for (int k = prob.k_begin(t); k < k1; ++k, ++it) {
-          const uint32_t s = it % STAGES, round = it / STAGES;
+        for (int k = prob.k_begin(t); k < k1; ++k) {
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
             *failed = 1;
             break;
           }
           char* a_dst = tiles + s * SL::kStageBytes;
-          prob.load(&map_a, &map_b, t, k, &full_bar[s], a_dst, a_dst + SL::kABytes);
+          prob.load(&map_a, &map_b, t, ls, &full_bar[s], a_dst, a_dst + SL::kABytes);
+          if (++s == STAGES) { s = 0; ++round; }
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_tf32(BN, prob.a_mn_major, prob.b_mn_major);
-      uint32_t it = 0, nt = 0;
+      uint32_t s = 0, round = 0, nt = 0;
       typename P::Tile t;
       for (int tile = blockIdx.x; tile < n_tiles && *failed == 0; tile += gridDim.x, ++nt) {
         prob.decode(tile, t);
@@ -133,8 +123,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int k0 = prob.k_begin(t), k1 = prob.k_end(t);
-        for (int k = k0; k < k1; ++k, ++it) {
-          const uint32_t s = it % STAGES, round = it / STAGES;
+        for (int k = k0; k < k1; ++k) {
           if (!mbar_wait(&full_bar[s], round & 1)) {
             *failed = 2;
             break;
@@ -155,6 +144,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             umma_tf32(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
+          if (++s == STAGES) { s = 0; ++round; }
         }
         umma_commit(&tfull_bar[acc]);  // accumulator complete
       }
@@ -162,12 +152,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   } else {
     // epilogue warps 2..5 own TMEM lanes 32*(warp % 4) .. +31
     const int quarter = warp & 3;
-    EpiCtx ctx;
-    ctx.map_c = &map_c;
-    ctx.staging = reinterpret_cast<float*>(staging + quarter * 2 * kStageTileBytes);
-    ctx.row = quarter * 32 + lane;
-    ctx.lane = lane;
-    ctx.chunk_parity = 0;
+    const int row = quarter * 32 + lane;
     uint32_t nt = 0;
     typename P::Tile t;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++nt) {
@@ -185,15 +170,12 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!prob.chunk_live(t, c0)) break;  // uniform across the warp
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
-        prob.store(t, ctx, c0, v);
-        ctx.chunk_parity ^= 1u;
+        prob.store(t, row, c0, v);
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
     }
-    // staging tiles must stay intact until the TMA stores that read them are done
-    if (lane == 0) bulk_wait<0>();
   }
 
   tc_fence_before();
@@ -210,15 +192,15 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 // together share the (large) A tile through L2.
 template <int BN>
 struct GemmProblem {
-  OperandPlan a, b;
+  OperandCoords a, b;
   EpiloguePlan ep;
   int a_mn_major, b_mn_major;
   int M, N, k_iters, splits, iters_per_split;
   int tiles_m, tiles_n, Z;
-  int tma_store;   // 1: output is [z][n][m] with m contiguous, written through map_c
   float* partial;  // split-K scratch [z*splits + s][M][N]
 
   struct Tile { int m0, n0, z, split, k0, k1; };
+  struct LoadState { int a_lo, a_hi, b_lo, b_hi; };
 
   __device__ __forceinline__ int num_tiles() const { return tiles_m * tiles_n * Z * splits; }
   __device__ __forceinline__ void decode(int tile, Tile& t) const {
@@ -232,41 +214,29 @@ struct GemmProblem {
   }
   __device__ __forceinline__ int k_begin(const Tile& t) const { return t.k0; }
   __device__ __forceinline__ int k_end(const Tile& t) const { return t.k1; }
+  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls) const {
+    ls.a_hi = a.k_inner > 0 ? t.k0 / a.k_inner : 0;
+    ls.a_lo = t.k0 - ls.a_hi * a.k_inner;
+    ls.b_hi = b.k_inner > 0 ? t.k0 / b.k_inner : 0;
+    ls.b_lo = t.k0 - ls.b_hi * b.k_inner;
+  }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
-                                       const Tile& t, int k, uint64_t* bar, char* a_dst,
+                                       const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
                                        char* b_dst) const {
     mbar_expect_tx(bar, (kBM + BN) * kBK * 4);
-    load_operand<kBM>(ma, a, bar, a_dst, t.m0, k, t.z);
-    load_operand<BN>(mb, b, bar, b_dst, t.n0, k, t.z);
+    load_operand<kBM>(ma, a, bar, a_dst, t.m0, ls.a_lo, ls.a_hi, t.z);
+    load_operand<BN>(mb, b, bar, b_dst, t.n0, ls.b_lo, ls.b_hi, t.z);
+    if (++ls.a_lo == a.k_inner) { ls.a_lo = 0; ++ls.a_hi; }
+    if (++ls.b_lo == b.k_inner) { ls.b_lo = 0; ++ls.b_hi; }
   }
   __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
     return t.n0 + c0 < N;
   }
 
-  __device__ __forceinline__ void store(const Tile& t, const EpiCtx& ctx, int c0,
-                                        const float* v) const {
-    const int m = t.m0 + ctx.row;
-    const int nb = t.n0 + c0;
-    if (tma_store) {
-      // staging tile [32 columns][32 rows]: lanes write consecutive floats of one column
-      float* buf = ctx.staging + ctx.chunk_parity * (kStageTileBytes / 4);
-      if (ctx.lane == 0) bulk_wait_read<1>();  // the store that used this buffer has read it
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float r = v[j];
-        if (ep.bias_n && nb + j < N) r += ep.bias_n[nb + j];
-        buf[j * 32 + ctx.lane] = r;
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (ctx.lane == 0 && t.m0 + (ctx.row & ~31) < M) {  // a box past the last row has nothing to write
-        tma_store_3d(ctx.map_c, buf, t.m0 + (ctx.row & ~31), nb, t.z);
-        bulk_commit();
-      }
-      return;
-    }
+  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v) const {
+    const int m = t.m0 + row;
     if (m >= M) return;
+    const int nb = t.n0 + c0;
     if (splits > 1) {
       float* dst = partial + ((long long)(t.z * splits + t.split) * M + m) * N + nb;
       if (nb + 32 <= N && (N & 3) == 0) {
@@ -284,7 +254,16 @@ struct GemmProblem {
     const long long m_off =
         epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) + (long long)t.z * ep.z_stride;
     const float bm = ep.bias_m ? ep.bias_m[m] : 0.f;
-    const bool simple = ep.beta == 0.f && ep.n_div == 0 && ep.bias_n == nullptr;
+    const bool simple = ep.beta == 0.f && ep.n_div == 0;
+    if (simple && nb + 32 <= N && ep.bias_n != nullptr) {
+      // strided columns with a per-column bias (convolution output planes)
+      float* dst = ep.out + m_off + (long long)nb * ep.n_stride;
+      const long long ns = ep.n_stride;
+      const float* bn = ep.bias_n + nb;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) dst[j * ns] = ep.alpha * v[j] + bm + bn[j];
+      return;
+    }
     if (simple && nb + 32 <= N) {
       float* dst = ep.out + m_off + (long long)nb * ep.n_stride;
       if (ep.n_stride == 1 && ((m_off + nb) & 3) == 0 &&
@@ -315,11 +294,10 @@ struct GemmProblem {
 };
 
 // ------------------------------------------------------------- host launch
-// Launches the persistent kernel for problem P: one CTA per SM (fewer when there are fewer
-// tiles).  mc may be null when the problem never stores through TMA.
+// Launches the persistent kernel for problem P: one CTA per SM (fewer when there are fewer tiles).
 template <class P, int BN>
-int launch_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& mb,
-                   const CUtensorMap* mc, const P& prob, long long tiles, cudaStream_t st) {
+int launch_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& mb, const P& prob,
+                   long long tiles, cudaStream_t st) {
   constexpr int STAGES = stages_for(BN);
   using SL = SmemLayout<BN, STAGES>;
   if (tiles <= 0) return FLB200_OK;
@@ -334,8 +312,8 @@ int launch_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& m
   }
   const long long sms = device_info().sm_count;
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  tc_persistent_kernel<P, BN, STAGES><<<grid, kThreads, SL::kTotal, st>>>(
-      ma, mb, mc ? *mc : ma, prob, status_ptr());
+  tc_persistent_kernel<P, BN, STAGES><<<grid, kThreads, SL::kTotal, st>>>(ma, mb, prob,
+                                                                          status_ptr());
   FLB200_AFTER_LAUNCH(name);
   count_tc_launch();
   return FLB200_OK;

@@ -12,7 +12,9 @@
 //     k     = taps x 32-channel chunks:  A = one TMA box [32 c][QW][PH][NB] of the source at
 //             the tap's offset (element strides implement the convolution stride),
 //             B = packed filter [tap][n][c] (K-major)
-//     out   = NCHW, optionally strided (the parity classes of a strided backward-data)
+//     out   = NCHW, optionally strided (the parity classes of a strided backward-data);
+//             lanes of a warp hold consecutive pixels of a row, so each column is stored
+//             as one coalesced run per patch row
 //
 //  PatchWgradProblem (backward-filter), one GEMM per tap:
 //     rows  m = output channels (A = dy in NHWC, MN-major boxes [32 co][32 pixels])
@@ -25,12 +27,14 @@
 namespace flb200 {
 namespace tc {
 
-constexpr int kMaxTaps = 64;
-
-struct TapTable {
-  short dw[kMaxTaps];   // added to the w coordinate of the A / B box
-  short dh[kMaxTaps];   // added to the h coordinate
-  short wtap[kMaxTaps]; // index of the tap in the packed filter / in the output
+// The taps a launch walks form a grid: tap (i, j) reads the source at offset
+// (dh0 + i*dh_step, dw0 + j*dw_step) and uses filter element (r0 + i*r_step, s0 + j*s_step).
+// Forward: every (r, s).  A parity class of a strided backward-data: the arithmetic
+// progressions of r and s whose offsets divide by the stride.
+struct TapGrid {
+  int ni, nj;
+  int dh0, dh_step, dw0, dw_step;
+  int r0, r_step, s0, s_step, kW;
 };
 
 template <int BN>
@@ -44,15 +48,15 @@ struct PatchConvProblem {
   // K loop
   int cchunks, ntaps;
   int a_w_mul, a_h_mul;      // A box origin = (q0 * a_w_mul + dw, p0 * a_h_mul + dh)
-  TapTable taps;
+  TapGrid taps;
   // output: out[img][co][oh][ow], oh = p * oh_mul + oh_add, ow = q * ow_mul + ow_add
   float* out;
   const float* bias;
   int out_H, out_W, out_C;
   int oh_mul, oh_add, ow_mul, ow_add;
-  int tma_store;  // 1: out is written through a 4-D TMA store map [w, h, c, n] (unit multipliers)
 
   struct Tile { int q0, p0, b0, n0; };
+  struct LoadState { int i, j, cc, aw, ah, wtap; };
 
   __device__ __forceinline__ int num_tiles() const { return tiles_q * tiles_p * tiles_b * tiles_n; }
   __device__ __forceinline__ void decode(int tile, Tile& t) const {
@@ -64,61 +68,57 @@ struct PatchConvProblem {
   }
   __device__ __forceinline__ int k_begin(const Tile&) const { return 0; }
   __device__ __forceinline__ int k_end(const Tile&) const { return ntaps * cchunks; }
+  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls) const {
+    ls.i = 0;
+    ls.j = 0;
+    ls.cc = 0;
+    ls.aw = t.q0 * a_w_mul + taps.dw0;
+    ls.ah = t.p0 * a_h_mul + taps.dh0;
+    ls.wtap = taps.r0 * taps.kW + taps.s0;
+  }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
-                                       const Tile& t, int k, uint64_t* bar, char* a_dst,
+                                       const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
                                        char* b_dst) const {
-    const int tap = k / cchunks, cc = k - tap * cchunks;
     mbar_expect_tx(bar, (kBM + BN) * kBK * 4);  // NB*PH*QW == 128 rows of 128 bytes + B tile
-    int ca[4] = {cc * kBK, t.q0 * a_w_mul + taps.dw[tap], t.p0 * a_h_mul + taps.dh[tap], t.b0};
+    int ca[4] = {ls.cc * kBK, ls.aw, ls.ah, t.b0};
     tma_load(ma, bar, a_dst, 4, ca);
-    int cb[4] = {cc * kBK, t.n0, taps.wtap[tap], 0};
+    int cb[4] = {ls.cc * kBK, t.n0, ls.wtap, 0};
     tma_load(mb, bar, b_dst, 3, cb);
+    if (++ls.cc == cchunks) {  // next tap: j fastest
+      ls.cc = 0;
+      ls.aw += taps.dw_step;
+      ls.wtap += taps.s_step;
+      if (++ls.j == taps.nj) {
+        ls.j = 0;
+        ++ls.i;
+        ls.aw -= taps.nj * taps.dw_step;
+        ls.ah += taps.dh_step;
+        ls.wtap += taps.r_step * taps.kW - taps.nj * taps.s_step;
+      }
+    }
   }
   __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
     return t.n0 + c0 < n_out;
   }
-  __device__ __forceinline__ void store(const Tile& t, const EpiCtx& ctx, int c0,
-                                        const float* v) const {
+  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v) const {
     const int nb = t.n0 + c0;
     // row -> (image, p, q) inside the patch
-    const int qw = ctx.row & (QW - 1);
-    const int ph = (ctx.row >> qw_shift) & (PH - 1);
-    const int bi = ctx.row >> (qw_shift + ph_shift);
-    if (tma_store) {
-      float* buf = ctx.staging + ctx.chunk_parity * (kStageTileBytes / 4);
-      if (ctx.lane == 0) bulk_wait_read<1>();
-      __syncwarp();
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        float r = v[j];
-        if (bias && nb + j < n_out) r += bias[nb + j];
-        buf[j * 32 + ctx.lane] = r;
-      }
-      fence_proxy_async();
-      __syncwarp();
-      // the warp's 32 rows are 32/QW full patch rows (QW <= 32) or a 32-wide piece of one row
-      const int row0 = ctx.row & ~31;
-      const int q_w = QW >= 32 ? t.q0 + (row0 & (QW - 1)) : t.q0;
-      const int p_w = t.p0 + ((row0 >> qw_shift) & (PH - 1));
-      const int b_w = t.b0 + (row0 >> (qw_shift + ph_shift));
-      if (ctx.lane == 0 && q_w < pix_w && p_w < pix_h && b_w < images) {
-        asm volatile(
-            "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
-                "l"(reinterpret_cast<uint64_t>(ctx.map_c)),
-            "r"(smem_u32(buf)), "r"(q_w), "r"(p_w), "r"(nb), "r"(b_w)
-            : "memory");
-        bulk_commit();
-      }
-      return;
-    }
-    const int q = t.q0 + qw, p = t.p0 + ph, img = t.b0 + bi;
+    const int q = t.q0 + (row & (QW - 1));
+    const int p = t.p0 + ((row >> qw_shift) & (PH - 1));
+    const int img = t.b0 + (row >> (qw_shift + ph_shift));
     if (q >= pix_w || p >= pix_h || img >= images) return;
     const long long plane = (long long)out_H * out_W;
     float* dst = out + ((long long)img * out_C + nb) * plane +
                  (long long)(p * oh_mul + oh_add) * out_W + (q * ow_mul + ow_add);
     if (nb + 32 <= n_out) {
+      if (bias) {
+        const float* bn = bias + nb;
 #pragma unroll
-      for (int j = 0; j < 32; ++j) dst[j * plane] = v[j] + (bias ? bias[nb + j] : 0.f);
+        for (int j = 0; j < 32; ++j) dst[j * plane] = v[j] + bn[j];
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j * plane] = v[j];
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 32; ++j)
@@ -135,10 +135,11 @@ struct PatchWgradProblem {
   int tiles_m, tiles_n, M, N;  // M = output channels, N = input channels
   int ntaps, splits, iters_per_split, k_iters;  // k_iters = images * tiles_p * tiles_q
   int b_w_mul, b_h_mul;        // B box origin = (q0 * b_w_mul + dw, p0 * b_h_mul + dh)
-  TapTable taps;
+  int kW, dil_x, dil_y, pad_x, pad_y;  // tap t = (r, s) = (t / kW, t % kW): dw = s*dil_x - pad_x
   float* partial;              // [split][tap][M][N]
 
   struct Tile { int m0, n0, tap, split, k0, k1; };
+  struct LoadState { int qi, pi, img, dw, dh; };
 
   __device__ __forceinline__ int num_tiles() const { return tiles_m * tiles_n * ntaps * splits; }
   __device__ __forceinline__ void decode(int tile, Tile& t) const {
@@ -152,30 +153,39 @@ struct PatchWgradProblem {
   }
   __device__ __forceinline__ int k_begin(const Tile& t) const { return t.k0; }
   __device__ __forceinline__ int k_end(const Tile& t) const { return t.k1; }
+  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls) const {
+    int r = t.k0;
+    ls.qi = r % tiles_q; r /= tiles_q;
+    ls.pi = r % tiles_p; r /= tiles_p;
+    ls.img = r;
+    const int tr = t.tap / kW, ts = t.tap - tr * kW;
+    ls.dw = ts * dil_x - pad_x;
+    ls.dh = tr * dil_y - pad_y;
+  }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
-                                       const Tile& t, int k, uint64_t* bar, char* a_dst,
+                                       const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
                                        char* b_dst) const {
-    int r = k;
-    const int q0 = (r % tiles_q) * QW; r /= tiles_q;
-    const int p0 = (r % tiles_p) * PH; r /= tiles_p;
-    const int img = r;
+    const int q0 = ls.qi * QW, p0 = ls.pi * PH;
     mbar_expect_tx(bar, (kBM + BN) * kBK * 4);
 #pragma unroll
     for (int j = 0; j < kBM / 32; ++j) {
-      int c[4] = {t.m0 + 32 * j, q0, p0, img};
+      int c[4] = {t.m0 + 32 * j, q0, p0, ls.img};
       tma_load(ma, bar, a_dst + j * (kBK * 128), 4, c);
     }
-    const int bw = q0 * b_w_mul + taps.dw[t.tap], bh = p0 * b_h_mul + taps.dh[t.tap];
+    const int bw = q0 * b_w_mul + ls.dw, bh = p0 * b_h_mul + ls.dh;
 #pragma unroll
     for (int j = 0; j < BN / 32; ++j) {
-      int c[4] = {t.n0 + 32 * j, bw, bh, img};
+      int c[4] = {t.n0 + 32 * j, bw, bh, ls.img};
       tma_load(mb, bar, b_dst + j * (kBK * 128), 4, c);
+    }
+    if (++ls.qi == tiles_q) {
+      ls.qi = 0;
+      if (++ls.pi == tiles_p) { ls.pi = 0; ++ls.img; }
     }
   }
   __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const { return t.n0 + c0 < N; }
-  __device__ __forceinline__ void store(const Tile& t, const EpiCtx& ctx, int c0,
-                                        const float* v) const {
-    const int m = t.m0 + ctx.row;
+  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v) const {
+    const int m = t.m0 + row;
     if (m >= M) return;
     const int nb = t.n0 + c0;
     float* dst = partial + (((long long)t.split * ntaps + t.tap) * M + m) * N + nb;
