@@ -412,7 +412,12 @@ def main() -> None:
     if args.impl == "reference":
         run_reference_arm(args)
     else:
-        run_gpu_arm(args)
+        try:
+            run_gpu_arm(args)
+        finally:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized():
+                dist.destroy_process_group()
 
 
 if __name__ == "__main__":

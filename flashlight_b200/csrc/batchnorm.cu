@@ -13,6 +13,7 @@
 #include "channel_ops.cuh"
 
 namespace flb200 {
+
 namespace {
 
 // ------------------------------------------------------------ functors

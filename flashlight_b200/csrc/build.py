@@ -76,13 +76,17 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     srcs = sources()
     with ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
         objs = list(pool.map(lambda s: _compile(s, verbose), srcs))
-    newest = max(o.stat().st_mtime for o in objs)
-    if force or not LIB.exists() or LIB.stat().st_mtime < newest:
+    # The link step is cheap and depends on the SET of objects too (a removed source must
+    # disappear from the library), so compare against a manifest rather than mtimes only.
+    manifest = OBJ_DIR / "link.manifest"
+    want = "\n".join(f"{o.name}:{o.stat().st_mtime_ns}" for o in objs)
+    if force or not LIB.exists() or not manifest.exists() or manifest.read_text() != want:
         cmd = [_nvcc(), "-shared", "-o", str(LIB), *map(str, objs),
                "-gencode", "arch=compute_100a,code=sm_100a"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+        manifest.write_text(want)
     return LIB
 
 

@@ -139,6 +139,58 @@ __global__ void __launch_bounds__(256) pool_backward_kernel(const T* __restrict_
   }
 }
 
+// Max-pooling gradient with the argmax payload, the hot case of the workloads.  A thread owns
+// a strip of four adjacent input pixels of one plane (one 16-byte store) and walks the few
+// windows that overlap the strip once, decoding where each window sent its gradient; planes
+// come from blockIdx.y so all index arithmetic is 32-bit.
+template <typename T>
+__global__ void __launch_bounds__(256)
+pool_backward_max_strip_kernel(const T* __restrict__ dy, const uint8_t* __restrict__ argmax,
+                               T* __restrict__ dx, PoolGeo g) {
+  const int strips_w = (g.W + 3) >> 2;
+  const int strips = strips_w * g.H;
+  const int in_plane = g.H * g.W, out_plane = g.Ho * g.Wo;
+  const bool vec_ok = (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0 &&
+                      sizeof(T) == 4;
+  for (long long plane = blockIdx.y; plane < g.planes; plane += gridDim.y) {
+    const T* dyp = dy + plane * out_plane;
+    const uint8_t* ap = argmax + plane * out_plane;
+    T* dxp = dx + plane * in_plane;
+    for (int si = blockIdx.x * blockDim.x + threadIdx.x; si < strips;
+         si += gridDim.x * blockDim.x) {
+      const int h = si / strips_w, w0 = (si - h * strips_w) << 2;
+      const int p_lo = max(ceil_div_pos(h + g.py - g.wy + 1, g.sy), 0);
+      const int p_hi = min((h + g.py) / g.sy, g.Ho - 1);
+      const int q_lo = max(ceil_div_pos(w0 + g.px - g.wx + 1, g.sx), 0);
+      const int q_hi = min((w0 + 3 + g.px) / g.sx, g.Wo - 1);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int p = p_lo; p <= p_hi; ++p) {
+        const int ky_mine = h + g.py - p * g.sy;
+        for (int q = q_lo; q <= q_hi; ++q) {
+          const int o = p * g.Wo + q;
+          const int sel = ap[o];
+          const int ky = sel / g.wx, kx = sel - ky * g.wx;
+          const int wt = q * g.sx - g.px + kx - w0;  // position inside the strip
+          if (ky == ky_mine && wt >= 0 && wt < 4) {
+            const float v = Num<T>::to_f(dyp[o]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (wt == j) acc[j] += v;
+          }
+        }
+      }
+      T* dst = dxp + h * g.W + w0;
+      if (vec_ok) {
+        *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (w0 + j < g.W) dst[j] = Num<T>::from_f(acc[j]);
+      }
+    }
+  }
+}
+
 int make_geo(const char* name, const flb200_pool2d_desc* d, PoolGeo* g) {
   FLB200_REQUIRE(d, "%s: null descriptor", name);
   FLB200_REQUIRE(d->W >= 1 && d->H >= 1 && d->C >= 1 && d->N >= 1, "%s: empty input", name);
@@ -211,6 +263,14 @@ int flb200_pool2d_backward(const flb200_pool2d_desc* d, const void* grad_y, cons
   const long long total = g.planes * g.H * g.W;
   const int grid = grid_for(total, 256);
   cudaStream_t st = as_stream(stream);
+  if (d->mode == FLB200_POOL_MAX && argmax && d->dtype == FLB200_F32) {
+    const int strips = ((g.W + 3) / 4) * g.H;
+    dim3 sgrid((unsigned)((strips + 255) / 256), (unsigned)(g.planes < 32768 ? g.planes : 32768));
+    pool_backward_max_strip_kernel<float><<<sgrid, 256, 0, st>>>(
+        static_cast<const float*>(grad_y), argmax, static_cast<float*>(grad_x), g);
+    FLB200_AFTER_LAUNCH("pool2d_backward_max");
+    return FLB200_OK;
+  }
   switch (d->dtype) {
     case FLB200_F32:
       pool_backward_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(grad_y),
