@@ -186,6 +186,7 @@ size_t tc_conv_workspace_bytes(const ConvGeo& g, int which) {
     return tc::plan_launch(g.Cout, g.C, k_iters, 1).workspace_bytes;
   }
   if (patch_conv_supported(g)) return patch_conv_workspace_bytes(g, which);
+  if (which != 1 && window_conv_supported(g)) return window_conv_workspace_bytes(g, which);
   const GeneralSizes s = general_sizes(g);
   if (which == 0) {
     return up256((size_t)s.kc * s.ld_out * 4) + up256((size_t)g.Cout * s.kp * 4) +
@@ -204,6 +205,8 @@ bool tc_conv_supported(const ConvGeo& g, int which, size_t workspace_bytes) {
   if (g.groups != 1) return false;
   if (direct_1x1(g)) return true;  // scratch only speeds up backward-filter (split-K)
   if (patch_conv_supported(g)) return workspace_bytes >= patch_conv_workspace_bytes(g, which);
+  if (which != 1 && window_conv_supported(g))
+    return workspace_bytes >= window_conv_workspace_bytes(g, which);
   const GeneralSizes s = general_sizes(g);
   if (s.kc > 65535 || s.k2 > 65535) return false;               // gather grids index k in y
   if (s.ld_out >= 0x7fffffffLL || s.ld_in >= 0x7fffffffLL) return false;
@@ -230,6 +233,7 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
                    st);
   }
   if (patch_conv_supported(g)) return patch_conv_forward(g, x, w, bias, y, ws, ws_bytes, st);
+  if (window_conv_supported(g)) return window_conv_forward(g, x, w, bias, y, ws, ws_bytes, st);
   const GeneralSizes s = general_sizes(g);
   char* base = static_cast<char*>(ws);
   float* col = reinterpret_cast<float*>(base);
@@ -319,6 +323,8 @@ int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, f
     return tc::run(ma, mb, pa, pb, ep, g.Cout, g.C, (long long)g.N * k_inner, 1, ws, ws_bytes, st);
   }
   if (patch_conv_supported(g)) return patch_conv_backward_filter(g, gy, x, gw, ws, ws_bytes, st);
+  if (window_conv_supported(g))
+    return window_conv_backward_filter(g, gy, x, gw, ws, ws_bytes, st);
   const GeneralSizes s = general_sizes(g);
   const int bn = tc::pick_bn(s.kc);
   char* base = static_cast<char*>(ws);

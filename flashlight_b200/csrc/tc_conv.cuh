@@ -36,4 +36,14 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
 int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
                                void* ws, size_t ws_bytes, cudaStream_t st);
 
+// Few-channel "row window" route (<= 4 input channels, e.g. the ResNet stem): forward and
+// backward-filter only; returns a non-zero status without launching anything if the driver
+// refuses the overlapping tensor map, so that the caller can take another route.
+bool window_conv_supported(const ConvGeo& g);
+size_t window_conv_workspace_bytes(const ConvGeo& g, int which);
+int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
+                        float* y, void* ws, size_t ws_bytes, cudaStream_t st);
+int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
+                                void* ws, size_t ws_bytes, cudaStream_t st);
+
 }  // namespace flb200

@@ -113,6 +113,21 @@ int nhwc_map(CUtensorMap* m, const float* base, int C, int cp, int W, int H, int
   return tc::make_tensor_map(m, base, 4, dims, strides, box, mode, es);
 }
 
+// The same tensor with the channel index split into (32 contiguous channels, group of 32):
+// [32, w, h, n, ceil(C / 32)].  One box of nbox groups lands in shared memory as nbox
+// consecutive [pixels][32 channels] blocks, the layout of an MN-major operand.  Channels past
+// C of the last group read the neighbouring pixel (or the bytes after the tensor, which the
+// callers keep inside their workspace); such rows / columns of the product are never stored.
+int nhwc_map5(CUtensorMap* m, const float* base, int C, int cp, int W, int H, int N, int box_w,
+              int box_h, int nbox, int sx, int sy) {
+  const uint64_t dims[5] = {32, (uint64_t)W, (uint64_t)H, (uint64_t)N, (uint64_t)((C + 31) / 32)};
+  const uint64_t strides[4] = {(uint64_t)cp * 4, (uint64_t)W * cp * 4, (uint64_t)H * W * cp * 4,
+                               128};
+  const uint32_t box[5] = {32, (uint32_t)(box_w * sx), (uint32_t)(box_h * sy), 1, (uint32_t)nbox};
+  const uint32_t es[5] = {1, (uint32_t)sx, (uint32_t)sy, 1, 1};
+  return tc::make_tensor_map(m, base, 5, dims, strides, box, tc::kMapMnMajor, es);
+}
+
 // Packed filter map [k, rows, taps].
 int filter_map(CUtensorMap* m, const float* base, int kext, int kp, int rows, int taps, int bn) {
   const uint64_t dims[3] = {(uint64_t)kext, (uint64_t)rows, (uint64_t)taps};
@@ -165,16 +180,33 @@ int run_patch_any(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const Pa
   return run_patch<256>(ma, mb, a, st);
 }
 
-struct WgradPlan { int QW, PH, tiles_q, tiles_p, k_iters, splits, ips, bn; size_t partial_bytes; };
-WgradPlan plan_wgrad(const ConvGeo& g) {
+struct WgradPlan {
+  int QW, PH, tiles_q, tiles_p, k_iters, splits, ips, bn;
+  int tg, tap_groups, cn_shift, tiles_n;
+  size_t partial_bytes;
+};
+// C = columns per tap, taps = number of taps (the window route passes 32 and kH).
+WgradPlan plan_wgrad(const ConvGeo& g, int C, int taps) {
   WgradPlan w;
   pick_k_patch(g.Wo, g.Ho, &w.QW, &w.PH);
   w.tiles_q = (g.Wo + w.QW - 1) / w.QW;
   w.tiles_p = (g.Ho + w.PH - 1) / w.PH;
   w.k_iters = g.N * w.tiles_p * w.tiles_q;
-  w.bn = tc::pick_bn(g.C);
-  const long long out_tiles = (long long)((g.Cout + tc::kBM - 1) / tc::kBM) *
-                              ((g.C + w.bn - 1) / w.bn) * g.RS;
+  const int cboxes = (C + 31) / 32;
+  if (cboxes >= 8) {
+    w.cn_shift = 3; w.tg = 1; w.tap_groups = taps; w.bn = 256;
+    w.tiles_n = (C + 255) / 256;
+  } else {
+    w.cn_shift = log2i(cboxes);
+    const int tg_max = 8 >> w.cn_shift;
+    w.tap_groups = (taps + tg_max - 1) / tg_max;
+    w.tg = (taps + w.tap_groups - 1) / w.tap_groups;
+    w.bn = tc::pick_bn(32 * (w.tg << w.cn_shift));
+    if (w.bn == 128 && 32 * (w.tg << w.cn_shift) > 128) w.bn = 256;
+    w.tiles_n = 1;
+  }
+  const long long out_tiles =
+      (long long)((g.Cout + tc::kBM - 1) / tc::kBM) * w.tiles_n * w.tap_groups;
   const long long target = 2LL * device_info().sm_count;
   long long splits = (target + out_tiles - 1) / out_tiles;
   const long long max_by_k = w.k_iters / 16 > 0 ? w.k_iters / 16 : 1;
@@ -184,26 +216,133 @@ WgradPlan plan_wgrad(const ConvGeo& g) {
   splits = (w.k_iters + ips - 1) / ips;
   w.splits = (int)splits;
   w.ips = (int)ips;
-  w.partial_bytes = (size_t)splits * g.RS * g.Cout * g.C * 4;
+  w.partial_bytes = (size_t)splits * taps * g.Cout * C * 4;
   return w;
 }
+WgradPlan plan_wgrad(const ConvGeo& g) { return plan_wgrad(g, g.C, g.RS); }
+
+inline int wgrad_a_boxes(int Cout) { return Cout >= tc::kBM ? tc::kBM / 32 : (Cout + 31) / 32; }
+
+// Tap geometry of a backward-filter launch: tap t = (t / kW, t % kW) reads x at
+// (s * dil_x - pad_x, r * dil_y - pad_y) from the output pixel's origin.
+struct WgradTaps { int C, ntaps, kW, dil_x, dil_y, pad_x, pad_y; };
 
 template <int BN>
-int run_wgrad(const CUtensorMap& ma, const CUtensorMap& mb, const ConvGeo& g, const WgradPlan& w,
-              float* partial, cudaStream_t st) {
+int run_wgrad(const CUtensorMap& ma, const CUtensorMap& mb, const ConvGeo& g, const WgradTaps& tp,
+              const WgradPlan& w, float* partial, cudaStream_t st) {
   tc::PatchWgradProblem<BN> p;
   p.a_mn_major = 1; p.b_mn_major = 1;
   p.QW = w.QW; p.PH = w.PH; p.tiles_q = w.tiles_q; p.tiles_p = w.tiles_p; p.images = g.N;
-  p.M = g.Cout; p.N = g.C;
+  p.M = g.Cout; p.N = tp.C;
   p.tiles_m = (g.Cout + tc::kBM - 1) / tc::kBM;
-  p.tiles_n = (g.C + BN - 1) / BN;
-  p.ntaps = g.RS; p.splits = w.splits; p.iters_per_split = w.ips; p.k_iters = w.k_iters;
+  p.tiles_n = w.tiles_n;
+  p.ntaps = tp.ntaps; p.tap_groups = w.tap_groups; p.tg = w.tg; p.cn_shift = w.cn_shift;
+  p.a_nbox = wgrad_a_boxes(g.Cout);
+  p.splits = w.splits; p.iters_per_split = w.ips; p.k_iters = w.k_iters;
   p.b_w_mul = g.sx; p.b_h_mul = g.sy;
-  p.kW = g.kW; p.dil_x = g.dx; p.dil_y = g.dy; p.pad_x = g.px; p.pad_y = g.py;
+  p.kW = tp.kW; p.dil_x = tp.dil_x; p.dil_y = tp.dil_y; p.pad_x = tp.pad_x; p.pad_y = tp.pad_y;
   p.partial = partial;
-  const long long tiles = (long long)p.tiles_m * p.tiles_n * p.ntaps * p.splits;
+  const long long tiles = (long long)p.tiles_m * p.tiles_n * p.tap_groups * p.splits;
   return tc::launch_problem<tc::PatchWgradProblem<BN>, BN>("tc_patch_wgrad", ma, mb, p, tiles,
                                                           st);
+}
+int run_wgrad_any(const CUtensorMap& ma, const CUtensorMap& mb, const ConvGeo& g,
+                  const WgradTaps& tp, const WgradPlan& w, float* partial, cudaStream_t st) {
+  if (w.bn == 32) return run_wgrad<32>(ma, mb, g, tp, w, partial, st);
+  if (w.bn == 64) return run_wgrad<64>(ma, mb, g, tp, w, partial, st);
+  if (w.bn == 128) return run_wgrad<128>(ma, mb, g, tp, w, partial, st);
+  return run_wgrad<256>(ma, mb, g, tp, w, partial, st);
+}
+
+// ------------------------------------------------ few-channel "row window" route
+// With <= 4 input channels a 32-channel K chunk would be almost empty.  Instead the K index
+// runs over (s, c): in a zero-padded NHWC copy with 4 channels per pixel the kW taps of one
+// filter row are 4*kW <= 32 CONTIGUOUS floats, so one 128-byte row of the A tile is a window
+// of 8 pixels starting at the output pixel's first tap.  Windows of neighbouring output
+// pixels overlap; the tensor map expresses that with a pixel stride (16 bytes) smaller than
+// the window extent.  The filter rows r are the taps of the implicit GEMM (k_iters = kH).
+constexpr int kWinPixels = 8;  // 32 floats / 4 channels
+
+// dst[n][hp][wp] = (x[n][0..C)[hp-py][wp-px], 0...) as one float4, zero outside the image.
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc4_pad_kernel(const float* __restrict__ x, float4* __restrict__ dst, int C, int H,
+                         int W, int Hp, int Wp, int py, int px, long long total) {
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total;
+       t += (long long)gridDim.x * blockDim.x) {
+    const int wp = (int)(t % Wp);
+    const long long r2 = t / Wp;
+    const int hp = (int)(r2 % Hp);
+    const long long n = r2 / Hp;
+    const int h = hp - py, w = wp - px;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (h >= 0 && h < H && w >= 0 && w < W) {
+      for (int c = 0; c < C; ++c) v[c] = x[((n * C + c) * H + h) * W + w];
+    }
+    dst[t] = make_float4(v[0], v[1], v[2], v[3]);
+  }
+}
+
+// wr[r][co][s*4 + c] = w[co][c][r][s], zero elsewhere (32 floats per row).
+__global__ void pack_filter_rows_kernel(const float* __restrict__ w, float* __restrict__ wr,
+                                        int Cout, int C, int kH, int kW) {
+  const int total = kH * Cout * 32;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+    const int j = t & 31, co = (t >> 5) % Cout, r = (t >> 5) / Cout;
+    const int s = j >> 2, c = j & 3;
+    wr[t] = (s < kW && c < C) ? w[((co * C + c) * kH + r) * kW + s] : 0.f;
+  }
+}
+
+// gw[co][c][r][s] = sum over splits of partial[split][co][r*32 + s*4 + c]
+__global__ void window_wgrad_reduce_kernel(const float* __restrict__ partial,
+                                           float* __restrict__ gw, int Cout, int C, int kH, int kW,
+                                           int splits) {
+  const int total = Cout * C * kH * kW;
+  const long long per_split = (long long)kH * Cout * 32;
+  for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < total; t += gridDim.x * blockDim.x) {
+    const int s = t % kW, r = (t / kW) % kH, c = (t / (kW * kH)) % C, co = t / (kW * kH * C);
+    const long long src = ((long long)co * kH + r) * 32 + s * 4 + c;
+    float acc = 0.f;
+    for (int sp = 0; sp < splits; ++sp) acc += partial[(long long)sp * per_split + src];
+    gw[t] = acc;
+  }
+}
+
+struct WindowGeo { int Hp, Wp, starts; };
+WindowGeo window_geo(const ConvGeo& g) {
+  WindowGeo w;
+  w.Hp = g.H + 2 * g.py;
+  w.Wp = g.W + 2 * g.px;
+  const int need = (g.Wo - 1) * g.sx + kWinPixels;
+  if (w.Wp < need) w.Wp = need;
+  w.starts = w.Wp - (kWinPixels - 1);
+  return w;
+}
+
+// [32-float window, window start pixel, padded row, image]: the pixel stride (16 bytes) is
+// smaller than the window, i.e. the rows of the view overlap.
+int window_map(CUtensorMap* m, const float* base, const WindowGeo& wg, int N, int box_w, int box_h,
+               int box_n, int sx, int sy) {
+  const uint64_t dims[4] = {32, (uint64_t)wg.starts, (uint64_t)wg.Hp, (uint64_t)N};
+  const uint64_t strides[3] = {16, (uint64_t)wg.Wp * 16, (uint64_t)wg.Hp * wg.Wp * 16};
+  const uint32_t box[4] = {32, (uint32_t)(box_w * sx), (uint32_t)(box_h * sy), (uint32_t)box_n};
+  const uint32_t es[4] = {1, (uint32_t)sx, (uint32_t)sy, 1};
+  return tc::make_tensor_map(m, base, 4, dims, strides, box, tc::kMapKMajor, es);
+}
+
+// Backward-filter view: a fifth index r (the filter row) steps dy padded rows, so one copy
+// of nbox >= kH groups brings the windows of every filter row of a 32-pixel patch as the
+// [pixels][32] blocks of an MN-major operand.  Row p*sy + r*dy can pass the image's last
+// padded row only for patch rows p >= Ho, where dy is zero and what is read instead (the next
+// image, or the bytes after the tensor inside the workspace) is finite.
+int window_rows_map(CUtensorMap* m, const float* base, const WindowGeo& wg, int N, int box_w,
+                    int box_h, int nbox, int sx, int sy, int kH, int dil_y) {
+  const uint64_t dims[5] = {32, (uint64_t)wg.starts, (uint64_t)wg.Hp, (uint64_t)N, (uint64_t)kH};
+  const uint64_t strides[4] = {16, (uint64_t)wg.Wp * 16, (uint64_t)wg.Hp * wg.Wp * 16,
+                               (uint64_t)dil_y * wg.Wp * 16};
+  const uint32_t box[5] = {32, (uint32_t)(box_w * sx), (uint32_t)(box_h * sy), 1, (uint32_t)nbox};
+  const uint32_t es[5] = {1, (uint32_t)sx, (uint32_t)sy, 1, 1};
+  return tc::make_tensor_map(m, base, 5, dims, strides, box, tc::kMapMnMajor, es);
 }
 
 }  // namespace
@@ -339,21 +478,111 @@ int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x
   if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
   if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
   CUtensorMap ma, mb;
-  if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH, 1, 1, 1,
-                        tc::kMapMnMajor))
+  if (int rc = nhwc_map5(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH,
+                         wgrad_a_boxes(g.Cout), 1, 1))
     return rc;
-  if (int rc = nhwc_map(&mb, xt, g.C, cp, g.W, g.H, g.N, wp.QW, wp.PH, 1, g.sx, g.sy,
-                        tc::kMapMnMajor))
+  if (int rc = nhwc_map5(&mb, xt, g.C, cp, g.W, g.H, g.N, wp.QW, wp.PH, 1 << wp.cn_shift, g.sx,
+                         g.sy))
     return rc;
-  int rc;
-  if (wp.bn == 32) rc = run_wgrad<32>(ma, mb, g, wp, partial, st);
-  else if (wp.bn == 64) rc = run_wgrad<64>(ma, mb, g, wp, partial, st);
-  else if (wp.bn == 128) rc = run_wgrad<128>(ma, mb, g, wp, partial, st);
-  else rc = run_wgrad<256>(ma, mb, g, wp, partial, st);
-  if (rc) return rc;
+  const WgradTaps tp{g.C, g.RS, g.kW, g.dx, g.dy, g.px, g.py};
+  if (int rc = run_wgrad_any(ma, mb, g, tp, wp, partial, st)) return rc;
   wgrad_reduce_kernel<<<grid_for((long long)g.RS * g.Cout * g.C, 256), 256, 0, st>>>(
       partial, gw, g.Cout, g.C, g.RS, wp.splits);
   FLB200_AFTER_LAUNCH("wgrad_reduce");
+  return FLB200_OK;
+}
+
+// ------------------------------------------------------- row-window interface
+bool window_conv_supported(const ConvGeo& g) {
+  if (!(g.groups == 1 && g.C <= 4 && g.kW <= kWinPixels && g.dx == 1 && g.Cout >= 16 &&
+        g.kH <= 8 && g.sx <= 2 && g.sy <= 2 && g.N <= 65535))
+    return false;
+  // Rows of the window view overlap (pixel stride < window extent).  Encoding a map reads no
+  // memory, so ask the driver up front, with a placeholder base, whether it takes this view;
+  // if not, the caller uses the gather route.
+  const WindowGeo wg = window_geo(g);
+  const Patch pt = pick_patch(g.Wo, g.Ho);
+  int qw, ph;
+  pick_k_patch(g.Wo, g.Ho, &qw, &ph);
+  CUtensorMap m;
+  const float* placeholder = reinterpret_cast<const float*>(uintptr_t(1) << 30);
+  return window_map(&m, placeholder, wg, g.N, pt.QW, pt.PH, pt.NB, g.sx, g.sy) == 0 &&
+         window_rows_map(&m, placeholder, wg, g.N, qw, ph, 8, g.sx, g.sy, g.kH, g.dy) == 0;
+}
+
+size_t window_conv_workspace_bytes(const ConvGeo& g, int which) {
+  const WindowGeo wg = window_geo(g);
+  const size_t xtp = up256((size_t)g.N * wg.Hp * wg.Wp * 16);
+  if (which == 0) return xtp + up256((size_t)g.kH * g.Cout * 32 * 4);
+  const int cop = up4(g.Cout);
+  // the backward-filter GEMM has 32 columns per tap and kH taps
+  return xtp + up256((size_t)g.N * g.HoWo * cop * 4) +
+         up256(plan_wgrad(g, 32 * g.kH, 1).partial_bytes);
+}
+
+int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
+                        float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+  (void)ws_bytes;
+  const WindowGeo wg = window_geo(g);
+  char* base = static_cast<char*>(ws);
+  float* xtp = reinterpret_cast<float*>(base);
+  float* wr = reinterpret_cast<float*>(base + up256((size_t)g.N * wg.Hp * wg.Wp * 16));
+  PatchArgs a{};
+  a.patch = pick_patch(g.Wo, g.Ho);
+  CUtensorMap ma, mb;
+  // the overlapping view is the one thing here the driver may refuse: check before launching
+  if (int rc = window_map(&ma, xtp, wg, g.N, a.patch.QW, a.patch.PH, a.patch.NB, g.sx, g.sy))
+    return rc;
+  const int bn = tc::pick_bn(g.Cout);
+  if (int rc = filter_map(&mb, wr, 32, 32, g.Cout, g.kH, bn)) return rc;
+  const long long total = (long long)g.N * wg.Hp * wg.Wp;
+  nchw_to_nhwc4_pad_kernel<<<grid_for(total, 256), 256, 0, st>>>(
+      x, reinterpret_cast<float4*>(xtp), g.C, g.H, g.W, wg.Hp, wg.Wp, g.py, g.px, total);
+  FLB200_AFTER_LAUNCH("nchw_to_nhwc4_pad");
+  pack_filter_rows_kernel<<<grid_for(g.kH * g.Cout * 32, 256), 256, 0, st>>>(w, wr, g.Cout, g.C,
+                                                                            g.kH, g.kW);
+  FLB200_AFTER_LAUNCH("pack_filter_rows");
+  a.pix_w = g.Wo; a.pix_h = g.Ho; a.images = g.N; a.n_out = g.Cout;
+  a.cchunks = 1;
+  a.ntaps = g.kH;
+  a.a_w_mul = g.sx; a.a_h_mul = g.sy;
+  a.taps = tc::TapGrid{g.kH, 1, 0, g.dy, 0, 0, 0, 1, 0, 0, 1};  // tap r: row offset r*dy, filter row r
+  a.out = y; a.bias = bias;
+  a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
+  a.oh_mul = 1; a.ow_mul = 1;
+  return run_patch_any(bn, ma, mb, a, st);
+}
+
+int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
+                                void* ws, size_t ws_bytes, cudaStream_t st) {
+  (void)ws_bytes;
+  const WindowGeo wg = window_geo(g);
+  const int cop = up4(g.Cout);
+  const WgradPlan wp = plan_wgrad(g, 32 * g.kH, 1);
+  char* base = static_cast<char*>(ws);
+  float* xtp = reinterpret_cast<float*>(base);
+  size_t off = up256((size_t)g.N * wg.Hp * wg.Wp * 16);
+  float* gyt = reinterpret_cast<float*>(base + off);
+  off += up256((size_t)g.N * g.HoWo * cop * 4);
+  float* partial = reinterpret_cast<float*>(base + off);
+  CUtensorMap ma, mb;
+  if (int rc = window_rows_map(&mb, xtp, wg, g.N, wp.QW, wp.PH, 1 << wp.cn_shift, g.sx, g.sy, g.kH,
+                               g.dy)) return rc;
+  if (int rc = nhwc_map5(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH,
+                         wgrad_a_boxes(g.Cout), 1, 1))
+    return rc;
+  const long long total = (long long)g.N * wg.Hp * wg.Wp;
+  nchw_to_nhwc4_pad_kernel<<<grid_for(total, 256), 256, 0, st>>>(
+      x, reinterpret_cast<float4*>(xtp), g.C, g.H, g.W, wg.Hp, wg.Wp, g.py, g.px, total);
+  FLB200_AFTER_LAUNCH("nchw_to_nhwc4_pad");
+  if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+  // One GEMM: M = Cout, N = kH blocks of 32 window floats, K = pixels.  The filter rows are
+  // the channel groups of the view, so the launch has a single tap at offset zero.
+  const WgradTaps tp{32 * g.kH, 1, 1, 1, 1, 0, 0};
+  if (int rc = run_wgrad_any(ma, mb, g, tp, wp, partial, st)) return rc;
+  window_wgrad_reduce_kernel<<<grid_for((long long)g.Cout * g.C * g.RS, 256), 256, 0, st>>>(
+      partial, gw, g.Cout, g.C, g.kH, g.kW, wp.splits);
+  FLB200_AFTER_LAUNCH("window_wgrad_reduce");
   return FLB200_OK;
 }
 

@@ -167,7 +167,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
       if (*failed != 0) break;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
-        if (!prob.chunk_live(t, c0)) break;  // uniform across the warp
+        if (!prob.chunk_live(t, c0)) continue;  // uniform across the warp; need not be a prefix
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
         prob.store(t, row, c0, v);

@@ -16,9 +16,11 @@
 //             lanes of a warp hold consecutive pixels of a row, so each column is stored
 //             as one coalesced run per patch row
 //
-//  PatchWgradProblem (backward-filter), one GEMM per tap:
+//  PatchWgradProblem (backward-filter), one GEMM per group of taps:
 //     rows  m = output channels (A = dy in NHWC, MN-major boxes [32 co][32 pixels])
-//     cols  n = input channels  (B = x in NHWC at the tap's offset, MN-major)
+//     cols  n = (tap of the group, input channel)  (B = x in NHWC at each tap's offset,
+//             MN-major); layers with few input channels put several taps side by side so
+//             that the dy tile is loaded once for all of them
 //     k     = 32-pixel patches (QW x PH) of every image; split over CTAs, partial sums are
 //             reduced in a fixed order by a second kernel.
 #pragma once
@@ -133,21 +135,29 @@ struct PatchWgradProblem {
   int QW, PH;                  // 32-pixel patch: QW * PH == 32
   int tiles_q, tiles_p, images;
   int tiles_m, tiles_n, M, N;  // M = output channels, N = input channels
-  int ntaps, splits, iters_per_split, k_iters;  // k_iters = images * tiles_p * tiles_q
+  // The BN columns of a tile are tg taps x (1 << cn_shift) boxes of 32 input channels, so a
+  // narrow layer shares one load of dy between several taps.
+  int ntaps, tap_groups, tg, cn_shift;
+  int a_nbox;                  // 32-channel boxes of dy per copy: min(4, ceil(M / 32))
+  int splits, iters_per_split, k_iters;  // k_iters = images * tiles_p * tiles_q
   int b_w_mul, b_h_mul;        // B box origin = (q0 * b_w_mul + dw, p0 * b_h_mul + dh)
   int kW, dil_x, dil_y, pad_x, pad_y;  // tap t = (r, s) = (t / kW, t % kW): dw = s*dil_x - pad_x
   float* partial;              // [split][tap][M][N]
 
-  struct Tile { int m0, n0, tap, split, k0, k1; };
-  struct LoadState { int qi, pi, img, dw, dh; };
+  struct Tile { int m0, n0, tap0, ntap, cn_live, split, k0, k1; };
+  struct LoadState { int qi, pi, img, dw0, dh0, s0; };
 
-  __device__ __forceinline__ int num_tiles() const { return tiles_m * tiles_n * ntaps * splits; }
+  __device__ __forceinline__ int num_tiles() const {
+    return tiles_m * tiles_n * tap_groups * splits;
+  }
   __device__ __forceinline__ void decode(int tile, Tile& t) const {
     int r = tile;
     t.split = r % splits; r /= splits;
     t.n0 = (r % tiles_n) * BN; r /= tiles_n;
     t.m0 = (r % tiles_m) * kBM; r /= tiles_m;
-    t.tap = r;
+    t.tap0 = r * tg;
+    t.ntap = min(tg, ntaps - t.tap0);
+    t.cn_live = min(1 << cn_shift, (N - t.n0 + 31) >> 5);
     t.k0 = t.split * iters_per_split;
     t.k1 = min(t.k0 + iters_per_split, k_iters);
   }
@@ -158,45 +168,59 @@ struct PatchWgradProblem {
     ls.qi = r % tiles_q; r /= tiles_q;
     ls.pi = r % tiles_p; r /= tiles_p;
     ls.img = r;
-    const int tr = t.tap / kW, ts = t.tap - tr * kW;
-    ls.dw = ts * dil_x - pad_x;
-    ls.dh = tr * dil_y - pad_y;
+    const int tr = t.tap0 / kW;
+    ls.s0 = t.tap0 - tr * kW;
+    ls.dw0 = ls.s0 * dil_x - pad_x;
+    ls.dh0 = tr * dil_y - pad_y;
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
                                        char* b_dst) const {
     const int q0 = ls.qi * QW, p0 = ls.pi * PH;
-    mbar_expect_tx(bar, (kBM + BN) * kBK * 4);
-#pragma unroll
-    for (int j = 0; j < kBM / 32; ++j) {
-      int c[4] = {t.m0 + 32 * j, q0, p0, ls.img};
-      tma_load(ma, bar, a_dst + j * (kBK * 128), 4, c);
-    }
-    const int bw = q0 * b_w_mul + ls.dw, bh = p0 * b_h_mul + ls.dh;
+    const int bw = q0 * b_w_mul, bh = p0 * b_h_mul;
+    // The channel index is split into (32 contiguous channels, group of 32) in both maps, so
+    // one copy brings every 32 x 32 box of an operand: a_nbox boxes of dy, and per tap
+    // 1 << cn_shift boxes of x.  Boxes past the last channel are zero-filled or hold a
+    // neighbouring pixel's channels; they only reach accumulator rows / columns that the
+    // epilogue never stores.
+    mbar_expect_tx(bar, (a_nbox + (t.ntap << cn_shift)) * (kBK * 128));
+    int ca[5] = {0, q0, p0, ls.img, t.m0 >> 5};
+    tma_load(ma, bar, a_dst, 5, ca);
+    int dw = ls.dw0, dh = ls.dh0, s = ls.s0;
 #pragma unroll
     for (int j = 0; j < BN / 32; ++j) {
-      int c[4] = {t.n0 + 32 * j, bw, bh, ls.img};
-      tma_load(mb, bar, b_dst + j * (kBK * 128), 4, c);
+      if (j < t.ntap) {
+        int cb[5] = {0, bw + dw, bh + dh, ls.img, t.n0 >> 5};
+        tma_load(mb, bar, b_dst + (j << cn_shift) * (kBK * 128), 5, cb);
+        dw += dil_x;
+        if (++s == kW) { s = 0; dw -= kW * dil_x; dh += dil_y; }
+      }
     }
     if (++ls.qi == tiles_q) {
       ls.qi = 0;
       if (++ls.pi == tiles_p) { ls.pi = 0; ++ls.img; }
     }
   }
-  __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const { return t.n0 + c0 < N; }
+  __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
+    const int j = c0 >> 5;
+    return (j >> cn_shift) < t.ntap && (j & ((1 << cn_shift) - 1)) < t.cn_live;
+  }
   __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v) const {
     const int m = t.m0 + row;
     if (m >= M) return;
-    const int nb = t.n0 + c0;
-    float* dst = partial + (((long long)t.split * ntaps + t.tap) * M + m) * N + nb;
+    const int j = c0 >> 5;
+    const int tap = t.tap0 + (j >> cn_shift);
+    const int nb = t.n0 + ((j & ((1 << cn_shift) - 1)) << 5);
+    float* dst = partial + (((long long)t.split * ntaps + tap) * M + m) * N + nb;
     if (nb + 32 <= N && (N & 3) == 0) {
 #pragma unroll
-      for (int j = 0; j < 32; j += 4)
-        *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      for (int jj = 0; jj < 32; jj += 4)
+        *reinterpret_cast<float4*>(dst + jj) =
+            make_float4(v[jj], v[jj + 1], v[jj + 2], v[jj + 3]);
     } else {
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (nb + j < N) dst[j] = v[j];
+      for (int jj = 0; jj < 32; ++jj)
+        if (nb + jj < N) dst[jj] = v[jj];
     }
   }
 };

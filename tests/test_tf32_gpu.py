@@ -131,6 +131,9 @@ TF32_CONV_CASES = [
     (2, 256, 14, 14, 512, 1, 1, 2, 2, 0, 0, 1, 1, 1, True),   # 1x1 stride 2 downsample
     (2, 3, 32, 32, 64, 7, 7, 2, 2, 3, 3, 1, 1, 1, True),      # stem: K = 147 (padded filter rows)
     (4, 1, 28, 28, 32, 5, 5, 1, 1, 2, 2, 1, 1, 1, True),      # MNIST conv1: K = 25
+    (3, 3, 37, 45, 24, 3, 3, 1, 2, 1, 0, 1, 1, 1, True),      # few channels, ragged, mixed stride
+    (2, 4, 20, 19, 40, 5, 8, 2, 1, 0, 3, 1, 2, 1, True),      # 4 channels, 8-wide filter rows, dilated rows
+    (2, 2, 12, 200, 16, 2, 3, 1, 1, 1, 1, 1, 1, 1, True),     # few channels, rows wider than one patch
     (2, 80, 1, 100, 96, 1, 13, 1, 1, 6, 0, 1, 1, 1, True),    # conv-ASR time convolution
     (7, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 1, 1, 1, True),        # reference test shape, ragged pixels
     (2, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 2, 1, 1, True),        # dilation
