@@ -207,15 +207,8 @@ WgradPlan plan_wgrad(const ConvGeo& g, int C, int taps) {
   }
   const long long out_tiles =
       (long long)((g.Cout + tc::kBM - 1) / tc::kBM) * w.tiles_n * w.tap_groups;
-  const long long target = 2LL * device_info().sm_count;
-  long long splits = (target + out_tiles - 1) / out_tiles;
-  const long long max_by_k = w.k_iters / 16 > 0 ? w.k_iters / 16 : 1;
-  if (splits > max_by_k) splits = max_by_k;
-  if (splits < 1) splits = 1;
-  long long ips = (w.k_iters + splits - 1) / splits;
-  splits = (w.k_iters + ips - 1) / ips;
-  w.splits = (int)splits;
-  w.ips = (int)ips;
+  tc::plan_splits(out_tiles, w.k_iters, 16, &w.splits, &w.ips);
+  const long long splits = w.splits;
   w.partial_bytes = (size_t)splits * taps * g.Cout * C * 4;
   return w;
 }

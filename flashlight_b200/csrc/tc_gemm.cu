@@ -135,26 +135,42 @@ int pick_bn(long long N) {
   return 256;
 }
 
+void plan_splits(long long tiles, long long k_iters, long long min_ips, int* splits_out,
+                 int* ips_out) {
+  // The persistent grid hands tile i to CTA i % grid, so the launch lasts
+  // ceil(tiles * splits / SMs) rounds of one tile each.  Pick the split count with the
+  // shortest critical path, charging every tile a fixed cost (pipeline fill, writing and
+  // re-reading its partial sums) expressed in stage iterations.
+  const long long sm = device_info().sm_count > 0 ? device_info().sm_count : 148;
+  if (tiles < 1) tiles = 1;
+  if (k_iters < 1) k_iters = 1;
+  long long smax = k_iters / (min_ips > 0 ? min_ips : 1);
+  const long long by_waves = (4 * sm + tiles - 1) / tiles;
+  if (smax > by_waves) smax = by_waves;
+  if (smax > 1024) smax = 1024;
+  if (smax < 1) smax = 1;
+  long long best_s = 1, best_ips = k_iters, best_cost = -1;
+  for (long long s = 1; s <= smax; ++s) {
+    const long long ips = (k_iters + s - 1) / s;
+    const long long se = (k_iters + ips - 1) / ips;
+    const long long rounds = (tiles * se + sm - 1) / sm;
+    const long long cost = rounds * (ips + (se > 1 ? 16 : 4));
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      best_s = se;
+      best_ips = ips;
+    }
+  }
+  *splits_out = (int)best_s;
+  *ips_out = (int)best_ips;
+}
+
 Launch plan_launch(long long M, long long N, long long k_iters, long long Z) {
   Launch L;
   L.bn = pick_bn(N);
   const long long tiles = ((M + kBM - 1) / kBM) * ((N + L.bn - 1) / L.bn) * Z;
-  const long long target = 2LL * device_info().sm_count;
-  long long splits = 1;
-  if (tiles < target && k_iters >= 16) {
-    splits = (target + tiles - 1) / tiles;
-    const long long max_by_k = k_iters / 8;  // at least 8 stage iterations (256 k) per split
-    if (splits > max_by_k) splits = max_by_k;
-    if (splits > 256) splits = 256;
-    if (splits < 1) splits = 1;
-  }
-  long long ips = (k_iters + splits - 1) / splits;
-  if (ips < 1) ips = 1;
-  splits = (k_iters + ips - 1) / ips;
-  if (splits < 1) splits = 1;
-  L.splits = (int)splits;
-  L.iters_per_split = (int)ips;
-  L.workspace_bytes = splits > 1 ? (size_t)(Z * splits * M * N) * sizeof(float) : 0;
+  plan_splits(tiles, k_iters, 8, &L.splits, &L.iters_per_split);
+  L.workspace_bytes = L.splits > 1 ? (size_t)(Z * L.splits * M * N) * sizeof(float) : 0;
   return L;
 }
 

@@ -71,6 +71,9 @@ struct Launch {
 int pick_bn(long long N);
 // Tile width, split-K factor and scratch size for an M x N output over k_iters stages, Z batches.
 Launch plan_launch(long long M, long long N, long long k_iters, long long Z);
+// Split-K factor for `tiles` output tiles of k_iters stage iterations each, at least min_ips
+// iterations per split, chosen so that tiles * splits fills whole rounds of the persistent grid.
+void plan_splits(long long tiles, long long k_iters, long long min_ips, int* splits, int* ips);
 
 // fp32 tensor map; dims[0] is the contiguous dimension, strides_bytes[i] belongs to
 // dims[i+1]; box[0] must be 32 elements.  mode: K-major operand tile (128-byte swizzle of
