@@ -28,6 +28,11 @@ class Conv2dDesc(C.Structure):
         "dtype", "math_mode")]
 
 
+class Conv2dCache(C.Structure):
+    _fields_ = [("x_cl", vp), ("x_cl_bytes", sz), ("x_cl_valid", i32),
+                ("gy_cl", vp), ("gy_cl_bytes", sz), ("gy_cl_valid", i32)]
+
+
 class Pool2dDesc(C.Structure):
     _fields_ = [(n, i32) for n in (
         "W", "H", "C", "N", "wx", "wy", "sx", "sy", "px", "py", "mode", "dtype")]
@@ -65,6 +70,13 @@ SIGNATURES = {
     "flb200_conv2d_forward": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, vp]),
     "flb200_conv2d_backward_data": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, sz, vp]),
     "flb200_conv2d_backward_filter_bias": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, vp]),
+    "flb200_conv2d_cache_bytes": (sz, [P(Conv2dDesc), C.c_int]),
+    "flb200_conv2d_forward_cached": (
+        C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, P(Conv2dCache), vp]),
+    "flb200_conv2d_backward_data_cached": (
+        C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, sz, P(Conv2dCache), vp]),
+    "flb200_conv2d_backward_filter_bias_cached": (
+        C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, P(Conv2dCache), vp]),
     "flb200_pool2d_output_dims": (C.c_int, [P(Pool2dDesc), P(i32), P(i32)]),
     "flb200_pool2d_forward": (C.c_int, [P(Pool2dDesc), vp, vp, vp, vp]),
     "flb200_pool2d_backward": (C.c_int, [P(Pool2dDesc), vp, vp, vp, vp, vp]),

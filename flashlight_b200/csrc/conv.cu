@@ -264,6 +264,21 @@ size_t flb200_conv2d_workspace_bytes(const flb200_conv2d_desc* d, int which) {
 int flb200_conv2d_forward(const flb200_conv2d_desc* d, const void* x, const void* w,
                           const void* bias, void* y, void* workspace, size_t workspace_bytes,
                           void* stream) {
+  return flb200_conv2d_forward_cached(d, x, w, bias, y, workspace, workspace_bytes, nullptr,
+                                      stream);
+}
+
+size_t flb200_conv2d_cache_bytes(const flb200_conv2d_desc* d, int which) {
+  ConvGeo g;
+  if (make_conv_geo("conv2d_cache_bytes", d, &g)) return 0;
+  if (d->math_mode != FLB200_MATH_TF32 || which < 0 || which > 1) return 0;
+  return tc_conv_cache_bytes(g, which);
+}
+
+int flb200_conv2d_forward_cached(const flb200_conv2d_desc* d, const void* x, const void* w,
+                                 const void* bias, void* y, void* workspace,
+                                 size_t workspace_bytes, flb200_conv2d_cache* cache,
+                                 void* stream) {
   ConvGeo g;
   if (int st = make_conv_geo("conv2d_forward", d, &g)) return st;
   FLB200_REQUIRE(x && w && y, "conv2d_forward: null tensor");
@@ -273,7 +288,7 @@ int flb200_conv2d_forward(const flb200_conv2d_desc* d, const void* x, const void
   const float* bf = static_cast<const float*>(bias);
   float* yf = static_cast<float*>(y);
   if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 0, workspace_bytes))
-    return tc_conv_forward(g, xf, wf, bf, yf, workspace, workspace_bytes, st);
+    return tc_conv_forward(g, xf, wf, bf, yf, workspace, workspace_bytes, st, cache);
   const long long n_total = (long long)g.N * g.HoWo;
   FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_forward: too many output pixels");
   const long long K = (long long)g.Cg * g.RS;
@@ -287,6 +302,14 @@ int flb200_conv2d_forward(const flb200_conv2d_desc* d, const void* x, const void
 int flb200_conv2d_backward_data(const flb200_conv2d_desc* d, const void* grad_y, const void* w,
                                 void* grad_x, void* workspace, size_t workspace_bytes,
                                 void* stream) {
+  return flb200_conv2d_backward_data_cached(d, grad_y, w, grad_x, workspace, workspace_bytes,
+                                            nullptr, stream);
+}
+
+int flb200_conv2d_backward_data_cached(const flb200_conv2d_desc* d, const void* grad_y,
+                                       const void* w, void* grad_x, void* workspace,
+                                       size_t workspace_bytes, flb200_conv2d_cache* cache,
+                                       void* stream) {
   ConvGeo g;
   if (int st = make_conv_geo("conv2d_backward_data", d, &g)) return st;
   FLB200_REQUIRE(grad_y && w && grad_x, "conv2d_backward_data: null tensor");
@@ -295,7 +318,7 @@ int flb200_conv2d_backward_data(const flb200_conv2d_desc* d, const void* grad_y,
   const float* wf = static_cast<const float*>(w);
   float* gxf = static_cast<float*>(grad_x);
   if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 1, workspace_bytes))
-    return tc_conv_backward_data(g, gyf, wf, gxf, workspace, workspace_bytes, st);
+    return tc_conv_backward_data(g, gyf, wf, gxf, workspace, workspace_bytes, st, cache);
   const long long n_total = (long long)g.N * g.HW;
   FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_backward_data: too many input pixels");
   DgradA al{wf, g};
@@ -308,6 +331,14 @@ int flb200_conv2d_backward_data(const flb200_conv2d_desc* d, const void* grad_y,
 int flb200_conv2d_backward_filter_bias(const flb200_conv2d_desc* d, const void* grad_y,
                                        const void* x, void* grad_w, void* grad_bias,
                                        void* workspace, size_t workspace_bytes, void* stream) {
+  return flb200_conv2d_backward_filter_bias_cached(d, grad_y, x, grad_w, grad_bias, workspace,
+                                                   workspace_bytes, nullptr, stream);
+}
+
+int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const void* grad_y,
+                                              const void* x, void* grad_w, void* grad_bias,
+                                              void* workspace, size_t workspace_bytes,
+                                              flb200_conv2d_cache* cache, void* stream) {
   ConvGeo g;
   if (int st = make_conv_geo("conv2d_backward_filter_bias", d, &g)) return st;
   FLB200_REQUIRE(grad_y && x && grad_w, "conv2d_backward_filter_bias: null tensor");
@@ -317,7 +348,7 @@ int flb200_conv2d_backward_filter_bias(const flb200_conv2d_desc* d, const void* 
   float* gwf = static_cast<float*>(grad_w);
   int rc;
   if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 2, workspace_bytes)) {
-    rc = tc_conv_backward_filter(g, gyf, xf, gwf, workspace, workspace_bytes, st);
+    rc = tc_conv_backward_filter(g, gyf, xf, gwf, workspace, workspace_bytes, st, cache);
   } else {
     const int n_total = g.Cg * g.RS;
     WgradA al{gyf, g};

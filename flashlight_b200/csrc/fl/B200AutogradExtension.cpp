@@ -52,6 +52,14 @@ struct PoolPayload : detail::AutogradPayloadData {
   Tensor argmax; // one byte per output element: selected window position
 };
 
+// Channels-last copies of x and grad_y that the tensor-core convolution routes keep between
+// the forward, backward-data and backward-filter calls of one fl::conv2d.
+struct ConvPayload : detail::AutogradPayloadData {
+  Tensor xCl, gyCl;
+  flb200_conv2d_cache cache{};
+  const void* gyFrom = nullptr; // device address of the grad_y that gyCl was made from
+};
+
 struct RnnPayload : detail::AutogradPayloadData {
   Tensor reserve;
 };
@@ -128,6 +136,42 @@ void* ptrOrNull(const Tensor& t, DevicePtr& holder) {
   return holder.get();
 }
 
+// The conv payload of this call site, created on first use; null when the route keeps no
+// copies or the caller passed no payload.
+std::shared_ptr<ConvPayload> convPayload(
+    const flb200_conv2d_desc& d, const std::shared_ptr<detail::AutogradPayload>& payload) {
+  if (!payload) {
+    return nullptr;
+  }
+  if (payload->data) {
+    // only conv2d call sites hand this payload to the convolution methods
+    return std::static_pointer_cast<ConvPayload>(payload->data);
+  }
+  const size_t xBytes = flb200_conv2d_cache_bytes(&d, 0);
+  const size_t gyBytes = flb200_conv2d_cache_bytes(&d, 1);
+  if (xBytes == 0 && gyBytes == 0) {
+    return nullptr;
+  }
+  auto data = std::make_shared<ConvPayload>();
+  data->cache.x_cl_bytes = xBytes;
+  data->cache.gy_cl_bytes = gyBytes;
+  payload->data = data;
+  return data;
+}
+
+// Allocates the buffer of one slot on first use and returns a pointer holder for it.
+void bindSlot(Tensor& buf, size_t bytes, DevicePtr& holder, void** slot) {
+  if (bytes == 0) {
+    *slot = nullptr;
+    return;
+  }
+  if (buf.isEmpty()) {
+    buf = scratch(bytes);
+  }
+  holder = DevicePtr(buf);
+  *slot = holder.get();
+}
+
 } // namespace
 
 B200AutogradExtension::B200AutogradExtension() : mathMode_(FLB200_MATH_STRICT_F32) {
@@ -152,7 +196,7 @@ bool B200AutogradExtension::isDataTypeSupported(const fl::dtype& dtype) const {
 Tensor B200AutogradExtension::conv2d(
     const Tensor& input, const Tensor& weights, const Tensor& bias, const int sx, const int sy,
     const int px, const int py, const int dx, const int dy, const int groups,
-    std::shared_ptr<detail::AutogradPayload>) {
+    std::shared_ptr<detail::AutogradPayload> payload) {
   requireF32(input, "conv2d");
   requireF32(weights, "conv2d");
   requireF32(bias, "conv2d");
@@ -163,13 +207,21 @@ Tensor B200AutogradExtension::conv2d(
   const size_t wsBytes = flb200_conv2d_workspace_bytes(&d, 0);
   auto ws = scratch(wsBytes);
   {
-    DevicePtr inPtr(input), wtPtr(weights), outPtr(output), wsPtr(ws), bsPtr;
+    DevicePtr inPtr(input), wtPtr(weights), outPtr(output), wsPtr(ws), bsPtr, xClPtr;
     void* bs = ptrOrNull(bias, bsPtr);
     const auto& st = stream();
+    auto conv = convPayload(d, payload);
+    if (conv) {
+      bindSlot(conv->xCl, conv->cache.x_cl_bytes, xClPtr, &conv->cache.x_cl);
+      conv->cache.x_cl_valid = 0;
+      conv->cache.gy_cl = nullptr; // no grad_y yet
+      relativeSync(st, {conv->xCl});
+    }
     relativeSync(st, {input, weights, bias, output, ws});
     check(
-        flb200_conv2d_forward(
-            &d, inPtr.get(), wtPtr.get(), bs, outPtr.get(), wsPtr.get(), wsBytes, st.handle()),
+        flb200_conv2d_forward_cached(
+            &d, inPtr.get(), wtPtr.get(), bs, outPtr.get(), wsPtr.get(), wsBytes,
+            conv ? &conv->cache : nullptr, st.handle()),
         "conv2d");
     relativeSync({output}, st);
   }
@@ -179,19 +231,28 @@ Tensor B200AutogradExtension::conv2d(
 Tensor B200AutogradExtension::conv2dBackwardData(
     const Tensor& gradOutput, const Tensor& input, const Tensor& weight, const int sx,
     const int sy, const int px, const int py, const int dx, const int dy, const int groups,
-    std::shared_ptr<DynamicBenchmark>, std::shared_ptr<detail::AutogradPayload>) {
+    std::shared_ptr<DynamicBenchmark>, std::shared_ptr<detail::AutogradPayload> payload) {
   requireF32(gradOutput, "conv2dBackwardData");
   const auto d = convDesc(input, weight, sx, sy, px, py, dx, dy, groups, mathMode_);
   auto gradInput = Tensor(input.shape(), input.type());
   const size_t wsBytes = flb200_conv2d_workspace_bytes(&d, 1);
   auto ws = scratch(wsBytes);
   {
-    DevicePtr goPtr(gradOutput), wtPtr(weight), giPtr(gradInput), wsPtr(ws);
+    DevicePtr goPtr(gradOutput), wtPtr(weight), giPtr(gradInput), wsPtr(ws), xClPtr, gyClPtr;
     const auto& st = stream();
+    auto conv = convPayload(d, payload);
+    if (conv) {
+      bindSlot(conv->xCl, conv->cache.x_cl_bytes, xClPtr, &conv->cache.x_cl);
+      bindSlot(conv->gyCl, conv->cache.gy_cl_bytes, gyClPtr, &conv->cache.gy_cl);
+      conv->cache.gy_cl_valid = 0;
+      conv->gyFrom = goPtr.get();
+      relativeSync(st, {conv->xCl, conv->gyCl});
+    }
     relativeSync(st, {gradOutput, weight, gradInput, ws});
     check(
-        flb200_conv2d_backward_data(
-            &d, goPtr.get(), wtPtr.get(), giPtr.get(), wsPtr.get(), wsBytes, st.handle()),
+        flb200_conv2d_backward_data_cached(
+            &d, goPtr.get(), wtPtr.get(), giPtr.get(), wsPtr.get(), wsBytes,
+            conv ? &conv->cache : nullptr, st.handle()),
         "conv2dBackwardData");
     relativeSync({gradInput}, st);
   }
@@ -202,7 +263,7 @@ std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
     const Tensor& gradOutput, const Tensor& input, const Tensor& weights, const Tensor& bias,
     const int sx, const int sy, const int px, const int py, const int dx, const int dy,
     const int groups, std::shared_ptr<DynamicBenchmark>, std::shared_ptr<DynamicBenchmark>,
-    std::shared_ptr<detail::AutogradPayload>) {
+    std::shared_ptr<detail::AutogradPayload> payload) {
   requireF32(gradOutput, "conv2dBackwardFilterBias");
   const auto d = convDesc(input, weights, sx, sy, px, py, dx, dy, groups, mathMode_);
   auto gradWeights = Tensor(weights.shape(), weights.type());
@@ -214,14 +275,36 @@ std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
   const size_t wsBytes = flb200_conv2d_workspace_bytes(&d, 2);
   auto ws = scratch(wsBytes);
   {
-    DevicePtr goPtr(gradOutput), inPtr(input), gwPtr(gradWeights), wsPtr(ws), gbPtr;
+    DevicePtr goPtr(gradOutput), inPtr(input), gwPtr(gradWeights), wsPtr(ws), gbPtr, xClPtr,
+        gyClPtr;
     void* gb = ptrOrNull(gradBias, gbPtr);
     const auto& st = stream();
+    auto conv = convPayload(d, payload);
+    if (conv) {
+      bindSlot(conv->xCl, conv->cache.x_cl_bytes, xClPtr, &conv->cache.x_cl);
+      if (!conv->gyCl.isEmpty()) {
+        bindSlot(conv->gyCl, conv->cache.gy_cl_bytes, gyClPtr, &conv->cache.gy_cl);
+      } else {
+        conv->cache.gy_cl = nullptr;
+      }
+      // the copy of grad_y is only good for the tensor backward-data made it from
+      if (conv->gyFrom != goPtr.get()) {
+        conv->cache.gy_cl_valid = 0;
+      }
+      relativeSync(st, {conv->xCl, conv->gyCl});
+    }
     relativeSync(st, {gradOutput, input, gradWeights, gradBias, ws});
     check(
-        flb200_conv2d_backward_filter_bias(
-            &d, goPtr.get(), inPtr.get(), gwPtr.get(), gb, wsPtr.get(), wsBytes, st.handle()),
+        flb200_conv2d_backward_filter_bias_cached(
+            &d, goPtr.get(), inPtr.get(), gwPtr.get(), gb, wsPtr.get(), wsBytes,
+            conv ? &conv->cache : nullptr, st.handle()),
         "conv2dBackwardFilterBias");
+    if (conv) {
+      conv->gyCl = Tensor(); // dead after this pass; x stays for a later backward
+      conv->gyFrom = nullptr;
+      conv->cache.gy_cl = nullptr;
+      conv->cache.gy_cl_valid = 0;
+    }
     relativeSync({gradWeights, gradBias}, st);
   }
   return {gradWeights, gradBias};

@@ -200,6 +200,13 @@ size_t tc_conv_workspace_bytes(const ConvGeo& g, int which) {
          tc::plan_launch(g.Cout, s.kc, (s.ld_out + tc::kBK - 1) / tc::kBK, 1).workspace_bytes;
 }
 
+size_t tc_conv_cache_bytes(const ConvGeo& g, int which) {
+  if (g.groups != 1 || !flb200_has_tensor_core_path() || direct_1x1(g)) return 0;
+  if (patch_conv_supported(g)) return patch_conv_cache_bytes(g, which);
+  if (window_conv_supported(g)) return window_conv_cache_bytes(g, which);
+  return 0;
+}
+
 bool tc_conv_supported(const ConvGeo& g, int which, size_t workspace_bytes) {
   if (!flb200_has_tensor_core_path()) return false;
   if (g.groups != 1) return false;
@@ -214,7 +221,8 @@ bool tc_conv_supported(const ConvGeo& g, int which, size_t workspace_bytes) {
 }
 
 int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias, float* y,
-                    void* ws, size_t ws_bytes, cudaStream_t st) {
+                    void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   CUtensorMap ma, mb;
   tc::EpiloguePlan ep{};
   ep.out = y;
@@ -232,8 +240,8 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
     return tc::run(ma, mb, pa, pb, ep, g.HW, g.Cout, (g.C + tc::kBK - 1) / tc::kBK, g.N, nullptr, 0,
                    st);
   }
-  if (patch_conv_supported(g)) return patch_conv_forward(g, x, w, bias, y, ws, ws_bytes, st);
-  if (window_conv_supported(g)) return window_conv_forward(g, x, w, bias, y, ws, ws_bytes, st);
+  if (patch_conv_supported(g)) return patch_conv_forward(g, x, w, bias, y, ws, ws_bytes, st, cache);
+  if (window_conv_supported(g)) return window_conv_forward(g, x, w, bias, y, ws, ws_bytes, st, cache);
   const GeneralSizes s = general_sizes(g);
   char* base = static_cast<char*>(ws);
   float* col = reinterpret_cast<float*>(base);
@@ -261,7 +269,8 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
 }
 
 int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx, void* ws,
-                          size_t ws_bytes, cudaStream_t st) {
+                          size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   CUtensorMap ma, mb;
   tc::EpiloguePlan ep{};
   ep.out = gx;
@@ -280,7 +289,7 @@ int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, flo
     return tc::run(ma, mb, pa, pb, ep, g.HW, g.C, (g.Cout + tc::kBK - 1) / tc::kBK, g.N, nullptr, 0,
                    st);
   }
-  if (patch_conv_supported(g)) return patch_conv_backward_data(g, gy, w, gx, ws, ws_bytes, st);
+  if (patch_conv_supported(g)) return patch_conv_backward_data(g, gy, w, gx, ws, ws_bytes, st, cache);
   const GeneralSizes s = general_sizes(g);
   char* base = static_cast<char*>(ws);
   float* col = reinterpret_cast<float*>(base);
@@ -303,7 +312,8 @@ int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, flo
 }
 
 int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw, void* ws,
-                            size_t ws_bytes, cudaStream_t st) {
+                            size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   CUtensorMap ma, mb;
   tc::EpiloguePlan ep{};
   ep.out = gw;
@@ -322,9 +332,9 @@ int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, f
     ep.m_stride = g.C;
     return tc::run(ma, mb, pa, pb, ep, g.Cout, g.C, (long long)g.N * k_inner, 1, ws, ws_bytes, st);
   }
-  if (patch_conv_supported(g)) return patch_conv_backward_filter(g, gy, x, gw, ws, ws_bytes, st);
+  if (patch_conv_supported(g)) return patch_conv_backward_filter(g, gy, x, gw, ws, ws_bytes, st, cache);
   if (window_conv_supported(g))
-    return window_conv_backward_filter(g, gy, x, gw, ws, ws_bytes, st);
+    return window_conv_backward_filter(g, gy, x, gw, ws, ws_bytes, st, cache);
   const GeneralSizes s = general_sizes(g);
   const int bn = tc::pick_bn(s.kc);
   char* base = static_cast<char*>(ws);

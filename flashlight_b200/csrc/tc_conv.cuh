@@ -18,32 +18,45 @@ int make_conv_geo(const char* name, const flb200_conv2d_desc* d, ConvGeo* g);
 // which: 0 forward, 1 backward-data, 2 backward-filter.
 bool tc_conv_supported(const ConvGeo& g, int which, size_t workspace_bytes);
 size_t tc_conv_workspace_bytes(const ConvGeo& g, int which);
+// Size of the channels-last copy of x (which 0) or grad_y (which 1) that can be kept between
+// the calls of one convolution; 0 for routes that make no such copy.
+size_t tc_conv_cache_bytes(const ConvGeo& g, int which);
 int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias, float* y,
-                    void* ws, size_t ws_bytes, cudaStream_t st);
+                    void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx, void* ws,
-                          size_t ws_bytes, cudaStream_t st);
+                          size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw, void* ws,
-                            size_t ws_bytes, cudaStream_t st);
+                            size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 
 // Channels-last implicit-GEMM route (tc_conv_patch.cu): no im2col matrix, one NHWC copy of the
 // activation operand per pass.
 bool patch_conv_supported(const ConvGeo& g);
 size_t patch_conv_workspace_bytes(const ConvGeo& g, int which);
+size_t patch_conv_cache_bytes(const ConvGeo& g, int which);
 int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
-                       float* y, void* ws, size_t ws_bytes, cudaStream_t st);
+                       float* y, void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx,
-                             void* ws, size_t ws_bytes, cudaStream_t st);
+                             void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
-                               void* ws, size_t ws_bytes, cudaStream_t st);
+                               void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 
 // Few-channel "row window" route (<= 4 input channels, e.g. the ResNet stem): forward and
 // backward-filter only; returns a non-zero status without launching anything if the driver
 // refuses the overlapping tensor map, so that the caller can take another route.
 bool window_conv_supported(const ConvGeo& g);
 size_t window_conv_workspace_bytes(const ConvGeo& g, int which);
+size_t window_conv_cache_bytes(const ConvGeo& g, int which);
 int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
-                        float* y, void* ws, size_t ws_bytes, cudaStream_t st);
+                        float* y, void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
-                                void* ws, size_t ws_bytes, cudaStream_t st);
+                                void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache = nullptr);
 
 }  // namespace flb200

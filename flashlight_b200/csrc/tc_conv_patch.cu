@@ -14,6 +14,25 @@ namespace {
 inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 inline int up4(int v) { return (v + 3) / 4 * 4; }
 
+// Where a channels-last copy lives: in the caller's cache when it has a large enough,
+// 256-byte aligned buffer for it, else at `fallback` inside the workspace.
+struct ClSlot {
+  float* buf;
+  int32_t* flag;  // the cache's valid flag, or null without a cache buffer
+  bool valid;     // the buffer already holds the copy
+};
+ClSlot cl_slot(flb200_conv2d_cache* c, int which, size_t bytes, float* fallback) {
+  ClSlot s{fallback, nullptr, false};
+  if (!c) return s;
+  void* b = which == 0 ? c->x_cl : c->gy_cl;
+  const size_t have = which == 0 ? c->x_cl_bytes : c->gy_cl_bytes;
+  if (!b || have < bytes || (reinterpret_cast<uintptr_t>(b) & 255) != 0) return s;
+  s.buf = static_cast<float*>(b);
+  s.flag = which == 0 ? &c->x_cl_valid : &c->gy_cl_valid;
+  s.valid = *s.flag != 0;
+  return s;
+}
+
 // dst[n][hw][cp] = src[n][c][hw] for c < C, 0 for the padding channels C <= c < cp.
 __global__ void __launch_bounds__(256)
 nchw_to_nhwc_kernel(const float* __restrict__ src, float* __restrict__ dst, int C, int cp,
@@ -357,14 +376,24 @@ size_t patch_conv_workspace_bytes(const ConvGeo& g, int which) {
          up256(plan_wgrad(g).partial_bytes);
 }
 
+size_t patch_conv_cache_bytes(const ConvGeo& g, int which) {
+  if (which == 0) return up256((size_t)g.N * g.HW * up4(g.C) * 4);
+  return up256((size_t)g.N * g.HoWo * up4(g.Cout) * 4);
+}
+
 int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
-                       float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+                       float* y, void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   (void)ws_bytes;
   const int cp = up4(g.C);
   char* base = static_cast<char*>(ws);
-  float* xt = reinterpret_cast<float*>(base);
+  const ClSlot xs = cl_slot(cache, 0, (size_t)g.N * g.HW * cp * 4, reinterpret_cast<float*>(base));
+  float* xt = xs.buf;
   float* wp = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HW * cp * 4));
-  if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
+  if (!xs.valid) {
+    if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
+    if (xs.flag) *xs.flag = 1;
+  }
   pack_filter_kernel<<<grid_for((long long)g.RS * g.Cout * cp, 256), 256, 0, st>>>(
       w, wp, g.Cout, g.C, g.RS, g.Cout, g.C, cp, 1);
   FLB200_AFTER_LAUNCH("pack_filter");
@@ -388,13 +417,17 @@ int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const f
 }
 
 int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx,
-                             void* ws, size_t ws_bytes, cudaStream_t st) {
+                             void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   (void)ws_bytes;
   const int cop = up4(g.Cout);
   char* base = static_cast<char*>(ws);
-  float* gyt = reinterpret_cast<float*>(base);
+  const ClSlot gs =
+      cl_slot(cache, 1, (size_t)g.N * g.HoWo * cop * 4, reinterpret_cast<float*>(base));
+  float* gyt = gs.buf;
   float* wd = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HoWo * cop * 4));
   if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+  if (gs.flag) *gs.flag = 1;  // backward-filter of the same grad_y can take it from here
   pack_filter_kernel<<<grid_for((long long)g.RS * g.C * cop, 256), 256, 0, st>>>(
       w, wd, g.Cout, g.C, g.RS, g.C, g.Cout, cop, 0);
   FLB200_AFTER_LAUNCH("pack_filter");
@@ -458,18 +491,29 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
 }
 
 int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
-                               void* ws, size_t ws_bytes, cudaStream_t st) {
+                               void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   (void)ws_bytes;
   const int cp = up4(g.C), cop = up4(g.Cout);
   const WgradPlan wp = plan_wgrad(g);
   char* base = static_cast<char*>(ws);
-  float* xt = reinterpret_cast<float*>(base);
+  const ClSlot xs = cl_slot(cache, 0, (size_t)g.N * g.HW * cp * 4, reinterpret_cast<float*>(base));
+  float* xt = xs.buf;
   size_t off = up256((size_t)g.N * g.HW * cp * 4);
-  float* gyt = reinterpret_cast<float*>(base + off);
+  const ClSlot gs =
+      cl_slot(cache, 1, (size_t)g.N * g.HoWo * cop * 4, reinterpret_cast<float*>(base + off));
+  float* gyt = gs.buf;
   off += up256((size_t)g.N * g.HoWo * cop * 4);
   float* partial = reinterpret_cast<float*>(base + off);
-  if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
-  if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+  if (!xs.valid) {
+    if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
+    if (xs.flag) *xs.flag = 1;
+  }
+  if (gs.valid) {
+    *gs.flag = 0;  // consumed: the next backward pass brings another grad_y
+  } else {
+    if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+  }
   CUtensorMap ma, mb;
   if (int rc = nhwc_map5(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH,
                          wgrad_a_boxes(g.Cout), 1, 1))
@@ -513,12 +557,21 @@ size_t window_conv_workspace_bytes(const ConvGeo& g, int which) {
          up256(plan_wgrad(g, 32 * g.kH, 1).partial_bytes);
 }
 
+size_t window_conv_cache_bytes(const ConvGeo& g, int which) {
+  if (which != 0) return 0;  // this route has no backward-data pass to share grad_y with
+  const WindowGeo wg = window_geo(g);
+  return up256((size_t)g.N * wg.Hp * wg.Wp * 16);
+}
+
 int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
-                        float* y, void* ws, size_t ws_bytes, cudaStream_t st) {
+                        float* y, void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   (void)ws_bytes;
   const WindowGeo wg = window_geo(g);
   char* base = static_cast<char*>(ws);
-  float* xtp = reinterpret_cast<float*>(base);
+  const ClSlot xs =
+      cl_slot(cache, 0, (size_t)g.N * wg.Hp * wg.Wp * 16, reinterpret_cast<float*>(base));
+  float* xtp = xs.buf;
   float* wr = reinterpret_cast<float*>(base + up256((size_t)g.N * wg.Hp * wg.Wp * 16));
   PatchArgs a{};
   a.patch = pick_patch(g.Wo, g.Ho);
@@ -528,10 +581,13 @@ int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const 
     return rc;
   const int bn = tc::pick_bn(g.Cout);
   if (int rc = filter_map(&mb, wr, 32, 32, g.Cout, g.kH, bn)) return rc;
-  const long long total = (long long)g.N * wg.Hp * wg.Wp;
-  nchw_to_nhwc4_pad_kernel<<<grid_for(total, 256), 256, 0, st>>>(
-      x, reinterpret_cast<float4*>(xtp), g.C, g.H, g.W, wg.Hp, wg.Wp, g.py, g.px, total);
-  FLB200_AFTER_LAUNCH("nchw_to_nhwc4_pad");
+  if (!xs.valid) {
+    const long long total = (long long)g.N * wg.Hp * wg.Wp;
+    nchw_to_nhwc4_pad_kernel<<<grid_for(total, 256), 256, 0, st>>>(
+        x, reinterpret_cast<float4*>(xtp), g.C, g.H, g.W, wg.Hp, wg.Wp, g.py, g.px, total);
+    FLB200_AFTER_LAUNCH("nchw_to_nhwc4_pad");
+    if (xs.flag) *xs.flag = 1;
+  }
   pack_filter_rows_kernel<<<grid_for(g.kH * g.Cout * 32, 256), 256, 0, st>>>(w, wr, g.Cout, g.C,
                                                                             g.kH, g.kW);
   FLB200_AFTER_LAUNCH("pack_filter_rows");
@@ -547,13 +603,16 @@ int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const 
 }
 
 int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
-                                void* ws, size_t ws_bytes, cudaStream_t st) {
+                                void* ws, size_t ws_bytes, cudaStream_t st,
+    flb200_conv2d_cache* cache) {
   (void)ws_bytes;
   const WindowGeo wg = window_geo(g);
   const int cop = up4(g.Cout);
   const WgradPlan wp = plan_wgrad(g, 32 * g.kH, 1);
   char* base = static_cast<char*>(ws);
-  float* xtp = reinterpret_cast<float*>(base);
+  const ClSlot xs =
+      cl_slot(cache, 0, (size_t)g.N * wg.Hp * wg.Wp * 16, reinterpret_cast<float*>(base));
+  float* xtp = xs.buf;
   size_t off = up256((size_t)g.N * wg.Hp * wg.Wp * 16);
   float* gyt = reinterpret_cast<float*>(base + off);
   off += up256((size_t)g.N * g.HoWo * cop * 4);
@@ -564,10 +623,13 @@ int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* 
   if (int rc = nhwc_map5(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH,
                          wgrad_a_boxes(g.Cout), 1, 1))
     return rc;
-  const long long total = (long long)g.N * wg.Hp * wg.Wp;
-  nchw_to_nhwc4_pad_kernel<<<grid_for(total, 256), 256, 0, st>>>(
-      x, reinterpret_cast<float4*>(xtp), g.C, g.H, g.W, wg.Hp, wg.Wp, g.py, g.px, total);
-  FLB200_AFTER_LAUNCH("nchw_to_nhwc4_pad");
+  if (!xs.valid) {
+    const long long total = (long long)g.N * wg.Hp * wg.Wp;
+    nchw_to_nhwc4_pad_kernel<<<grid_for(total, 256), 256, 0, st>>>(
+        x, reinterpret_cast<float4*>(xtp), g.C, g.H, g.W, wg.Hp, wg.Wp, g.py, g.px, total);
+    FLB200_AFTER_LAUNCH("nchw_to_nhwc4_pad");
+    if (xs.flag) *xs.flag = 1;
+  }
   if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
   // One GEMM: M = Cout, N = kH blocks of 32 window floats, K = pixels.  The filter rows are
   // the channel groups of the view, so the launch has a single tap at offset zero.

@@ -55,6 +55,52 @@ def workspace(nbytes: int, like: torch.Tensor) -> Optional[torch.Tensor]:
     return torch.empty(int(nbytes), dtype=torch.uint8, device=like.device)
 
 
+class _ConvLayoutCache:
+    """flb200_conv2d_cache plus the tensors behind it.  A copy is only trusted for the very
+    tensor it was made from: same storage address and same version counter."""
+
+    def __init__(self, x_bytes: int, gy_bytes: int, like: torch.Tensor):
+        self.c = L.Conv2dCache()
+        self.x_bytes, self.gy_bytes, self.device = int(x_bytes), int(gy_bytes), like.device
+        self.x_buf = self.gy_buf = None
+        self.x_key = self.gy_key = None
+
+    @staticmethod
+    def _key(t: torch.Tensor):
+        return (t.data_ptr(), t._version, tuple(t.shape))
+
+    def bind_x(self, x: torch.Tensor) -> None:
+        if self.x_bytes and self.x_buf is None:
+            self.x_buf = torch.empty(self.x_bytes, dtype=torch.uint8, device=self.device)
+            self.c.x_cl, self.c.x_cl_bytes = self.x_buf.data_ptr(), self.x_bytes
+        self.c.x_cl_valid = 0
+        self.x_key = self._key(x)
+
+    def check_x(self, x: torch.Tensor) -> None:
+        if self.x_key != self._key(x):
+            self.bind_x(x)
+
+    def bind_gy(self, gy: torch.Tensor) -> None:
+        if self.gy_bytes and self.gy_buf is None:
+            self.gy_buf = torch.empty(self.gy_bytes, dtype=torch.uint8, device=self.device)
+            self.c.gy_cl, self.c.gy_cl_bytes = self.gy_buf.data_ptr(), self.gy_bytes
+        self.c.gy_cl_valid = 0
+        self.gy_key = self._key(gy)
+
+    def check_gy(self, gy: torch.Tensor) -> None:
+        if self.gy_key != self._key(gy):
+            self.c.gy_cl_valid = 0
+
+    def release_gy(self) -> None:
+        """The copy of grad_y is dead after backward-filter; give its memory back."""
+        self.gy_buf = None
+        self.gy_key = None
+        self.c.gy_cl, self.c.gy_cl_bytes, self.c.gy_cl_valid = None, 0, 0
+
+    def ref(self):
+        return C.byref(self.c)
+
+
 class AutogradPayload:
     """detail::AutogradPayload: a nullable slot that forward fills and backward reads."""
 
@@ -96,8 +142,14 @@ def default_math_mode() -> int:
 class B200AutogradExtension:
     """sm_100a implementation of the Flashlight autograd extension interface."""
 
-    def __init__(self, math_mode: Optional[int] = None):
+    def __init__(self, math_mode: Optional[int] = None, cache_layouts: Optional[bool] = None):
         self.math_mode = default_math_mode() if math_mode is None else math_mode
+        # Keep the channels-last copies of x and grad_y in the payload of each conv2d call
+        # site (forward -> backward-filter, backward-data -> backward-filter).  Costs one
+        # extra copy of x per convolution that uses one; FLB200_CACHE_LAYOUTS=0 turns it off.
+        if cache_layouts is None:
+            cache_layouts = os.environ.get("FLB200_CACHE_LAYOUTS", "1") != "0"
+        self.cache_layouts = cache_layouts
 
     # ------------------------------------------------------------ registry
     def isDataTypeSupported(self, dtype) -> bool:
@@ -120,6 +172,20 @@ class B200AutogradExtension:
         return L.Conv2dDesc(W, H, Cin, N, kW, kH, Cout, sx, sy, px, py, dx, dy, groups, L.F32,
                             self.math_mode)
 
+    def _conv_cache(self, d, payload, like) -> Optional["_ConvLayoutCache"]:
+        """The layout cache kept in the payload of one conv2d call site (None when the route
+        keeps no channels-last copies, when there is no payload, or when caching is off)."""
+        if payload is None or not self.cache_layouts:
+            return None
+        if isinstance(payload.data, _ConvLayoutCache):
+            return payload.data
+        nx = L.lib.flb200_conv2d_cache_bytes(C.byref(d), 0)
+        ng = L.lib.flb200_conv2d_cache_bytes(C.byref(d), 1)
+        if nx == 0 and ng == 0:
+            return None
+        payload.data = _ConvLayoutCache(nx, ng, like)
+        return payload.data
+
     def conv2d(self, input, weights, bias, sx, sy, px, py, dx, dy, groups, payload=None):
         d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups)
         wo, ho = L.i32(), L.i32()
@@ -129,8 +195,12 @@ class B200AutogradExtension:
             raise ValueError("conv2d: bias must have one element per output channel")
         nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 0)
         ws = workspace(nbytes, input)
-        L.check(L.lib.flb200_conv2d_forward(C.byref(d), ptr(input), ptr(weights), ptr(bias), ptr(out),
-                                            ptr(ws), nbytes, stream_handle()))
+        cache = self._conv_cache(d, payload, input)
+        if cache is not None:
+            cache.bind_x(input)
+        L.check(L.lib.flb200_conv2d_forward_cached(
+            C.byref(d), ptr(input), ptr(weights), ptr(bias), ptr(out), ptr(ws), nbytes,
+            cache.ref() if cache is not None else None, stream_handle()))
         return out
 
     def conv2dBackwardData(self, gradOutput, input, weight, sx, sy, px, py, dx, dy, groups,
@@ -139,8 +209,12 @@ class B200AutogradExtension:
         grad_in = torch.empty_like(input)
         nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 1)
         ws = workspace(nbytes, input)
-        L.check(L.lib.flb200_conv2d_backward_data(C.byref(d), ptr(gradOutput), ptr(weight),
-                                                  ptr(grad_in), ptr(ws), nbytes, stream_handle()))
+        cache = self._conv_cache(d, payload, input)
+        if cache is not None:
+            cache.bind_gy(gradOutput)
+        L.check(L.lib.flb200_conv2d_backward_data_cached(
+            C.byref(d), ptr(gradOutput), ptr(weight), ptr(grad_in), ptr(ws), nbytes,
+            cache.ref() if cache is not None else None, stream_handle()))
         return grad_in
 
     def conv2dBackwardFilterBias(self, gradOutput, input, weights, bias, sx, sy, px, py, dx, dy,
@@ -150,9 +224,15 @@ class B200AutogradExtension:
         grad_b = torch.empty_like(bias) if bias is not None else None
         nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 2)
         ws = workspace(nbytes, input)
-        L.check(L.lib.flb200_conv2d_backward_filter_bias(
+        cache = self._conv_cache(d, autogradPayload, input)
+        if cache is not None:
+            cache.check_x(input)
+            cache.check_gy(gradOutput)
+        L.check(L.lib.flb200_conv2d_backward_filter_bias_cached(
             C.byref(d), ptr(gradOutput), ptr(input), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes,
-            stream_handle()))
+            cache.ref() if cache is not None else None, stream_handle()))
+        if cache is not None:
+            cache.release_gy()
         return grad_w, grad_b
 
     # --------------------------------------------------------------- pool2d

@@ -105,6 +105,45 @@ int flb200_conv2d_backward_filter_bias(const flb200_conv2d_desc* d, const void* 
                                        void* workspace, size_t workspace_bytes,
                                        void* stream);
 
+/* Keeping layout copies between the calls of one convolution.  The tensor-core routes read
+ * x and grad_y from channels-last copies; a caller that passes the same cache to the forward
+ * call and to both backward calls of one fl::conv2d lets backward-filter reuse the copy of x
+ * made by forward and the copy of grad_y made by backward-data instead of making them again.
+ * The reference hands every backend the same kind of per-call-site state:
+ * std::shared_ptr<detail::AutogradPayload> in flashlight/fl/autograd/tensor/
+ * AutogradExtension.h:58-69, 110-138.  The caller owns both buffers (sizes from
+ * flb200_conv2d_cache_bytes; a NULL or short buffer is simply not used) and the flags:
+ *   x_cl_valid   set by forward (and by backward-filter when it had to make the copy);
+ *                clear it when x changes.
+ *   gy_cl_valid  set by backward-data, consumed and cleared by backward-filter, which
+ *                therefore must be called with the same grad_y as that backward-data call.
+ * Routes that make no such copy leave the cache untouched. */
+typedef struct flb200_conv2d_cache {
+  void* x_cl;
+  size_t x_cl_bytes;
+  int32_t x_cl_valid;
+  void* gy_cl;
+  size_t gy_cl_bytes;
+  int32_t gy_cl_valid;
+} flb200_conv2d_cache;
+
+/* which: 0 the copy of x, 1 the copy of grad_y; 0 bytes when the route keeps none. */
+size_t flb200_conv2d_cache_bytes(const flb200_conv2d_desc* d, int which);
+
+/* The three calls above with a cache (may be NULL: then they are the calls above). */
+int flb200_conv2d_forward_cached(const flb200_conv2d_desc* d, const void* x, const void* w,
+                                 const void* bias, void* y, void* workspace,
+                                 size_t workspace_bytes, flb200_conv2d_cache* cache,
+                                 void* stream);
+int flb200_conv2d_backward_data_cached(const flb200_conv2d_desc* d, const void* grad_y,
+                                       const void* w, void* grad_x, void* workspace,
+                                       size_t workspace_bytes, flb200_conv2d_cache* cache,
+                                       void* stream);
+int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const void* grad_y,
+                                              const void* x, void* grad_w, void* grad_bias,
+                                              void* workspace, size_t workspace_bytes,
+                                              flb200_conv2d_cache* cache, void* stream);
+
 /* ------------------------------------------------------- pool2d (a5, a8) */
 typedef struct flb200_pool2d_desc {
   int32_t W, H, C, N;

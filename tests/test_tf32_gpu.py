@@ -1,6 +1,8 @@
 """TF32 (tcgen05 tensor-core) mode against the fp64 oracle.  Bound: relative error
 relative to the tensor scale (tests/parity.py scaled_err) <= 2e-3 — fp32 operands are read with a 10-bit mantissa (2^-11 relative
 rounding each) and accumulated in fp32; strict mode keeps the 1e-4 bound."""
+import ctypes as C
+
 import pytest
 import torch
 
@@ -190,3 +192,57 @@ def test_rnn_tf32(L):
                                     gy.double(), None, None)
     assert_close_scaled(dx, wdx, 5e-3, "rnn dx (tf32)")
     assert_close_scaled(dw, wdw, 5e-3, "rnn dw (tf32)")
+
+
+# ------------------------------------------------------------- layout cache
+@pytest.mark.parametrize("case", [
+    (2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1),     # channels-last patch route
+    (2, 128, 14, 14, 128, 3, 3, 2, 2, 1, 1, 1, 1, 1),   # strided
+    (2, 3, 32, 32, 64, 7, 7, 2, 2, 3, 3, 1, 1, 1),      # row-window route (caches x only)
+    (2, 64, 16, 16, 256, 1, 1, 1, 1, 0, 0, 1, 1, 1),    # direct 1x1: nothing to cache
+])
+def test_conv2d_layout_cache(L, case):
+    """With a payload the backward-filter pass reuses the channels-last copies made by the
+    forward and backward-data passes; results are bit-identical to the uncached calls, and a
+    copy is never reused for a different tensor."""
+    from flashlight_b200.extension import AutogradPayload, B200AutogradExtension
+    N, Cin, H, W, Cout, kH, kW, sx, sy, px, py, dx, dy, groups = case
+    plain = B200AutogradExtension(math_mode=L.MATH_TF32, cache_layouts=False)
+    cached = B200AutogradExtension(math_mode=L.MATH_TF32, cache_layouts=True)
+    x = randn(N, Cin, H, W, seed=31).cuda()
+    w = (randn(Cout, Cin, kH, kW, seed=32) * (1.0 / (Cin * kH * kW) ** 0.5)).cuda()
+    args = (sx, sy, px, py, dx, dy, groups)
+    y0 = plain.conv2d(x, w, None, *args)
+    gy = randn(*y0.shape, seed=33).cuda()
+    gx0 = plain.conv2dBackwardData(gy, x, w, *args)
+    gw0, _ = plain.conv2dBackwardFilterBias(gy, x, w, None, *args)
+
+    payload = AutogradPayload()
+    before = L.kernel_launches()
+    y1 = cached.conv2d(x, w, None, *args, payload)
+    gx1 = cached.conv2dBackwardData(gy, x, w, *args, None, payload)
+    gw1, _ = cached.conv2dBackwardFilterBias(gy, x, w, None, *args, None, None, payload)
+    with_cache = L.kernel_launches() - before
+    before = L.kernel_launches()
+    plain.conv2d(x, w, None, *args)
+    plain.conv2dBackwardData(gy, x, w, *args)
+    plain.conv2dBackwardFilterBias(gy, x, w, None, *args)
+    without = L.kernel_launches() - before
+    assert torch.equal(y0, y1) and torch.equal(gx0, gx1) and torch.equal(gw0, gw1)
+    keeps = L.lib.flb200_conv2d_cache_bytes(
+        C.byref(cached._conv_desc(x, w, *args)), 0) > 0
+    assert (with_cache < without) == keeps, (with_cache, without)
+
+    # a second backward pass with another grad_y must not see the first one's copy
+    gy2 = randn(*y0.shape, seed=34).cuda()
+    gx2 = cached.conv2dBackwardData(gy2, x, w, *args, None, payload)
+    gy3 = randn(*y0.shape, seed=35).cuda()
+    gw3, _ = cached.conv2dBackwardFilterBias(gy3, x, w, None, *args, None, None, payload)
+    want3, _ = plain.conv2dBackwardFilterBias(gy3, x, w, None, *args)
+    assert torch.equal(gx2, plain.conv2dBackwardData(gy2, x, w, *args))
+    assert torch.equal(gw3, want3)
+    # ... nor a changed x (in-place update bumps the version counter)
+    x.mul_(0.5)
+    gw4, _ = cached.conv2dBackwardFilterBias(gy3, x, w, None, *args, None, None, payload)
+    want4, _ = plain.conv2dBackwardFilterBias(gy3, x, w, None, *args)
+    assert torch.equal(gw4, want4)
