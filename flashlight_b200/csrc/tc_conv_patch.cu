@@ -62,6 +62,55 @@ int to_nhwc(const float* src, float* dst, int N, int C, int cp, int HW, cudaStre
   return FLB200_OK;
 }
 
+// The same transposition of every (sy, sx)-th pixel only: dst[n][p][q][c] = src[n][c][p*sy][q*sx].
+__global__ void __launch_bounds__(256)
+nchw_to_nhwc_sampled_kernel(const float* __restrict__ src, float* __restrict__ dst, int C, int cp,
+                            int HW, int W, int Wo, int HoWo, int sx, int sy) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int hw0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const long long n = blockIdx.z;
+  const int o = hw0 + tx;
+  const int p = o / Wo, q = o - p * Wo;
+  const long long from = (long long)p * sy * W + (long long)q * sx;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = c0 + ty + 8 * i;
+    tile[ty + 8 * i][tx] = (c < C && o < HoWo) ? src[(n * C + c) * HW + from] : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int hw = hw0 + ty + 8 * i, c = c0 + tx;
+    if (hw < HoWo && c < cp) dst[(n * HoWo + hw) * cp + c] = tile[tx][ty + 8 * i];
+  }
+}
+
+// A 1 x 1 convolution with a stride and no padding only ever reads every (sy, sx)-th pixel:
+// its channels-last copy keeps just those, and the rest of the pass is a stride-1 convolution
+// on the Wo x Ho image.  Returns the geometry the forward and backward-filter passes run on.
+bool samples_input(const ConvGeo& g) {
+  return g.RS == 1 && g.px == 0 && g.py == 0 && (g.sx > 1 || g.sy > 1);
+}
+ConvGeo sampled_geo(const ConvGeo& g) {
+  ConvGeo e = g;
+  if (samples_input(g)) {
+    e.W = g.Wo; e.H = g.Ho; e.HW = g.HoWo;
+    e.sx = 1; e.sy = 1;
+  }
+  return e;
+}
+// Channels-last copy of x for the forward / backward-filter passes of geometry g.
+int x_to_nhwc(const ConvGeo& g, const float* x, float* xt, int cp, cudaStream_t st) {
+  if (!samples_input(g)) return to_nhwc(x, xt, g.N, g.C, cp, g.HW, st);
+  dim3 grid((unsigned)((g.HoWo + 31) / 32), (unsigned)((cp + 31) / 32), (unsigned)g.N);
+  FLB200_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "nchw_to_nhwc: extent out of range");
+  nchw_to_nhwc_sampled_kernel<<<grid, 256, 0, st>>>(x, xt, g.C, cp, g.HW, g.W, g.Wo, g.HoWo, g.sx,
+                                                   g.sy);
+  FLB200_AFTER_LAUNCH("nchw_to_nhwc_sampled");
+  return FLB200_OK;
+}
+
 // Filter w[co][ci][tap] repacked to out[tap][rows][kp] with (rows, k) = (co, ci) for the
 // forward pass and (ci, co) for backward-data; k >= its extent is zero.
 __global__ void pack_filter_kernel(const float* __restrict__ w, float* __restrict__ out, int Cout,
@@ -366,7 +415,8 @@ bool patch_conv_supported(const ConvGeo& g) {
          g.sx <= 2 && g.sy <= 2 && g.N <= 65535;
 }
 
-size_t patch_conv_workspace_bytes(const ConvGeo& g, int which) {
+size_t patch_conv_workspace_bytes(const ConvGeo& g0, int which) {
+  const ConvGeo g = which == 1 ? g0 : sampled_geo(g0);
   const int cp = up4(g.C), cop = up4(g.Cout);
   if (which == 0)
     return up256((size_t)g.N * g.HW * cp * 4) + up256((size_t)g.RS * g.Cout * cp * 4);
@@ -377,21 +427,22 @@ size_t patch_conv_workspace_bytes(const ConvGeo& g, int which) {
 }
 
 size_t patch_conv_cache_bytes(const ConvGeo& g, int which) {
-  if (which == 0) return up256((size_t)g.N * g.HW * up4(g.C) * 4);
+  if (which == 0) return up256((size_t)g.N * sampled_geo(g).HW * up4(g.C) * 4);
   return up256((size_t)g.N * g.HoWo * up4(g.Cout) * 4);
 }
 
-int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
+int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const float* bias,
                        float* y, void* ws, size_t ws_bytes, cudaStream_t st,
-    flb200_conv2d_cache* cache) {
+                       flb200_conv2d_cache* cache) {
   (void)ws_bytes;
+  const ConvGeo g = sampled_geo(g0);
   const int cp = up4(g.C);
   char* base = static_cast<char*>(ws);
   const ClSlot xs = cl_slot(cache, 0, (size_t)g.N * g.HW * cp * 4, reinterpret_cast<float*>(base));
   float* xt = xs.buf;
   float* wp = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HW * cp * 4));
   if (!xs.valid) {
-    if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
+    if (int rc = x_to_nhwc(g0, x, xt, cp, st)) return rc;
     if (xs.flag) *xs.flag = 1;
   }
   pack_filter_kernel<<<grid_for((long long)g.RS * g.Cout * cp, 256), 256, 0, st>>>(
@@ -490,9 +541,10 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
   return FLB200_OK;
 }
 
-int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
+int patch_conv_backward_filter(const ConvGeo& g0, const float* gy, const float* x, float* gw,
                                void* ws, size_t ws_bytes, cudaStream_t st,
-    flb200_conv2d_cache* cache) {
+                               flb200_conv2d_cache* cache) {
+  const ConvGeo g = sampled_geo(g0);
   (void)ws_bytes;
   const int cp = up4(g.C), cop = up4(g.Cout);
   const WgradPlan wp = plan_wgrad(g);
@@ -506,7 +558,7 @@ int patch_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x
   off += up256((size_t)g.N * g.HoWo * cop * 4);
   float* partial = reinterpret_cast<float*>(base + off);
   if (!xs.valid) {
-    if (int rc = to_nhwc(x, xt, g.N, g.C, cp, g.HW, st)) return rc;
+    if (int rc = x_to_nhwc(g0, x, xt, cp, st)) return rc;
     if (xs.flag) *xs.flag = 1;
   }
   if (gs.valid) {
