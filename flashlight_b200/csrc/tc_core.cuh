@@ -202,26 +202,6 @@ __device__ __forceinline__ void operand_coords(const OperandCoords& p, int mn, i
     c[d] = p.base[d] + mn * p.mn_mul[d] + k_lo * p.k_mul[d] + k_hi * p.k2_mul[d] + z * p.z_mul[d];
 }
 
-// Issues the TMA loads of one operand tile (ROWS = 128 for A, BN for B) into `dst`.
-template <int ROWS>
-__device__ __forceinline__ void load_operand(const CUtensorMap* map, const OperandCoords& p,
-                                             uint64_t* bar, char* dst, int mn0, int k_lo, int k_hi,
-                                             int z) {
-  int c[4];
-  operand_coords(p, mn0, k_lo, k_hi, z, c);
-  if (p.mn_major) {
-#pragma unroll
-    for (int j = 0; j < ROWS / 32; ++j) {
-      int cj[4];
-#pragma unroll
-      for (int d = 0; d < 4; ++d) cj[d] = c[d] + 32 * j * p.mn_mul[d];
-      tma_load(map, bar, dst + j * (kBK * 128), p.rank, cj);
-    }
-  } else {
-    tma_load(map, bar, dst, p.rank, c);
-  }
-}
-
 __device__ __forceinline__ long long epi_off(int idx, int div, long long stride,
                                              long long outer) {
   if (div == 0) return (long long)idx * stride;

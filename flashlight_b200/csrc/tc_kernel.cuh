@@ -3,10 +3,12 @@
 //   D = sum_k A(m,k) * B(k,n),  fp32 operands read as TF32, fp32 accumulation in TMEM.
 //
 // One CTA per SM walks a static list of 128 x BN output tiles:
-//   warp 0   : TMA producer — one lane issues cp.async.bulk.tensor loads (never multicast)
-//              into a STAGES-deep ring of 128-byte-swizzled shared-memory tiles and runs
-//              ahead into the next output tile while the current one drains.  Its per-stage
-//              work is a handful of multiply-adds: coordinates advance incrementally.
+//   warp 0   : TMA producer — issues cp.async.bulk.tensor loads (never multicast) into a
+//              STAGES-deep ring of 128-byte-swizzled shared-memory tiles and runs ahead into
+//              the next output tile while the current one drains.  Lane 0 owns the
+//              barriers; every lane issues at most one copy per stage, so the boxes of a
+//              stage go out together.  Per-stage work is a handful of multiply-adds:
+//              coordinates advance incrementally.
 //   warp 1   : allocates TMEM (2 accumulators of BN columns); one lane issues tcgen05.mma
 //              for each ready stage and tcgen05.commit to free the stage / publish the tile
 //   warps 2-5: epilogue — tcgen05.ld the finished accumulator (32 lanes each) and store it
@@ -19,13 +21,16 @@
 //
 // A problem policy P tells the skeleton what a tile is:
 //   int  a_mn_major, b_mn_major;
+//   static constexpr bool kWarpProducer;  // load() is called by the whole warp (else lane 0)
 //   struct Tile;  struct LoadState;
 //   __device__ int  num_tiles() const;
 //   __device__ void decode(int tile, Tile&) const;
 //   __device__ int  k_begin(const Tile&) const;  __device__ int k_end(const Tile&) const;
-//   __device__ void load_begin(const Tile&, LoadState&) const;     // once per tile
+//   __device__ void load_begin(const Tile&, LoadState&, int lane) const;   // once per tile
 //   __device__ void load(const CUtensorMap* a, const CUtensorMap* b, const Tile&, LoadState&,
-//                        uint64_t* bar, char* a_dst, char* b_dst) const;  // one stage, advances
+//                        uint64_t* bar, char* a_dst, char* b_dst, int lane) const;
+//                        // one stage, called by the whole warp: lane 0 posts the byte count,
+//                        // lane i issues copy i; every lane advances its LoadState
 //   __device__ bool chunk_live(const Tile&, int c0) const;                // warp-uniform
 //   __device__ void store(const Tile&, int row, int c0, const float* v) const;  // 32 columns
 #pragma once
@@ -89,13 +94,41 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
-      uint32_t s = 0, round = 0;
-      typename P::Tile t;
-      typename P::LoadState ls;
+    uint32_t s = 0, round = 0;
+    typename P::Tile t;
+    typename P::LoadState ls;
+    if constexpr (P::kWarpProducer) {
+      // All 32 lanes walk the loop: lane 0 waits for the stage to be free and posts the byte
+      // count, then each lane issues one of the stage's copies (a single instruction for
+      // the warp), so a stage made of many boxes costs the same issue time as a small one.
+      bool live = true;
+      for (int tile = blockIdx.x; live && tile < n_tiles; tile += gridDim.x) {
+        int stop = 0;
+        if (lane == 0) stop = *failed;
+        if (__shfl_sync(0xffffffffu, stop, 0) != 0) break;
+        prob.decode(tile, t);
+        prob.load_begin(t, ls, lane);
+        const int k1 = prob.k_end(t);
+        for (int k = prob.k_begin(t); k < k1; ++k) {
+          int ok = 1;
+          if (lane == 0 && round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+            *failed = 1;
+            ok = 0;
+          }
+          if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
+            live = false;
+            break;
+          }
+          char* a_dst = tiles + s * SL::kStageBytes;
+          prob.load(&map_a, &map_b, t, ls, &full_bar[s], a_dst, a_dst + SL::kABytes, lane);
+          if (++s == STAGES) { s = 0; ++round; }
+        }
+      }
+    } else if (lane == 0) {
+      // Two copies per stage: one lane does everything and the loop has no warp exchange.
       for (int tile = blockIdx.x; tile < n_tiles && *failed == 0; tile += gridDim.x) {
         prob.decode(tile, t);
-        prob.load_begin(t, ls);
+        prob.load_begin(t, ls, 0);
         const int k1 = prob.k_end(t);
         for (int k = prob.k_begin(t); k < k1; ++k) {
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
@@ -103,7 +136,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             break;
           }
           char* a_dst = tiles + s * SL::kStageBytes;
-          prob.load(&map_a, &map_b, t, ls, &full_bar[s], a_dst, a_dst + SL::kABytes);
+          prob.load(&map_a, &map_b, t, ls, &full_bar[s], a_dst, a_dst + SL::kABytes, 0);
           if (++s == STAGES) { s = 0; ++round; }
         }
       }
@@ -192,6 +225,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 // together share the (large) A tile through L2.
 template <int BN>
 struct GemmProblem {
+  static constexpr bool kWarpProducer = true;
   OperandCoords a, b;
   EpiloguePlan ep;
   int a_mn_major, b_mn_major;
@@ -214,7 +248,7 @@ struct GemmProblem {
   }
   __device__ __forceinline__ int k_begin(const Tile& t) const { return t.k0; }
   __device__ __forceinline__ int k_end(const Tile& t) const { return t.k1; }
-  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls) const {
+  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls, int) const {
     ls.a_hi = a.k_inner > 0 ? t.k0 / a.k_inner : 0;
     ls.a_lo = t.k0 - ls.a_hi * a.k_inner;
     ls.b_hi = b.k_inner > 0 ? t.k0 / b.k_inner : 0;
@@ -222,10 +256,22 @@ struct GemmProblem {
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst) const {
-    mbar_expect_tx(bar, (kBM + BN) * kBK * 4);
-    load_operand<kBM>(ma, a, bar, a_dst, t.m0, ls.a_lo, ls.a_hi, t.z);
-    load_operand<BN>(mb, b, bar, b_dst, t.n0, ls.b_lo, ls.b_hi, t.z);
+                                       char* b_dst, int lane) const {
+    if (lane == 0) mbar_expect_tx(bar, (kBM + BN) * kBK * 4);
+    __syncwarp();
+    // a K-major operand is one box, an MN-major one a box per 32 rows: lanes [0, na) take A,
+    // lanes [na, na + nb) take B
+    const int na = a_mn_major ? kBM / 32 : 1, nb = b_mn_major ? BN / 32 : 1;
+    if (lane < na) {
+      int c[4];
+      operand_coords(a, t.m0 + 32 * lane, ls.a_lo, ls.a_hi, t.z, c);
+      tma_load(ma, bar, a_dst + lane * (kBK * 128), a.rank, c);
+    } else if (lane < na + nb) {
+      const int j = lane - na;
+      int c[4];
+      operand_coords(b, t.n0 + 32 * j, ls.b_lo, ls.b_hi, t.z, c);
+      tma_load(mb, bar, b_dst + j * (kBK * 128), b.rank, c);
+    }
     if (++ls.a_lo == a.k_inner) { ls.a_lo = 0; ++ls.a_hi; }
     if (++ls.b_lo == b.k_inner) { ls.b_lo = 0; ++ls.b_hi; }
   }

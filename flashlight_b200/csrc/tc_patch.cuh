@@ -41,6 +41,7 @@ struct TapGrid {
 
 template <int BN>
 struct PatchConvProblem {
+  static constexpr bool kWarpProducer = false;
   int a_mn_major, b_mn_major;  // 0, 0
   // patch geometry (all powers of two, NB * PH * QW == 128)
   int QW, PH, NB, qw_shift, ph_shift;
@@ -70,7 +71,7 @@ struct PatchConvProblem {
   }
   __device__ __forceinline__ int k_begin(const Tile&) const { return 0; }
   __device__ __forceinline__ int k_end(const Tile&) const { return ntaps * cchunks; }
-  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls) const {
+  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls, int) const {
     ls.i = 0;
     ls.j = 0;
     ls.cc = 0;
@@ -80,7 +81,7 @@ struct PatchConvProblem {
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst) const {
+                                       char* b_dst, int) const {
     mbar_expect_tx(bar, (kBM + BN) * kBK * 4);  // NB*PH*QW == 128 rows of 128 bytes + B tile
     int ca[4] = {ls.cc * kBK, ls.aw, ls.ah, t.b0};
     tma_load(ma, bar, a_dst, 4, ca);
@@ -131,6 +132,7 @@ struct PatchConvProblem {
 
 template <int BN>
 struct PatchWgradProblem {
+  static constexpr bool kWarpProducer = true;
   int a_mn_major, b_mn_major;  // 1, 1
   int QW, PH;                  // 32-pixel patch: QW * PH == 32
   int tiles_q, tiles_p, images;
@@ -145,7 +147,7 @@ struct PatchWgradProblem {
   float* partial;              // [split][tap][M][N]
 
   struct Tile { int m0, n0, tap0, ntap, cn_live, split, k0, k1; };
-  struct LoadState { int qi, pi, img, dw0, dh0, s0; };
+  struct LoadState { int qi, pi, img, dw, dh; };
 
   __device__ __forceinline__ int num_tiles() const {
     return tiles_m * tiles_n * tap_groups * splits;
@@ -163,38 +165,34 @@ struct PatchWgradProblem {
   }
   __device__ __forceinline__ int k_begin(const Tile& t) const { return t.k0; }
   __device__ __forceinline__ int k_end(const Tile& t) const { return t.k1; }
-  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls) const {
+  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls, int lane) const {
     int r = t.k0;
     ls.qi = r % tiles_q; r /= tiles_q;
     ls.pi = r % tiles_p; r /= tiles_p;
     ls.img = r;
-    const int tr = t.tap0 / kW;
-    ls.s0 = t.tap0 - tr * kW;
-    ls.dw0 = ls.s0 * dil_x - pad_x;
-    ls.dh0 = tr * dil_y - pad_y;
+    // lane 0 copies dy, lane j >= 1 the x box of tap tap0 + j - 1
+    const int tap = t.tap0 + max(lane - 1, 0);
+    const int tr = tap / kW, ts = tap - tr * kW;
+    ls.dw = ts * dil_x - pad_x;
+    ls.dh = tr * dil_y - pad_y;
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst) const {
+                                       char* b_dst, int lane) const {
     const int q0 = ls.qi * QW, p0 = ls.pi * PH;
-    const int bw = q0 * b_w_mul, bh = p0 * b_h_mul;
     // The channel index is split into (32 contiguous channels, group of 32) in both maps, so
     // one copy brings every 32 x 32 box of an operand: a_nbox boxes of dy, and per tap
     // 1 << cn_shift boxes of x.  Boxes past the last channel are zero-filled or hold a
     // neighbouring pixel's channels; they only reach accumulator rows / columns that the
     // epilogue never stores.
-    mbar_expect_tx(bar, (a_nbox + (t.ntap << cn_shift)) * (kBK * 128));
-    int ca[5] = {0, q0, p0, ls.img, t.m0 >> 5};
-    tma_load(ma, bar, a_dst, 5, ca);
-    int dw = ls.dw0, dh = ls.dh0, s = ls.s0;
-#pragma unroll
-    for (int j = 0; j < BN / 32; ++j) {
-      if (j < t.ntap) {
-        int cb[5] = {0, bw + dw, bh + dh, ls.img, t.n0 >> 5};
-        tma_load(mb, bar, b_dst + (j << cn_shift) * (kBK * 128), 5, cb);
-        dw += dil_x;
-        if (++s == kW) { s = 0; dw -= kW * dil_x; dh += dil_y; }
-      }
+    if (lane == 0) mbar_expect_tx(bar, (a_nbox + (t.ntap << cn_shift)) * (kBK * 128));
+    __syncwarp();
+    if (lane == 0) {
+      int ca[5] = {0, q0, p0, ls.img, t.m0 >> 5};
+      tma_load(ma, bar, a_dst, 5, ca);
+    } else if (lane <= t.ntap) {
+      int cb[5] = {0, q0 * b_w_mul + ls.dw, p0 * b_h_mul + ls.dh, ls.img, t.n0 >> 5};
+      tma_load(mb, bar, b_dst + ((lane - 1) << cn_shift) * (kBK * 128), 5, cb);
     }
     if (++ls.qi == tiles_q) {
       ls.qi = 0;
