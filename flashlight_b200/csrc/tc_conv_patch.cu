@@ -221,7 +221,7 @@ struct PatchArgs {
   tc::TapGrid taps;
   float* out;
   const float* bias;
-  int out_H, out_W, out_C, oh_mul, oh_add, ow_mul, ow_add;
+  int out_H, out_W, out_C, oh_mul, oh_add, ow_mul, ow_add, fill_cell;
 };
 template <int BN>
 int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, cudaStream_t st) {
@@ -238,6 +238,7 @@ int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, 
   p.out = a.out; p.bias = a.bias;
   p.out_H = a.out_H; p.out_W = a.out_W; p.out_C = a.out_C;
   p.oh_mul = a.oh_mul; p.oh_add = a.oh_add; p.ow_mul = a.ow_mul; p.ow_add = a.ow_add;
+  p.fill_cell = a.fill_cell;
   return launch_patch<BN>(ma, mb, p, st);
 }
 int run_patch_any(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a,
@@ -507,12 +508,21 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
     pr.off_step = -(pr.step * dil) / stride;
     return pr;
   };
-  bool any_empty = false;
+  int empty = 0, live = 0;
+  bool origin_live = false;
   for (int ca = 0; ca < g.sy; ++ca)
-    for (int cb = 0; cb < g.sx; ++cb)
-      any_empty = any_empty || progression(ca, g.py, g.dy, g.sy, g.kH).count == 0 ||
-                  progression(cb, g.px, g.dx, g.sx, g.kW).count == 0;
-  if (any_empty) FLB200_CUDA_CHECK(cudaMemsetAsync(gx, 0, (size_t)g.N * g.C * g.HW * 4, st));
+    for (int cb = 0; cb < g.sx; ++cb) {
+      const bool none = progression(ca, g.py, g.dy, g.sy, g.kH).count == 0 ||
+                        progression(cb, g.px, g.dx, g.sx, g.kW).count == 0;
+      empty += none;
+      live += !none;
+      if (!none && ca == 0 && cb == 0) origin_live = true;
+    }
+  // When (0, 0) is the only class that any tap reaches (a 1 x 1 filter without padding) its
+  // launch writes the zeros of the other classes itself; otherwise clear gx first.
+  const bool fill_cell = live == 1 && origin_live && empty > 0;
+  if (empty > 0 && !fill_cell)
+    FLB200_CUDA_CHECK(cudaMemsetAsync(gx, 0, (size_t)g.N * g.C * g.HW * 4, st));
   for (int ca = 0; ca < g.sy; ++ca)
     for (int cb = 0; cb < g.sx; ++cb) {
       const Prog ph = progression(ca, g.py, g.dy, g.sy, g.kH);
@@ -532,6 +542,7 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
       a.out = gx; a.bias = nullptr;
       a.out_H = g.H; a.out_W = g.W; a.out_C = g.C;
       a.oh_mul = g.sy; a.oh_add = ca; a.ow_mul = g.sx; a.ow_add = cb;
+      a.fill_cell = fill_cell ? 1 : 0;
       CUtensorMap ma;
       if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, a.patch.QW, a.patch.PH,
                             a.patch.NB, 1, 1, tc::kMapKMajor))

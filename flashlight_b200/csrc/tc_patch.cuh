@@ -57,6 +57,7 @@ struct PatchConvProblem {
   const float* bias;
   int out_H, out_W, out_C;
   int oh_mul, oh_add, ow_mul, ow_add;
+  int fill_cell;  // see store()
 
   struct Tile { int q0, p0, b0, n0; };
   struct LoadState { int i, j, cc, aw, ah, wtap; };
@@ -111,6 +112,30 @@ struct PatchConvProblem {
     const int img = t.b0 + (row >> (qw_shift + ph_shift));
     if (q >= pix_w || p >= pix_h || img >= images) return;
     const long long plane = (long long)out_H * out_W;
+    if (fill_cell) {
+      // Strided backward-data whose only class with taps is (0, 0): this pixel owns the whole
+      // oh_mul x ow_mul cell and writes its zeros too, so the tensor needs no separate
+      // clearing pass and every 32-byte sector is written whole.
+      float* cell = out + ((long long)img * out_C + nb) * plane +
+                    (long long)(p * oh_mul) * out_W + q * ow_mul;
+      const bool pair = ow_mul == 2 && (out_W & 1) == 0;
+      for (int a = 0; a < oh_mul; ++a) {
+        if (p * oh_mul + a >= out_H) break;
+        float* rowp = cell + (long long)a * out_W;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (nb + j >= n_out) break;
+          const float val = a == 0 ? v[j] : 0.f;
+          if (pair) {
+            *reinterpret_cast<float2*>(rowp + j * plane) = make_float2(val, 0.f);
+          } else {
+            for (int b = 0; b < ow_mul; ++b)
+              if (q * ow_mul + b < out_W) rowp[j * plane + b] = b == 0 ? val : 0.f;
+          }
+        }
+      }
+      return;
+    }
     float* dst = out + ((long long)img * out_C + nb) * plane +
                  (long long)(p * oh_mul + oh_add) * out_W + (q * ow_mul + ow_add);
     if (nb + 32 <= n_out) {

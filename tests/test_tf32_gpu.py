@@ -131,6 +131,7 @@ TF32_CONV_CASES = [
     (2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1, True),     # 3x3
     (2, 128, 14, 14, 128, 3, 3, 2, 2, 1, 1, 1, 1, 1, True),   # 3x3 stride 2
     (2, 256, 14, 14, 512, 1, 1, 2, 2, 0, 0, 1, 1, 1, True),   # 1x1 stride 2 downsample
+    (2, 32, 9, 11, 48, 1, 1, 3, 2, 0, 0, 1, 1, 1, True),      # 1x1, strides (3, 2), odd extents
     (2, 3, 32, 32, 64, 7, 7, 2, 2, 3, 3, 1, 1, 1, True),      # stem: K = 147 (padded filter rows)
     (4, 1, 28, 28, 32, 5, 5, 1, 1, 2, 2, 1, 1, 1, True),      # MNIST conv1: K = 25
     (3, 3, 37, 45, 24, 3, 3, 1, 2, 1, 0, 1, 1, 1, True),      # few channels, ragged, mixed stride
