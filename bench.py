@@ -244,6 +244,14 @@ def install_timers(timer: OpTimer, ext, F):
 
 
 TENSOR_OPS = {"conv2d", "conv2dBackwardData", "conv2dBackwardFilterBias", "linear", "linear_backward"}
+CONV_OPS = ("conv2d", "conv2dBackwardData", "conv2dBackwardFilterBias")
+CONV_KERNEL = "tc_persistent_kernel (conv2d + conv2dBackwardData + conv2dBackwardFilterBias)"
+# dram__bytes_read.sum + dram__bytes_write.sum of every convolution kernel of one step at
+# batch 256 in TF32 mode, from one ncu capture of
+# `python -m flashlight_b200.opbench --suite resnet50_step_convs --batch 256 --math tf32`
+# (summary under profiles/); algorithmic bytes of the same calls: 66.2e9.
+CONV_DRAM_BYTES_PER_STEP_B256 = 74.6e9
+FP32_FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
 def run_gpu_arm(args) -> None:
@@ -349,16 +357,33 @@ def run_gpu_arm(args) -> None:
     peaks = measured_peaks()
     ops = timer.summary()
     total_op_ms = sum(v["ms"] for v in ops.values()) or 1.0
-    top = max(ops, key=lambda k: ops[k]["ms"])
-    tv = ops[top]
-    if top in TENSOR_OPS:
+    # The dominant kernel is the tcgen05 contraction (tc_persistent_kernel) behind the three
+    # convolution operators; they are reported as one group, helpers (layout copies, split-K
+    # reductions) included, because that is what one convolution call costs.
+    conv_ops = [k for k in CONV_OPS if k in ops]
+    groups = {k: v for k, v in ops.items() if k not in CONV_OPS}
+    if conv_ops:
+        groups[CONV_KERNEL] = {key: sum(ops[k][key] for k in conv_ops)
+                               for key in ("ms", "flops", "bytes", "calls")}
+    top = max(groups, key=lambda k: groups[k]["ms"])
+    tv = groups[top]
+    if top == CONV_KERNEL or top in TENSOR_OPS:
         achieved = tv["flops"] / (tv["ms"] * 1e-3) / 1e12
-        # TF32 has half the tensor rate of bf16; the measured bf16 cuBLAS figure is the only
-        # driver-measured tensor number, so the TF32 peak is taken as half of it.
-        peak = peaks["bf16_tflops_sustained"] / 2
+        if math_mode == L.MATH_TF32:
+            # TF32 has half the tensor rate of bf16; the measured bf16 cuBLAS figure is the
+            # only driver-measured tensor number, so the TF32 peak is taken as half of it.
+            peak = peaks["bf16_tflops_sustained"] / 2
+            src = f"{peaks['source']} bf16 sustained / 2 (tf32 rate)"
+            traffic = None
+            if top == CONV_KERNEL and B == 256:
+                traffic = CONV_DRAM_BYTES_PER_STEP_B256 * args.steps / max(tv["calls"], 1)
+        else:
+            peak = FP32_FMA_TFLOPS
+            src = "nominal fp32 FMA rate (148 SMs x 128 lanes x 2 x 1.965 GHz): strict mode uses no tensor cores"
+            traffic = None
         roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None,
-                "peak_source": f"{peaks['source']} bf16 sustained / 2 (tf32 rate)"}
+                "frac": achieved / peak, "traffic": traffic, "peak_source": src,
+                "per": "convolution call (average over the step's calls)"}
     else:
         achieved = tv["bytes"] / (tv["ms"] * 1e-3) / 1e9
         peak = peaks["hbm_gbs"]

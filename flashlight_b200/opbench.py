@@ -140,6 +140,40 @@ def bench_conv(op, conv, iters, math):
                   extra={"hbm_floor_ms": nbytes / (peaks()[0] * 1e9) * 1e3})
 
 
+def measure_cublas_tf32(n=8192, burst_iters=20, sustained_s=3.0):
+    """The denominator that TF32-mode fractions can be read against: cuBLAS (through
+    torch.matmul, TF32 allowed) on n^3, as a short burst and as a seconds-long loop under
+    the power cap.  Library code measuring the peak; never on an operator's path."""
+    import time
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(n, n, device="cuda")
+        b = torch.randn(n, n, device="cuda")
+        for _ in range(5):
+            a @ b
+        burst_ms = time_op(lambda: a @ b, burst_iters)
+        torch.cuda.synchronize()
+        t0 = time.time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = 0
+        e0.record()
+        while time.time() - t0 < sustained_s:
+            for _ in range(20):
+                a @ b
+            iters += 20
+            torch.cuda.synchronize()
+        e1.record()
+        torch.cuda.synchronize()
+        sustained_ms = e0.elapsed_time(e1) / iters
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    flops = 2.0 * n ** 3
+    print(json.dumps({"op": "cublas_tf32_peak", "n": n,
+                      "burst_tflops": flops / (burst_ms * 1e-3) / 1e12,
+                      "sustained_tflops": flops / (sustained_ms * 1e-3) / 1e12}), flush=True)
+
+
 # distinct ResNet-50 convolution shapes: Cin, H(=W), Cout, k, stride, pad
 RESNET50_CONVS = [
     (3, 224, 64, 7, 2, 3), (64, 56, 64, 1, 1, 0), (64, 56, 64, 3, 1, 1), (64, 56, 256, 1, 1, 0),
@@ -151,6 +185,42 @@ RESNET50_CONVS = [
     (512, 7, 2048, 1, 1, 0), (1024, 14, 2048, 1, 2, 0), (2048, 7, 512, 1, 1, 0),
     (512, 7, 512, 3, 1, 1),
 ]
+
+
+# how often each shape above occurs in ResNet-50 (bottleneck blocks 3-4-6-3)
+RESNET50_COUNTS = [1, 1, 3, 4, 2, 1, 1, 4, 1, 3, 3, 1, 1, 6, 1, 5, 5, 1, 1, 3, 1, 2, 2]
+
+
+def suite_resnet50_step_convs(batch, math):
+    """Every convolution call of one ResNet-50 training step, once, in the call pattern of
+    the autograd tape (forward, backward-data, backward-filter sharing one payload) and with
+    nothing else on the device: the command to put under a profiler when the per-step DRAM
+    traffic of the convolution kernels is wanted at the full batch size."""
+    mode = L.MATH_TF32 if math == "tf32" else L.MATH_STRICT_F32
+    ext = B200AutogradExtension(mode)
+    flops = 0.0
+    algo_bytes = 0
+    for (ci, hw, co, k, s, p), count in zip(RESNET50_CONVS, RESNET50_COUNTS):
+        x = torch.randn(batch, ci, hw, hw, device="cuda")
+        w = torch.randn(co, ci, k, k, device="cuda") * (1.0 / (ci * k * k) ** 0.5)
+        args = (s, s, p, p, 1, 1, 1)
+        for _ in range(count):
+            payload = AutogradPayload()
+            y = ext.conv2d(x, w, None, *args, payload)
+            g = torch.ones_like(y)
+            n_pass = 2
+            if ci != 3:
+                ext.conv2dBackwardData(g, x, w, *args, None, payload)
+                n_pass = 3
+            ext.conv2dBackwardFilterBias(g, x, w, None, *args, None, None, payload)
+            flops += n_pass * 2.0 * y.numel() * ci * k * k
+            # interface tensors of the three calls: each reads two of {x, w, y} and writes one
+            algo_bytes += n_pass * 4 * (x.numel() + y.numel() + w.numel())
+            del y, g, payload
+        torch.cuda.synchronize()
+    print(json.dumps({"suite": "resnet50_step_convs", "batch": batch, "math": math,
+                      "conv_calls": int(sum(RESNET50_COUNTS) * 3 - 1), "flops": flops,
+                      "algorithmic_bytes": algo_bytes}), flush=True)
 
 
 def suite_resnet50(batch, iters, math):
@@ -185,6 +255,10 @@ def main():
         raise SystemExit("opbench needs a CUDA device")
     shape = tuple(int(v) for v in a.shape.split(","))
     conv = tuple(int(v) for v in a.conv.split(","))
+    if a.op == "cublas_tf32_peak":
+        return measure_cublas_tf32()
+    if a.suite == "resnet50_step_convs":
+        return suite_resnet50_step_convs(a.batch, a.math)
     if a.suite == "resnet50":
         return suite_resnet50(a.batch, a.iters, a.math)
     if a.op in ("relu", "relu_backward", "add", "gelu_backward"):

@@ -111,7 +111,8 @@ int flb200_conv2d_backward_filter_bias(const flb200_conv2d_desc* d, const void* 
  * made by forward and the copy of grad_y made by backward-data instead of making them again.
  * The reference hands every backend the same kind of per-call-site state:
  * std::shared_ptr<detail::AutogradPayload> in flashlight/fl/autograd/tensor/
- * AutogradExtension.h:58-69, 110-138.  The caller owns both buffers (sizes from
+ * AutogradExtension.h:58-69, 110-138 (created once per call site in
+ * flashlight/fl/autograd/Functions.cpp:1341).  The caller owns both buffers (sizes from
  * flb200_conv2d_cache_bytes; a NULL or short buffer is simply not used) and the flags:
  *   x_cl_valid   set by forward (and by backward-filter when it had to make the copy);
  *                clear it when x changes.
