@@ -324,7 +324,7 @@ int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, f
     const int k_inner = (g.HW + tc::kBK - 1) / tc::kBK;
     if (int rc = map3d(&ma, gy, g.HW, g.Cout, g.N, g.HW, (long long)g.Cout * g.HW, tc::kBM, false))
       return rc;
-    if (int rc = map3d(&mb, x, g.HW, g.C, g.N, g.HW, (long long)g.C * g.HW, bn, false)) return rc;
+    if (int rc = map3d(&mb, x, g.HW, g.C, g.N, g.HW, (long long)g.C * g.HW, tc::b_box_rows(g.Cout, g.C, (long long)g.N * k_inner, false, false), false)) return rc;
     tc::OperandPlan pa = plan_k_major(3), pb = plan_k_major(3);
     pa.k2_dim = pb.k2_dim = 2;
     pa.k2_scale = pb.k2_scale = 1;
@@ -348,7 +348,7 @@ int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, f
                                                                       s.hwp_out, s.ld_out);
   FLB200_AFTER_LAUNCH("planes_to_rows");
   if (int rc = map2d(&ma, dyt, s.ld_out, g.Cout, s.ld_out, tc::kBM, false)) return rc;
-  if (int rc = map2d(&mb, col, s.ld_out, s.kc, s.ld_out, bn, false)) return rc;
+  if (int rc = map2d(&mb, col, s.ld_out, s.kc, s.ld_out, tc::b_box_rows(g.Cout, s.kc, (s.ld_out + tc::kBK - 1) / tc::kBK, false, false), false)) return rc;
   ep.m_stride = s.kc;
   return tc::run(ma, mb, plan_k_major(2), plan_k_major(2), ep, g.Cout, s.kc,
                  (s.ld_out + tc::kBK - 1) / tc::kBK, 1, base + off, ws_bytes - off, st);

@@ -3,7 +3,6 @@
 //
 // Scratch traffic per pass: one transposed copy of the activation operand (8 bytes per
 // element) and a repacked filter; there is no im2col matrix.
-#include <cstdlib>
 
 #include "tc_conv.cuh"
 #include "tc_patch.cuh"
@@ -204,17 +203,13 @@ int filter_map(CUtensorMap* m, const float* base, int kext, int kp, int rows, in
   return tc::make_tensor_map(m, base, 3, dims, strides, box, tc::kMapKMajor);
 }
 
-template <int BN>
-int launch_patch(const CUtensorMap& ma, const CUtensorMap& mb, tc::PatchConvProblem<BN>& p,
-                 cudaStream_t st) {
-  p.tiles_n = (p.n_out + BN - 1) / BN;
-  const long long tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b * p.tiles_n;
-  FLB200_REQUIRE(tiles < 0x7fffffffLL, "patch conv: too many tiles");
-  return tc::launch_problem<tc::PatchConvProblem<BN>, BN>("tc_patch_conv", ma, mb, p, tiles, st);
-}
+// CTA pairs (tc_pair.cuh) for 256-column tiles: each CTA then loads half of the filter tile.
+// Measured on the ResNet-50 step: about 1 % of the step; no gain at 128 columns.
+bool patch_uses_pairs(int bn) { return bn >= 256; }
 
 // Fills the parts of the problem that do not depend on BN and launches with the BN that fits
-// the number of output channels.
+// the number of output channels.  The filter map must have been made with
+// filter_box_rows(bn) rows per box.
 struct PatchArgs {
   Patch patch;
   int pix_w, pix_h, images, n_out, cchunks, ntaps, a_w_mul, a_h_mul;
@@ -223,6 +218,8 @@ struct PatchArgs {
   const float* bias;
   int out_H, out_W, out_C, oh_mul, oh_add, ow_mul, ow_add, fill_cell;
 };
+int filter_box_rows(int bn) { return patch_uses_pairs(bn) ? bn / 2 : bn; }
+
 template <int BN>
 int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, cudaStream_t st) {
   tc::PatchConvProblem<BN> p;
@@ -239,7 +236,15 @@ int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, 
   p.out_H = a.out_H; p.out_W = a.out_W; p.out_C = a.out_C;
   p.oh_mul = a.oh_mul; p.oh_add = a.oh_add; p.ow_mul = a.ow_mul; p.ow_add = a.ow_add;
   p.fill_cell = a.fill_cell;
-  return launch_patch<BN>(ma, mb, p, st);
+  p.tiles_n = (p.n_out + BN - 1) / BN;
+  const long long m_tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b;
+  FLB200_REQUIRE(m_tiles * p.tiles_n < 0x7fffffffLL, "patch conv: too many tiles");
+  if constexpr (BN >= 256) {
+    return tc::launch_pair_problem<tc::PatchConvProblem<BN>, BN>(
+        "tc_patch_conv_pair", ma, mb, p, ((m_tiles + 1) / 2) * p.tiles_n, st);
+  }
+  return tc::launch_problem<tc::PatchConvProblem<BN>, BN>("tc_patch_conv", ma, mb, p,
+                                                          m_tiles * p.tiles_n, st);
 }
 int run_patch_any(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a,
                   cudaStream_t st) {
@@ -464,7 +469,7 @@ int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const 
   if (int rc = nhwc_map(&ma, xt, g.C, cp, g.W, g.H, g.N, a.patch.QW, a.patch.PH, a.patch.NB, g.sx,
                         g.sy, tc::kMapKMajor))
     return rc;
-  if (int rc = filter_map(&mb, wp, g.C, cp, g.Cout, g.RS, bn)) return rc;
+  if (int rc = filter_map(&mb, wp, g.C, cp, g.Cout, g.RS, filter_box_rows(bn))) return rc;
   return run_patch_any(bn, ma, mb, a, st);
 }
 
@@ -485,7 +490,7 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
   FLB200_AFTER_LAUNCH("pack_filter");
   const int bn = tc::pick_bn(g.C);
   CUtensorMap mb;
-  if (int rc = filter_map(&mb, wd, g.Cout, cop, g.C, g.RS, bn)) return rc;
+  if (int rc = filter_map(&mb, wd, g.Cout, cop, g.C, g.RS, filter_box_rows(bn))) return rc;
   // One launch per parity class (a, b) of the input pixel: h = p*sy + a, w = q*sx + b.  Only
   // the taps with (a + py - r*dy) divisible by sy reach that class.
   // One launch per parity class (a, b) of the input pixel: h = p*sy + a, w = q*sx + b.  Only
@@ -643,7 +648,7 @@ int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const 
   if (int rc = window_map(&ma, xtp, wg, g.N, a.patch.QW, a.patch.PH, a.patch.NB, g.sx, g.sy))
     return rc;
   const int bn = tc::pick_bn(g.Cout);
-  if (int rc = filter_map(&mb, wr, 32, 32, g.Cout, g.kH, bn)) return rc;
+  if (int rc = filter_map(&mb, wr, 32, 32, g.Cout, g.kH, filter_box_rows(bn))) return rc;
   if (!xs.valid) {
     const long long total = (long long)g.N * wg.Hp * wg.Wp;
     nchw_to_nhwc4_pad_kernel<<<grid_for(total, 256), 256, 0, st>>>(

@@ -7,7 +7,7 @@
 #include <cstdlib>
 #include <mutex>
 
-#include "tc_kernel.cuh"
+#include "tc_pair.cuh"
 
 namespace flb200 {
 namespace tc {
@@ -123,6 +123,12 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const Opera
   p.partial = partial;
   const long long tiles = (long long)p.tiles_m * p.tiles_n * Z * L.splits;
   FLB200_REQUIRE(tiles < 0x7fffffffLL, "tc_gemm: too many tiles");
+  if constexpr (BN >= 128) {
+    if (gemm_uses_pairs(M, N, k_iters, pa.mn_major != 0, pb.mn_major != 0)) {
+      const long long pair_tiles = (long long)((p.tiles_m + 1) / 2) * p.tiles_n * Z * L.splits;
+      return launch_pair_problem<GemmProblem<BN>, BN>("tc_gemm_pair", ma, mb, p, pair_tiles, st);
+    }
+  }
   return launch_problem<GemmProblem<BN>, BN>("tc_gemm", ma, mb, p, tiles, st);
 }
 
@@ -133,6 +139,15 @@ int pick_bn(long long N) {
   if (N <= 64) return 64;
   if (N < 192) return 128;
   return 256;
+}
+
+bool gemm_uses_pairs(long long M, long long N, long long k_iters, bool a_mn_major,
+                     bool b_mn_major) {
+  return pick_bn(N) >= 128 && M > kBM && !a_mn_major && !b_mn_major && k_iters >= 64;
+}
+int b_box_rows(long long M, long long N, long long k_iters, bool a_mn_major, bool b_mn_major) {
+  const int bn = pick_bn(N);
+  return gemm_uses_pairs(M, N, k_iters, a_mn_major, b_mn_major) ? bn / 2 : bn;
 }
 
 void plan_splits(long long tiles, long long k_iters, long long min_ips, int* splits_out,
@@ -306,7 +321,8 @@ int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void*
     M = d->m; N = d->n;
     const int bn = tc::pick_bn(N);
     if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch, tc::kBM, &ma, &pa)) return rc;
-    if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch, bn, &mb, &pb)) return rc;
+    if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch,
+                               tc::b_box_rows(M, N, k_iters, p.a.mn_major, p.b.mn_major), &mb, &pb)) return rc;
     ep.m_stride = d->c_row;
     ep.n_stride = d->c_col;
   } else {
@@ -314,7 +330,8 @@ int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void*
     M = d->n; N = d->m;
     const int bn = tc::pick_bn(N);
     if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch, tc::kBM, &ma, &pa)) return rc;
-    if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch, bn, &mb, &pb)) return rc;
+    if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch,
+                               tc::b_box_rows(M, N, k_iters, p.b.mn_major, p.a.mn_major), &mb, &pb)) return rc;
     ep.m_stride = d->c_col;
     ep.n_stride = d->c_row;
   }

@@ -69,6 +69,14 @@ struct Launch {
 };
 
 int pick_bn(long long N);
+// Whether an M x N contraction runs on CTA pairs (two SMs per 256 x BN tile, each loading half
+// of the B tile), and the number of rows a K-major B map must put in one box accordingly.
+// Pairs pay off when both operands are K-major single boxes and the K loop is long (the
+// backward-filter shapes); tiles with a short K loop lose more to the cross-CTA hand-offs
+// per tile than they gain (measured).
+bool gemm_uses_pairs(long long M, long long N, long long k_iters, bool a_mn_major,
+                     bool b_mn_major);
+int b_box_rows(long long M, long long N, long long k_iters, bool a_mn_major, bool b_mn_major);
 // Tile width, split-K factor and scratch size for an M x N output over k_iters stages, Z batches.
 Launch plan_launch(long long M, long long N, long long k_iters, long long Z);
 // Split-K factor for `tiles` output tiles of k_iters stage iterations each, at least min_ips

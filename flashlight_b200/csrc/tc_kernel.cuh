@@ -275,6 +275,41 @@ struct GemmProblem {
     if (++ls.a_lo == a.k_inner) { ls.a_lo = 0; ++ls.a_hi; }
     if (++ls.b_lo == b.k_inner) { ls.b_lo = 0; ++ls.b_hi; }
   }
+  // CTA pairs (tc_pair.cuh): the halves of a pair tile are two consecutive 128-row blocks of
+  // the same column block, batch and K slice; row blocks run fastest, then splits, columns,
+  // batches.  With an odd number of row blocks the last pair has a phantom half past M
+  // (zero-filled loads, masked stores).
+  __device__ __forceinline__ int num_pair_tiles() const {
+    return ((tiles_m + 1) >> 1) * splits * tiles_n * Z;
+  }
+  __device__ __forceinline__ void decode_pair(int tile, int rank, Tile& t) const {
+    const int pairs_m = (tiles_m + 1) >> 1;
+    int r = tile;
+    t.m0 = (2 * (r % pairs_m) + rank) * kBM; r /= pairs_m;
+    t.split = r % splits; r /= splits;
+    t.n0 = (r % tiles_n) * BN; r /= tiles_n;
+    t.z = r;
+    t.k0 = t.split * iters_per_split;
+    t.k1 = min(t.k0 + iters_per_split, k_iters);
+  }
+  __device__ __forceinline__ void load_pair(const CUtensorMap* ma, const CUtensorMap* mb,
+                                            const Tile& t, LoadState& ls, uint32_t full_bar,
+                                            char* a_dst, char* b_dst, int rank, int lane) const {
+    // this CTA's 128 rows of A and its BN/2 columns of B
+    const int na = a_mn_major ? kBM / 32 : 1, nb = b_mn_major ? BN / 64 : 1;
+    if (lane < na) {
+      int c[4];
+      operand_coords(a, t.m0 + 32 * lane, ls.a_lo, ls.a_hi, t.z, c);
+      tma_load_pair(ma, full_bar, a_dst + lane * (kBK * 128), a.rank, c);
+    } else if (lane < na + nb) {
+      const int j = lane - na;
+      int c[4];
+      operand_coords(b, t.n0 + rank * (BN / 2) + 32 * j, ls.b_lo, ls.b_hi, t.z, c);
+      tma_load_pair(mb, full_bar, b_dst + j * (kBK * 128), b.rank, c);
+    }
+    if (++ls.a_lo == a.k_inner) { ls.a_lo = 0; ++ls.a_hi; }
+    if (++ls.b_lo == b.k_inner) { ls.b_lo = 0; ++ls.b_hi; }
+  }
   __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
     return t.n0 + c0 < N;
   }

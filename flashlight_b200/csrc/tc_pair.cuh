@@ -1,0 +1,252 @@
+// The persistent tcgen05 contraction on CTA PAIRS (tcgen05 cta_group::2).
+//
+// Two CTAs of a 2-CTA cluster (two SMs) compute one 256 x BN output tile: each CTA owns
+// 128 rows of it (its own accumulator in its own TMEM) and brings its own 128 x 32 A tile,
+// but only HALF of the 32 x BN B tile per stage; the tensor cores of both SMs read both
+// halves.  Per SM and stage that is 16 KB + BN * 64 bytes instead of 16 KB + BN * 128:
+// at BN = 256 a third less TMA traffic for the same math, and six stages fit in the ring
+// instead of four.  One tcgen05.mma.cta_group::2 issued by the leader CTA (cluster rank 0)
+// drives both SMs.
+//
+// Hand-offs (every wait bounded as in tc_kernel.cuh):
+//   full[s]    leader's barrier; the TMA loads of BOTH CTAs complete their bytes on it
+//              (cp.async.bulk.tensor .cta_group::2, plain loads: nothing is multicast)
+//   empty[s]   one per CTA; tcgen05.commit.cta_group::2 arrives on both when the MMAs that
+//              read stage s are done
+//   tfull[a]   one per CTA; tcgen05.commit arrives on both when accumulator a is complete
+//   tempty[a]  leader's barrier; the 4 epilogue warps of each CTA arrive on it (the peer's
+//              through a remote mbarrier.arrive) once they have drained accumulator a
+// The cluster synchronises after barrier initialisation and before TMEM is freed, so no CTA
+// signals a barrier of a peer that has not started or has already left.
+//
+// A policy used here adds to the interface of tc_kernel.cuh:
+//   __device__ int  num_pair_tiles() const;
+//   __device__ void decode_pair(int pair_tile, int rank, Tile&) const;  // this CTA's half
+//   __device__ void load_pair(const CUtensorMap* a, const CUtensorMap* b, const Tile&, LoadState&,
+//                             uint32_t full_bar_cluster_addr, char* a_dst, char* b_dst,
+//                             int rank, int lane) const;
+//                             // called by the whole producer warp; lane i issues copy i.
+//                             // A: this CTA's 128 rows; B: rows n0 + rank * BN/2 ...
+#pragma once
+#include <cuda_runtime.h>
+
+#include "tc_kernel.cuh"
+
+namespace flb200 {
+namespace tc {
+
+template <int BN, int STAGES>
+struct PairSmemLayout {
+  static constexpr int kABytes = kBM * kBK * 4;         // 16 KB: this CTA's 128 rows
+  static constexpr int kBBytes = (BN / 2) * kBK * 4;    // this CTA's half of the columns
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTileBytes = STAGES * kStageBytes;
+  static constexpr int kBarBytes = 512;
+  static constexpr int kTotal = kTileBytes + kBarBytes + 1024;
+};
+constexpr int pair_stages_for(int bn) { return bn >= 256 ? 6 : 8; }
+
+template <class P, int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads)
+tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+               const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
+  using SL = PairSmemLayout<BN, STAGES>;
+  static_assert(BN >= 64 && BN % 64 == 0, "each CTA holds BN/2 columns in 32-column boxes");
+  extern __shared__ char smem_raw[];
+  char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                        ~static_cast<uintptr_t>(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + SL::kTileBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tfull_bar = empty_bar + STAGES;
+  uint64_t* tempty_bar = tfull_bar + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  constexpr uint32_t kTmemCols = 2 * BN;
+  const int n_tiles = prob.num_pair_tiles();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);   // leader: its own arrive.expect_tx for both CTAs' bytes
+      mbar_init(&empty_bar[s], 1);  // one tcgen05.commit arrival
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull_bar[a], 1);
+      mbar_init(&tempty_bar[a], 8);  // leader: 4 epilogue warps of each CTA
+    }
+    *failed = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) tmem_alloc_pair(tmem_slot, kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // The whole warp walks the loop (see tc_kernel.cuh): lane 0 owns the barriers, lane i
+    // issues copy i of the stage.
+    uint32_t s = 0, round = 0;
+    typename P::Tile t;
+    typename P::LoadState ls;
+    bool live = true;
+    for (int tile = pair; live && tile < n_tiles; tile += n_pairs) {
+      int stop = 0;
+      if (lane == 0) stop = *failed;
+      if (__shfl_sync(0xffffffffu, stop, 0) != 0) {
+        live = false;
+        break;
+      }
+      prob.decode_pair(tile, (int)rank, t);
+      prob.load_begin(t, ls, lane);
+      const int k1 = prob.k_end(t);
+      for (int k = prob.k_begin(t); k < k1; ++k) {
+        int ok = 1;
+        if (lane == 0) {
+          if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
+            *failed = 1;
+            ok = 0;
+          } else if (rank == 0) {
+            mbar_expect_tx(&full_bar[s], 2 * SL::kStageBytes);
+          }
+        }
+        if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
+          live = false;
+          break;
+        }
+        char* a_dst = tiles + s * SL::kStageBytes;
+        prob.load_pair(&map_a, &map_b, t, ls, mapa_u32(smem_u32(&full_bar[s]), 0), a_dst,
+                       a_dst + SL::kABytes, (int)rank, lane);
+        if (++s == STAGES) { s = 0; ++round; }
+      }
+    }
+    // The leader's last commits still arrive on this CTA's empty barriers: wait for them
+    // so that the CTA does not leave while they are in flight.
+    if (live && lane == 0 && *failed == 0) {
+      for (int i = 0; i < STAGES; ++i) {
+        const uint32_t fills = round + (static_cast<uint32_t>(i) < s ? 1u : 0u);
+        if (fills > 0 && !mbar_wait(&empty_bar[i], (fills - 1) & 1)) {
+          *failed = 1;
+          break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc_tf32_pair(BN, prob.a_mn_major, prob.b_mn_major);
+      uint32_t s = 0, round = 0, nt = 0;
+      typename P::Tile t;
+      for (int tile = pair; tile < n_tiles && *failed == 0; tile += n_pairs, ++nt) {
+        prob.decode_pair(tile, 0, t);
+        const uint32_t acc = nt & 1, around = nt >> 1;
+        if (around > 0 && !mbar_wait(&tempty_bar[acc], (around - 1) & 1)) {
+          *failed = 4;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        const int k0 = prob.k_begin(t), k1 = prob.k_end(t);
+        for (int k = k0; k < k1; ++k) {
+          if (!mbar_wait(&full_bar[s], round & 1)) {
+            *failed = 2;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + s * SL::kStageBytes);
+          const uint32_t b_addr = a_addr + SL::kABytes;
+#pragma unroll
+          for (int j = 0; j < kBK / kUmmaK; ++j) {
+            const uint64_t ad = prob.a_mn_major
+                                    ? umma_desc(a_addr + j * 1024, kBK * 128, 512, 1)
+                                    : umma_desc(a_addr + j * 32, 16, 1024, 2);
+            const uint64_t bd = prob.b_mn_major
+                                    ? umma_desc(b_addr + j * 1024, kBK * 128, 512, 1)
+                                    : umma_desc(b_addr + j * 32, 16, 1024, 2);
+            umma_tf32_pair(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[s]);  // frees stage s in both CTAs
+          if (++s == STAGES) { s = 0; ++round; }
+        }
+        umma_commit_pair(&tfull_bar[acc]);  // both CTAs' halves of the accumulator complete
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    uint32_t nt = 0;
+    typename P::Tile t;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++nt) {
+      prob.decode_pair(tile, (int)rank, t);
+      const uint32_t acc = nt & 1, around = nt >> 1;
+      if (*failed != 0) break;
+      if (!mbar_wait(&tfull_bar[acc], around & 1)) {
+        *failed = 3;
+        break;
+      }
+      tc_fence_after();
+      if (*failed != 0) break;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        if (!prob.chunk_live(t, c0)) continue;
+        float v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
+        prob.store(t, row, c0, v);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *failed != 0 && status) atomicExch(status, *failed);
+  cluster_sync_all();  // the peer is done with this CTA's barriers and tensor memory
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <class P, int BN>
+int launch_pair_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& mb,
+                        const P& prob, long long pair_tiles, cudaStream_t st) {
+  constexpr int STAGES = pair_stages_for(BN);
+  using SL = PairSmemLayout<BN, STAGES>;
+  if (pair_tiles <= 0) return FLB200_OK;
+  static bool configured[64] = {false};
+  int dev = 0;
+  FLB200_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_pair_kernel<P, BN, STAGES>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SL::kTotal));
+    configured[dev] = true;
+  }
+  const long long pairs = device_info().sm_count / 2;
+  const unsigned grid = 2u * (unsigned)(pair_tiles < pairs ? pair_tiles : pairs);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = SL::kTotal;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  FLB200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tc_pair_kernel<P, BN, STAGES>, ma, mb, prob,
+                                       status_ptr()));
+  FLB200_AFTER_LAUNCH(name);
+  count_tc_launch();
+  return FLB200_OK;
+}
+
+}  // namespace tc
+}  // namespace flb200

@@ -24,7 +24,7 @@
 //     k     = 32-pixel patches (QW x PH) of every image; split over CTAs, partial sums are
 //             reduced in a fixed order by a second kernel.
 #pragma once
-#include "tc_kernel.cuh"
+#include "tc_pair.cuh"
 
 namespace flb200 {
 namespace tc {
@@ -70,6 +70,48 @@ struct PatchConvProblem {
     t.p0 = (r % tiles_p) * PH; r /= tiles_p;
     t.b0 = r * NB;
   }
+  // CTA pairs: the two halves of a pair tile are consecutive pixel patches that share the
+  // column block n0 (hence the whole B tile and the K loop).  Patches are enumerated fastest,
+  // column blocks slowest; an odd patch count leaves the last pair a phantom half whose image
+  // index is out of range (its loads are zero-filled, its stores masked).
+  __device__ __forceinline__ int num_pair_tiles() const {
+    return ((tiles_q * tiles_p * tiles_b + 1) >> 1) * tiles_n;
+  }
+  __device__ __forceinline__ void decode_pair(int tile, int rank, Tile& t) const {
+    const int pairs_m = (tiles_q * tiles_p * tiles_b + 1) >> 1;
+    const int nt = tile / pairs_m;
+    int r = 2 * (tile - nt * pairs_m) + rank;
+    t.n0 = nt * BN;
+    t.q0 = (r % tiles_q) * QW; r /= tiles_q;
+    t.p0 = (r % tiles_p) * PH; r /= tiles_p;
+    t.b0 = r * NB;
+  }
+  __device__ __forceinline__ void load_pair(const CUtensorMap* ma, const CUtensorMap* mb,
+                                            const Tile& t, LoadState& ls, uint32_t full_bar,
+                                            char* a_dst, char* b_dst, int rank, int lane) const {
+    if (lane == 0) {
+      int ca[4] = {ls.cc * kBK, ls.aw, ls.ah, t.b0};
+      tma_load_pair(ma, full_bar, a_dst, 4, ca);
+    } else if (lane == 1) {
+      int cb[4] = {ls.cc * kBK, t.n0 + rank * (BN / 2), ls.wtap, 0};  // this CTA's half of B
+      tma_load_pair(mb, full_bar, b_dst, 3, cb);
+    }
+    advance(ls);
+  }
+  __device__ __forceinline__ void advance(LoadState& ls) const {
+    if (++ls.cc == cchunks) {  // next tap: j fastest
+      ls.cc = 0;
+      ls.aw += taps.dw_step;
+      ls.wtap += taps.s_step;
+      if (++ls.j == taps.nj) {
+        ls.j = 0;
+        ++ls.i;
+        ls.aw -= taps.nj * taps.dw_step;
+        ls.ah += taps.dh_step;
+        ls.wtap += taps.r_step * taps.kW - taps.nj * taps.s_step;
+      }
+    }
+  }
   __device__ __forceinline__ int k_begin(const Tile&) const { return 0; }
   __device__ __forceinline__ int k_end(const Tile&) const { return ntaps * cchunks; }
   __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls, int) const {
@@ -88,18 +130,7 @@ struct PatchConvProblem {
     tma_load(ma, bar, a_dst, 4, ca);
     int cb[4] = {ls.cc * kBK, t.n0, ls.wtap, 0};
     tma_load(mb, bar, b_dst, 3, cb);
-    if (++ls.cc == cchunks) {  // next tap: j fastest
-      ls.cc = 0;
-      ls.aw += taps.dw_step;
-      ls.wtap += taps.s_step;
-      if (++ls.j == taps.nj) {
-        ls.j = 0;
-        ++ls.i;
-        ls.aw -= taps.nj * taps.dw_step;
-        ls.ah += taps.dh_step;
-        ls.wtap += taps.r_step * taps.kW - taps.nj * taps.s_step;
-      }
-    }
+    advance(ls);
   }
   __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
     return t.n0 + c0 < n_out;
