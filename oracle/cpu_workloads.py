@@ -60,3 +60,62 @@ def resnet50_step(params, x, targets, blocks=(3, 4, 6, 3)):
     loss = resnet50_loss(ps, x, targets, blocks)
     grads = torch.autograd.grad(loss, ps)
     return loss.detach(), grads
+
+
+def _step(loss_fn, params, *args):
+    ps = [p.detach().clone().requires_grad_(True) for p in params]
+    loss = loss_fn(ps, *args)
+    grads = torch.autograd.grad(loss, ps)
+    return loss.detach(), grads
+
+
+def mnist_convnet_loss(params, x, targets, dropout_mask, p_drop=0.5):
+    """The README convnet (flashlight README.md quick start): conv 5x5 SAME + ReLU + maxpool 2x2
+    twice, Linear 3136->1024, ReLU, Dropout (mask given as data, kept values scaled by
+    1/(1-p): flashlight/fl/autograd/Functions.cpp:1777-1785), Linear 1024->10, logSoftmax, CE.
+    params: conv1 w, b, conv2 w, b, fc1 w (I,O), b, fc2 w (I,O), b."""
+    w1, b1, w2, b2, f1, c1, f2, c2 = params
+    h = F.max_pool2d(F.relu(F.conv2d(x, w1, b1, padding=2)), 2, 2)
+    h = F.max_pool2d(F.relu(F.conv2d(h, w2, b2, padding=2)), 2, 2)
+    h = F.relu(h.reshape(h.shape[0], -1) @ f1 + c1)
+    h = h * dropout_mask / (1.0 - p_drop)
+    return F.nll_loss(F.log_softmax(h @ f2 + c2, -1), targets.long())
+
+
+def mnist_convnet_step(params, x, targets, dropout_mask):
+    return _step(mnist_convnet_loss, params, x, targets, dropout_mask)
+
+
+def conv_asr_loss(params, x, targets, kw=13, eps=1e-5):
+    """x (B, feat, 1, T).  Each layer: Conv2D kW x 1 SAME with bias
+    (flashlight/pkg/runtime/common/SequentialBuilder.cpp:215-226), LayerNorm over fl axes
+    {0,1,2} = all of (T, 1, C) of one batch element, no affine (:332-350), ReLU; then frames
+    become rows (b, t) and a Linear gives class scores; frame-wise mean cross entropy.
+    params: (conv w, conv b) per layer, then head w (C, classes), head b."""
+    it = iter(params[:-2])
+    h = x
+    for w in it:
+        b = next(it)
+        h = F.conv2d(h, w, b, padding=(0, same_pad(h.shape[-1], kw, 1)))
+        h = F.relu(F.layer_norm(h, h.shape[1:], None, None, eps))
+    B, C, _, T = h.shape
+    rows = h.permute(0, 3, 2, 1).reshape(B * T, C)
+    scores = rows @ params[-2] + params[-1]
+    return F.nll_loss(F.log_softmax(scores, -1), targets.long())
+
+
+def conv_asr_step(params, x, targets, kw=13):
+    return _step(lambda ps, a, b: conv_asr_loss(ps, a, b, kw), params, x, targets)
+
+
+def bilstm_loss(params, x, target, hidden, layers):
+    """x (T, B, I); fl::RNN(I, hidden, layers, LSTM, bidirectional) then mean squared error
+    against a dense target (flashlight/fl/nn/modules/Loss.cpp:17-31).  params: the flat weight
+    vector."""
+    from oracle import flref
+    y, _, _ = flref.rnn(x, None, None, params[0], hidden, layers, flref.RNN_LSTM, True)
+    return ((y - target) ** 2).mean()
+
+
+def bilstm_step(params, x, target, hidden, layers):
+    return _step(lambda ps, a, b: bilstm_loss(ps, a, b, hidden, layers), params, x, target)

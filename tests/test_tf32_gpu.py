@@ -138,6 +138,8 @@ TF32_CONV_CASES = [
     (2, 4, 20, 19, 40, 5, 8, 2, 1, 0, 3, 1, 2, 1, True),      # 4 channels, 8-wide filter rows, dilated rows
     (2, 2, 12, 200, 16, 2, 3, 1, 1, 1, 1, 1, 1, 1, True),     # few channels, rows wider than one patch
     (2, 80, 1, 100, 96, 1, 13, 1, 1, 6, 0, 1, 1, 1, True),    # conv-ASR time convolution
+    (3, 48, 1, 50, 48, 1, 13, 1, 1, 6, 0, 1, 1, 1, True),     # 48 channels: half-filled 32-channel groups
+    (3, 16, 1, 50, 48, 1, 13, 1, 1, 6, 0, 1, 1, 1, True),     # 16 channels
     (7, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 1, 1, 1, True),        # reference test shape, ragged pixels
     (2, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 2, 1, 1, True),        # dilation
     (2, 8, 9, 10, 6, 3, 4, 1, 1, 2, 1, 1, 1, 2, False),       # groups: fp32 kernel

@@ -1,0 +1,112 @@
+"""One training step of each benchmark workload (scaled down) on the GPU kernels against the
+CPU restatement in oracle/cpu_workloads.py: loss and every parameter gradient.
+
+Bounds: strict fp32 mode — loss 1e-4 relative, every gradient within 1e-3 of its largest
+magnitude (a whole network deep, the per-operator 1e-4 bound compounds).  TF32 mode — loss 2e-3
+relative; gradients are only bounded in the aggregate (relative L2 error <= 0.15 per parameter):
+operand rounding moves pre-activations by ~1e-3, which flips ReLU masks and max-pool winners of
+near-tied elements, and every flip reroutes gradient.  On the tensors that actually occur inside
+these steps each TF32 operator stays within its own 2e-3 bound (tests/test_tf32_gpu.py is the
+per-operator gate); the aggregate bound here only guards against gross errors."""
+import pytest
+import torch
+
+from oracle import cpu_workloads as CW
+
+pytestmark = pytest.mark.gpu
+
+BOUNDS = {"strict": (1e-4, 1e-3), "tf32": (2e-3, 0.15)}
+
+
+@pytest.fixture(scope="module")
+def L():
+    from flashlight_b200 import _lib
+    if not _lib.lib.flb200_has_tensor_core_path():
+        pytest.fail("tensor-core path unavailable on this device")
+    return _lib
+
+
+@pytest.fixture(params=["strict", "tf32"])
+def mode(request, L):
+    from flashlight_b200 import autograd as A
+    A.set_math_mode(L.MATH_TF32 if request.param == "tf32" else L.MATH_STRICT_F32)
+    yield request.param
+    A.set_math_mode(L.MATH_STRICT_F32)
+
+
+def check_step(model, loss, want_loss, want_grads, mode):
+    loss_tol, grad_tol = BOUNDS[mode]
+    got = float(loss.tensor.cpu())
+    want = float(want_loss)
+    assert abs(got - want) <= loss_tol * max(1.0, abs(want)), (got, want)
+    params = model.parameters()
+    assert len(params) == len(want_grads)
+    for i, (p, wg) in enumerate(zip(params, want_grads)):
+        assert p.grad is not None, f"parameter {i} received no gradient"
+        gg = p.grad.detach().cpu().double().reshape(wg.shape)
+        if mode == "strict":
+            scale = float(wg.abs().max()) or 1.0
+            err = float((gg - wg).abs().max()) / scale
+        else:
+            err = float((gg - wg).norm()) / (float(wg.norm()) or 1.0)
+        assert err <= grad_tol, f"parameter {i} {tuple(wg.shape)}: gradient error {err:.3e}"
+
+
+def host_params(model):
+    return [p.tensor.detach().cpu().double() for p in model.parameters()]
+
+
+def test_mnist_convnet_step(L, mode):
+    from flashlight_b200 import nn, workloads
+    model = workloads.mnist_convnet(seed=3)
+    drop = [m for m in model.trunk.children if isinstance(m, nn.Dropout)][0]
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(16, 1, 28, 28, generator=g)
+    t = torch.randint(0, 10, (16,), generator=g, dtype=torch.int32)
+    state = drop.gen.get_state()  # the mask is drawn from this state during forward
+    loss = model.loss(x.cuda(), t.cuda())
+    loss.backward()
+    g2 = torch.Generator()
+    g2.set_state(state)
+    mask = (torch.rand((16, 1024), generator=g2) > 0.5).double()
+    want_loss, want_grads = CW.mnist_convnet_step(host_params(model), x.double(), t, mask)
+    check_step(model, loss, want_loss, want_grads, mode)
+
+
+def test_resnet_step(L, mode):
+    from flashlight_b200 import workloads
+    model = workloads.resnet50(seed=7, blocks=(1, 1, 1), classes=10, width=16)
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(4, 3, 112, 112, generator=g)
+    t = torch.randint(0, 10, (4,), generator=g, dtype=torch.int32)
+    loss = model.loss(x.cuda(), t.cuda())
+    loss.backward()
+    want_loss, want_grads = CW.resnet50_step(host_params(model), x.double(), t, blocks=(1, 1, 1))
+    check_step(model, loss, want_loss, want_grads, mode)
+
+
+def test_conv_asr_step(L, mode):
+    from flashlight_b200 import workloads
+    model = workloads.ConvAsr(feat=16, channels=48, layers=3, classes=7, kw=13, seed=9)
+    g = torch.Generator().manual_seed(13)
+    B, T = 3, 50
+    x = torch.randn(B, 16, 1, T, generator=g)
+    t = torch.randint(0, 7, (B * T,), generator=g, dtype=torch.int32)
+    loss = model.loss(x.cuda(), t.cuda())
+    loss.backward()
+    want_loss, want_grads = CW.conv_asr_step(host_params(model), x.double(), t)
+    check_step(model, loss, want_loss, want_grads, mode)
+
+
+def test_bilstm_step(L, mode):
+    from flashlight_b200 import workloads
+    hidden, layers, T, B, I = 32, 2, 9, 4, 20
+    model = workloads.BiLstm(input_size=I, hidden=hidden, layers=layers, seed=17)
+    g = torch.Generator().manual_seed(19)
+    x = torch.randn(T, B, I, generator=g)
+    target = torch.randn(T, B, 2 * hidden, generator=g)
+    loss = model.loss(x.cuda(), target.cuda())
+    loss.backward()
+    want_loss, want_grads = CW.bilstm_step(host_params(model), x.double(), target.double(), hidden,
+                                           layers)
+    check_step(model, loss, want_loss, want_grads, mode)
