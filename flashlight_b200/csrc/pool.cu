@@ -139,6 +139,187 @@ __global__ void __launch_bounds__(256) pool_backward_kernel(const T* __restrict_
   }
 }
 
+// ------------------------------------------------------------ tiled fp32 max pooling
+// The generic kernels above read each input element through the cache once per covering
+// window.  For fp32 max pooling (the workloads' hot case) a CTA instead owns a band of
+// output rows of one plane: the input rows the band needs are one contiguous range, copied
+// to shared memory with 16-byte loads; windows are then scanned out of shared memory.
+// band_rows output rows per CTA; tile = ((band_rows - 1) * sy + wy) * W floats of dynamic
+// shared memory.  Same selection rule as window_argmax.
+// WX, WY, SX, SY: window and stride as compile-time constants for the common cases (0 = take
+// them from the geometry), so that the index arithmetic has no runtime divisions.
+template <int WX, int WY, int SX, int SY>
+__global__ void __launch_bounds__(256)
+pool_forward_max_tile_kernel(const float* __restrict__ x, float* __restrict__ y,
+                             uint8_t* __restrict__ argmax, PoolGeo g, int band_rows, int nbands) {
+  extern __shared__ float tile[];
+  const int wx = WX ? WX : g.wx, wy = WY ? WY : g.wy, sx = SX ? SX : g.sx, sy = SY ? SY : g.sy;
+  const long long plane = blockIdx.x / nbands;
+  const int band = blockIdx.x - (int)(plane * nbands);
+  const int p0 = band * band_rows;
+  const int p1 = min(p0 + band_rows, g.Ho);
+  const int h_lo = max(p0 * sy - g.py, 0);
+  const int h_hi = min((p1 - 1) * sy - g.py + wy, g.H);
+  const float* src = x + plane * (long long)g.H * g.W + (long long)h_lo * g.W;
+  const int n = (h_hi - h_lo) * g.W;
+  if ((g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    for (int i = threadIdx.x * 4; i < n; i += 256 * 4)
+      *reinterpret_cast<float4*>(tile + i) = *reinterpret_cast<const float4*>(src + i);
+  } else {
+    for (int i = threadIdx.x; i < n; i += 256) tile[i] = src[i];
+  }
+  __syncthreads();
+  float* yp = y + plane * (long long)g.Ho * g.Wo;
+  uint8_t* ap = argmax ? argmax + plane * (long long)g.Ho * g.Wo : nullptr;
+  // 64 x 4 threads: columns across the x index, rows across the y index
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  for (int p = p0 + ty; p < p1; p += 4) {
+    const int h0 = p * sy - g.py;
+    for (int q = tx; q < g.Wo; q += 64) {
+      const int w0 = q * sx - g.px;
+      float best = -INFINITY;
+      int arg = 255;
+      if (h0 >= 0 && h0 + wy <= g.H && w0 >= 0 && w0 + wx <= g.W) {
+        // window inside the image: no per-element bounds checks
+        const float* row = tile + (h0 - h_lo) * g.W + w0;
+        best = row[0];
+        arg = 0;
+#pragma unroll
+        for (int ky = 0; ky < wy; ++ky) {
+#pragma unroll
+          for (int kx = 0; kx < wx; ++kx) {
+            const float v = row[ky * g.W + kx];
+            if (v > best || v != v) {
+              best = v;
+              arg = ky * wx + kx;
+            }
+          }
+        }
+      } else {
+#pragma unroll
+        for (int ky = 0; ky < wy; ++ky) {
+          const int h = h0 + ky;
+          if (h < 0 || h >= g.H) continue;
+          const float* row = tile + (h - h_lo) * g.W;
+#pragma unroll
+          for (int kx = 0; kx < wx; ++kx) {
+            const int w = w0 + kx;
+            if (w < 0 || w >= g.W) continue;
+            const float v = row[w];
+            if (arg == 255 || v > best || v != v) {
+              best = v;
+              arg = ky * wx + kx;
+            }
+          }
+        }
+      }
+      yp[p * g.Wo + q] = best;
+      if (ap) ap[p * g.Wo + q] = (uint8_t)arg;
+    }
+  }
+}
+
+// Gradient: a CTA owns a band of INPUT rows of one plane, copies the dy values and argmax
+// bytes of every output row whose windows reach the band into shared memory, and each thread
+// then gathers a strip of four input pixels from them in a fixed order (no atomics).
+template <int WX, int WY, int SX, int SY>
+__global__ void __launch_bounds__(256)
+pool_backward_max_tile_kernel(const float* __restrict__ dy, const uint8_t* __restrict__ argmax,
+                              float* __restrict__ dx, PoolGeo g, int band_rows, int nbands,
+                              int max_out_rows) {
+  extern __shared__ float tile[];  // [max_out_rows][Wo] dy, then the argmax bytes
+  const int wx = WX ? WX : g.wx, wy = WY ? WY : g.wy, sx = SX ? SX : g.sx, sy = SY ? SY : g.sy;
+  uint8_t* sel = reinterpret_cast<uint8_t*>(tile + (size_t)max_out_rows * g.Wo);
+  const long long plane = blockIdx.x / nbands;
+  const int band = blockIdx.x - (int)(plane * nbands);
+  const int h0 = band * band_rows;
+  const int h1 = min(h0 + band_rows, g.H);
+  const int p_lo = max(ceil_div_pos(h0 + g.py - wy + 1, sy), 0);
+  const int p_hi = min((h1 - 1 + g.py) / sy, g.Ho - 1);
+  const int n = (p_hi - p_lo + 1) * g.Wo;
+  const long long obase = plane * (long long)g.Ho * g.Wo + (long long)p_lo * g.Wo;
+  for (int i = threadIdx.x; i < n; i += 256) {
+    tile[i] = dy[obase + i];
+    sel[i] = argmax[obase + i];
+  }
+  __syncthreads();
+  const int strips_w = (g.W + 3) >> 2;
+  float* dxp = dx + plane * (long long)g.H * g.W;
+  const bool vec_ok = (g.W & 3) == 0 && (reinterpret_cast<uintptr_t>(dx) & 15) == 0;
+  // 32 x 8 threads: strips of four pixels across a row, rows across ty
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int h = h0 + ty; h < h1; h += 8) {
+    const int pa = max(ceil_div_pos(h + g.py - wy + 1, sy), 0);
+    const int pb = min((h + g.py) / sy, g.Ho - 1);
+    for (int sw = tx; sw < strips_w; sw += 32) {
+      const int w0 = sw << 2;
+      const int qa = max(ceil_div_pos(w0 + g.px - wx + 1, sx), 0);
+      const int qb = min((w0 + 3 + g.px) / sx, g.Wo - 1);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int p = pa; p <= pb; ++p) {
+        const int ky_mine = h + g.py - p * sy;
+        const int rbase = (p - p_lo) * g.Wo;
+        for (int q = qa; q <= qb; ++q) {
+          const int s = sel[rbase + q];
+          const int ky = s / wx, kx = s - ky * wx;
+          const int wt = q * sx - g.px + kx - w0;  // position inside the strip
+          if (ky == ky_mine && wt >= 0 && wt < 4) {
+            const float v = tile[rbase + q];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (wt == j) acc[j] += v;
+          }
+        }
+      }
+      float* dst = dxp + (long long)h * g.W + w0;
+      if (vec_ok) {
+        *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (w0 + j < g.W) dst[j] = acc[j];
+      }
+    }
+  }
+}
+
+template <int WX, int WY, int SX, int SY>
+void launch_pool_fwd_tile(const float* x, float* y, uint8_t* argmax, const PoolGeo& g, int band,
+                          int nbands, size_t smem, cudaStream_t st) {
+  pool_forward_max_tile_kernel<WX, WY, SX, SY><<<(unsigned)(g.planes * nbands), 256, smem, st>>>(
+      x, y, argmax, g, band, nbands);
+}
+template <int WX, int WY, int SX, int SY>
+void launch_pool_bwd_tile(const float* dy, const uint8_t* argmax, float* dx, const PoolGeo& g,
+                          int band, int nbands, int out_rows, size_t smem, cudaStream_t st) {
+  pool_backward_max_tile_kernel<WX, WY, SX, SY>
+      <<<(unsigned)(g.planes * nbands), 256, smem, st>>>(dy, argmax, dx, g, band, nbands, out_rows);
+}
+bool is_window(const PoolGeo& g, int wx, int wy, int sx, int sy) {
+  return g.wx == wx && g.wy == wy && g.sx == sx && g.sy == sy;
+}
+
+// Band height for the tiled kernels: enough outputs per CTA to occupy 256 threads, tile within
+// 40 KB.  Returns 0 when a single band does not fit (very wide planes): generic kernels then.
+int pool_fwd_band_rows(const PoolGeo& g) {
+  int rows = (512 + g.Wo - 1) / g.Wo;
+  if (rows > g.Ho) rows = g.Ho;
+  while (rows > 1 && (size_t)((rows - 1) * g.sy + g.wy) * g.W * 4 > 40 * 1024) --rows;
+  if ((size_t)((rows - 1) * g.sy + g.wy) * g.W * 4 > 40 * 1024) return 0;
+  return rows;
+}
+int pool_bwd_band_rows(const PoolGeo& g, int* max_out_rows) {
+  int rows = (2048 + g.W - 1) / g.W;  // ~512 strips of four pixels
+  if (rows > g.H) rows = g.H;
+  for (;; --rows) {
+    const int outs = (rows + g.wy - 2) / g.sy + 2;
+    if ((size_t)outs * g.Wo * 5 + 16 <= 40 * 1024 || rows <= 1) {
+      *max_out_rows = outs;
+      return (size_t)outs * g.Wo * 5 + 16 <= 40 * 1024 ? rows : 0;
+    }
+  }
+}
+
 // Max-pooling gradient with the argmax payload, the hot case of the workloads.  A thread owns
 // a strip of four adjacent input pixels of one plane (one 16-byte store) and walks the few
 // windows that overlap the strip once, decoding where each window sent its gradient; planes
@@ -233,6 +414,23 @@ int flb200_pool2d_forward(const flb200_pool2d_desc* d, const void* x, void* y, u
   const long long total = g.planes * g.Ho * g.Wo;
   const int grid = grid_for(total, 256);
   cudaStream_t st = as_stream(stream);
+  if (d->mode == FLB200_POOL_MAX && d->dtype == FLB200_F32) {
+    const int band = pool_fwd_band_rows(g);
+    const long long nbands = band > 0 ? (g.Ho + band - 1) / band : 0;
+    if (band > 0 && g.planes * nbands < 0x7fffffffLL) {
+      const size_t smem = (size_t)((band - 1) * g.sy + g.wy) * g.W * sizeof(float);
+      const float* xf = static_cast<const float*>(x);
+      float* yf = static_cast<float*>(y);
+      if (is_window(g, 3, 3, 2, 2))
+        launch_pool_fwd_tile<3, 3, 2, 2>(xf, yf, argmax, g, band, (int)nbands, smem, st);
+      else if (is_window(g, 2, 2, 2, 2))
+        launch_pool_fwd_tile<2, 2, 2, 2>(xf, yf, argmax, g, band, (int)nbands, smem, st);
+      else
+        launch_pool_fwd_tile<0, 0, 0, 0>(xf, yf, argmax, g, band, (int)nbands, smem, st);
+      FLB200_AFTER_LAUNCH("pool2d_forward_max_tile");
+      return FLB200_OK;
+    }
+  }
   switch (d->dtype) {
     case FLB200_F32:
       pool_forward_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(x),
@@ -264,6 +462,22 @@ int flb200_pool2d_backward(const flb200_pool2d_desc* d, const void* grad_y, cons
   const int grid = grid_for(total, 256);
   cudaStream_t st = as_stream(stream);
   if (d->mode == FLB200_POOL_MAX && argmax && d->dtype == FLB200_F32) {
+    int out_rows = 0;
+    const int band = pool_bwd_band_rows(g, &out_rows);
+    const long long nbands = band > 0 ? (g.H + band - 1) / band : 0;
+    if (band > 0 && g.planes * nbands < 0x7fffffffLL) {
+      const size_t smem = (size_t)out_rows * g.Wo * 5 + 16;
+      const float* gyf = static_cast<const float*>(grad_y);
+      float* gxf = static_cast<float*>(grad_x);
+      if (is_window(g, 3, 3, 2, 2))
+        launch_pool_bwd_tile<3, 3, 2, 2>(gyf, argmax, gxf, g, band, (int)nbands, out_rows, smem, st);
+      else if (is_window(g, 2, 2, 2, 2))
+        launch_pool_bwd_tile<2, 2, 2, 2>(gyf, argmax, gxf, g, band, (int)nbands, out_rows, smem, st);
+      else
+        launch_pool_bwd_tile<0, 0, 0, 0>(gyf, argmax, gxf, g, band, (int)nbands, out_rows, smem, st);
+      FLB200_AFTER_LAUNCH("pool2d_backward_max_tile");
+      return FLB200_OK;
+    }
     const int strips = ((g.W + 3) / 4) * g.H;
     dim3 sgrid((unsigned)((strips + 255) / 256), (unsigned)(g.planes < 32768 ? g.planes : 32768));
     pool_backward_max_strip_kernel<float><<<sgrid, 256, 0, st>>>(
