@@ -304,3 +304,98 @@ def log_softmax_cross_entropy(x: Variable, targets: torch.Tensor, reduction=L.RE
         inputs[0].addGrad(F.log_softmax_cross_entropy_backward(y, gl, state))
 
     return Variable(loss, False, [x], grad_func)
+
+
+# ------------------------------------------------ pieces of the Transformer workload
+def glue(x: Variable, fwd, bwd) -> Variable:
+    """A data-movement step that has no kernel in this library (permutations between the
+    [rows, features] and [batch*heads, T, head] views, exp, the causal mask).  `fwd` maps the
+    tensor, `bwd` maps the output gradient back; both are torch calls and are named as glue
+    wherever a workload uses them."""
+    y = fwd(x.tensor)
+
+    def grad_func(inputs, gy):
+        inputs[0].addGrad(bwd(gy))
+
+    return Variable(y, False, [x], grad_func)
+
+
+def bmm(a: Variable, b: Variable, trans_b: bool = False) -> Variable:
+    """Batched matmul (Functions.cpp:827-946): a (Z, M, K); b (Z, K, N), or (Z, N, K) when
+    trans_b.  The three contractions of forward and backward are strided views of the same
+    buffers handed to flb200_matmul — no transposed copies."""
+    mode = extension().math_mode
+    at, bt = a.tensor.contiguous(), b.tensor.contiguous()
+    Z, M, K = at.shape
+    N = bt.shape[1] if trans_b else bt.shape[2]
+    bs = (1, K) if trans_b else (N, 1)           # strides of B viewed as (K, N)
+    b_elems = bt.shape[1] * bt.shape[2]
+    y = F.matmul(at, bt, m=M, n=N, k=K, a_strides=(K, 1), b_strides=bs, batch=Z,
+                 batch_strides=(M * K, b_elems, 0), math_mode=mode)
+
+    def grad_func(inputs, gy):
+        gy = gy.contiguous()
+        if inputs[0].isCalcGrad():
+            # dA (M, K) = dY (M, N) @ B^T (N, K)
+            bts = (K, 1) if trans_b else (1, N)  # strides of B viewed as (N, K)
+            ga = F.matmul(gy, bt, m=M, n=K, k=N, a_strides=(N, 1), b_strides=bts, batch=Z,
+                          batch_strides=(M * N, b_elems, 0), math_mode=mode)
+            inputs[0].addGrad(ga)
+        if inputs[1].isCalcGrad():
+            if trans_b:
+                # dB (N, K) = dY^T (N, M) @ A (M, K)
+                gb = F.matmul(gy, at, m=N, n=K, k=M, a_strides=(1, N), b_strides=(K, 1), batch=Z,
+                              batch_strides=(M * N, M * K, 0), math_mode=mode)
+            else:
+                # dB (K, N) = A^T (K, M) @ dY (M, N)
+                gb = F.matmul(at, gy, m=K, n=N, k=M, a_strides=(1, K), b_strides=(N, 1), batch=Z,
+                              batch_strides=(M * K, M * N, 0), math_mode=mode)
+            inputs[1].addGrad(gb)
+
+    return Variable(y, False, [a, b], grad_func)
+
+
+def softmax_rows(x: Variable) -> Variable:
+    """softmax over the last dimension as exp(logSoftmax(x)) (Functions.cpp:1021-1042): the
+    row reductions run in the logSoftmax kernels, exp and the product with the output are
+    torch glue.  dX = logSoftmaxBackward(l, dP * P)."""
+    l = F.log_softmax(x.tensor)
+    p = torch.exp(l)
+
+    def grad_func(inputs, gy):
+        inputs[0].addGrad(F.log_softmax_backward(l, gy * p))
+
+    return Variable(p, False, [x], grad_func)
+
+
+def affine_rows(x: Variable, w: Variable, b: Variable) -> Variable:
+    """y = x * tile(w) + tile(b) over rows of features: the affine part of fl::LayerNorm
+    (flashlight/fl/nn/modules/LayerNorm.cpp:99-110).  The products are torch glue; the two
+    parameter gradients are channel sums over the rows (channel_sum kernel)."""
+    xt, wt = x.tensor, w.tensor
+    y = torch.addcmul(b.tensor, xt, wt)
+
+    def grad_func(inputs, gy):
+        rows, feat = gy.numel() // gy.shape[-1], gy.shape[-1]
+        if inputs[0].isCalcGrad():
+            inputs[0].addGrad(gy * wt)
+        if inputs[1].isCalcGrad():
+            inputs[1].addGrad(F.channel_sum((gy * xt).contiguous(), rows, feat, 1).reshape(wt.shape))
+        if inputs[2].isCalcGrad():
+            inputs[2].addGrad(F.channel_sum(gy.contiguous(), rows, feat, 1).reshape(wt.shape))
+
+    return Variable(y, False, [x, w, b], grad_func)
+
+
+def embedding(table: Variable, ids: torch.Tensor) -> Variable:
+    """fl::embedding (Functions.cpp:1707-1749): rows of the table picked by token id; the
+    gradient is a scatter-add into the table.  Both are torch glue (index_select / index_add_)."""
+    flat = ids.reshape(-1).long()
+    y = table.tensor.index_select(0, flat)
+
+    def grad_func(inputs, gy):
+        g = torch.zeros_like(table.tensor)
+        g.index_add_(0, flat, gy)
+        inputs[0].addGrad(g)
+
+    return Variable(y, False, [table], grad_func)

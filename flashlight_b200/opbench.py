@@ -241,6 +241,50 @@ def suite_resnet50(batch, iters, math):
     bench_bias_grad((batch, 64, 112, 112), iters)
 
 
+def suite_workloads(iters, math, which):
+    """Forward + backward step time of the other synthetic workloads at their full sizes
+    (the ResNet-50 step is bench.py's job): MNIST convnet batch 64, conv-ASR 12 x 1024
+    channels T=1000 batch 16, 3-layer bidirectional LSTM H=1024 T=500 batch 32."""
+    from . import autograd as A
+    from . import workloads
+    A.set_math_mode(L.MATH_TF32 if math == "tf32" else L.MATH_STRICT_F32)
+    g = torch.Generator().manual_seed(1234)
+
+    def run(name, model, x, t, units, unit):
+        x, t = x.cuda(), t.cuda()
+
+        def step():
+            model.zeroGrad()
+            loss = model.loss(x, t)
+            loss.backward()
+            return loss
+
+        ms = time_op(step, iters, warmup=2)
+        print(json.dumps({"workload": name, "math": math, "ms_per_step": ms,
+                          "value": units / (ms * 1e-3), "unit": unit,
+                          "loss": float(step().tensor.cpu())}), flush=True)
+
+    if which in ("all", "mnist"):
+        run("mnist_convnet_b64", workloads.mnist_convnet(),
+            torch.randn(64, 1, 28, 28, generator=g),
+            torch.randint(0, 10, (64,), generator=g, dtype=torch.int32), 64, "images/s")
+    if which in ("all", "asr"):
+        B, T = 16, 1000
+        run("conv_asr_b16_t1000", workloads.ConvAsr(),
+            torch.randn(B, 80, 1, T, generator=g),
+            torch.randint(0, 30, (B * T,), generator=g, dtype=torch.int32), B * T, "frames/s")
+    if which in ("all", "transformer"):
+        B, T = 8, 512
+        run("transformer_lm_12x768_t512_b8", workloads.TransformerLM(),
+            torch.randint(0, 32000, (B, T), generator=g),
+            torch.randint(0, 32000, (B * T,), generator=g, dtype=torch.int32), B * T, "tokens/s")
+    if which in ("all", "bilstm"):
+        T, B = 500, 32
+        run("bilstm_h1024_t500_b32", workloads.BiLstm(),
+            torch.randn(T, B, 80, generator=g), torch.randn(T, B, 2048, generator=g), B,
+            "sequences/s")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--op")
@@ -257,6 +301,9 @@ def main():
     conv = tuple(int(v) for v in a.conv.split(","))
     if a.op == "cublas_tf32_peak":
         return measure_cublas_tf32()
+    if a.suite and a.suite.startswith("workloads"):
+        which = a.suite.split(":")[1] if ":" in a.suite else "all"
+        return suite_workloads(a.iters, a.math, which)
     if a.suite == "resnet50_step_convs":
         return suite_resnet50_step_convs(a.batch, a.math)
     if a.suite == "resnet50":

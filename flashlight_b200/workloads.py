@@ -184,3 +184,89 @@ def mse(y: Variable, target: torch.Tensor) -> Variable:
 
     loss = Variable(total / n, False, [y], grad_func)
     return loss
+
+
+class TransformerLM(nn.Module):
+    """Decoder-only language model of the fifth benchmark configuration: token embedding,
+    `layers` pre-LayerNorm blocks (x += attn(LN1(x)); x += mlp(LN2(x)), the block of
+    flashlight/pkg/vision/nn/VisionTransformer.cpp:169-170 with LayerNorm eps 1e-6 and affine),
+    multi-head attention with a causal additive mask and q scaled by 1/sqrt(head dim)
+    (flashlight/fl/contrib/modules/Transformer.cpp:112-119, Functions.cpp:1828-1891), mlp =
+    w2(gelu(w1 x)) with the tanh-form GELU (Functions.cpp:1791-1796), a final LayerNorm, an
+    untied output projection and full-softmax cross entropy.
+
+    Runs in fp32 / TF32: the contractions (q k v projections, scores, context, output and mlp
+    projections, vocabulary projection and all their gradients), LayerNorm statistics, GELU,
+    logSoftmax and the loss run on this library's kernels; head split / merge permutations,
+    exp, the LayerNorm affine products, the residual stream and the embedding gather /
+    scatter-add are torch glue (autograd.glue and friends)."""
+
+    def __init__(self, vocab=32000, d=768, heads=12, ffn=3072, layers=12, seed=1234, device="cuda"):
+        super().__init__()
+        gen = torch.Generator().manual_seed(seed)
+        self.d, self.heads, self.layers = d, heads, layers
+        mk = lambda i, o: nn.Linear(i, o, True, gen, device)
+        ones = lambda n: Variable(torch.ones(n, device=device), True)
+        zeros = lambda n: Variable(torch.zeros(n, device=device), True)
+        self.embed = Variable((torch.randn(vocab, d, generator=gen) * 0.02).to(device), True)
+        self.params = [self.embed]
+        self.blocks = []
+        for _ in range(layers):
+            blk = {"ln1": (ones(d), zeros(d)), "qkv": mk(d, 3 * d), "proj": mk(d, d),
+                   "ln2": (ones(d), zeros(d)), "w1": mk(d, ffn), "w2": mk(ffn, d)}
+            self.blocks.append(blk)
+            self.params += list(blk["ln1"]) + list(blk["ln2"])
+            self.children += [blk["qkv"], blk["proj"], blk["w1"], blk["w2"]]
+        self.ln_f = (ones(d), zeros(d))
+        self.params += list(self.ln_f)
+        self.head = mk(d, vocab)
+        self.children.append(self.head)
+        self.norm = nn.LayerNorm([0], 2, eps=1e-6)
+
+    def parameters(self):
+        """embedding; per block ln1 w, b, qkv w, b, proj w, b, ln2 w, b, w1 w, b, w2 w, b;
+        final LayerNorm w, b; head w, b."""
+        out = [self.embed]
+        for blk in self.blocks:
+            out += list(blk["ln1"]) + blk["qkv"].parameters() + blk["proj"].parameters()
+            out += list(blk["ln2"]) + blk["w1"].parameters() + blk["w2"].parameters()
+        return out + list(self.ln_f) + self.head.parameters()
+
+    def _ln(self, x, wb):
+        return A.affine_rows(self.norm(x), wb[0], wb[1])
+
+    def _attention(self, x, blk, B, T, mask):
+        d, h = self.d, self.heads
+        hd = d // h
+        qkv = blk["qkv"](x)  # (B*T, 3d)
+
+        def split(i, scale):
+            fwd = lambda t: (t.reshape(B, T, 3, h, hd)[:, :, i].permute(0, 2, 1, 3) * scale) \
+                .reshape(B * h, T, hd).contiguous()
+
+            def bwd(g):
+                full = torch.zeros(B, T, 3, h, hd, device=g.device, dtype=g.dtype)
+                full[:, :, i] = (g.reshape(B, h, T, hd) * scale).permute(0, 2, 1, 3)
+                return full.reshape(B * T, 3 * d)
+
+            return A.glue(qkv, fwd, bwd)
+
+        q, k, v = split(0, 1.0 / math.sqrt(hd)), split(1, 1.0), split(2, 1.0)
+        scores = A.bmm(q, k, trans_b=True)                        # (B*h, T, T)
+        scores = A.glue(scores, lambda t: t + mask, lambda g: g)  # causal additive mask
+        ctx = A.bmm(A.softmax_rows(scores), v)                    # (B*h, T, hd)
+        merged = A.glue(
+            ctx, lambda t: t.reshape(B, h, T, hd).permute(0, 2, 1, 3).reshape(B * T, d).contiguous(),
+            lambda g: g.reshape(B, T, h, hd).permute(0, 2, 1, 3).reshape(B * h, T, hd).contiguous())
+        return blk["proj"](merged)
+
+    def loss(self, ids: torch.Tensor, targets: torch.Tensor) -> Variable:
+        """ids (B, T) token ids; targets (B*T,) next-token labels."""
+        B, T = ids.shape
+        x = A.embedding(self.embed, ids)  # (B*T, d)
+        mask = torch.full((T, T), float("-inf"), device=x.tensor.device).triu(1)
+        for blk in self.blocks:
+            x = A.add(x, self._attention(self._ln(x, blk["ln1"]), blk, B, T, mask))
+            x = A.add(x, blk["w2"](A.gelu(blk["w1"](self._ln(x, blk["ln2"])))))
+        scores = self.head(self._ln(x, self.ln_f))
+        return A.log_softmax_cross_entropy(scores, targets)

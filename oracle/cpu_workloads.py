@@ -119,3 +119,42 @@ def bilstm_loss(params, x, target, hidden, layers):
 
 def bilstm_step(params, x, target, hidden, layers):
     return _step(lambda ps, a, b: bilstm_loss(ps, a, b, hidden, layers), params, x, target)
+
+
+def transformer_lm_loss(params, ids, targets, heads, layers, eps=1e-6):
+    """Pre-LayerNorm decoder (flashlight/pkg/vision/nn/VisionTransformer.cpp:169-170 block,
+    causal additive mask as flashlight/fl/contrib/modules/Transformer.cpp:112-119, q scaled by
+    1/sqrt(head dim), tanh-form GELU).  params in the order of
+    flashlight_b200.workloads.TransformerLM.parameters(); Linear weights are (in, out)."""
+    it = iter(params)
+    embed = next(it)
+    B, T = ids.shape
+    d = embed.shape[1]
+    hd = d // heads
+    x = embed[ids.reshape(-1).long()]
+    mask = torch.full((T, T), float("-inf"), dtype=x.dtype).triu(1)
+
+    def ln(h):
+        w, b = next(it), next(it)
+        return F.layer_norm(h, (d,), w, b, eps)
+
+    def lin(h):
+        w, b = next(it), next(it)
+        return h @ w + b
+
+    for _ in range(layers):
+        qkv = lin(ln(x)).reshape(B, T, 3, heads, hd)
+        q = qkv[:, :, 0].permute(0, 2, 1, 3) / hd ** 0.5
+        k = qkv[:, :, 1].permute(0, 2, 1, 3)
+        v = qkv[:, :, 2].permute(0, 2, 1, 3)
+        p = torch.softmax(q @ k.transpose(-1, -2) + mask, -1)
+        ctx = (p @ v).permute(0, 2, 1, 3).reshape(B * T, d)
+        x = x + lin(ctx)
+        h = lin(ln(x))
+        x = x + lin(F.gelu(h, approximate="tanh"))
+    scores = lin(ln(x))
+    return F.nll_loss(F.log_softmax(scores, -1), targets.long())
+
+
+def transformer_lm_step(params, ids, targets, heads, layers):
+    return _step(lambda ps, a, b: transformer_lm_loss(ps, a, b, heads, layers), params, ids, targets)

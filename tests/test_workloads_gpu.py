@@ -110,3 +110,16 @@ def test_bilstm_step(L, mode):
     want_loss, want_grads = CW.bilstm_step(host_params(model), x.double(), target.double(), hidden,
                                            layers)
     check_step(model, loss, want_loss, want_grads, mode)
+
+
+def test_transformer_lm_step(L, mode):
+    from flashlight_b200 import workloads
+    model = workloads.TransformerLM(vocab=97, d=64, heads=4, ffn=128, layers=2, seed=23)
+    g = torch.Generator().manual_seed(29)
+    B, T = 3, 24
+    ids = torch.randint(0, 97, (B, T), generator=g)
+    t = torch.randint(0, 97, (B * T,), generator=g, dtype=torch.int32)
+    loss = model.loss(ids.cuda(), t.cuda())
+    loss.backward()
+    want_loss, want_grads = CW.transformer_lm_step(host_params(model), ids, t, heads=4, layers=2)
+    check_step(model, loss, want_loss, want_grads, mode)
