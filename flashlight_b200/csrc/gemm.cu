@@ -32,7 +32,8 @@ int matmul_simt(const flb200_matmul_desc* d, const void* a, const void* b, void*
 int check_desc(const flb200_matmul_desc* d, const void* a, const void* b, const void* c) {
   FLB200_REQUIRE(d, "matmul: null descriptor");
   FLB200_REQUIRE(d->m >= 0 && d->n >= 0 && d->k >= 0 && d->batch >= 1, "matmul: negative extent");
-  FLB200_REQUIRE(d->dtype == FLB200_F32, "matmul: only f32 is built (dtype %d)", d->dtype);
+  FLB200_REQUIRE(d->dtype == FLB200_F32 || d->dtype == FLB200_BF16,
+                 "matmul: f32 and bf16 are built (dtype %d)", d->dtype);
   FLB200_REQUIRE(d->math_mode == FLB200_MATH_STRICT_F32 || d->math_mode == FLB200_MATH_TF32,
                  "matmul: unknown math mode %d", d->math_mode);
   FLB200_REQUIRE((a && b && c) || d->m == 0 || d->n == 0, "matmul: null matrix");
@@ -44,6 +45,15 @@ int run_matmul(const flb200_matmul_desc* d, const void* a, const void* b, void* 
   if (int st = check_desc(d, a, b, c)) return st;
   if (d->m == 0 || d->n == 0) return FLB200_OK;
   cudaStream_t st = as_stream(stream);
+  if (d->dtype == FLB200_BF16) {
+    // bf16 operands, fp32 accumulation, bf16 result: tensor cores only (no fp32-FMA kernel
+    // reads bf16), whatever the math mode says
+    if (!tc_gemm_supported(d, a, b, c))
+      return fail(FLB200_UNSUPPORTED,
+                  "matmul: bf16 needs the tensor-core path (sm_100, 16-byte aligned operands "
+                  "with one unit stride each)");
+    return tc_gemm_run(d, a, b, c, ws, ws_bytes, st);
+  }
   if (d->math_mode == FLB200_MATH_TF32 && tc_gemm_supported(d, a, b, c))
     return tc_gemm_run(d, a, b, c, ws, ws_bytes, st);
   return matmul_simt(d, a, b, c, ws, ws_bytes, st);

@@ -2,6 +2,8 @@
 // TMA tensor maps + operand plans, picks the tile width and the split-K factor,
 // and launches tc_gemm_kernel (tc_core.cuh).  Used by flb200_matmul / the linear
 // gradients in TF32 mode, by the convolution paths in tc_conv.cu and by rnn.cu.
+#include <cuda_bf16.h>
+
 #include "tc_gemm.cuh"
 
 #include <cstdlib>
@@ -38,7 +40,7 @@ static EncodeTiledFn encode_tiled_fn() {
 // 128-byte swizzle of 16-byte chunks, MN-major ones the swizzle of 32-byte chunks.
 int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                     const uint64_t* strides_bytes, const uint32_t* box, int mode,
-                    const uint32_t* elem_strides) {
+                    const uint32_t* elem_strides, bool bf16) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return fail(FLB200_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
   cuuint64_t gd[5];
@@ -50,7 +52,8 @@ int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t
     es[i] = elem_strides ? elem_strides[i] : 1;
     if (i > 0) gs[i - 1] = strides_bytes[i - 1];
   }
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, (cuuint32_t)rank, const_cast<void*>(base),
+  CUresult r = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                  (cuuint32_t)rank, const_cast<void*>(base),
                   gd, gs, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   mode == kMapStaging ? CU_TENSOR_MAP_SWIZZLE_NONE
                                       : (mode == kMapMnMajor ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
@@ -99,11 +102,18 @@ tc_splitk_reduce_kernel(const float* __restrict__ partial, EpiloguePlan ep, int 
     if (ep.m_valid != 0 && ep.m_div != 0 && (m % ep.m_div) >= ep.m_valid) continue;
     float s = 0.f;
     for (int sp = 0; sp < splits; ++sp) s += partial[((long long)z * splits + sp) * mn + r];
-    float* dst = ep.out + epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) +
-                 epi_off(n, ep.n_div, ep.n_stride, ep.n_outer) + (long long)z * ep.z_stride;
+    const long long off = epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) +
+                          epi_off(n, ep.n_div, ep.n_stride, ep.n_outer) + (long long)z * ep.z_stride;
     float v = ep.alpha * s + (ep.bias_m ? ep.bias_m[m] : 0.f) + (ep.bias_n ? ep.bias_n[n] : 0.f);
-    if (ep.beta != 0.f) v += ep.beta * *dst;
-    *dst = v;
+    if (ep.out_bf16) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ep.out) + off;
+      if (ep.beta != 0.f) v += ep.beta * __bfloat162float(*dst);
+      *dst = __float2bfloat16(v);
+    } else {
+      float* dst = ep.out + off;
+      if (ep.beta != 0.f) v += ep.beta * *dst;
+      *dst = v;
+    }
   }
 }
 
@@ -111,8 +121,9 @@ template <int BN>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa,
                        const OperandPlan& pb, const EpiloguePlan& ep, long long M, long long N,
                        long long k_iters, long long Z, const Launch& L, float* partial,
-                       cudaStream_t st) {
+                       cudaStream_t st, bool bf16) {
   GemmProblem<BN> p;
+  p.bf16 = bf16 ? 1 : 0;
   p.a = make_coords(pa); p.b = make_coords(pb); p.ep = ep;
   p.a_mn_major = pa.mn_major; p.b_mn_major = pb.mn_major;
   p.M = (int)M; p.N = (int)N; p.k_iters = (int)k_iters;
@@ -124,7 +135,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const Opera
   const long long tiles = (long long)p.tiles_m * p.tiles_n * Z * L.splits;
   FLB200_REQUIRE(tiles < 0x7fffffffLL, "tc_gemm: too many tiles");
   if constexpr (BN >= 128) {
-    if (gemm_uses_pairs(M, N, k_iters, pa.mn_major != 0, pb.mn_major != 0)) {
+    if (!bf16 && gemm_uses_pairs(M, N, k_iters, pa.mn_major != 0, pb.mn_major != 0)) {
       const long long pair_tiles = (long long)((p.tiles_m + 1) / 2) * p.tiles_n * Z * L.splits;
       return launch_pair_problem<GemmProblem<BN>, BN>("tc_gemm_pair", ma, mb, p, pair_tiles, st);
     }
@@ -191,7 +202,7 @@ Launch plan_launch(long long M, long long N, long long k_iters, long long Z) {
 
 int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, const OperandPlan& pb,
         const EpiloguePlan& ep, long long M, long long N, long long k_iters, long long Z, void* ws,
-        size_t ws_bytes, cudaStream_t st) {
+        size_t ws_bytes, cudaStream_t st, bool bf16) {
   Launch L = plan_launch(M, N, k_iters, Z);
   if (L.splits > 1 && (!ws || ws_bytes < L.workspace_bytes)) {
     L.splits = 1;
@@ -199,10 +210,10 @@ int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, con
   }
   float* partial = static_cast<float*>(ws);
   int rc;
-  if (L.bn == 32) rc = launch_gemm<32>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
-  else if (L.bn == 64) rc = launch_gemm<64>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
-  else if (L.bn == 128) rc = launch_gemm<128>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
-  else rc = launch_gemm<256>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st);
+  if (L.bn == 32) rc = launch_gemm<32>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st, bf16);
+  else if (L.bn == 64) rc = launch_gemm<64>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st, bf16);
+  else if (L.bn == 128) rc = launch_gemm<128>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st, bf16);
+  else rc = launch_gemm<256>(ma, mb, pa, pb, ep, M, N, k_iters, Z, L, partial, st, bf16);
   if (rc) return rc;
   if (L.splits > 1) {
     const int rgrid = grid_for(M * N * Z, 256);
@@ -223,12 +234,14 @@ struct Side {
 };
 
 // op(r, k) at base[r*row + k*col]: decide the major and the leading dimension.
-Side classify(long long row, long long col, long long rows, long long K) {
+// `vec` = elements per 16 bytes (4 for fp32, 8 for bf16): leading dimensions must keep every
+// row 16-byte aligned.
+Side classify(long long row, long long col, long long rows, long long K, long long vec) {
   Side s{false, false, 0};
-  if (col == 1 && (row % 4 == 0 || rows == 1) && row >= 1) {
-    s = Side{true, false, rows == 1 ? (K + 3) / 4 * 4 : row};
-  } else if (row == 1 && (col % 4 == 0 || K == 1) && col >= 1) {
-    s = Side{true, true, K == 1 ? (rows + 3) / 4 * 4 : col};
+  if (col == 1 && (row % vec == 0 || rows == 1) && row >= 1) {
+    s = Side{true, false, rows == 1 ? (K + vec - 1) / vec * vec : row};
+  } else if (row == 1 && (col % vec == 0 || K == 1) && col >= 1) {
+    s = Side{true, true, K == 1 ? (rows + vec - 1) / vec * vec : col};
   }
   return s;
 }
@@ -241,14 +254,17 @@ struct Prepared {
 
 Prepared prepare(const flb200_matmul_desc* d, const void* a, const void* b, const void* c) {
   Prepared p;
-  if (d->dtype != FLB200_F32 || d->m < 1 || d->n < 1 || d->k < 1) return p;
+  const bool bf16 = d->dtype == FLB200_BF16;
+  if ((d->dtype != FLB200_F32 && !bf16) || d->m < 1 || d->n < 1 || d->k < 1) return p;
+  const long long vec = bf16 ? 8 : 4;
   if (!aligned16(a) || !aligned16(b) || !c) return p;
-  if (d->batch > 1 && (d->a_batch % 4 != 0 || d->b_batch % 4 != 0)) return p;
-  // too little work to pay for a tensor-core launch: leave it to the fp32 kernel
-  if ((double)d->m * (double)d->n * (double)d->k < 262144.0) return p;
-  p.a = classify(d->a_row, d->a_col, d->m, d->k);
+  if (d->batch > 1 && (d->a_batch % vec != 0 || d->b_batch % vec != 0)) return p;
+  // too little work to pay for a tensor-core launch: leave it to the fp32 kernel (bf16 has
+  // no other kernel and always comes here)
+  if (!bf16 && (double)d->m * (double)d->n * (double)d->k < 262144.0) return p;
+  p.a = classify(d->a_row, d->a_col, d->m, d->k, vec);
   // B(k, n): "row" of the operand is n with stride b_col; k stride is b_row
-  p.b = classify(d->b_col, d->b_row, d->n, d->k);
+  p.b = classify(d->b_col, d->b_row, d->n, d->k, vec);
   if (!p.a.ok || !p.b.ok) return p;
   p.swap = d->m < 64 && d->n > d->m;  // put the long extent on the 128-row side of the MMA
   p.ok = true;
@@ -257,7 +273,10 @@ Prepared prepare(const flb200_matmul_desc* d, const void* a, const void* b, cons
 
 // Tensor map + plan of one operand: rows x K matrix (+ batch).
 int build_operand(const Side& s, const void* base, long long rows, long long K, long long batch,
-                  long long batch_stride, int tile_rows, CUtensorMap* map, tc::OperandPlan* plan) {
+                  long long batch_stride, int tile_rows, CUtensorMap* map, tc::OperandPlan* plan,
+                  bool bf16) {
+  const uint32_t kstage = bf16 ? 64 : tc::kBK;   // elements of K per stage (128 bytes)
+  const uint64_t esize = bf16 ? 2 : 4;
   uint64_t dims[3], strides[2];
   uint32_t box[3];
   *plan = tc::OperandPlan{};
@@ -265,26 +284,29 @@ int build_operand(const Side& s, const void* base, long long rows, long long K, 
   plan->k2_dim = -1;
   if (s.mn_major) {
     dims[0] = (uint64_t)rows; dims[1] = (uint64_t)K;
-    box[0] = 32; box[1] = tc::kBK;
+    box[0] = bf16 ? 64 : 32; box[1] = kstage;
     plan->mn_major = 1; plan->mn_dim = 0; plan->k_dim = 1;
   } else {
     dims[0] = (uint64_t)K; dims[1] = (uint64_t)rows;
-    box[0] = tc::kBK; box[1] = (uint32_t)tile_rows;
+    box[0] = kstage; box[1] = (uint32_t)tile_rows;
     plan->mn_major = 0; plan->mn_dim = 1; plan->k_dim = 0;
   }
-  strides[0] = (uint64_t)s.ld * 4;
+  plan->k_elems = (int)kstage;
+  strides[0] = (uint64_t)s.ld * esize;
   int rank = 2;
   plan->z_dim = -1;
   if (batch > 1) {
     dims[2] = (uint64_t)batch;
-    strides[1] = (uint64_t)batch_stride * 4;
+    strides[1] = (uint64_t)batch_stride * esize;
     box[2] = 1;
     rank = 3;
     plan->z_dim = 2;
   }
   plan->rank = rank;
+  // bf16 tiles use the plain 128-byte swizzle for both majors
   return tc::make_tensor_map(map, base, rank, dims, strides, box,
-                             s.mn_major ? tc::kMapMnMajor : tc::kMapKMajor);
+                             s.mn_major && !bf16 ? tc::kMapMnMajor : tc::kMapKMajor, nullptr,
+                             bf16);
 }
 
 }  // namespace
@@ -297,7 +319,8 @@ bool tc_gemm_supported(const flb200_matmul_desc* d, const void* a, const void* b
 
 size_t tc_gemm_workspace_bytes(const flb200_matmul_desc* d) {
   if (!d || d->m < 1 || d->n < 1 || d->k < 1) return 0;
-  const long long k_iters = (d->k + tc::kBK - 1) / tc::kBK;
+  const long long kstage = d->dtype == FLB200_BF16 ? 64 : tc::kBK;
+  const long long k_iters = (d->k + kstage - 1) / kstage;
   // the swapped orientation has the same M*N; take the larger split count of both
   const size_t w1 = tc::plan_launch(d->m, d->n, k_iters, d->batch).workspace_bytes;
   const size_t w2 = tc::plan_launch(d->n, d->m, k_iters, d->batch).workspace_bytes;
@@ -308,11 +331,14 @@ int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void*
                 size_t ws_bytes, cudaStream_t st) {
   const Prepared p = prepare(d, a, b, c);
   if (!p.ok) return fail(FLB200_UNSUPPORTED, "tc_gemm: layout not covered");
-  const long long k_iters = (d->k + tc::kBK - 1) / tc::kBK;
+  const bool bf16 = d->dtype == FLB200_BF16;
+  const long long kstage = bf16 ? 64 : tc::kBK;
+  const long long k_iters = (d->k + kstage - 1) / kstage;
   CUtensorMap ma, mb;
   tc::OperandPlan pa, pb;
   tc::EpiloguePlan ep{};
   ep.out = static_cast<float*>(c);
+  ep.out_bf16 = bf16 ? 1 : 0;
   ep.alpha = d->alpha;
   ep.beta = d->beta;
   ep.z_stride = d->c_batch;
@@ -320,22 +346,24 @@ int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void*
   if (!p.swap) {
     M = d->m; N = d->n;
     const int bn = tc::pick_bn(N);
-    if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch, tc::kBM, &ma, &pa)) return rc;
+    if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch, tc::kBM, &ma, &pa, bf16)) return rc;
     if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch,
-                               tc::b_box_rows(M, N, k_iters, p.a.mn_major, p.b.mn_major), &mb, &pb)) return rc;
+                               bf16 ? bn : tc::b_box_rows(M, N, k_iters, p.a.mn_major, p.b.mn_major), &mb,
+                               &pb, bf16)) return rc;
     ep.m_stride = d->c_row;
     ep.n_stride = d->c_col;
   } else {
     // C^T = B^T A^T: the kernel's rows are the caller's columns
     M = d->n; N = d->m;
     const int bn = tc::pick_bn(N);
-    if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch, tc::kBM, &ma, &pa)) return rc;
+    if (int rc = build_operand(p.b, b, d->n, d->k, d->batch, d->b_batch, tc::kBM, &ma, &pa, bf16)) return rc;
     if (int rc = build_operand(p.a, a, d->m, d->k, d->batch, d->a_batch,
-                               tc::b_box_rows(M, N, k_iters, p.b.mn_major, p.a.mn_major), &mb, &pb)) return rc;
+                               bf16 ? bn : tc::b_box_rows(M, N, k_iters, p.b.mn_major, p.a.mn_major), &mb,
+                               &pb, bf16)) return rc;
     ep.m_stride = d->c_col;
     ep.n_stride = d->c_row;
   }
-  return tc::run(ma, mb, pa, pb, ep, M, N, k_iters, d->batch, ws, ws_bytes, st);
+  return tc::run(ma, mb, pa, pb, ep, M, N, k_iters, d->batch, ws, ws_bytes, st, bf16);
 }
 
 }  // namespace flb200

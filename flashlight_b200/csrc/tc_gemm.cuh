@@ -31,6 +31,7 @@ struct OperandPlan {
   int k_inner;   // stage iterations per k2 step (ceil(extent of k_dim / kBK)); 0 = single level
   int k2_scale;  // coordinate step per k_hi
   int base[4];
+  int k_elems;   // elements per stage along K: 0 = kBK (fp32), 64 for 2-byte operands
 };
 
 // The same plan flattened for the device: per-dimension multipliers of the tile offset, the
@@ -45,7 +46,7 @@ inline OperandCoords make_coords(const OperandPlan& p) {
   for (int d = 0; d < 4; ++d) {
     c.base[d] = p.base[d];
     c.mn_mul[d] = d == p.mn_dim ? 1 : 0;
-    c.k_mul[d] = d == p.k_dim ? kBK : 0;
+    c.k_mul[d] = d == p.k_dim ? (p.k_elems ? p.k_elems : kBK) : 0;
     c.k2_mul[d] = d == p.k2_dim ? p.k2_scale : 0;
     c.z_mul[d] = d == p.z_dim ? 1 : 0;
   }
@@ -61,6 +62,7 @@ struct EpiloguePlan {
   const float* bias_m;  // added per row (may be null)
   const float* bias_n;  // added per column (may be null)
   float alpha, beta;
+  int out_bf16;         // `out` points at __nv_bfloat16 (offsets are in elements either way)
 };
 
 struct Launch {
@@ -92,7 +94,7 @@ void plan_splits(long long tiles, long long k_iters, long long min_ips, int* spl
 enum { kMapKMajor = 0, kMapMnMajor = 1, kMapStaging = 2 };
 int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                     const uint64_t* strides_bytes, const uint32_t* box, int mode,
-                    const uint32_t* elem_strides = nullptr);
+                    const uint32_t* elem_strides = nullptr, bool bf16 = false);
 
 // Address of the device flag that bounded waits raise (per device), and the launch counter.
 int* status_ptr();
@@ -102,7 +104,7 @@ void count_tc_launch();
 // enough scratch the contraction runs unsplit.
 int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, const OperandPlan& pb,
         const EpiloguePlan& ep, long long M, long long N, long long k_iters, long long Z, void* ws,
-        size_t ws_bytes, cudaStream_t st);
+        size_t ws_bytes, cudaStream_t st, bool bf16 = false);
 
 }  // namespace tc
 }  // namespace flb200

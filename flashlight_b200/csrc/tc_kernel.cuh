@@ -34,6 +34,8 @@
 //   __device__ bool chunk_live(const Tile&, int c0) const;                // warp-uniform
 //   __device__ void store(const Tile&, int row, int c0, const float* v) const;  // 32 columns
 #pragma once
+#include <cuda_bf16.h>
+
 #include "tc_core.cuh"
 
 namespace flb200 {
@@ -143,7 +145,15 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc_tf32(BN, prob.a_mn_major, prob.b_mn_major);
+      bool bf16 = false;
+      if constexpr (P::kBf16Capable) bf16 = prob.bf16 != 0;
+      const uint32_t idesc = bf16 ? umma_idesc_bf16(BN, prob.a_mn_major, prob.b_mn_major)
+                                  : umma_idesc_tf32(BN, prob.a_mn_major, prob.b_mn_major);
+      // MN-major tiles: fp32 in 32 x 32 boxes with the 32-byte-chunk swizzle (4 KB apart, k
+      // atoms 512 B apart, 8 k-rows = 1 KB per MMA); bf16 in 64 x 64 boxes with the plain
+      // 128-byte swizzle (8 KB apart, k atoms 1 KB apart, 16 k-rows = 2 KB per MMA)
+      const uint32_t mn_lbo = bf16 ? 8192 : kBK * 128, mn_sbo = bf16 ? 1024 : 512;
+      const uint32_t mn_step = bf16 ? 2048 : 1024, mn_layout = bf16 ? 2 : 1;
       uint32_t s = 0, round = 0, nt = 0;
       typename P::Tile t;
       for (int tile = blockIdx.x; tile < n_tiles && *failed == 0; tile += gridDim.x, ++nt) {
@@ -169,12 +179,13 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             // K-major: step 8 elements = 32 bytes inside the swizzled row;
             // MN-major: step 8 k-rows = 1024 bytes inside each box.
             const uint64_t ad = prob.a_mn_major
-                                    ? umma_desc(a_addr + j * 1024, kBK * 128, 512, 1)
+                                    ? umma_desc(a_addr + j * mn_step, mn_lbo, mn_sbo, mn_layout)
                                     : umma_desc(a_addr + j * 32, 16, 1024, 2);
             const uint64_t bd = prob.b_mn_major
-                                    ? umma_desc(b_addr + j * 1024, kBK * 128, 512, 1)
+                                    ? umma_desc(b_addr + j * mn_step, mn_lbo, mn_sbo, mn_layout)
                                     : umma_desc(b_addr + j * 32, 16, 1024, 2);
-            umma_tf32(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
+            if (bf16) umma_bf16(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
+            else umma_tf32(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
           }
           umma_commit(&empty_bar[s]);  // frees the stage once these MMAs have read it
           if (++s == STAGES) { s = 0; ++round; }
@@ -226,6 +237,8 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 template <int BN>
 struct GemmProblem {
   static constexpr bool kWarpProducer = true;
+  static constexpr bool kBf16Capable = true;
+  int bf16;  // operands are bf16 (64 elements per stage), else fp32 read as TF32
   OperandCoords a, b;
   EpiloguePlan ep;
   int a_mn_major, b_mn_major;
@@ -261,16 +274,17 @@ struct GemmProblem {
     __syncwarp();
     // a K-major operand is one box, an MN-major one a box per 32 rows: lanes [0, na) take A,
     // lanes [na, na + nb) take B
-    const int na = a_mn_major ? kBM / 32 : 1, nb = b_mn_major ? BN / 32 : 1;
+    const int box_mn = bf16 ? 64 : 32, box_bytes = bf16 ? 8192 : kBK * 128;
+    const int na = a_mn_major ? kBM / box_mn : 1, nb = b_mn_major ? BN / box_mn : 1;
     if (lane < na) {
       int c[4];
-      operand_coords(a, t.m0 + 32 * lane, ls.a_lo, ls.a_hi, t.z, c);
-      tma_load(ma, bar, a_dst + lane * (kBK * 128), a.rank, c);
+      operand_coords(a, t.m0 + box_mn * lane, ls.a_lo, ls.a_hi, t.z, c);
+      tma_load(ma, bar, a_dst + lane * box_bytes, a.rank, c);
     } else if (lane < na + nb) {
       const int j = lane - na;
       int c[4];
-      operand_coords(b, t.n0 + 32 * j, ls.b_lo, ls.b_hi, t.z, c);
-      tma_load(mb, bar, b_dst + j * (kBK * 128), b.rank, c);
+      operand_coords(b, t.n0 + box_mn * j, ls.b_lo, ls.b_hi, t.z, c);
+      tma_load(mb, bar, b_dst + j * box_bytes, b.rank, c);
     }
     if (++ls.a_lo == a.k_inner) { ls.a_lo = 0; ++ls.a_hi; }
     if (++ls.b_lo == b.k_inner) { ls.b_lo = 0; ++ls.b_hi; }
@@ -335,6 +349,35 @@ struct GemmProblem {
     const long long m_off =
         epi_off(m, ep.m_div, ep.m_stride, ep.m_outer) + (long long)t.z * ep.z_stride;
     const float bm = ep.bias_m ? ep.bias_m[m] : 0.f;
+    if (ep.out_bf16) {
+      __nv_bfloat16* outb = reinterpret_cast<__nv_bfloat16*>(ep.out);
+      if (ep.beta == 0.f && ep.n_div == 0 && ep.n_stride == 1 && nb + 32 <= N &&
+          ep.bias_n == nullptr && ((m_off + nb) & 7) == 0 &&
+          (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) {
+        uint4* dst = reinterpret_cast<uint4*>(outb + m_off + nb);
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          __nv_bfloat162 h[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            h[q] = __floats2bfloat162_rn(ep.alpha * v[j + 2 * q] + bm,
+                                         ep.alpha * v[j + 2 * q + 1] + bm);
+          dst[j >> 3] = *reinterpret_cast<uint4*>(h);
+        }
+        return;
+      }
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int n = nb + j;
+        if (n < N) {
+          __nv_bfloat16* dst = outb + m_off + epi_off(n, ep.n_div, ep.n_stride, ep.n_outer);
+          float r = ep.alpha * v[j] + bm + (ep.bias_n ? ep.bias_n[n] : 0.f);
+          if (ep.beta != 0.f) r += ep.beta * __bfloat162float(*dst);
+          *dst = __float2bfloat16(r);
+        }
+      }
+      return;
+    }
     const bool simple = ep.beta == 0.f && ep.n_div == 0;
     if (simple && nb + 32 <= N && ep.bias_n != nullptr) {
       // strided columns with a per-column bias (convolution output planes)

@@ -42,6 +42,7 @@ struct TapGrid {
 template <int BN>
 struct PatchConvProblem {
   static constexpr bool kWarpProducer = false;
+  static constexpr bool kBf16Capable = false;
   int a_mn_major, b_mn_major;  // 0, 0
   // patch geometry (all powers of two, NB * PH * QW == 128)
   int QW, PH, NB, qw_shift, ph_shift;
@@ -189,6 +190,7 @@ struct PatchConvProblem {
 template <int BN>
 struct PatchWgradProblem {
   static constexpr bool kWarpProducer = true;
+  static constexpr bool kBf16Capable = false;
   int a_mn_major, b_mn_major;  // 1, 1
   int QW, PH;                  // 32-pixel patch: QW * PH == 32
   int tiles_q, tiles_p, images;

@@ -155,7 +155,7 @@ def matmul(a, b, c=None, *, m, n, k, a_strides, b_strides, c_strides=None, batch
         batch_strides = (batch_strides[0], batch_strides[1], m * n)
     d = L.MatmulDesc(m, n, k, batch, a_strides[0], a_strides[1], batch_strides[0], b_strides[0],
                      b_strides[1], batch_strides[1], c_strides[0], c_strides[1], batch_strides[2],
-                     alpha, beta, L.F32, mode)
+                     alpha, beta, dtype_code(a), mode)
     nbytes = L.lib.flb200_matmul_workspace_bytes(C.byref(d))
     ws = workspace(nbytes, a)
     L.check(L.lib.flb200_matmul(C.byref(d), ptr(a), ptr(b), ptr(c), ptr(ws), nbytes, stream_handle()))

@@ -222,7 +222,8 @@ typedef struct flb200_matmul_desc {
   int64_t b_row, b_col, b_batch; /* B(kk,j) at b[kk*b_row + j*b_col + b*b_batch] */
   int64_t c_row, c_col, c_batch;
   float alpha, beta;
-  int32_t dtype;      /* FLB200_F32 */
+  int32_t dtype;      /* FLB200_F32, or FLB200_BF16: bf16 A, B and C, fp32 accumulation on the
+                       * tensor cores (needs 16-byte aligned operands with one unit stride each) */
   int32_t math_mode;  /* FLB200_MATH_* */
 } flb200_matmul_desc;
 

@@ -249,3 +249,38 @@ def test_conv2d_layout_cache(L, case):
     gw4, _ = cached.conv2dBackwardFilterBias(gy3, x, w, None, *args, None, None, payload)
     want4, _ = plain.conv2dBackwardFilterBias(gy3, x, w, None, *args)
     assert torch.equal(gw4, want4)
+
+
+# ------------------------------------------------------------- bf16 contraction
+BF16_CASES = [
+    # m, n, k, batch, a transposed (m contiguous), b transposed (n contiguous)
+    (256, 128, 512, 1, False, False),
+    (200, 72, 136, 1, False, False),     # ragged tiles, K not a multiple of the 64-element stage
+    (256, 256, 64, 1, True, False),      # A with the m index contiguous
+    (192, 320, 256, 1, False, True),     # B with the n index contiguous
+    (128, 128, 4096, 1, True, True),     # both, long K (split-K)
+    (96, 64, 128, 6, False, True),       # batched (attention-sized)
+    (24, 512, 768, 1, False, False),     # few rows: operands swap sides
+]
+
+
+@pytest.mark.parametrize("case", BF16_CASES)
+def test_matmul_bf16(L, case):
+    """bf16 operands and result, fp32 accumulation in tensor memory.  Bound: 1e-2 of the result's
+    largest magnitude (the result is rounded to 8 mantissa bits; inputs are exact in bf16)."""
+    from flashlight_b200 import functions as F
+    m, n, k, batch, ta, tb = case
+    a = randn(batch, k, m, seed=41) if ta else randn(batch, m, k, seed=41)
+    b = randn(batch, n, k, seed=42) if not tb else randn(batch, k, n, seed=42)
+    ab, bb = a.to(torch.bfloat16), b.to(torch.bfloat16)
+    A64 = (ab.double().transpose(1, 2) if ta else ab.double())
+    B64 = (bb.double().transpose(1, 2) if not tb else bb.double())
+    want = A64 @ B64
+    a_str = (1, m) if ta else (k, 1)
+    b_str = (n, 1) if tb else (1, k)      # strides of B viewed as (k, n)
+    before = L.lib.flb200_tc_kernel_launches()
+    got = F.matmul(ab.cuda(), bb.cuda(), m=m, n=n, k=k, a_strides=a_str, b_strides=b_str,
+                   batch=batch, batch_strides=(m * k, n * k, 0))
+    assert got.dtype == torch.bfloat16
+    assert L.lib.flb200_tc_kernel_launches() > before
+    assert_close_scaled(got.float().reshape(want.shape), want, 1e-2, "bf16 matmul")
