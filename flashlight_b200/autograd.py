@@ -201,8 +201,45 @@ def rnn(x: Variable, hx: Optional[Variable], cx: Optional[Variable], w: Variable
     return out_y, out_h, out_c
 
 
+def cast(x: Variable, dtype) -> Variable:
+    """Variable::astype (flashlight/fl/autograd/Variable.cpp:160-175): the gradient is cast back
+    to the input's type, which is how fp32 master weights receive the gradients of their bf16
+    copies.  torch glue."""
+    src = x.tensor.dtype
+    if src == dtype:
+        return x
+    return glue(x, lambda t: t.to(dtype), lambda g: g.to(src))
+
+
+def _linear_bf16(x: Variable, w: Variable, b: Optional[Variable]) -> Variable:
+    """fl::linear on bf16 tensors: the three contractions go to flb200_matmul as strided views
+    (bf16 operands, fp32 accumulation); bias (fp32) through the channel kernels."""
+    xt, wt = x.tensor.contiguous(), w.tensor.contiguous()
+    I, O = wt.shape
+    rows = xt.numel() // I
+    y = F.matmul(xt, wt, m=rows, n=O, k=I, a_strides=(I, 1), b_strides=(O, 1))
+    y = y.reshape(tuple(xt.shape[:-1]) + (O,))
+    if b is not None:
+        F.channel_bias_add(y, b.tensor, rows, O, 1, out=y)
+
+    def grad_func(inputs, gy):
+        gy = gy.contiguous()
+        if inputs[0].isCalcGrad():   # dX (rows, I) = dY (rows, O) @ W^T (O, I)
+            gx = F.matmul(gy, wt, m=rows, n=I, k=O, a_strides=(O, 1), b_strides=(1, O))
+            inputs[0].addGrad(gx.reshape(xt.shape))
+        if inputs[1].isCalcGrad():   # dW (I, O) = X^T (I, rows) @ dY (rows, O)
+            inputs[1].addGrad(F.matmul(xt, gy, m=I, n=O, k=rows, a_strides=(1, I),
+                                       b_strides=(O, 1)))
+        if b is not None and inputs[2].isCalcGrad():
+            inputs[2].addGrad(F.channel_sum(gy, rows, O, 1).reshape(b.tensor.shape))
+
+    return Variable(y, False, [x, w] + ([b] if b is not None else []), grad_func)
+
+
 def linear(x: Variable, w: Variable, b: Optional[Variable]) -> Variable:
     """fl::linear (Functions.cpp:1255-1309)."""
+    if x.tensor.dtype == torch.bfloat16:
+        return _linear_bf16(x, w, b)
     mode = extension().math_mode
     bt = b.tensor if b is not None else None
     y = F.linear(x.tensor, w.tensor, bt, math_mode=mode)

@@ -204,6 +204,8 @@ int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, con
         const EpiloguePlan& ep, long long M, long long N, long long k_iters, long long Z, void* ws,
         size_t ws_bytes, cudaStream_t st, bool bf16) {
   Launch L = plan_launch(M, N, k_iters, Z);
+  // an MN-major bf16 B tile is made of 64-column boxes: no narrower tile than one box
+  if (bf16 && pb.mn_major && L.bn < 64) L.bn = 64;
   if (L.splits > 1 && (!ws || ws_bytes < L.workspace_bytes)) {
     L.splits = 1;
     L.iters_per_split = (int)k_iters;

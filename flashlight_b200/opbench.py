@@ -247,7 +247,7 @@ def suite_workloads(iters, math, which):
     channels T=1000 batch 16, 3-layer bidirectional LSTM H=1024 T=500 batch 32."""
     from . import autograd as A
     from . import workloads
-    A.set_math_mode(L.MATH_TF32 if math == "tf32" else L.MATH_STRICT_F32)
+    A.set_math_mode(L.MATH_STRICT_F32 if math == "strict" else L.MATH_TF32)
     g = torch.Generator().manual_seed(1234)
 
     def run(name, model, x, t, units, unit):
@@ -275,7 +275,8 @@ def suite_workloads(iters, math, which):
             torch.randint(0, 30, (B * T,), generator=g, dtype=torch.int32), B * T, "frames/s")
     if which in ("all", "transformer"):
         B, T = 8, 512
-        run("transformer_lm_12x768_t512_b8", workloads.TransformerLM(),
+        dt = torch.bfloat16 if math == "bf16" else torch.float32
+        run("transformer_lm_12x768_t512_b8", workloads.TransformerLM(compute_dtype=dt),
             torch.randint(0, 32000, (B, T), generator=g),
             torch.randint(0, 32000, (B * T,), generator=g, dtype=torch.int32), B * T, "tokens/s")
     if which in ("all", "bilstm"):
@@ -293,7 +294,8 @@ def main():
     ap.add_argument("--conv", default="64,64,56,56,64,3,1,1")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--math", default="strict", choices=["strict", "tf32"])
+    ap.add_argument("--math", default="strict", choices=["strict", "tf32", "bf16"],
+                    help="bf16 only applies to the transformer workload")
     a = ap.parse_args()
     if not torch.cuda.is_available():
         raise SystemExit("opbench needs a CUDA device")

@@ -195,16 +195,23 @@ class TransformerLM(nn.Module):
     w2(gelu(w1 x)) with the tanh-form GELU (Functions.cpp:1791-1796), a final LayerNorm, an
     untied output projection and full-softmax cross entropy.
 
-    Runs in fp32 / TF32: the contractions (q k v projections, scores, context, output and mlp
+    Runs in fp32 / TF32, or with compute_dtype=torch.bfloat16 (bf16 activations and matrix
+    operands, fp32 accumulation, fp32 master weights).  The contractions (q k v projections, scores, context, output and mlp
     projections, vocabulary projection and all their gradients), LayerNorm statistics, GELU,
     logSoftmax and the loss run on this library's kernels; head split / merge permutations,
     exp, the LayerNorm affine products, the residual stream and the embedding gather /
     scatter-add are torch glue (autograd.glue and friends)."""
 
-    def __init__(self, vocab=32000, d=768, heads=12, ffn=3072, layers=12, seed=1234, device="cuda"):
+    def __init__(self, vocab=32000, d=768, heads=12, ffn=3072, layers=12, seed=1234, device="cuda",
+                 compute_dtype=torch.float32):
         super().__init__()
         gen = torch.Generator().manual_seed(seed)
         self.d, self.heads, self.layers = d, heads, layers
+        # bf16 compute with fp32 master weights: parameters stay fp32; the matrices and the
+        # embedding are cast to bf16 where they are used and their gradients come back as fp32
+        # (autograd.cast); biases and LayerNorm parameters are used in fp32 by the kernels or
+        # cast likewise; the class scores are cast to fp32 for the loss.
+        self.compute_dtype = compute_dtype
         mk = lambda i, o: nn.Linear(i, o, True, gen, device)
         ones = lambda n: Variable(torch.ones(n, device=device), True)
         zeros = lambda n: Variable(torch.zeros(n, device=device), True)
@@ -233,12 +240,17 @@ class TransformerLM(nn.Module):
         return out + list(self.ln_f) + self.head.parameters()
 
     def _ln(self, x, wb):
-        return A.affine_rows(self.norm(x), wb[0], wb[1])
+        dt = self.compute_dtype
+        return A.affine_rows(self.norm(x), A.cast(wb[0], dt), A.cast(wb[1], dt))
+
+    def _lin(self, mod, x):
+        w = A.cast(mod.params[0], self.compute_dtype)
+        return A.linear(x, w, mod.params[1])
 
     def _attention(self, x, blk, B, T, mask):
         d, h = self.d, self.heads
         hd = d // h
-        qkv = blk["qkv"](x)  # (B*T, 3d)
+        qkv = self._lin(blk["qkv"], x)  # (B*T, 3d)
 
         def split(i, scale):
             fwd = lambda t: (t.reshape(B, T, 3, h, hd)[:, :, i].permute(0, 2, 1, 3) * scale) \
@@ -258,15 +270,17 @@ class TransformerLM(nn.Module):
         merged = A.glue(
             ctx, lambda t: t.reshape(B, h, T, hd).permute(0, 2, 1, 3).reshape(B * T, d).contiguous(),
             lambda g: g.reshape(B, T, h, hd).permute(0, 2, 1, 3).reshape(B * h, T, hd).contiguous())
-        return blk["proj"](merged)
+        return self._lin(blk["proj"], merged)
 
     def loss(self, ids: torch.Tensor, targets: torch.Tensor) -> Variable:
         """ids (B, T) token ids; targets (B*T,) next-token labels."""
         B, T = ids.shape
-        x = A.embedding(self.embed, ids)  # (B*T, d)
-        mask = torch.full((T, T), float("-inf"), device=x.tensor.device).triu(1)
+        x = A.embedding(A.cast(self.embed, self.compute_dtype), ids)  # (B*T, d)
+        mask = torch.full((T, T), float("-inf"), device=x.tensor.device,
+                          dtype=self.compute_dtype).triu(1)
         for blk in self.blocks:
             x = A.add(x, self._attention(self._ln(x, blk["ln1"]), blk, B, T, mask))
-            x = A.add(x, blk["w2"](A.gelu(blk["w1"](self._ln(x, blk["ln2"])))))
-        scores = self.head(self._ln(x, self.ln_f))
+            h = A.gelu(self._lin(blk["w1"], self._ln(x, blk["ln2"])))
+            x = A.add(x, self._lin(blk["w2"], h))
+        scores = A.cast(self._lin(self.head, self._ln(x, self.ln_f)), torch.float32)
         return A.log_softmax_cross_entropy(scores, targets)

@@ -35,3 +35,18 @@ def reference_root():
     if not REFERENCE.exists():
         pytest.skip("reference checkout not present on this machine")
     return REFERENCE
+
+
+@pytest.fixture(autouse=True)
+def _no_expired_device_waits(request):
+    """Every wait inside the tensor-core kernels is bounded; one that runs out only raises a
+    device flag.  After each GPU test the flag must be clear, so that a wait that expired can
+    never pass as a slow success."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from flashlight_b200 import _lib
+    assert _lib.lib.flb200_tc_poll_status(None) == 0, "a bounded device wait ran out in this test"

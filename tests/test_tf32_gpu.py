@@ -261,6 +261,8 @@ BF16_CASES = [
     (128, 128, 4096, 1, True, True),     # both, long K (split-K)
     (96, 64, 128, 6, False, True),       # batched (attention-sized)
     (24, 512, 768, 1, False, False),     # few rows: operands swap sides
+    (24, 16, 24, 12, False, True),       # attention context at a toy size: n below one 64-column box
+    (16, 24, 40, 5, True, True),
 ]
 
 
@@ -284,3 +286,4 @@ def test_matmul_bf16(L, case):
     assert got.dtype == torch.bfloat16
     assert L.lib.flb200_tc_kernel_launches() > before
     assert_close_scaled(got.float().reshape(want.shape), want, 1e-2, "bf16 matmul")
+    assert L.lib.flb200_tc_poll_status(None) == 0  # no bounded wait ran out

@@ -123,3 +123,28 @@ def test_transformer_lm_step(L, mode):
     loss.backward()
     want_loss, want_grads = CW.transformer_lm_step(host_params(model), ids, t, heads=4, layers=2)
     check_step(model, loss, want_loss, want_grads, mode)
+
+
+def test_transformer_lm_step_bf16(L):
+    """bf16 compute with fp32 master weights against the fp64 restatement on the same fp32
+    parameters.  Bounds: loss 3e-2 relative; every master-weight gradient within 0.25 relative
+    L2 error (8 mantissa bits per activation, two blocks deep) and fp32 in type."""
+    from flashlight_b200 import workloads
+    model = workloads.TransformerLM(vocab=96, d=64, heads=4, ffn=128, layers=2, seed=23,
+                                    compute_dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(29)
+    B, T = 3, 24
+    ids = torch.randint(0, 96, (B, T), generator=g)
+    t = torch.randint(0, 96, (B * T,), generator=g, dtype=torch.int32)
+    before = L.lib.flb200_tc_kernel_launches()
+    loss = model.loss(ids.cuda(), t.cuda())
+    loss.backward()
+    assert L.lib.flb200_tc_kernel_launches() > before
+    want_loss, want_grads = CW.transformer_lm_step(host_params(model), ids, t, heads=4, layers=2)
+    got = float(loss.tensor.cpu())
+    assert abs(got - float(want_loss)) <= 3e-2 * abs(float(want_loss)), (got, float(want_loss))
+    for i, (p, wg) in enumerate(zip(model.parameters(), want_grads)):
+        assert p.grad is not None and p.grad.dtype == torch.float32, i
+        gg = p.grad.detach().cpu().double().reshape(wg.shape)
+        err = float((gg - wg).norm()) / (float(wg.norm()) or 1.0)
+        assert err <= 0.25, f"parameter {i} {tuple(wg.shape)}: relative L2 error {err:.3e}"
