@@ -1,6 +1,5 @@
-// TF32 tensor-core convolution passes built on the tcgen05 contraction (tc_gemm.cuh).
-//
-// Two routes, both over fl's native NCHW buffers (no layout change at the boundary):
+// TF32 tensor-core convolution passes built on the tcgen05 contraction (tc_gemm.cuh), all over
+// fl's native NCHW buffers (no layout change at the boundary).  Four routes, tried in order:
 //
 //  * direct 1x1 (stride 1, no padding, H*W a multiple of 4): the image planes ARE the
 //    GEMM operands.  TMA reads x[n] / dy[n] as [channels][pixels] matrices (pixel index
@@ -10,14 +9,19 @@
 //      backward data  dx[n](hw, ci) = sum_co dy[n](co, hw) * w(co, ci)
 //      backward filt  dw(co, ci)    = sum_{n, hw} dy[n](co, hw) * x[n](ci, hw)   (split-K)
 //
-//  * general (any filter / stride / padding / dilation, groups == 1): the shifted
-//    windows cannot be fetched by TMA from NCHW (a tap offset breaks the 16-byte start
-//    rule), so a gather kernel first lays the im2col matrix col[k][n][hw_pad] out in
-//    scratch (pixel axis padded per image to a multiple of 4, padding = 0) and the
-//    passes become plain GEMMs on it.  Backward data gathers dy the same way with the
-//    transposed taps; backward filter also copies dy to [co][n][hw_pad].
+//  * channels-last patch route (tc_conv_patch.cu): >= 16 channels in and out, <= 64 taps,
+//    stride <= 2.  One NHWC copy of the activation operand, then an implicit GEMM whose tap
+//    shifts are TMA coordinates.
 //
-// Algorithmic flops 2*M*N*K of the implicit GEMM; the gather traffic is overhead.
+//  * row-window route (tc_conv_patch.cu): <= 4 input channels (forward, backward-filter).
+//
+//  * gather route (this file; any filter / stride / padding / dilation, groups == 1): a
+//    gather kernel lays the im2col matrix col[k][n][hw_pad] out in scratch (pixel axis
+//    padded per image to a multiple of 4, padding = 0) and the passes become plain GEMMs on
+//    it.  Backward data gathers dy the same way with the transposed taps; backward filter
+//    also copies dy to [co][n][hw_pad].
+//
+// Algorithmic flops 2*M*N*K of the implicit GEMM; copies and gathers are overhead.
 #include "tc_conv.cuh"
 
 #include "tc_gemm.cuh"

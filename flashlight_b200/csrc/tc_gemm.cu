@@ -6,7 +6,6 @@
 
 #include "tc_gemm.cuh"
 
-#include <cstdlib>
 #include <mutex>
 
 #include "tc_pair.cuh"
