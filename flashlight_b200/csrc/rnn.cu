@@ -17,6 +17,7 @@
 // The reserve space (forward -> backward payload) holds the activated gates,
 // cell states, GRU candidates' recurrent part and the outputs of inner layers.
 #include "common.cuh"
+#include "rnn_step.cuh"
 
 namespace flb200 {
 namespace {
@@ -359,10 +360,24 @@ int flb200_rnn_forward(const flb200_rnn_desc* d, const void* x, const void* hx, 
       const float* h_prev = hxf ? hxf + (long long)p * BH : zero;
       long long hp_stride = H;
       const float* c_prev = cxf ? cxf + (long long)p * BH : zero;
+      // LSTM in TF32 mode: one fused kernel per step (contraction + reduction + cell)
+      const bool fused = r.mode == FLB200_RNN_LSTM && lstm_step_supported(d->math_mode, B, H);
+      CUtensorMap map_whh;
+      if (fused)
+        if (int rc = lstm_step_weight_map(&map_whh, wf + po.w_hh, H)) return rc;
       for (int step = 0; step < T; ++step) {
         const int t = dir == 0 ? step : T - 1 - step;
         float* g_t = gates + (long long)t * B * GH;
         float* h_t = out + (long long)t * B * out_stride + (long long)dir * H;
+        if (fused) {
+          if (int rc = lstm_step_forward(map_whh, h_prev, hp_stride, g_t, c_prev, H,
+                                         cells + (long long)t * BH, h_t, out_stride, B, H, st))
+            return rc;
+          h_prev = h_t;
+          hp_stride = out_stride;
+          c_prev = cells + (long long)t * BH;
+          continue;
+        }
         if (r.mode == FLB200_RNN_GRU) {
           if (int rc = mm(d->math_mode, B, GH, H, h_prev, hp_stride, 1, wf + po.w_hh, 1, H, gh, GH,
                           0.f, mmws, mmws_bytes, stream))

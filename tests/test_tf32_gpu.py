@@ -174,11 +174,17 @@ def test_conv2d_tf32(L, case):
         assert n1 == 0 and n2 == 0 and n3 == 0
 
 
-def test_rnn_tf32(L):
-    """The recurrent and input GEMMs of the RNN run on the tensor-core kernel in TF32 mode."""
+@pytest.mark.parametrize("dims", [
+    (80, 128, 2, 32, 6),    # per-step contraction + cell kernel
+    (80, 256, 2, 32, 5),    # fused LSTM step, one CTA per cluster
+    (48, 512, 2, 7, 4),     # fused step, clusters of 2, ragged batch
+    (40, 1024, 1, 32, 3),   # fused step, clusters of 4 (the biLSTM workload's hidden size)
+])
+def test_rnn_tf32(L, dims):
+    """The recurrent and input GEMMs of the RNN run on the tensor-core kernels in TF32 mode."""
     from flashlight_b200.extension import AutogradPayload, B200AutogradExtension, RNNGradData
     ext = B200AutogradExtension(math_mode=L.MATH_TF32)
-    I, H, L_, B, T = 80, 128, 2, 32, 6
+    I, H, L_, B, T = dims
     n = R.rnn_num_params(I, H, L_, R.RNN_LSTM, True)
     w = randn(n, seed=40) * (0.5 / H ** 0.5)
     x = randn(T, B, I, seed=41)
