@@ -234,6 +234,12 @@ def install_timers(timer: OpTimer, ext, F):
     F.relu = timer.wrap("relu", F.relu, lambda out, x: (0.0, 2 * _numel_bytes(x)))
     F.relu_backward = timer.wrap("relu_backward", F.relu_backward,
                                  lambda out, x, gy: (0.0, 3 * _numel_bytes(x)))
+    # the bit-mask variants keep the operator's algorithmic byte counts (8 and 12 B/elem) so
+    # that the reported GB/s stays comparable; they move 8.1 B/elem each
+    F.relu_with_mask = timer.wrap("relu", F.relu_with_mask,
+                                  lambda out, x: (0.0, 2 * _numel_bytes(x)))
+    F.relu_backward_mask = timer.wrap("relu_backward", F.relu_backward_mask,
+                                      lambda out, mask, gy: (0.0, 3 * _numel_bytes(gy)))
     F.add = timer.wrap("add", F.add, lambda out, a, b, **k: (0.0, 3 * _numel_bytes(a)))
     F.linear = timer.wrap("linear", F.linear,
                           lambda out, x, w, b=None, **k: (2.0 * out.numel() * w.shape[0],

@@ -270,7 +270,18 @@ def _unary(x: Variable, fwd, bwd, save_output: bool) -> Variable:
 
 
 def relu(x: Variable) -> Variable:
-    # The mask (x > 0) equals (y > 0), so the output is the saved tensor and the input can be freed.
+    """fl::relu.  For contiguous f32 tensors the forward kernel also writes the predicate x > 0
+    as a bit mask and the gradient reads dy and the mask (a third less traffic than reading
+    dy and y); otherwise the output is the saved tensor ((x > 0) equals (y > 0))."""
+    t = x.tensor
+    if t.dtype == torch.float32 and t.is_contiguous() and t.data_ptr() % 16 == 0:
+        y, mask = F.relu_with_mask(t)
+
+        def grad_func(inputs, gy):
+            g = gy if gy.is_contiguous() and gy.data_ptr() % 16 == 0 else gy.contiguous().clone()
+            inputs[0].addGrad(F.relu_backward_mask(mask, g))
+
+        return Variable(y, False, [x], grad_func)
     return _unary(x, F.relu, F.relu_backward, True)
 
 

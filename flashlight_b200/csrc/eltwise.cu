@@ -203,7 +203,116 @@ struct Add {
 
 using namespace flb200;
 
+// ---- relu with a bit mask ----------------------------------------------------------------
+// Forward writes, next to y, one bit per element (x > 0); backward then reads dy and the mask
+// (4.125 bytes per element) instead of dy and y (8).  A thread owns groups of 8 elements: two
+// 16-byte vectors and one mask byte, two groups in flight per iteration.
+__device__ __forceinline__ unsigned relu8(const float4& a, const float4& b, float4& ya, float4& yb) {
+  const ReluFwd f{};
+  ya = make_float4(f(a.x), f(a.y), f(a.z), f(a.w));
+  yb = make_float4(f(b.x), f(b.y), f(b.z), f(b.w));
+  return (a.x > 0.f ? 1u : 0u) | (a.y > 0.f ? 2u : 0u) | (a.z > 0.f ? 4u : 0u) |
+         (a.w > 0.f ? 8u : 0u) | (b.x > 0.f ? 16u : 0u) | (b.y > 0.f ? 32u : 0u) |
+         (b.z > 0.f ? 64u : 0u) | (b.w > 0.f ? 128u : 0u);
+}
+
+__global__ void __launch_bounds__(256)
+relu_forward_mask_kernel(const float* __restrict__ x, float* __restrict__ y,
+                         uint8_t* __restrict__ mask, long long n) {
+  const long long full = n >> 3;  // complete groups of 8
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float4* xv = reinterpret_cast<const float4*>(x);
+  float4* yv = reinterpret_cast<float4*>(y);
+  long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; g + stride < full; g += 2 * stride) {
+    const long long g2 = g + stride;
+    const float4 a0 = xv[2 * g], b0 = xv[2 * g + 1], a1 = xv[2 * g2], b1 = xv[2 * g2 + 1];
+    float4 ya, yb;
+    mask[g] = (uint8_t)relu8(a0, b0, ya, yb);
+    yv[2 * g] = ya; yv[2 * g + 1] = yb;
+    mask[g2] = (uint8_t)relu8(a1, b1, ya, yb);
+    yv[2 * g2] = ya; yv[2 * g2 + 1] = yb;
+  }
+  if (g < full) {
+    float4 ya, yb;
+    mask[g] = (uint8_t)relu8(xv[2 * g], xv[2 * g + 1], ya, yb);
+    yv[2 * g] = ya; yv[2 * g + 1] = yb;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && (n & 7)) {  // ragged tail
+    unsigned bits = 0;
+    for (long long i = full * 8; i < n; ++i) {
+      y[i] = ReluFwd{}(x[i]);
+      bits |= (x[i] > 0.f ? 1u : 0u) << (i - full * 8);
+    }
+    mask[full] = (uint8_t)bits;
+  }
+}
+
+__device__ __forceinline__ void relu_bwd8(unsigned m, const float4& a, const float4& b, float4& da,
+                                          float4& db) {
+  da = make_float4(m & 1u ? a.x : 0.f, m & 2u ? a.y : 0.f, m & 4u ? a.z : 0.f, m & 8u ? a.w : 0.f);
+  db = make_float4(m & 16u ? b.x : 0.f, m & 32u ? b.y : 0.f, m & 64u ? b.z : 0.f,
+                   m & 128u ? b.w : 0.f);
+}
+
+__global__ void __launch_bounds__(256)
+relu_backward_mask_kernel(const uint8_t* __restrict__ mask, const float* __restrict__ dy,
+                          float* __restrict__ dx, long long n) {
+  const long long full = n >> 3;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const float4* gv = reinterpret_cast<const float4*>(dy);
+  float4* ov = reinterpret_cast<float4*>(dx);
+  long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; g + stride < full; g += 2 * stride) {
+    const long long g2 = g + stride;
+    const unsigned m0 = mask[g], m1 = mask[g2];
+    const float4 a0 = gv[2 * g], b0 = gv[2 * g + 1], a1 = gv[2 * g2], b1 = gv[2 * g2 + 1];
+    float4 da, db;
+    relu_bwd8(m0, a0, b0, da, db);
+    ov[2 * g] = da; ov[2 * g + 1] = db;
+    relu_bwd8(m1, a1, b1, da, db);
+    ov[2 * g2] = da; ov[2 * g2 + 1] = db;
+  }
+  if (g < full) {
+    float4 da, db;
+    relu_bwd8(mask[g], gv[2 * g], gv[2 * g + 1], da, db);
+    ov[2 * g] = da; ov[2 * g + 1] = db;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0 && (n & 7)) {
+    const unsigned bits = mask[full];
+    for (long long i = full * 8; i < n; ++i) dx[i] = (bits >> (i - full * 8)) & 1u ? dy[i] : 0.f;
+  }
+}
+
 extern "C" {
+
+int flb200_relu_forward_mask(const void* x, void* y, uint8_t* mask, int64_t n, int dtype,
+                             void* stream) {
+  FLB200_REQUIRE(n >= 0, "relu_forward_mask: negative size");
+  if (n == 0) return FLB200_OK;
+  FLB200_REQUIRE(x && y && mask, "relu_forward_mask: null tensor");
+  if (dtype != FLB200_F32 || !aligned16(x) || !aligned16(y))
+    return fail(FLB200_UNSUPPORTED, "relu_forward_mask: f32 tensors aligned to 16 bytes only");
+  const int grid = grid_for((n + 7) / 8, 256 * 2);
+  relu_forward_mask_kernel<<<grid, 256, 0, as_stream(stream)>>>(
+      static_cast<const float*>(x), static_cast<float*>(y), mask, n);
+  FLB200_AFTER_LAUNCH("relu_forward_mask");
+  return FLB200_OK;
+}
+
+int flb200_relu_backward_mask(const uint8_t* mask, const void* grad_y, void* grad_x, int64_t n,
+                              int dtype, void* stream) {
+  FLB200_REQUIRE(n >= 0, "relu_backward_mask: negative size");
+  if (n == 0) return FLB200_OK;
+  FLB200_REQUIRE(mask && grad_y && grad_x, "relu_backward_mask: null tensor");
+  if (dtype != FLB200_F32 || !aligned16(grad_y) || !aligned16(grad_x))
+    return fail(FLB200_UNSUPPORTED, "relu_backward_mask: f32 tensors aligned to 16 bytes only");
+  const int grid = grid_for((n + 7) / 8, 256 * 2);
+  relu_backward_mask_kernel<<<grid, 256, 0, as_stream(stream)>>>(
+      mask, static_cast<const float*>(grad_y), static_cast<float*>(grad_x), n);
+  FLB200_AFTER_LAUNCH("relu_backward_mask");
+  return FLB200_OK;
+}
 
 int flb200_relu_forward(const void* x, void* y, int64_t n, int dtype, void* stream) {
   return dispatch_unary("relu_forward", x, y, n, dtype, ReluFwd{}, stream);

@@ -42,6 +42,22 @@ def relu_backward(x, grad_y):
     return _binary(L.lib.flb200_relu_backward, x, grad_y)
 
 
+def relu_with_mask(x):
+    """relu that also returns the predicate x > 0 packed 8 elements per byte."""
+    y = torch.empty_like(x)
+    mask = torch.empty((x.numel() + 7) // 8, dtype=torch.uint8, device=x.device)
+    L.check(L.lib.flb200_relu_forward_mask(ptr(x), ptr(y), ptr(mask), x.numel(), dtype_code(x),
+                                           stream_handle()))
+    return y, mask
+
+
+def relu_backward_mask(mask, grad_y):
+    gx = torch.empty_like(grad_y)
+    L.check(L.lib.flb200_relu_backward_mask(ptr(mask), ptr(grad_y), ptr(gx), grad_y.numel(),
+                                            dtype_code(grad_y), stream_handle()))
+    return gx
+
+
 def gelu(x):
     """fl::gelu, tanh form (Functions.cpp:1791-1796)."""
     return _unary(L.lib.flb200_gelu_forward, x)

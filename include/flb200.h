@@ -271,6 +271,16 @@ int flb200_channel_sum_static_scratch(const void* in, float* out, int64_t outer,
 int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t outer,
                             int64_t channels, int64_t inner, int dtype, void* stream);
 
+/* relu with the predicate kept as one bit per element instead of a tensor: the reference's
+ * gradFunc multiplies dy by (result > 0) and keeps `result` alive for that
+ * (Functions.cpp:329-338, 1787-1789); here forward also writes mask[i / 8] bit (i % 8) = x[i] > 0
+ * (ceil(n / 8) bytes, caller-owned) and backward reads dy and the mask only.  f32, 16-byte
+ * aligned tensors. */
+int flb200_relu_forward_mask(const void* x, void* y, uint8_t* mask, int64_t n, int dtype,
+                             void* stream);
+int flb200_relu_backward_mask(const uint8_t* mask, const void* grad_y, void* grad_x, int64_t n,
+                              int dtype, void* stream);
+
 /* relu = max(x, 0) (Functions.cpp:1787-1789); gradient (x > 0) * dy (Functions.cpp:329-338). */
 int flb200_relu_forward(const void* x, void* y, int64_t n, int dtype, void* stream);
 int flb200_relu_backward(const void* x, const void* grad_y, void* grad_x, int64_t n,

@@ -389,3 +389,23 @@ def test_rnn_backward_without_output_gradient(ext):
     with pytest.raises(ValueError):
         ext.rnnBackward(x.cuda(), None, None, w.cuda(), RNNGradData(), y, L_, H, R.RNN_LSTM, False, 0.0,
                         None)
+
+
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 1000, 4096 + 5, 3 * 1024 * 1024 + 3])
+def test_relu_bit_mask(fx, n):
+    """relu with the x > 0 predicate packed 8 per byte: same y as the plain kernel, the mask
+    bits equal the predicate, and the masked gradient equals (x > 0) * dy bit for bit — also for
+    NaN (propagates through y, no gradient), negative zero and ragged tails."""
+    x = randn(n, seed=51)
+    if n >= 9:
+        x[3], x[4], x[5] = float("nan"), -0.0, 0.0
+    g = randn(n, seed=52)
+    xd, gd = x.cuda(), g.cuda()
+    y, mask = fx.relu_with_mask(xd)
+    assert torch.equal(torch.nan_to_num(y, nan=123.0), torch.nan_to_num(fx.relu(xd), nan=123.0))
+    bits = (x > 0).to(torch.uint8)
+    bits = torch.cat([bits, torch.zeros((-n) % 8, dtype=torch.uint8)]).reshape(-1, 8)
+    want_mask = (bits * (2 ** torch.arange(8, dtype=torch.uint8))).sum(1).to(torch.uint8)
+    assert torch.equal(mask.cpu(), want_mask)
+    gx = fx.relu_backward_mask(mask, gd)
+    assert torch.equal(gx.cpu(), torch.where(x > 0, g, torch.zeros_like(g)))
