@@ -5,7 +5,7 @@
 //
 // Work split: a cluster owns 32 hidden units (all four gates = the 128 rows of one UMMA tile,
 // gate-major), its KS CTAs split K = H into slices of 256.  A CTA brings its whole operand
-// slice (128 x 256 of W_hh, 32 x 256 of h_prev) with one burst of TMA loads on one mbarrier,
+// slice (128 x 256 of W_hh, 32 x 256 of h_prev) with one burst of TMA loads (a barrier per k tile),
 // issues 32 tcgen05.mma (M = 128, N = 32 batch columns, TF32), copies its 128 x 32 partial
 // accumulator from tensor memory to shared memory, and after a cluster barrier each CTA sums
 // the partials of 32 / KS units over the cluster's shared memories (DSMEM), adds the input
@@ -28,7 +28,7 @@ constexpr int kStagesK = kSliceK / kBK;     // 8 tiles of 32 k
 constexpr int kABytes = kBM * kBK * 4;      // 16 KB per k tile
 constexpr int kBBytes = 32 * kBK * 4;       // 4 KB per k tile (32 batch rows)
 constexpr int kPartStride = 33;             // floats per partial row (bank-conflict padding)
-constexpr int kSmemBytes = kStagesK * (kABytes + kBBytes) + kBM * kPartStride * 4 + 64 + 1024;
+constexpr int kSmemBytes = kStagesK * (kABytes + kBBytes) + kBM * kPartStride * 4 + 128 + 1024;
 
 struct StepArgs {
   float* gates;          // [B][4H]: input projection + biases in, activated gates out
@@ -59,8 +59,8 @@ lstm_step_kernel(const __grid_constant__ CUtensorMap map_w,
   char* a_tiles = tiles;
   char* b_tiles = tiles + kStagesK * kABytes;
   float* part = reinterpret_cast<float*>(b_tiles + kStagesK * kBBytes);
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(part + kBM * kPartStride);
-  uint64_t* done_bar = full_bar + 1;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(part + kBM * kPartStride);  // [kStagesK]
+  uint64_t* done_bar = full_bar + kStagesK;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(done_bar + 1);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -70,7 +70,7 @@ lstm_step_kernel(const __grid_constant__ CUtensorMap map_w,
   const int H = a.H;
 
   if (threadIdx.x == 0) {
-    mbar_init(full_bar, 1);
+    for (int s = 0; s < kStagesK; ++s) mbar_init(&full_bar[s], 1);
     mbar_init(done_bar, 1);
     *failed = 0;
     fence_barrier_init();
@@ -82,33 +82,33 @@ lstm_step_kernel(const __grid_constant__ CUtensorMap map_w,
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) mbar_expect_tx(full_bar, kStagesK * (kABytes + kBBytes));
+    // one barrier per k tile, so that the MMAs of tile 0 start while later tiles are in flight
+    if (lane < kStagesK) mbar_expect_tx(&full_bar[lane], kABytes + kBBytes);
     __syncwarp();
     {  // 32 boxes of W_hh: k tile = lane / 4, gate = lane % 4
       const int s = lane >> 2, g = lane & 3;
       int c[2] = {rank * kSliceK + s * kBK, g * H + group * 32};
-      tma_load(&map_w, full_bar, a_tiles + s * kABytes + g * (32 * 128), 2, c);
+      tma_load(&map_w, &full_bar[s], a_tiles + s * kABytes + g * (32 * 128), 2, c);
     }
     if (lane < kStagesK) {  // 8 boxes of h_prev (rows past the batch are zero-filled)
       int c[2] = {rank * kSliceK + lane * kBK, 0};
-      tma_load(&map_h, full_bar, b_tiles + lane * kBBytes, 2, c);
+      tma_load(&map_h, &full_bar[lane], b_tiles + lane * kBBytes, 2, c);
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      if (!mbar_wait(full_bar, 0)) {
-        *failed = 1;
-      } else {
-        tc_fence_after();
-        const uint32_t idesc = umma_idesc_tf32(32, 0, 0);
-#pragma unroll
-        for (int s = 0; s < kStagesK; ++s) {
-          const uint32_t a_addr = smem_u32(a_tiles + s * kABytes);
-          const uint32_t b_addr = smem_u32(b_tiles + s * kBBytes);
-#pragma unroll
-          for (int j = 0; j < kBK / kUmmaK; ++j)
-            umma_tf32(tmem_base, umma_desc(a_addr + j * 32, 16, 1024, 2),
-                      umma_desc(b_addr + j * 32, 16, 1024, 2), idesc, (s | j) ? 1u : 0u);
+      const uint32_t idesc = umma_idesc_tf32(32, 0, 0);
+      for (int s = 0; s < kStagesK; ++s) {
+        if (!mbar_wait(&full_bar[s], 0)) {
+          *failed = 1;
+          break;
         }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(a_tiles + s * kABytes);
+        const uint32_t b_addr = smem_u32(b_tiles + s * kBBytes);
+#pragma unroll
+        for (int j = 0; j < kBK / kUmmaK; ++j)
+          umma_tf32(tmem_base, umma_desc(a_addr + j * 32, 16, 1024, 2),
+                    umma_desc(b_addr + j * 32, 16, 1024, 2), idesc, (s | j) ? 1u : 0u);
       }
       umma_commit(done_bar);  // arrives when every MMA issued above (possibly none) is done
     }

@@ -174,7 +174,7 @@ def mse(y: Variable, target: torch.Tensor) -> Variable:
     n = y.tensor.numel()
     diff = F.add(y.tensor, -target)  # negation of the constant target is input preparation
     sq = F.dropout_apply(diff, diff, 0.0)  # diff * diff * 1
-    total = F.channel_sum(sq.reshape(-1), n, 1, 1)
+    total = F.channel_sum(sq.reshape(-1), 1, 1, n)  # one channel, n contiguous elements
 
     def grad_func(inputs, gl):
         # d/dy = 2 (y - t) / n * gl ; gl is a device scalar of ones in the benchmark
