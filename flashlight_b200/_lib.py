@@ -96,6 +96,7 @@ SIGNATURES = {
     "flb200_channel_sum": (C.c_int, [vp, vp, i64, i64, i64, C.c_int, vp, sz, vp]),
     "flb200_channel_sum_static_scratch": (C.c_int, [vp, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_channel_bias_add": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_int, vp]),
+    "flb200_sgd_step": (C.c_int, [vp, vp, vp, i64, f32, f32, f32, C.c_int, f32, C.c_int, C.c_int, vp]),
     "flb200_relu_forward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_relu_backward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_relu_forward": (C.c_int, [vp, vp, i64, C.c_int, vp]),

@@ -284,7 +284,60 @@ relu_backward_mask_kernel(const uint8_t* __restrict__ mask, const float* __restr
   }
 }
 
+// ---- SGD step --------------------------------------------------------------------------------
+// One pass over a parameter: reads p, g, v, writes p and v (20 bytes per element; the reference's
+// chain of whole-tensor operations moves about three times that).
+__global__ void __launch_bounds__(256)
+sgd_step_kernel(float* __restrict__ p, float* __restrict__ g, float* __restrict__ v, long long n,
+                float lr, float mu, float wd, int nesterov, float grad_scale, int grad_mode) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(p) | reinterpret_cast<uintptr_t>(g) |
+                     (v ? reinterpret_cast<uintptr_t>(v) : 0)) & 15) == 0;
+  auto one = [&](float pp, float gg, float& vv) {
+    gg = gg * grad_scale + wd * pp;
+    if (mu != 0.f) {
+      vv = mu * vv + gg;
+      gg = nesterov ? gg + mu * vv : vv;
+    }
+    return pp - lr * gg;
+  };
+  const long long nv = vec ? n >> 2 : 0;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += stride) {
+    float4 pp = reinterpret_cast<float4*>(p)[i];
+    const float4 gg = reinterpret_cast<const float4*>(g)[i];
+    float4 vv = v ? reinterpret_cast<float4*>(v)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    pp.x = one(pp.x, gg.x, vv.x); pp.y = one(pp.y, gg.y, vv.y);
+    pp.z = one(pp.z, gg.z, vv.z); pp.w = one(pp.w, gg.w, vv.w);
+    reinterpret_cast<float4*>(p)[i] = pp;
+    if (v) reinterpret_cast<float4*>(v)[i] = vv;
+    if (grad_mode == 1) reinterpret_cast<float4*>(g)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (long long i = nv * 4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+    float vv = v ? v[i] : 0.f;
+    p[i] = one(p[i], g[i], vv);
+    if (v) v[i] = vv;
+    if (grad_mode == 1) g[i] = 0.f;
+  }
+}
+
 extern "C" {
+
+int flb200_sgd_step(void* param, void* grad, void* velocity, int64_t n, float lr, float momentum,
+                    float weight_decay, int nesterov, float grad_scale, int zero_grad, int dtype,
+                    void* stream) {
+  FLB200_REQUIRE(n >= 0, "sgd_step: negative size");
+  if (n == 0) return FLB200_OK;
+  FLB200_REQUIRE(param && grad, "sgd_step: null tensor");
+  FLB200_REQUIRE(momentum == 0.f || velocity, "sgd_step: momentum needs a velocity buffer");
+  if (dtype != FLB200_F32) return fail(FLB200_UNSUPPORTED, "sgd_step: f32 parameters only");
+  const int grid = grid_for((n + 3) / 4, 256);
+  sgd_step_kernel<<<grid, 256, 0, as_stream(stream)>>>(
+      static_cast<float*>(param), static_cast<float*>(grad),
+      momentum != 0.f ? static_cast<float*>(velocity) : nullptr, n, lr, momentum, weight_decay,
+      nesterov ? 1 : 0, grad_scale, zero_grad ? 1 : 0);
+  FLB200_AFTER_LAUNCH("sgd_step");
+  return FLB200_OK;
+}
 
 int flb200_relu_forward_mask(const void* x, void* y, uint8_t* mask, int64_t n, int dtype,
                              void* stream) {

@@ -301,6 +301,18 @@ int flb200_dropout_apply(const void* in, const void* mask, void* out, float scal
 /* out = a + b: Variable::addGrad fan-in accumulation (flashlight/fl/autograd/Variable.cpp:205-211). In place allowed. */
 int flb200_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
 
+/* fl::SGDOptimizer::step for one parameter in one pass
+ * (flashlight/fl/optim/SGDOptimizer.cpp:38-68):
+ *   g = grad_scale * grad + weight_decay * p;   v = momentum * v + g   (momentum != 0)
+ *   g = nesterov ? g + momentum * v : v;        p = p - lr * g
+ * grad_scale folds the 1/world-size of the data-parallel average
+ * (flashlight/fl/nn/DistributedUtils.cpp:16-22); zero_grad != 0 clears grad in the same pass
+ * (the zeroGrad() of the next step).  velocity may be NULL when momentum == 0.  Unlike the
+ * reference, grad is not left holding the update direction.  f32. */
+int flb200_sgd_step(void* param, void* grad, void* velocity, int64_t n, float lr, float momentum,
+                    float weight_decay, int nesterov, float grad_scale, int zero_grad, int dtype,
+                    void* stream);
+
 /* logSoftmax over fl dim 0: x, y [C, X] column-major (Functions.cpp:1044-1070). */
 int flb200_log_softmax_forward(const void* x, void* y, int64_t C, int64_t X, int dtype,
                                void* stream);

@@ -428,3 +428,12 @@ def rnn_backward(x, hx, cx, w, hidden, layers, mode, bidirectional, gy, ghy, gcy
         if dcx is None:
             dcx = torch.zeros_like(cr)
     return dx, dhx, dcx, dw
+
+
+def sgd_step(p, g, v, lr, momentum, weight_decay, nesterov, grad_scale=1.0):
+    """flashlight/fl/optim/SGDOptimizer.cpp:38-68 on one parameter; returns (p, v)."""
+    g = g * grad_scale + weight_decay * p
+    if momentum != 0:
+        v = momentum * v + g
+        g = g + momentum * v if nesterov else v
+    return p - lr * g, v

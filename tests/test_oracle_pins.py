@@ -232,3 +232,22 @@ def test_linear_oracle():
     wx, ww, wb = torch.autograd.grad(F.linear(xr, wr.t(), br), (xr, wr, br), gy)
     gx, gw, gb = R.linear_backward(x, w, gy, True)
     assert rel_err(gx, wx) < 1e-12 and rel_err(gw, ww) < 1e-12 and rel_err(gb, wb) < 1e-12
+
+
+def test_sgd_rule_matches_the_torch_optimizer():
+    """fl::SGDOptimizer's update (weight decay added to the gradient, momentum buffer without
+    dampening, optional Nesterov) is torch.optim.SGD's; three steps must agree."""
+    import torch
+    from oracle import flref as R
+    for nesterov in (False, True):
+        g = torch.Generator().manual_seed(3)
+        p = torch.randn(257, generator=g, dtype=torch.float64)
+        tp = p.clone().requires_grad_(True)
+        opt = torch.optim.SGD([tp], lr=0.1, momentum=0.9, weight_decay=0.1, nesterov=nesterov)
+        v = torch.zeros_like(p)
+        for _ in range(3):
+            grad = torch.randn(257, generator=g, dtype=torch.float64)
+            tp.grad = grad.clone()
+            opt.step()
+            p, v = R.sgd_step(p, grad, v, 0.1, 0.9, 0.1, nesterov)
+        assert torch.allclose(p, tp.detach(), rtol=0, atol=1e-12)

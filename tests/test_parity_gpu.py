@@ -409,3 +409,29 @@ def test_relu_bit_mask(fx, n):
     assert torch.equal(mask.cpu(), want_mask)
     gx = fx.relu_backward_mask(mask, gd)
     assert torch.equal(gx.cpu(), torch.where(x > 0, g, torch.zeros_like(g)))
+
+
+@pytest.mark.parametrize("cfg", [
+    (0.1, 0.9, 0.1, False, 1.0),      # the reference benchmark's setting
+    (0.05, 0.9, 0.0, True, 0.125),    # Nesterov, gradient averaged over 8 ranks
+    (0.01, 0.0, 0.01, False, 1.0),    # no momentum: no velocity buffer
+])
+@pytest.mark.parametrize("n", [1, 1023, 4096 + 3, 2_000_003])
+def test_sgd_step(cfg, n):
+    """Fused SGD step against the reference's update rule, three steps in a row."""
+    from flashlight_b200.autograd import Variable
+    from flashlight_b200.optim import SGDOptimizer
+    lr, mu, wd, nesterov, scale = cfg
+    p0 = randn(n, seed=61)
+    param = Variable(p0.clone().cuda(), True)
+    opt = SGDOptimizer([param], lr, mu, wd, nesterov)
+    want_p, want_v = p0.double(), torch.zeros(n, dtype=torch.float64)
+    for it in range(3):
+        g = randn(n, seed=62 + it)
+        param.grad = g.clone().cuda()
+        opt.step(grad_scale=scale, zero_grad=(it == 2))
+        want_p, want_v = R.sgd_step(want_p, g.double(), want_v, lr, mu, wd, nesterov, scale)
+    assert_close(param.tensor, want_p, 1e-5, "sgd parameter")
+    if mu != 0:
+        assert_close(opt.velocities[0], want_v, 1e-5, "sgd velocity")
+    assert float(param.grad.abs().max()) == 0.0  # cleared by the last step
