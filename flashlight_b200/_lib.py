@@ -18,6 +18,7 @@ POOL_MAX, POOL_AVG_INCLUDE_PAD, POOL_AVG_EXCLUDE_PAD = 0, 1, 2
 RNN_RELU, RNN_TANH, RNN_LSTM, RNN_GRU = 0, 1, 2, 3
 MATH_STRICT_F32, MATH_TF32 = 0, 1
 REDUCE_NONE, REDUCE_MEAN, REDUCE_SUM = 0, 1, 2
+IDS_I32, IDS_I64 = 0, 1
 
 i32, i64, f32, f64, vp, sz = C.c_int32, C.c_int64, C.c_float, C.c_double, C.c_void_p, C.c_size_t
 
@@ -96,6 +97,8 @@ SIGNATURES = {
     "flb200_channel_sum": (C.c_int, [vp, vp, i64, i64, i64, C.c_int, vp, sz, vp]),
     "flb200_channel_sum_static_scratch": (C.c_int, [vp, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_channel_bias_add": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_int, vp]),
+    "flb200_embedding_forward": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, C.c_int, vp]),
+    "flb200_embedding_backward": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_sgd_step": (C.c_int, [vp, vp, vp, i64, f32, f32, f32, C.c_int, f32, C.c_int, C.c_int, vp]),
     "flb200_relu_forward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_relu_backward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),

@@ -437,13 +437,13 @@ def affine_rows(x: Variable, w: Variable, b: Variable) -> Variable:
 
 def embedding(table: Variable, ids: torch.Tensor) -> Variable:
     """fl::embedding (Functions.cpp:1707-1749): rows of the table picked by token id; the
-    gradient is a scatter-add into the table.  Both are torch glue (index_select / index_add_)."""
-    flat = ids.reshape(-1).long()
-    y = table.tensor.index_select(0, flat)
+    gradient is a scatter-add into the table, done without atomics (embedding.cu).  The table
+    gradient is always f32: when the table is a bf16 copy of fp32 master weights (autograd.cast)
+    the master receives it without a round trip through bf16."""
+    vocab = table.tensor.shape[0]
+    y = F.embedding(table.tensor, ids)
 
     def grad_func(inputs, gy):
-        g = torch.zeros_like(table.tensor)
-        g.index_add_(0, flat, gy)
-        inputs[0].addGrad(g)
+        inputs[0].addGrad(F.embedding_backward(gy, ids, vocab))
 
     return Variable(y, False, [table], grad_func)

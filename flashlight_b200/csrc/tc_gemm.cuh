@@ -1,6 +1,7 @@
-// Host interface of the tcgen05 (tensor-core) TF32 contraction: the plan structs that
-// describe how operands are fetched by TMA and how the accumulator is stored, and the
-// entry points used by matmul, the convolution paths and the RNN.
+// Host interface of the tcgen05 (tensor-core) contraction — fp32 operands read as TF32, or
+// bf16 operands — with fp32 accumulation: the plan structs that describe how operands are
+// fetched by TMA and how the accumulator is stored, and the entry points used by matmul, the
+// convolution paths and the RNN.
 #pragma once
 #include <cuda.h>
 

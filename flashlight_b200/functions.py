@@ -253,3 +253,33 @@ def log_softmax_cross_entropy_backward(y, grad_loss, state: CrossEntropyState):
         ptr(y), ptr(grad_loss), ptr(state.targets), state.count.data_ptr(), ptr(gx), Cc, X,
         state.reduction, state.ignore_index, dtype_code(y), stream_handle()))
     return gx
+
+
+# ------------------------------------------------------------------ embedding
+def _ids(ids):
+    if ids.dtype == torch.int64:
+        return ids.contiguous(), L.IDS_I64
+    if ids.dtype == torch.int32:
+        return ids.contiguous(), L.IDS_I32
+    raise ValueError("embedding: ids must be int32 or int64")
+
+
+def embedding(table, ids):
+    """fl::embedding forward: rows of `table` (vocab, dim) picked by `ids` (any shape)."""
+    flat, code = _ids(ids.reshape(-1))
+    vocab, dim = table.shape
+    out = torch.empty((flat.numel(), dim), dtype=table.dtype, device=table.device)
+    L.check(L.lib.flb200_embedding_forward(ptr(table), ptr(flat), code, ptr(out), flat.numel(), dim,
+                                           vocab, dtype_code(table), stream_handle()))
+    return out
+
+
+def embedding_backward(grad_out, ids, vocab: int):
+    """Gradient of the table (f32, (vocab, dim)), summed in position order without atomics."""
+    flat, code = _ids(ids.reshape(-1))
+    g = grad_out.contiguous()
+    dim = g.shape[-1]
+    table_grad = torch.empty((vocab, dim), dtype=torch.float32, device=g.device)
+    L.check(L.lib.flb200_embedding_backward(ptr(g), ptr(flat), code, ptr(table_grad), flat.numel(),
+                                            dim, vocab, dtype_code(g), stream_handle()))
+    return table_grad

@@ -6,6 +6,8 @@ operator for operator over the B200 kernels (nn.py / autograd.py).
   conv_asr        12 x (Conv2D k=13x1 SAME, LayerNorm{0,1,2}, ReLU) + Linear + CE
                   (flashlight/pkg/runtime/common/SequentialBuilder.cpp:215-226, 332-350)
   bilstm          fl::RNN(80, 1024, 3, LSTM, bidirectional) + MSE
+  TransformerLM   12 pre-LayerNorm decoder blocks, d = 768, 12 heads, FFN 3072, vocabulary
+                  32000, causal mask; fp32 / TF32 or bf16 compute with fp32 master weights
 
 Each builder returns a model whose `loss(inputs, targets)` builds the tape and
 returns the scalar loss Variable; `loss(...).backward()` is the measured step.
@@ -198,9 +200,9 @@ class TransformerLM(nn.Module):
     Runs in fp32 / TF32, or with compute_dtype=torch.bfloat16 (bf16 activations and matrix
     operands, fp32 accumulation, fp32 master weights).  The contractions (q k v projections, scores, context, output and mlp
     projections, vocabulary projection and all their gradients), LayerNorm statistics, GELU,
-    logSoftmax and the loss run on this library's kernels; head split / merge permutations,
-    exp, the LayerNorm affine products, the residual stream and the embedding gather /
-    scatter-add are torch glue (autograd.glue and friends)."""
+    logSoftmax, the loss, the residual adds and the embedding lookup with its scatter-add
+    gradient run on this library's kernels; head split / merge permutations,
+    exp and the LayerNorm affine products are torch glue (autograd.glue and friends)."""
 
     def __init__(self, vocab=32000, d=768, heads=12, ffn=3072, layers=12, seed=1234, device="cuda",
                  compute_dtype=torch.float32):

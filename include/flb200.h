@@ -313,6 +313,19 @@ int flb200_sgd_step(void* param, void* grad, void* velocity, int64_t n, float lr
                     float weight_decay, int nesterov, float grad_scale, int zero_grad, int dtype,
                     void* stream);
 
+/* fl::embedding (Functions.cpp:1707-1749): out row r = table row ids[r]; table [vocab][dim]
+ * row-major (fl [dim, vocab]), ids int32 or int64, out [rows][dim].  Ids outside [0, vocab)
+ * give a zero row / are ignored by the gradient. */
+enum { FLB200_IDS_I32 = 0, FLB200_IDS_I64 = 1 };
+int flb200_embedding_forward(const void* table, const void* ids, int ids_dtype, void* out,
+                             int64_t rows, int64_t dim, int64_t vocab, int dtype, void* stream);
+/* Its gradient: grad_table [vocab][dim] (f32, fully overwritten) = sum of the grad_out rows of
+ * every position holding that id, added in increasing position order (no atomics; the
+ * reference's kernel uses atomicAdd: flashlight/fl/tensor/backend/af/AdvancedIndex.cu:28-79). */
+int flb200_embedding_backward(const void* grad_out, const void* ids, int ids_dtype,
+                              float* grad_table, int64_t rows, int64_t dim, int64_t vocab,
+                              int dtype, void* stream);
+
 /* logSoftmax over fl dim 0: x, y [C, X] column-major (Functions.cpp:1044-1070). */
 int flb200_log_softmax_forward(const void* x, void* y, int64_t C, int64_t X, int dtype,
                                void* stream);

@@ -2,9 +2,11 @@
 
 The reference's own CPU path (ArrayFire-CPU tensors + OneDnnAutogradExtension) cannot be built
 in this image, so the timed CPU baseline is the same operator sequence on torch-CPU (which
-links the same oneDNN generation), driven by torch autograd, on all host threads.  Topology:
-flashlight/pkg/vision/models/Resnet.cpp:67-121, 161-172, 210-230.  Used by bench.py's
-cpu_baseline leg and its `--impl reference` arm, and by the end-to-end parity test.
+links the same oneDNN generation), driven by torch autograd, on all host threads.  ResNet-50
+topology: flashlight/pkg/vision/models/Resnet.cpp:67-121, 161-172, 210-230; used by bench.py's
+cpu_baseline leg and its `--impl reference` arm.  The restatements of the other four synthetic
+workloads (MNIST convnet, conv-ASR, biLSTM, Transformer-LM) further down are the checkers of
+tests/test_workloads_gpu.py.
 """
 from __future__ import annotations
 

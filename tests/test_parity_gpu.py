@@ -435,3 +435,26 @@ def test_sgd_step(cfg, n):
     if mu != 0:
         assert_close(opt.velocities[0], want_v, 1e-5, "sgd velocity")
     assert float(param.grad.abs().max()) == 0.0  # cleared by the last step
+
+
+@pytest.mark.parametrize("case", [
+    (97, 64, 72, torch.int64, torch.float32),       # toy vocabulary, repeated ids
+    (1000, 768, 513, torch.int32, torch.float32),   # dim of the transformer workload
+    (50, 1100, 40, torch.int64, torch.float32),     # dim > 1024: two column chunks
+    (300, 96, 700, torch.int64, torch.bfloat16),    # bf16 activations, f32 table gradient
+])
+def test_embedding(fx, case):
+    """Row gather and its scatter-add gradient (no atomics: two runs are bit-identical)."""
+    vocab, dim, rows, itype, dtype = case
+    g = torch.Generator().manual_seed(71)
+    table = randn(vocab, dim, seed=72).to(dtype)
+    ids = torch.randint(0, vocab, (rows,), generator=g).to(itype)
+    ids[: rows // 3] = ids[0]  # one heavily repeated id
+    out = fx.embedding(table.cuda(), ids.cuda())
+    assert torch.equal(out.cpu(), table[ids.long()])
+    gy = randn(rows, dim, seed=73).to(dtype)
+    got = fx.embedding_backward(gy.cuda(), ids.cuda(), vocab)
+    again = fx.embedding_backward(gy.cuda(), ids.cuda(), vocab)
+    assert got.dtype == torch.float32 and torch.equal(got, again)
+    want = torch.zeros(vocab, dim, dtype=torch.float64).index_add_(0, ids.long(), gy.double())
+    assert_close(got, want, 1e-5, "embedding gradient")
