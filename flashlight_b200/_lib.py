@@ -99,6 +99,8 @@ SIGNATURES = {
     "flb200_channel_bias_add": (C.c_int, [vp, vp, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_embedding_forward": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_embedding_backward": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, C.c_int, vp]),
+    "flb200_softmax_forward": (C.c_int, [vp, vp, i64, i64, f32, i64, C.c_int, vp]),
+    "flb200_softmax_backward": (C.c_int, [vp, vp, vp, i64, i64, f32, C.c_int, vp]),
     "flb200_sgd_step": (C.c_int, [vp, vp, vp, i64, f32, f32, f32, C.c_int, f32, C.c_int, C.c_int, vp]),
     "flb200_relu_forward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_relu_backward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),

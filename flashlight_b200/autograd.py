@@ -403,15 +403,15 @@ def bmm(a: Variable, b: Variable, trans_b: bool = False) -> Variable:
     return Variable(y, False, [a, b], grad_func)
 
 
-def softmax_rows(x: Variable) -> Variable:
-    """softmax over the last dimension as exp(logSoftmax(x)) (Functions.cpp:1021-1042): the
-    row reductions run in the logSoftmax kernels, exp and the product with the output are
-    torch glue.  dX = logSoftmaxBackward(l, dP * P)."""
-    l = F.log_softmax(x.tensor)
-    p = torch.exp(l)
+def softmax_rows(x: Variable, scale: float = 1.0, causal_period: int = 0) -> Variable:
+    """softmax over the last dimension (Functions.cpp:1021-1042) of scale * x, with the causal
+    mask of attention scores folded in when causal_period = T (x is a stack of T-row score
+    matrices): one kernel forward, one backward (attention_softmax.cu)."""
+    xt = x.tensor.contiguous()
+    p = F.softmax(xt, scale, causal_period)
 
     def grad_func(inputs, gy):
-        inputs[0].addGrad(F.log_softmax_backward(l, gy * p))
+        inputs[0].addGrad(F.softmax_backward(p, gy.contiguous(), scale))
 
     return Variable(p, False, [x], grad_func)
 

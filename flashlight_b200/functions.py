@@ -283,3 +283,22 @@ def embedding_backward(grad_out, ids, vocab: int):
     L.check(L.lib.flb200_embedding_backward(ptr(g), ptr(flat), code, ptr(table_grad), flat.numel(),
                                             dim, vocab, dtype_code(g), stream_handle()))
     return table_grad
+
+
+# ------------------------------------------------------------------ attention softmax
+def softmax(x, scale: float = 1.0, causal_period: int = 0):
+    """softmax over the last dim of scale * x, optionally with the causal mask of stacked
+    (period x cols) score matrices folded in."""
+    Cc, X = _cx(x)
+    y = torch.empty_like(x)
+    L.check(L.lib.flb200_softmax_forward(ptr(x), ptr(y), Cc, X, scale, causal_period, dtype_code(x),
+                                         stream_handle()))
+    return y
+
+
+def softmax_backward(y, grad_y, scale: float = 1.0):
+    Cc, X = _cx(y)
+    gx = torch.empty_like(y)
+    L.check(L.lib.flb200_softmax_backward(ptr(y), ptr(grad_y), ptr(gx), Cc, X, scale, dtype_code(y),
+                                          stream_handle()))
+    return gx

@@ -201,8 +201,8 @@ class TransformerLM(nn.Module):
     operands, fp32 accumulation, fp32 master weights).  The contractions (q k v projections, scores, context, output and mlp
     projections, vocabulary projection and all their gradients), LayerNorm statistics, GELU,
     logSoftmax, the loss, the residual adds and the embedding lookup with its scatter-add
-    gradient run on this library's kernels; head split / merge permutations,
-    exp and the LayerNorm affine products are torch glue (autograd.glue and friends)."""
+    gradient and the scaled causal softmax run on this library's kernels; head split / merge
+    permutations and the LayerNorm affine products are torch glue (autograd.glue and friends)."""
 
     def __init__(self, vocab=32000, d=768, heads=12, ffn=3072, layers=12, seed=1234, device="cuda",
                  compute_dtype=torch.float32):
@@ -265,10 +265,11 @@ class TransformerLM(nn.Module):
 
             return A.glue(qkv, fwd, bwd)
 
-        q, k, v = split(0, 1.0 / math.sqrt(hd)), split(1, 1.0), split(2, 1.0)
+        q, k, v = split(0, 1.0), split(1, 1.0), split(2, 1.0)
         scores = A.bmm(q, k, trans_b=True)                        # (B*h, T, T)
-        scores = A.glue(scores, lambda t: t + mask, lambda g: g)  # causal additive mask
-        ctx = A.bmm(A.softmax_rows(scores), v)                    # (B*h, T, hd)
+        # scale 1/sqrt(head dim) and the causal mask are folded into the softmax kernel
+        probs = A.softmax_rows(scores, 1.0 / math.sqrt(hd), causal_period=T)
+        ctx = A.bmm(probs, v)                                     # (B*h, T, hd)
         merged = A.glue(
             ctx, lambda t: t.reshape(B, h, T, hd).permute(0, 2, 1, 3).reshape(B * T, d).contiguous(),
             lambda g: g.reshape(B, T, h, hd).permute(0, 2, 1, 3).reshape(B * h, T, hd).contiguous())
@@ -278,8 +279,7 @@ class TransformerLM(nn.Module):
         """ids (B, T) token ids; targets (B*T,) next-token labels."""
         B, T = ids.shape
         x = A.embedding(A.cast(self.embed, self.compute_dtype), ids)  # (B*T, d)
-        mask = torch.full((T, T), float("-inf"), device=x.tensor.device,
-                          dtype=self.compute_dtype).triu(1)
+        mask = None
         for blk in self.blocks:
             x = A.add(x, self._attention(self._ln(x, blk["ln1"]), blk, B, T, mask))
             h = A.gelu(self._lin(blk["w1"], self._ln(x, blk["ln2"])))

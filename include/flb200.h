@@ -326,6 +326,17 @@ int flb200_embedding_backward(const void* grad_out, const void* ids, int ids_dty
                               float* grad_table, int64_t rows, int64_t dim, int64_t vocab,
                               int dtype, void* stream);
 
+/* softmax over fl dim 0 (Functions.cpp:1021-1042) of attention scores, with the score scale and
+ * the causal mask of flashlight/fl/contrib/modules/Transformer.cpp:112-119 folded in:
+ * x, y [cols, rows]; y = softmax(scale * x + mask), where with causal_period = T > 0 the rows
+ * are T x cols matrices stacked along rows and column c of row r is masked (-inf) when
+ * c > r mod T; causal_period = 0: no mask.  cols <= 2048.
+ * Gradient: grad_x = scale * y * (grad_y - sum_c grad_y * y). */
+int flb200_softmax_forward(const void* x, void* y, int64_t cols, int64_t rows, float scale,
+                           int64_t causal_period, int dtype, void* stream);
+int flb200_softmax_backward(const void* y, const void* grad_y, void* grad_x, int64_t cols,
+                            int64_t rows, float scale, int dtype, void* stream);
+
 /* logSoftmax over fl dim 0: x, y [C, X] column-major (Functions.cpp:1044-1070). */
 int flb200_log_softmax_forward(const void* x, void* y, int64_t C, int64_t X, int dtype,
                                void* stream);

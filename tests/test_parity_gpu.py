@@ -458,3 +458,33 @@ def test_embedding(fx, case):
     assert got.dtype == torch.float32 and torch.equal(got, again)
     want = torch.zeros(vocab, dim, dtype=torch.float64).index_add_(0, ids.long(), gy.double())
     assert_close(got, want, 1e-5, "embedding gradient")
+
+
+@pytest.mark.parametrize("case", [
+    (24, 24, 3, True, torch.float32),      # toy attention block, causal
+    (512, 512, 2, True, torch.float32),    # the transformer workload's row length
+    (100, 37, 1, False, torch.float32),    # ragged, no mask
+    (1500, 64, 1, False, torch.float32),   # > 1024 columns
+    (128, 128, 2, True, torch.bfloat16),
+])
+def test_attention_softmax(fx, case):
+    """Scaled softmax with the causal mask folded in, and its gradient, against fp64."""
+    cols, T, nmat, causal, dtype = case
+    rows = T * nmat
+    x = randn(rows, cols, seed=81).to(dtype)
+    gy = randn(rows, cols, seed=82).to(dtype)
+    scale = 0.37
+    z = x.double() * scale
+    if causal:
+        r = torch.arange(rows).remainder(T)[:, None]
+        z = z.masked_fill(torch.arange(cols)[None, :] > r, float("-inf"))
+    want = torch.softmax(z, -1)
+    y = fx.softmax(x.cuda(), scale, T if causal else 0)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert_close(y.float(), want, tol, "softmax")
+    if causal:
+        assert float(y.float().cpu().masked_select(torch.arange(cols)[None, :] > r).abs().max()) == 0.0
+    yd = y.double().cpu()
+    want_dx = scale * yd * (gy.double() - (gy.double() * yd).sum(-1, keepdim=True))
+    dx = fx.softmax_backward(y, gy.cuda(), scale)
+    assert_close(dx.float(), want_dx, tol, "softmax gradient")
