@@ -288,7 +288,7 @@ def run_gpu_arm(args) -> None:
         D.distributedInit("nccl")
     dev = torch.device("cuda", local)
 
-    math_mode = L.MATH_TF32 if args.math == "tf32" else L.MATH_STRICT_F32
+    math_mode = L.MATH_BY_NAME[args.math]
     A.set_math_mode(math_mode)
     model = workloads.resnet50(seed=1234, device=dev)
     reducer = None
@@ -384,7 +384,7 @@ def run_gpu_arm(args) -> None:
     tv = groups[top]
     if top == CONV_KERNEL or top in TENSOR_OPS:
         achieved = tv["flops"] / (tv["ms"] * 1e-3) / 1e12
-        if math_mode == L.MATH_TF32:
+        if math_mode != L.MATH_STRICT_F32:
             # TF32 has half the tensor rate of bf16; the measured bf16 cuBLAS figure is the
             # only driver-measured tensor number, so the TF32 peak is taken as half of it.
             peak = peaks["bf16_tflops_sustained"] / 2
@@ -427,7 +427,8 @@ def run_gpu_arm(args) -> None:
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None,
-        "dtype": "tf32" if math_mode == L.MATH_TF32 else "f32", "data": "synthetic",
+        "dtype": {L.MATH_TF32: "tf32", L.MATH_F32X3: "f32 (3xTF32 tensor-core products)"}.get(
+            math_mode, "f32"), "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch_per_gpu": B, "global_batch": B * world,
                    "parallelism": f"dp{world}", "math_mode": args.math,
                    "l2": "inputs and activations larger than L2 (no flush needed)",
@@ -450,7 +451,7 @@ def main() -> None:
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
-    ap.add_argument("--math", default=os.environ.get("FLB200_MATH", "tf32"), choices=["tf32", "strict"])
+    ap.add_argument("--math", default=os.environ.get("FLB200_MATH", "tf32"), choices=["tf32", "strict", "f32x3"])
     ap.add_argument("--bucket-mb", type=int, default=32)
     ap.add_argument("--cpu-batch", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")

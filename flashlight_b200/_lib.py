@@ -16,7 +16,8 @@ OK, INVALID_ARG, UNSUPPORTED, LAUNCH_FAILURE, TIMEOUT, WORKSPACE_TOO_SMALL = ran
 F32, F16, BF16 = 0, 1, 2
 POOL_MAX, POOL_AVG_INCLUDE_PAD, POOL_AVG_EXCLUDE_PAD = 0, 1, 2
 RNN_RELU, RNN_TANH, RNN_LSTM, RNN_GRU = 0, 1, 2, 3
-MATH_STRICT_F32, MATH_TF32 = 0, 1
+MATH_STRICT_F32, MATH_TF32, MATH_F32X3 = 0, 1, 2
+MATH_BY_NAME = {"strict": MATH_STRICT_F32, "tf32": MATH_TF32, "f32x3": MATH_F32X3}
 REDUCE_NONE, REDUCE_MEAN, REDUCE_SUM = 0, 1, 2
 IDS_I32, IDS_I64 = 0, 1
 

@@ -16,6 +16,7 @@
 // fall through to the fp32 kernel.
 #include "simt_gemm.cuh"
 #include "tc_conv.cuh"
+#include "tc_gemm.cuh"
 
 namespace flb200 {
 
@@ -29,7 +30,7 @@ int make_conv_geo(const char* name, const flb200_conv2d_desc* d, ConvGeo* g) {
                  "%s: channels (%d in, %d out) not divisible by groups (%d)", name, d->C, d->Cout,
                  d->groups);
   FLB200_REQUIRE(d->dtype == FLB200_F32, "%s: only f32 is built (dtype %d)", name, d->dtype);
-  FLB200_REQUIRE(d->math_mode == FLB200_MATH_STRICT_F32 || d->math_mode == FLB200_MATH_TF32,
+  FLB200_REQUIRE(d->math_mode >= FLB200_MATH_STRICT_F32 && d->math_mode <= FLB200_MATH_F32X3,
                  "%s: unknown math mode %d", name, d->math_mode);
   const int ekw = 1 + (d->kW - 1) * d->dx, ekh = 1 + (d->kH - 1) * d->dy;
   FLB200_REQUIRE(d->W + 2 * d->px >= ekw && d->H + 2 * d->py >= ekh,
@@ -257,7 +258,7 @@ size_t flb200_conv2d_workspace_bytes(const flb200_conv2d_desc* d, int which) {
                .workspace_bytes;
     need = max_sz(need, flb200_channel_sum_workspace_bytes(g.N, g.Cout, g.HoWo));
   }
-  if (d->math_mode == FLB200_MATH_TF32) need = max_sz(need, tc_conv_workspace_bytes(g, which));
+  if (d->math_mode != FLB200_MATH_STRICT_F32) need = max_sz(need, tc_conv_workspace_bytes(g, which));
   return need;
 }
 
@@ -271,7 +272,7 @@ int flb200_conv2d_forward(const flb200_conv2d_desc* d, const void* x, const void
 size_t flb200_conv2d_cache_bytes(const flb200_conv2d_desc* d, int which) {
   ConvGeo g;
   if (make_conv_geo("conv2d_cache_bytes", d, &g)) return 0;
-  if (d->math_mode != FLB200_MATH_TF32 || which < 0 || which > 1) return 0;
+  if (d->math_mode == FLB200_MATH_STRICT_F32 || which < 0 || which > 1) return 0;
   return tc_conv_cache_bytes(g, which);
 }
 
@@ -287,7 +288,8 @@ int flb200_conv2d_forward_cached(const flb200_conv2d_desc* d, const void* x, con
   const float* wf = static_cast<const float*>(w);
   const float* bf = static_cast<const float*>(bias);
   float* yf = static_cast<float*>(y);
-  if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 0, workspace_bytes))
+  tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
+  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_conv_supported(g, 0, workspace_bytes))
     return tc_conv_forward(g, xf, wf, bf, yf, workspace, workspace_bytes, st, cache);
   const long long n_total = (long long)g.N * g.HoWo;
   FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_forward: too many output pixels");
@@ -317,7 +319,8 @@ int flb200_conv2d_backward_data_cached(const flb200_conv2d_desc* d, const void* 
   const float* gyf = static_cast<const float*>(grad_y);
   const float* wf = static_cast<const float*>(w);
   float* gxf = static_cast<float*>(grad_x);
-  if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 1, workspace_bytes))
+  tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
+  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_conv_supported(g, 1, workspace_bytes))
     return tc_conv_backward_data(g, gyf, wf, gxf, workspace, workspace_bytes, st, cache);
   const long long n_total = (long long)g.N * g.HW;
   FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_backward_data: too many input pixels");
@@ -347,7 +350,8 @@ int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const
   const float* xf = static_cast<const float*>(x);
   float* gwf = static_cast<float*>(grad_w);
   int rc;
-  if (d->math_mode == FLB200_MATH_TF32 && tc_conv_supported(g, 2, workspace_bytes)) {
+  tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
+  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_conv_supported(g, 2, workspace_bytes)) {
     rc = tc_conv_backward_filter(g, gyf, xf, gwf, workspace, workspace_bytes, st, cache);
   } else {
     const int n_total = g.Cg * g.RS;

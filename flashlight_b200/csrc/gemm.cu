@@ -34,7 +34,7 @@ int check_desc(const flb200_matmul_desc* d, const void* a, const void* b, const 
   FLB200_REQUIRE(d->m >= 0 && d->n >= 0 && d->k >= 0 && d->batch >= 1, "matmul: negative extent");
   FLB200_REQUIRE(d->dtype == FLB200_F32 || d->dtype == FLB200_BF16,
                  "matmul: f32 and bf16 are built (dtype %d)", d->dtype);
-  FLB200_REQUIRE(d->math_mode == FLB200_MATH_STRICT_F32 || d->math_mode == FLB200_MATH_TF32,
+  FLB200_REQUIRE(d->math_mode >= FLB200_MATH_STRICT_F32 && d->math_mode <= FLB200_MATH_F32X3,
                  "matmul: unknown math mode %d", d->math_mode);
   FLB200_REQUIRE((a && b && c) || d->m == 0 || d->n == 0, "matmul: null matrix");
   return FLB200_OK;
@@ -54,7 +54,8 @@ int run_matmul(const flb200_matmul_desc* d, const void* a, const void* b, void* 
                   "with one unit stride each)");
     return tc_gemm_run(d, a, b, c, ws, ws_bytes, st);
   }
-  if (d->math_mode == FLB200_MATH_TF32 && tc_gemm_supported(d, a, b, c))
+  tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
+  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_gemm_supported(d, a, b, c))
     return tc_gemm_run(d, a, b, c, ws, ws_bytes, st);
   return matmul_simt(d, a, b, c, ws, ws_bytes, st);
 }

@@ -243,7 +243,7 @@ int filter_map(CUtensorMap* m, const float* base, int kext, int kp, int rows, in
 
 // CTA pairs (tc_pair.cuh) for 256-column tiles: each CTA then loads half of the filter tile.
 // Measured on the ResNet-50 step: about 1 % of the step; no gain at 128 columns.
-bool patch_uses_pairs(int bn) { return bn >= 256; }
+bool patch_uses_pairs(int bn) { return bn >= 256 && !tc::x3_enabled(); }
 
 // Fills the parts of the problem that do not depend on BN and launches with the BN that fits
 // the number of output channels.  The filter map must have been made with
@@ -278,6 +278,7 @@ int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, 
   const long long m_tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b;
   FLB200_REQUIRE(m_tiles * p.tiles_n < 0x7fffffffLL, "patch conv: too many tiles");
   if constexpr (BN >= 256) {
+    if (patch_uses_pairs(BN))
     return tc::launch_pair_problem<tc::PatchConvProblem<BN>, BN>(
         "tc_patch_conv_pair", ma, mb, p, ((m_tiles + 1) / 2) * p.tiles_n, st);
   }

@@ -64,6 +64,13 @@ int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t
   return FLB200_OK;
 }
 
+namespace {
+thread_local bool t_x3 = false;
+}
+bool x3_enabled() { return t_x3; }
+X3Scope::X3Scope(bool on) : prev(t_x3) { t_x3 = on; }
+X3Scope::~X3Scope() { t_x3 = prev; }
+
 std::atomic<long long> g_tc_launches{0};
 void count_tc_launch() { g_tc_launches.fetch_add(1, std::memory_order_relaxed); }
 
@@ -134,7 +141,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const Opera
   const long long tiles = (long long)p.tiles_m * p.tiles_n * Z * L.splits;
   FLB200_REQUIRE(tiles < 0x7fffffffLL, "tc_gemm: too many tiles");
   if constexpr (BN >= 128) {
-    if (!bf16 && gemm_uses_pairs(M, N, k_iters, pa.mn_major != 0, pb.mn_major != 0)) {
+    if (!bf16 && !x3_enabled() &&
+        gemm_uses_pairs(M, N, k_iters, pa.mn_major != 0, pb.mn_major != 0)) {
       const long long pair_tiles = (long long)((p.tiles_m + 1) / 2) * p.tiles_n * Z * L.splits;
       return launch_pair_problem<GemmProblem<BN>, BN>("tc_gemm_pair", ma, mb, p, pair_tiles, st);
     }
@@ -153,6 +161,7 @@ int pick_bn(long long N) {
 
 bool gemm_uses_pairs(long long M, long long N, long long k_iters, bool a_mn_major,
                      bool b_mn_major) {
+  if (x3_enabled()) return false;  // the CTA-pair kernel has no 3xTF32 instantiation
   return pick_bn(N) >= 128 && M > kBM && !a_mn_major && !b_mn_major && k_iters >= 64;
 }
 int b_box_rows(long long M, long long N, long long k_iters, bool a_mn_major, bool b_mn_major) {

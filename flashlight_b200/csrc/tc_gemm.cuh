@@ -97,6 +97,15 @@ int make_tensor_map(CUtensorMap* map, const void* base, int rank, const uint64_t
                     const uint64_t* strides_bytes, const uint32_t* box, int mode,
                     const uint32_t* elem_strides = nullptr, bool bf16 = false);
 
+// 3xTF32 ("fp32-grade") mode of the current host thread: set by the C entry points around a
+// call (X3Scope), read where kernels are launched.
+bool x3_enabled();
+struct X3Scope {
+  explicit X3Scope(bool on);
+  ~X3Scope();
+  bool prev;
+};
+
 // Address of the device flag that bounded waits raise (per device), and the launch counter.
 int* status_ptr();
 void count_tc_launch();

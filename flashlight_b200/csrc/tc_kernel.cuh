@@ -11,6 +11,9 @@
 //              coordinates advance incrementally.
 //   warp 1   : allocates TMEM (2 accumulators of BN columns); one lane issues tcgen05.mma
 //              for each ready stage and tcgen05.commit to free the stage / publish the tile
+//   warps 6-9: only in the 3xTF32 instantiation (fp32-grade products): split every landed
+//              operand element into a TF32-exact high part and the remainder, so that the MMA
+//              warp can issue a_lo*b_hi + a_hi*b_lo + a_hi*b_hi
 //   warps 2-5: epilogue — tcgen05.ld the finished accumulator (32 lanes each) and store it
 //              from registers (coalesced 128-byte rows when the row index is contiguous in
 //              memory, 16-byte vectors when the column index is) while the MMA warp already
@@ -41,11 +44,13 @@
 namespace flb200 {
 namespace tc {
 
-template <int BN, int STAGES>
+// X3 = 1: every stage also holds the low-order tiles of the 3xTF32 split (see the kernel).
+template <int BN, int STAGES, int X3 = 0>
 struct SmemLayout {
   static constexpr int kABytes = kBM * kBK * 4;  // 16 KB
   static constexpr int kBBytes = BN * kBK * 4;
-  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kLoOffset = kABytes + kBBytes;  // low-order A tile, then low-order B tile
+  static constexpr int kStageBytes = (X3 ? 2 : 1) * (kABytes + kBBytes);
   static constexpr int kTileBytes = STAGES * kStageBytes;
   static constexpr int kBarBytes = 512;
   static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // + slack to align to 1024
@@ -53,16 +58,18 @@ struct SmemLayout {
 
 // ~200 KB of tiles per CTA
 constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : (bn >= 64 ? 8 : 10)); }
+constexpr int stages_for_x3(int bn) { return bn >= 256 ? 2 : (bn >= 128 ? 3 : (bn >= 64 ? 4 : 5)); }
+constexpr int kThreadsX3 = kThreads + 128;  // four more warps split the operands
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <class P, int BN, int STAGES>
-__global__ void __launch_bounds__(kThreads)
+template <class P, int BN, int STAGES, int X3 = 0>
+__global__ void __launch_bounds__(X3 ? kThreadsX3 : kThreads)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
-  using SL = SmemLayout<BN, STAGES>;
+  using SL = SmemLayout<BN, STAGES, X3>;
   extern __shared__ char smem_raw[];
   char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                         ~static_cast<uintptr_t>(1023));
@@ -70,7 +77,8 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* tfull_bar = empty_bar + STAGES;   // [2] accumulator ready for the epilogue
   uint64_t* tempty_bar = tfull_bar + 2;       // [2] accumulator drained, MMA may overwrite
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+  uint64_t* split_bar = tempty_bar + 2;       // [STAGES] X3: low-order tiles of the stage written
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(split_bar + STAGES);
   volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -81,6 +89,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
+      mbar_init(&split_bar[s], 4);  // one arrival per splitting warp
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
@@ -167,13 +176,36 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int k0 = prob.k_begin(t), k1 = prob.k_end(t);
         for (int k = k0; k < k1; ++k) {
-          if (!mbar_wait(&full_bar[s], round & 1)) {
+          if (!mbar_wait(X3 ? &split_bar[s] : &full_bar[s], round & 1)) {
             *failed = 2;
             break;
           }
           tc_fence_after();
           const uint32_t a_addr = smem_u32(tiles + s * SL::kStageBytes);
           const uint32_t b_addr = a_addr + SL::kABytes;
+          if constexpr (X3 != 0) {
+            // a * b ~ a_hi * b_hi + a_lo * b_hi + a_hi * b_lo with x = x_hi + x_lo, x_hi exact
+            // in TF32: fp32-grade products out of three tensor-core passes
+            const uint32_t al_addr = a_addr + SL::kLoOffset;
+            const uint32_t bl_addr = al_addr + SL::kABytes;
+#pragma unroll
+            for (int j = 0; j < kBK / kUmmaK; ++j) {
+              const uint32_t ao = prob.a_mn_major ? j * mn_step : j * 32;
+              const uint32_t bo = prob.b_mn_major ? j * mn_step : j * 32;
+              auto desc = [&](uint32_t addr, bool mn) {
+                return mn ? umma_desc(addr, mn_lbo, mn_sbo, mn_layout) : umma_desc(addr, 16, 1024, 2);
+              };
+              const uint64_t ah = desc(a_addr + ao, prob.a_mn_major);
+              const uint64_t bh = desc(b_addr + bo, prob.b_mn_major);
+              umma_tf32(d_tmem, desc(al_addr + ao, prob.a_mn_major), bh, idesc,
+                        (k > k0 || j > 0) ? 1u : 0u);
+              umma_tf32(d_tmem, ah, desc(bl_addr + bo, prob.b_mn_major), idesc, 1u);
+              umma_tf32(d_tmem, ah, bh, idesc, 1u);
+            }
+            umma_commit(&empty_bar[s]);
+            if (++s == STAGES) { s = 0; ++round; }
+            continue;
+          }
 #pragma unroll
           for (int j = 0; j < kBK / kUmmaK; ++j) {
             // K-major: step 8 elements = 32 bytes inside the swizzled row;
@@ -191,6 +223,44 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
           if (++s == STAGES) { s = 0; ++round; }
         }
         umma_commit(&tfull_bar[acc]);  // accumulator complete
+      }
+    }
+  } else if (X3 != 0 && warp >= 6) {
+    // splitting warps (X3 only): once a stage has landed, rewrite every operand element x in
+    // place as x_hi (low 13 mantissa bits cleared: exact in TF32 however the tensor core
+    // converts) and write x_lo = x - x_hi at the same offset of the stage's low-order tiles;
+    // elementwise at equal offsets, so the swizzled layout carries over unchanged.
+    const int t128 = threadIdx.x - 6 * 32;
+    uint32_t s = 0, round = 0;
+    typename P::Tile t;
+    bool live = true;
+    for (int tile = blockIdx.x; live && tile < n_tiles; tile += gridDim.x) {
+      prob.decode(tile, t);
+      const int k0 = prob.k_begin(t), k1 = prob.k_end(t);
+      for (int k = k0; k < k1; ++k) {
+        if (*failed != 0 || !mbar_wait(&full_bar[s], round & 1)) {
+          if (*failed == 0) *failed = 5;
+          live = false;
+          break;
+        }
+        float4* hi = reinterpret_cast<float4*>(tiles + s * SL::kStageBytes);
+        float4* lo = reinterpret_cast<float4*>(tiles + s * SL::kStageBytes + SL::kLoOffset);
+        constexpr int kVec = SL::kLoOffset / 16;
+#pragma unroll 4
+        for (int i = t128; i < kVec; i += 128) {
+          const float4 v = hi[i];
+          float4 h;
+          h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u);
+          h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u);
+          h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u);
+          h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u);
+          hi[i] = h;
+          lo[i] = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+        }
+        fence_proxy_async();  // these generic-proxy writes are read by the tensor core next
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&split_bar[s]);
+        if (++s == STAGES) { s = 0; ++round; }
       }
     }
   } else {
@@ -419,28 +489,35 @@ struct GemmProblem {
 
 // ------------------------------------------------------------- host launch
 // Launches the persistent kernel for problem P: one CTA per SM (fewer when there are fewer tiles).
-template <class P, int BN>
-int launch_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& mb, const P& prob,
-                   long long tiles, cudaStream_t st) {
-  constexpr int STAGES = stages_for(BN);
-  using SL = SmemLayout<BN, STAGES>;
-  if (tiles <= 0) return FLB200_OK;
+template <class P, int BN, int STAGES, int X3>
+int launch_problem_as(const char* name, const CUtensorMap& ma, const CUtensorMap& mb, const P& prob,
+                      long long tiles, cudaStream_t st) {
+  using SL = SmemLayout<BN, STAGES, X3>;
   static bool configured[64] = {false};
   int dev = 0;
   FLB200_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_persistent_kernel<P, BN, STAGES>,
+    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_persistent_kernel<P, BN, STAGES, X3>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            SL::kTotal));
     configured[dev] = true;
   }
   const long long sms = device_info().sm_count;
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  tc_persistent_kernel<P, BN, STAGES><<<grid, kThreads, SL::kTotal, st>>>(ma, mb, prob,
-                                                                          status_ptr());
+  tc_persistent_kernel<P, BN, STAGES, X3><<<grid, X3 ? kThreadsX3 : kThreads, SL::kTotal, st>>>(
+      ma, mb, prob, status_ptr());
   FLB200_AFTER_LAUNCH(name);
   count_tc_launch();
   return FLB200_OK;
+}
+
+template <class P, int BN>
+int launch_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& mb, const P& prob,
+                   long long tiles, cudaStream_t st) {
+  if (tiles <= 0) return FLB200_OK;
+  if (x3_enabled())
+    return launch_problem_as<P, BN, stages_for_x3(BN), 1>(name, ma, mb, prob, tiles, st);
+  return launch_problem_as<P, BN, stages_for(BN), 0>(name, ma, mb, prob, tiles, st);
 }
 
 }  // namespace tc

@@ -136,6 +136,8 @@ def _shape4(t: torch.Tensor):
 
 def default_math_mode() -> int:
     """FLB200_TF32=1 selects the tensor-core (TF32) kernels, FLB200_TF32=0 strict fp32."""
+    if os.environ.get("FLB200_MATH", "") in L.MATH_BY_NAME:  # strict | tf32 | f32x3
+        return L.MATH_BY_NAME[os.environ["FLB200_MATH"]]
     return L.MATH_TF32 if os.environ.get("FLB200_TF32", "0") not in ("0", "", "false") else L.MATH_STRICT_F32
 
 

@@ -120,7 +120,7 @@ def bench_bias_grad(shape, iters):
 
 def bench_conv(op, conv, iters, math):
     N, Cin, H, W, Cout, k, s, p = conv
-    mode = L.MATH_TF32 if math == "tf32" else L.MATH_STRICT_F32
+    mode = L.MATH_BY_NAME.get(math, L.MATH_TF32)
     ext = B200AutogradExtension(mode)
     x = torch.randn(N, Cin, H, W, device="cuda")
     w = torch.randn(Cout, Cin, k, k, device="cuda") * (1.0 / (Cin * k * k) ** 0.5)
@@ -196,7 +196,7 @@ def suite_resnet50_step_convs(batch, math):
     the autograd tape (forward, backward-data, backward-filter sharing one payload) and with
     nothing else on the device: the command to put under a profiler when the per-step DRAM
     traffic of the convolution kernels is wanted at the full batch size."""
-    mode = L.MATH_TF32 if math == "tf32" else L.MATH_STRICT_F32
+    mode = L.MATH_BY_NAME.get(math, L.MATH_TF32)
     ext = B200AutogradExtension(mode)
     flops = 0.0
     algo_bytes = 0
@@ -247,7 +247,7 @@ def suite_workloads(iters, math, which):
     channels T=1000 batch 16, 3-layer bidirectional LSTM H=1024 T=500 batch 32."""
     from . import autograd as A
     from . import workloads
-    A.set_math_mode(L.MATH_STRICT_F32 if math == "strict" else L.MATH_TF32)
+    A.set_math_mode(L.MATH_BY_NAME.get(math, L.MATH_TF32))
     g = torch.Generator().manual_seed(1234)
 
     def run(name, model, x, t, units, unit):
@@ -294,7 +294,7 @@ def main():
     ap.add_argument("--conv", default="64,64,56,56,64,3,1,1")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--math", default="strict", choices=["strict", "tf32", "bf16"],
+    ap.add_argument("--math", default="strict", choices=["strict", "tf32", "f32x3", "bf16"],
                     help="bf16 only applies to the transformer workload")
     a = ap.parse_args()
     if not torch.cuda.is_available():

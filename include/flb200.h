@@ -46,7 +46,12 @@ enum { FLB200_RNN_RELU = 0, FLB200_RNN_TANH = 1, FLB200_RNN_LSTM = 2, FLB200_RNN
  * STRICT = fp32 FMA everywhere (meets 1e-4 parity); TF32 = tcgen05 kind::tf32
  * with fp32 accumulation in tensor memory where a tensor-core kernel exists for
  * the shape, fp32 FMA otherwise. */
-enum { FLB200_MATH_STRICT_F32 = 0, FLB200_MATH_TF32 = 1 };
+/* STRICT_F32: fp32 FMA kernels.  TF32: tensor cores, operands read with a 10-bit mantissa.
+ * F32X3: tensor cores with every operand split into a TF32-exact high part and the remainder
+ * and three passes per product (a_lo*b_hi + a_hi*b_lo + a_hi*b_hi): products carry about 21
+ * mantissa bits, fp32 accumulation in tensor memory: errors of a few 1e-6 of the result's scale
+ * (TF32: ~1e-3), at about two thirds of the TF32 speed on a ResNet-50 step. */
+enum { FLB200_MATH_STRICT_F32 = 0, FLB200_MATH_TF32 = 1, FLB200_MATH_F32X3 = 2 };
 
 /* fl::ReduceMode (flashlight/fl/autograd/Functions.h) */
 enum { FLB200_REDUCE_NONE = 0, FLB200_REDUCE_MEAN = 1, FLB200_REDUCE_SUM = 2 };
