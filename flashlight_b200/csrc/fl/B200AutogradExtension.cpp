@@ -179,6 +179,17 @@ B200AutogradExtension::B200AutogradExtension() : mathMode_(FLB200_MATH_STRICT_F3
   if (env && env[0] != '\0' && env[0] != '0') {
     mathMode_ = FLB200_MATH_TF32;
   }
+  // FLB200_MATH=strict|tf32|f32x3 names the mode and wins over FLB200_TF32
+  if (const char* name = std::getenv("FLB200_MATH")) {
+    const std::string mode(name);
+    if (mode == "strict") {
+      mathMode_ = FLB200_MATH_STRICT_F32;
+    } else if (mode == "tf32") {
+      mathMode_ = FLB200_MATH_TF32;
+    } else if (mode == "f32x3") {
+      mathMode_ = FLB200_MATH_F32X3;
+    }
+  }
 }
 
 const CUDAStream& B200AutogradExtension::stream() {

@@ -81,7 +81,8 @@ class B200AutogradExtension final : public AutogradExtension {
       std::shared_ptr<detail::AutogradPayload> payload) override;
 
  private:
-  // FLB200_MATH_STRICT_F32 or FLB200_MATH_TF32 (environment variable FLB200_TF32, read once)
+  // FLB200_MATH_STRICT_F32, _TF32 or _F32X3 (environment FLB200_MATH=strict|tf32|f32x3, or
+  // FLB200_TF32=1; read once)
   int mathMode_;
   // the stream the kernels run on; ordered against the tensors' streams around every call
   std::shared_ptr<CUDAStream> stream_;
