@@ -27,6 +27,9 @@ NVCC_FLAGS = [
     "--expt-relaxed-constexpr",
     "-DFLB200_BUILDING=1",
 ]
+# Extra nvcc flags for one-off builds, e.g. FLB200_NVCC_EXTRA=-DFLB200_TC_PROFILE (per-role
+# stall accounting of the tensor-core kernel, printed to stderr after every launch).
+NVCC_FLAGS += os.environ.get("FLB200_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:

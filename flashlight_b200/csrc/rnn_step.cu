@@ -97,18 +97,18 @@ lstm_step_kernel(const __grid_constant__ CUtensorMap map_w,
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_tf32(32, 0, 0);
+      const uint64_t a_desc0 = umma_desc(smem_u32(a_tiles), 16, 1024, 2);
+      const uint64_t b_desc0 = umma_desc(smem_u32(b_tiles), 16, 1024, 2);
       for (int s = 0; s < kStagesK; ++s) {
         if (!mbar_wait(&full_bar[s], 0)) {
           *failed = 1;
           break;
         }
         tc_fence_after();
-        const uint32_t a_addr = smem_u32(a_tiles + s * kABytes);
-        const uint32_t b_addr = smem_u32(b_tiles + s * kBBytes);
 #pragma unroll
         for (int j = 0; j < kBK / kUmmaK; ++j)
-          umma_tf32(tmem_base, umma_desc(a_addr + j * 32, 16, 1024, 2),
-                    umma_desc(b_addr + j * 32, 16, 1024, 2), idesc, (s | j) ? 1u : 0u);
+          umma_tf32(tmem_base, umma_desc_advance(a_desc0, s * kABytes + j * 32),
+                    umma_desc_advance(b_desc0, s * kBBytes + j * 32), idesc, (s | j) ? 1u : 0u);
       }
       umma_commit(done_bar);  // arrives when every MMA issued above (possibly none) is done
     }

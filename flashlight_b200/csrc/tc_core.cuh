@@ -41,6 +41,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                "r"(bytes)
                : "memory");
 }
+// Adds to the barrier's pending byte count without arriving; the phase cannot complete before
+// the arrival that follows.
+__device__ __forceinline__ void mbar_expect_tx_only(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+// Byte count of one sub-block of a stage: the last sub-block of the stage also arrives.
+__device__ __forceinline__ void mbar_post_tx(uint64_t* bar, uint32_t bytes, bool last) {
+  if (last) mbar_expect_tx(bar, bytes);
+  else mbar_expect_tx_only(bar, bytes);
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -195,6 +207,17 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= (uint64_t)1 << 46;  // descriptor version for sm_100
   d |= (uint64_t)layout_type << 61;  // 2 = SWIZZLE_128B, 1 = SWIZZLE_128B_BASE32B
   return d;
+}
+// The descriptor of the same layout `bytes` further into shared memory.  The start-address
+// field is the low 14 bits (address / 16); any address inside the CTA's shared memory fits, so
+// the addition never carries into the neighbouring field and touches the low word only.
+// Building a descriptor from scratch costs the single issuing thread tens of dependent
+// instructions; measured, an MMA loop that rebuilds both descriptors per instruction issues one
+// tcgen05.mma per ~220 clocks, one that offsets two prebuilt descriptors one per ~50 clocks
+// (the shared-memory read time of a 128 x 64 x 8 TF32 MMA).
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t desc, uint32_t bytes) {
+  const uint32_t lo = (uint32_t)desc + (bytes >> 4);
+  return (desc & 0xffffffff00000000ull) | lo;
 }
 // Instruction descriptor for kind::tf32, fp32 accumulate, M = 128.
 __host__ __device__ inline uint32_t umma_idesc_tf32(int n, int a_mn_major, int b_mn_major) {

@@ -138,6 +138,14 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   } else if (warp == 1) {
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc_tf32_pair(BN, prob.a_mn_major, prob.b_mn_major);
+      // descriptors of the ring's first stage; every MMA offsets them
+      const uint32_t ring = smem_u32(tiles);
+      const uint64_t a_desc0 = prob.a_mn_major ? umma_desc(ring, kBK * 128, 512, 1)
+                                               : umma_desc(ring, 16, 1024, 2);
+      const uint64_t b_desc0 = prob.b_mn_major
+                                   ? umma_desc(ring + SL::kABytes, kBK * 128, 512, 1)
+                                   : umma_desc(ring + SL::kABytes, 16, 1024, 2);
+      const uint32_t a_jstep = prob.a_mn_major ? 1024 : 32, b_jstep = prob.b_mn_major ? 1024 : 32;
       uint32_t s = 0, round = 0, nt = 0;
       typename P::Tile t;
       for (int tile = pair; tile < n_tiles && *failed == 0; tile += n_pairs, ++nt) {
@@ -156,16 +164,11 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(tiles + s * SL::kStageBytes);
-          const uint32_t b_addr = a_addr + SL::kABytes;
+          const uint32_t off = s * SL::kStageBytes;
 #pragma unroll
           for (int j = 0; j < kBK / kUmmaK; ++j) {
-            const uint64_t ad = prob.a_mn_major
-                                    ? umma_desc(a_addr + j * 1024, kBK * 128, 512, 1)
-                                    : umma_desc(a_addr + j * 32, 16, 1024, 2);
-            const uint64_t bd = prob.b_mn_major
-                                    ? umma_desc(b_addr + j * 1024, kBK * 128, 512, 1)
-                                    : umma_desc(b_addr + j * 32, 16, 1024, 2);
+            const uint64_t ad = umma_desc_advance(a_desc0, off + j * a_jstep);
+            const uint64_t bd = umma_desc_advance(b_desc0, off + j * b_jstep);
             umma_tf32_pair(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
           }
           umma_commit_pair(&empty_bar[s]);  // frees stage s in both CTAs

@@ -125,8 +125,8 @@ struct PatchConvProblem {
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst, int) const {
-    mbar_expect_tx(bar, (kBM + BN) * kBK * 4);  // NB*PH*QW == 128 rows of 128 bytes + B tile
+                                       char* b_dst, int, bool last) const {
+    mbar_post_tx(bar, (kBM + BN) * kBK * 4, last);  // NB*PH*QW == 128 rows of 128 bytes + B tile
     int ca[4] = {ls.cc * kBK, ls.aw, ls.ah, t.b0};
     tma_load(ma, bar, a_dst, 4, ca);
     int cb[4] = {ls.cc * kBK, t.n0, ls.wtap, 0};
@@ -236,14 +236,14 @@ struct PatchWgradProblem {
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst, int lane) const {
+                                       char* b_dst, int lane, bool last) const {
     const int q0 = ls.qi * QW, p0 = ls.pi * PH;
     // The channel index is split into (32 contiguous channels, group of 32) in both maps, so
     // one copy brings every 32 x 32 box of an operand: a_nbox boxes of dy, and per tap
     // 1 << cn_shift boxes of x.  Boxes past the last channel are zero-filled or hold a
     // neighbouring pixel's channels; they only reach accumulator rows / columns that the
     // epilogue never stores.
-    if (lane == 0) mbar_expect_tx(bar, (a_nbox + (t.ntap << cn_shift)) * (kBK * 128));
+    if (lane == 0) mbar_post_tx(bar, (a_nbox + (t.ntap << cn_shift)) * (kBK * 128), last);
     __syncwarp();
     if (lane == 0) {
       int ca[5] = {0, q0, p0, ls.img, t.m0 >> 5};
