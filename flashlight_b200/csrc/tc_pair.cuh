@@ -46,12 +46,15 @@ struct PairSmemLayout {
 };
 constexpr int pair_stages_for(int bn) { return bn >= 256 ? 6 : 8; }
 
-template <class P, int BN, int STAGES>
+template <class P, int BN, int STAGES, int KSUB = 2>
 __global__ void __launch_bounds__(kThreads)
 tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
   using SL = PairSmemLayout<BN, STAGES>;
   static_assert(BN >= 64 && BN % 64 == 0, "each CTA holds BN/2 columns in 32-column boxes");
+  // the ring's sub-stages change hands in groups of KSUB (see tc_kernel.cuh)
+  static_assert(STAGES % KSUB == 0, "ring must be whole groups");
+  constexpr int NG = STAGES / KSUB;
   extern __shared__ char smem_raw[];
   char* tiles = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                         ~static_cast<uintptr_t>(1023));
@@ -69,7 +72,7 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   const int n_tiles = prob.num_pair_tiles();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NG; ++s) {
       mbar_init(&full_bar[s], 1);   // leader: its own arrive.expect_tx for both CTAs' bytes
       mbar_init(&empty_bar[s], 1);  // one tcgen05.commit arrival
     }
@@ -94,6 +97,8 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     typename P::Tile t;
     typename P::LoadState ls;
     bool live = true;
+    TC_PROF_VAR(p_wait);
+    TC_PROF_NOW(p_t0);
     for (int tile = pair; live && tile < n_tiles; tile += n_pairs) {
       int stop = 0;
       if (lane == 0) stop = *failed;
@@ -104,30 +109,41 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       prob.decode_pair(tile, (int)rank, t);
       prob.load_begin(t, ls, lane);
       const int k1 = prob.k_end(t);
-      for (int k = prob.k_begin(t); k < k1; ++k) {
+      for (int k = prob.k_begin(t); k < k1; k += KSUB) {
+        const int kn = min(KSUB, k1 - k);
         int ok = 1;
+        TC_PROF_NOW(w0);
         if (lane == 0) {
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
             *failed = 1;
             ok = 0;
           } else if (rank == 0) {
-            mbar_expect_tx(&full_bar[s], 2 * SL::kStageBytes);
+            mbar_expect_tx(&full_bar[s], kn * 2 * SL::kStageBytes);
           }
         }
+        TC_PROF_ADD(p_wait, w0);
         if (__shfl_sync(0xffffffffu, ok, 0) == 0) {
           live = false;
           break;
         }
-        char* a_dst = tiles + s * SL::kStageBytes;
-        prob.load_pair(&map_a, &map_b, t, ls, mapa_u32(smem_u32(&full_bar[s]), 0), a_dst,
-                       a_dst + SL::kABytes, (int)rank, lane);
-        if (++s == STAGES) { s = 0; ++round; }
+        const uint32_t full_leader = mapa_u32(smem_u32(&full_bar[s]), 0);
+#pragma unroll
+        for (int sub = 0; sub < KSUB; ++sub) {
+          if (sub >= kn) break;
+          char* a_dst = tiles + (s * KSUB + sub) * SL::kStageBytes;
+          prob.load_pair(&map_a, &map_b, t, ls, full_leader, a_dst, a_dst + SL::kABytes,
+                         (int)rank, lane);
+        }
+        if (++s == NG) { s = 0; ++round; }
       }
     }
+#ifdef FLB200_TC_PROFILE
+    if (lane == 0) { TC_PROF_PUT(0, p_wait); TC_PROF_PUT(1, clock64() - p_t0); }
+#endif
     // The leader's last commits still arrive on this CTA's empty barriers: wait for them
     // so that the CTA does not leave while they are in flight.
     if (live && lane == 0 && *failed == 0) {
-      for (int i = 0; i < STAGES; ++i) {
+      for (int i = 0; i < NG; ++i) {
         const uint32_t fills = round + (static_cast<uint32_t>(i) < s ? 1u : 0u);
         if (fills > 0 && !mbar_wait(&empty_bar[i], (fills - 1) & 1)) {
           *failed = 1;
@@ -148,48 +164,69 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t a_jstep = prob.a_mn_major ? 1024 : 32, b_jstep = prob.b_mn_major ? 1024 : 32;
       uint32_t s = 0, round = 0, nt = 0;
       typename P::Tile t;
+      TC_PROF_VAR(m_full);
+      TC_PROF_VAR(m_acc);
+      TC_PROF_NOW(m_t0);
       for (int tile = pair; tile < n_tiles && *failed == 0; tile += n_pairs, ++nt) {
         prob.decode_pair(tile, 0, t);
         const uint32_t acc = nt & 1, around = nt >> 1;
+        TC_PROF_NOW(w0);
         if (around > 0 && !mbar_wait(&tempty_bar[acc], (around - 1) & 1)) {
           *failed = 4;
           break;
         }
+        TC_PROF_ADD(m_acc, w0);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int k0 = prob.k_begin(t), k1 = prob.k_end(t);
-        for (int k = k0; k < k1; ++k) {
+        for (int k = k0; k < k1; k += KSUB) {
+          const int kn = min(KSUB, k1 - k);
+          TC_PROF_NOW(w1);
           if (!mbar_wait(&full_bar[s], round & 1)) {
             *failed = 2;
             break;
           }
+          TC_PROF_ADD(m_full, w1);
           tc_fence_after();
-          const uint32_t off = s * SL::kStageBytes;
 #pragma unroll
-          for (int j = 0; j < kBK / kUmmaK; ++j) {
-            const uint64_t ad = umma_desc_advance(a_desc0, off + j * a_jstep);
-            const uint64_t bd = umma_desc_advance(b_desc0, off + j * b_jstep);
-            umma_tf32_pair(d_tmem, ad, bd, idesc, (k > k0 || j > 0) ? 1u : 0u);
+          for (int sub = 0; sub < KSUB; ++sub) {
+            if (sub >= kn) break;
+            const uint32_t off = (s * KSUB + sub) * SL::kStageBytes;
+#pragma unroll
+            for (int j = 0; j < kBK / kUmmaK; ++j) {
+              const uint64_t ad = umma_desc_advance(a_desc0, off + j * a_jstep);
+              const uint64_t bd = umma_desc_advance(b_desc0, off + j * b_jstep);
+              umma_tf32_pair(d_tmem, ad, bd, idesc, (k > k0 || sub > 0 || j > 0) ? 1u : 0u);
+            }
           }
-          umma_commit_pair(&empty_bar[s]);  // frees stage s in both CTAs
-          if (++s == STAGES) { s = 0; ++round; }
+          umma_commit_pair(&empty_bar[s]);  // frees the group in both CTAs
+          if (++s == NG) { s = 0; ++round; }
         }
         umma_commit_pair(&tfull_bar[acc]);  // both CTAs' halves of the accumulator complete
       }
+#ifdef FLB200_TC_PROFILE
+      TC_PROF_PUT(2, m_full); TC_PROF_PUT(3, m_acc); TC_PROF_PUT(4, clock64() - m_t0);
+#endif
     }
   } else {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     uint32_t nt = 0;
     typename P::Tile t;
+    TC_PROF_VAR(e_wait);
+    TC_PROF_VAR(e_store);
+    TC_PROF_NOW(e_t0);
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++nt) {
       prob.decode_pair(tile, (int)rank, t);
       const uint32_t acc = nt & 1, around = nt >> 1;
       if (*failed != 0) break;
+      TC_PROF_NOW(w0);
       if (!mbar_wait(&tfull_bar[acc], around & 1)) {
         *failed = 3;
         break;
       }
+      TC_PROF_ADD(e_wait, w0);
+      TC_PROF_NOW(w1);
       tc_fence_after();
       if (*failed != 0) break;
 #pragma unroll 1
@@ -202,7 +239,11 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty_bar[acc]), 0));
+      TC_PROF_ADD(e_store, w1);
     }
+#ifdef FLB200_TC_PROFILE
+    if (threadIdx.x == 64) { TC_PROF_PUT(5, e_wait); TC_PROF_PUT(6, e_store); TC_PROF_PUT(7, clock64() - e_t0); }
+#endif
   }
 
   tc_fence_before();
@@ -215,7 +256,10 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   }
 }
 
-template <class P, int BN>
+// KSUB = 2 pays where the operands come out of L2 and the producer's barrier chain is the
+// limit (the patch convolution); contractions that stream both operands from DRAM keep single
+// sub-stages: coarser hand-overs cost them bytes in flight (measured both ways).
+template <class P, int BN, int KSUB = 1>
 int launch_pair_problem(const char* name, const CUtensorMap& ma, const CUtensorMap& mb,
                         const P& prob, long long pair_tiles, cudaStream_t st) {
   constexpr int STAGES = pair_stages_for(BN);
@@ -225,7 +269,7 @@ int launch_pair_problem(const char* name, const CUtensorMap& ma, const CUtensorM
   int dev = 0;
   FLB200_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_pair_kernel<P, BN, STAGES>,
+    FLB200_CUDA_CHECK(cudaFuncSetAttribute(tc_pair_kernel<P, BN, STAGES, KSUB>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            SL::kTotal));
     configured[dev] = true;
@@ -244,10 +288,27 @@ int launch_pair_problem(const char* name, const CUtensorMap& ma, const CUtensorM
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FLB200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tc_pair_kernel<P, BN, STAGES>, ma, mb, prob,
+  FLB200_CUDA_CHECK(cudaLaunchKernelEx(&cfg, tc_pair_kernel<P, BN, STAGES, KSUB>, ma, mb, prob,
                                        status_ptr()));
   FLB200_AFTER_LAUNCH(name);
   count_tc_launch();
+#ifdef FLB200_TC_PROFILE
+  {
+    cudaStreamSynchronize(st);
+    static long long h[256 * 8];
+    cudaMemcpyFromSymbol(h, g_tc_profile, sizeof(h));
+    double a[8] = {0};  // leaders (even CTAs) only: the MMA slots of the peers are never written
+    unsigned n = 0;
+    for (unsigned c = 0; c < grid && c < 256; c += 2, ++n)
+      for (int i = 0; i < 8; ++i) a[i] += (double)h[c * 8 + i];
+    for (int i = 0; i < 8; ++i) a[i] /= n ? n : 1;
+    fprintf(stderr,
+            "tc profile %s (pairs) BN=%d stages=%d ksub=%d tiles=%lld grid=%u | producer wait %.0f of %.0f | "
+            "mma wait full %.0f, accumulator %.0f of %.0f | epilogue wait %.0f, store %.0f of %.0f "
+            "(mean clocks per leader CTA)\n",
+            name, BN, STAGES, KSUB, pair_tiles, grid, a[0], a[1], a[2], a[3], a[4], a[5], a[6], a[7]);
+  }
+#endif
   return FLB200_OK;
 }
 
