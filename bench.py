@@ -250,6 +250,11 @@ def install_timers(timer: OpTimer, ext, F):
     F.relu_backward_mask = timer.wrap("relu_backward", F.relu_backward_mask,
                                       lambda out, mask, gy: (0.0, 3 * _numel_bytes(gy)))
     F.add = timer.wrap("add", F.add, lambda out, a, b, **k: (0.0, 3 * _numel_bytes(a)))
+    # fused residual join (add + relu) and its two-addend gradient: bytes actually moved
+    F.add_relu_with_mask = timer.wrap("add_relu", F.add_relu_with_mask,
+                                      lambda out, a, b: (0.0, 3 * _numel_bytes(a)))
+    F.relu_backward_mask_sum = timer.wrap("relu_backward_sum", F.relu_backward_mask_sum,
+                                          lambda out, mask, ga, gb: (0.0, 3 * _numel_bytes(ga)))
     F.linear = timer.wrap("linear", F.linear,
                           lambda out, x, w, b=None, **k: (2.0 * out.numel() * w.shape[0],
                                                           _numel_bytes(x, w, out)))

@@ -105,6 +105,8 @@ SIGNATURES = {
     "flb200_sgd_step": (C.c_int, [vp, vp, vp, i64, f32, f32, f32, C.c_int, f32, C.c_int, C.c_int, vp]),
     "flb200_relu_forward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_relu_backward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
+    "flb200_add_relu_forward_mask": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, vp]),
+    "flb200_relu_backward_mask_sum": (C.c_int, [vp, vp, vp, vp, i64, C.c_int, vp]),
     "flb200_relu_forward": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "flb200_relu_backward": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_gelu_forward": (C.c_int, [vp, vp, i64, C.c_int, vp]),

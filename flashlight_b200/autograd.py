@@ -41,9 +41,28 @@ class Variable:
         self.inputs: List[Variable] = list(inputs)
         self.grad_func = grad_func
         self.calc_grad = calc_grad or any(i.calc_grad for i in self.inputs)
-        self.grad: Optional[torch.Tensor] = None
+        self._grad: Optional[torch.Tensor] = None
         self._grad_owned = False
+        # A second gradient contribution is kept apart until somebody reads `grad`: a
+        # grad_func that can take two addends (grad_func2) then sums them inside its own
+        # kernel instead of paying a whole-tensor addition first.
+        self._grad_second: Optional[torch.Tensor] = None
+        self.grad_func2: Optional[Callable] = None
         self.grad_hook: Optional[Callable[["Variable"], None]] = None
+
+    @property
+    def grad(self) -> Optional[torch.Tensor]:
+        if self._grad_second is not None:
+            second, self._grad_second = self._grad_second, None
+            if self._grad_owned:
+                F.add(self._grad, second, out=self._grad)
+            else:  # the first gradient may be shared with another Variable: never write into it
+                self._grad, self._grad_owned = F.add(self._grad, second), True
+        return self._grad
+
+    @grad.setter
+    def grad(self, value: Optional[torch.Tensor]) -> None:
+        self._grad, self._grad_second, self._grad_owned = value, None, False
 
     # Variable::isCalcGrad / addGrad (Variable.cpp:185-211)
     def isCalcGrad(self) -> bool:
@@ -55,15 +74,19 @@ class Variable:
         if g.shape != self.tensor.shape:
             raise ValueError(f"addGrad: given gradient has dimensions not equal to this Variable's "
                              f"dimensions: {tuple(g.shape)} vs {tuple(self.tensor.shape)}")
-        if self.grad is None:
-            self.grad, self._grad_owned = g, False
-        elif self._grad_owned:
-            F.add(self.grad, g, out=self.grad)
-        else:  # the first gradient may be shared with another Variable: never write into it
-            self.grad, self._grad_owned = F.add(self.grad, g), True
+        if self._grad is None:
+            self._grad, self._grad_owned = g, False
+        elif self._grad_second is None and self.grad_func2 is not None:
+            self._grad_second = g
+        else:
+            total = self.grad  # folds a pending second contribution in
+            if self._grad_owned:
+                F.add(total, g, out=total)
+            else:
+                self._grad, self._grad_owned = F.add(total, g), True
 
     def zeroGrad(self) -> None:
-        self.grad, self._grad_owned = None, False
+        self.grad = None
 
     def registerGradHook(self, hook: Callable[["Variable"], None]) -> None:
         self.grad_hook = hook
@@ -89,12 +112,17 @@ class Variable:
                 if id(inp) not in seen:
                     stack.append((inp, False))
         for node in reversed(order):
-            if node.grad_func is not None and node.grad is not None:
+            if node.grad_func2 is not None and node._grad_second is not None:
+                first, second = node._grad, node._grad_second
+                node._grad_second = None
+                node.grad_func2(node.inputs, first, second)
+            elif node.grad_func is not None and node.grad is not None:
                 node.grad_func(node.inputs, node.grad)
             if node.grad_hook is not None and node.grad is not None:
                 node.grad_hook(node)
             if not retain_graph and node.grad_func is not None:
                 node.grad_func = None
+                node.grad_func2 = None
                 node.inputs = []
                 node.grad = None
 
@@ -278,11 +306,45 @@ def relu(x: Variable) -> Variable:
         y, mask = F.relu_with_mask(t)
 
         def grad_func(inputs, gy):
-            g = gy if gy.is_contiguous() and gy.data_ptr() % 16 == 0 else gy.contiguous().clone()
-            inputs[0].addGrad(F.relu_backward_mask(mask, g))
+            inputs[0].addGrad(F.relu_backward_mask(mask, _aligned(gy)))
 
-        return Variable(y, False, [x], grad_func)
+        def grad_func2(inputs, ga, gb):
+            inputs[0].addGrad(F.relu_backward_mask_sum(mask, _aligned(ga), _aligned(gb)))
+
+        out = Variable(y, False, [x], grad_func)
+        out.grad_func2 = grad_func2
+        return out
     return _unary(x, F.relu, F.relu_backward, True)
+
+
+def _aligned(g: torch.Tensor) -> torch.Tensor:
+    return g if g.is_contiguous() and g.data_ptr() % 16 == 0 else g.contiguous().clone()
+
+
+def add_relu(a: Variable, b: Variable) -> Variable:
+    """relu(a + b), the residual join of a ResNet block (Resnet.cpp:67-121), as one kernel
+    forward (sum, relu and the predicate bit mask) and one backward: both addends receive
+    mask ? dy : 0, and when the output fed two consumers their two gradients are summed inside
+    that kernel.  Falls back to add + relu for tensors the fused kernels do not take."""
+    ta, tb = a.tensor, b.tensor
+    if not (ta.dtype == torch.float32 and ta.shape == tb.shape and ta.is_contiguous() and
+            tb.is_contiguous() and ta.data_ptr() % 16 == 0 and tb.data_ptr() % 16 == 0):
+        return relu(add(a, b))
+    y, mask = F.add_relu_with_mask(ta, tb)
+
+    def grad_func(inputs, gy):
+        gx = F.relu_backward_mask(mask, _aligned(gy))
+        inputs[0].addGrad(gx)
+        inputs[1].addGrad(gx)
+
+    def grad_func2(inputs, ga, gb):
+        gx = F.relu_backward_mask_sum(mask, _aligned(ga), _aligned(gb))
+        inputs[0].addGrad(gx)
+        inputs[1].addGrad(gx)
+
+    out = Variable(y, False, [a, b], grad_func)
+    out.grad_func2 = grad_func2
+    return out
 
 
 def gelu(x: Variable) -> Variable:

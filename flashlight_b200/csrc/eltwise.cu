@@ -216,17 +216,28 @@ __device__ __forceinline__ unsigned relu8(const float4& a, const float4& b, floa
          (b.z > 0.f ? 64u : 0u) | (b.w > 0.f ? 128u : 0u);
 }
 
+__device__ __forceinline__ float4 add4(const float4& a, const float4& b) {
+  return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
+// ADD: the input is the sum x + x2 (a residual join fused with its relu), else x alone.
+template <bool ADD>
 __global__ void __launch_bounds__(256)
-relu_forward_mask_kernel(const float* __restrict__ x, float* __restrict__ y,
-                         uint8_t* __restrict__ mask, long long n) {
+relu_forward_mask_kernel(const float* __restrict__ x, const float* __restrict__ x2,
+                         float* __restrict__ y, uint8_t* __restrict__ mask, long long n) {
   const long long full = n >> 3;  // complete groups of 8
   const long long stride = (long long)gridDim.x * blockDim.x;
   const float4* xv = reinterpret_cast<const float4*>(x);
+  const float4* x2v = reinterpret_cast<const float4*>(x2);
   float4* yv = reinterpret_cast<float4*>(y);
   long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   for (; g + stride < full; g += 2 * stride) {
     const long long g2 = g + stride;
-    const float4 a0 = xv[2 * g], b0 = xv[2 * g + 1], a1 = xv[2 * g2], b1 = xv[2 * g2 + 1];
+    float4 a0 = xv[2 * g], b0 = xv[2 * g + 1], a1 = xv[2 * g2], b1 = xv[2 * g2 + 1];
+    if (ADD) {
+      const float4 c0 = x2v[2 * g], d0 = x2v[2 * g + 1], c1 = x2v[2 * g2], d1 = x2v[2 * g2 + 1];
+      a0 = add4(a0, c0); b0 = add4(b0, d0); a1 = add4(a1, c1); b1 = add4(b1, d1);
+    }
     float4 ya, yb;
     mask[g] = (uint8_t)relu8(a0, b0, ya, yb);
     yv[2 * g] = ya; yv[2 * g + 1] = yb;
@@ -234,15 +245,18 @@ relu_forward_mask_kernel(const float* __restrict__ x, float* __restrict__ y,
     yv[2 * g2] = ya; yv[2 * g2 + 1] = yb;
   }
   if (g < full) {
+    float4 a0 = xv[2 * g], b0 = xv[2 * g + 1];
+    if (ADD) { a0 = add4(a0, x2v[2 * g]); b0 = add4(b0, x2v[2 * g + 1]); }
     float4 ya, yb;
-    mask[g] = (uint8_t)relu8(xv[2 * g], xv[2 * g + 1], ya, yb);
+    mask[g] = (uint8_t)relu8(a0, b0, ya, yb);
     yv[2 * g] = ya; yv[2 * g + 1] = yb;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0 && (n & 7)) {  // ragged tail
     unsigned bits = 0;
     for (long long i = full * 8; i < n; ++i) {
-      y[i] = ReluFwd{}(x[i]);
-      bits |= (x[i] > 0.f ? 1u : 0u) << (i - full * 8);
+      const float v = ADD ? x[i] + x2[i] : x[i];
+      y[i] = ReluFwd{}(v);
+      bits |= (v > 0.f ? 1u : 0u) << (i - full * 8);
     }
     mask[full] = (uint8_t)bits;
   }
@@ -255,18 +269,26 @@ __device__ __forceinline__ void relu_bwd8(unsigned m, const float4& a, const flo
                    m & 128u ? b.w : 0.f);
 }
 
+// ADD: the gradient is the sum dy + dy2 (two consumers of the relu's output, summed on the fly
+// instead of by a separate accumulation pass), else dy alone.
+template <bool ADD>
 __global__ void __launch_bounds__(256)
 relu_backward_mask_kernel(const uint8_t* __restrict__ mask, const float* __restrict__ dy,
-                          float* __restrict__ dx, long long n) {
+                          const float* __restrict__ dy2, float* __restrict__ dx, long long n) {
   const long long full = n >> 3;
   const long long stride = (long long)gridDim.x * blockDim.x;
   const float4* gv = reinterpret_cast<const float4*>(dy);
+  const float4* g2v = reinterpret_cast<const float4*>(dy2);
   float4* ov = reinterpret_cast<float4*>(dx);
   long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   for (; g + stride < full; g += 2 * stride) {
     const long long g2 = g + stride;
     const unsigned m0 = mask[g], m1 = mask[g2];
-    const float4 a0 = gv[2 * g], b0 = gv[2 * g + 1], a1 = gv[2 * g2], b1 = gv[2 * g2 + 1];
+    float4 a0 = gv[2 * g], b0 = gv[2 * g + 1], a1 = gv[2 * g2], b1 = gv[2 * g2 + 1];
+    if (ADD) {
+      const float4 c0 = g2v[2 * g], d0 = g2v[2 * g + 1], c1 = g2v[2 * g2], d1 = g2v[2 * g2 + 1];
+      a0 = add4(a0, c0); b0 = add4(b0, d0); a1 = add4(a1, c1); b1 = add4(b1, d1);
+    }
     float4 da, db;
     relu_bwd8(m0, a0, b0, da, db);
     ov[2 * g] = da; ov[2 * g + 1] = db;
@@ -274,13 +296,16 @@ relu_backward_mask_kernel(const uint8_t* __restrict__ mask, const float* __restr
     ov[2 * g2] = da; ov[2 * g2 + 1] = db;
   }
   if (g < full) {
+    float4 a0 = gv[2 * g], b0 = gv[2 * g + 1];
+    if (ADD) { a0 = add4(a0, g2v[2 * g]); b0 = add4(b0, g2v[2 * g + 1]); }
     float4 da, db;
-    relu_bwd8(mask[g], gv[2 * g], gv[2 * g + 1], da, db);
+    relu_bwd8(mask[g], a0, b0, da, db);
     ov[2 * g] = da; ov[2 * g + 1] = db;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0 && (n & 7)) {
     const unsigned bits = mask[full];
-    for (long long i = full * 8; i < n; ++i) dx[i] = (bits >> (i - full * 8)) & 1u ? dy[i] : 0.f;
+    for (long long i = full * 8; i < n; ++i)
+      dx[i] = (bits >> (i - full * 8)) & 1u ? (ADD ? dy[i] + dy2[i] : dy[i]) : 0.f;
   }
 }
 
@@ -339,32 +364,61 @@ int flb200_sgd_step(void* param, void* grad, void* velocity, int64_t n, float lr
   return FLB200_OK;
 }
 
-int flb200_relu_forward_mask(const void* x, void* y, uint8_t* mask, int64_t n, int dtype,
-                             void* stream) {
-  FLB200_REQUIRE(n >= 0, "relu_forward_mask: negative size");
+namespace {
+int relu_mask_forward(const char* name, const void* x, const void* x2, void* y, uint8_t* mask,
+                      int64_t n, int dtype, void* stream) {
+  FLB200_REQUIRE(n >= 0, "%s: negative size", name);
   if (n == 0) return FLB200_OK;
-  FLB200_REQUIRE(x && y && mask, "relu_forward_mask: null tensor");
-  if (dtype != FLB200_F32 || !aligned16(x) || !aligned16(y))
-    return fail(FLB200_UNSUPPORTED, "relu_forward_mask: f32 tensors aligned to 16 bytes only");
+  FLB200_REQUIRE(x && y && mask, "%s: null tensor", name);
+  if (dtype != FLB200_F32 || !aligned16(x) || !aligned16(y) || (x2 && !aligned16(x2)))
+    return fail(FLB200_UNSUPPORTED, "%s: f32 tensors aligned to 16 bytes only", name);
   const int grid = grid_for((n + 7) / 8, 256 * 2);
-  relu_forward_mask_kernel<<<grid, 256, 0, as_stream(stream)>>>(
-      static_cast<const float*>(x), static_cast<float*>(y), mask, n);
-  FLB200_AFTER_LAUNCH("relu_forward_mask");
+  if (x2)
+    relu_forward_mask_kernel<true><<<grid, 256, 0, as_stream(stream)>>>(
+        static_cast<const float*>(x), static_cast<const float*>(x2), static_cast<float*>(y), mask, n);
+  else
+    relu_forward_mask_kernel<false><<<grid, 256, 0, as_stream(stream)>>>(
+        static_cast<const float*>(x), nullptr, static_cast<float*>(y), mask, n);
+  FLB200_AFTER_LAUNCH(name);
   return FLB200_OK;
 }
+int relu_mask_backward(const char* name, const uint8_t* mask, const void* g1, const void* g2,
+                       void* grad_x, int64_t n, int dtype, void* stream) {
+  FLB200_REQUIRE(n >= 0, "%s: negative size", name);
+  if (n == 0) return FLB200_OK;
+  FLB200_REQUIRE(mask && g1 && grad_x, "%s: null tensor", name);
+  if (dtype != FLB200_F32 || !aligned16(g1) || !aligned16(grad_x) || (g2 && !aligned16(g2)))
+    return fail(FLB200_UNSUPPORTED, "%s: f32 tensors aligned to 16 bytes only", name);
+  const int grid = grid_for((n + 7) / 8, 256 * 2);
+  if (g2)
+    relu_backward_mask_kernel<true><<<grid, 256, 0, as_stream(stream)>>>(
+        mask, static_cast<const float*>(g1), static_cast<const float*>(g2),
+        static_cast<float*>(grad_x), n);
+  else
+    relu_backward_mask_kernel<false><<<grid, 256, 0, as_stream(stream)>>>(
+        mask, static_cast<const float*>(g1), nullptr, static_cast<float*>(grad_x), n);
+  FLB200_AFTER_LAUNCH(name);
+  return FLB200_OK;
+}
+}  // namespace
 
+int flb200_relu_forward_mask(const void* x, void* y, uint8_t* mask, int64_t n, int dtype,
+                             void* stream) {
+  return relu_mask_forward("relu_forward_mask", x, nullptr, y, mask, n, dtype, stream);
+}
+int flb200_add_relu_forward_mask(const void* a, const void* b, void* y, uint8_t* mask, int64_t n,
+                                 int dtype, void* stream) {
+  FLB200_REQUIRE(b != nullptr || n == 0, "add_relu_forward_mask: null tensor");
+  return relu_mask_forward("add_relu_forward_mask", a, b, y, mask, n, dtype, stream);
+}
 int flb200_relu_backward_mask(const uint8_t* mask, const void* grad_y, void* grad_x, int64_t n,
                               int dtype, void* stream) {
-  FLB200_REQUIRE(n >= 0, "relu_backward_mask: negative size");
-  if (n == 0) return FLB200_OK;
-  FLB200_REQUIRE(mask && grad_y && grad_x, "relu_backward_mask: null tensor");
-  if (dtype != FLB200_F32 || !aligned16(grad_y) || !aligned16(grad_x))
-    return fail(FLB200_UNSUPPORTED, "relu_backward_mask: f32 tensors aligned to 16 bytes only");
-  const int grid = grid_for((n + 7) / 8, 256 * 2);
-  relu_backward_mask_kernel<<<grid, 256, 0, as_stream(stream)>>>(
-      mask, static_cast<const float*>(grad_y), static_cast<float*>(grad_x), n);
-  FLB200_AFTER_LAUNCH("relu_backward_mask");
-  return FLB200_OK;
+  return relu_mask_backward("relu_backward_mask", mask, grad_y, nullptr, grad_x, n, dtype, stream);
+}
+int flb200_relu_backward_mask_sum(const uint8_t* mask, const void* grad_y_a, const void* grad_y_b,
+                                  void* grad_x, int64_t n, int dtype, void* stream) {
+  return relu_mask_backward("relu_backward_mask_sum", mask, grad_y_a, grad_y_b, grad_x, n, dtype,
+                            stream);
 }
 
 int flb200_relu_forward(const void* x, void* y, int64_t n, int dtype, void* stream) {

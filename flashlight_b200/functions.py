@@ -58,6 +58,24 @@ def relu_backward_mask(mask, grad_y):
     return gx
 
 
+def add_relu_with_mask(a, b):
+    """relu(a + b) in one pass, with the predicate (a + b) > 0 packed 8 elements per byte."""
+    y = torch.empty_like(a)
+    mask = torch.empty((a.numel() + 7) // 8, dtype=torch.uint8, device=a.device)
+    L.check(L.lib.flb200_add_relu_forward_mask(ptr(a), ptr(b), ptr(y), ptr(mask), a.numel(),
+                                               dtype_code(a), stream_handle()))
+    return y, mask
+
+
+def relu_backward_mask_sum(mask, grad_a, grad_b):
+    """mask ? grad_a + grad_b : 0 — the relu gradient of an output with two consumers."""
+    gx = torch.empty_like(grad_a)
+    L.check(L.lib.flb200_relu_backward_mask_sum(ptr(mask), ptr(grad_a), ptr(grad_b), ptr(gx),
+                                                grad_a.numel(), dtype_code(grad_a),
+                                                stream_handle()))
+    return gx
+
+
 def gelu(x):
     """fl::gelu, tanh form (Functions.cpp:1791-1796)."""
     return _unary(L.lib.flb200_gelu_forward, x)

@@ -15,6 +15,7 @@ returns the scalar loss Variable; `loss(...).backward()` is the measured step.
 from __future__ import annotations
 
 import math
+import os
 from typing import List
 
 import torch
@@ -24,6 +25,11 @@ from . import autograd as A
 from . import functions as F
 from . import nn
 from .autograd import Variable
+
+
+# Fused residual join: relu(out + shortcut) as one kernel with a one-kernel gradient
+# (autograd.add_relu).  FLB200_FUSE=0 keeps the reference's operator-by-operator chain.
+FUSE_RESIDUAL_RELU = os.environ.get("FLB200_FUSE", "1") not in ("0", "false")
 
 
 class Bottleneck(nn.Module):
@@ -49,6 +55,8 @@ class Bottleneck(nn.Module):
         out = A.relu(self.b2(self.c2(out)))
         out = self.b3(self.c3(out))
         shortcut = self.down(x) if self.down is not None else x
+        if FUSE_RESIDUAL_RELU:
+            return A.add_relu(out, shortcut)
         return A.relu(A.add(out, shortcut))
 
 

@@ -411,6 +411,62 @@ def test_relu_bit_mask(fx, n):
     assert torch.equal(gx.cpu(), torch.where(x > 0, g, torch.zeros_like(g)))
 
 
+@pytest.mark.parametrize("n", [1, 7, 8, 9, 1000, 4096 + 5, 3 * 1024 * 1024 + 3])
+def test_add_relu_bit_mask(fx, n):
+    """The fused residual join: y = relu(a + b) and its mask bit for bit equal to the add kernel
+    followed by the relu kernel; the two-addend gradient equals mask * (ga + gb) computed with
+    the add kernel first.  NaN in either addend propagates, ragged tails included."""
+    a, b = randn(n, seed=53), randn(n, seed=54)
+    if n >= 9:
+        a[3], b[4], a[5], b[5] = float("nan"), float("nan"), 1.5, -1.5
+    ga, gb = randn(n, seed=55), randn(n, seed=56)
+    ad, bd = a.cuda(), b.cuda()
+    y, mask = fx.add_relu_with_mask(ad, bd)
+    y_ref, mask_ref = fx.relu_with_mask(fx.add(ad, bd))
+    assert torch.equal(torch.nan_to_num(y, nan=123.0), torch.nan_to_num(y_ref, nan=123.0))
+    assert torch.equal(mask, mask_ref)
+    assert torch.equal(torch.nan_to_num(y.cpu(), nan=123.0),
+                       torch.nan_to_num(torch.relu(a + b), nan=123.0))
+    gx = fx.relu_backward_mask_sum(mask, ga.cuda(), gb.cuda())
+    assert torch.equal(gx, fx.relu_backward_mask(mask, fx.add(ga.cuda(), gb.cuda())))
+    assert torch.equal(gx.cpu(), torch.where((a + b) > 0, ga + gb, torch.zeros_like(ga)))
+
+
+def test_tape_fused_residual_join_matches_operator_chain():
+    """autograd.add_relu (one kernel each way, two-consumer gradients summed inside it) gives
+    the same output and the same input gradients, bit for bit, as relu(add(a, b)) with the
+    tape's whole-tensor gradient accumulation."""
+    from flashlight_b200 import autograd as A
+    from flashlight_b200.autograd import Variable
+
+    def run(fused):
+        a = Variable(randn(4, 8, 6, 6, seed=71).cuda(), True)
+        b = Variable(randn(4, 8, 6, 6, seed=72).cuda(), True)
+        y = A.add_relu(a, b) if fused else A.relu(A.add(a, b))
+        # two consumers of y, then a third so that every accumulation path is walked
+        z = A.add(A.tanh(y), A.gelu(y))
+        z = A.add(z, y)
+        z.backward(randn(4, 8, 6, 6, seed=73).cuda())
+        return y.tensor.clone(), a.grad.clone(), b.grad.clone()
+
+    y0, ga0, gb0 = run(False)
+    y1, ga1, gb1 = run(True)
+    assert torch.equal(y0, y1)
+    # the fused path sums three contributions in a different association order
+    assert_close(ga1, ga0.cpu().double(), 1e-6, "fused residual join: grad a")
+    assert_close(gb1, gb0.cpu().double(), 1e-6, "fused residual join: grad b")
+
+    def run2(fused):
+        a = Variable(randn(4, 8, 6, 6, seed=71).cuda(), True)
+        b = Variable(randn(4, 8, 6, 6, seed=72).cuda(), True)
+        y = A.add_relu(a, b) if fused else A.relu(A.add(a, b))
+        z = A.add(A.tanh(y), A.gelu(y))  # exactly two consumers: the in-kernel sum
+        z.backward(randn(4, 8, 6, 6, seed=73).cuda())
+        return a.grad.clone()
+
+    assert torch.equal(run2(False), run2(True))
+
+
 @pytest.mark.parametrize("cfg", [
     (0.1, 0.9, 0.1, False, 1.0),      # the reference benchmark's setting
     (0.05, 0.9, 0.0, True, 0.125),    # Nesterov, gradient averaged over 8 ranks
