@@ -237,6 +237,9 @@ def install_timers(timer: OpTimer, ext, F):
                                lambda out, x, *a, **k: (0.0, 2 * _numel_bytes(x)))
     ext.batchnormBackward = timer.wrap("batchnormBackward", ext.batchnormBackward,
                                        lambda out, gy, sm, sv, x, *a, **k: (0.0, 3 * _numel_bytes(x)))
+    ext.batchnormReluBackward = timer.wrap(
+        "batchnormBackward", ext.batchnormReluBackward,
+        lambda out, gy, sm, sv, x, *a, **k: (0.0, 3 * _numel_bytes(x)))
     ext.pool2d = timer.wrap("pool2d", ext.pool2d, lambda out, x, *a, **k: (0.0, _numel_bytes(x, out)))
     ext.pool2dBackward = timer.wrap("pool2dBackward", ext.pool2dBackward,
                                     lambda out, gy, x, *a, **k: (0.0, 2 * _numel_bytes(x) + _numel_bytes(gy)))

@@ -88,6 +88,10 @@ SIGNATURES = {
                                            f64, f64, vp, vp, sz, vp]),
     "flb200_batchnorm_backward": (C.c_int, [P(BatchnormDesc), vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                             sz, vp]),
+    "flb200_batchnorm_relu_forward": (C.c_int, [P(BatchnormDesc), vp, vp, vp, vp, vp, vp, vp,
+                                                C.c_int, f64, f64, vp, vp, sz, vp]),
+    "flb200_batchnorm_relu_backward": (C.c_int, [P(BatchnormDesc), vp, vp, vp, vp, vp, vp, vp, vp,
+                                                 vp, vp, sz, vp]),
     "flb200_matmul_workspace_bytes": (sz, [P(MatmulDesc)]),
     "flb200_matmul": (C.c_int, [P(MatmulDesc), vp, vp, vp, vp, sz, vp]),
     "flb200_linear_workspace_bytes": (sz, [i64, i64, i64, C.c_int]),

@@ -168,18 +168,25 @@ def pool2d(x: Variable, wx, wy, sx, sy, px, py, mode=L.POOL_MAX) -> Variable:
 
 def batchnorm(x: Variable, weight: Optional[Variable], bias: Optional[Variable],
               running_mean: Optional[torch.Tensor], running_var: Optional[torch.Tensor],
-              axes: Sequence[int], train: bool, momentum: float, epsilon: float) -> Variable:
-    """fl::batchnorm (Functions.cpp:1498-1565)."""
+              axes: Sequence[int], train: bool, momentum: float, epsilon: float,
+              relu: bool = False) -> Variable:
+    """fl::batchnorm (Functions.cpp:1498-1565).  relu=True is relu(batchnorm(x)) as one
+    operator: no separate relu pass forward or backward, nothing extra saved."""
     ext = extension()
     wt = weight.tensor if weight is not None else None
     bt = bias.tensor if bias is not None else None
     y, save_mean, save_var = ext.batchnorm(x.tensor, wt, bt, running_mean, running_var, axes, train,
-                                           momentum, epsilon, None)
+                                           momentum, epsilon, None, relu=relu)
     xt = x.tensor
     ins = [x] + ([weight] if weight is not None else []) + ([bias] if bias is not None else [])
 
     def grad_func(inputs, gy):
-        gx, gw, gb = ext.batchnormBackward(gy, save_mean, save_var, xt, wt, axes, train, epsilon, None)
+        if relu:
+            gx, gw, gb = ext.batchnormReluBackward(gy, save_mean, save_var, xt, wt, bt, axes, train,
+                                                   epsilon, None)
+        else:
+            gx, gw, gb = ext.batchnormBackward(gy, save_mean, save_var, xt, wt, axes, train,
+                                               epsilon, None)
         inputs[0].addGrad(gx)
         k = 1
         if weight is not None:

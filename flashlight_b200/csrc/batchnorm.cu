@@ -55,14 +55,60 @@ struct BnBwdReduceF {  // a = x, b = dy
   }
 };
 
-struct BnFwdApplyF {  // y = (x - mean) * scale + shift
+// The normalised, scaled and shifted value.  One expression for the forward pass and for the
+// fused-relu backward passes, which recompute it to get the relu predicate back from x.
+__device__ __forceinline__ float bn_value(float x, float mean, float scale, float shift) {
+  return __fmaf_rn(x - mean, scale, shift);
+}
+// scale = invstd * gamma from the SAVED (rounded) invstd, so that backward can rebuild it.
+__device__ __forceinline__ float bn_scale(float invstd, const float* weight, long long c) {
+  return (float)((double)invstd * (weight ? (double)weight[c] : 1.0));
+}
+
+template <bool RELU>
+struct BnFwdApplyF {  // y = (x - mean) * scale + shift, then max(., 0) when RELU
   const float* mean;
   const float* scale;  // invstd * gamma
   const float* shift;  // beta
   struct K { float mean, scale, shift; };
   __device__ K channel(long long c) const { return K{mean[c], scale[c], shift ? shift[c] : 0.f}; }
   __device__ float apply(const K& k, float a, float) const {
-    return (a - k.mean) * k.scale + k.shift;
+    const float z = bn_value(a, k.mean, k.scale, k.shift);
+    return RELU ? (z > 0.f ? z : (z != z ? z : 0.f)) : z;
+  }
+};
+
+// Backward of relu(batchnorm(x)): the relu predicate is rebuilt from x (z > 0 with z exactly
+// as forward computed it), so neither the output nor a mask is read and the relu gradient
+// costs no pass of its own.  a = x, b = dy.
+struct BnReluBwdReduceF {
+  const float* mean;
+  const float* invstd;
+  const float* weight;
+  const float* shift;
+  struct K { float mean, scale, shift; };
+  __device__ K channel(long long c) const {
+    return K{mean[c], bn_scale(invstd[c], weight, c), shift ? shift[c] : 0.f};
+  }
+  __device__ void accumulate(const K& k, float a, float b, float& s0, float& s1) const {
+    const float g = bn_value(a, k.mean, k.scale, k.shift) > 0.f ? b : 0.f;
+    s0 += g;
+    s1 += g * (a - k.mean);
+  }
+};
+struct BnReluBwdApplyF {
+  const float4* coef;  // (mean, k1, mean_dbeta, k4)
+  const float* invstd;
+  const float* weight;
+  const float* shift;
+  struct K { float mean, k1, mb, k4, scale, shift; };
+  __device__ K channel(long long c) const {
+    const float4 v = coef[c];
+    return K{v.x, v.y, v.z, v.w, bn_scale(invstd[c], weight, c), shift ? shift[c] : 0.f};
+  }
+  __device__ float apply(const K& k, float a, float b) const {
+    const float g = bn_value(a, k.mean, k.scale, k.shift) > 0.f ? b : 0.f;
+    return k.k1 * (g - k.mb - (a - k.mean) * k.k4);
   }
 };
 
@@ -123,7 +169,7 @@ __global__ void bn_stats_finalize_kernel(const float2* __restrict__ partial, int
   const double invstd = 1.0 / sqrt(var + eps);
   save_mean[c] = (float)mean;
   save_invstd[c] = (float)invstd;
-  scale[c] = (float)(invstd * (weight ? (double)weight[c] : 1.0));
+  scale[c] = bn_scale((float)invstd, weight, c);
   if (running_mean) running_mean[c] = (float)((1.0 - momentum) * running_mean[c] + momentum * mean);
   if (running_var) {
     const double unbiased = count > 1.0 ? var * count / (count - 1.0) : var;
@@ -362,11 +408,11 @@ size_t flb200_batchnorm_workspace_bytes(const flb200_batchnorm_desc* d) {
          align_up((size_t)d->channels * sizeof(float4), 256);
 }
 
-int flb200_batchnorm_forward(const flb200_batchnorm_desc* d, const void* x, const float* weight,
-                             const float* bias, float* running_mean, float* running_var,
-                             float* save_mean, float* save_invstd, int train, double momentum,
-                             double epsilon, void* y, void* workspace, size_t workspace_bytes,
-                             void* stream) {
+static int batchnorm_forward_impl(bool relu, const flb200_batchnorm_desc* d, const void* x,
+                                  const float* weight, const float* bias, float* running_mean,
+                                  float* running_var, float* save_mean, float* save_invstd,
+                                  int train, double momentum, double epsilon, void* y,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d, "batchnorm_forward: null descriptor");
   if (int st = check_geo("batchnorm_forward", d->outer, d->channels, d->inner)) return st;
   FLB200_REQUIRE(x && y, "batchnorm_forward: null tensor");
@@ -403,18 +449,44 @@ int flb200_batchnorm_forward(const flb200_batchnorm_desc* d, const void* x, cons
     FLB200_AFTER_LAUNCH("batchnorm_infer_prepare");
     mean_ptr = running_mean;
   }
-  BnFwdApplyF af{mean_ptr, scale, bias};
-  FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_forward",
-                        rc = (launch_apply<T, 1>("batchnorm_apply", x, nullptr, y, d->outer, C,
-                                                 d->inner, af, st)));
+  if (relu) {
+    BnFwdApplyF<true> af{mean_ptr, scale, bias};
+    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_relu_forward",
+                          rc = (launch_apply<T, 1>("batchnorm_relu_apply", x, nullptr, y, d->outer,
+                                                   C, d->inner, af, st)));
+  } else {
+    BnFwdApplyF<false> af{mean_ptr, scale, bias};
+    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_forward",
+                          rc = (launch_apply<T, 1>("batchnorm_apply", x, nullptr, y, d->outer, C,
+                                                   d->inner, af, st)));
+  }
   return rc;
 }
 
-int flb200_batchnorm_backward(const flb200_batchnorm_desc* d, const void* grad_y, const void* x,
-                              const float* weight, const float* save_mean,
-                              const float* save_invstd, void* grad_x, float* grad_weight,
-                              float* grad_bias, void* workspace, size_t workspace_bytes,
-                              void* stream) {
+int flb200_batchnorm_forward(const flb200_batchnorm_desc* d, const void* x, const float* weight,
+                             const float* bias, float* running_mean, float* running_var,
+                             float* save_mean, float* save_invstd, int train, double momentum,
+                             double epsilon, void* y, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+  return batchnorm_forward_impl(false, d, x, weight, bias, running_mean, running_var, save_mean,
+                                save_invstd, train, momentum, epsilon, y, workspace,
+                                workspace_bytes, stream);
+}
+int flb200_batchnorm_relu_forward(const flb200_batchnorm_desc* d, const void* x,
+                                  const float* weight, const float* bias, float* running_mean,
+                                  float* running_var, float* save_mean, float* save_invstd,
+                                  int train, double momentum, double epsilon, void* y,
+                                  void* workspace, size_t workspace_bytes, void* stream) {
+  return batchnorm_forward_impl(true, d, x, weight, bias, running_mean, running_var, save_mean,
+                                save_invstd, train, momentum, epsilon, y, workspace,
+                                workspace_bytes, stream);
+}
+
+static int batchnorm_backward_impl(bool relu, const flb200_batchnorm_desc* d, const void* grad_y,
+                                   const void* x, const float* weight, const float* bias,
+                                   const float* save_mean, const float* save_invstd, void* grad_x,
+                                   float* grad_weight, float* grad_bias, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d, "batchnorm_backward: null descriptor");
   if (int st = check_geo("batchnorm_backward", d->outer, d->channels, d->inner)) return st;
   FLB200_REQUIRE(grad_y && x && save_mean && save_invstd && grad_x && grad_weight && grad_bias,
@@ -431,20 +503,54 @@ int flb200_batchnorm_backward(const flb200_batchnorm_desc* d, const void* grad_y
   off += align_up((size_t)C * sizeof(float), 256);
   float4* coef = reinterpret_cast<float4*>(ws + off);
   int rc = FLB200_OK, splits = 0;
-  BnBwdReduceF rf{save_mean};
-  FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_backward",
-                        rc = (launch_reduce<T, 2>("batchnorm_backward_reduce", x, grad_y, partial,
-                                                  d->outer, C, d->inner, rf, &splits, st)));
+  if (relu) {
+    BnReluBwdReduceF rf{save_mean, save_invstd, weight, bias};
+    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_relu_backward",
+                          rc = (launch_reduce<T, 2>("batchnorm_relu_backward_reduce", x, grad_y,
+                                                    partial, d->outer, C, d->inner, rf, &splits,
+                                                    st)));
+  } else {
+    BnBwdReduceF rf{save_mean};
+    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_backward",
+                          rc = (launch_reduce<T, 2>("batchnorm_backward_reduce", x, grad_y,
+                                                    partial, d->outer, C, d->inner, rf, &splits,
+                                                    st)));
+  }
   if (rc) return rc;
   bn_bwd_finalize_kernel<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(
       partial, splits, C, (double)d->outer * (double)d->inner, weight, save_mean, save_invstd,
       grad_weight, grad_bias, coef);
   FLB200_AFTER_LAUNCH("batchnorm_backward_finalize");
-  BnBwdApplyF af{coef};
-  FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_backward",
-                        rc = (launch_apply<T, 2>("batchnorm_backward_apply", x, grad_y, grad_x,
-                                                 d->outer, C, d->inner, af, st)));
+  if (relu) {
+    BnReluBwdApplyF af{coef, save_invstd, weight, bias};
+    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_relu_backward",
+                          rc = (launch_apply<T, 2>("batchnorm_relu_backward_apply", x, grad_y,
+                                                   grad_x, d->outer, C, d->inner, af, st)));
+  } else {
+    BnBwdApplyF af{coef};
+    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_backward",
+                          rc = (launch_apply<T, 2>("batchnorm_backward_apply", x, grad_y, grad_x,
+                                                   d->outer, C, d->inner, af, st)));
+  }
   return rc;
+}
+
+int flb200_batchnorm_backward(const flb200_batchnorm_desc* d, const void* grad_y, const void* x,
+                              const float* weight, const float* save_mean,
+                              const float* save_invstd, void* grad_x, float* grad_weight,
+                              float* grad_bias, void* workspace, size_t workspace_bytes,
+                              void* stream) {
+  return batchnorm_backward_impl(false, d, grad_y, x, weight, nullptr, save_mean, save_invstd,
+                                 grad_x, grad_weight, grad_bias, workspace, workspace_bytes,
+                                 stream);
+}
+int flb200_batchnorm_relu_backward(const flb200_batchnorm_desc* d, const void* grad_y,
+                                   const void* x, const float* weight, const float* bias,
+                                   const float* save_mean, const float* save_invstd,
+                                   void* grad_x, float* grad_weight, float* grad_bias,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+  return batchnorm_backward_impl(true, d, grad_y, x, weight, bias, save_mean, save_invstd, grad_x,
+                                 grad_weight, grad_bias, workspace, workspace_bytes, stream);
 }
 
 }  // extern "C"

@@ -277,9 +277,10 @@ class B200AutogradExtension:
         return d
 
     def batchnorm(self, input, weight, bias, runningMean, runningVar, axes, train, momentum,
-                  epsilon, payload=None):
+                  epsilon, payload=None, relu=False):
         """Returns (output, saveMean, saveVar).  saveVar holds 1/sqrt(var + eps).
-        runningMean / runningVar are updated in place when given."""
+        runningMean / runningVar are updated in place when given.  relu=True returns
+        relu(batchnorm(x)) from the same two passes (pair it with batchnormReluBackward)."""
         d = self._bn_desc(input, axes)
         for t in (weight, bias, runningMean, runningVar):
             if t is not None and t.dtype != torch.float32:
@@ -295,7 +296,8 @@ class B200AutogradExtension:
             save_var = torch.empty(d.channels, dtype=torch.float32, device=input.device)
         nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
         ws = workspace(nbytes, input)
-        L.check(L.lib.flb200_batchnorm_forward(
+        forward = L.lib.flb200_batchnorm_relu_forward if relu else L.lib.flb200_batchnorm_forward
+        L.check(forward(
             C.byref(d), ptr(input), ptr(weight), ptr(bias), ptr(runningMean), ptr(runningVar),
             ptr(save_mean), ptr(save_var), 1 if train else 0, float(momentum), float(epsilon),
             ptr(out), ptr(ws), nbytes, stream_handle()))
@@ -315,6 +317,23 @@ class B200AutogradExtension:
         L.check(L.lib.flb200_batchnorm_backward(
             C.byref(d), ptr(gradOutput), ptr(input), ptr(weight), ptr(saveMean), ptr(saveVar),
             ptr(grad_in), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes, stream_handle()))
+        return grad_in, grad_w, grad_b
+
+    def batchnormReluBackward(self, gradOutput, saveMean, saveVar, input, weight, bias, axes, train,
+                              epsilon, payload=None):
+        """Gradient of relu(batchnorm(x)) given the gradient of the relu output: the predicate
+        is rebuilt from the input, so no output tensor or mask is needed."""
+        if not train:
+            raise RuntimeError("can't compute batchnorm grad when train was not specified")
+        d = self._bn_desc(input, axes)
+        grad_in = torch.empty_like(input)
+        grad_w = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        grad_b = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_batchnorm_relu_backward(
+            C.byref(d), ptr(gradOutput), ptr(input), ptr(weight), ptr(bias), ptr(saveMean),
+            ptr(saveVar), ptr(grad_in), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes, stream_handle()))
         return grad_in, grad_w, grad_b
 
     # ------------------------------------------------------------------ rnn

@@ -56,8 +56,8 @@ class Module:
         for c in self.children:
             c.train(mode)
 
-    def __call__(self, x):
-        return self.forward(x)
+    def __call__(self, x, **kwargs):
+        return self.forward(x, **kwargs)
 
 
 class Sequential(Module):
@@ -127,11 +127,12 @@ class BatchNorm(Module):
         self.running_mean = torch.zeros(feat_size, device=device)
         self.running_var = torch.ones(feat_size, device=device)
 
-    def forward(self, x):
+    def forward(self, x, relu=False):
+        """relu=True: the module's output is relu(batchnorm(x)), computed as one operator."""
         w = self.params[0] if self.params else None
         b = self.params[1] if self.params else None
         return A.batchnorm(x, w, b, self.running_mean, self.running_var, self.axes, self.train_mode,
-                           self.momentum, self.eps)
+                           self.momentum, self.eps, relu=relu)
 
 
 class LayerNorm(Module):

@@ -27,9 +27,11 @@ from . import nn
 from .autograd import Variable
 
 
-# Fused residual join: relu(out + shortcut) as one kernel with a one-kernel gradient
-# (autograd.add_relu).  FLB200_FUSE=0 keeps the reference's operator-by-operator chain.
+# Operator fusions of the ResNet block: relu(out + shortcut) as one kernel with a one-kernel
+# gradient (autograd.add_relu), and relu(batchnorm(x)) as one operator (autograd.batchnorm
+# with relu=True).  FLB200_FUSE=0 keeps the reference's operator-by-operator chain.
 FUSE_RESIDUAL_RELU = os.environ.get("FLB200_FUSE", "1") not in ("0", "false")
+FUSE_BATCHNORM_RELU = FUSE_RESIDUAL_RELU
 
 
 class Bottleneck(nn.Module):
@@ -51,8 +53,12 @@ class Bottleneck(nn.Module):
             self.children.append(self.down)
 
     def forward(self, x):
-        out = A.relu(self.b1(self.c1(x)))
-        out = A.relu(self.b2(self.c2(out)))
+        if FUSE_BATCHNORM_RELU:
+            out = self.b1(self.c1(x), relu=True)
+            out = self.b2(self.c2(out), relu=True)
+        else:
+            out = A.relu(self.b1(self.c1(x)))
+            out = A.relu(self.b2(self.c2(out)))
         out = self.b3(self.c3(out))
         shortcut = self.down(x) if self.down is not None else x
         if FUSE_RESIDUAL_RELU:

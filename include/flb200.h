@@ -215,6 +215,24 @@ int flb200_batchnorm_backward(const flb200_batchnorm_desc* d, const void* grad_y
                               void* grad_x, float* grad_weight, float* grad_bias,
                               void* workspace, size_t workspace_bytes, void* stream);
 
+/* relu(batchnorm(x)) as one operator (the conv -> BatchNorm -> ReLU chain of
+ * flashlight/pkg/vision/models/Resnet.cpp:67-121): the apply pass clamps at zero, and the
+ * backward passes rebuild the relu predicate from x (the normalised value is recomputed with
+ * the very expression forward used), so the relu costs no pass of its own in either
+ * direction and nothing extra is saved.  Arguments as flb200_batchnorm_forward / _backward;
+ * backward also takes the bias (NULL = zeros) and grad_y is the gradient of the relu output. */
+int flb200_batchnorm_relu_forward(const flb200_batchnorm_desc* d, const void* x,
+                                  const float* weight, const float* bias,
+                                  float* running_mean, float* running_var,
+                                  float* save_mean, float* save_invstd, int train,
+                                  double momentum, double epsilon, void* y,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+int flb200_batchnorm_relu_backward(const flb200_batchnorm_desc* d, const void* grad_y,
+                                   const void* x, const float* weight, const float* bias,
+                                   const float* save_mean, const float* save_invstd,
+                                   void* grad_x, float* grad_weight, float* grad_bias,
+                                   void* workspace, size_t workspace_bytes, void* stream);
+
 /* --------------------------------------------------------- matmul (a9) */
 /* C[m,n] = alpha * sum_k A(m,k) B(k,n) + beta * C[m,n] on ROW-MAJOR views with
  * explicit element strides, so that every fl::matmul / matmulTN / matmulNT

@@ -138,6 +138,39 @@ def test_batchnorm_forward_backward(ext, shape, axes, affine):
     assert_close(yi, wyi, STRICT_TOL, "bn inference")
 
 
+@pytest.mark.parametrize("shape,axes", BN_CASES)
+@pytest.mark.parametrize("affine", [True, False])
+def test_batchnorm_relu_fused(ext, fx, shape, axes, affine):
+    """relu(batchnorm(x)) as one operator: the output equals the relu kernel applied to the plain
+    operator's output bit for bit, statistics are the plain operator's, and the gradients equal
+    the plain batchnorm gradient of the relu-masked dy (the oracle's chain) — the predicate is
+    rebuilt from x, nothing else is saved."""
+    x = randn(*shape, seed=10) * 1.7 + 0.4
+    ch = R.batchnorm_geometry(tuple(reversed(shape)), axes)[1]
+    w = (randn(ch, seed=11).abs() + 0.5) if affine else None
+    b = randn(ch, seed=12) if affine else None
+    xd = x.cuda()
+    y0, sm0, sv0 = ext.batchnorm(xd, dev(w), dev(b), None, None, axes, True, 0.0, 1e-5)
+    y1, sm1, sv1 = ext.batchnorm(xd, dev(w), dev(b), None, None, axes, True, 0.0, 1e-5, relu=True)
+    assert torch.equal(sm0, sm1) and torch.equal(sv0, sv1)
+    assert torch.equal(y1, fx.relu(y0))
+    gy = randn(*shape, seed=15).cuda()
+    masked = fx.relu_backward(y0, gy)
+    dx0, dg0, db0 = ext.batchnormBackward(masked, sm0, sv0, xd, dev(w), axes, True, 1e-5)
+    dx1, dg1, db1 = ext.batchnormReluBackward(gy, sm1, sv1, xd, dev(w), dev(b), axes, True, 1e-5)
+    assert torch.equal(dx0, dx1) and torch.equal(dg0, dg1) and torch.equal(db0, db1)
+    # and against the fp64 oracle's chain batchnorm -> relu
+    wy, *_ = R.batchnorm(x.double(), f64(w), f64(b), None, None, axes, True, 0.0, 1e-5)
+    assert_close(y1, R.relu(wy), STRICT_TOL, "bn+relu y")
+    # a predicate that flips between fp32 and fp64 at |y| ~ 1e-7 moves dx by one element's dy
+    # over the channel size, far below the bound
+    wdx, wdg, wdb = R.batchnorm_backward(R.relu_backward(wy, gy.cpu().double()), x.double(), f64(w),
+                                         axes, 1e-5)
+    assert_close(dx1, wdx, STRICT_TOL, "bn+relu dx")
+    assert_close(dg1, wdg, STRICT_TOL, "bn+relu dgamma")
+    assert_close(db1, wdb, STRICT_TOL, "bn+relu dbeta")
+
+
 def test_batchnorm_large_mean_is_well_conditioned(ext):
     x = randn(8, 32, 14, 14, seed=16) * 0.05 + 100.0
     y, sm, sv = ext.batchnorm(x.cuda(), None, None, None, None, [2], True, 0.0, 1e-5)
