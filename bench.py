@@ -237,6 +237,8 @@ def install_timers(timer: OpTimer, ext, F):
                                lambda out, x, *a, **k: (0.0, 2 * _numel_bytes(x)))
     ext.batchnormBackward = timer.wrap("batchnormBackward", ext.batchnormBackward,
                                        lambda out, gy, sm, sv, x, *a, **k: (0.0, 3 * _numel_bytes(x)))
+    ext.batchnormAddRelu = timer.wrap("batchnorm_add_relu", ext.batchnormAddRelu,
+                                      lambda out, x, *a, **k: (0.0, 3 * _numel_bytes(x)))
     ext.batchnormReluBackward = timer.wrap(
         "batchnormBackward", ext.batchnormReluBackward,
         lambda out, gy, sm, sv, x, *a, **k: (0.0, 3 * _numel_bytes(x)))

@@ -197,6 +197,45 @@ def batchnorm(x: Variable, weight: Optional[Variable], bias: Optional[Variable],
     return Variable(y, False, ins, grad_func)
 
 
+def batchnorm_add_relu(x: Variable, addend: Variable, weight: Optional[Variable],
+                       bias: Optional[Variable], running_mean, running_var, axes: Sequence[int],
+                       train: bool, momentum: float, epsilon: float) -> Variable:
+    """relu(batchnorm(x) + addend): the tail of a residual block.  Forward is the statistics
+    pass plus ONE apply pass that also reads the shortcut and writes the relu mask; backward is
+    the masked (two-consumer-summing) relu gradient, which is the addend's gradient, followed by
+    the batchnorm gradient.  Shapes the fused kernel does not take run the operators one by one."""
+    ext = extension()
+    if not ext.batchnormAddReluSupported(x.tensor, addend.tensor, axes):
+        return add_relu(batchnorm(x, weight, bias, running_mean, running_var, axes, train, momentum,
+                                  epsilon), addend)
+    wt = weight.tensor if weight is not None else None
+    bt = bias.tensor if bias is not None else None
+    xt = x.tensor
+    y, mask, save_mean, save_var = ext.batchnormAddRelu(xt, addend.tensor, wt, bt, running_mean,
+                                                        running_var, axes, train, momentum, epsilon)
+    ins = [x, addend] + ([weight] if weight is not None else []) + ([bias] if bias is not None else [])
+
+    def finish(inputs, gz):
+        inputs[1].addGrad(gz)
+        gx, gw, gb = ext.batchnormBackward(gz, save_mean, save_var, xt, wt, axes, train, epsilon, None)
+        inputs[0].addGrad(gx)
+        k = 2
+        if weight is not None:
+            inputs[k].addGrad(gw.reshape(wt.shape)); k += 1
+        if bias is not None:
+            inputs[k].addGrad(gb.reshape(bt.shape))
+
+    def grad_func(inputs, gy):
+        finish(inputs, F.relu_backward_mask(mask, _aligned(gy)))
+
+    def grad_func2(inputs, ga, gb):
+        finish(inputs, F.relu_backward_mask_sum(mask, _aligned(ga), _aligned(gb)))
+
+    out = Variable(y, False, ins, grad_func)
+    out.grad_func2 = grad_func2
+    return out
+
+
 def rnn(x: Variable, hx: Optional[Variable], cx: Optional[Variable], w: Variable, hidden: int,
         layers: int, mode: int, bidirectional: bool, dropout: float = 0.0):
     """fl::rnn (Functions.cpp:1606-1705): three outputs sharing one gradient computation."""

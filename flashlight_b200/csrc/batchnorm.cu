@@ -124,6 +124,43 @@ struct BnBwdApplyF {  // a = x, b = dy: dx = k1 * (dy - mb - (x - mean) * k4)
   }
 };
 
+// y = relu(batchnorm(x) + addend) and the bit mask of the predicate (bit i % 8 of byte i / 8 in
+// the tensor's linear order, the layout of the relu mask kernels): the last batchnorm of a
+// residual block fused with the block's join.  A thread owns 8 consecutive elements of one
+// channel row (inner % 8 == 0), i.e. two 16-byte vectors of each input and one mask byte.
+__global__ void __launch_bounds__(kChanThreads)
+bn_add_relu_apply_kernel(const float* __restrict__ x, const float* __restrict__ addend,
+                         float* __restrict__ y, uint8_t* __restrict__ mask, ChannelGeo g,
+                         const float* __restrict__ mean, const float* __restrict__ scale,
+                         const float* __restrict__ shift) {
+  const long long c = blockIdx.x;
+  const float m = mean[c], sc = scale[c], sh = shift ? shift[c] : 0.f;
+  long long begin = (long long)blockIdx.y * g.chunk;
+  long long end = begin + g.chunk;
+  if (end > g.per_channel) end = g.per_channel;
+  for (long long e = begin + (long long)threadIdx.x * 8; e < end; e += (long long)kChanThreads * 8) {
+    const long long off = channel_elem_offset(g, c, e);
+    const float4 a0 = *reinterpret_cast<const float4*>(x + off);
+    const float4 a1 = *reinterpret_cast<const float4*>(x + off + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(addend + off);
+    const float4 s1 = *reinterpret_cast<const float4*>(addend + off + 4);
+    const float z[8] = {bn_value(a0.x, m, sc, sh) + s0.x, bn_value(a0.y, m, sc, sh) + s0.y,
+                        bn_value(a0.z, m, sc, sh) + s0.z, bn_value(a0.w, m, sc, sh) + s0.w,
+                        bn_value(a1.x, m, sc, sh) + s1.x, bn_value(a1.y, m, sc, sh) + s1.y,
+                        bn_value(a1.z, m, sc, sh) + s1.z, bn_value(a1.w, m, sc, sh) + s1.w};
+    float r[8];
+    unsigned bits = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      r[j] = z[j] > 0.f ? z[j] : (z[j] != z[j] ? z[j] : 0.f);
+      bits |= (z[j] > 0.f ? 1u : 0u) << j;
+    }
+    *reinterpret_cast<float4*>(y + off) = make_float4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<float4*>(y + off + 4) = make_float4(r[4], r[5], r[6], r[7]);
+    mask[off >> 3] = (uint8_t)bits;
+  }
+}
+
 struct BiasAddF {
   const float* bias;
   struct K { float b; };
@@ -408,7 +445,8 @@ size_t flb200_batchnorm_workspace_bytes(const flb200_batchnorm_desc* d) {
          align_up((size_t)d->channels * sizeof(float4), 256);
 }
 
-static int batchnorm_forward_impl(bool relu, const flb200_batchnorm_desc* d, const void* x,
+static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
+                                  const flb200_batchnorm_desc* d, const void* x,
                                   const float* weight, const float* bias, float* running_mean,
                                   float* running_var, float* save_mean, float* save_invstd,
                                   int train, double momentum, double epsilon, void* y,
@@ -449,7 +487,13 @@ static int batchnorm_forward_impl(bool relu, const flb200_batchnorm_desc* d, con
     FLB200_AFTER_LAUNCH("batchnorm_infer_prepare");
     mean_ptr = running_mean;
   }
-  if (relu) {
+  if (addend) {
+    const ChannelGeo g = make_channel_geo(d->outer, C, d->inner);
+    bn_add_relu_apply_kernel<<<dim3((unsigned)C, (unsigned)g.splits), kChanThreads, 0, st>>>(
+        static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
+        mask, g, mean_ptr, scale, bias);
+    FLB200_AFTER_LAUNCH("batchnorm_add_relu_apply");
+  } else if (relu) {
     BnFwdApplyF<true> af{mean_ptr, scale, bias};
     FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_relu_forward",
                           rc = (launch_apply<T, 1>("batchnorm_relu_apply", x, nullptr, y, d->outer,
@@ -468,7 +512,8 @@ int flb200_batchnorm_forward(const flb200_batchnorm_desc* d, const void* x, cons
                              float* save_mean, float* save_invstd, int train, double momentum,
                              double epsilon, void* y, void* workspace, size_t workspace_bytes,
                              void* stream) {
-  return batchnorm_forward_impl(false, d, x, weight, bias, running_mean, running_var, save_mean,
+  return batchnorm_forward_impl(false, nullptr, nullptr, d, x, weight, bias, running_mean,
+                                running_var, save_mean,
                                 save_invstd, train, momentum, epsilon, y, workspace,
                                 workspace_bytes, stream);
 }
@@ -477,8 +522,26 @@ int flb200_batchnorm_relu_forward(const flb200_batchnorm_desc* d, const void* x,
                                   float* running_var, float* save_mean, float* save_invstd,
                                   int train, double momentum, double epsilon, void* y,
                                   void* workspace, size_t workspace_bytes, void* stream) {
-  return batchnorm_forward_impl(true, d, x, weight, bias, running_mean, running_var, save_mean,
+  return batchnorm_forward_impl(true, nullptr, nullptr, d, x, weight, bias, running_mean,
+                                running_var, save_mean,
                                 save_invstd, train, momentum, epsilon, y, workspace,
+                                workspace_bytes, stream);
+}
+
+int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void* x,
+                                      const void* addend, const float* weight, const float* bias,
+                                      float* running_mean, float* running_var, float* save_mean,
+                                      float* save_invstd, int train, double momentum,
+                                      double epsilon, void* y, uint8_t* mask, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+  FLB200_REQUIRE(d && addend && mask, "batchnorm_add_relu_forward: null argument");
+  if (d->dtype != FLB200_F32 || d->inner % 8 != 0 || !aligned16(x) || !aligned16(addend) ||
+      !aligned16(y))
+    return fail(FLB200_UNSUPPORTED,
+                "batchnorm_add_relu_forward: f32, 16-byte aligned tensors with a multiple of 8 "
+                "elements per channel row only");
+  return batchnorm_forward_impl(true, addend, mask, d, x, weight, bias, running_mean, running_var,
+                                save_mean, save_invstd, train, momentum, epsilon, y, workspace,
                                 workspace_bytes, stream);
 }
 

@@ -319,6 +319,31 @@ class B200AutogradExtension:
             ptr(grad_in), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes, stream_handle()))
         return grad_in, grad_w, grad_b
 
+    def batchnormAddReluSupported(self, input, addend, axes) -> bool:
+        d = self._bn_desc(input, axes)
+        return (input.dtype == torch.float32 and d.inner % 8 == 0 and addend.shape == input.shape
+                and addend.dtype == input.dtype and input.is_contiguous() and addend.is_contiguous()
+                and input.data_ptr() % 16 == 0 and addend.data_ptr() % 16 == 0)
+
+    def batchnormAddRelu(self, input, addend, weight, bias, runningMean, runningVar, axes, train,
+                         momentum, epsilon, payload=None):
+        """relu(batchnorm(input) + addend) with the predicate's bit mask: returns
+        (output, mask, saveMean, saveVar).  Check batchnormAddReluSupported first."""
+        d = self._bn_desc(input, axes)
+        out = torch.empty_like(input)
+        mask = torch.empty((input.numel() + 7) // 8, dtype=torch.uint8, device=input.device)
+        save_mean = save_var = None
+        if train:
+            save_mean = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+            save_var = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_batchnorm_add_relu_forward(
+            C.byref(d), ptr(input), ptr(addend), ptr(weight), ptr(bias), ptr(runningMean),
+            ptr(runningVar), ptr(save_mean), ptr(save_var), 1 if train else 0, float(momentum),
+            float(epsilon), ptr(out), ptr(mask), ptr(ws), nbytes, stream_handle()))
+        return out, mask, save_mean, save_var
+
     def batchnormReluBackward(self, gradOutput, saveMean, saveVar, input, weight, bias, axes, train,
                               epsilon, payload=None):
         """Gradient of relu(batchnorm(x)) given the gradient of the relu output: the predicate

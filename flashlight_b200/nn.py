@@ -127,10 +127,14 @@ class BatchNorm(Module):
         self.running_mean = torch.zeros(feat_size, device=device)
         self.running_var = torch.ones(feat_size, device=device)
 
-    def forward(self, x, relu=False):
-        """relu=True: the module's output is relu(batchnorm(x)), computed as one operator."""
+    def forward(self, x, relu=False, addend=None):
+        """relu=True: the module's output is relu(batchnorm(x)), computed as one operator;
+        with `addend` it is relu(batchnorm(x) + addend), a residual block's tail."""
         w = self.params[0] if self.params else None
         b = self.params[1] if self.params else None
+        if addend is not None:
+            return A.batchnorm_add_relu(x, addend, w, b, self.running_mean, self.running_var,
+                                        self.axes, self.train_mode, self.momentum, self.eps)
         return A.batchnorm(x, w, b, self.running_mean, self.running_var, self.axes, self.train_mode,
                            self.momentum, self.eps, relu=relu)
 

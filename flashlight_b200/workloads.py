@@ -59,8 +59,10 @@ class Bottleneck(nn.Module):
         else:
             out = A.relu(self.b1(self.c1(x)))
             out = A.relu(self.b2(self.c2(out)))
-        out = self.b3(self.c3(out))
         shortcut = self.down(x) if self.down is not None else x
+        if FUSE_BATCHNORM_RELU:
+            return self.b3(self.c3(out), addend=shortcut)
+        out = self.b3(self.c3(out))
         if FUSE_RESIDUAL_RELU:
             return A.add_relu(out, shortcut)
         return A.relu(A.add(out, shortcut))

@@ -227,6 +227,19 @@ int flb200_batchnorm_relu_forward(const flb200_batchnorm_desc* d, const void* x,
                                   float* save_mean, float* save_invstd, int train,
                                   double momentum, double epsilon, void* y,
                                   void* workspace, size_t workspace_bytes, void* stream);
+/* y = relu(batchnorm(x) + addend): the last BatchNorm of a residual block fused with the block's
+ * join (Resnet.cpp:67-121), plus the bit mask of the predicate in the layout of
+ * flb200_relu_forward_mask (ceil(n / 8) bytes).  Gradient: flb200_relu_backward_mask(_sum) gives
+ * the gradient of the sum (= the addend's gradient), flb200_batchnorm_backward of that gives the
+ * rest.  f32, 16-byte aligned, inner % 8 == 0; otherwise FLB200_UNSUPPORTED (run the two
+ * operators separately). */
+int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void* x,
+                                      const void* addend, const float* weight,
+                                      const float* bias, float* running_mean,
+                                      float* running_var, float* save_mean,
+                                      float* save_invstd, int train, double momentum,
+                                      double epsilon, void* y, uint8_t* mask, void* workspace,
+                                      size_t workspace_bytes, void* stream);
 int flb200_batchnorm_relu_backward(const flb200_batchnorm_desc* d, const void* grad_y,
                                    const void* x, const float* weight, const float* bias,
                                    const float* save_mean, const float* save_invstd,

@@ -171,6 +171,50 @@ def test_batchnorm_relu_fused(ext, fx, shape, axes, affine):
     assert_close(db1, wdb, STRICT_TOL, "bn+relu dbeta")
 
 
+@pytest.mark.parametrize("shape", [(8, 64, 28, 28), (4, 32, 4, 6), (2, 16, 8, 8)])
+def test_batchnorm_add_relu_fused(ext, fx, shape):
+    """relu(batchnorm(x) + shortcut) in one apply pass: output and mask bit for bit equal to the
+    batchnorm operator followed by the fused add + relu kernel; unsupported row lengths are
+    reported so that the caller runs the operators one by one."""
+    x = randn(*shape, seed=10) * 1.7 + 0.4
+    s = randn(*shape, seed=17)
+    ch = shape[1]
+    w, b = randn(ch, seed=11).abs() + 0.5, randn(ch, seed=12)
+    xd, sd = x.cuda(), s.cuda()
+    assert ext.batchnormAddReluSupported(xd, sd, [2])
+    y0, sm0, sv0 = ext.batchnorm(xd, w.cuda(), b.cuda(), None, None, [2], True, 0.0, 1e-5)
+    want_y, want_mask = fx.add_relu_with_mask(y0, sd)
+    y1, mask1, sm1, sv1 = ext.batchnormAddRelu(xd, sd, w.cuda(), b.cuda(), None, None, [2], True,
+                                               0.0, 1e-5)
+    assert torch.equal(y1, want_y) and torch.equal(mask1, want_mask)
+    assert torch.equal(sm0, sm1) and torch.equal(sv0, sv1)
+    odd = randn(2, 4, 7, 7, seed=3).cuda()   # 49 elements per channel row
+    assert not ext.batchnormAddReluSupported(odd, odd, [2])
+
+
+def test_tape_batchnorm_add_relu_matches_operator_chain():
+    """The tape's fused block tail gives the gradients of relu(add(batchnorm(x), s))."""
+    from flashlight_b200 import autograd as A
+    from flashlight_b200.autograd import Variable
+
+    def run(fused, shape):
+        x = Variable((randn(*shape, seed=81) * 1.3 + 0.2).cuda(), True)
+        s = Variable(randn(*shape, seed=82).cuda(), True)
+        w = Variable((randn(shape[1], seed=83).abs() + 0.5).cuda(), True)
+        b = Variable(randn(shape[1], seed=84).cuda(), True)
+        if fused:
+            y = A.batchnorm_add_relu(x, s, w, b, None, None, [2], True, 0.0, 1e-5)
+        else:
+            y = A.relu(A.add(A.batchnorm(x, w, b, None, None, [2], True, 0.0, 1e-5), s))
+        z = A.add(A.tanh(y), A.gelu(y))
+        z.backward(randn(*shape, seed=85).cuda())
+        return [t.clone() for t in (y.tensor, x.grad, s.grad, w.grad, b.grad)]
+
+    for shape in [(4, 16, 8, 8), (2, 8, 7, 7)]:  # fused kernel / fallback chain
+        for got, want in zip(run(True, shape), run(False, shape)):
+            assert torch.equal(got, want)
+
+
 def test_batchnorm_large_mean_is_well_conditioned(ext):
     x = randn(8, 32, 14, 14, seed=16) * 0.05 + 100.0
     y, sm, sv = ext.batchnorm(x.cuda(), None, None, None, None, [2], True, 0.0, 1e-5)
