@@ -29,7 +29,8 @@
 //   __device__ int  num_tiles() const;
 //   __device__ void decode(int tile, Tile&) const;
 //   __device__ int  k_begin(const Tile&) const;  __device__ int k_end(const Tile&) const;
-//   __device__ void load_begin(const Tile&, LoadState&, int lane) const;   // once per tile
+//   __device__ void load_begin(const Tile&, LoadState&, int copy) const;   // once per tile;
+//                        // copy = index of the stage's copy this lane will issue
 //   __device__ void load(const CUtensorMap* a, const CUtensorMap* b, const Tile&, LoadState&,
 //                        uint64_t* bar, char* a_dst, char* b_dst, int lane) const;
 //                        // one stage, called by the whole warp: lane 0 posts the byte count,
@@ -60,6 +61,14 @@ struct SmemLayout {
 constexpr int stages_for(int bn) { return bn >= 256 ? 4 : (bn >= 128 ? 6 : (bn >= 64 ? 8 : 10)); }
 constexpr int stages_for_x3(int bn) { return bn >= 256 ? 2 : (bn >= 128 ? 3 : (bn >= 64 ? 4 : 5)); }
 constexpr int kThreadsX3 = kThreads + 128;  // four more warps split the operands
+// Policies whose stage is several copies get a second producer warp (warp 6): issuing one TMA
+// copy costs the issuing warp ~110-130 clocks and copies issued from different lanes of one
+// warp still go out one after the other, so a stage of 5 to 12 copies took 650 to 1500 clocks
+// to issue against ~500 clocks of MMAs; two warps issue the even and the odd copies.
+template <class P, int X3>
+constexpr int threads_for() {
+  return X3 ? kThreadsX3 : (P::kWarpProducer ? kThreads + 32 : kThreads);
+}
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -83,7 +92,7 @@ static __device__ long long g_tc_profile[256 * 8];
 #endif
 
 template <class P, int BN, int STAGES, int X3 = 0, int KSUB = 1>
-__global__ void __launch_bounds__(X3 ? kThreadsX3 : kThreads)
+__global__ void __launch_bounds__(threads_for<P, X3>())
 tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
   using SL = SmemLayout<BN, STAGES, X3>;
@@ -128,10 +137,15 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  constexpr bool kTwoProducers = P::kWarpProducer && X3 == 0;
+  if (warp == 0 || (kTwoProducers && warp == 6)) {
     uint32_t s = 0, round = 0;
     typename P::Tile t;
     typename P::LoadState ls;
+    // part / parts: this warp issues the copies whose index is congruent to part mod parts;
+    // part 0 also posts the stage's byte count
+    const int part = warp == 0 ? 0 : 1;
+    constexpr int parts = kTwoProducers ? 2 : 1;
     if constexpr (P::kWarpProducer) {
       // All 32 lanes walk the loop: lane 0 waits for the stage to be free and posts the byte
       // count, then each lane issues one of the stage's copies (a single instruction for
@@ -144,7 +158,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         if (lane == 0) stop = *failed;
         if (__shfl_sync(0xffffffffu, stop, 0) != 0) break;
         prob.decode(tile, t);
-        prob.load_begin(t, ls, lane);
+        prob.load_begin(t, ls, lane * parts + part);  // the index of the copy this lane issues
         const int k1 = prob.k_end(t);
         for (int k = prob.k_begin(t); k < k1; k += KSUB) {
           int ok = 1;
@@ -164,13 +178,13 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             if (sub >= kn) break;
             char* a_dst = tiles + (s * KSUB + sub) * SL::kStageBytes;
             prob.load(&map_a, &map_b, t, ls, &full_bar[s], a_dst, a_dst + SL::kABytes, lane,
-                      sub == kn - 1);
+                      sub == kn - 1, part, parts);
           }
           if (++s == NG) { s = 0; ++round; }
         }
       }
 #ifdef FLB200_TC_PROFILE
-      if (lane == 0) { TC_PROF_PUT(0, p_wait); TC_PROF_PUT(1, clock64() - p_t0); }
+      if (lane == 0 && part == 0) { TC_PROF_PUT(0, p_wait); TC_PROF_PUT(1, clock64() - p_t0); }
 #endif
     } else if (lane == 0) {
       // Two copies per stage: one lane does everything and the loop has no warp exchange.
@@ -193,7 +207,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
             if (sub >= kn) break;
             char* a_dst = tiles + (s * KSUB + sub) * SL::kStageBytes;
             prob.load(&map_a, &map_b, t, ls, &full_bar[s], a_dst, a_dst + SL::kABytes, 0,
-                      sub == kn - 1);
+                      sub == kn - 1, 0, 1);
           }
           if (++s == NG) { s = 0; ++round; }
         }
@@ -328,7 +342,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         if (++s == NG) { s = 0; ++round; }
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     // epilogue warps 2..5 own TMEM lanes 32*(warp % 4) .. +31
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -414,19 +428,21 @@ struct GemmProblem {
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst, int lane, bool last) const {
-    if (lane == 0) mbar_post_tx(bar, (kBM + BN) * kBK * 4, last);
+                                       char* b_dst, int lane, bool last, int part,
+                                       int parts) const {
+    if (lane == 0 && part == 0) mbar_post_tx(bar, (kBM + BN) * kBK * 4, last);
     __syncwarp();
-    // a K-major operand is one box, an MN-major one a box per 32 rows: lanes [0, na) take A,
-    // lanes [na, na + nb) take B
+    // a K-major operand is one box, an MN-major one a box per 32 rows: copies [0, na) are A,
+    // [na, na + nb) are B; copy i is issued by lane i / parts of producer warp i % parts
     const int box_mn = bf16 ? 64 : 32, box_bytes = bf16 ? 8192 : kBK * 128;
     const int na = a_mn_major ? kBM / box_mn : 1, nb = b_mn_major ? BN / box_mn : 1;
-    if (lane < na) {
+    const int copy = lane * parts + part;
+    if (copy < na) {
       int c[4];
-      operand_coords(a, t.m0 + box_mn * lane, ls.a_lo, ls.a_hi, t.z, c);
-      tma_load(ma, bar, a_dst + lane * box_bytes, a.rank, c);
-    } else if (lane < na + nb) {
-      const int j = lane - na;
+      operand_coords(a, t.m0 + box_mn * copy, ls.a_lo, ls.a_hi, t.z, c);
+      tma_load(ma, bar, a_dst + copy * box_bytes, a.rank, c);
+    } else if (copy < na + nb) {
+      const int j = copy - na;
       int c[4];
       operand_coords(b, t.n0 + box_mn * j, ls.b_lo, ls.b_hi, t.z, c);
       tma_load(mb, bar, b_dst + j * box_bytes, b.rank, c);
@@ -579,7 +595,7 @@ int launch_problem_as(const char* name, const CUtensorMap& ma, const CUtensorMap
   }
   const long long sms = device_info().sm_count;
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  tc_persistent_kernel<P, BN, STAGES, X3, KSUB><<<grid, X3 ? kThreadsX3 : kThreads, SL::kTotal, st>>>(
+  tc_persistent_kernel<P, BN, STAGES, X3, KSUB><<<grid, threads_for<P, X3>(), SL::kTotal, st>>>(
       ma, mb, prob, status_ptr());
   FLB200_AFTER_LAUNCH(name);
   count_tc_launch();

@@ -125,7 +125,7 @@ struct PatchConvProblem {
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst, int, bool last) const {
+                                       char* b_dst, int, bool last, int, int) const {
     mbar_post_tx(bar, (kBM + BN) * kBK * 4, last);  // NB*PH*QW == 128 rows of 128 bytes + B tile
     int ca[4] = {ls.cc * kBK, ls.aw, ls.ah, t.b0};
     tma_load(ma, bar, a_dst, 4, ca);
@@ -223,34 +223,37 @@ struct PatchWgradProblem {
   }
   __device__ __forceinline__ int k_begin(const Tile& t) const { return t.k0; }
   __device__ __forceinline__ int k_end(const Tile& t) const { return t.k1; }
-  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls, int lane) const {
+  __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls, int copy) const {
     int r = t.k0;
     ls.qi = r % tiles_q; r /= tiles_q;
     ls.pi = r % tiles_p; r /= tiles_p;
     ls.img = r;
-    // lane 0 copies dy, lane j >= 1 the x box of tap tap0 + j - 1
-    const int tap = t.tap0 + max(lane - 1, 0);
+    // copy 0 is dy, copy j >= 1 the x box of tap tap0 + j - 1
+    const int tap = t.tap0 + max(copy - 1, 0);
     const int tr = tap / kW, ts = tap - tr * kW;
     ls.dw = ts * dil_x - pad_x;
     ls.dh = tr * dil_y - pad_y;
   }
   __device__ __forceinline__ void load(const CUtensorMap* ma, const CUtensorMap* mb,
                                        const Tile& t, LoadState& ls, uint64_t* bar, char* a_dst,
-                                       char* b_dst, int lane, bool last) const {
+                                       char* b_dst, int lane, bool last, int part,
+                                       int parts) const {
     const int q0 = ls.qi * QW, p0 = ls.pi * PH;
+    const int copy = lane * parts + part;
     // The channel index is split into (32 contiguous channels, group of 32) in both maps, so
     // one copy brings every 32 x 32 box of an operand: a_nbox boxes of dy, and per tap
     // 1 << cn_shift boxes of x.  Boxes past the last channel are zero-filled or hold a
     // neighbouring pixel's channels; they only reach accumulator rows / columns that the
     // epilogue never stores.
-    if (lane == 0) mbar_post_tx(bar, (a_nbox + (t.ntap << cn_shift)) * (kBK * 128), last);
+    if (lane == 0 && part == 0)
+      mbar_post_tx(bar, (a_nbox + (t.ntap << cn_shift)) * (kBK * 128), last);
     __syncwarp();
-    if (lane == 0) {
+    if (copy == 0) {
       int ca[5] = {0, q0, p0, ls.img, t.m0 >> 5};
       tma_load(ma, bar, a_dst, 5, ca);
-    } else if (lane <= t.ntap) {
+    } else if (copy <= t.ntap) {
       int cb[5] = {0, q0 * b_w_mul + ls.dw, p0 * b_h_mul + ls.dh, ls.img, t.n0 >> 5};
-      tma_load(mb, bar, b_dst + ((lane - 1) << cn_shift) * (kBK * 128), 5, cb);
+      tma_load(mb, bar, b_dst + ((copy - 1) << cn_shift) * (kBK * 128), 5, cb);
     }
     if (++ls.qi == tiles_q) {
       ls.qi = 0;
