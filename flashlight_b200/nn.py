@@ -139,6 +139,13 @@ class BatchNorm(Module):
                            self.momentum, self.eps, relu=relu)
 
 
+class BatchNormReLU(BatchNorm):
+    """fl::BatchNorm followed by fl::ReLU as one operator (same parameters and statistics)."""
+
+    def forward(self, x, relu=True, addend=None):
+        return super().forward(x, relu=relu, addend=addend)
+
+
 class LayerNorm(Module):
     """fl::LayerNorm (flashlight/fl/nn/modules/LayerNorm.cpp:42-131): batchnorm over the
     complement of the normalised axes with momentum 0, then a separate affine over the

@@ -93,8 +93,11 @@ def resnet50(seed: int = 1234, device: str = "cuda", blocks=(3, 4, 6, 3), classe
     gen = torch.Generator().manual_seed(seed)
     m = nn.Sequential()
     m.add(nn.Conv2D(3, width, 7, 7, 2, 2, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device))
-    m.add(nn.BatchNorm(2, width, gen=gen, device=device))
-    m.add(nn.ReLU())
+    if FUSE_BATCHNORM_RELU:
+        m.add(nn.BatchNormReLU(2, width, gen=gen, device=device))
+    else:
+        m.add(nn.BatchNorm(2, width, gen=gen, device=device))
+        m.add(nn.ReLU())
     m.add(nn.Pool2D(3, 3, 2, 2, nn.SAME, nn.SAME, L.POOL_MAX))
     in_c = width
     for i, nb in enumerate(blocks):
