@@ -302,14 +302,14 @@ bool is_window(const PoolGeo& g, int wx, int wy, int sx, int sy) {
 // Band height for the tiled kernels: enough outputs per CTA to occupy 256 threads, tile within
 // 40 KB.  Returns 0 when a single band does not fit (very wide planes): generic kernels then.
 int pool_fwd_band_rows(const PoolGeo& g) {
-  int rows = (512 + g.Wo - 1) / g.Wo;
+  int rows = (1024 + g.Wo - 1) / g.Wo;  // ~1024 outputs per CTA (measured best of 256..4096)
   if (rows > g.Ho) rows = g.Ho;
   while (rows > 1 && (size_t)((rows - 1) * g.sy + g.wy) * g.W * 4 > 40 * 1024) --rows;
   if ((size_t)((rows - 1) * g.sy + g.wy) * g.W * 4 > 40 * 1024) return 0;
   return rows;
 }
 int pool_bwd_band_rows(const PoolGeo& g, int* max_out_rows) {
-  int rows = (2048 + g.W - 1) / g.W;  // ~512 strips of four pixels
+  int rows = (16384 + g.W - 1) / g.W;  // ~4096 strips of four pixels (measured best of 1K..16K)
   if (rows > g.H) rows = g.H;
   for (;; --rows) {
     const int outs = (rows + g.wy - 2) / g.sy + 2;
