@@ -239,6 +239,9 @@ def install_timers(timer: OpTimer, ext, F):
                                        lambda out, gy, sm, sv, x, *a, **k: (0.0, 3 * _numel_bytes(x)))
     ext.batchnormAddRelu = timer.wrap("batchnorm_add_relu", ext.batchnormAddRelu,
                                       lambda out, x, *a, **k: (0.0, 3 * _numel_bytes(x)))
+    ext.batchnormAddReluBackward = timer.wrap(
+        "batchnorm_add_relu_backward", ext.batchnormAddReluBackward,
+        lambda out, mask, ga, gb, sm, sv, x, *a, **k: (0.0, 5 * _numel_bytes(x)))
     ext.batchnormReluBackward = timer.wrap(
         "batchnormBackward", ext.batchnormReluBackward,
         lambda out, gy, sm, sv, x, *a, **k: (0.0, 3 * _numel_bytes(x)))

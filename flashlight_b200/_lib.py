@@ -92,6 +92,8 @@ SIGNATURES = {
                                                 C.c_int, f64, f64, vp, vp, sz, vp]),
     "flb200_batchnorm_add_relu_forward": (C.c_int, [P(BatchnormDesc), vp, vp, vp, vp, vp, vp, vp,
                                                     vp, C.c_int, f64, f64, vp, vp, vp, sz, vp]),
+    "flb200_batchnorm_add_relu_backward": (C.c_int, [P(BatchnormDesc), vp, vp, vp, vp, vp, vp, vp,
+                                                     vp, vp, vp, vp, vp, sz, vp]),
     "flb200_batchnorm_relu_backward": (C.c_int, [P(BatchnormDesc), vp, vp, vp, vp, vp, vp, vp, vp,
                                                  vp, vp, sz, vp]),
     "flb200_matmul_workspace_bytes": (sz, [P(MatmulDesc)]),

@@ -215,21 +215,21 @@ def batchnorm_add_relu(x: Variable, addend: Variable, weight: Optional[Variable]
                                                         running_var, axes, train, momentum, epsilon)
     ins = [x, addend] + ([weight] if weight is not None else []) + ([bias] if bias is not None else [])
 
-    def finish(inputs, gz):
+    def grad_func2(inputs, ga, gb):
+        # the first batch-norm pass forms mask ? ga + gb : 0, writes it and reduces it
+        gz, gx, gw, gbias = ext.batchnormAddReluBackward(
+            mask, _aligned(ga), _aligned(gb) if gb is not None else None, save_mean, save_var, xt,
+            wt, axes, train, epsilon, None)
         inputs[1].addGrad(gz)
-        gx, gw, gb = ext.batchnormBackward(gz, save_mean, save_var, xt, wt, axes, train, epsilon, None)
         inputs[0].addGrad(gx)
         k = 2
         if weight is not None:
             inputs[k].addGrad(gw.reshape(wt.shape)); k += 1
         if bias is not None:
-            inputs[k].addGrad(gb.reshape(bt.shape))
+            inputs[k].addGrad(gbias.reshape(bt.shape))
 
     def grad_func(inputs, gy):
-        finish(inputs, F.relu_backward_mask(mask, _aligned(gy)))
-
-    def grad_func2(inputs, ga, gb):
-        finish(inputs, F.relu_backward_mask_sum(mask, _aligned(ga), _aligned(gb)))
+        grad_func2(inputs, gy, None)
 
     out = Variable(y, False, ins, grad_func)
     out.grad_func2 = grad_func2

@@ -161,6 +161,54 @@ bn_add_relu_apply_kernel(const float* __restrict__ x, const float* __restrict__ 
   }
 }
 
+// First pass of the batch-norm gradient at a residual block's tail.  The gradient that reaches
+// the batch-norm is the relu gradient of the join, mask ? (ga + gb) : 0, where ga and gb come
+// from the join's two consumers (gb may be null).  Instead of a relu-gradient kernel that
+// writes that tensor and a reduction pass that reads it back, this pass forms it, writes it
+// (it is also the shortcut's gradient and the apply pass's input) and reduces it in one go:
+// s0 = sum g, s1 = sum g * (x - mean).  8 consecutive elements of a channel row per thread.
+__global__ void __launch_bounds__(kChanThreads)
+bn_tail_backward_reduce_kernel(const float* __restrict__ x, const float* __restrict__ ga,
+                               const float* __restrict__ gb, const uint8_t* __restrict__ mask,
+                               float* __restrict__ gz, float2* __restrict__ partial, ChannelGeo g,
+                               const float* __restrict__ mean) {
+  __shared__ float scratch[32];
+  const long long c = blockIdx.x;
+  const float m = mean[c];
+  long long begin = (long long)blockIdx.y * g.chunk;
+  long long end = begin + g.chunk;
+  if (end > g.per_channel) end = g.per_channel;
+  float s0 = 0.f, s1 = 0.f;
+  for (long long e = begin + (long long)threadIdx.x * 8; e < end; e += (long long)kChanThreads * 8) {
+    const long long off = channel_elem_offset(g, c, e);
+    const float4 x0 = *reinterpret_cast<const float4*>(x + off);
+    const float4 x1 = *reinterpret_cast<const float4*>(x + off + 4);
+    float4 a0 = *reinterpret_cast<const float4*>(ga + off);
+    float4 a1 = *reinterpret_cast<const float4*>(ga + off + 4);
+    if (gb) {
+      const float4 b0 = *reinterpret_cast<const float4*>(gb + off);
+      const float4 b1 = *reinterpret_cast<const float4*>(gb + off + 4);
+      a0 = make_float4(a0.x + b0.x, a0.y + b0.y, a0.z + b0.z, a0.w + b0.w);
+      a1 = make_float4(a1.x + b1.x, a1.y + b1.y, a1.z + b1.z, a1.w + b1.w);
+    }
+    const unsigned bits = mask[off >> 3];
+    const float v[8] = {bits & 1u ? a0.x : 0.f,  bits & 2u ? a0.y : 0.f,  bits & 4u ? a0.z : 0.f,
+                        bits & 8u ? a0.w : 0.f,  bits & 16u ? a1.x : 0.f, bits & 32u ? a1.y : 0.f,
+                        bits & 64u ? a1.z : 0.f, bits & 128u ? a1.w : 0.f};
+    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    *reinterpret_cast<float4*>(gz + off) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(gz + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s0 += v[j];
+      s1 += v[j] * (xs[j] - m);
+    }
+  }
+  s0 = block_sum(s0, scratch);
+  s1 = block_sum(s1, scratch);
+  if (threadIdx.x == 0) partial[c * g.splits + blockIdx.y] = make_float2(s0, s1);
+}
+
 struct BiasAddF {
   const float* bias;
   struct K { float b; };
@@ -545,8 +593,12 @@ int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void
                                 workspace_bytes, stream);
 }
 
-static int batchnorm_backward_impl(bool relu, const flb200_batchnorm_desc* d, const void* grad_y,
-                                   const void* x, const float* weight, const float* bias,
+// tail_mask != null: grad_y / tail_gb are the join's two incoming gradients (tail_gb may be
+// null), tail_sum receives mask ? grad_y + tail_gb : 0 and is what the batch-norm differentiates.
+static int batchnorm_backward_impl(bool relu, const uint8_t* tail_mask, const void* tail_gb,
+                                   void* tail_sum, const flb200_batchnorm_desc* d,
+                                   const void* grad_y, const void* x, const float* weight,
+                                   const float* bias,
                                    const float* save_mean, const float* save_invstd, void* grad_x,
                                    float* grad_weight, float* grad_bias, void* workspace,
                                    size_t workspace_bytes, void* stream) {
@@ -566,7 +618,16 @@ static int batchnorm_backward_impl(bool relu, const flb200_batchnorm_desc* d, co
   off += align_up((size_t)C * sizeof(float), 256);
   float4* coef = reinterpret_cast<float4*>(ws + off);
   int rc = FLB200_OK, splits = 0;
-  if (relu) {
+  if (tail_mask) {
+    const ChannelGeo g = make_channel_geo(d->outer, C, d->inner);
+    bn_tail_backward_reduce_kernel<<<dim3((unsigned)C, (unsigned)g.splits), kChanThreads, 0, st>>>(
+        static_cast<const float*>(x), static_cast<const float*>(grad_y),
+        static_cast<const float*>(tail_gb), tail_mask, static_cast<float*>(tail_sum), partial, g,
+        save_mean);
+    FLB200_AFTER_LAUNCH("batchnorm_tail_backward_reduce");
+    splits = g.splits;
+    grad_y = tail_sum;
+  } else if (relu) {
     BnReluBwdReduceF rf{save_mean, save_invstd, weight, bias};
     FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_relu_backward",
                           rc = (launch_reduce<T, 2>("batchnorm_relu_backward_reduce", x, grad_y,
@@ -603,7 +664,8 @@ int flb200_batchnorm_backward(const flb200_batchnorm_desc* d, const void* grad_y
                               const float* save_invstd, void* grad_x, float* grad_weight,
                               float* grad_bias, void* workspace, size_t workspace_bytes,
                               void* stream) {
-  return batchnorm_backward_impl(false, d, grad_y, x, weight, nullptr, save_mean, save_invstd,
+  return batchnorm_backward_impl(false, nullptr, nullptr, nullptr, d, grad_y, x, weight, nullptr,
+                                 save_mean, save_invstd,
                                  grad_x, grad_weight, grad_bias, workspace, workspace_bytes,
                                  stream);
 }
@@ -612,8 +674,25 @@ int flb200_batchnorm_relu_backward(const flb200_batchnorm_desc* d, const void* g
                                    const float* save_mean, const float* save_invstd,
                                    void* grad_x, float* grad_weight, float* grad_bias,
                                    void* workspace, size_t workspace_bytes, void* stream) {
-  return batchnorm_backward_impl(true, d, grad_y, x, weight, bias, save_mean, save_invstd, grad_x,
-                                 grad_weight, grad_bias, workspace, workspace_bytes, stream);
+  return batchnorm_backward_impl(true, nullptr, nullptr, nullptr, d, grad_y, x, weight, bias,
+                                 save_mean, save_invstd, grad_x, grad_weight, grad_bias, workspace,
+                                 workspace_bytes, stream);
+}
+int flb200_batchnorm_add_relu_backward(const flb200_batchnorm_desc* d, const uint8_t* mask,
+                                       const void* grad_y_a, const void* grad_y_b, const void* x,
+                                       const float* weight, const float* save_mean,
+                                       const float* save_invstd, void* grad_sum, void* grad_x,
+                                       float* grad_weight, float* grad_bias, void* workspace,
+                                       size_t workspace_bytes, void* stream) {
+  FLB200_REQUIRE(d && mask && grad_y_a && grad_sum, "batchnorm_add_relu_backward: null argument");
+  if (d->dtype != FLB200_F32 || d->inner % 8 != 0 || !aligned16(x) || !aligned16(grad_y_a) ||
+      !aligned16(grad_sum) || (grad_y_b && !aligned16(grad_y_b)))
+    return fail(FLB200_UNSUPPORTED,
+                "batchnorm_add_relu_backward: f32, 16-byte aligned tensors with a multiple of 8 "
+                "elements per channel row only");
+  return batchnorm_backward_impl(false, mask, grad_y_b, grad_sum, d, grad_y_a, x, weight, nullptr,
+                                 save_mean, save_invstd, grad_x, grad_weight, grad_bias, workspace,
+                                 workspace_bytes, stream);
 }
 
 }  // extern "C"

@@ -344,6 +344,25 @@ class B200AutogradExtension:
             float(epsilon), ptr(out), ptr(mask), ptr(ws), nbytes, stream_handle()))
         return out, mask, save_mean, save_var
 
+    def batchnormAddReluBackward(self, mask, gradA, gradB, saveMean, saveVar, input, weight, axes,
+                                 train, epsilon, payload=None):
+        """Gradient of batchnormAddRelu: returns (gradSum, gradInput, gradWeight, gradBias) where
+        gradSum = mask ? gradA + gradB : 0 is the addend's gradient (gradB may be None)."""
+        if not train:
+            raise RuntimeError("can't compute batchnorm grad when train was not specified")
+        d = self._bn_desc(input, axes)
+        grad_sum = torch.empty_like(input)
+        grad_in = torch.empty_like(input)
+        grad_w = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        grad_b = torch.empty(d.channels, dtype=torch.float32, device=input.device)
+        nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
+        ws = workspace(nbytes, input)
+        L.check(L.lib.flb200_batchnorm_add_relu_backward(
+            C.byref(d), ptr(mask), ptr(gradA), ptr(gradB), ptr(input), ptr(weight), ptr(saveMean),
+            ptr(saveVar), ptr(grad_sum), ptr(grad_in), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes,
+            stream_handle()))
+        return grad_sum, grad_in, grad_w, grad_b
+
     def batchnormReluBackward(self, gradOutput, saveMean, saveVar, input, weight, bias, axes, train,
                               epsilon, payload=None):
         """Gradient of relu(batchnorm(x)) given the gradient of the relu output: the predicate

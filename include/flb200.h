@@ -240,6 +240,17 @@ int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void
                                       float* save_invstd, int train, double momentum,
                                       double epsilon, void* y, uint8_t* mask, void* workspace,
                                       size_t workspace_bytes, void* stream);
+/* Gradient of flb200_batchnorm_add_relu_forward given the gradients of its output's consumers
+ * (grad_y_b may be NULL): grad_sum = mask ? grad_y_a + grad_y_b : 0 is written (the addend's
+ * gradient) while the first batch-norm pass reduces it, then grad_x / grad_weight / grad_bias
+ * as flb200_batchnorm_backward.  Same shape restrictions as the forward call. */
+int flb200_batchnorm_add_relu_backward(const flb200_batchnorm_desc* d, const uint8_t* mask,
+                                       const void* grad_y_a, const void* grad_y_b,
+                                       const void* x, const float* weight,
+                                       const float* save_mean, const float* save_invstd,
+                                       void* grad_sum, void* grad_x, float* grad_weight,
+                                       float* grad_bias, void* workspace,
+                                       size_t workspace_bytes, void* stream);
 int flb200_batchnorm_relu_backward(const flb200_batchnorm_desc* d, const void* grad_y,
                                    const void* x, const float* weight, const float* bias,
                                    const float* save_mean, const float* save_invstd,

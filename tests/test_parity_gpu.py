@@ -190,6 +190,18 @@ def test_batchnorm_add_relu_fused(ext, fx, shape):
     assert torch.equal(sm0, sm1) and torch.equal(sv0, sv1)
     odd = randn(2, 4, 7, 7, seed=3).cuda()   # 49 elements per channel row
     assert not ext.batchnormAddReluSupported(odd, odd, [2])
+    # gradient: the join's relu gradient formed inside the first batch-norm pass
+    ga, gb = randn(*shape, seed=18).cuda(), randn(*shape, seed=19).cuda()
+    for second in (gb, None):
+        gz0 = fx.relu_backward_mask_sum(mask1, ga, second) if second is not None else \
+            fx.relu_backward_mask(mask1, ga)
+        dx0, dg0, db0 = ext.batchnormBackward(gz0, sm0, sv0, xd, w.cuda(), [2], True, 1e-5)
+        gz1, dx1, dg1, db1 = ext.batchnormAddReluBackward(mask1, ga, second, sm1, sv1, xd, w.cuda(),
+                                                          [2], True, 1e-5)
+        assert torch.equal(gz0, gz1)
+        assert_close(dx1, dx0.cpu().double(), 1e-5, "block tail dx")
+        assert_close(dg1, dg0.cpu().double(), 1e-5, "block tail dgamma")
+        assert_close(db1, db0.cpu().double(), 1e-5, "block tail dbeta")
 
 
 def test_tape_batchnorm_add_relu_matches_operator_chain():
@@ -210,9 +222,13 @@ def test_tape_batchnorm_add_relu_matches_operator_chain():
         z.backward(randn(*shape, seed=85).cuda())
         return [t.clone() for t in (y.tensor, x.grad, s.grad, w.grad, b.grad)]
 
-    for shape in [(4, 16, 8, 8), (2, 8, 7, 7)]:  # fused kernel / fallback chain
-        for got, want in zip(run(True, shape), run(False, shape)):
-            assert torch.equal(got, want)
+    for shape in [(4, 16, 8, 8), (2, 8, 7, 7)]:  # fused kernels / fallback chain
+        got, want = run(True, shape), run(False, shape)
+        assert torch.equal(got[0], want[0])   # y
+        assert torch.equal(got[2], want[2])   # shortcut gradient: mask ? ga + gb : 0
+        # the fused first pass sums the channel in a different order than the generic one
+        for g, w, what in zip(got[1::2][:1] + got[3:], want[1::2][:1] + want[3:], ("dx", "dgamma", "dbeta")):
+            assert_close(g, w.cpu().double(), 1e-5, f"fused block tail {what}")
 
 
 def test_batchnorm_large_mean_is_well_conditioned(ext):
