@@ -124,40 +124,44 @@ struct BnBwdApplyF {  // a = x, b = dy: dx = k1 * (dy - mb - (x - mean) * k4)
   }
 };
 
-// y = relu(batchnorm(x) + addend) and the bit mask of the predicate (bit i % 8 of byte i / 8 in
-// the tensor's linear order, the layout of the relu mask kernels): the last batchnorm of a
-// residual block fused with the block's join.  A thread owns 8 consecutive elements of one
-// channel row (inner % 8 == 0), i.e. two 16-byte vectors of each input and one mask byte.
+// y = relu(batchnorm(x) + addend) and the bit mask of the predicate: the last batchnorm of a
+// residual block fused with the block's join.  A thread owns G consecutive elements of one
+// channel row (G = 8 when rows are a multiple of 8 elements, else 4) and one mask byte:
+// bit j of byte (offset / G) belongs to element offset + j.
+template <int G>
 __global__ void __launch_bounds__(kChanThreads)
 bn_add_relu_apply_kernel(const float* __restrict__ x, const float* __restrict__ addend,
                          float* __restrict__ y, uint8_t* __restrict__ mask, ChannelGeo g,
                          const float* __restrict__ mean, const float* __restrict__ scale,
                          const float* __restrict__ shift) {
+  constexpr int NV = G / 4;
   const long long c = blockIdx.x;
   const float m = mean[c], sc = scale[c], sh = shift ? shift[c] : 0.f;
   long long begin = (long long)blockIdx.y * g.chunk;
   long long end = begin + g.chunk;
   if (end > g.per_channel) end = g.per_channel;
-  for (long long e = begin + (long long)threadIdx.x * 8; e < end; e += (long long)kChanThreads * 8) {
+  for (long long e = begin + (long long)threadIdx.x * G; e < end; e += (long long)kChanThreads * G) {
     const long long off = channel_elem_offset(g, c, e);
-    const float4 a0 = *reinterpret_cast<const float4*>(x + off);
-    const float4 a1 = *reinterpret_cast<const float4*>(x + off + 4);
-    const float4 s0 = *reinterpret_cast<const float4*>(addend + off);
-    const float4 s1 = *reinterpret_cast<const float4*>(addend + off + 4);
-    const float z[8] = {bn_value(a0.x, m, sc, sh) + s0.x, bn_value(a0.y, m, sc, sh) + s0.y,
-                        bn_value(a0.z, m, sc, sh) + s0.z, bn_value(a0.w, m, sc, sh) + s0.w,
-                        bn_value(a1.x, m, sc, sh) + s1.x, bn_value(a1.y, m, sc, sh) + s1.y,
-                        bn_value(a1.z, m, sc, sh) + s1.z, bn_value(a1.w, m, sc, sh) + s1.w};
-    float r[8];
+    float4 a[NV], s[NV];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      a[v] = *reinterpret_cast<const float4*>(x + off + 4 * v);
+      s[v] = *reinterpret_cast<const float4*>(addend + off + 4 * v);
+    }
     unsigned bits = 0;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      r[j] = z[j] > 0.f ? z[j] : (z[j] != z[j] ? z[j] : 0.f);
-      bits |= (z[j] > 0.f ? 1u : 0u) << j;
+    for (int v = 0; v < NV; ++v) {
+      const float z[4] = {bn_value(a[v].x, m, sc, sh) + s[v].x, bn_value(a[v].y, m, sc, sh) + s[v].y,
+                          bn_value(a[v].z, m, sc, sh) + s[v].z, bn_value(a[v].w, m, sc, sh) + s[v].w};
+      float r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        r[j] = z[j] > 0.f ? z[j] : (z[j] != z[j] ? z[j] : 0.f);
+        bits |= (z[j] > 0.f ? 1u : 0u) << (4 * v + j);
+      }
+      *reinterpret_cast<float4*>(y + off + 4 * v) = make_float4(r[0], r[1], r[2], r[3]);
     }
-    *reinterpret_cast<float4*>(y + off) = make_float4(r[0], r[1], r[2], r[3]);
-    *reinterpret_cast<float4*>(y + off + 4) = make_float4(r[4], r[5], r[6], r[7]);
-    mask[off >> 3] = (uint8_t)bits;
+    mask[off / G] = (uint8_t)bits;
   }
 }
 
@@ -166,12 +170,15 @@ bn_add_relu_apply_kernel(const float* __restrict__ x, const float* __restrict__ 
 // from the join's two consumers (gb may be null).  Instead of a relu-gradient kernel that
 // writes that tensor and a reduction pass that reads it back, this pass forms it, writes it
 // (it is also the shortcut's gradient and the apply pass's input) and reduces it in one go:
-// s0 = sum g, s1 = sum g * (x - mean).  8 consecutive elements of a channel row per thread.
+// s0 = sum g, s1 = sum g * (x - mean).  G consecutive elements of a channel row per thread,
+// mask layout as above.
+template <int G>
 __global__ void __launch_bounds__(kChanThreads)
 bn_tail_backward_reduce_kernel(const float* __restrict__ x, const float* __restrict__ ga,
                                const float* __restrict__ gb, const uint8_t* __restrict__ mask,
                                float* __restrict__ gz, float2* __restrict__ partial, ChannelGeo g,
                                const float* __restrict__ mean) {
+  constexpr int NV = G / 4;
   __shared__ float scratch[32];
   const long long c = blockIdx.x;
   const float m = mean[c];
@@ -179,29 +186,27 @@ bn_tail_backward_reduce_kernel(const float* __restrict__ x, const float* __restr
   long long end = begin + g.chunk;
   if (end > g.per_channel) end = g.per_channel;
   float s0 = 0.f, s1 = 0.f;
-  for (long long e = begin + (long long)threadIdx.x * 8; e < end; e += (long long)kChanThreads * 8) {
+  for (long long e = begin + (long long)threadIdx.x * G; e < end; e += (long long)kChanThreads * G) {
     const long long off = channel_elem_offset(g, c, e);
-    const float4 x0 = *reinterpret_cast<const float4*>(x + off);
-    const float4 x1 = *reinterpret_cast<const float4*>(x + off + 4);
-    float4 a0 = *reinterpret_cast<const float4*>(ga + off);
-    float4 a1 = *reinterpret_cast<const float4*>(ga + off + 4);
-    if (gb) {
-      const float4 b0 = *reinterpret_cast<const float4*>(gb + off);
-      const float4 b1 = *reinterpret_cast<const float4*>(gb + off + 4);
-      a0 = make_float4(a0.x + b0.x, a0.y + b0.y, a0.z + b0.z, a0.w + b0.w);
-      a1 = make_float4(a1.x + b1.x, a1.y + b1.y, a1.z + b1.z, a1.w + b1.w);
-    }
-    const unsigned bits = mask[off >> 3];
-    const float v[8] = {bits & 1u ? a0.x : 0.f,  bits & 2u ? a0.y : 0.f,  bits & 4u ? a0.z : 0.f,
-                        bits & 8u ? a0.w : 0.f,  bits & 16u ? a1.x : 0.f, bits & 32u ? a1.y : 0.f,
-                        bits & 64u ? a1.z : 0.f, bits & 128u ? a1.w : 0.f};
-    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-    *reinterpret_cast<float4*>(gz + off) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(gz + off + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    float4 xv[NV], av[NV];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      s0 += v[j];
-      s1 += v[j] * (xs[j] - m);
+    for (int v = 0; v < NV; ++v) {
+      xv[v] = *reinterpret_cast<const float4*>(x + off + 4 * v);
+      av[v] = *reinterpret_cast<const float4*>(ga + off + 4 * v);
+      if (gb) {
+        const float4 b = *reinterpret_cast<const float4*>(gb + off + 4 * v);
+        av[v] = make_float4(av[v].x + b.x, av[v].y + b.y, av[v].z + b.z, av[v].w + b.w);
+      }
+    }
+    const unsigned bits = mask[off / G];
+#pragma unroll
+    for (int v = 0; v < NV; ++v) {
+      const unsigned b4 = bits >> (4 * v);
+      const float4 r = make_float4(b4 & 1u ? av[v].x : 0.f, b4 & 2u ? av[v].y : 0.f,
+                                   b4 & 4u ? av[v].z : 0.f, b4 & 8u ? av[v].w : 0.f);
+      *reinterpret_cast<float4*>(gz + off + 4 * v) = r;
+      s0 += (r.x + r.y) + (r.z + r.w);
+      s1 += r.x * (xv[v].x - m) + r.y * (xv[v].y - m) + r.z * (xv[v].z - m) + r.w * (xv[v].w - m);
     }
   }
   s0 = block_sum(s0, scratch);
@@ -537,9 +542,15 @@ static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
   }
   if (addend) {
     const ChannelGeo g = make_channel_geo(d->outer, C, d->inner);
-    bn_add_relu_apply_kernel<<<dim3((unsigned)C, (unsigned)g.splits), kChanThreads, 0, st>>>(
-        static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
-        mask, g, mean_ptr, scale, bias);
+    const dim3 grid((unsigned)C, (unsigned)g.splits);
+    if (d->inner % 8 == 0)
+      bn_add_relu_apply_kernel<8><<<grid, kChanThreads, 0, st>>>(
+          static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
+          mask, g, mean_ptr, scale, bias);
+    else
+      bn_add_relu_apply_kernel<4><<<grid, kChanThreads, 0, st>>>(
+          static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
+          mask, g, mean_ptr, scale, bias);
     FLB200_AFTER_LAUNCH("batchnorm_add_relu_apply");
   } else if (relu) {
     BnFwdApplyF<true> af{mean_ptr, scale, bias};
@@ -583,10 +594,10 @@ int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void
                                       double epsilon, void* y, uint8_t* mask, void* workspace,
                                       size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d && addend && mask, "batchnorm_add_relu_forward: null argument");
-  if (d->dtype != FLB200_F32 || d->inner % 8 != 0 || !aligned16(x) || !aligned16(addend) ||
+  if (d->dtype != FLB200_F32 || d->inner % 4 != 0 || !aligned16(x) || !aligned16(addend) ||
       !aligned16(y))
     return fail(FLB200_UNSUPPORTED,
-                "batchnorm_add_relu_forward: f32, 16-byte aligned tensors with a multiple of 8 "
+                "batchnorm_add_relu_forward: f32, 16-byte aligned tensors with a multiple of 4 "
                 "elements per channel row only");
   return batchnorm_forward_impl(true, addend, mask, d, x, weight, bias, running_mean, running_var,
                                 save_mean, save_invstd, train, momentum, epsilon, y, workspace,
@@ -620,10 +631,17 @@ static int batchnorm_backward_impl(bool relu, const uint8_t* tail_mask, const vo
   int rc = FLB200_OK, splits = 0;
   if (tail_mask) {
     const ChannelGeo g = make_channel_geo(d->outer, C, d->inner);
-    bn_tail_backward_reduce_kernel<<<dim3((unsigned)C, (unsigned)g.splits), kChanThreads, 0, st>>>(
-        static_cast<const float*>(x), static_cast<const float*>(grad_y),
-        static_cast<const float*>(tail_gb), tail_mask, static_cast<float*>(tail_sum), partial, g,
-        save_mean);
+    const dim3 grid((unsigned)C, (unsigned)g.splits);
+    if (d->inner % 8 == 0)
+      bn_tail_backward_reduce_kernel<8><<<grid, kChanThreads, 0, st>>>(
+          static_cast<const float*>(x), static_cast<const float*>(grad_y),
+          static_cast<const float*>(tail_gb), tail_mask, static_cast<float*>(tail_sum), partial, g,
+          save_mean);
+    else
+      bn_tail_backward_reduce_kernel<4><<<grid, kChanThreads, 0, st>>>(
+          static_cast<const float*>(x), static_cast<const float*>(grad_y),
+          static_cast<const float*>(tail_gb), tail_mask, static_cast<float*>(tail_sum), partial, g,
+          save_mean);
     FLB200_AFTER_LAUNCH("batchnorm_tail_backward_reduce");
     splits = g.splits;
     grad_y = tail_sum;
@@ -685,10 +703,10 @@ int flb200_batchnorm_add_relu_backward(const flb200_batchnorm_desc* d, const uin
                                        float* grad_weight, float* grad_bias, void* workspace,
                                        size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d && mask && grad_y_a && grad_sum, "batchnorm_add_relu_backward: null argument");
-  if (d->dtype != FLB200_F32 || d->inner % 8 != 0 || !aligned16(x) || !aligned16(grad_y_a) ||
+  if (d->dtype != FLB200_F32 || d->inner % 4 != 0 || !aligned16(x) || !aligned16(grad_y_a) ||
       !aligned16(grad_sum) || (grad_y_b && !aligned16(grad_y_b)))
     return fail(FLB200_UNSUPPORTED,
-                "batchnorm_add_relu_backward: f32, 16-byte aligned tensors with a multiple of 8 "
+                "batchnorm_add_relu_backward: f32, 16-byte aligned tensors with a multiple of 4 "
                 "elements per channel row only");
   return batchnorm_backward_impl(false, mask, grad_y_b, grad_sum, d, grad_y_a, x, weight, nullptr,
                                  save_mean, save_invstd, grad_x, grad_weight, grad_bias, workspace,

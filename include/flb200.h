@@ -228,11 +228,11 @@ int flb200_batchnorm_relu_forward(const flb200_batchnorm_desc* d, const void* x,
                                   double momentum, double epsilon, void* y,
                                   void* workspace, size_t workspace_bytes, void* stream);
 /* y = relu(batchnorm(x) + addend): the last BatchNorm of a residual block fused with the block's
- * join (Resnet.cpp:67-121), plus the bit mask of the predicate in the layout of
- * flb200_relu_forward_mask (ceil(n / 8) bytes).  Gradient: flb200_relu_backward_mask(_sum) gives
- * the gradient of the sum (= the addend's gradient), flb200_batchnorm_backward of that gives the
- * rest.  f32, 16-byte aligned, inner % 8 == 0; otherwise FLB200_UNSUPPORTED (run the two
- * operators separately). */
+ * join (Resnet.cpp:67-121), plus the bit mask of the predicate for
+ * flb200_batchnorm_add_relu_backward: `mask` needs ceil(n / 4) bytes (rows of a multiple of 8
+ * elements use one byte per 8 elements, in the layout of flb200_relu_forward_mask; other rows
+ * one byte per 4).  f32, 16-byte aligned, inner % 4 == 0; otherwise FLB200_UNSUPPORTED (run
+ * the two operators separately). */
 int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void* x,
                                       const void* addend, const float* weight,
                                       const float* bias, float* running_mean,
