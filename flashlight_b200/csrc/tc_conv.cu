@@ -235,7 +235,9 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
   const int bn = tc::pick_bn(g.Cout);
   if (direct_1x1(g)) {
     if (int rc = map3d(&ma, x, g.HW, g.C, g.N, g.HW, (long long)g.C * g.HW, 32, true)) return rc;
-    if (int rc = map2d(&mb, w, g.C, g.Cout, g.C, bn, false)) return rc;
+    // a K-major B tile is one box of all the tile's rows, or of half of them on CTA pairs
+    const long long k_iters = (g.C + tc::kBK - 1) / tc::kBK;
+    if (int rc = map2d(&mb, w, g.C, g.Cout, g.C, tc::b_box_rows(g.HW, g.Cout, k_iters, true, false), false)) return rc;
     tc::OperandPlan pa = plan_mn_major(3), pb = plan_k_major(2);
     pa.z_dim = 2;
     ep.m_stride = 1;
@@ -262,7 +264,7 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
     wsrc = wp;
   }
   if (int rc = map2d(&ma, col, s.ld_out, s.kc, s.ld_out, 32, true)) return rc;
-  if (int rc = map2d(&mb, wsrc, s.kc, g.Cout, s.kp, bn, false)) return rc;
+  if (int rc = map2d(&mb, wsrc, s.kc, g.Cout, s.kp, tc::b_box_rows(s.ld_out, g.Cout, (s.kc + tc::kBK - 1) / tc::kBK, true, false), false)) return rc;
   ep.m_div = s.hwp_out;
   ep.m_valid = g.HoWo;
   ep.m_outer = (long long)g.Cout * g.HoWo;
@@ -305,7 +307,7 @@ int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, flo
   transpose_filter_kernel<<<grid_for((long long)g.C * s.k2p, 256), 256, 0, st>>>(w, wt, g, s.k2p);
   FLB200_AFTER_LAUNCH("transpose_filter");
   if (int rc = map2d(&ma, col, s.ld_in, s.k2, s.ld_in, 32, true)) return rc;
-  if (int rc = map2d(&mb, wt, s.k2, g.C, s.k2p, bn, false)) return rc;
+  if (int rc = map2d(&mb, wt, s.k2, g.C, s.k2p, tc::b_box_rows(s.ld_in, g.C, (s.k2 + tc::kBK - 1) / tc::kBK, true, false), false)) return rc;
   ep.m_div = s.hwp_in;
   ep.m_valid = g.HW;
   ep.m_outer = (long long)g.C * g.HW;

@@ -162,6 +162,8 @@ int pick_bn(long long N) {
 bool gemm_uses_pairs(long long M, long long N, long long k_iters, bool a_mn_major,
                      bool b_mn_major) {
   if (x3_enabled()) return false;  // the CTA-pair kernel has no 3xTF32 instantiation
+  // MN-major operands run correctly on pairs but slower (measured 2-24 % on the 1x1 layers):
+  // their stage is 8 copies per CTA, issued by the pair kernel's single producer warp.
   return pick_bn(N) >= 128 && M > kBM && !a_mn_major && !b_mn_major && k_iters >= 64;
 }
 int b_box_rows(long long M, long long N, long long k_iters, bool a_mn_major, bool b_mn_major) {
