@@ -75,8 +75,9 @@ int pick_bn(long long N);
 // Whether an M x N contraction runs on CTA pairs (two SMs per 256 x BN tile, each loading half
 // of the B tile), and the number of rows a K-major B map must put in one box accordingly.
 // Pairs pay off when both operands are K-major single boxes and the K loop is long (the
-// backward-filter shapes); tiles with a short K loop lose more to the cross-CTA hand-offs
-// per tile than they gain (measured).
+// backward-filter shapes), and for an MN-major A with a K-major B at 256 columns (the 1x1
+// forward layers); tiles with a short K loop lose more to the cross-CTA hand-offs per tile
+// than they gain (measured).  Every K-major B map must take its box rows from b_box_rows.
 bool gemm_uses_pairs(long long M, long long N, long long k_iters, bool a_mn_major,
                      bool b_mn_major);
 int b_box_rows(long long M, long long N, long long k_iters, bool a_mn_major, bool b_mn_major);

@@ -469,15 +469,16 @@ struct GemmProblem {
   }
   __device__ __forceinline__ void load_pair(const CUtensorMap* ma, const CUtensorMap* mb,
                                             const Tile& t, LoadState& ls, uint32_t full_bar,
-                                            char* a_dst, char* b_dst, int rank, int lane) const {
-    // this CTA's 128 rows of A and its BN/2 columns of B
+                                            char* a_dst, char* b_dst, int rank, int copy) const {
+    // this CTA's 128 rows of A and its BN/2 columns of B; `copy` = which of the stage's copies
+    // the calling lane issues
     const int na = a_mn_major ? kBM / 32 : 1, nb = b_mn_major ? BN / 64 : 1;
-    if (lane < na) {
+    if (copy < na) {
       int c[4];
-      operand_coords(a, t.m0 + 32 * lane, ls.a_lo, ls.a_hi, t.z, c);
-      tma_load_pair(ma, full_bar, a_dst + lane * (kBK * 128), a.rank, c);
-    } else if (lane < na + nb) {
-      const int j = lane - na;
+      operand_coords(a, t.m0 + 32 * copy, ls.a_lo, ls.a_hi, t.z, c);
+      tma_load_pair(ma, full_bar, a_dst + copy * (kBK * 128), a.rank, c);
+    } else if (copy < na + nb) {
+      const int j = copy - na;
       int c[4];
       operand_coords(b, t.n0 + rank * (BN / 2) + 32 * j, ls.b_lo, ls.b_hi, t.z, c);
       tma_load_pair(mb, full_bar, b_dst + j * (kBK * 128), b.rank, c);

@@ -46,8 +46,13 @@ struct PairSmemLayout {
 };
 constexpr int pair_stages_for(int bn) { return bn >= 256 ? 6 : 8; }
 
+// Threads: the six warps of tc_kernel.cuh plus, for policies whose stage is several copies, a
+// second producer warp (warp 6) that issues every other copy.
+template <class P>
+constexpr int pair_threads_for() { return P::kWarpProducer ? kThreads + 32 : kThreads; }
+
 template <class P, int BN, int STAGES, int KSUB = 2>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(pair_threads_for<P>())
 tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
   using SL = PairSmemLayout<BN, STAGES>;
@@ -90,9 +95,12 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  constexpr bool kTwoProducers = P::kWarpProducer;
+  if (warp == 0 || (kTwoProducers && warp == 6)) {
     // The whole warp walks the loop (see tc_kernel.cuh): lane 0 owns the barriers, lane i
-    // issues copy i of the stage.
+    // issues copy i * parts + part of the stage; the leader's part 0 posts the byte count.
+    const int part = warp == 0 ? 0 : 1;
+    constexpr int parts = kTwoProducers ? 2 : 1;
     uint32_t s = 0, round = 0;
     typename P::Tile t;
     typename P::LoadState ls;
@@ -107,7 +115,7 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         break;
       }
       prob.decode_pair(tile, (int)rank, t);
-      prob.load_begin(t, ls, lane);
+      prob.load_begin(t, ls, lane * parts + part);
       const int k1 = prob.k_end(t);
       for (int k = prob.k_begin(t); k < k1; k += KSUB) {
         const int kn = min(KSUB, k1 - k);
@@ -117,7 +125,7 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if (round > 0 && !mbar_wait(&empty_bar[s], (round - 1) & 1)) {
             *failed = 1;
             ok = 0;
-          } else if (rank == 0) {
+          } else if (rank == 0 && part == 0) {
             mbar_expect_tx(&full_bar[s], kn * 2 * SL::kStageBytes);
           }
         }
@@ -132,17 +140,17 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
           if (sub >= kn) break;
           char* a_dst = tiles + (s * KSUB + sub) * SL::kStageBytes;
           prob.load_pair(&map_a, &map_b, t, ls, full_leader, a_dst, a_dst + SL::kABytes,
-                         (int)rank, lane);
+                         (int)rank, lane * parts + part);
         }
         if (++s == NG) { s = 0; ++round; }
       }
     }
 #ifdef FLB200_TC_PROFILE
-    if (lane == 0) { TC_PROF_PUT(0, p_wait); TC_PROF_PUT(1, clock64() - p_t0); }
+    if (lane == 0 && part == 0) { TC_PROF_PUT(0, p_wait); TC_PROF_PUT(1, clock64() - p_t0); }
 #endif
     // The leader's last commits still arrive on this CTA's empty barriers: wait for them
     // so that the CTA does not leave while they are in flight.
-    if (live && lane == 0 && *failed == 0) {
+    if (live && lane == 0 && part == 0 && *failed == 0) {
       for (int i = 0; i < NG; ++i) {
         const uint32_t fills = round + (static_cast<uint32_t>(i) < s ? 1u : 0u);
         if (fills > 0 && !mbar_wait(&empty_bar[i], (fills - 1) & 1)) {
@@ -208,7 +216,7 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       TC_PROF_PUT(2, m_full); TC_PROF_PUT(3, m_acc); TC_PROF_PUT(4, clock64() - m_t0);
 #endif
     }
-  } else {
+  } else if (warp >= 2 && warp < 6) {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     uint32_t nt = 0;
@@ -278,7 +286,7 @@ int launch_pair_problem(const char* name, const CUtensorMap& ma, const CUtensorM
   const unsigned grid = 2u * (unsigned)(pair_tiles < pairs ? pair_tiles : pairs);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(pair_threads_for<P>());
   cfg.dynamicSmemBytes = SL::kTotal;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
