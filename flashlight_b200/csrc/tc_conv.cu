@@ -285,9 +285,18 @@ int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, flo
   if (direct_1x1(g)) {
     if (int rc = map3d(&ma, gy, g.HW, g.Cout, g.N, g.HW, (long long)g.Cout * g.HW, 32, true))
       return rc;
-    // B(k = co, n = ci) = w[co][ci]: the n index is contiguous
-    if (int rc = map2d(&mb, w, g.C, g.Cout, g.C, 32, true)) return rc;
+    // B(k = co, n = ci) = w[co][ci]: the n index is contiguous.  With a multiple of 32 input
+    // channels the map splits ci into (32, group) and the whole B tile is one copy.
     tc::OperandPlan pa = plan_mn_major(3), pb = plan_mn_major(2);
+    if (g.C % 32 == 0) {
+      const uint64_t dims[3] = {32, (uint64_t)g.Cout, (uint64_t)(g.C / 32)};
+      const uint64_t strides[2] = {(uint64_t)g.C * 4, 128};
+      const uint32_t box[3] = {32, 32, (uint32_t)(bn / 32)};
+      if (int rc = tc::make_tensor_map(&mb, w, 3, dims, strides, box, tc::kMapMnMajor)) return rc;
+      pb.rank = 3; pb.mn_dim = 2; pb.k_dim = 1; pb.mn_grouped = 1;
+    } else if (int rc = map2d(&mb, w, g.C, g.Cout, g.C, 32, true)) {
+      return rc;
+    }
     pa.z_dim = 2;
     ep.m_stride = 1;
     ep.n_stride = g.HW;

@@ -238,7 +238,8 @@ __device__ __forceinline__ void operand_coords(const OperandCoords& p, int mn, i
                                                int z, int* c) {
 #pragma unroll
   for (int d = 0; d < 4; ++d)
-    c[d] = p.base[d] + mn * p.mn_mul[d] + k_lo * p.k_mul[d] + k_hi * p.k2_mul[d] + z * p.z_mul[d];
+    c[d] = p.base[d] + (mn >> p.mn_shift) * p.mn_mul[d] + k_lo * p.k_mul[d] +
+           k_hi * p.k2_mul[d] + z * p.z_mul[d];
 }
 
 // ------------------------------------------------------ CTA pairs (cta_group::2)

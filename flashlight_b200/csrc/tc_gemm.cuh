@@ -33,6 +33,10 @@ struct OperandPlan {
   int k2_scale;  // coordinate step per k_hi
   int base[4];
   int k_elems;   // elements per stage along K: 0 = kBK (fp32), 64 for 2-byte operands
+  // MN-major fp32 operand whose m / n extent is a multiple of 32: the map splits that index
+  // into (32 contiguous, group of 32) and mn_dim is the GROUP dimension, so ONE copy of
+  // `tile rows / 32` groups lands as the same consecutive 32 x 32 boxes as one copy per box.
+  int mn_grouped;
 };
 
 // The same plan flattened for the device: per-dimension multipliers of the tile offset, the
@@ -40,10 +44,12 @@ struct OperandPlan {
 struct OperandCoords {
   int rank, mn_major, k_inner;
   int base[4], mn_mul[4], k_mul[4], k2_mul[4], z_mul[4];
+  int mn_shift;  // 5 for a grouped MN-major operand (the coordinate counts groups of 32), else 0
 };
 inline OperandCoords make_coords(const OperandPlan& p) {
   OperandCoords c{};
   c.rank = p.rank; c.mn_major = p.mn_major; c.k_inner = p.k_inner;
+  c.mn_shift = p.mn_grouped ? 5 : 0;
   for (int d = 0; d < 4; ++d) {
     c.base[d] = p.base[d];
     c.mn_mul[d] = d == p.mn_dim ? 1 : 0;

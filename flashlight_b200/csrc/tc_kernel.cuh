@@ -435,7 +435,8 @@ struct GemmProblem {
     // a K-major operand is one box, an MN-major one a box per 32 rows: copies [0, na) are A,
     // [na, na + nb) are B; copy i is issued by lane i / parts of producer warp i % parts
     const int box_mn = bf16 ? 64 : 32, box_bytes = bf16 ? 8192 : kBK * 128;
-    const int na = a_mn_major ? kBM / box_mn : 1, nb = b_mn_major ? BN / box_mn : 1;
+    const int na = a_mn_major && !a.mn_shift ? kBM / box_mn : 1;
+    const int nb = b_mn_major && !b.mn_shift ? BN / box_mn : 1;  // grouped: one copy
     const int copy = lane * parts + part;
     if (copy < na) {
       int c[4];
