@@ -281,6 +281,22 @@ def test_pool2d(ext, mode, geo, with_payload):
         assert torch.equal(payload.data.argmax.cpu(), torch.from_numpy(arg))
 
 
+@pytest.mark.parametrize("mode", [R.POOL_AVG_INCLUDE_PAD, R.POOL_AVG_EXCLUDE_PAD])
+def test_global_average_pool(ext, mode):
+    """The ResNet head: one 7x7 window over an unpadded 7x7 plane (the gradient has a kernel of
+    its own: every pixel receives dy / 49)."""
+    x = randn(5, 11, 7, 7, seed=27)
+    y = ext.pool2d(x.cuda(), 7, 7, 1, 1, 0, 0, mode, None)
+    want = R.pool2d(x.double(), 7, 7, 1, 1, 0, 0, mode)
+    assert tuple(y.shape) == (5, 11, 1, 1)
+    assert_close(y, want, 1e-5, "global average pool")
+    gy = randn(5, 11, 1, 1, seed=28)
+    gx = ext.pool2dBackward(gy.cuda(), x.cuda(), y, 7, 7, 1, 1, 0, 0, mode, None)
+    assert_close(gx, R.pool2d_backward(gy.double(), x.double(), 7, 7, 1, 1, 0, 0, mode), 1e-6,
+                 "global average pool gradient")
+    assert torch.equal(gx.cpu(), (gy / 49.0).expand(5, 11, 7, 7))
+
+
 @pytest.mark.parametrize("geo", [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1)])
 def test_max_pool_ties_after_relu(ext, geo):
     """Half the activations are exactly zero after ReLU: ties must resolve like the oracle."""
