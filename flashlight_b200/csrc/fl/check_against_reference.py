@@ -7,6 +7,7 @@ Flashlight binary needs ArrayFire and cereal, which this image does not have.
 Usage: python check_against_reference.py [reference_root]
 """
 import subprocess
+import os
 import sys
 from pathlib import Path
 
@@ -15,7 +16,8 @@ ROOT = HERE.parent.parent.parent
 
 
 def main() -> int:
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    ref = Path(sys.argv[1] if len(sys.argv) > 1 else
+               os.environ.get("FLASHLIGHT_REFERENCE", "/root/reference"))
     if not (ref / "flashlight/fl/autograd/tensor/AutogradExtension.h").exists():
         print(f"reference headers not found under {ref}: nothing checked")
         return 0

@@ -8,7 +8,8 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-REFERENCE = Path("/root/reference")
+# checkout of the flashlight project, where present (FLASHLIGHT_REFERENCE overrides the default)
+REFERENCE = Path(os.environ.get("FLASHLIGHT_REFERENCE", "/root/reference"))
 
 
 def pytest_configure(config):
