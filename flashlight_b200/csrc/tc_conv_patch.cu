@@ -258,11 +258,12 @@ bool patch_uses_pairs(int bn) { return bn >= 256 && !tc::x3_enabled(); }
 // filter_box_rows(bn) rows per box.
 struct PatchArgs {
   Patch patch;
-  int pix_w, pix_h, images, n_out, cchunks, ntaps, a_w_mul, a_h_mul;
-  tc::TapGrid taps;
+  int pix_w, pix_h, images, n_out, cchunks, a_w_mul, a_h_mul;
+  int ncls;                                   // parity classes in this launch (1 = forward)
+  tc::PatchClass cls[tc::kMaxPatchClasses];   // taps and output offsets of each
   float* out;
   const float* bias;
-  int out_H, out_W, out_C, oh_mul, oh_add, ow_mul, ow_add, fill_cell;
+  int out_H, out_W, out_C, oh_mul, ow_mul, fill_cell;
 };
 int filter_box_rows(int bn) { return patch_uses_pairs(bn) ? bn / 2 : bn; }
 
@@ -276,22 +277,24 @@ int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, 
   p.tiles_p = (a.pix_h + p.PH - 1) / p.PH;
   p.tiles_b = (a.images + p.NB - 1) / p.NB;
   p.pix_w = a.pix_w; p.pix_h = a.pix_h; p.images = a.images; p.n_out = a.n_out;
-  p.cchunks = a.cchunks; p.ntaps = a.ntaps; p.a_w_mul = a.a_w_mul; p.a_h_mul = a.a_h_mul;
-  p.taps = a.taps;
+  p.cchunks = a.cchunks; p.a_w_mul = a.a_w_mul; p.a_h_mul = a.a_h_mul;
+  p.ncls = a.ncls;
+  for (int c = 0; c < tc::kMaxPatchClasses; ++c) p.cls[c] = a.cls[c < a.ncls ? c : 0];
   p.out = a.out; p.bias = a.bias;
   p.out_H = a.out_H; p.out_W = a.out_W; p.out_C = a.out_C;
-  p.oh_mul = a.oh_mul; p.oh_add = a.oh_add; p.ow_mul = a.ow_mul; p.ow_add = a.ow_add;
+  p.oh_mul = a.oh_mul; p.ow_mul = a.ow_mul;
   p.fill_cell = a.fill_cell;
   p.tiles_n = (p.n_out + BN - 1) / BN;
   const long long m_tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b;
-  FLB200_REQUIRE(m_tiles * p.tiles_n < 0x7fffffffLL, "patch conv: too many tiles");
+  FLB200_REQUIRE(a.ncls >= 1 && a.ncls <= tc::kMaxPatchClasses, "patch conv: bad class count");
+  FLB200_REQUIRE(m_tiles * p.tiles_n * a.ncls < 0x7fffffffLL, "patch conv: too many tiles");
   if constexpr (BN >= 256) {
     if (patch_uses_pairs(BN))
     return tc::launch_pair_problem<tc::PatchConvProblem<BN>, BN, 2>(
-        "tc_patch_conv_pair", ma, mb, p, ((m_tiles + 1) / 2) * p.tiles_n, st);
+        "tc_patch_conv_pair", ma, mb, p, ((m_tiles + 1) / 2) * p.tiles_n * a.ncls, st);
   }
   return tc::launch_problem<tc::PatchConvProblem<BN>, BN>("tc_patch_conv", ma, mb, p,
-                                                          m_tiles * p.tiles_n, st);
+                                                          m_tiles * p.tiles_n * a.ncls, st);
 }
 int run_patch_any(int bn, const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a,
                   cudaStream_t st) {
@@ -505,9 +508,10 @@ int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const 
   a.patch = pick_patch(g.Wo, g.Ho, g.N);
   a.pix_w = g.Wo; a.pix_h = g.Ho; a.images = g.N; a.n_out = g.Cout;
   a.cchunks = (g.C + tc::kBK - 1) / tc::kBK;
-  a.ntaps = g.RS;
   a.a_w_mul = g.sx; a.a_h_mul = g.sy;
-  a.taps = tc::TapGrid{g.kH, g.kW, -g.py, g.dy, -g.px, g.dx, 0, 1, 0, 1, g.kW};
+  a.ncls = 1;
+  a.cls[0] = tc::PatchClass{tc::TapGrid{g.kH, g.kW, -g.py, g.dy, -g.px, g.dx, 0, 1, 0, 1, g.kW},
+                            g.RS, 0, 0};
   a.out = y; a.bias = bias;
   a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
   a.oh_mul = 1; a.ow_mul = 1;
@@ -575,32 +579,51 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
   const bool fill_cell = live == 1 && origin_live && empty > 0;
   if (empty > 0 && !fill_cell)
     FLB200_CUDA_CHECK(cudaMemsetAsync(gx, 0, (size_t)g.N * g.C * g.HW * 4, st));
+  // The classes of one launch must have the same pixel extent (H, W multiples of the stride)
+  // and fit the policy's class table; then ONE launch walks all of them, the classes of a
+  // pixel patch as consecutive tiles, so that their interleaved stores meet in L2.  Otherwise
+  // one launch per class.
+  // (Measured on the ResNet-50 layers: 15-31 % faster with 256-column tiles, 6 % slower at 128.)
+  const bool merge = !fill_cell && live > 1 && live <= tc::kMaxPatchClasses && g.H % g.sy == 0 &&
+                     g.W % g.sx == 0 && bn >= 256;
+  PatchArgs a{};
+  a.images = g.N; a.n_out = g.C;
+  a.cchunks = (g.Cout + tc::kBK - 1) / tc::kBK;
+  a.a_w_mul = 1; a.a_h_mul = 1;
+  a.out = gx; a.bias = nullptr;
+  a.out_H = g.H; a.out_W = g.W; a.out_C = g.C;
+  a.oh_mul = g.sy; a.ow_mul = g.sx;
+  a.fill_cell = fill_cell ? 1 : 0;
+  auto launch = [&](PatchArgs& args) -> int {
+    args.patch = pick_patch(args.pix_w, args.pix_h, g.N);
+    CUtensorMap ma;
+    if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, args.patch.QW, args.patch.PH,
+                          args.patch.NB, 1, 1, tc::kMapKMajor))
+      return rc;
+    return run_patch_any(bn, ma, mb, args, st);
+  };
   for (int ca = 0; ca < g.sy; ++ca)
     for (int cb = 0; cb < g.sx; ++cb) {
       const Prog ph = progression(ca, g.py, g.dy, g.sy, g.kH);
       const Prog pw = progression(cb, g.px, g.dx, g.sx, g.kW);
       if (ph.count == 0 || pw.count == 0) continue;
-      PatchArgs a{};
-      a.pix_h = (g.H - ca + g.sy - 1) / g.sy;
-      a.pix_w = (g.W - cb + g.sx - 1) / g.sx;
-      if (a.pix_h <= 0 || a.pix_w <= 0) continue;
-      a.taps = tc::TapGrid{ph.count, pw.count, ph.off0, ph.off_step, pw.off0, pw.off_step,
-                           ph.first, ph.step, pw.first, pw.step, g.kW};
-      a.patch = pick_patch(a.pix_w, a.pix_h, g.N);
-      a.images = g.N; a.n_out = g.C;
-      a.cchunks = (g.Cout + tc::kBK - 1) / tc::kBK;
-      a.ntaps = ph.count * pw.count;
-      a.a_w_mul = 1; a.a_h_mul = 1;
-      a.out = gx; a.bias = nullptr;
-      a.out_H = g.H; a.out_W = g.W; a.out_C = g.C;
-      a.oh_mul = g.sy; a.oh_add = ca; a.ow_mul = g.sx; a.ow_add = cb;
-      a.fill_cell = fill_cell ? 1 : 0;
-      CUtensorMap ma;
-      if (int rc = nhwc_map(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, a.patch.QW, a.patch.PH,
-                            a.patch.NB, 1, 1, tc::kMapKMajor))
-        return rc;
-      if (int rc = run_patch_any(bn, ma, mb, a, st)) return rc;
+      const int pix_h = (g.H - ca + g.sy - 1) / g.sy, pix_w = (g.W - cb + g.sx - 1) / g.sx;
+      if (pix_h <= 0 || pix_w <= 0) continue;
+      const tc::PatchClass pc{
+          tc::TapGrid{ph.count, pw.count, ph.off0, ph.off_step, pw.off0, pw.off_step, ph.first,
+                      ph.step, pw.first, pw.step, g.kW},
+          ph.count * pw.count, ca, cb};
+      a.pix_h = pix_h; a.pix_w = pix_w;
+      if (merge) {
+        a.cls[a.ncls++] = pc;
+      } else {
+        a.ncls = 1;
+        a.cls[0] = pc;
+        if (int rc = launch(a)) return rc;
+      }
     }
+  if (merge && a.ncls > 0)
+    if (int rc = launch(a)) return rc;
   return FLB200_OK;
 }
 
@@ -708,9 +731,9 @@ int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const 
   FLB200_AFTER_LAUNCH("pack_filter_rows");
   a.pix_w = g.Wo; a.pix_h = g.Ho; a.images = g.N; a.n_out = g.Cout;
   a.cchunks = 1;
-  a.ntaps = g.kH;
   a.a_w_mul = g.sx; a.a_h_mul = g.sy;
-  a.taps = tc::TapGrid{g.kH, 1, 0, g.dy, 0, 0, 0, 1, 0, 0, 1};  // tap r: row offset r*dy, filter row r
+  a.ncls = 1;  // tap r: row offset r*dy, filter row r
+  a.cls[0] = tc::PatchClass{tc::TapGrid{g.kH, 1, 0, g.dy, 0, 0, 0, 1, 0, 0, 1}, g.kH, 0, 0};
   a.out = y; a.bias = bias;
   a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
   a.oh_mul = 1; a.ow_mul = 1;

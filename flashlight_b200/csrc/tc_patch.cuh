@@ -39,6 +39,14 @@ struct TapGrid {
   int r0, r_step, s0, s_step, kW;
 };
 
+// One parity class of a launch (a forward pass has a single class): its taps and where its
+// pixels land in the output.
+struct PatchClass {
+  TapGrid taps;
+  int ntaps, oh_add, ow_add;
+};
+constexpr int kMaxPatchClasses = 4;
+
 template <int BN>
 struct PatchConvProblem {
   static constexpr bool kWarpProducer = false;
@@ -50,22 +58,29 @@ struct PatchConvProblem {
   int pix_w, pix_h, images;  // extent of the pixel grid the rows walk over
   int n_out;                 // number of output channels (columns)
   // K loop
-  int cchunks, ntaps;
+  int cchunks;
   int a_w_mul, a_h_mul;      // A box origin = (q0 * a_w_mul + dw, p0 * a_h_mul + dh)
-  TapGrid taps;
+  // Parity classes served by this launch (strided backward-data with equal class extents: the
+  // classes of one pixel patch are consecutive tiles, so that the interleaved stores of the
+  // classes meet in L2 instead of reaching DRAM as half-written sectors of separate launches).
+  int ncls;
+  PatchClass cls[kMaxPatchClasses];
   // output: out[img][co][oh][ow], oh = p * oh_mul + oh_add, ow = q * ow_mul + ow_add
   float* out;
   const float* bias;
   int out_H, out_W, out_C;
-  int oh_mul, oh_add, ow_mul, ow_add;
+  int oh_mul, ow_mul;
   int fill_cell;  // see store()
 
-  struct Tile { int q0, p0, b0, n0; };
-  struct LoadState { int i, j, cc, aw, ah, wtap; };
+  struct Tile { int q0, p0, b0, n0, c; };
+  struct LoadState { int i, j, cc, aw, ah, wtap, c; };
 
-  __device__ __forceinline__ int num_tiles() const { return tiles_q * tiles_p * tiles_b * tiles_n; }
+  __device__ __forceinline__ int num_tiles() const {
+    return tiles_q * tiles_p * tiles_b * tiles_n * ncls;
+  }
   __device__ __forceinline__ void decode(int tile, Tile& t) const {
     int r = tile;
+    t.c = r % ncls; r /= ncls;
     t.n0 = (r % tiles_n) * BN; r /= tiles_n;
     t.q0 = (r % tiles_q) * QW; r /= tiles_q;
     t.p0 = (r % tiles_p) * PH; r /= tiles_p;
@@ -76,10 +91,12 @@ struct PatchConvProblem {
   // column blocks slowest; an odd patch count leaves the last pair a phantom half whose image
   // index is out of range (its loads are zero-filled, its stores masked).
   __device__ __forceinline__ int num_pair_tiles() const {
-    return ((tiles_q * tiles_p * tiles_b + 1) >> 1) * tiles_n;
+    return ((tiles_q * tiles_p * tiles_b + 1) >> 1) * tiles_n * ncls;
   }
   __device__ __forceinline__ void decode_pair(int tile, int rank, Tile& t) const {
     const int pairs_m = (tiles_q * tiles_p * tiles_b + 1) >> 1;
+    t.c = tile % ncls;
+    tile /= ncls;
     const int nt = tile / pairs_m;
     int r = 2 * (tile - nt * pairs_m) + rank;
     t.n0 = nt * BN;
@@ -101,6 +118,7 @@ struct PatchConvProblem {
   }
   __device__ __forceinline__ void advance(LoadState& ls) const {
     if (++ls.cc == cchunks) {  // next tap: j fastest
+      const TapGrid& taps = cls[ls.c].taps;
       ls.cc = 0;
       ls.aw += taps.dw_step;
       ls.wtap += taps.s_step;
@@ -114,11 +132,13 @@ struct PatchConvProblem {
     }
   }
   __device__ __forceinline__ int k_begin(const Tile&) const { return 0; }
-  __device__ __forceinline__ int k_end(const Tile&) const { return ntaps * cchunks; }
+  __device__ __forceinline__ int k_end(const Tile& t) const { return cls[t.c].ntaps * cchunks; }
   __device__ __forceinline__ void load_begin(const Tile& t, LoadState& ls, int) const {
     ls.i = 0;
     ls.j = 0;
     ls.cc = 0;
+    const TapGrid& taps = cls[t.c].taps;
+    ls.c = t.c;
     ls.aw = t.q0 * a_w_mul + taps.dw0;
     ls.ah = t.p0 * a_h_mul + taps.dh0;
     ls.wtap = taps.r0 * taps.kW + taps.s0;
@@ -169,7 +189,7 @@ struct PatchConvProblem {
       return;
     }
     float* dst = out + ((long long)img * out_C + nb) * plane +
-                 (long long)(p * oh_mul + oh_add) * out_W + (q * ow_mul + ow_add);
+                 (long long)(p * oh_mul + cls[t.c].oh_add) * out_W + (q * ow_mul + cls[t.c].ow_add);
     if (nb + 32 <= n_out) {
       if (bias) {
         const float* bn = bias + nb;

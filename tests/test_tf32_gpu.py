@@ -130,6 +130,8 @@ TF32_CONV_CASES = [
     (4, 512, 7, 7, 128, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),     # 1x1 on 49-pixel planes: general route
     (2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1, True),     # 3x3
     (2, 128, 14, 14, 128, 3, 3, 2, 2, 1, 1, 1, 1, 1, True),   # 3x3 stride 2
+    (2, 32, 15, 13, 32, 3, 3, 2, 2, 1, 1, 1, 1, 1, True),     # 3x3 stride 2, odd extents: one launch per parity class
+    (3, 256, 16, 16, 256, 3, 3, 2, 2, 1, 1, 1, 1, 1, True),   # 3x3 stride 2 on CTA pairs: the classes share a launch
     (2, 256, 14, 14, 512, 1, 1, 2, 2, 0, 0, 1, 1, 1, True),   # 1x1 stride 2 downsample
     (2, 32, 9, 11, 48, 1, 1, 3, 2, 0, 0, 1, 1, 1, True),      # 1x1, strides (3, 2), odd extents
     (2, 3, 32, 32, 64, 7, 7, 2, 2, 3, 3, 1, 1, 1, True),      # stem: K = 147 (padded filter rows)
