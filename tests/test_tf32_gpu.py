@@ -127,6 +127,8 @@ TF32_CONV_CASES = [
     (2, 64, 16, 16, 256, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),    # direct 1x1, expand
     (3, 256, 14, 14, 64, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),    # direct 1x1, reduce, 196 pixels
     (2, 128, 28, 28, 128, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),   # direct 1x1
+    (8, 256, 16, 16, 256, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),   # direct 1x1 big enough for CTA pairs: forward (planes MN-major), backward filter (64 K blocks)
+    (3, 288, 12, 12, 320, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),   # pairs with a phantom half tile and a ragged column block
     (4, 512, 7, 7, 128, 1, 1, 1, 1, 0, 0, 1, 1, 1, True),     # 1x1 on 49-pixel planes: general route
     (2, 64, 14, 14, 64, 3, 3, 1, 1, 1, 1, 1, 1, 1, True),     # 3x3
     (2, 128, 14, 14, 128, 3, 3, 2, 2, 1, 1, 1, 1, 1, True),   # 3x3 stride 2
