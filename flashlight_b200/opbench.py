@@ -93,7 +93,27 @@ def bench_bn(op, shape, iters, axes=(2,)):
     if op == "batchnorm":
         ms = time_op(lambda: ext.batchnorm(x, w, b, rm, rv, list(axes), True, 0.1, 1e-5), iters)
         return report(op, list(shape), ms, nbytes=8 * n)
+    if op == "batchnormRelu":  # relu(batchnorm(x)): same bytes as batchnorm
+        ms = time_op(lambda: ext.batchnorm(x, w, b, rm, rv, list(axes), True, 0.1, 1e-5, relu=True),
+                     iters)
+        return report(op, list(shape), ms, nbytes=8 * n)
+    if op == "batchnormAddRelu":  # relu(batchnorm(x) + shortcut): reads x twice + shortcut, writes y
+        ms = time_op(lambda: ext.batchnormAddRelu(x, g, w, b, rm, rv, list(axes), True, 0.1, 1e-5),
+                     iters)
+        return report(op, list(shape), ms, nbytes=12 * n)
+    if op == "batchnormAddReluBackward":
+        # two incoming gradients and the mask in; the join's gradient and dx out (20 B/elem of
+        # interface traffic; the passes move 28)
+        _, mask, sm, sv = ext.batchnormAddRelu(x, g, w, b, rm, rv, list(axes), True, 0.1, 1e-5)
+        g2 = torch.randn(shape, device="cuda")
+        ms = time_op(lambda: ext.batchnormAddReluBackward(mask, g, g2, sm, sv, x, w, list(axes), True,
+                                                          1e-5), iters)
+        return report(op, list(shape), ms, nbytes=20 * n)
     _, sm, sv = ext.batchnorm(x, w, b, rm, rv, list(axes), True, 0.1, 1e-5)
+    if op == "batchnormReluBackward":
+        ms = time_op(lambda: ext.batchnormReluBackward(g, sm, sv, x, w, b, list(axes), True, 1e-5),
+                     iters)
+        return report(op, list(shape), ms, nbytes=12 * n)
     ms = time_op(lambda: ext.batchnormBackward(g, sm, sv, x, w, list(axes), True, 1e-5), iters)
     return report(op, list(shape), ms, nbytes=12 * n)
 
@@ -312,7 +332,8 @@ def main():
         return suite_resnet50(a.batch, a.iters, a.math)
     if a.op in ("relu", "relu_backward", "add", "gelu_backward"):
         return bench_eltwise(a.op, shape, a.iters)
-    if a.op in ("batchnorm", "batchnormBackward"):
+    if a.op in ("batchnorm", "batchnormBackward", "batchnormRelu", "batchnormReluBackward",
+                "batchnormAddRelu", "batchnormAddReluBackward"):
         return bench_bn(a.op, shape, a.iters)
     if a.op in ("pool2d", "pool2dBackward"):
         return bench_pool(a.op, shape, a.iters)
