@@ -14,7 +14,9 @@
 //   warps 6-9: only in the 3xTF32 instantiation (fp32-grade products): split every landed
 //              operand element into a TF32-exact high part and the remainder, so that the MMA
 //              warp can issue a_lo*b_hi + a_hi*b_lo + a_hi*b_hi
-//   warps 2-5: epilogue — tcgen05.ld the finished accumulator (32 lanes each) and store it
+//   warps 2-5 (and four more behind the producers for tiles of 128+ columns, each group
+//              taking every other 32-column chunk):
+//              epilogue — tcgen05.ld the finished accumulator (32 lanes each) and store it
 //              from registers (coalesced 128-byte rows when the row index is contiguous in
 //              memory, 16-byte vectors when the column index is) while the MMA warp already
 //              fills the other accumulator
@@ -65,9 +67,19 @@ constexpr int kThreadsX3 = kThreads + 128;  // four more warps split the operand
 // copy costs the issuing warp ~110-130 clocks and copies issued from different lanes of one
 // warp still go out one after the other, so a stage of 5 to 12 copies took 650 to 1500 clocks
 // to issue against ~500 clocks of MMAs; two warps issue the even and the odd copies.
+// Tiles of 128 or more columns get a second group of four epilogue warps (each group drains
+// every other 32-column chunk of the accumulator): with one group, shapes with a short K loop
+// and a large output (1x1 layers on 56x56 planes: 2 K blocks per 128 KB tile) were bound by the
+// time four warps need to store a tile.
+template <int X3, int BN>
+constexpr int epilogue_groups() { return (X3 == 0 && BN >= 128) ? 2 : 1; }
 template <class P, int X3>
+constexpr int second_epilogue_first_warp() { return P::kWarpProducer && X3 == 0 ? 7 : 6; }
+template <class P, int X3, int BN>
 constexpr int threads_for() {
-  return X3 ? kThreadsX3 : (P::kWarpProducer ? kThreads + 32 : kThreads);
+  if (X3) return kThreadsX3;
+  if (epilogue_groups<X3, BN>() == 2) return (second_epilogue_first_warp<P, X3>() + 4) * 32;
+  return P::kWarpProducer ? kThreads + 32 : kThreads;
 }
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -92,7 +104,7 @@ static __device__ long long g_tc_profile[256 * 8];
 #endif
 
 template <class P, int BN, int STAGES, int X3 = 0, int KSUB = 1>
-__global__ void __launch_bounds__(threads_for<P, X3>())
+__global__ void __launch_bounds__(threads_for<P, X3, BN>())
 tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
   using SL = SmemLayout<BN, STAGES, X3>;
@@ -126,7 +138,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 4);  // one arrival per epilogue warp
+      mbar_init(&tempty_bar[a], 4 * epilogue_groups<X3, BN>());  // one arrival per epilogue warp
     }
     *failed = 0;
     fence_barrier_init();
@@ -342,8 +354,13 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         if (++s == NG) { s = 0; ++round; }
       }
     }
-  } else if (warp >= 2 && warp < 6) {
-    // epilogue warps 2..5 own TMEM lanes 32*(warp % 4) .. +31
+  } else if ((warp >= 2 && warp < 6) ||
+             (epilogue_groups<X3, BN>() == 2 && warp >= second_epilogue_first_warp<P, X3>() &&
+              warp < second_epilogue_first_warp<P, X3>() + 4)) {
+    // an epilogue warp owns TMEM lanes 32*(warp % 4) .. +31; group 0 = warps 2..5 drains the
+    // even 32-column chunks (all of them when there is one group), group 1 the odd ones
+    constexpr int kGroups = epilogue_groups<X3, BN>();
+    const int group = warp < 6 ? 0 : 1;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     uint32_t nt = 0;
@@ -365,7 +382,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_after();
       if (*failed != 0) break;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 32 * group; c0 < BN; c0 += 32 * kGroups) {
         if (!prob.chunk_live(t, c0)) continue;  // uniform across the warp; need not be a prefix
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
@@ -597,7 +614,7 @@ int launch_problem_as(const char* name, const CUtensorMap& ma, const CUtensorMap
   }
   const long long sms = device_info().sm_count;
   const unsigned grid = (unsigned)(tiles < sms ? tiles : sms);
-  tc_persistent_kernel<P, BN, STAGES, X3, KSUB><<<grid, threads_for<P, X3>(), SL::kTotal, st>>>(
+  tc_persistent_kernel<P, BN, STAGES, X3, KSUB><<<grid, threads_for<P, X3, BN>(), SL::kTotal, st>>>(
       ma, mb, prob, status_ptr());
   FLB200_AFTER_LAUNCH(name);
   count_tc_launch();

@@ -14,7 +14,7 @@
 //   empty[s]   one per CTA; tcgen05.commit.cta_group::2 arrives on both when the MMAs that
 //              read stage s are done
 //   tfull[a]   one per CTA; tcgen05.commit arrives on both when accumulator a is complete
-//   tempty[a]  leader's barrier; the 4 epilogue warps of each CTA arrive on it (the peer's
+//   tempty[a]  leader's barrier; the 8 epilogue warps of each CTA arrive on it (the peer's
 //              through a remote mbarrier.arrive) once they have drained accumulator a
 // The cluster synchronises after barrier initialisation and before TMEM is freed, so no CTA
 // signals a barrier of a peer that has not started or has already left.
@@ -48,8 +48,11 @@ constexpr int pair_stages_for(int bn) { return bn >= 256 ? 6 : 8; }
 
 // Threads: the six warps of tc_kernel.cuh plus, for policies whose stage is several copies, a
 // second producer warp (warp 6) that issues every other copy.
+// ... and a second group of four epilogue warps (see tc_kernel.cuh) behind them.
 template <class P>
-constexpr int pair_threads_for() { return P::kWarpProducer ? kThreads + 32 : kThreads; }
+constexpr int pair_second_epilogue_first_warp() { return P::kWarpProducer ? 7 : 6; }
+template <class P>
+constexpr int pair_threads_for() { return (pair_second_epilogue_first_warp<P>() + 4) * 32; }
 
 template <class P, int BN, int STAGES, int KSUB = 2>
 __global__ void __launch_bounds__(pair_threads_for<P>())
@@ -83,7 +86,7 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tfull_bar[a], 1);
-      mbar_init(&tempty_bar[a], 8);  // leader: 4 epilogue warps of each CTA
+      mbar_init(&tempty_bar[a], 16);  // leader: 8 epilogue warps of each CTA
     }
     *failed = 0;
     fence_barrier_init();
@@ -216,7 +219,11 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       TC_PROF_PUT(2, m_full); TC_PROF_PUT(3, m_acc); TC_PROF_PUT(4, clock64() - m_t0);
 #endif
     }
-  } else if (warp >= 2 && warp < 6) {
+  } else if ((warp >= 2 && warp < 6) || (warp >= pair_second_epilogue_first_warp<P>() &&
+                                        warp < pair_second_epilogue_first_warp<P>() + 4)) {
+    // two groups of four epilogue warps: group 0 drains the even 32-column chunks, group 1 the
+    // odd ones; a warp owns TMEM lanes 32 * (warp % 4) .. + 31
+    const int group = warp < 6 ? 0 : 1;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     uint32_t nt = 0;
@@ -238,7 +245,7 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
       tc_fence_after();
       if (*failed != 0) break;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 32 * group; c0 < BN; c0 += 64) {
         if (!prob.chunk_live(t, c0)) continue;
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
