@@ -278,7 +278,7 @@ CONV_KERNEL = "tc_persistent_kernel (conv2d + conv2dBackwardData + conv2dBackwar
 # batch 256 in TF32 mode, from one ncu capture of
 # `python -m flashlight_b200.opbench --suite resnet50_step_convs --batch 256 --math tf32`
 # (summary under profiles/); algorithmic bytes of the same calls: 66.2e9.
-CONV_DRAM_BYTES_PER_STEP_B256 = 74.6e9
+CONV_DRAM_BYTES_PER_STEP_B256 = 75.2e9
 FP32_FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
