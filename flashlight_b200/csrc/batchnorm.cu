@@ -214,6 +214,50 @@ bn_tail_backward_reduce_kernel(const float* __restrict__ x, const float* __restr
   if (threadIdx.x == 0) partial[c * g.splits + blockIdx.y] = make_float2(s0, s1);
 }
 
+// The same two passes for channel rows of any length (one element and one mask byte per
+// thread step): the 7 x 7 planes of the last ResNet stage.
+__global__ void __launch_bounds__(kChanThreads)
+bn_add_relu_apply_scalar_kernel(const float* __restrict__ x, const float* __restrict__ addend,
+                                float* __restrict__ y, uint8_t* __restrict__ mask, ChannelGeo g,
+                                const float* __restrict__ mean, const float* __restrict__ scale,
+                                const float* __restrict__ shift) {
+  const long long c = blockIdx.x;
+  const float m = mean[c], sc = scale[c], sh = shift ? shift[c] : 0.f;
+  long long begin = (long long)blockIdx.y * g.chunk;
+  long long end = begin + g.chunk;
+  if (end > g.per_channel) end = g.per_channel;
+  for (long long e = begin + threadIdx.x; e < end; e += kChanThreads) {
+    const long long off = channel_elem_offset(g, c, e);
+    const float z = bn_value(x[off], m, sc, sh) + addend[off];
+    y[off] = z > 0.f ? z : (z != z ? z : 0.f);
+    mask[off] = z > 0.f ? 1 : 0;
+  }
+}
+__global__ void __launch_bounds__(kChanThreads)
+bn_tail_backward_reduce_scalar_kernel(const float* __restrict__ x, const float* __restrict__ ga,
+                                      const float* __restrict__ gb,
+                                      const uint8_t* __restrict__ mask, float* __restrict__ gz,
+                                      float2* __restrict__ partial, ChannelGeo g,
+                                      const float* __restrict__ mean) {
+  __shared__ float scratch[32];
+  const long long c = blockIdx.x;
+  const float m = mean[c];
+  long long begin = (long long)blockIdx.y * g.chunk;
+  long long end = begin + g.chunk;
+  if (end > g.per_channel) end = g.per_channel;
+  float s0 = 0.f, s1 = 0.f;
+  for (long long e = begin + threadIdx.x; e < end; e += kChanThreads) {
+    const long long off = channel_elem_offset(g, c, e);
+    const float r = mask[off] ? (gb ? ga[off] + gb[off] : ga[off]) : 0.f;
+    gz[off] = r;
+    s0 += r;
+    s1 += r * (x[off] - m);
+  }
+  s0 = block_sum(s0, scratch);
+  s1 = block_sum(s1, scratch);
+  if (threadIdx.x == 0) partial[c * g.splits + blockIdx.y] = make_float2(s0, s1);
+}
+
 struct BiasAddF {
   const float* bias;
   struct K { float b; };
@@ -547,6 +591,10 @@ static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
       bn_add_relu_apply_kernel<8><<<grid, kChanThreads, 0, st>>>(
           static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
           mask, g, mean_ptr, scale, bias);
+    else if (d->inner % 4 != 0)
+      bn_add_relu_apply_scalar_kernel<<<grid, kChanThreads, 0, st>>>(
+          static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
+          mask, g, mean_ptr, scale, bias);
     else
       bn_add_relu_apply_kernel<4><<<grid, kChanThreads, 0, st>>>(
           static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
@@ -594,11 +642,10 @@ int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void
                                       double epsilon, void* y, uint8_t* mask, void* workspace,
                                       size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d && addend && mask, "batchnorm_add_relu_forward: null argument");
-  if (d->dtype != FLB200_F32 || d->inner % 4 != 0 || !aligned16(x) || !aligned16(addend) ||
+  if (d->dtype != FLB200_F32 || d->inner < 2 || !aligned16(x) || !aligned16(addend) ||
       !aligned16(y))
     return fail(FLB200_UNSUPPORTED,
-                "batchnorm_add_relu_forward: f32, 16-byte aligned tensors with a multiple of 4 "
-                "elements per channel row only");
+                "batchnorm_add_relu_forward: f32, 16-byte aligned tensors in a spatial layout only");
   return batchnorm_forward_impl(true, addend, mask, d, x, weight, bias, running_mean, running_var,
                                 save_mean, save_invstd, train, momentum, epsilon, y, workspace,
                                 workspace_bytes, stream);
@@ -634,6 +681,11 @@ static int batchnorm_backward_impl(bool relu, const uint8_t* tail_mask, const vo
     const dim3 grid((unsigned)C, (unsigned)g.splits);
     if (d->inner % 8 == 0)
       bn_tail_backward_reduce_kernel<8><<<grid, kChanThreads, 0, st>>>(
+          static_cast<const float*>(x), static_cast<const float*>(grad_y),
+          static_cast<const float*>(tail_gb), tail_mask, static_cast<float*>(tail_sum), partial, g,
+          save_mean);
+    else if (d->inner % 4 != 0)
+      bn_tail_backward_reduce_scalar_kernel<<<grid, kChanThreads, 0, st>>>(
           static_cast<const float*>(x), static_cast<const float*>(grad_y),
           static_cast<const float*>(tail_gb), tail_mask, static_cast<float*>(tail_sum), partial, g,
           save_mean);
@@ -703,11 +755,10 @@ int flb200_batchnorm_add_relu_backward(const flb200_batchnorm_desc* d, const uin
                                        float* grad_weight, float* grad_bias, void* workspace,
                                        size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d && mask && grad_y_a && grad_sum, "batchnorm_add_relu_backward: null argument");
-  if (d->dtype != FLB200_F32 || d->inner % 4 != 0 || !aligned16(x) || !aligned16(grad_y_a) ||
+  if (d->dtype != FLB200_F32 || d->inner < 2 || !aligned16(x) || !aligned16(grad_y_a) ||
       !aligned16(grad_sum) || (grad_y_b && !aligned16(grad_y_b)))
     return fail(FLB200_UNSUPPORTED,
-                "batchnorm_add_relu_backward: f32, 16-byte aligned tensors with a multiple of 4 "
-                "elements per channel row only");
+                "batchnorm_add_relu_backward: f32, 16-byte aligned tensors in a spatial layout only");
   return batchnorm_backward_impl(false, mask, grad_y_b, grad_sum, d, grad_y_a, x, weight, nullptr,
                                  save_mean, save_invstd, grad_x, grad_weight, grad_bias, workspace,
                                  workspace_bytes, stream);

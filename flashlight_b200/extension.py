@@ -321,7 +321,7 @@ class B200AutogradExtension:
 
     def batchnormAddReluSupported(self, input, addend, axes) -> bool:
         d = self._bn_desc(input, axes)
-        return (input.dtype == torch.float32 and d.inner % 4 == 0 and addend.shape == input.shape
+        return (input.dtype == torch.float32 and d.inner > 1 and addend.shape == input.shape
                 and addend.dtype == input.dtype and input.is_contiguous() and addend.is_contiguous()
                 and input.data_ptr() % 16 == 0 and addend.data_ptr() % 16 == 0)
 
@@ -331,7 +331,7 @@ class B200AutogradExtension:
         (output, mask, saveMean, saveVar).  Check batchnormAddReluSupported first."""
         d = self._bn_desc(input, axes)
         out = torch.empty_like(input)
-        group = 8 if d.inner % 8 == 0 else 4  # elements per mask byte
+        group = 8 if d.inner % 8 == 0 else (4 if d.inner % 4 == 0 else 1)  # elements per mask byte
         mask = torch.empty((input.numel() + group - 1) // group, dtype=torch.uint8,
                            device=input.device)
         save_mean = save_var = None

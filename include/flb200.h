@@ -229,10 +229,10 @@ int flb200_batchnorm_relu_forward(const flb200_batchnorm_desc* d, const void* x,
                                   void* workspace, size_t workspace_bytes, void* stream);
 /* y = relu(batchnorm(x) + addend): the last BatchNorm of a residual block fused with the block's
  * join (Resnet.cpp:67-121), plus the bit mask of the predicate for
- * flb200_batchnorm_add_relu_backward: `mask` needs ceil(n / 4) bytes (rows of a multiple of 8
- * elements use one byte per 8 elements, in the layout of flb200_relu_forward_mask; other rows
- * one byte per 4).  f32, 16-byte aligned, inner % 4 == 0; otherwise FLB200_UNSUPPORTED (run
- * the two operators separately). */
+ * flb200_batchnorm_add_relu_backward: `mask` needs n bytes (channel rows of a multiple of 8
+ * elements use one byte per 8 elements, in the layout of flb200_relu_forward_mask; of a multiple
+ * of 4, one byte per 4; other rows one byte per element).  f32, 16-byte aligned, spatial layout
+ * (inner > 1); otherwise FLB200_UNSUPPORTED (run the two operators separately). */
 int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void* x,
                                       const void* addend, const float* weight,
                                       const float* bias, float* running_mean,

@@ -172,7 +172,7 @@ def test_batchnorm_relu_fused(ext, fx, shape, axes, affine):
 
 
 @pytest.mark.parametrize("shape", [(8, 64, 28, 28), (4, 32, 4, 6), (2, 16, 8, 8), (4, 32, 14, 14),
-                                   (3, 8, 2, 6)])
+                                   (3, 8, 2, 6), (4, 16, 7, 7), (2, 5, 3, 5)])
 def test_batchnorm_add_relu_fused(ext, fx, shape):
     """relu(batchnorm(x) + shortcut) in one apply pass: output and mask bit for bit equal to the
     batchnorm operator followed by the fused add + relu kernel; unsupported row lengths are
@@ -190,11 +190,13 @@ def test_batchnorm_add_relu_fused(ext, fx, shape):
     assert torch.equal(y1, want_y)
     if (shape[2] * shape[3]) % 8 == 0:   # one mask byte per 8 elements: the relu kernels' layout
         assert torch.equal(mask1, want_mask)
-    else:                                # one byte per 4 elements, private to the fused pair
+    elif (shape[2] * shape[3]) % 4 == 0:  # one byte per 4 elements, private to the fused pair
         assert mask1.numel() == (x.numel() + 3) // 4
+    else:                                 # one byte per element
+        assert mask1.numel() == x.numel()
     assert torch.equal(sm0, sm1) and torch.equal(sv0, sv1)
-    odd = randn(2, 4, 7, 7, seed=3).cuda()   # 49 elements per channel row
-    assert not ext.batchnormAddReluSupported(odd, odd, [2])
+    flat = randn(6, 4, seed=3).cuda()        # per-activation layout: run operator by operator
+    assert not ext.batchnormAddReluSupported(flat, flat, [0])
     # gradient: the join's relu gradient formed inside the first batch-norm pass
     ga, gb = randn(*shape, seed=18).cuda(), randn(*shape, seed=19).cuda()
     for second in (gb, None):
@@ -227,7 +229,7 @@ def test_tape_batchnorm_add_relu_matches_operator_chain():
         z.backward(randn(*shape, seed=85).cuda())
         return [t.clone() for t in (y.tensor, x.grad, s.grad, w.grad, b.grad)]
 
-    for shape in [(4, 16, 8, 8), (2, 8, 6, 6), (2, 8, 7, 7)]:  # fused (8 / 4 per byte) / fallback
+    for shape in [(4, 16, 8, 8), (2, 8, 6, 6), (2, 8, 7, 7)]:  # mask bytes per 8 / 4 / 1 elements
         got, want = run(True, shape), run(False, shape)
         assert torch.equal(got[0], want[0])   # y
         assert torch.equal(got[2], want[2])   # shortcut gradient: mask ? ga + gb : 0
