@@ -491,7 +491,7 @@ def run_gpu_arm(args) -> None:
 
     cpu_base = None
     if world == 1 and not args.no_cpu_baseline:
-        cpu_base, _, _ = cpu_sample(args.cpu_batch, 3, 1, budget_s=25.0)
+        cpu_base, _, _ = cpu_sample(args.cpu_batch, 12, 1, budget_s=25.0)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
