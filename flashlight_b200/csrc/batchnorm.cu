@@ -10,6 +10,7 @@
 // Backward:            pass 1 (sum dy, sum dy*(x-mean)) -> finalize -> pass 2.
 // Algorithmic bytes per element: forward 8 (+4 for the second read when the
 // slab does not stay in L2), backward 12 (+8 likewise).
+#include <mutex>
 #include "channel_ops.cuh"
 
 namespace flb200 {
@@ -468,16 +469,28 @@ int flb200_channel_sum_static_scratch(const void* in, float* out, int64_t outer,
                 "built-in scratch holds %zu; use flb200_channel_sum with caller scratch",
                 need, (size_t)kStaticScratchBytes);
   // In host code the array's name is only a handle; the device address has to be looked up,
-  // once per device, with that device current.  This happens on the first call per device.
+  // once per device, with that device current.  This happens on the first call per device
+  // (guarded, so that two host threads making that first call at once do not race); the
+  // lookup can make the CUDA runtime load this library's device code, which may allocate, so
+  // the no-allocation promise holds from the second call on: callers warm each device up once
+  // at start-up.
+  static std::once_flag looked_up[64];
   static void* device_addr[64] = {nullptr};
+  static cudaError_t lookup_error[64];
   int dev = 0;
   FLB200_CUDA_CHECK(cudaGetDevice(&dev));
   FLB200_REQUIRE(dev >= 0 && dev < 64, "channel_sum_static_scratch: device ordinal %d out of range",
                  dev);
-  if (!device_addr[dev]) {
+  std::call_once(looked_up[dev], [dev] {
     void* p = nullptr;
-    FLB200_CUDA_CHECK(cudaGetSymbolAddress(&p, g_channel_sum_scratch));
-    device_addr[dev] = p;
+    lookup_error[dev] = cudaGetSymbolAddress(&p, g_channel_sum_scratch);
+    device_addr[dev] = lookup_error[dev] == cudaSuccess ? p : nullptr;
+  });
+  if (!device_addr[dev]) {
+    (void)cudaGetLastError();
+    return fail(FLB200_LAUNCH_FAILURE,
+                "channel_sum_static_scratch: cudaGetSymbolAddress failed on device %d: %s", dev,
+                cudaGetErrorString(lookup_error[dev]));
   }
   // Every partial is written before it is read, so stale contents of earlier calls do no harm.
   return flb200_channel_sum(in, out, outer, channels, inner, dtype, device_addr[dev],

@@ -228,6 +228,15 @@ struct WgradEpilogue {
 
 inline size_t max_sz(size_t a, size_t b) { return a > b ? a : b; }
 
+// The tensor-core routes hand the tensors to TMA (16-byte aligned base addresses) and carve
+// 256-byte-aligned sub-buffers out of the workspace that the kernels access with 16-byte
+// vectors: an offset view or an odd workspace must not reach them (a misaligned vector access
+// is a sticky device fault).  Such calls run on the fp32 kernels, which take any alignment.
+inline bool tc_operands_aligned(const void* a, const void* b, const void* c, const void* d,
+                                const void* ws) {
+  return aligned16(a) && aligned16(b) && aligned16(c) && aligned16(d) && aligned16(ws);
+}
+
 }  // namespace
 }  // namespace flb200
 
@@ -289,7 +298,8 @@ int flb200_conv2d_forward_cached(const flb200_conv2d_desc* d, const void* x, con
   const float* bf = static_cast<const float*>(bias);
   float* yf = static_cast<float*>(y);
   tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
-  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_conv_supported(g, 0, workspace_bytes))
+  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_operands_aligned(x, w, y, bias, workspace) &&
+      tc_conv_supported(g, 0, workspace_bytes))
     return tc_conv_forward(g, xf, wf, bf, yf, workspace, workspace_bytes, st, cache);
   const long long n_total = (long long)g.N * g.HoWo;
   FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_forward: too many output pixels");
@@ -320,7 +330,9 @@ int flb200_conv2d_backward_data_cached(const flb200_conv2d_desc* d, const void* 
   const float* wf = static_cast<const float*>(w);
   float* gxf = static_cast<float*>(grad_x);
   tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
-  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_conv_supported(g, 1, workspace_bytes))
+  if (d->math_mode != FLB200_MATH_STRICT_F32 &&
+      tc_operands_aligned(grad_y, w, grad_x, nullptr, workspace) &&
+      tc_conv_supported(g, 1, workspace_bytes))
     return tc_conv_backward_data(g, gyf, wf, gxf, workspace, workspace_bytes, st, cache);
   const long long n_total = (long long)g.N * g.HW;
   FLB200_REQUIRE(n_total < 0x7fffffffLL, "conv2d_backward_data: too many input pixels");
@@ -351,7 +363,9 @@ int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const
   float* gwf = static_cast<float*>(grad_w);
   int rc;
   tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
-  if (d->math_mode != FLB200_MATH_STRICT_F32 && tc_conv_supported(g, 2, workspace_bytes)) {
+  if (d->math_mode != FLB200_MATH_STRICT_F32 &&
+      tc_operands_aligned(grad_y, x, grad_w, nullptr, workspace) &&
+      tc_conv_supported(g, 2, workspace_bytes)) {
     rc = tc_conv_backward_filter(g, gyf, xf, gwf, workspace, workspace_bytes, st, cache);
   } else {
     const int n_total = g.Cg * g.RS;

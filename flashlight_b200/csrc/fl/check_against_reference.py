@@ -16,10 +16,11 @@ ROOT = HERE.parent.parent.parent
 
 
 def main() -> int:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else
-               os.environ.get("FLASHLIGHT_REFERENCE", "/root/reference"))
-    if not (ref / "flashlight/fl/autograd/tensor/AutogradExtension.h").exists():
-        print(f"reference headers not found under {ref}: nothing checked")
+    sys.path.insert(0, str(ROOT))
+    from flashlight_b200._reference import find_reference
+    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else find_reference()
+    if ref is None or not (ref / "flashlight/fl/autograd/tensor/AutogradExtension.h").exists():
+        print("reference headers not found (set FLASHLIGHT_REFERENCE): nothing checked")
         return 0
     out = HERE / "build"
     out.mkdir(exist_ok=True)

@@ -390,9 +390,11 @@ int make_geo(const char* name, const flb200_pool2d_desc* d, PoolGeo* g) {
   FLB200_REQUIRE(d->W >= 1 && d->H >= 1 && d->C >= 1 && d->N >= 1, "%s: empty input", name);
   FLB200_REQUIRE(d->wx >= 1 && d->wy >= 1 && d->sx >= 1 && d->sy >= 1 && d->px >= 0 && d->py >= 0,
                  "%s: bad window/stride/padding", name);
-  FLB200_REQUIRE(d->wx * d->wy <= 255, "%s: window larger than 255 elements", name);
   FLB200_REQUIRE(d->mode >= FLB200_POOL_MAX && d->mode <= FLB200_POOL_AVG_EXCLUDE_PAD,
                  "%s: unknown pooling mode %d", name, d->mode);
+  // only max pooling keeps a window position in its one-byte argmax payload
+  FLB200_REQUIRE(d->mode != FLB200_POOL_MAX || (long long)d->wx * d->wy <= 255,
+                 "%s: max-pooling window larger than 255 elements", name);
   FLB200_REQUIRE(d->W + 2 * d->px >= d->wx && d->H + 2 * d->py >= d->wy,
                  "%s: window larger than padded input", name);
   g->W = d->W; g->H = d->H;

@@ -212,7 +212,15 @@ class CoalescingReducer(Reducer):
 
 class BucketReducer(Reducer):
     """The B200 reducer: flat buckets in reverse parameter order, one in-place asynchronous
-    all-reduce per bucket fired the moment its last gradient lands, no copy back."""
+    all-reduce per bucket, no copy back.
+
+    The collectives of a step are issued in bucket order on every rank, whatever order the
+    gradients arrive in: a bucket whose last gradient has landed is reduced as soon as every
+    bucket before it has been, and finalize() reduces the rest in the same order.  A parameter
+    that received no gradient on this rank contributes zeros (its slice is cleared first, so that
+    nothing of an earlier step is averaged in); ranks on which different parameters went unused
+    therefore still pair the same buffers, and after finalize() every rank holds the same
+    averaged gradient for every parameter of a reduced bucket."""
 
     def __init__(self, params: Sequence, scale: Optional[float] = None,
                  bucket_bytes: int = DEFAULT_BUCKET_BYTES):
@@ -220,8 +228,7 @@ class BucketReducer(Reducer):
         self.scale = (1.0 / getWorldSize()) if scale is None else scale
         self.slot = {}
         self.buckets: List[torch.Tensor] = []
-        self.remaining: List[int] = []
-        self.expected: List[int] = []
+        self.members: List[List] = []
         cur: List = []
         cur_bytes = 0
         groups: List[List] = []
@@ -242,36 +249,56 @@ class BucketReducer(Reducer):
                 self.slot[id(p)] = (bi, off, p.tensor.numel())
                 off += p.tensor.numel()
             self.buckets.append(flat)
-            self.expected.append(len(grp))
+            self.members.append(list(grp))
+        self.expected = [len(g) for g in self.members]
+        self._reset()
+
+    def _reset(self) -> None:
         self.remaining = list(self.expected)
+        self.arrived = [set() for _ in self.members]
+        self.next_bucket = 0  # buckets below this index have been reduced in this step
 
     def bucket_view(self, p) -> torch.Tensor:
         bi, off, n = self.slot[id(p)]
         return self.buckets[bi][off:off + n].view(p.tensor.shape)
 
+    def _fire_ready(self) -> None:
+        while self.next_bucket < len(self.buckets) and self.remaining[self.next_bucket] == 0:
+            allReduce(self.buckets[self.next_bucket], self.scale, True)
+            self.next_bucket += 1
+
     def add(self, var) -> None:
         if var.grad is None:
             return
         bi, off, n = self.slot[id(var)]
+        if id(var) in self.arrived[bi]:
+            raise RuntimeError("BucketReducer: a parameter's gradient was added twice in one step")
+        if bi < self.next_bucket:
+            raise RuntimeError("BucketReducer: gradient arrived after its bucket was reduced")
         view = self.buckets[bi][off:off + n].view(var.tensor.shape)
         if var.grad.data_ptr() != view.data_ptr():
             view.copy_(var.grad)
             var.grad = view
             var._grad_owned = True
+        self.arrived[bi].add(id(var))
         self.remaining[bi] -= 1
-        if self.remaining[bi] == 0:
-            allReduce(self.buckets[bi], self.scale, True)
+        self._fire_ready()
 
     def finalize(self) -> None:
-        for bi, left in enumerate(self.remaining):
-            if left not in (0, self.expected[bi]):
-                raise RuntimeError(f"BucketReducer: bucket {bi} is missing {left} gradients")
-            if left == self.expected[bi] and getWorldSize() > 1:
-                # no parameter of this bucket received a gradient in this step on this rank;
-                # every rank must still take part in the collective
+        world = getWorldSize()
+        for bi in range(self.next_bucket, len(self.buckets)):
+            for p in self.members[bi]:
+                if id(p) not in self.arrived[bi]:
+                    # unused on this rank in this step: contribute zeros, not last step's values
+                    self.bucket_view(p).zero_()
+                    if world > 1:
+                        p.grad = self.bucket_view(p)
+                        p._grad_owned = True
+            if world > 1:
                 allReduce(self.buckets[bi], self.scale, True)
+        self.next_bucket = len(self.buckets)
         syncDistributed()
-        self.remaining = list(self.expected)
+        self._reset()
 
 
 def distributeModuleGrads(module, reducer: Reducer) -> None:

@@ -308,9 +308,12 @@ int flb200_channel_sum(const void* in, float* out, int64_t outer, int64_t channe
  * The partial sums live in a 1 MiB array built into the library (held by every GPU that loads
  * it, until the process exits); shapes that need more are refused with FLB200_INVALID_ARG — use
  * flb200_channel_sum with your own scratch for those.  Calls neither cudaMalloc nor cudaFree.
- * The first call on a device looks up the array's device address; make that first call before
- * any stream capture begins.  All calls share the one array: two calls that may overlap on the
- * GPU (different streams, no ordering between them) race and give wrong sums. */
+ * The first call on a device looks up the array's device address (thread-safe); that lookup can
+ * make the CUDA runtime load the library's device code, which may allocate.  So make one warm-up
+ * call per device at start-up, before any stream capture begins and before the situation in
+ * which allocating is forbidden: from the second call on nothing is allocated.  All calls share
+ * the one array: two calls that may overlap on the GPU (different streams, no ordering between
+ * them) race and give wrong sums. */
 int flb200_channel_sum_static_scratch(const void* in, float* out, int64_t outer,
                                       int64_t channels, int64_t inner, int dtype, void* stream);
 

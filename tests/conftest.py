@@ -8,8 +8,11 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-# checkout of the flashlight project, where present (FLASHLIGHT_REFERENCE overrides the default)
-REFERENCE = Path(os.environ.get("FLASHLIGHT_REFERENCE", "/root/reference"))
+from flashlight_b200._reference import find_reference  # noqa: E402
+
+# checkout of the flashlight project, where present (FLASHLIGHT_REFERENCE, or a directory
+# `reference` beside the repository)
+REFERENCE = find_reference()
 
 
 def pytest_configure(config):
@@ -33,7 +36,7 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture(scope="session")
 def reference_root():
-    if not REFERENCE.exists():
+    if REFERENCE is None:
         pytest.skip("reference checkout not present on this machine")
     return REFERENCE
 

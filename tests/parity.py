@@ -8,9 +8,12 @@ STRICT_TOL = 1e-4
 TF32_TOL = 5e-3
 
 
-def rel_err(got, want) -> float:
-    """max_i |got_i - want_i| / max(|want_i|, 1e-2 * max|want|): element-wise relative
-    error with a floor at 1% of the tensor's largest magnitude, so that entries that are
+REL_FLOOR = 1e-3
+
+
+def rel_err(got, want, floor: float = REL_FLOOR) -> float:
+    """max_i |got_i - want_i| / max(|want_i|, floor * max|want|): element-wise relative
+    error with a floor at 0.1% of the tensor's largest magnitude, so that entries that are
     tiny through cancellation are measured against the tensor's scale."""
     g = torch.as_tensor(got).detach().double().cpu().reshape(-1)
     w = torch.as_tensor(want).detach().double().cpu().reshape(-1)
@@ -22,7 +25,7 @@ def rel_err(got, want) -> float:
     scale = float(w.abs().max())
     if scale == 0.0:
         return float(g.abs().max())
-    den = torch.clamp(w.abs(), min=1e-2 * scale)
+    den = torch.clamp(w.abs(), min=floor * scale)
     return float(((g - w).abs() / den).max())
 
 

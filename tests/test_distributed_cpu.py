@@ -105,12 +105,32 @@ def _reducers(rank, world, D):
         for i, p in enumerate(reversed(ps)):
             assert torch.allclose(p.grad, torch.full(p.tensor.shape, (world + 1) / 2 * (i + 1) + step))
             assert p.grad.data_ptr() == red.bucket_view(p).data_ptr()
-    # a bucket that got only part of its gradients is an error on the host, before any collective
-    ps[-1].grad = torch.ones(sizes[-1])
-    bad = D.BucketReducer(ps[:2] + [ps[-1]], bucket_bytes=1 << 20)
-    bad.add(ps[-1])
-    with pytest.raises(RuntimeError, match="missing"):
-        bad.finalize()
+    # One rank skips a parameter and the gradients arrive in another order than the buckets:
+    # every rank still issues one collective per bucket, in bucket order, the skipped slice
+    # contributes zeros (not the previous step's values), and both ranks end with the same
+    # gradient for every parameter.
+    skip = 1  # ps[1] gets no gradient on rank 1
+    order = [0, 4, 2, 1, 3] if rank == 0 else [3, 0, 4, 2]
+    for i in order:
+        p = ps[i]
+        p.grad = torch.full(p.tensor.shape, float(10 * (rank + 1) + i))
+        p.grad_hook(p)
+    if rank == 1:
+        ps[skip].grad = None
+    red.finalize()
+    for i, p in enumerate(ps):
+        ranks = [r for r in range(world) if not (r == 1 and i == skip)]
+        want = sum(10 * (r + 1) + i for r in ranks) / world
+        assert p.grad is not None and torch.allclose(p.grad, torch.full(p.tensor.shape, want)), (i, p.grad)
+    # the same gradient twice in one step is a host-side error before any collective
+    ps[0].grad = torch.ones(sizes[0])
+    red.add(ps[0])
+    with pytest.raises(RuntimeError, match="twice"):
+        red.add(ps[0])
+    for p in ps[1:]:
+        p.grad = torch.ones(p.tensor.shape)
+        red.add(p)
+    red.finalize()
     D.barrier()
 
 

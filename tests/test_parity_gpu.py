@@ -284,6 +284,23 @@ def test_pool2d(ext, mode, geo, with_payload):
 
 
 @pytest.mark.parametrize("mode", [R.POOL_AVG_INCLUDE_PAD, R.POOL_AVG_EXCLUDE_PAD])
+def test_large_average_window(ext, mode):
+    """A 16x16 average window has 256 elements: more than the one-byte argmax payload of max
+    pooling can index, but averages need no argmax and the reference backends accept them."""
+    x = randn(2, 3, 20, 18, seed=29)
+    y = ext.pool2d(x.cuda(), 16, 16, 2, 2, 1, 1, mode, None)
+    want = R.pool2d(x.double(), 16, 16, 2, 2, 1, 1, mode)
+    assert tuple(y.shape) == tuple(want.shape)
+    assert_close(y, want, 1e-5, "16x16 average pool")
+    gy = randn(*want.shape, seed=30)
+    gx = ext.pool2dBackward(gy.cuda(), x.cuda(), y, 16, 16, 2, 2, 1, 1, mode, None)
+    assert_close(gx, R.pool2d_backward(gy.double(), x.double(), 16, 16, 2, 2, 1, 1, mode), 1e-5,
+                 "16x16 average pool gradient")
+    with pytest.raises(Exception):
+        ext.pool2d(x.cuda(), 16, 16, 2, 2, 1, 1, R.POOL_MAX, None)
+
+
+@pytest.mark.parametrize("mode", [R.POOL_AVG_INCLUDE_PAD, R.POOL_AVG_EXCLUDE_PAD])
 def test_global_average_pool(ext, mode):
     """The ResNet head: one 7x7 window over an unpadded 7x7 plane (the gradient has a kernel of
     its own: every pixel receives dy / 49)."""
