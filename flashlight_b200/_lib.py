@@ -17,6 +17,7 @@ F32, F16, BF16 = 0, 1, 2
 POOL_MAX, POOL_AVG_INCLUDE_PAD, POOL_AVG_EXCLUDE_PAD = 0, 1, 2
 RNN_RELU, RNN_TANH, RNN_LSTM, RNN_GRU = 0, 1, 2, 3
 MATH_STRICT_F32, MATH_TF32, MATH_F32X3 = 0, 1, 2
+LAYOUT_NCHW, LAYOUT_NCHW_IN_NHWC_OUT, LAYOUT_NHWC = 0, 2, 3
 MATH_BY_NAME = {"strict": MATH_STRICT_F32, "tf32": MATH_TF32, "f32x3": MATH_F32X3}
 REDUCE_NONE, REDUCE_MEAN, REDUCE_SUM = 0, 1, 2
 IDS_I32, IDS_I64 = 0, 1
@@ -27,7 +28,7 @@ i32, i64, f32, f64, vp, sz = C.c_int32, C.c_int64, C.c_float, C.c_double, C.c_vo
 class Conv2dDesc(C.Structure):
     _fields_ = [(n, i32) for n in (
         "W", "H", "C", "N", "kW", "kH", "Cout", "sx", "sy", "px", "py", "dx", "dy", "groups",
-        "dtype", "math_mode")]
+        "dtype", "math_mode", "layout")]
 
 
 class Conv2dCache(C.Structure):
@@ -37,7 +38,7 @@ class Conv2dCache(C.Structure):
 
 class Pool2dDesc(C.Structure):
     _fields_ = [(n, i32) for n in (
-        "W", "H", "C", "N", "wx", "wy", "sx", "sy", "px", "py", "mode", "dtype")]
+        "W", "H", "C", "N", "wx", "wy", "sx", "sy", "px", "py", "mode", "dtype", "layout")]
 
 
 class BatchnormDesc(C.Structure):

@@ -16,7 +16,8 @@ import torch
 
 from . import _lib as L
 from . import functions as F
-from .extension import AutogradPayload, B200AutogradExtension, RNNGradData
+from .extension import (AutogradPayload, B200AutogradExtension, RNNGradData, is_dense,
+                        same_layout)
 
 _ext: Optional[B200AutogradExtension] = None
 
@@ -129,13 +130,14 @@ class Variable:
 
 # ------------------------------------------------------------------ functions
 def conv2d(x: Variable, w: Variable, b: Optional[Variable], sx=1, sy=1, px=0, py=0, dx=1, dy=1,
-           groups=1) -> Variable:
-    """fl::conv2d (Functions.cpp:1327-1452)."""
+           groups=1, channels_last_out: Optional[bool] = None) -> Variable:
+    """fl::conv2d (Functions.cpp:1327-1452).  channels_last_out=True: the output is stored
+    channels-last although the input is in fl's order (a network's first convolution)."""
     ext = extension()
     args = (sx, sy, px, py, dx, dy, groups)
     payload = AutogradPayload()
     bt = b.tensor if b is not None else None
-    y = ext.conv2d(x.tensor, w.tensor, bt, *args, payload)
+    y = ext.conv2d(x.tensor, w.tensor, bt, *args, payload, channels_last_out=channels_last_out)
     xt, wt = x.tensor, w.tensor
 
     def grad_func(inputs, gy):
@@ -348,7 +350,7 @@ def relu(x: Variable) -> Variable:
     as a bit mask and the gradient reads dy and the mask (a third less traffic than reading
     dy and y); otherwise the output is the saved tensor ((x > 0) equals (y > 0))."""
     t = x.tensor
-    if t.dtype == torch.float32 and t.is_contiguous() and t.data_ptr() % 16 == 0:
+    if t.dtype == torch.float32 and is_dense(t) and t.data_ptr() % 16 == 0:
         y, mask = F.relu_with_mask(t)
 
         def grad_func(inputs, gy):
@@ -364,7 +366,7 @@ def relu(x: Variable) -> Variable:
 
 
 def _aligned(g: torch.Tensor) -> torch.Tensor:
-    return g if g.is_contiguous() and g.data_ptr() % 16 == 0 else g.contiguous().clone()
+    return g if is_dense(g) and g.data_ptr() % 16 == 0 else g.contiguous().clone()
 
 
 def add_relu(a: Variable, b: Variable) -> Variable:
@@ -373,8 +375,8 @@ def add_relu(a: Variable, b: Variable) -> Variable:
     mask ? dy : 0, and when the output fed two consumers their two gradients are summed inside
     that kernel.  Falls back to add + relu for tensors the fused kernels do not take."""
     ta, tb = a.tensor, b.tensor
-    if not (ta.dtype == torch.float32 and ta.shape == tb.shape and ta.is_contiguous() and
-            tb.is_contiguous() and ta.data_ptr() % 16 == 0 and tb.data_ptr() % 16 == 0):
+    if not (ta.dtype == torch.float32 and same_layout(ta, tb) and is_dense(ta) and
+            is_dense(tb) and ta.data_ptr() % 16 == 0 and tb.data_ptr() % 16 == 0):
         return relu(add(a, b))
     y, mask = F.add_relu_with_mask(ta, tb)
 

@@ -11,6 +11,8 @@
 // Algorithmic bytes per element: forward 8 (+4 for the second read when the
 // slab does not stay in L2), backward 12 (+8 likewise).
 #include <mutex>
+#include <type_traits>
+
 #include "channel_ops.cuh"
 
 namespace flb200 {
@@ -259,6 +261,125 @@ bn_tail_backward_reduce_scalar_kernel(const float* __restrict__ x, const float* 
   if (threadIdx.x == 0) partial[c * g.splits + blockIdx.y] = make_float2(s0, s1);
 }
 
+// The two passes above for channels-last tensors ([pixels][channels], channels a multiple of 8):
+// a thread owns 8 consecutive channels of a pixel = two 16-byte vectors and one mask byte (bit j
+// of byte offset / 8 belongs to element offset + j, the layout of flb200_relu_forward_mask).  A
+// CTA is CO channel octets x 256 / CO row lanes (CO a power of two <= 32).
+struct OctetTiling { int co_shift, col_blocks; };
+inline OctetTiling octet_tiling(long long channels) {
+  const long long octs = channels / 8;
+  int shift = 0;
+  while ((2LL << shift) <= octs && shift < 5) ++shift;
+  return OctetTiling{shift, (int)((octs + (1LL << shift) - 1) >> shift)};
+}
+
+__global__ void __launch_bounds__(256)
+bn_add_relu_apply_cl_kernel(const float* __restrict__ x, const float* __restrict__ addend,
+                            float* __restrict__ y, uint8_t* __restrict__ mask, long long rows,
+                            long long channels, long long rows_per_split, int co_shift,
+                            const float* __restrict__ mean, const float* __restrict__ scale,
+                            const float* __restrict__ shift) {
+  const int co = 1 << co_shift, rl = 256 >> co_shift;
+  const int tq = threadIdx.x & (co - 1), tr = threadIdx.x >> co_shift;
+  const long long c = ((long long)blockIdx.x * co + tq) * 8;
+  if (c >= channels) return;
+  float m[8], sc[8], sh[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    m[j] = mean[c + j];
+    sc[j] = scale[c + j];
+    sh[j] = shift ? shift[c + j] : 0.f;
+  }
+  const long long r0 = (long long)blockIdx.y * rows_per_split;
+  long long r1 = r0 + rows_per_split;
+  if (r1 > rows) r1 = rows;
+  for (long long r = r0 + tr; r < r1; r += rl) {
+    const long long off = r * channels + c;
+    float a[8], s[8], z[8];
+    *reinterpret_cast<float4*>(a) = *reinterpret_cast<const float4*>(x + off);
+    *reinterpret_cast<float4*>(a + 4) = *reinterpret_cast<const float4*>(x + off + 4);
+    *reinterpret_cast<float4*>(s) = *reinterpret_cast<const float4*>(addend + off);
+    *reinterpret_cast<float4*>(s + 4) = *reinterpret_cast<const float4*>(addend + off + 4);
+    unsigned bits = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = bn_value(a[j], m[j], sc[j], sh[j]) + s[j];
+      z[j] = v > 0.f ? v : (v != v ? v : 0.f);
+      bits |= (v > 0.f ? 1u : 0u) << j;
+    }
+    *reinterpret_cast<float4*>(y + off) = make_float4(z[0], z[1], z[2], z[3]);
+    *reinterpret_cast<float4*>(y + off + 4) = make_float4(z[4], z[5], z[6], z[7]);
+    mask[off >> 3] = (uint8_t)bits;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_tail_backward_reduce_cl_kernel(const float* __restrict__ x, const float* __restrict__ ga,
+                                  const float* __restrict__ gb, const uint8_t* __restrict__ mask,
+                                  float* __restrict__ gz, float2* __restrict__ partial,
+                                  long long rows, long long channels, int splits,
+                                  long long rows_per_split, int co_shift,
+                                  const float* __restrict__ mean) {
+  __shared__ float sh0[2048];
+  __shared__ float sh1[2048];
+  const int co = 1 << co_shift, rl = 256 >> co_shift;
+  const int tq = threadIdx.x & (co - 1), tr = threadIdx.x >> co_shift;
+  const long long c = ((long long)blockIdx.x * co + tq) * 8;
+  float s0[8], s1[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s0[j] = s1[j] = 0.f;
+  if (c < channels) {
+    float m[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m[j] = mean[c + j];
+    const long long r0 = (long long)blockIdx.y * rows_per_split;
+    long long r1 = r0 + rows_per_split;
+    if (r1 > rows) r1 = rows;
+    for (long long r = r0 + tr; r < r1; r += rl) {
+      const long long off = r * channels + c;
+      float xv[8], av[8];
+      *reinterpret_cast<float4*>(xv) = *reinterpret_cast<const float4*>(x + off);
+      *reinterpret_cast<float4*>(xv + 4) = *reinterpret_cast<const float4*>(x + off + 4);
+      *reinterpret_cast<float4*>(av) = *reinterpret_cast<const float4*>(ga + off);
+      *reinterpret_cast<float4*>(av + 4) = *reinterpret_cast<const float4*>(ga + off + 4);
+      if (gb) {
+        float bv[8];
+        *reinterpret_cast<float4*>(bv) = *reinterpret_cast<const float4*>(gb + off);
+        *reinterpret_cast<float4*>(bv + 4) = *reinterpret_cast<const float4*>(gb + off + 4);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) av[j] += bv[j];
+      }
+      const unsigned bits = mask[off >> 3];
+      float rv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        rv[j] = (bits >> j) & 1u ? av[j] : 0.f;
+        s0[j] += rv[j];
+        s1[j] += rv[j] * (xv[j] - m[j]);
+      }
+      *reinterpret_cast<float4*>(gz + off) = make_float4(rv[0], rv[1], rv[2], rv[3]);
+      *reinterpret_cast<float4*>(gz + off + 4) = make_float4(rv[4], rv[5], rv[6], rv[7]);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    sh0[(tr << (co_shift + 3)) + tq * 8 + j] = s0[j];
+    sh1[(tr << (co_shift + 3)) + tq * 8 + j] = s1[j];
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < 8 * co) {
+    const long long cc = (long long)blockIdx.x * co * 8 + threadIdx.x;
+    if (cc < channels) {
+      float t0 = 0.f, t1 = 0.f;
+      for (int i = 0; i < rl; ++i) {
+        t0 += sh0[(i << (co_shift + 3)) + threadIdx.x];
+        t1 += sh1[(i << (co_shift + 3)) + threadIdx.x];
+      }
+      partial[cc * splits + blockIdx.y] = make_float2(t0, t1);
+    }
+  }
+}
+
 struct BiasAddF {
   const float* bias;
   struct K { float b; };
@@ -267,13 +388,36 @@ struct BiasAddF {
 };
 
 // ----------------------------------------------------- finalize kernels
+// One warp per channel: the lanes add the channel's per-split partial sums (double), lane 0
+// finishes.  kFinThreads threads per CTA = kFinThreads / 32 channels.
+constexpr int kFinThreads = 128;
+inline unsigned fin_grid(long long channels) {
+  return (unsigned)((channels * 32 + kFinThreads - 1) / kFinThreads);
+}
+__device__ __forceinline__ bool fin_sums(const float2* __restrict__ partial, int splits,
+                                         long long channels, long long* c_out, double* s0_out,
+                                         double* s1_out) {
+  const long long c = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (c >= channels) return false;  // whole warps only: c is uniform across a warp
+  double s0 = 0.0, s1 = 0.0;
+  for (int i = lane; i < splits; i += 32) {
+    const float2 p = partial[c * splits + i];
+    s0 += (double)p.x;
+    s1 += (double)p.y;
+  }
+  *s0_out = warp_sum(s0);
+  *s1_out = warp_sum(s1);
+  *c_out = c;
+  return lane == 0;
+}
+
 __global__ void sum_finalize_kernel(const float2* __restrict__ partial, int splits,
                                     long long channels, float* __restrict__ out) {
-  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
-  double s = 0.0;
-  for (int i = 0; i < splits; ++i) s += (double)partial[c * splits + i].x;
-  out[c] = (float)s;
+  long long c;
+  double s0, s1;
+  if (!fin_sums(partial, splits, channels, &c, &s0, &s1)) return;
+  out[c] = (float)s0;
 }
 
 // Turns the shifted sums into mean / inverse std, updates the running stats and
@@ -287,16 +431,11 @@ __global__ void bn_stats_finalize_kernel(const float2* __restrict__ partial, int
                                          float* __restrict__ save_mean,
                                          float* __restrict__ save_invstd,
                                          float* __restrict__ scale) {
-  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
+  long long c;
+  double s0, s1;
+  if (!fin_sums(partial, splits, channels, &c, &s0, &s1)) return;
   StatsF sf{reinterpret_cast<const float*>(x), inner, dtype};
   const double shift = (double)sf.channel(c).shift;
-  double s0 = 0.0, s1 = 0.0;
-  for (int i = 0; i < splits; ++i) {
-    const float2 p = partial[c * splits + i];
-    s0 += (double)p.x;
-    s1 += (double)p.y;
-  }
   const double md = s0 / count;
   double var = s1 / count - md * md;
   if (var < 0.0) var = 0.0;
@@ -329,14 +468,9 @@ __global__ void bn_bwd_finalize_kernel(const float2* __restrict__ partial, int s
                                        float* __restrict__ grad_weight,
                                        float* __restrict__ grad_bias,
                                        float4* __restrict__ coef) {
-  const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= channels) return;
-  double s0 = 0.0, s1 = 0.0;
-  for (int i = 0; i < splits; ++i) {
-    const float2 p = partial[c * splits + i];
-    s0 += (double)p.x;
-    s1 += (double)p.y;
-  }
+  long long c;
+  double s0, s1;
+  if (!fin_sums(partial, splits, channels, &c, &s0, &s1)) return;
   const double invstd = (double)save_invstd[c];
   const double gamma = weight ? (double)weight[c] : 1.0;
   grad_bias[c] = (float)s0;
@@ -353,6 +487,18 @@ int launch_reduce(const char* name, const void* a, const void* b, float2* partia
   if (inner == 1) {
     const int splits = column_splits(outer, channels);
     const long long rps = (outer + splits - 1) / splits;
+    if constexpr (std::is_same<T, float>::value) {
+      if (channels % 4 == 0 && aligned16(a) && (NIN == 1 || aligned16(b))) {
+        const ColumnTiling ct = column_tiling(channels);
+        dim3 vgrid((unsigned)ct.col_blocks, (unsigned)splits);
+        column_reduce_vec_kernel<NIN, F><<<vgrid, 256, 0, st>>>(
+            static_cast<const float*>(a), static_cast<const float*>(b), partial, outer, channels,
+            splits, rps, ct.cq_shift, f);
+        FLB200_AFTER_LAUNCH(name);
+        *splits_out = splits;
+        return FLB200_OK;
+      }
+    }
     dim3 grid((unsigned)((channels + 31) / 32), (unsigned)splits);
     column_reduce_kernel<T, NIN, F><<<grid, 256, 0, st>>>(
         static_cast<const T*>(a), static_cast<const T*>(b), partial, outer, channels, splits, rps,
@@ -379,6 +525,23 @@ template <typename T, int NIN, typename F>
 int launch_apply(const char* name, const void* a, const void* b, void* out, long long outer,
                  long long channels, long long inner, F f, cudaStream_t st) {
   if (inner == 1) {
+    if constexpr (std::is_same<T, float>::value) {
+      if (channels % 4 == 0 && aligned16(a) && aligned16(out) && (NIN == 1 || aligned16(b))) {
+        const ColumnTiling ct = column_tiling(channels);
+        // about 16 CTAs per SM, at least 32 rows each
+        long long splits = (16LL * device_info().sm_count + ct.col_blocks - 1) / ct.col_blocks;
+        if (splits > (outer + 31) / 32) splits = (outer + 31) / 32;
+        if (splits > 65535) splits = 65535;
+        if (splits < 1) splits = 1;
+        const long long rps = (outer + splits - 1) / splits;
+        dim3 vgrid((unsigned)ct.col_blocks, (unsigned)splits);
+        column_apply_vec_kernel<NIN, F><<<vgrid, 256, 0, st>>>(
+            static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(out),
+            outer, channels, rps, ct.cq_shift, f);
+        FLB200_AFTER_LAUNCH(name);
+        return FLB200_OK;
+      }
+    }
     const int grid = grid_for(outer * channels, 256 * 4);
     column_apply_kernel<T, NIN, F><<<grid, 256, 0, st>>>(
         static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), outer, channels,
@@ -443,8 +606,7 @@ int flb200_channel_sum(const void* in, float* out, int64_t outer, int64_t channe
                         rc = (launch_reduce<T, 1>("channel_sum", in, nullptr, partial, outer,
                                                   channels, inner, SumF{}, &splits, st)));
   if (rc) return rc;
-  sum_finalize_kernel<<<(unsigned)((channels + 127) / 128), 128, 0, st>>>(partial, splits, channels,
-                                                                        out);
+  sum_finalize_kernel<<<fin_grid(channels), kFinThreads, 0, st>>>(partial, splits, channels, out);
   FLB200_AFTER_LAUNCH("channel_sum_finalize");
   return FLB200_OK;
 }
@@ -574,7 +736,6 @@ static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
   float2* partial = reinterpret_cast<float2*>(ws);
   float* scale =
       reinterpret_cast<float*>(ws + align_up(channel_partial_bytes(d->outer, C, d->inner), 256));
-  const unsigned fin_grid = (unsigned)((C + 127) / 128);
   int rc = FLB200_OK;
   const float* mean_ptr;
   if (train) {
@@ -585,7 +746,7 @@ static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
                           rc = (launch_reduce<T, 1>("batchnorm_stats", x, nullptr, partial,
                                                     d->outer, C, d->inner, sf, &splits, st)));
     if (rc) return rc;
-    bn_stats_finalize_kernel<<<fin_grid, 128, 0, st>>>(
+    bn_stats_finalize_kernel<<<fin_grid(C), kFinThreads, 0, st>>>(
         partial, splits, C, (double)d->outer * (double)d->inner, x, d->inner, d->dtype, weight,
         epsilon, momentum, running_mean, running_var, save_mean, save_invstd, scale);
     FLB200_AFTER_LAUNCH("batchnorm_stats_finalize");
@@ -593,11 +754,23 @@ static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
   } else {
     FLB200_REQUIRE(running_mean && running_var,
                    "batchnorm_forward: inference needs running_mean/running_var");
-    bn_infer_prepare_kernel<<<fin_grid, 128, 0, st>>>(C, weight, running_var, epsilon, scale);
+    bn_infer_prepare_kernel<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(C, weight, running_var,
+                                                                         epsilon, scale);
     FLB200_AFTER_LAUNCH("batchnorm_infer_prepare");
     mean_ptr = running_mean;
   }
-  if (addend) {
+  if (addend && d->inner == 1) {
+    const OctetTiling ot = octet_tiling(C);
+    long long splits = (16LL * device_info().sm_count + ot.col_blocks - 1) / ot.col_blocks;
+    if (splits > (d->outer + 31) / 32) splits = (d->outer + 31) / 32;
+    if (splits > 65535) splits = 65535;
+    if (splits < 1) splits = 1;
+    const long long rps = (d->outer + splits - 1) / splits;
+    bn_add_relu_apply_cl_kernel<<<dim3((unsigned)ot.col_blocks, (unsigned)splits), 256, 0, st>>>(
+        static_cast<const float*>(x), static_cast<const float*>(addend), static_cast<float*>(y),
+        mask, d->outer, C, rps, ot.co_shift, mean_ptr, scale, bias);
+    FLB200_AFTER_LAUNCH("batchnorm_add_relu_apply_channels_last");
+  } else if (addend) {
     const ChannelGeo g = make_channel_geo(d->outer, C, d->inner);
     const dim3 grid((unsigned)C, (unsigned)g.splits);
     if (d->inner % 8 == 0)
@@ -655,10 +828,11 @@ int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void
                                       double epsilon, void* y, uint8_t* mask, void* workspace,
                                       size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d && addend && mask, "batchnorm_add_relu_forward: null argument");
-  if (d->dtype != FLB200_F32 || d->inner < 2 || !aligned16(x) || !aligned16(addend) ||
-      !aligned16(y))
+  if (d->dtype != FLB200_F32 || (d->inner < 2 && d->channels % 8 != 0) || !aligned16(x) ||
+      !aligned16(addend) || !aligned16(y))
     return fail(FLB200_UNSUPPORTED,
-                "batchnorm_add_relu_forward: f32, 16-byte aligned tensors in a spatial layout only");
+                "batchnorm_add_relu_forward: f32, 16-byte aligned tensors, in a spatial layout or "
+                "channels-last with a multiple of 8 channels, only");
   return batchnorm_forward_impl(true, addend, mask, d, x, weight, bias, running_mean, running_var,
                                 save_mean, save_invstd, train, momentum, epsilon, y, workspace,
                                 workspace_bytes, stream);
@@ -689,7 +863,18 @@ static int batchnorm_backward_impl(bool relu, const uint8_t* tail_mask, const vo
   off += align_up((size_t)C * sizeof(float), 256);
   float4* coef = reinterpret_cast<float4*>(ws + off);
   int rc = FLB200_OK, splits = 0;
-  if (tail_mask) {
+  if (tail_mask && d->inner == 1) {
+    const OctetTiling ot = octet_tiling(C);
+    splits = column_splits(d->outer, C);
+    const long long rps = (d->outer + splits - 1) / splits;
+    bn_tail_backward_reduce_cl_kernel<<<dim3((unsigned)ot.col_blocks, (unsigned)splits), 256, 0,
+                                        st>>>(
+        static_cast<const float*>(x), static_cast<const float*>(grad_y),
+        static_cast<const float*>(tail_gb), tail_mask, static_cast<float*>(tail_sum), partial,
+        d->outer, C, splits, rps, ot.co_shift, save_mean);
+    FLB200_AFTER_LAUNCH("batchnorm_tail_backward_reduce_channels_last");
+    grad_y = tail_sum;
+  } else if (tail_mask) {
     const ChannelGeo g = make_channel_geo(d->outer, C, d->inner);
     const dim3 grid((unsigned)C, (unsigned)g.splits);
     if (d->inner % 8 == 0)
@@ -724,7 +909,7 @@ static int batchnorm_backward_impl(bool relu, const uint8_t* tail_mask, const vo
                                                     st)));
   }
   if (rc) return rc;
-  bn_bwd_finalize_kernel<<<(unsigned)((C + 127) / 128), 128, 0, st>>>(
+  bn_bwd_finalize_kernel<<<fin_grid(C), kFinThreads, 0, st>>>(
       partial, splits, C, (double)d->outer * (double)d->inner, weight, save_mean, save_invstd,
       grad_weight, grad_bias, coef);
   FLB200_AFTER_LAUNCH("batchnorm_backward_finalize");
@@ -768,10 +953,11 @@ int flb200_batchnorm_add_relu_backward(const flb200_batchnorm_desc* d, const uin
                                        float* grad_weight, float* grad_bias, void* workspace,
                                        size_t workspace_bytes, void* stream) {
   FLB200_REQUIRE(d && mask && grad_y_a && grad_sum, "batchnorm_add_relu_backward: null argument");
-  if (d->dtype != FLB200_F32 || d->inner < 2 || !aligned16(x) || !aligned16(grad_y_a) ||
-      !aligned16(grad_sum) || (grad_y_b && !aligned16(grad_y_b)))
+  if (d->dtype != FLB200_F32 || (d->inner < 2 && d->channels % 8 != 0) || !aligned16(x) ||
+      !aligned16(grad_y_a) || !aligned16(grad_sum) || (grad_y_b && !aligned16(grad_y_b)))
     return fail(FLB200_UNSUPPORTED,
-                "batchnorm_add_relu_backward: f32, 16-byte aligned tensors in a spatial layout only");
+                "batchnorm_add_relu_backward: f32, 16-byte aligned tensors, in a spatial layout or "
+                "channels-last with a multiple of 8 channels, only");
   return batchnorm_backward_impl(false, mask, grad_y_b, grad_sum, d, grad_y_a, x, weight, nullptr,
                                  save_mean, save_invstd, grad_x, grad_weight, grad_bias, workspace,
                                  workspace_bytes, stream);

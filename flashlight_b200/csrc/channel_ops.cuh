@@ -211,26 +211,161 @@ column_apply_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restr
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// inner == 1 with fp32 data, channels a multiple of 4 and 16-byte aligned tensors (the
+// channels-last image tensors, [pixels][channels]): the same column reduction and per-channel
+// pass with 16-byte accesses.  A CTA of 256 threads is CQ column quads (4 channels each, CQ a
+// power of two <= 64) x 256 / CQ row lanes; a thread keeps the constants of its four channels in
+// registers and walks the rows of its split with four independent loads in flight.
+struct ColumnTiling {
+  int cq_shift;    // log2(CQ)
+  int col_blocks;  // ceil(channels / (4 * CQ))
+};
+inline ColumnTiling column_tiling(long long channels) {
+  const long long quads = (channels + 3) / 4;
+  int shift = 0;
+  while ((2LL << shift) <= quads && shift < 6) ++shift;
+  ColumnTiling t;
+  t.cq_shift = shift;
+  t.col_blocks = (int)((quads + (1LL << shift) - 1) >> shift);
+  return t;
+}
+
+template <int NIN, typename F>
+__global__ void __launch_bounds__(256)
+column_reduce_vec_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                         float2* __restrict__ partial, long long rows, long long channels,
+                         int splits, long long rows_per_split, int cq_shift, F f) {
+  __shared__ float sh0[1024];
+  __shared__ float sh1[1024];
+  const int cq = 1 << cq_shift, rl = 256 >> cq_shift;
+  const int tq = threadIdx.x & (cq - 1), tr = threadIdx.x >> cq_shift;
+  const long long c = ((long long)blockIdx.x * cq + tq) * 4;
+  const int s = blockIdx.y;
+  float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+  const bool live = c < channels;
+  if (live) {
+    typename F::K k[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) k[j] = f.channel(c + j);
+    const long long r0 = (long long)s * rows_per_split;
+    long long r1 = r0 + rows_per_split;
+    if (r1 > rows) r1 = rows;
+    long long r = r0 + tr;
+    for (; r + 3LL * rl < r1; r += 4LL * rl) {
+      float4 va[4], vb[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long off = (r + (long long)u * rl) * channels + c;
+        va[u] = *reinterpret_cast<const float4*>(a + off);
+        if (NIN == 2) vb[u] = *reinterpret_cast<const float4*>(b + off);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        f.accumulate(k[0], va[u].x, NIN == 2 ? vb[u].x : 0.f, s0[0], s1[0]);
+        f.accumulate(k[1], va[u].y, NIN == 2 ? vb[u].y : 0.f, s0[1], s1[1]);
+        f.accumulate(k[2], va[u].z, NIN == 2 ? vb[u].z : 0.f, s0[2], s1[2]);
+        f.accumulate(k[3], va[u].w, NIN == 2 ? vb[u].w : 0.f, s0[3], s1[3]);
+      }
+    }
+    for (; r < r1; r += rl) {
+      const long long off = r * channels + c;
+      const float4 va = *reinterpret_cast<const float4*>(a + off);
+      float4 vb = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (NIN == 2) vb = *reinterpret_cast<const float4*>(b + off);
+      f.accumulate(k[0], va.x, vb.x, s0[0], s1[0]);
+      f.accumulate(k[1], va.y, vb.y, s0[1], s1[1]);
+      f.accumulate(k[2], va.z, vb.z, s0[2], s1[2]);
+      f.accumulate(k[3], va.w, vb.w, s0[3], s1[3]);
+    }
+  }
+  // sh[tr][tq * 4 + j]: 256 threads x 4 values
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    sh0[(tr << (cq_shift + 2)) + tq * 4 + j] = s0[j];
+    sh1[(tr << (cq_shift + 2)) + tq * 4 + j] = s1[j];
+  }
+  __syncthreads();
+  // thread t < 4 * CQ finishes column t of the block
+  if ((int)threadIdx.x < 4 * cq) {
+    const long long cc = (long long)blockIdx.x * cq * 4 + threadIdx.x;
+    if (cc < channels) {
+      float t0 = 0.f, t1 = 0.f;
+      for (int i = 0; i < rl; ++i) {
+        t0 += sh0[(i << (cq_shift + 2)) + threadIdx.x];
+        t1 += sh1[(i << (cq_shift + 2)) + threadIdx.x];
+      }
+      partial[cc * splits + s] = make_float2(t0, t1);
+    }
+  }
+}
+
+template <int NIN, typename F>
+__global__ void __launch_bounds__(256)
+column_apply_vec_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                        float* __restrict__ out, long long rows, long long channels,
+                        long long rows_per_split, int cq_shift, F f) {
+  const int cq = 1 << cq_shift, rl = 256 >> cq_shift;
+  const int tq = threadIdx.x & (cq - 1), tr = threadIdx.x >> cq_shift;
+  const long long c = ((long long)blockIdx.x * cq + tq) * 4;
+  if (c >= channels) return;
+  typename F::K k[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) k[j] = f.channel(c + j);
+  const long long r0 = (long long)blockIdx.y * rows_per_split;
+  long long r1 = r0 + rows_per_split;
+  if (r1 > rows) r1 = rows;
+  long long r = r0 + tr;
+  for (; r + 3LL * rl < r1; r += 4LL * rl) {
+    float4 va[4], vb[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long off = (r + (long long)u * rl) * channels + c;
+      va[u] = *reinterpret_cast<const float4*>(a + off);
+      if (NIN == 2) vb[u] = *reinterpret_cast<const float4*>(b + off);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long off = (r + (long long)u * rl) * channels + c;
+      *reinterpret_cast<float4*>(out + off) =
+          make_float4(f.apply(k[0], va[u].x, NIN == 2 ? vb[u].x : 0.f),
+                      f.apply(k[1], va[u].y, NIN == 2 ? vb[u].y : 0.f),
+                      f.apply(k[2], va[u].z, NIN == 2 ? vb[u].z : 0.f),
+                      f.apply(k[3], va[u].w, NIN == 2 ? vb[u].w : 0.f));
+    }
+  }
+  for (; r < r1; r += rl) {
+    const long long off = r * channels + c;
+    const float4 va = *reinterpret_cast<const float4*>(a + off);
+    float4 vb = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (NIN == 2) vb = *reinterpret_cast<const float4*>(b + off);
+    *reinterpret_cast<float4*>(out + off) =
+        make_float4(f.apply(k[0], va.x, vb.x), f.apply(k[1], va.y, vb.y), f.apply(k[2], va.z, vb.z),
+                    f.apply(k[3], va.w, vb.w));
+  }
+}
+
+// Splits of the column path (rows handled per CTA): about six CTAs per SM over the vector
+// tiling's column blocks, at least 64 rows each, at most 512 splits.
+inline int column_splits(long long rows, long long channels) {
+  const long long col_blocks = column_tiling(channels).col_blocks;
+  long long splits = (6LL * device_info().sm_count + col_blocks - 1) / col_blocks;
+  const long long max_by_work = (rows + 63) / 64;
+  if (splits > max_by_work) splits = max_by_work;
+  if (splits > 512) splits = 512;
+  if (splits < 1) splits = 1;
+  return static_cast<int>(splits);
+}
+
 // Scratch bytes for the (channel, split) partial sums of any op built on these.
 inline size_t channel_partial_bytes(long long outer, long long channels, long long inner) {
   long long splits;
   if (inner == 1) {
-    splits = 64;  // upper bound used by the column path
+    splits = column_splits(outer, channels);
   } else {
     splits = make_channel_geo(outer, channels, inner).splits;
   }
   return static_cast<size_t>(channels) * static_cast<size_t>(splits) * sizeof(float2);
-}
-
-// Splits of the column path: enough CTAs to fill the device, at most 64.
-inline int column_splits(long long rows, long long channels) {
-  const long long col_blocks = (channels + 31) / 32;
-  long long splits = (2LL * 8 * device_info().sm_count + col_blocks - 1) / col_blocks;
-  const long long max_by_work = (rows + 63) / 64;
-  if (splits > max_by_work) splits = max_by_work;
-  if (splits > 64) splits = 64;
-  if (splits < 1) splits = 1;
-  return static_cast<int>(splits);
 }
 
 }  // namespace flb200

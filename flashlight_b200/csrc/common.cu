@@ -50,7 +50,7 @@ const DeviceInfo& device_info() {
 
 extern "C" {
 
-int flb200_abi_version(void) { return 1; }
+int flb200_abi_version(void) { return 2; }
 
 const char* flb200_status_string(int status) {
   switch (status) {

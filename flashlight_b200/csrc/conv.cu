@@ -46,6 +46,15 @@ int make_conv_geo(const char* name, const flb200_conv2d_desc* d, ConvGeo* g) {
   g->HW = d->H * d->W;
   g->HoWo = g->Ho * g->Wo;
   g->RS = d->kH * d->kW;
+  FLB200_REQUIRE(d->layout == FLB200_LAYOUT_NCHW || d->layout == FLB200_LAYOUT_NHWC ||
+                     d->layout == FLB200_LAYOUT_NCHW_IN_NHWC_OUT,
+                 "%s: unknown layout %d", name, d->layout);
+  g->x_cl = d->layout == FLB200_LAYOUT_NHWC;
+  g->y_cl = d->layout != FLB200_LAYOUT_NCHW;
+  g->x_cs = g->x_cl ? 1 : g->HW;
+  g->x_ps = g->x_cl ? d->C : 1;
+  g->y_cs = g->y_cl ? 1 : g->HoWo;
+  g->y_ps = g->y_cl ? d->Cout : 1;
   return FLB200_OK;
 }
 
@@ -64,19 +73,19 @@ struct FpropB {
     if (n >= n_total) return Row{-1, 0, 0};
     const int img = n / g.HoWo, pq = n - img * g.HoWo;
     const int p = pq / g.Wo, q = pq - p * g.Wo;
-    return Row{((long long)img * g.C + (long long)z * g.Cg) * g.HW, p * g.sy - g.py,
+    return Row{(long long)img * g.C * g.HW + (long long)z * g.Cg * g.x_cs, p * g.sy - g.py,
                q * g.sx - g.px};
   }
   __device__ Kk kk(long long k, int) const {
     const int ki = (int)k;
     const int ci = ki / g.RS, rs = ki - ci * g.RS;
     const int r = rs / g.kW, s = rs - r * g.kW;
-    return Kk{ci * g.HW, r * g.dy, s * g.dx};
+    return Kk{ci * g.x_cs, r * g.dy, s * g.dx};
   }
   __device__ float load(const Row& r, const Kk& k) const {
     const int h = r.h0 + k.dh, w = r.w0 + k.dw;
     if (r.base < 0 || h < 0 || h >= g.H || w < 0 || w >= g.W) return 0.f;
-    return x[r.base + k.off + h * g.W + w];
+    return x[r.base + k.off + (long long)(h * g.W + w) * g.x_ps];
   }
 };
 
@@ -88,11 +97,11 @@ struct FpropEpilogue {
   struct Col { long long off; };
   __device__ Row row(int m, int z) const {
     const int co = z * g.Coutg + m;
-    return Row{(long long)co * g.HoWo, bias ? bias[co] : 0.f};
+    return Row{(long long)co * g.y_cs, bias ? bias[co] : 0.f};
   }
   __device__ Col col(int n, int) const {
     const int img = n / g.HoWo, pq = n - img * g.HoWo;
-    return Col{(long long)img * g.Cout * g.HoWo + pq};
+    return Col{(long long)img * g.Cout * g.HoWo + (long long)pq * g.y_ps};
   }
   __device__ void store(const Row& r, const Col& c, float acc) const {
     y[r.off + c.off] = acc + r.b;
@@ -133,13 +142,14 @@ struct DgradB {
     if (n >= n_total) return Row{-1, 0, 0};
     const int img = n / g.HW, hw = n - img * g.HW;
     const int h = hw / g.W, w = hw - h * g.W;
-    return Row{((long long)img * g.Cout + (long long)z * g.Coutg) * g.HoWo, h + g.py, w + g.px};
+    return Row{(long long)img * g.Cout * g.HoWo + (long long)z * g.Coutg * g.y_cs, h + g.py,
+               w + g.px};
   }
   __device__ Kk kk(long long k, int) const {
     const int ki = (int)k;
     const int co = ki / g.RS, rs = ki - co * g.RS;
     const int r = rs / g.kW, s = rs - r * g.kW;
-    return Kk{co * g.HoWo, r * g.dy, s * g.dx};
+    return Kk{co * g.y_cs, r * g.dy, s * g.dx};
   }
   __device__ float load(const Row& r, const Kk& k) const {
     const int th = r.hh - k.dh, tw = r.ww - k.dw;
@@ -148,7 +158,7 @@ struct DgradB {
     if (g.sy != 1) { p = th / g.sy; if (p * g.sy != th) return 0.f; }
     if (g.sx != 1) { q = tw / g.sx; if (q * g.sx != tw) return 0.f; }
     if (p >= g.Ho || q >= g.Wo) return 0.f;
-    return gy[r.base + k.off + p * g.Wo + q];
+    return gy[r.base + k.off + (long long)(p * g.Wo + q) * g.y_ps];
   }
 };
 
@@ -157,10 +167,10 @@ struct DgradEpilogue {
   ConvGeo g;
   struct Row { long long off; };
   struct Col { long long off; };
-  __device__ Row row(int m, int z) const { return Row{((long long)z * g.Cg + m) * g.HW}; }
+  __device__ Row row(int m, int z) const { return Row{((long long)z * g.Cg + m) * g.x_cs}; }
   __device__ Col col(int n, int) const {
     const int img = n / g.HW, hw = n - img * g.HW;
-    return Col{(long long)img * g.C * g.HW + hw};
+    return Col{(long long)img * g.C * g.HW + (long long)hw * g.x_ps};
   }
   __device__ void store(const Row& r, const Col& c, float acc) const { gx[r.off + c.off] = acc; }
 };
@@ -175,12 +185,12 @@ struct WgradA {
   struct Kk { long long off; };
   __device__ Row row(int m, int z) const {
     if (m >= g.Coutg) return Row{-1};
-    return Row{((long long)z * g.Coutg + m) * g.HoWo};
+    return Row{((long long)z * g.Coutg + m) * g.y_cs};
   }
   __device__ Kk kk(long long k, int) const {
     const long long img = k / g.HoWo;
     const int pq = (int)(k - img * g.HoWo);
-    return Kk{img * g.Cout * g.HoWo + pq};
+    return Kk{img * g.Cout * g.HoWo + (long long)pq * g.y_ps};
   }
   __device__ float load(const Row& r, const Kk& k) const {
     return r.off >= 0 ? gy[r.off + k.off] : 0.f;
@@ -199,7 +209,7 @@ struct WgradB {
     if (n >= n_total) return Row{-1, 0, 0};
     const int ci = n / g.RS, rs = n - ci * g.RS;
     const int r = rs / g.kW, s = rs - r * g.kW;
-    return Row{((long long)z * g.Cg + ci) * g.HW, r * g.dy - g.py, s * g.dx - g.px};
+    return Row{((long long)z * g.Cg + ci) * g.x_cs, r * g.dy - g.py, s * g.dx - g.px};
   }
   __device__ Kk kk(long long k, int) const {
     const long long img = k / g.HoWo;
@@ -210,7 +220,7 @@ struct WgradB {
   __device__ float load(const Row& r, const Kk& k) const {
     const int h = k.h0 + r.dh, w = k.w0 + r.dw;
     if (r.off < 0 || h < 0 || h >= g.H || w < 0 || w >= g.W) return 0.f;
-    return x[k.base + r.off + h * g.W + w];
+    return x[k.base + r.off + (long long)(h * g.W + w) * g.x_ps];
   }
 };
 
@@ -265,7 +275,8 @@ size_t flb200_conv2d_workspace_bytes(const flb200_conv2d_desc* d, int which) {
   } else {
     need = plan_simt(g.Coutg, (long long)g.Cg * g.RS, (long long)g.N * g.HoWo, g.groups)
                .workspace_bytes;
-    need = max_sz(need, flb200_channel_sum_workspace_bytes(g.N, g.Cout, g.HoWo));
+    need = max_sz(need, g.y_cl ? flb200_channel_sum_workspace_bytes((int64_t)g.N * g.HoWo, g.Cout, 1)
+                               : flb200_channel_sum_workspace_bytes(g.N, g.Cout, g.HoWo));
   }
   if (d->math_mode != FLB200_MATH_STRICT_F32) need = max_sz(need, tc_conv_workspace_bytes(g, which));
   return need;
@@ -379,6 +390,9 @@ int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const
   if (grad_bias) {
     // db[co] = sum over batch and output pixels of dy — one pass over dy
     // (flashlight/fl/autograd/tensor/backend/cudnn/Conv2D.cpp:737).
+    if (g.y_cl)  // [pixels][Cout]: column sums
+      return flb200_channel_sum(grad_y, static_cast<float*>(grad_bias), (int64_t)g.N * g.HoWo,
+                                g.Cout, 1, FLB200_F32, workspace, workspace_bytes, stream);
     return flb200_channel_sum(grad_y, static_cast<float*>(grad_bias), g.N, g.Cout, g.HoWo,
                               FLB200_F32, workspace, workspace_bytes, stream);
   }

@@ -79,6 +79,7 @@ flb200_conv2d_desc convDesc(
   d.sx = sx; d.sy = sy; d.px = px; d.py = py; d.dx = dx; d.dy = dy; d.groups = groups;
   d.dtype = FLB200_F32;
   d.math_mode = mathMode;
+  d.layout = FLB200_LAYOUT_NCHW;  // fl tensors are [W,H,C,N]
   if (dimOr1(weights, 2) * groups != d.C) {
     throw std::invalid_argument("conv2d: weight channels x groups do not match the input");
   }
@@ -95,6 +96,7 @@ flb200_pool2d_desc poolDesc(
   d.wx = wx; d.wy = wy; d.sx = sx; d.sy = sy; d.px = px; d.py = py;
   d.mode = static_cast<int>(mode);
   d.dtype = FLB200_F32;
+  d.layout = FLB200_LAYOUT_NCHW;
   return d;
 }
 

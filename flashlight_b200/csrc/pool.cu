@@ -385,6 +385,190 @@ pool_backward_max_strip_kernel(const T* __restrict__ dy, const uint8_t* __restri
   }
 }
 
+// ------------------------------------------------------------ channels-last tensors
+// x [N][H][W][C]: the channel is the contiguous index, so a thread owns V consecutive
+// channels of one output (forward) or input (backward) pixel and every access is one V-wide
+// vector, coalesced across the threads of a warp; a window is then wx * wy such vectors.
+// Selection rule, NaN behaviour, divisors and the argmax payload (one byte per output element,
+// in the tensor's own element order) are those of the kernels above.
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+pool_forward_cl_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ argmax,
+                       PoolGeo g, int C, long long total) {
+  const int cv = C / V;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int c = (int)(t % cv) * V;
+    long long r = t / cv;
+    const int q = (int)(r % g.Wo); r /= g.Wo;
+    const int p = (int)(r % g.Ho);
+    const long long n = r / g.Ho;
+    const int h0 = p * g.sy - g.py, w0 = q * g.sx - g.px;
+    const T* xn = x + n * (long long)g.H * g.W * C + c;
+    float acc[V];
+    int arg[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) { acc[j] = g.mode == FLB200_POOL_MAX ? -INFINITY : 0.f; arg[j] = 255; }
+    for (int ky = 0; ky < g.wy; ++ky) {
+      const int h = h0 + ky;
+      if (h < 0 || h >= g.H) continue;
+      for (int kx = 0; kx < g.wx; ++kx) {
+        const int w = w0 + kx;
+        if (w < 0 || w >= g.W) continue;
+        const T* src = xn + ((long long)h * g.W + w) * C;
+        T vals[V];
+        if (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(vals) = *reinterpret_cast<const uint4*>(src);
+        else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) vals[j] = src[j];
+        }
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          const float v = Num<T>::to_f(vals[j]);
+          if (g.mode == FLB200_POOL_MAX) {
+            if (arg[j] == 255 || v > acc[j] || v != v) { acc[j] = v; arg[j] = ky * g.wx + kx; }
+          } else {
+            acc[j] += v;
+          }
+        }
+      }
+    }
+    const float div = g.mode == FLB200_POOL_MAX ? 1.f : window_divisor(g, p, q);
+    const long long o = ((n * g.Ho + p) * g.Wo + q) * (long long)C + c;
+    T outv[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j)
+      outv[j] = Num<T>::from_f(g.mode == FLB200_POOL_MAX ? acc[j] : acc[j] / div);
+    if (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(y + o) = *reinterpret_cast<const uint4*>(outv);
+    else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) y[o + j] = outv[j];
+    }
+    if (argmax && g.mode == FLB200_POOL_MAX) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) argmax[o + j] = (uint8_t)arg[j];
+    }
+  }
+}
+
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+pool_backward_cl_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                        const uint8_t* __restrict__ argmax, T* __restrict__ dx, PoolGeo g, int C,
+                        long long total) {
+  const int cv = C / V;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
+    const int c = (int)(t % cv) * V;
+    long long r = t / cv;
+    const int w = (int)(r % g.W); r /= g.W;
+    const int h = (int)(r % g.H);
+    const long long n = r / g.H;
+    const int p_lo = max(ceil_div_pos(h + g.py - g.wy + 1, g.sy), 0);
+    const int p_hi = min((h + g.py) / g.sy, g.Ho - 1);
+    const int q_lo = max(ceil_div_pos(w + g.px - g.wx + 1, g.sx), 0);
+    const int q_hi = min((w + g.px) / g.sx, g.Wo - 1);
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+    for (int p = p_lo; p <= p_hi; ++p) {
+      for (int q = q_lo; q <= q_hi; ++q) {
+        const long long o = ((n * g.Ho + p) * g.Wo + q) * (long long)C + c;
+        T gv[V];
+        if (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(gv) = *reinterpret_cast<const uint4*>(dy + o);
+        else {
+#pragma unroll
+          for (int j = 0; j < V; ++j) gv[j] = dy[o + j];
+        }
+        if (g.mode == FLB200_POOL_MAX) {
+          const int mine = (h + g.py - p * g.sy) * g.wx + (w + g.px - q * g.sx);
+#pragma unroll
+          for (int j = 0; j < V; ++j) {
+            int sel;
+            if (argmax) {
+              sel = argmax[o + j];
+            } else {  // recompute the selection of window (p, q) for channel c + j from x
+              const int h0 = p * g.sy - g.py, w0 = q * g.sx - g.px;
+              float best = -INFINITY;
+              sel = 255;
+              for (int ky = 0; ky < g.wy; ++ky) {
+                const int hh = h0 + ky;
+                if (hh < 0 || hh >= g.H) continue;
+                for (int kx = 0; kx < g.wx; ++kx) {
+                  const int ww = w0 + kx;
+                  if (ww < 0 || ww >= g.W) continue;
+                  const float v = Num<T>::to_f(x[((n * g.H + hh) * g.W + ww) * (long long)C + c + j]);
+                  if (sel == 255 || v > best || v != v) { best = v; sel = ky * g.wx + kx; }
+                }
+              }
+            }
+            if (sel == mine) acc[j] += Num<T>::to_f(gv[j]);
+          }
+        } else {
+          const float div = window_divisor(g, p, q);
+#pragma unroll
+          for (int j = 0; j < V; ++j) acc[j] += Num<T>::to_f(gv[j]) / div;
+        }
+      }
+    }
+    const long long i = ((n * g.H + h) * g.W + w) * (long long)C + c;
+    T outv[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) outv[j] = Num<T>::from_f(acc[j]);
+    if (V * sizeof(T) == 16) *reinterpret_cast<uint4*>(dx + i) = *reinterpret_cast<const uint4*>(outv);
+    else {
+#pragma unroll
+      for (int j = 0; j < V; ++j) dx[i + j] = outv[j];
+    }
+  }
+}
+
+template <typename T>
+int launch_pool_cl(bool backward, const PoolGeo& g, int C, int N, const void* a, const void* x,
+                   const uint8_t* argmax_in, uint8_t* argmax_out, void* out, cudaStream_t st) {
+  constexpr int V = 16 / sizeof(T);
+  const long long pixels = (long long)N * (backward ? (long long)g.H * g.W : (long long)g.Ho * g.Wo);
+  const bool vec = C % V == 0 && aligned16(a) && aligned16(out) && (!x || aligned16(x));
+  const long long total = pixels * (vec ? C / V : C);
+  const int grid = grid_for(total, 256);
+  if (!backward) {
+    if (vec)
+      pool_forward_cl_kernel<T, V><<<grid, 256, 0, st>>>(static_cast<const T*>(a),
+                                                         static_cast<T*>(out), argmax_out, g, C, total);
+    else
+      pool_forward_cl_kernel<T, 1><<<grid, 256, 0, st>>>(static_cast<const T*>(a),
+                                                         static_cast<T*>(out), argmax_out, g, C, total);
+    FLB200_AFTER_LAUNCH("pool2d_forward_channels_last");
+  } else {
+    if (vec)
+      pool_backward_cl_kernel<T, V><<<grid, 256, 0, st>>>(
+          static_cast<const T*>(a), static_cast<const T*>(x), argmax_in, static_cast<T*>(out), g, C,
+          total);
+    else
+      pool_backward_cl_kernel<T, 1><<<grid, 256, 0, st>>>(
+          static_cast<const T*>(a), static_cast<const T*>(x), argmax_in, static_cast<T*>(out), g, C,
+          total);
+    FLB200_AFTER_LAUNCH("pool2d_backward_channels_last");
+  }
+  return FLB200_OK;
+}
+
+int pool_cl_dispatch(bool backward, const flb200_pool2d_desc* d, const PoolGeo& g, const void* a,
+                     const void* x, const uint8_t* argmax_in, uint8_t* argmax_out, void* out,
+                     cudaStream_t st) {
+  switch (d->dtype) {
+    case FLB200_F32:
+      return launch_pool_cl<float>(backward, g, d->C, d->N, a, x, argmax_in, argmax_out, out, st);
+    case FLB200_F16:
+      return launch_pool_cl<__half>(backward, g, d->C, d->N, a, x, argmax_in, argmax_out, out, st);
+    case FLB200_BF16:
+      return launch_pool_cl<__nv_bfloat16>(backward, g, d->C, d->N, a, x, argmax_in, argmax_out, out,
+                                           st);
+    default:
+      return fail(FLB200_UNSUPPORTED, "pool2d: unknown dtype %d", d->dtype);
+  }
+}
+
 int make_geo(const char* name, const flb200_pool2d_desc* d, PoolGeo* g) {
   FLB200_REQUIRE(d, "%s: null descriptor", name);
   FLB200_REQUIRE(d->W >= 1 && d->H >= 1 && d->C >= 1 && d->N >= 1, "%s: empty input", name);
@@ -397,6 +581,8 @@ int make_geo(const char* name, const flb200_pool2d_desc* d, PoolGeo* g) {
                  "%s: max-pooling window larger than 255 elements", name);
   FLB200_REQUIRE(d->W + 2 * d->px >= d->wx && d->H + 2 * d->py >= d->wy,
                  "%s: window larger than padded input", name);
+  FLB200_REQUIRE(d->layout == FLB200_LAYOUT_NCHW || d->layout == FLB200_LAYOUT_NHWC,
+                 "%s: unknown layout %d", name, d->layout);
   g->W = d->W; g->H = d->H;
   g->Wo = 1 + (d->W + 2 * d->px - d->wx) / d->sx;
   g->Ho = 1 + (d->H + 2 * d->py - d->wy) / d->sy;
@@ -429,6 +615,8 @@ int flb200_pool2d_forward(const flb200_pool2d_desc* d, const void* x, void* y, u
   const long long total = g.planes * g.Ho * g.Wo;
   const int grid = grid_for(total, 256);
   cudaStream_t st = as_stream(stream);
+  if (d->layout == FLB200_LAYOUT_NHWC)
+    return pool_cl_dispatch(false, d, g, x, nullptr, nullptr, argmax, y, st);
   if (d->mode == FLB200_POOL_MAX && d->dtype == FLB200_F32) {
     const int band = pool_fwd_band_rows(g);
     const long long nbands = band > 0 ? (g.Ho + band - 1) / band : 0;
@@ -476,6 +664,8 @@ int flb200_pool2d_backward(const flb200_pool2d_desc* d, const void* grad_y, cons
   const long long total = g.planes * g.H * g.W;
   const int grid = grid_for(total, 256);
   cudaStream_t st = as_stream(stream);
+  if (d->layout == FLB200_LAYOUT_NHWC)
+    return pool_cl_dispatch(true, d, g, grad_y, x, argmax, nullptr, grad_x, st);
   if (d->mode == FLB200_POOL_MAX && argmax && d->dtype == FLB200_F32) {
     int out_rows = 0;
     const int band = pool_bwd_band_rows(g, &out_rows);

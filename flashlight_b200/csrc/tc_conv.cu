@@ -151,8 +151,37 @@ tc::OperandPlan plan_mn_major(int rank) {  // dims [rows, K, ...]
 }
 
 bool direct_1x1(const ConvGeo& g) {
-  return g.kW == 1 && g.kH == 1 && g.sx == 1 && g.sy == 1 && g.px == 0 && g.py == 0 &&
-         g.groups == 1 && g.HW % 4 == 0 && g.C % 4 == 0;
+  return !g.x_cl && !g.y_cl && g.kW == 1 && g.kH == 1 && g.sx == 1 && g.sy == 1 && g.px == 0 &&
+         g.py == 0 && g.groups == 1 && g.HW % 4 == 0 && g.C % 4 == 0;
+}
+// The same layer over channels-last tensors: x is the [pixels][C] matrix and y the
+// [pixels][Cout] matrix of a plain GEMM, whatever the plane size.
+//   forward        y(p, co)  = sum_ci x(p, ci) * w(co, ci)       both operands K-major
+//   backward data  dx(p, ci) = sum_co dy(p, co) * wT(ci, co)     wT: filter transposed in scratch
+//   backward filt  the channels-last patch route over the batch as one row of pixels
+bool cl_1x1(const ConvGeo& g) {
+  return g.x_cl && g.y_cl && g.kW == 1 && g.kH == 1 && g.sx == 1 && g.sy == 1 && g.px == 0 &&
+         g.py == 0 && g.groups == 1 && g.C % 4 == 0 && g.Cout % 4 == 0 &&
+         (long long)g.N * g.HW < 0x7fffffffLL;
+}
+
+// wt[ci][co] = w[co][ci] (1 x 1 filters), row stride Cout.
+__global__ void transpose_1x1_filter_kernel(const float* __restrict__ w, float* __restrict__ wt,
+                                            int Cout, int C) {
+  __shared__ float tile[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int ci0 = blockIdx.x * 32, co0 = blockIdx.y * 32;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int co = co0 + ty + 8 * i, ci = ci0 + tx;
+    tile[ty + 8 * i][tx] = (co < Cout && ci < C) ? w[(long long)co * C + ci] : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int ci = ci0 + ty + 8 * i, co = co0 + tx;
+    if (ci < C && co < Cout) wt[(long long)ci * Cout + co] = tile[tx][ty + 8 * i];
+  }
 }
 
 struct GeneralSizes {
@@ -184,6 +213,11 @@ dim3 gather_grid(long long ld, int rows) {
 // -------------------------------------------------------------- interface
 size_t tc_conv_workspace_bytes(const ConvGeo& g, int which) {
   if (g.groups != 1) return 0;
+  if (cl_1x1(g)) {
+    if (which == 0) return 0;
+    if (which == 1) return up256((size_t)g.C * g.Cout * 4);
+    return patch_conv_supported(g) ? patch_conv_workspace_bytes(g, 2) : 0;
+  }
   if (direct_1x1(g)) {
     if (which != 2) return 0;
     const long long k_iters = (long long)g.N * ((g.HW + tc::kBK - 1) / tc::kBK);
@@ -214,6 +248,10 @@ size_t tc_conv_cache_bytes(const ConvGeo& g, int which) {
 bool tc_conv_supported(const ConvGeo& g, int which, size_t workspace_bytes) {
   if (!flb200_has_tensor_core_path()) return false;
   if (g.groups != 1) return false;
+  if (cl_1x1(g) && which != 2) return workspace_bytes >= tc_conv_workspace_bytes(g, which);
+  // the other channels-last shapes run on the patch / row-window routes or not at all
+  if ((g.x_cl || g.y_cl) && !patch_conv_supported(g) && !(which != 1 && window_conv_supported(g)))
+    return false;
   if (direct_1x1(g)) return true;  // scratch only speeds up backward-filter (split-K)
   if (patch_conv_supported(g)) return workspace_bytes >= patch_conv_workspace_bytes(g, which);
   if (which != 1 && window_conv_supported(g))
@@ -233,6 +271,17 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
   ep.alpha = 1.f;
   ep.bias_n = bias;
   const int bn = tc::pick_bn(g.Cout);
+  if (cl_1x1(g)) {
+    const long long M = (long long)g.N * g.HW, k_iters = (g.C + tc::kBK - 1) / tc::kBK;
+    if (int rc = map2d(&ma, x, g.C, M, g.C, tc::kBM, false)) return rc;
+    if (int rc = map2d(&mb, w, g.C, g.Cout, g.C, tc::b_box_rows(M, g.Cout, k_iters, false, false),
+                       false))
+      return rc;
+    ep.m_stride = g.Cout;
+    ep.n_stride = 1;
+    return tc::run(ma, mb, plan_k_major(2), plan_k_major(2), ep, M, g.Cout, k_iters, 1, nullptr, 0,
+                   st);
+  }
   if (direct_1x1(g)) {
     if (int rc = map3d(&ma, x, g.HW, g.C, g.N, g.HW, (long long)g.C * g.HW, 32, true)) return rc;
     // a K-major B tile is one box of all the tile's rows, or of half of them on CTA pairs
@@ -282,6 +331,20 @@ int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, flo
   ep.out = gx;
   ep.alpha = 1.f;
   const int bn = tc::pick_bn(g.C);
+  if (cl_1x1(g)) {
+    const long long M = (long long)g.N * g.HW, k_iters = (g.Cout + tc::kBK - 1) / tc::kBK;
+    float* wt = static_cast<float*>(ws);
+    dim3 tgrid((unsigned)((g.C + 31) / 32), (unsigned)((g.Cout + 31) / 32));
+    transpose_1x1_filter_kernel<<<tgrid, 256, 0, st>>>(w, wt, g.Cout, g.C);
+    FLB200_AFTER_LAUNCH("transpose_1x1_filter");
+    if (int rc = map2d(&ma, gy, g.Cout, M, g.Cout, tc::kBM, false)) return rc;
+    if (int rc = map2d(&mb, wt, g.Cout, g.C, g.Cout, tc::b_box_rows(M, g.C, k_iters, false, false),
+                       false))
+      return rc;
+    ep.m_stride = g.C;
+    ep.n_stride = 1;
+    return tc::run(ma, mb, plan_k_major(2), plan_k_major(2), ep, M, g.C, k_iters, 1, nullptr, 0, st);
+  }
   if (direct_1x1(g)) {
     if (int rc = map3d(&ma, gy, g.HW, g.Cout, g.N, g.HW, (long long)g.Cout * g.HW, 32, true))
       return rc;

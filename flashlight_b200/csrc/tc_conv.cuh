@@ -11,6 +11,11 @@ struct ConvGeo {
   int sx, sy, px, py, dx, dy, groups;
   int Wo, Ho, Cg, Coutg;
   int HW, HoWo, RS;
+  // Memory layout of the activations: x / grad_x and y / grad_y are [N][C][H][W] (fl's own
+  // order) or channels-last [N][H][W][C].  Element (img, c, pixel) of x sits at
+  // img * C * HW + c * x_cs + pixel * x_ps; likewise y with Cout, HoWo, y_cs, y_ps.
+  int x_cl, y_cl;
+  int x_cs, x_ps, y_cs, y_ps;
 };
 
 int make_conv_geo(const char* name, const flb200_conv2d_desc* d, ConvGeo* g);

@@ -127,7 +127,22 @@ nchw_to_nhwc_sampled_kernel(const float* __restrict__ src, float* __restrict__ d
 // its channels-last copy keeps just those, and the rest of the pass is a stride-1 convolution
 // on the Wo x Ho image.  Returns the geometry the forward and backward-filter passes run on.
 bool samples_input(const ConvGeo& g) {
-  return g.RS == 1 && g.px == 0 && g.py == 0 && (g.sx > 1 || g.sy > 1);
+  // (a channels-last x is read in place, with the stride in the tensor map)
+  return !g.x_cl && g.RS == 1 && g.px == 0 && g.py == 0 && (g.sx > 1 || g.sy > 1);
+}
+// Backward-filter of a 1 x 1, stride 1, unpadded convolution over channels-last tensors: the
+// K index is the pixel, and any 32 consecutive pixels make a K block, so the batch is walked
+// as ONE image of N * H * W pixels in a row (no padded patch rows on 14 x 14 or 7 x 7 planes).
+ConvGeo cl_wgrad_geo(const ConvGeo& g) {
+  ConvGeo e = g;
+  if (g.x_cl && g.y_cl && g.RS == 1 && g.sx == 1 && g.sy == 1 && g.px == 0 && g.py == 0 &&
+      (long long)g.N * g.HW < 0x7fffffffLL) {
+    e.W = e.Wo = g.N * g.HW;
+    e.H = e.Ho = 1;
+    e.N = 1;
+    e.HW = e.HoWo = e.W;
+  }
+  return e;
 }
 ConvGeo sampled_geo(const ConvGeo& g) {
   ConvGeo e = g;
@@ -263,7 +278,7 @@ struct PatchArgs {
   tc::PatchClass cls[tc::kMaxPatchClasses];   // taps and output offsets of each
   float* out;
   const float* bias;
-  int out_H, out_W, out_C, oh_mul, ow_mul, fill_cell;
+  int out_H, out_W, out_C, oh_mul, ow_mul, fill_cell, out_cl;
 };
 int filter_box_rows(int bn) { return patch_uses_pairs(bn) ? bn / 2 : bn; }
 
@@ -284,6 +299,7 @@ int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, 
   p.out_H = a.out_H; p.out_W = a.out_W; p.out_C = a.out_C;
   p.oh_mul = a.oh_mul; p.ow_mul = a.ow_mul;
   p.fill_cell = a.fill_cell;
+  p.out_cl = a.out_cl;
   p.tiles_n = (p.n_out + BN - 1) / BN;
   const long long m_tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b;
   FLB200_REQUIRE(a.ncls >= 1 && a.ncls <= tc::kMaxPatchClasses, "patch conv: bad class count");
@@ -467,24 +483,30 @@ int window_rows_map(CUtensorMap* m, const float* base, const WindowGeo& wg, int 
 // ---------------------------------------------------------------- interface
 bool patch_conv_supported(const ConvGeo& g) {
   // small channel counts would waste most of each 32-wide K chunk: those stay on the gather route
-  return g.groups == 1 && g.RS <= 64 && g.C >= 16 && g.Cout >= 16 &&
-         g.sx <= 2 && g.sy <= 2 && g.N <= 65535;
+  if (!(g.groups == 1 && g.RS <= 64 && g.C >= 16 && g.Cout >= 16 && g.sx <= 2 && g.sy <= 2 &&
+        g.N <= 65535))
+    return false;
+  // channels-last tensors are read in place: their pixel stride must be a multiple of 16 bytes
+  if (g.x_cl && g.C % 4 != 0) return false;
+  if (g.y_cl && g.Cout % 4 != 0) return false;
+  return g.x_cl == g.y_cl;
 }
 
+// Channels-last tensors are the operands themselves: no copy, no cache, and the scratch holds
+// the repacked filter / the split-K partial sums only.
 size_t patch_conv_workspace_bytes(const ConvGeo& g0, int which) {
   const ConvGeo g = which == 1 ? g0 : sampled_geo(g0);
   const int cp = up4(g.C), cop = up4(g.Cout);
-  if (which == 0)
-    return up256((size_t)g.N * g.HW * cp * 4) + up256((size_t)g.RS * g.Cout * cp * 4);
-  if (which == 1)
-    return up256((size_t)g.N * g.HoWo * cop * 4) + up256((size_t)g.RS * g.C * cop * 4);
-  return up256((size_t)g.N * g.HW * cp * 4) + up256((size_t)g.N * g.HoWo * cop * 4) +
-         up256(plan_wgrad(g).partial_bytes);
+  const size_t x_copy = g.x_cl ? 0 : up256((size_t)g.N * g.HW * cp * 4);
+  const size_t gy_copy = g.y_cl ? 0 : up256((size_t)g.N * g.HoWo * cop * 4);
+  if (which == 0) return x_copy + up256((size_t)g.RS * g.Cout * cp * 4);
+  if (which == 1) return gy_copy + up256((size_t)g.RS * g.C * cop * 4);
+  return x_copy + gy_copy + up256(plan_wgrad(cl_wgrad_geo(g)).partial_bytes);
 }
 
 size_t patch_conv_cache_bytes(const ConvGeo& g, int which) {
-  if (which == 0) return up256((size_t)g.N * sampled_geo(g).HW * up4(g.C) * 4);
-  return up256((size_t)g.N * g.HoWo * up4(g.Cout) * 4);
+  if (which == 0) return g.x_cl ? 0 : up256((size_t)g.N * sampled_geo(g).HW * up4(g.C) * 4);
+  return g.y_cl ? 0 : up256((size_t)g.N * g.HoWo * up4(g.Cout) * 4);
 }
 
 int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const float* bias,
@@ -494,12 +516,17 @@ int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const 
   const ConvGeo g = sampled_geo(g0);
   const int cp = up4(g.C);
   char* base = static_cast<char*>(ws);
-  const ClSlot xs = cl_slot(cache, 0, (size_t)g.N * g.HW * cp * 4, reinterpret_cast<float*>(base));
-  float* xt = xs.buf;
-  float* wp = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HW * cp * 4));
-  if (!xs.valid) {
-    if (int rc = x_to_nhwc(g0, x, xt, cp, st)) return rc;
-    if (xs.flag) *xs.flag = 1;
+  const float* xt = x;
+  float* wp = reinterpret_cast<float*>(base);
+  if (!g.x_cl) {
+    const ClSlot xs =
+        cl_slot(cache, 0, (size_t)g.N * g.HW * cp * 4, reinterpret_cast<float*>(base));
+    wp = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HW * cp * 4));
+    if (!xs.valid) {
+      if (int rc = x_to_nhwc(g0, x, xs.buf, cp, st)) return rc;
+      if (xs.flag) *xs.flag = 1;
+    }
+    xt = xs.buf;
   }
   pack_filter_kernel<<<grid_for((long long)g.RS * g.Cout * cp, 256), 256, 0, st>>>(
       w, wp, g.Cout, g.C, g.RS, g.Cout, g.C, cp, 1);
@@ -515,6 +542,7 @@ int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const 
   a.out = y; a.bias = bias;
   a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
   a.oh_mul = 1; a.ow_mul = 1;
+  a.out_cl = g.y_cl;
   const int bn = tc::pick_bn(g.Cout);
   CUtensorMap ma, mb;
   if (int rc = nhwc_map(&ma, xt, g.C, cp, g.W, g.H, g.N, a.patch.QW, a.patch.PH, a.patch.NB, g.sx,
@@ -530,12 +558,16 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
   (void)ws_bytes;
   const int cop = up4(g.Cout);
   char* base = static_cast<char*>(ws);
-  const ClSlot gs =
-      cl_slot(cache, 1, (size_t)g.N * g.HoWo * cop * 4, reinterpret_cast<float*>(base));
-  float* gyt = gs.buf;
-  float* wd = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HoWo * cop * 4));
-  if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
-  if (gs.flag) *gs.flag = 1;  // backward-filter of the same grad_y can take it from here
+  const float* gyt = gy;
+  float* wd = reinterpret_cast<float*>(base);
+  if (!g.y_cl) {
+    const ClSlot gs =
+        cl_slot(cache, 1, (size_t)g.N * g.HoWo * cop * 4, reinterpret_cast<float*>(base));
+    wd = reinterpret_cast<float*>(base + up256((size_t)g.N * g.HoWo * cop * 4));
+    if (int rc = to_nhwc(gy, gs.buf, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+    if (gs.flag) *gs.flag = 1;  // backward-filter of the same grad_y can take it from here
+    gyt = gs.buf;
+  }
   pack_filter_kernel<<<grid_for((long long)g.RS * g.C * cop, 256), 256, 0, st>>>(
       w, wd, g.Cout, g.C, g.RS, g.C, g.Cout, cop, 0);
   FLB200_AFTER_LAUNCH("pack_filter");
@@ -594,6 +626,7 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
   a.out_H = g.H; a.out_W = g.W; a.out_C = g.C;
   a.oh_mul = g.sy; a.ow_mul = g.sx;
   a.fill_cell = fill_cell ? 1 : 0;
+  a.out_cl = g.x_cl;
   auto launch = [&](PatchArgs& args) -> int {
     args.patch = pick_patch(args.pix_w, args.pix_h, g.N);
     CUtensorMap ma;
@@ -630,28 +663,36 @@ int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, 
 int patch_conv_backward_filter(const ConvGeo& g0, const float* gy, const float* x, float* gw,
                                void* ws, size_t ws_bytes, cudaStream_t st,
                                flb200_conv2d_cache* cache) {
-  const ConvGeo g = sampled_geo(g0);
+  const ConvGeo g = cl_wgrad_geo(sampled_geo(g0));
   (void)ws_bytes;
   const int cp = up4(g.C), cop = up4(g.Cout);
   const WgradPlan wp = plan_wgrad(g);
   char* base = static_cast<char*>(ws);
-  const ClSlot xs = cl_slot(cache, 0, (size_t)g.N * g.HW * cp * 4, reinterpret_cast<float*>(base));
-  float* xt = xs.buf;
-  size_t off = up256((size_t)g.N * g.HW * cp * 4);
-  const ClSlot gs =
-      cl_slot(cache, 1, (size_t)g.N * g.HoWo * cop * 4, reinterpret_cast<float*>(base + off));
-  float* gyt = gs.buf;
-  off += up256((size_t)g.N * g.HoWo * cop * 4);
+  size_t off = 0;
+  const float* xt = x;
+  if (!g.x_cl) {
+    const ClSlot xs =
+        cl_slot(cache, 0, (size_t)g.N * g.HW * cp * 4, reinterpret_cast<float*>(base));
+    off += up256((size_t)g.N * g.HW * cp * 4);
+    if (!xs.valid) {
+      if (int rc = x_to_nhwc(g0, x, xs.buf, cp, st)) return rc;
+      if (xs.flag) *xs.flag = 1;
+    }
+    xt = xs.buf;
+  }
+  const float* gyt = gy;
+  if (!g.y_cl) {
+    const ClSlot gs =
+        cl_slot(cache, 1, (size_t)g.N * g.HoWo * cop * 4, reinterpret_cast<float*>(base + off));
+    off += up256((size_t)g.N * g.HoWo * cop * 4);
+    if (gs.valid) {
+      *gs.flag = 0;  // consumed: the next backward pass brings another grad_y
+    } else {
+      if (int rc = to_nhwc(gy, gs.buf, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+    }
+    gyt = gs.buf;
+  }
   float* partial = reinterpret_cast<float*>(base + off);
-  if (!xs.valid) {
-    if (int rc = x_to_nhwc(g0, x, xt, cp, st)) return rc;
-    if (xs.flag) *xs.flag = 1;
-  }
-  if (gs.valid) {
-    *gs.flag = 0;  // consumed: the next backward pass brings another grad_y
-  } else {
-    if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
-  }
   CUtensorMap ma, mb;
   if (int rc = nhwc_map5(&ma, gyt, g.Cout, cop, g.Wo, g.Ho, g.N, wp.QW, wp.PH,
                          wgrad_a_boxes(g.Cout), 1, 1))
@@ -672,6 +713,9 @@ bool window_conv_supported(const ConvGeo& g) {
   if (!(g.groups == 1 && g.C <= 4 && g.kW <= kWinPixels && g.dx == 1 && g.Cout >= 16 &&
         g.kH <= 8 && g.sx <= 2 && g.sy <= 2 && g.N <= 65535))
     return false;
+  // x is gathered from fl's order into the padded 4-channel copy; y / grad_y may be
+  // channels-last (then read and written in place)
+  if (g.x_cl || (g.y_cl && g.Cout % 4 != 0)) return false;
   // Rows of the window view overlap (pixel stride < window extent).  Encoding a map reads no
   // memory, so ask the driver up front, with a placeholder base, whether it takes this view;
   // if not, the caller uses the gather route.
@@ -691,7 +735,7 @@ size_t window_conv_workspace_bytes(const ConvGeo& g, int which) {
   if (which == 0) return xtp + up256((size_t)g.kH * g.Cout * 32 * 4);
   const int cop = up4(g.Cout);
   // the backward-filter GEMM has 32 columns per tap and kH taps
-  return xtp + up256((size_t)g.N * g.HoWo * cop * 4) +
+  return xtp + (g.y_cl ? 0 : up256((size_t)g.N * g.HoWo * cop * 4)) +
          up256(plan_wgrad(g, 32 * g.kH, 1).partial_bytes);
 }
 
@@ -737,6 +781,7 @@ int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const 
   a.out = y; a.bias = bias;
   a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
   a.oh_mul = 1; a.ow_mul = 1;
+  a.out_cl = g.y_cl;
   return run_patch_any(bn, ma, mb, a, st);
 }
 
@@ -752,8 +797,13 @@ int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* 
       cl_slot(cache, 0, (size_t)g.N * wg.Hp * wg.Wp * 16, reinterpret_cast<float*>(base));
   float* xtp = xs.buf;
   size_t off = up256((size_t)g.N * wg.Hp * wg.Wp * 16);
-  float* gyt = reinterpret_cast<float*>(base + off);
-  off += up256((size_t)g.N * g.HoWo * cop * 4);
+  const float* gyt = gy;
+  float* gy_copy = nullptr;
+  if (!g.y_cl) {
+    gy_copy = reinterpret_cast<float*>(base + off);
+    gyt = gy_copy;
+    off += up256((size_t)g.N * g.HoWo * cop * 4);
+  }
   float* partial = reinterpret_cast<float*>(base + off);
   CUtensorMap ma, mb;
   if (int rc = window_rows_map(&mb, xtp, wg, g.N, wp.QW, wp.PH, 1 << wp.cn_shift, g.sx, g.sy, g.kH,
@@ -768,7 +818,8 @@ int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* 
     FLB200_AFTER_LAUNCH("nchw_to_nhwc4_pad");
     if (xs.flag) *xs.flag = 1;
   }
-  if (int rc = to_nhwc(gy, gyt, g.N, g.Cout, cop, g.HoWo, st)) return rc;
+  if (gy_copy)
+    if (int rc = to_nhwc(gy, gy_copy, g.N, g.Cout, cop, g.HoWo, st)) return rc;
   // One GEMM: M = Cout, N = kH blocks of 32 window floats, K = pixels.  The filter rows are
   // the channel groups of the view, so the launch has a single tap at offset zero.
   const WgradTaps tp{32 * g.kH, 1, 1, 1, 1, 0, 0};

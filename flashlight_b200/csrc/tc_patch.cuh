@@ -71,6 +71,7 @@ struct PatchConvProblem {
   int out_H, out_W, out_C;
   int oh_mul, ow_mul;
   int fill_cell;  // see store()
+  int out_cl;     // output stored channels-last: out[img][oh][ow][co]
 
   struct Tile { int q0, p0, b0, n0, c; };
   struct LoadState { int i, j, cc, aw, ah, wtap, c; };
@@ -163,6 +164,39 @@ struct PatchConvProblem {
     const int p = t.p0 + ((row >> qw_shift) & (PH - 1));
     const int img = t.b0 + (row >> (qw_shift + ph_shift));
     if (q >= pix_w || p >= pix_h || img >= images) return;
+    if (out_cl) {
+      // channels-last: the 32 columns of this chunk are 128 contiguous bytes of one pixel
+      const int oh0 = p * oh_mul + (fill_cell ? 0 : cls[t.c].oh_add);
+      const int ow0 = q * ow_mul + (fill_cell ? 0 : cls[t.c].ow_add);
+      const int cell_h = fill_cell ? oh_mul : 1, cell_w = fill_cell ? ow_mul : 1;
+      for (int a = 0; a < cell_h; ++a) {
+        if (oh0 + a >= out_H) break;
+        for (int b = 0; b < cell_w; ++b) {
+          if (ow0 + b >= out_W) break;
+          float* dst = out + (((long long)img * out_H + oh0 + a) * out_W + ow0 + b) * out_C + nb;
+          const bool mine = a == 0 && b == 0;  // the other pixels of a cell receive zeros
+          if (nb + 32 <= n_out && (out_C & 3) == 0) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 val = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (mine) {
+                val = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (bias) {
+                  val.x += bias[nb + j]; val.y += bias[nb + j + 1];
+                  val.z += bias[nb + j + 2]; val.w += bias[nb + j + 3];
+                }
+              }
+              *reinterpret_cast<float4*>(dst + j) = val;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (nb + j < n_out) dst[j] = mine ? v[j] + (bias ? bias[nb + j] : 0.f) : 0.f;
+          }
+        }
+      }
+      return;
+    }
     const long long plane = (long long)out_H * out_W;
     if (fill_cell) {
       // Strided backward-data whose only class with taps is (0, 0): this pixel owns the whole

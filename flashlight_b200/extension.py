@@ -12,6 +12,14 @@ stands for the fl tensor [d_0, ..., d_{k-1}] — fl is column-major, so the byte
 are identical.  An image batch fl [W,H,C,N] is torch (N,C,H,W); `axes` and every
 other dimension index are fl indices (0 = fastest).  An absent (empty) fl tensor
 is None.  Out-parameters of the reference (saveMean, saveVar) are returned.
+
+Channels-last storage: an image batch may also be a torch tensor in
+torch.channels_last memory format (same logical (N,C,H,W) indexing, bytes laid out
+[N][H][W][C]).  conv2d, pool2d and batchnorm over the channel axis take such tensors
+as they are (FLB200_LAYOUT_NHWC), return their results in the same format, and the
+element-wise functions work on any two tensors of equal layout, so a network whose
+first convolution is called with channels_last_out=True keeps every activation in
+the layout the tensor-core convolutions read natively and no layout copy is made.
 """
 from __future__ import annotations
 
@@ -39,10 +47,31 @@ def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
         return None
     if not t.is_cuda:
         raise ValueError("the B200 autograd extension needs device (CUDA) tensors")
-    if not t.is_contiguous():
+    if not is_dense(t):
         # fl::DevicePtr also refuses non-contiguous tensors (flashlight/fl/common/DevicePtr.cpp:16-33)
         raise ValueError("can't get device pointer of non-contiguous tensor")
     return t.data_ptr()
+
+
+def is_channels_last(t: Optional[torch.Tensor]) -> bool:
+    """True for a 4-d tensor stored [N][H][W][C] whose bytes differ from the [N][C][H][W] order
+    (with one channel or 1x1 planes the two orders coincide and the tensor counts as the latter)."""
+    return (t is not None and t.dim() == 4 and not t.is_contiguous()
+            and t.is_contiguous(memory_format=torch.channels_last))
+
+
+def is_dense(t: torch.Tensor) -> bool:
+    """Contiguous in fl's order or in channels-last order."""
+    return t.is_contiguous() or is_channels_last(t)
+
+
+def same_layout(a: torch.Tensor, b: torch.Tensor) -> bool:
+    return a.shape == b.shape and is_channels_last(a) == is_channels_last(b)
+
+
+def empty_images(shape, like: torch.Tensor, channels_last: bool) -> torch.Tensor:
+    fmt = torch.channels_last if channels_last else torch.contiguous_format
+    return torch.empty(shape, dtype=like.dtype, device=like.device, memory_format=fmt)
 
 
 def stream_handle() -> int:
@@ -163,16 +192,23 @@ class B200AutogradExtension:
         return None
 
     # --------------------------------------------------------------- conv2d
-    def _conv_desc(self, input, weights, sx, sy, px, py, dx, dy, groups) -> L.Conv2dDesc:
+    def _conv_desc(self, input, weights, sx, sy, px, py, dx, dy, groups,
+                   output_channels_last: Optional[bool] = None) -> L.Conv2dDesc:
+        """output_channels_last: layout of y / grad_y; None = that of the input."""
         if input.dtype != torch.float32 or weights.dtype != torch.float32:
             raise ValueError("conv2d: only f32 tensors are supported")
+        x_cl = is_channels_last(input)
+        y_cl = x_cl if output_channels_last is None else bool(output_channels_last)
+        if x_cl and not y_cl:
+            raise ValueError("conv2d: a channels-last input gives a channels-last output")
+        layout = L.LAYOUT_NHWC if x_cl else (L.LAYOUT_NCHW_IN_NHWC_OUT if y_cl else L.LAYOUT_NCHW)
         W, H, Cin, N = _shape4(input)
         kW, kH, Cg, Cout = _shape4(weights)
         if Cg * groups != Cin:
             raise ValueError(
                 f"conv2d: weight has {Cg} input channels per group x {groups} groups, input has {Cin}")
         return L.Conv2dDesc(W, H, Cin, N, kW, kH, Cout, sx, sy, px, py, dx, dy, groups, L.F32,
-                            self.math_mode)
+                            self.math_mode, layout)
 
     def _conv_cache(self, d, payload, like) -> Optional["_ConvLayoutCache"]:
         """The layout cache kept in the payload of one conv2d call site (None when the route
@@ -188,11 +224,14 @@ class B200AutogradExtension:
         payload.data = _ConvLayoutCache(nx, ng, like)
         return payload.data
 
-    def conv2d(self, input, weights, bias, sx, sy, px, py, dx, dy, groups, payload=None):
-        d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups)
+    def conv2d(self, input, weights, bias, sx, sy, px, py, dx, dy, groups, payload=None,
+               channels_last_out: Optional[bool] = None):
+        """channels_last_out=True on an input in fl's order: the output (and from there the whole
+        network) is stored channels-last; a channels-last input always gives such an output."""
+        d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups, channels_last_out)
         wo, ho = L.i32(), L.i32()
         L.check(L.lib.flb200_conv2d_output_dims(C.byref(d), C.byref(wo), C.byref(ho)))
-        out = torch.empty((d.N, d.Cout, ho.value, wo.value), dtype=input.dtype, device=input.device)
+        out = empty_images((d.N, d.Cout, ho.value, wo.value), input, d.layout != L.LAYOUT_NCHW)
         if bias is not None and bias.numel() != d.Cout:
             raise ValueError("conv2d: bias must have one element per output channel")
         nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 0)
@@ -207,7 +246,8 @@ class B200AutogradExtension:
 
     def conv2dBackwardData(self, gradOutput, input, weight, sx, sy, px, py, dx, dy, groups,
                            dataGradBenchmark=None, payload=None):
-        d = self._conv_desc(input, weight, sx, sy, px, py, dx, dy, groups)
+        d = self._conv_desc(input, weight, sx, sy, px, py, dx, dy, groups,
+                            is_channels_last(gradOutput) or is_channels_last(input))
         grad_in = torch.empty_like(input)
         nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 1)
         ws = workspace(nbytes, input)
@@ -221,7 +261,8 @@ class B200AutogradExtension:
 
     def conv2dBackwardFilterBias(self, gradOutput, input, weights, bias, sx, sy, px, py, dx, dy,
                                  groups, filterBench=None, biasBench=None, autogradPayload=None):
-        d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups)
+        d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups,
+                            is_channels_last(gradOutput) or is_channels_last(input))
         grad_w = torch.empty_like(weights)
         grad_b = torch.empty_like(bias) if bias is not None else None
         nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 2)
@@ -241,16 +282,17 @@ class B200AutogradExtension:
     @staticmethod
     def _pool_desc(input, wx, wy, sx, sy, px, py, mode) -> L.Pool2dDesc:
         W, H, Cc, N = _shape4(input)
-        return L.Pool2dDesc(W, H, Cc, N, wx, wy, sx, sy, px, py, int(mode), dtype_code(input))
+        return L.Pool2dDesc(W, H, Cc, N, wx, wy, sx, sy, px, py, int(mode), dtype_code(input),
+                            L.LAYOUT_NHWC if is_channels_last(input) else L.LAYOUT_NCHW)
 
     def pool2d(self, input, wx, wy, sx, sy, px, py, mode, payload=None):
         d = self._pool_desc(input, wx, wy, sx, sy, px, py, mode)
         wo, ho = L.i32(), L.i32()
         L.check(L.lib.flb200_pool2d_output_dims(C.byref(d), C.byref(wo), C.byref(ho)))
-        out = torch.empty((d.N, d.C, ho.value, wo.value), dtype=input.dtype, device=input.device)
+        out = empty_images((d.N, d.C, ho.value, wo.value), input, d.layout == L.LAYOUT_NHWC)
         argmax = None
         if payload is not None and int(mode) == L.POOL_MAX:
-            argmax = torch.empty(out.shape, dtype=torch.uint8, device=input.device)
+            argmax = torch.empty_like(out, dtype=torch.uint8)
             payload.data = _PoolPayload(argmax)
         L.check(L.lib.flb200_pool2d_forward(C.byref(d), ptr(input), ptr(out), ptr(argmax),
                                             stream_handle()))
@@ -268,6 +310,12 @@ class B200AutogradExtension:
     # ------------------------------------------------------------ batchnorm
     @staticmethod
     def _bn_desc(input, axes: Sequence[int]) -> L.BatchnormDesc:
+        if is_channels_last(input):
+            # stored [N][H][W][C]: statistics per channel are column sums of a [pixels][C] matrix
+            if list(axes) != [2]:
+                raise ValueError("batchnorm: a channels-last tensor is normalised over fl axis 2 only")
+            n, c, h, w = input.shape
+            return L.BatchnormDesc(n * h * w, c, 1, dtype_code(input))
         fl_shape = tuple(reversed(input.shape))
         shape = (L.i64 * len(fl_shape))(*fl_shape)
         ax = (L.i32 * len(axes))(*axes)
@@ -321,8 +369,9 @@ class B200AutogradExtension:
 
     def batchnormAddReluSupported(self, input, addend, axes) -> bool:
         d = self._bn_desc(input, axes)
-        return (input.dtype == torch.float32 and d.inner > 1 and addend.shape == input.shape
-                and addend.dtype == input.dtype and input.is_contiguous() and addend.is_contiguous()
+        shape_ok = d.inner > 1 or (is_channels_last(input) and d.channels % 8 == 0)
+        return (input.dtype == torch.float32 and shape_ok and same_layout(input, addend)
+                and addend.dtype == input.dtype and is_dense(input)
                 and input.data_ptr() % 16 == 0 and addend.data_ptr() % 16 == 0)
 
     def batchnormAddRelu(self, input, addend, weight, bias, runningMean, runningVar, axes, train,
@@ -331,7 +380,8 @@ class B200AutogradExtension:
         (output, mask, saveMean, saveVar).  Check batchnormAddReluSupported first."""
         d = self._bn_desc(input, axes)
         out = torch.empty_like(input)
-        group = 8 if d.inner % 8 == 0 else (4 if d.inner % 4 == 0 else 1)  # elements per mask byte
+        # elements per mask byte: 8 consecutive channels of a pixel for channels-last tensors
+        group = 8 if d.inner % 8 == 0 or d.inner == 1 else (4 if d.inner % 4 == 0 else 1)
         mask = torch.empty((input.numel() + group - 1) // group, dtype=torch.uint8,
                            device=input.device)
         save_mean = save_var = None

@@ -15,7 +15,8 @@ from typing import Optional
 import torch
 
 from . import _lib as L
-from .extension import dtype_code, ptr, stream_handle, workspace, default_math_mode
+from .extension import (default_math_mode, dtype_code, ptr, same_layout, stream_handle,
+                        workspace)
 
 
 def _unary(fn, x):
@@ -25,8 +26,8 @@ def _unary(fn, x):
 
 
 def _binary(fn, a, b):
-    if a.shape != b.shape or a.dtype != b.dtype:
-        raise ValueError("operands must have the same shape and dtype")
+    if not same_layout(a, b) or a.dtype != b.dtype:
+        raise ValueError("operands must have the same shape, memory layout and dtype")
     out = torch.empty_like(a)
     L.check(fn(ptr(a), ptr(b), ptr(out), a.numel(), dtype_code(a), stream_handle()))
     return out
@@ -60,6 +61,8 @@ def relu_backward_mask(mask, grad_y):
 
 def add_relu_with_mask(a, b):
     """relu(a + b) in one pass, with the predicate (a + b) > 0 packed 8 elements per byte."""
+    if not same_layout(a, b):
+        raise ValueError("operands must have the same shape and memory layout")
     y = torch.empty_like(a)
     mask = torch.empty((a.numel() + 7) // 8, dtype=torch.uint8, device=a.device)
     L.check(L.lib.flb200_add_relu_forward_mask(ptr(a), ptr(b), ptr(y), ptr(mask), a.numel(),
@@ -69,6 +72,8 @@ def add_relu_with_mask(a, b):
 
 def relu_backward_mask_sum(mask, grad_a, grad_b):
     """mask ? grad_a + grad_b : 0 — the relu gradient of an output with two consumers."""
+    if not same_layout(grad_a, grad_b):
+        raise ValueError("operands must have the same shape and memory layout")
     gx = torch.empty_like(grad_a)
     L.check(L.lib.flb200_relu_backward_mask_sum(ptr(mask), ptr(grad_a), ptr(grad_b), ptr(gx),
                                                 grad_a.numel(), dtype_code(grad_a),
@@ -96,8 +101,8 @@ def tanh_backward(y, grad_y):
 
 def dropout_apply(x, mask, p: float):
     """x * mask / (1 - p): forward with x, gradient with dy (Functions.cpp:1777-1785)."""
-    if x.shape != mask.shape or x.dtype != mask.dtype:
-        raise ValueError("mask must match the tensor's shape and dtype")
+    if not same_layout(x, mask) or x.dtype != mask.dtype:
+        raise ValueError("mask must match the tensor's shape, memory layout and dtype")
     out = torch.empty_like(x)
     L.check(L.lib.flb200_dropout_apply(ptr(x), ptr(mask), ptr(out), 1.0 / (1.0 - p), x.numel(),
                                        dtype_code(x), stream_handle()))
@@ -106,8 +111,8 @@ def dropout_apply(x, mask, p: float):
 
 def add(a, b, out=None):
     """Gradient fan-in accumulation of Variable::addGrad (Variable.cpp:205-211)."""
-    if a.shape != b.shape or a.dtype != b.dtype:
-        raise ValueError("operands must have the same shape and dtype")
+    if not same_layout(a, b) or a.dtype != b.dtype:
+        raise ValueError("operands must have the same shape, memory layout and dtype")
     if out is None:
         out = torch.empty_like(a)
     L.check(L.lib.flb200_add(ptr(a), ptr(b), ptr(out), a.numel(), dtype_code(a), stream_handle()))

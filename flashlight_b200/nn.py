@@ -79,9 +79,12 @@ class Conv2D(Module):
     fan-in kW*kH*Cin/groups, bias U(+-sqrt(1/fan_in))."""
 
     def __init__(self, n_in, n_out, wx, wy, sx=1, sy=1, px=0, py=0, dx=1, dy=1, bias=True, groups=1,
-                 gen=None, device="cuda"):
+                 gen=None, device="cuda", channels_last_out=None):
         super().__init__()
         self.cfg = (n_in, n_out, wx, wy, sx, sy, px, py, dx, dy, groups)
+        # True on a network's first convolution: its output, and with it every activation
+        # downstream, is stored channels-last (see extension.py)
+        self.channels_last_out = channels_last_out
         fan_in = wx * wy * n_in // groups
         bound = math.sqrt(3.0) * math.sqrt(1.0 / fan_in)
         self.params.append(Variable(_uniform((n_out, n_in // groups, wy, wx), bound, gen, device), True))
@@ -94,7 +97,8 @@ class Conv2D(Module):
         px = derive_padding(W, wx, sx, px, dx)
         py = derive_padding(H, wy, sy, py, dy)
         b = self.params[1] if len(self.params) > 1 else None
-        return A.conv2d(x, self.params[0], b, sx, sy, px, py, dx, dy, groups)
+        return A.conv2d(x, self.params[0], b, sx, sy, px, py, dx, dy, groups,
+                        channels_last_out=self.channels_last_out)
 
 
 class Linear(Module):

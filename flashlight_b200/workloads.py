@@ -16,7 +16,7 @@ from __future__ import annotations
 
 import math
 import os
-from typing import List
+from typing import List, Optional
 
 import torch
 
@@ -32,6 +32,10 @@ from .autograd import Variable
 # with relu=True).  FLB200_FUSE=0 keeps the reference's operator-by-operator chain.
 FUSE_RESIDUAL_RELU = os.environ.get("FLB200_FUSE", "1") not in ("0", "false")
 FUSE_BATCHNORM_RELU = FUSE_RESIDUAL_RELU
+# Activations stored channels-last from the first convolution's output on (the layout the
+# tensor-core convolutions read natively: no layout copies anywhere in the step).
+# FLB200_CHANNELS_LAST=0 keeps every tensor in fl's own [W,H,C,N] order.
+CHANNELS_LAST = os.environ.get("FLB200_CHANNELS_LAST", "1") not in ("0", "false")
 
 
 class Bottleneck(nn.Module):
@@ -88,11 +92,17 @@ class ClassifierModel(nn.Module):
 
 
 def resnet50(seed: int = 1234, device: str = "cuda", blocks=(3, 4, 6, 3), classes: int = 1000,
-             width: int = 64) -> ClassifierModel:
-    """resnet50() of Resnet.cpp:210-230; `blocks` / `width` only shrink it for tests."""
+             width: int = 64, channels_last: Optional[bool] = None) -> ClassifierModel:
+    """resnet50() of Resnet.cpp:210-230; `blocks` / `width` only shrink it for tests.
+    channels_last (default: CHANNELS_LAST): the stem takes the images in fl's order and every
+    activation after it is stored channels-last; parameters and their gradients keep the
+    reference's layout either way."""
     gen = torch.Generator().manual_seed(seed)
+    if channels_last is None:
+        channels_last = CHANNELS_LAST
     m = nn.Sequential()
-    m.add(nn.Conv2D(3, width, 7, 7, 2, 2, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device))
+    m.add(nn.Conv2D(3, width, 7, 7, 2, 2, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device,
+                    channels_last_out=True if channels_last else None))
     if FUSE_BATCHNORM_RELU:
         m.add(nn.BatchNormReLU(2, width, gen=gen, device=device))
     else:

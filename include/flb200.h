@@ -53,6 +53,15 @@ enum { FLB200_RNN_RELU = 0, FLB200_RNN_TANH = 1, FLB200_RNN_LSTM = 2, FLB200_RNN
  * (TF32: ~1e-3), at about two thirds of the TF32 speed on a ResNet-50 step. */
 enum { FLB200_MATH_STRICT_F32 = 0, FLB200_MATH_TF32 = 1, FLB200_MATH_F32X3 = 2 };
 
+/* Memory layout of image tensors.  NCHW is fl's own: an fl tensor [W,H,C,N] (column-major) read
+ * row-major.  NHWC ("channels-last") is the same logical tensor stored as fl [C,W,H,N]: the
+ * layout the tensor-core convolutions read natively (a filter tap then shifts whole pixels and
+ * the contiguous index is the channel), so a network that keeps its activations channels-last
+ * between operators pays for no layout copy at all.  Filters, biases and statistics keep the
+ * reference layout in every mode.  NCHW_IN_NHWC_OUT is for a network's first convolution: x
+ * (and nothing else) arrives in fl's order, y / grad_y are channels-last. */
+enum { FLB200_LAYOUT_NCHW = 0, FLB200_LAYOUT_NCHW_IN_NHWC_OUT = 2, FLB200_LAYOUT_NHWC = 3 };
+
 /* fl::ReduceMode (flashlight/fl/autograd/Functions.h) */
 enum { FLB200_REDUCE_NONE = 0, FLB200_REDUCE_MEAN = 1, FLB200_REDUCE_SUM = 2 };
 
@@ -82,11 +91,16 @@ typedef struct flb200_conv2d_desc {
   int32_t sx, sy, px, py, dx, dy, groups;
   int32_t dtype;      /* FLB200_F32 only */
   int32_t math_mode;  /* FLB200_MATH_* */
+  int32_t layout;     /* FLB200_LAYOUT_* of x / grad_x and y / grad_y (0 = fl's own) */
 } flb200_conv2d_desc;
 
 int flb200_conv2d_output_dims(const flb200_conv2d_desc* d, int32_t* Wo, int32_t* Ho);
 
-/* which: 0 forward, 1 backward-data, 2 backward-filter(+bias) */
+/* which: 0 forward, 1 backward-data, 2 backward-filter(+bias).
+ * Alignment: any 4-byte aligned tensor and workspace is accepted.  The tensor-core modes
+ * (TF32, F32X3) only engage when x / w / y (grad_y, grad_x, grad_w) and the workspace start on
+ * 16-byte boundaries (TMA and 16-byte vector accesses); a call with an offset view or an odd
+ * workspace runs on the fp32 kernels instead, with fp32 results. */
 size_t flb200_conv2d_workspace_bytes(const flb200_conv2d_desc* d, int which);
 
 /* fl::AutogradExtension::conv2d — flashlight/fl/autograd/tensor/AutogradExtension.h:58-69.
@@ -156,6 +170,7 @@ typedef struct flb200_pool2d_desc {
   int32_t wx, wy, sx, sy, px, py;
   int32_t mode;   /* FLB200_POOL_* */
   int32_t dtype;  /* FLB200_F32 */
+  int32_t layout; /* FLB200_LAYOUT_NCHW or FLB200_LAYOUT_NHWC (x, y, argmax and gradients alike) */
 } flb200_pool2d_desc;
 
 /* Wo = 1 + (W + 2 px - wx) / sx — flashlight/fl/autograd/tensor/backend/onednn/Pool2D.cpp:100-102 */

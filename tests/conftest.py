@@ -54,3 +54,17 @@ def _no_expired_device_waits(request):
         return
     from flashlight_b200 import _lib
     assert _lib.lib.flb200_tc_poll_status(None) == 0, "a bounded device wait ran out in this test"
+
+
+def pytest_sessionfinish(session, exitstatus):
+    """Largest element-wise relative errors (floor at 0.1 % of the tensor scale) seen by
+    tests/parity.assert_close in this session: the measured worst cases behind the bounds."""
+    try:
+        from tests.parity import WORST
+    except Exception:  # pragma: no cover
+        return
+    if not WORST:
+        return
+    top = sorted(WORST.items(), key=lambda kv: -kv[1])[:12]
+    print("\nworst relative errors at the 0.1 % floor: " +
+          ", ".join(f"{k or '?'} {v:.2e}" for k, v in top))

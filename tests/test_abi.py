@@ -29,7 +29,7 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_status_strings_and_version():
-    assert L.lib.flb200_abi_version() == 1
+    assert L.lib.flb200_abi_version() == 2
     assert L.lib.flb200_status_string(0) == b"ok"
     assert b"invalid" in L.lib.flb200_status_string(L.INVALID_ARG)
 

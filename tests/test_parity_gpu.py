@@ -291,10 +291,10 @@ def test_large_average_window(ext, mode):
     y = ext.pool2d(x.cuda(), 16, 16, 2, 2, 1, 1, mode, None)
     want = R.pool2d(x.double(), 16, 16, 2, 2, 1, 1, mode)
     assert tuple(y.shape) == tuple(want.shape)
-    assert_close(y, want, 1e-5, "16x16 average pool")
+    assert_close(y, want, 5e-5, "16x16 average pool")  # fp32 sum of 256 values
     gy = randn(*want.shape, seed=30)
     gx = ext.pool2dBackward(gy.cuda(), x.cuda(), y, 16, 16, 2, 2, 1, 1, mode, None)
-    assert_close(gx, R.pool2d_backward(gy.double(), x.double(), 16, 16, 2, 2, 1, 1, mode), 1e-5,
+    assert_close(gx, R.pool2d_backward(gy.double(), x.double(), 16, 16, 2, 2, 1, 1, mode), 5e-5,
                  "16x16 average pool gradient")
     with pytest.raises(Exception):
         ext.pool2d(x.cuda(), 16, 16, 2, 2, 1, 1, R.POOL_MAX, None)

@@ -178,6 +178,51 @@ def test_conv2d_tf32(L, case):
         assert n1 == 0 and n2 == 0 and n3 == 0
 
 
+@pytest.mark.parametrize("which", ["x", "w", "gy"])
+@pytest.mark.parametrize("case", [(2, 64, 16, 16, 256, 1, 1, 0), (2, 64, 14, 14, 64, 3, 1, 1)])
+def test_conv2d_tf32_unaligned_operand_runs_on_fp32_kernel(L, case, which):
+    """The tensor-core routes hand their operands to TMA and use 16-byte vectors on the scratch:
+    a tensor that starts 4 bytes off a 16-byte boundary (an offset view) must never reach them.
+    The call still succeeds, on the fp32 kernel, and meets the strict bound."""
+    from flashlight_b200.extension import B200AutogradExtension
+    N, Cin, H, W, Cout, k, s, p = case
+    ext = B200AutogradExtension(math_mode=L.MATH_TF32, cache_layouts=False)
+
+    def off_by_4(t):  # same values, storage starting one float past an aligned address
+        buf = torch.empty(t.numel() + 1, dtype=t.dtype, device="cuda")
+        view = buf[1:].view(t.shape)
+        view.copy_(t)
+        assert view.data_ptr() % 16 == 4
+        return view
+
+    x = randn(N, Cin, H, W, seed=51)
+    w = randn(Cout, Cin, k, k, seed=52) * (1.0 / (Cin * k * k) ** 0.5)
+    args = (s, s, p, p, 1, 1, 1)
+    want = R.conv2d(x.double(), w.double(), None, *args)
+    gy = randn(*want.shape, seed=53)
+    xd = off_by_4(x) if which == "x" else x.cuda()
+    wd = off_by_4(w) if which == "w" else w.cuda()
+    gyd = off_by_4(gy) if which == "gy" else gy.cuda()
+    def check(got, wanted, op_uses, what):
+        # the passes that read the offset tensor run in fp32 (strict bound); the third pass
+        # still takes the tensor-core route (TF32 bound)
+        if which in op_uses:
+            assert_close(got, wanted, 1e-4, what + " on an offset view")
+        else:
+            assert_close_scaled(got, wanted, TF32_SCALED_TOL, what)
+
+    y, n1 = tc_delta(L, lambda: ext.conv2d(xd, wd, None, *args))
+    check(y, want, ("x", "w"), "conv forward")
+    gx, n2 = tc_delta(L, lambda: ext.conv2dBackwardData(gyd, xd, wd, *args))
+    check(gx, R.conv2d_backward_data(gy.double(), x.shape, w.double(), *args), ("gy", "w"),
+          "conv backward data")
+    (gw, _), n3 = tc_delta(L, lambda: ext.conv2dBackwardFilterBias(gyd, xd, wd, None, *args))
+    wgw, _ = R.conv2d_backward_filter_bias(gy.double(), x.double(), w.shape, False, *args)
+    check(gw, wgw, ("gy", "x"), "conv backward filter")
+    uses = {"x": (n1, n3), "w": (n1, n2), "gy": (n2, n3)}[which]
+    assert uses == (0, 0), f"an unaligned {which} reached a tensor-core kernel: {uses}"
+
+
 @pytest.mark.parametrize("dims", [
     (80, 128, 2, 32, 6),    # per-step contraction + cell kernel
     (80, 256, 2, 32, 5),    # fused LSTM step, one CTA per cluster
