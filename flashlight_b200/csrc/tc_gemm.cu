@@ -6,6 +6,7 @@
 
 #include "tc_gemm.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 #include "tc_pair.cuh"
@@ -159,6 +160,11 @@ int pick_bn(long long N) {
   return 256;
 }
 
+static long long env_ll(const char* name, long long dflt) {
+  const char* v = getenv(name);
+  return v && *v ? atoll(v) : dflt;
+}
+
 bool gemm_uses_pairs(long long M, long long N, long long k_iters, bool a_mn_major,
                      bool b_mn_major) {
   if (x3_enabled()) return false;  // the CTA-pair kernel has no 3xTF32 instantiation
@@ -166,7 +172,14 @@ bool gemm_uses_pairs(long long M, long long N, long long k_iters, bool a_mn_majo
   // with 256-column tiles; with both operands MN-major (1x1 backward data: 8 copies per CTA
   // and stage) pairs measured between 7 % faster and 11 % slower and are not used.
   if (a_mn_major && !b_mn_major) return pick_bn(N) >= 256 && M > kBM && k_iters >= 8;
-  return pick_bn(N) >= 128 && M > kBM && !a_mn_major && !b_mn_major && k_iters >= 64;
+  if (a_mn_major || b_mn_major) return false;
+  // both K-major: long K loops (backward-filter of 1 x 1 layers) ...
+  if (pick_bn(N) >= 128 && M > kBM && k_iters >= 64) return true;
+  // ... and tall products with wide rows (1 x 1 layers over channels-last tensors, linear
+  // layers): every 128-row tile re-reads the whole B panel out of L2, a pair halves that
+  static const long long min_k = env_ll("FLB200_PAIR_MIN_K", 4);
+  static const long long min_bn = env_ll("FLB200_PAIR_MIN_BN", 256);
+  return pick_bn(N) >= min_bn && M >= 8 * kBM && k_iters >= min_k;
 }
 int b_box_rows(long long M, long long N, long long k_iters, bool a_mn_major, bool b_mn_major) {
   const int bn = pick_bn(N);

@@ -38,7 +38,10 @@
 //                        // one stage, called by the whole warp: lane 0 posts the byte count,
 //                        // lane i issues copy i; every lane advances its LoadState
 //   __device__ bool chunk_live(const Tile&, int c0) const;                // warp-uniform
-//   __device__ void store(const Tile&, int row, int c0, const float* v) const;  // 32 columns
+//   __device__ void store(const Tile&, int row, int c0, const float* v, float* stage,
+//                         int lane) const;   // 32 columns of row `row`; called by all 32 lanes
+//                         // of an epilogue warp (rows row - lane .. + 31), `stage` is the
+//                         // warp's 4 KB staging tile for policies that store through it
 #pragma once
 #include <cuda_bf16.h>
 
@@ -46,6 +49,26 @@
 
 namespace flb200 {
 namespace tc {
+
+// Staging tile of one epilogue warp and the transposing store through it.  The accumulator
+// arrives with one row per lane (32 consecutive columns in registers).  Written to a row-major
+// output as it is, every store instruction touches 32 rows at 16 bytes each (32 memory sectors,
+// half filled); staged through shared memory, an instruction stores 4 whole 128-byte rows.
+// Layout: row r, 16-byte chunk q at chunk (q ^ (r & 7)) of row r: conflict-free both ways.
+constexpr int kEpiStageBytes = 32 * 128;
+__device__ __forceinline__ void epi_stage_write(float* stage, int lane, const float* v) {
+  float4* rowp = reinterpret_cast<float4*>(stage) + lane * 8;
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    rowp[q ^ (lane & 7)] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  __syncwarp();
+}
+// The float4 that lane `lane` stores in step k (0..7): row 4 * k + lane / 8, columns
+// 4 * (lane % 8) .. + 3 of the chunk.
+__device__ __forceinline__ float4 epi_stage_read(const float* stage, int lane, int k) {
+  const int r = 4 * k + (lane >> 3), q = lane & 7;
+  return reinterpret_cast<const float4*>(stage)[r * 8 + (q ^ (r & 7))];
+}
 
 // X3 = 1: every stage also holds the low-order tiles of the 3xTF32 split (see the kernel).
 template <int BN, int STAGES, int X3 = 0>
@@ -56,7 +79,10 @@ struct SmemLayout {
   static constexpr int kStageBytes = (X3 ? 2 : 1) * (kABytes + kBBytes);
   static constexpr int kTileBytes = STAGES * kStageBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int kTotal = kTileBytes + kBarBytes + 1024;  // + slack to align to 1024
+  // 4 KB per epilogue warp: a 32 x 32 accumulator chunk is turned from "one row per lane" into
+  // "128 contiguous bytes per 8 lanes" through it before it is stored to a row-major output
+  static constexpr int kStagingBytes = ((X3 == 0 && BN >= 128) ? 8 : 4) * kEpiStageBytes;
+  static constexpr int kTotal = kTileBytes + kBarBytes + kStagingBytes + 1024;  // + slack to align
 };
 
 // ~200 KB of tiles per CTA
@@ -363,6 +389,10 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
     const int group = warp < 6 ? 0 : 1;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
+    float* stage = reinterpret_cast<float*>(tiles + SL::kTileBytes + SL::kBarBytes +
+                                            (group * 4 + (warp < 6 ? warp - 2
+                                                                   : warp - second_epilogue_first_warp<P, X3>())) *
+                                                kEpiStageBytes);
     uint32_t nt = 0;
     typename P::Tile t;
     TC_PROF_VAR(e_wait);
@@ -386,7 +416,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!prob.chunk_live(t, c0)) continue;  // uniform across the warp; need not be a prefix
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
-        prob.store(t, row, c0, v);
+        prob.store(t, row, c0, v, stage, lane);
       }
       tc_fence_before();
       __syncwarp();
@@ -508,10 +538,47 @@ struct GemmProblem {
     return t.n0 + c0 < N;
   }
 
-  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v) const {
+  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v,
+                                        float* stage, int lane) const {
     const int m = t.m0 + row;
-    if (m >= M) return;
     const int nb = t.n0 + c0;
+    // Row-major fp32 output with nothing but alpha to apply (a linear layer's product, a 1 x 1
+    // convolution over channels-last tensors, split-K partial sums): through the staging tile,
+    // whole 128-byte rows per store instruction.  The condition is uniform across the warp.
+    {
+      float* base = nullptr;
+      long long ld = 0;
+      float scale = 1.f;
+      if (splits > 1) {
+        if ((N & 3) == 0) {
+          base = partial + ((long long)(t.z * splits + t.split) * M) * N;
+          ld = N;
+        }
+      } else if (!ep.out_bf16 && ep.beta == 0.f && ep.n_div == 0 && ep.m_div == 0 &&
+                 ep.n_stride == 1 && ep.bias_m == nullptr && ep.bias_n == nullptr &&
+                 (ep.m_stride & 3) == 0 && ((ep.z_stride * t.z) & 3) == 0 &&
+                 (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) {
+        base = ep.out + (long long)t.z * ep.z_stride;
+        ld = ep.m_stride;
+        scale = ep.alpha;
+      }
+      if (base != nullptr && nb + 32 <= N) {
+        float w[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) w[j] = scale * v[j];
+        epi_stage_write(stage, lane, w);
+        const int m_first = m - lane;  // first row of this warp
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int mr = m_first + 4 * k + (lane >> 3);
+          const float4 val = epi_stage_read(stage, lane, k);
+          if (mr < M) *reinterpret_cast<float4*>(base + (long long)mr * ld + nb + 4 * (lane & 7)) = val;
+        }
+        __syncwarp();  // the tile is rewritten by the next chunk
+        return;
+      }
+    }
+    if (m >= M) return;
     if (splits > 1) {
       float* dst = partial + ((long long)(t.z * splits + t.split) * M + m) * N + nb;
       if (nb + 32 <= N && (N & 3) == 0) {

@@ -42,7 +42,8 @@ struct PairSmemLayout {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTileBytes = STAGES * kStageBytes;
   static constexpr int kBarBytes = 512;
-  static constexpr int kTotal = kTileBytes + kBarBytes + 1024;
+  static constexpr int kStagingBytes = 8 * kEpiStageBytes;  // one staging tile per epilogue warp
+  static constexpr int kTotal = kTileBytes + kBarBytes + kStagingBytes + 1024;
 };
 constexpr int pair_stages_for(int bn) { return bn >= 256 ? 6 : 8; }
 
@@ -226,6 +227,10 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
     const int group = warp < 6 ? 0 : 1;
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
+    float* stage = reinterpret_cast<float*>(
+        tiles + SL::kTileBytes + SL::kBarBytes +
+        (group * 4 + (warp < 6 ? warp - 2 : warp - pair_second_epilogue_first_warp<P>())) *
+            kEpiStageBytes);
     uint32_t nt = 0;
     typename P::Tile t;
     TC_PROF_VAR(e_wait);
@@ -249,7 +254,7 @@ tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
         if (!prob.chunk_live(t, c0)) continue;
         float v[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * BN + (uint32_t)c0, v);
-        prob.store(t, row, c0, v);
+        prob.store(t, row, c0, v, stage, lane);
       }
       tc_fence_before();
       __syncwarp();

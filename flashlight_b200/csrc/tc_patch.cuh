@@ -157,8 +157,36 @@ struct PatchConvProblem {
   __device__ __forceinline__ bool chunk_live(const Tile& t, int c0) const {
     return t.n0 + c0 < n_out;
   }
-  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v) const {
+  // output address of row `r` of the tile (channels-last output, class offsets applied), or
+  // null for a row outside the image
+  __device__ __forceinline__ float* cl_row(const Tile& t, int r) const {
+    const int q = t.q0 + (r & (QW - 1));
+    const int p = t.p0 + ((r >> qw_shift) & (PH - 1));
+    const int img = t.b0 + (r >> (qw_shift + ph_shift));
+    if (q >= pix_w || p >= pix_h || img >= images) return nullptr;
+    return out + (((long long)img * out_H + p * oh_mul + cls[t.c].oh_add) * out_W + q * ow_mul +
+                  cls[t.c].ow_add) * out_C;
+  }
+  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v,
+                                        float* stage, int lane) const {
     const int nb = t.n0 + c0;
+    if (out_cl && !fill_cell && nb + 32 <= n_out && (out_C & 3) == 0) {
+      // channels-last output: through the warp's staging tile, 4 whole 128-byte pixel rows per
+      // store instruction (see tc_kernel.cuh)
+      epi_stage_write(stage, lane, v);
+      float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (bias) bq = *reinterpret_cast<const float4*>(bias + nb + 4 * (lane & 7));
+      const int r_first = row - lane;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        float* dst = cl_row(t, r_first + 4 * k + (lane >> 3));
+        float4 val = epi_stage_read(stage, lane, k);
+        val.x += bq.x; val.y += bq.y; val.z += bq.z; val.w += bq.w;
+        if (dst) *reinterpret_cast<float4*>(dst + nb + 4 * (lane & 7)) = val;
+      }
+      __syncwarp();
+      return;
+    }
     // row -> (image, p, q) inside the patch
     const int q = t.q0 + (row & (QW - 1));
     const int p = t.p0 + ((row >> qw_shift) & (PH - 1));
@@ -318,7 +346,8 @@ struct PatchWgradProblem {
     const int j = c0 >> 5;
     return (j >> cn_shift) < t.ntap && (j & ((1 << cn_shift) - 1)) < t.cn_live;
   }
-  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v) const {
+  __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v, float*,
+                                        int) const {
     const int m = t.m0 + row;
     if (m >= M) return;
     const int j = c0 >> 5;

@@ -26,6 +26,11 @@ from . import functions as F
 from .extension import AutogradPayload, B200AutogradExtension
 
 ROOT = Path(__file__).resolve().parent.parent
+CHANNELS_LAST = False  # --channels-last: image tensors stored [N][H][W][C]
+
+
+def images(t):
+    return t.contiguous(memory_format=torch.channels_last) if CHANNELS_LAST and t.dim() == 4 else t
 
 
 def peaks():
@@ -52,6 +57,8 @@ def time_op(fn, iters, warmup=3):
 def report(op, desc, ms, nbytes=None, flops=None, math="strict", extra=None):
     hbm, bf16, src = peaks()
     line = {"op": op, "case": desc, "ms": ms, "math": math}
+    if CHANNELS_LAST:
+        line["layout"] = "channels_last"
     if flops:
         tf = flops / (ms * 1e-3) / 1e12
         peak = bf16 / 2  # tf32 tensor rate = half the bf16 rate
@@ -83,8 +90,8 @@ def bench_eltwise(op, shape, iters):
 
 def bench_bn(op, shape, iters, axes=(2,)):
     ext = B200AutogradExtension(L.MATH_STRICT_F32)
-    x = torch.randn(shape, device="cuda")
-    g = torch.randn(shape, device="cuda")
+    x = images(torch.randn(shape, device="cuda"))
+    g = images(torch.randn(shape, device="cuda"))
     ch = shape[1]
     w = torch.rand(ch, device="cuda")
     b = torch.zeros(ch, device="cuda")
@@ -105,7 +112,7 @@ def bench_bn(op, shape, iters, axes=(2,)):
         # two incoming gradients and the mask in; the join's gradient and dx out (20 B/elem of
         # interface traffic; the passes move 28)
         _, mask, sm, sv = ext.batchnormAddRelu(x, g, w, b, rm, rv, list(axes), True, 0.1, 1e-5)
-        g2 = torch.randn(shape, device="cuda")
+        g2 = images(torch.randn(shape, device="cuda"))
         ms = time_op(lambda: ext.batchnormAddReluBackward(mask, g, g2, sm, sv, x, w, list(axes), True,
                                                           1e-5), iters)
         return report(op, list(shape), ms, nbytes=20 * n)
@@ -120,7 +127,7 @@ def bench_bn(op, shape, iters, axes=(2,)):
 
 def bench_pool(op, shape, iters, geo=(3, 3, 2, 2, 1, 1), mode=L.POOL_MAX):
     ext = B200AutogradExtension(L.MATH_STRICT_F32)
-    x = torch.randn(shape, device="cuda")
+    x = images(torch.randn(shape, device="cuda"))
     payload = AutogradPayload()
     y = ext.pool2d(x, *geo, mode, payload)
     g = torch.randn_like(y)
@@ -143,13 +150,16 @@ def bench_conv(op, conv, iters, math):
     mode = L.MATH_BY_NAME.get(math, L.MATH_TF32)
     ext = B200AutogradExtension(mode)
     x = torch.randn(N, Cin, H, W, device="cuda")
+    first = CHANNELS_LAST and Cin <= 4  # a network's first layer: x in fl's order, y channels-last
+    if not first:
+        x = images(x)
     w = torch.randn(Cout, Cin, k, k, device="cuda") * (1.0 / (Cin * k * k) ** 0.5)
     args = (s, s, p, p, 1, 1, 1)
-    y = ext.conv2d(x, w, None, *args)
+    y = ext.conv2d(x, w, None, *args, None, True if first else None)
     g = torch.randn_like(y)
     flops = 2.0 * y.numel() * Cin * k * k
     if op == "conv2d":
-        fn = lambda: ext.conv2d(x, w, None, *args)
+        fn = lambda: ext.conv2d(x, w, None, *args, None, True if first else None)
     elif op == "conv2dBackwardData":
         fn = lambda: ext.conv2dBackwardData(g, x, w, *args)
     else:
@@ -314,9 +324,13 @@ def main():
     ap.add_argument("--conv", default="64,64,56,56,64,3,1,1")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--channels-last", action="store_true",
+                    help="image tensors stored channels-last ([N][H][W][C])")
     ap.add_argument("--math", default="strict", choices=["strict", "tf32", "f32x3", "bf16"],
                     help="bf16 only applies to the transformer workload")
     a = ap.parse_args()
+    global CHANNELS_LAST
+    CHANNELS_LAST = a.channels_last
     if not torch.cuda.is_available():
         raise SystemExit("opbench needs a CUDA device")
     shape = tuple(int(v) for v in a.shape.split(","))
