@@ -252,16 +252,18 @@ column_reduce_vec_kernel(const float* __restrict__ a, const float* __restrict__ 
     long long r1 = r0 + rows_per_split;
     if (r1 > rows) r1 = rows;
     long long r = r0 + tr;
-    for (; r + 3LL * rl < r1; r += 4LL * rl) {
-      float4 va[4], vb[4];
+    // eight 16-byte loads in flight per thread: 8 rows of one tensor or 4 rows of two
+    constexpr int U = NIN == 2 ? 4 : 8;
+    for (; r + (long long)(U - 1) * rl < r1; r += (long long)U * rl) {
+      float4 va[U], vb[U];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         const long long off = (r + (long long)u * rl) * channels + c;
         va[u] = *reinterpret_cast<const float4*>(a + off);
         if (NIN == 2) vb[u] = *reinterpret_cast<const float4*>(b + off);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < U; ++u) {
         f.accumulate(k[0], va[u].x, NIN == 2 ? vb[u].x : 0.f, s0[0], s1[0]);
         f.accumulate(k[1], va[u].y, NIN == 2 ? vb[u].y : 0.f, s0[1], s1[1]);
         f.accumulate(k[2], va[u].z, NIN == 2 ? vb[u].z : 0.f, s0[2], s1[2]);

@@ -181,6 +181,9 @@ B200AutogradExtension::B200AutogradExtension() : mathMode_(FLB200_MATH_STRICT_F3
   if (env && env[0] != '\0' && env[0] != '0') {
     mathMode_ = FLB200_MATH_TF32;
   }
+  if (const char* poll = std::getenv("FLB200_POLL_EVERY_CALL")) {
+    pollEveryCall_ = poll[0] != '\0' && poll[0] != '0';
+  }
   // FLB200_MATH=strict|tf32|f32x3 names the mode and wins over FLB200_TF32
   if (const char* name = std::getenv("FLB200_MATH")) {
     const std::string mode(name);
@@ -192,6 +195,10 @@ B200AutogradExtension::B200AutogradExtension() : mathMode_(FLB200_MATH_STRICT_F3
       mathMode_ = FLB200_MATH_F32X3;
     }
   }
+}
+
+void B200AutogradExtension::checkDeviceWaits() {
+  check(flb200_tc_poll_status(stream().handle()), "B200AutogradExtension");
 }
 
 const CUDAStream& B200AutogradExtension::stream() {
@@ -237,6 +244,9 @@ Tensor B200AutogradExtension::conv2d(
             conv ? &conv->cache : nullptr, st.handle()),
         "conv2d");
     relativeSync({output}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return output;
 }
@@ -268,6 +278,9 @@ Tensor B200AutogradExtension::conv2dBackwardData(
             conv ? &conv->cache : nullptr, st.handle()),
         "conv2dBackwardData");
     relativeSync({gradInput}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return gradInput;
 }
@@ -319,6 +332,9 @@ std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
       conv->cache.gy_cl_valid = 0;
     }
     relativeSync({gradWeights, gradBias}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return {gradWeights, gradBias};
 }
@@ -332,13 +348,18 @@ Tensor B200AutogradExtension::pool2d(
   int32_t wo = 0, ho = 0;
   check(flb200_pool2d_output_dims(&d, &wo, &ho), "pool2d");
   auto output = Tensor({wo, ho, d.C, d.N}, input.type());
-  Tensor argmax;
+  // The argmax tensor is created inside the payload and used from there (as the cuDNN backend
+  // does with its reserve space, cudnn/RNN.cpp:157-175): copying an fl::Tensor may be an eager
+  // deep copy or copy-on-write depending on the tensor backend, and a copy taken before the
+  // kernel ran would not see what it writes.
+  Tensor none;
+  std::shared_ptr<PoolPayload> data;
   if (payload && mode == PoolingMode::MAX) {
-    argmax = Tensor({wo, ho, d.C, d.N}, fl::dtype::u8);
-    auto data = std::make_shared<PoolPayload>();
-    data->argmax = argmax;
+    data = std::make_shared<PoolPayload>();
+    data->argmax = Tensor({wo, ho, d.C, d.N}, fl::dtype::u8);
     payload->data = data;
   }
+  const Tensor& argmax = data ? data->argmax : none;
   {
     DevicePtr inPtr(input), outPtr(output), amPtr;
     void* am = ptrOrNull(argmax, amPtr);
@@ -349,6 +370,9 @@ Tensor B200AutogradExtension::pool2d(
             &d, inPtr.get(), outPtr.get(), static_cast<uint8_t*>(am), st.handle()),
         "pool2d");
     relativeSync({output, argmax}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return output;
 }
@@ -360,10 +384,10 @@ Tensor B200AutogradExtension::pool2dBackward(
   requireF32(gradOutput, "pool2dBackward");
   const auto d = poolDesc(input, wx, wy, sx, sy, px, py, mode);
   auto gradInput = Tensor(input.shape(), input.type());
-  Tensor argmax;
-  if (payload && payload->data) {
-    argmax = std::static_pointer_cast<PoolPayload>(payload->data)->argmax;
-  }
+  Tensor none;
+  const Tensor& argmax = payload && payload->data
+      ? std::static_pointer_cast<PoolPayload>(payload->data)->argmax
+      : none;
   {
     DevicePtr goPtr(gradOutput), inPtr(input), giPtr(gradInput), amPtr;
     void* am = ptrOrNull(argmax, amPtr);
@@ -375,6 +399,9 @@ Tensor B200AutogradExtension::pool2dBackward(
             st.handle()),
         "pool2dBackward");
     relativeSync({gradInput}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return gradInput;
 }
@@ -418,6 +445,9 @@ Tensor B200AutogradExtension::batchnorm(
             outPtr.get(), wsPtr.get(), wsBytes, st.handle()),
         "batchnorm");
     relativeSync({output, runningMean, runningVar, saveMean, saveVar}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return output;
 }
@@ -450,6 +480,9 @@ std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::batchnormBackward(
             wsPtr.get(), wsBytes, st.handle()),
         "batchnormBackward");
     relativeSync({gradIn, gradWt, gradBs}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return std::make_tuple(gradIn, gradWt, gradBs);
 }
@@ -480,15 +513,16 @@ std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::rnn(
   if (mode == RnnMode::LSTM) {
     cy = Tensor({hiddenSize, d.batch, numLayers * dirs}, input.type());
   }
-  Tensor reserve;
+  Tensor none;
+  std::shared_ptr<RnnPayload> data;
   size_t reserveBytes = 0;
-  if (payload) {
+  if (payload) {  // created inside the payload and used from there (see pool2d)
     reserveBytes = flb200_rnn_reserve_bytes(&d);
-    reserve = scratch(reserveBytes);
-    auto data = std::make_shared<RnnPayload>();
-    data->reserve = reserve;
+    data = std::make_shared<RnnPayload>();
+    data->reserve = scratch(reserveBytes);
     payload->data = data;
   }
+  const Tensor& reserve = data ? data->reserve : none;
   const size_t wsBytes = flb200_rnn_workspace_bytes(&d, payload ? 0 : 2);
   auto ws = scratch(wsBytes);
   {
@@ -502,6 +536,10 @@ std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::rnn(
             wsPtr.get(), wsBytes, st.handle()),
         "rnn");
     relativeSync({y, hy, cy, reserve}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
+
   }
   return std::make_tuple(y, hy, cy);
 }
@@ -517,7 +555,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> B200AutogradExtension::rnnBackward(
         "B200AutogradExtension::rnnBackward given null detail::AutogradPayload");
   }
   const auto d = rnnDesc(input, hiddenSize, numLayers, mode, bidirectional, mathMode_);
-  auto reserve = std::static_pointer_cast<RnnPayload>(payload->data)->reserve;
+  const Tensor& reserve = std::static_pointer_cast<RnnPayload>(payload->data)->reserve;
   const auto x = input.asContiguousTensor();
   const auto hx = hiddenState.isEmpty() ? hiddenState : hiddenState.asContiguousTensor();
   const auto cx = cellState.isEmpty() ? cellState : cellState.asContiguousTensor();
@@ -550,6 +588,9 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> B200AutogradExtension::rnnBackward(
             static_cast<size_t>(reserve.elements()), wsPtr.get(), wsBytes, st.handle()),
         "rnnBackward");
     relativeSync({dx, dhx, dcx, dw}, st);
+    if (pollEveryCall_) {
+      checkDeviceWaits();
+    }
   }
   return std::make_tuple(dx, dhx, dcx, dw);
 }

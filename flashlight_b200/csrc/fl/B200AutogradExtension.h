@@ -26,6 +26,14 @@ class B200AutogradExtension final : public AutogradExtension {
   // fp32 is the built dtype of the dense operators (f16 / bf16 exist for the element-wise ones)
   bool isDataTypeSupported(const fl::dtype& dtype) const override;
 
+  // Every wait inside the tensor-core kernels is bounded: one that runs out raises a device
+  // flag and the kernel returns with partial results instead of hanging the GPU.  This call
+  // synchronises the extension's stream, reads and clears the flag and throws
+  // std::runtime_error if it was set.  Call it wherever the host synchronises anyway (end of
+  // a step, before reading a loss); with FLB200_POLL_EVERY_CALL=1 in the environment every
+  // operator does it after its launch (debugging aid: it serialises host and device).
+  void checkDeviceWaits();
+
   /**************************** Forward ****************************/
   Tensor conv2d(
       const Tensor& input, const Tensor& weights, const Tensor& bias, const int sx, const int sy,
@@ -84,6 +92,7 @@ class B200AutogradExtension final : public AutogradExtension {
   // FLB200_MATH_STRICT_F32, _TF32 or _F32X3 (environment FLB200_MATH=strict|tf32|f32x3, or
   // FLB200_TF32=1; read once)
   int mathMode_;
+  bool pollEveryCall_ = false;
   // the stream the kernels run on; ordered against the tensors' streams around every call
   std::shared_ptr<CUDAStream> stream_;
   const CUDAStream& stream();

@@ -13,6 +13,7 @@
 #include "common.cuh"
 
 #include <cfloat>
+#include <type_traits>
 
 namespace flb200 {
 namespace {
@@ -394,15 +395,16 @@ pool_backward_max_strip_kernel(const T* __restrict__ dy, const uint8_t* __restri
 template <typename T, int V>
 __global__ void __launch_bounds__(256)
 pool_forward_cl_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __restrict__ argmax,
-                       PoolGeo g, int C, long long total) {
-  const int cv = C / V;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
-    const int c = (int)(t % cv) * V;
-    long long r = t / cv;
-    const int q = (int)(r % g.Wo); r /= g.Wo;
-    const int p = (int)(r % g.Ho);
-    const long long n = r / g.Ho;
+                       PoolGeo g, int C, int per_image) {
+  // blockIdx.y = image; the index inside an image fits 32 bits (checked by the launcher)
+  const unsigned cv = C / V;
+  const long long n = blockIdx.y;
+  for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < (unsigned)per_image;
+       t += gridDim.x * blockDim.x) {
+    const unsigned pix = t / cv;
+    const int c = (int)(t - pix * cv) * V;
+    const int p = (int)(pix / (unsigned)g.Wo);
+    const int q = (int)(pix - (unsigned)p * (unsigned)g.Wo);
     const int h0 = p * g.sy - g.py, w0 = q * g.sx - g.px;
     const T* xn = x + n * (long long)g.H * g.W * C + c;
     float acc[V];
@@ -445,8 +447,15 @@ pool_forward_cl_kernel(const T* __restrict__ x, T* __restrict__ y, uint8_t* __re
       for (int j = 0; j < V; ++j) y[o + j] = outv[j];
     }
     if (argmax && g.mode == FLB200_POOL_MAX) {
+      uint8_t sels[V];
 #pragma unroll
-      for (int j = 0; j < V; ++j) argmax[o + j] = (uint8_t)arg[j];
+      for (int j = 0; j < V; ++j) sels[j] = (uint8_t)arg[j];
+      if (V == 4) *reinterpret_cast<uint32_t*>(argmax + o) = *reinterpret_cast<const uint32_t*>(sels);
+      else if (V == 8) *reinterpret_cast<uint2*>(argmax + o) = *reinterpret_cast<const uint2*>(sels);
+      else {
+#pragma unroll
+        for (int j = 0; j < V; ++j) argmax[o + j] = sels[j];
+      }
     }
   }
 }
@@ -455,15 +464,15 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256)
 pool_backward_cl_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                         const uint8_t* __restrict__ argmax, T* __restrict__ dx, PoolGeo g, int C,
-                        long long total) {
-  const int cv = C / V;
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += stride) {
-    const int c = (int)(t % cv) * V;
-    long long r = t / cv;
-    const int w = (int)(r % g.W); r /= g.W;
-    const int h = (int)(r % g.H);
-    const long long n = r / g.H;
+                        int per_image) {
+  const unsigned cv = C / V;
+  const long long n = blockIdx.y;
+  for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < (unsigned)per_image;
+       t += gridDim.x * blockDim.x) {
+    const unsigned pix = t / cv;
+    const int c = (int)(t - pix * cv) * V;
+    const int h = (int)(pix / (unsigned)g.W);
+    const int w = (int)(pix - (unsigned)h * (unsigned)g.W);
     const int p_lo = max(ceil_div_pos(h + g.py - g.wy + 1, g.sy), 0);
     const int p_hi = min((h + g.py) / g.sy, g.Ho - 1);
     const int q_lo = max(ceil_div_pos(w + g.px - g.wx + 1, g.sx), 0);
@@ -482,11 +491,20 @@ pool_backward_cl_kernel(const T* __restrict__ dy, const T* __restrict__ x,
         }
         if (g.mode == FLB200_POOL_MAX) {
           const int mine = (h + g.py - p * g.sy) * g.wx + (w + g.px - q * g.sx);
+          uint8_t sels[V];
+          if (argmax) {  // the V window positions in one load (o is a multiple of V)
+            if (V == 4) *reinterpret_cast<uint32_t*>(sels) = *reinterpret_cast<const uint32_t*>(argmax + o);
+            else if (V == 8) *reinterpret_cast<uint2*>(sels) = *reinterpret_cast<const uint2*>(argmax + o);
+            else {
+#pragma unroll
+              for (int j = 0; j < V; ++j) sels[j] = argmax[o + j];
+            }
+          }
 #pragma unroll
           for (int j = 0; j < V; ++j) {
             int sel;
             if (argmax) {
-              sel = argmax[o + j];
+              sel = sels[j];
             } else {  // recompute the selection of window (p, q) for channel c + j from x
               const int h0 = p * g.sy - g.py, w0 = q * g.sx - g.px;
               float best = -INFINITY;
@@ -523,31 +541,96 @@ pool_backward_cl_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   }
 }
 
+// The hot case of the above with everything known at compile time: fp32, max pooling with the
+// argmax payload, square WIN x WIN window, stride S both ways (3x3 / 2 and 2x2 / 2), four
+// channels per thread.  An input pixel lies in at most ceil(WIN / S)^2 windows; their
+// candidates are enumerated without divisions or data-dependent loop bounds.
+template <int WIN, int S>
+__global__ void __launch_bounds__(256)
+pool_backward_max_cl_fixed_kernel(const float* __restrict__ dy, const uint8_t* __restrict__ argmax,
+                                  float* __restrict__ dx, PoolGeo g, int C, int cv_shift,
+                                  int per_image) {
+  constexpr int NW = (WIN + S - 1) / S;  // windows per axis that can cover a pixel
+  const long long n = blockIdx.y;
+  const unsigned cv = (unsigned)C >> 2;
+  for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < (unsigned)per_image;
+       t += gridDim.x * blockDim.x) {
+    const unsigned pix = cv_shift >= 0 ? t >> cv_shift : t / cv;
+    const int c = (int)(t - pix * cv) * 4;
+    const int h = (int)(pix / (unsigned)g.W);
+    const int w = (int)(pix - (unsigned)h * (unsigned)g.W);
+    const int hp = h + g.py, wp = w + g.px;
+    const int p1 = hp / S, q1 = wp / S;  // S is a compile-time constant: shifts
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int a = 0; a < NW; ++a) {
+      const int p = p1 - a, ky = hp - p * S;
+      if (p < 0 || p >= g.Ho || ky >= WIN) continue;
+#pragma unroll
+      for (int b = 0; b < NW; ++b) {
+        const int q = q1 - b, kx = wp - q * S;
+        if (q < 0 || q >= g.Wo || kx >= WIN) continue;
+        const long long o = ((n * g.Ho + p) * g.Wo + q) * (long long)C + c;
+        const uint32_t sel = *reinterpret_cast<const uint32_t*>(argmax + o);
+        const float4 gv = *reinterpret_cast<const float4*>(dy + o);
+        const uint32_t mine = (uint32_t)(ky * WIN + kx);
+        if ((sel & 0xffu) == mine) acc.x += gv.x;
+        if (((sel >> 8) & 0xffu) == mine) acc.y += gv.y;
+        if (((sel >> 16) & 0xffu) == mine) acc.z += gv.z;
+        if ((sel >> 24) == mine) acc.w += gv.w;
+      }
+    }
+    *reinterpret_cast<float4*>(dx + ((n * g.H + h) * g.W + w) * (long long)C + c) = acc;
+  }
+}
+
 template <typename T>
 int launch_pool_cl(bool backward, const PoolGeo& g, int C, int N, const void* a, const void* x,
                    const uint8_t* argmax_in, uint8_t* argmax_out, void* out, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
-  const long long pixels = (long long)N * (backward ? (long long)g.H * g.W : (long long)g.Ho * g.Wo);
-  const bool vec = C % V == 0 && aligned16(a) && aligned16(out) && (!x || aligned16(x));
-  const long long total = pixels * (vec ? C / V : C);
-  const int grid = grid_for(total, 256);
+  const long long pixels = backward ? (long long)g.H * g.W : (long long)g.Ho * g.Wo;
+  const bool vec = C % V == 0 && aligned16(a) && aligned16(out) && (!x || aligned16(x)) &&
+                   (reinterpret_cast<uintptr_t>(argmax_in) & (V - 1)) == 0 &&
+                   (reinterpret_cast<uintptr_t>(argmax_out) & (V - 1)) == 0;
+  const long long per_image = pixels * (vec ? C / V : C);
+  FLB200_REQUIRE(per_image < 0x7fffffffLL && N <= 65535, "pool2d: image too large");
+  long long bx = (per_image + 255) / 256;
+  if (bx > 4096) bx = 4096;
+  const dim3 grid((unsigned)bx, (unsigned)N);
+  const int pi = (int)per_image;
   if (!backward) {
     if (vec)
       pool_forward_cl_kernel<T, V><<<grid, 256, 0, st>>>(static_cast<const T*>(a),
-                                                         static_cast<T*>(out), argmax_out, g, C, total);
+                                                         static_cast<T*>(out), argmax_out, g, C, pi);
     else
       pool_forward_cl_kernel<T, 1><<<grid, 256, 0, st>>>(static_cast<const T*>(a),
-                                                         static_cast<T*>(out), argmax_out, g, C, total);
+                                                         static_cast<T*>(out), argmax_out, g, C, pi);
     FLB200_AFTER_LAUNCH("pool2d_forward_channels_last");
   } else {
+    if constexpr (std::is_same<T, float>::value) {
+      if (vec && g.mode == FLB200_POOL_MAX && argmax_in && g.wx == g.wy && g.sx == g.sy &&
+          g.sx == 2 && (g.wx == 3 || g.wx == 2)) {
+        const unsigned cvv = (unsigned)C / 4;
+        int shift = -1;
+        if ((cvv & (cvv - 1)) == 0) { shift = 0; while ((1u << shift) < cvv) ++shift; }
+        if (g.wx == 3)
+          pool_backward_max_cl_fixed_kernel<3, 2><<<grid, 256, 0, st>>>(
+              static_cast<const float*>(a), argmax_in, static_cast<float*>(out), g, C, shift, pi);
+        else
+          pool_backward_max_cl_fixed_kernel<2, 2><<<grid, 256, 0, st>>>(
+              static_cast<const float*>(a), argmax_in, static_cast<float*>(out), g, C, shift, pi);
+        FLB200_AFTER_LAUNCH("pool2d_backward_max_channels_last");
+        return FLB200_OK;
+      }
+    }
     if (vec)
       pool_backward_cl_kernel<T, V><<<grid, 256, 0, st>>>(
           static_cast<const T*>(a), static_cast<const T*>(x), argmax_in, static_cast<T*>(out), g, C,
-          total);
+          pi);
     else
       pool_backward_cl_kernel<T, 1><<<grid, 256, 0, st>>>(
           static_cast<const T*>(a), static_cast<const T*>(x), argmax_in, static_cast<T*>(out), g, C,
-          total);
+          pi);
     FLB200_AFTER_LAUNCH("pool2d_backward_channels_last");
   }
   return FLB200_OK;
