@@ -43,6 +43,16 @@ def measured_peaks():
             "source": "fallback"}
 
 
+def cpu_model() -> str:
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 # ------------------------------------------------------------------ CPU arm
 def cpu_sample(batch: int, steps: int, warmup: int, budget_s: float, seed: int = 1234):
     """Times the CPU stand-in on `batch` images per step; stops early once budget_s is spent."""
@@ -65,7 +75,7 @@ def cpu_sample(batch: int, steps: int, warmup: int, budget_s: float, seed: int =
             break
     dt = time.perf_counter() - t0
     return {"value": batch * done / dt, "unit": UNIT, "cores": torch.get_num_threads(),
-            "kind": "port",
+            "cpu_model": cpu_model(), "kind": "port",
             "sample": f"{done} steps of {batch} images (torch-CPU oneDNN stand-in, fp32), "
                       f"{dt:.1f} s"}, dt / done * 1e3, done
 
@@ -113,6 +123,8 @@ def run_reference_arm(args) -> None:
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch_per_step": batch,
+                   "stand_in": True, "stand_in_backend": "torch-cpu (oneDNN + MKL)",
+                   "reference_buildable": False, "sample_scaled_from_batch": 256,
                    "note": "the reference's oneDNN CPU backend cannot be built in this image; "
                            "this arm times the torch-CPU stand-in (same oneDNN generation) on a "
                            "bounded sample of the workload"},
@@ -271,6 +283,170 @@ def install_timers(timer: OpTimer, ext, F):
         lambda out, x, w, gy, *a, **k: (4.0 * gy.numel() * w.shape[0], _numel_bytes(x, w, gy) * 2))
 
 
+
+# ------------------------------------------------- reported-only side legs (N = 1)
+def vendor_library_leg(torch, batch, steps=5, warmup=3):
+    """The same ResNet-50 step through the vendor libraries (torch-CUDA: cuDNN / cuBLAS with
+    TF32 allowed, channels-last tensors, cudnn.benchmark on) on the same GPU, for orientation
+    only: none of this library's code runs here and nothing of it feeds `value`."""
+    from oracle import cpu_workloads
+    prev = (torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32,
+            torch.backends.cudnn.benchmark)
+    torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cudnn.benchmark = True
+    try:
+        g = torch.Generator().manual_seed(1234)
+        params = [p.cuda() for p in _resnet50_params_cpu(g)]
+        params = [p.contiguous(memory_format=torch.channels_last) if p.dim() == 4 else p
+                  for p in params]
+        x = torch.randn(batch, 3, 224, 224, generator=g).cuda().contiguous(
+            memory_format=torch.channels_last)
+        t = torch.randint(0, 1000, (batch,), generator=g).cuda()
+        for _ in range(warmup):
+            cpu_workloads.resnet50_step(params, x, t)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            cpu_workloads.resnet50_step(params, x, t)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        return {"what": "torch-CUDA (cuDNN, TF32 allowed, channels_last, cudnn.benchmark) "
+                        "forward + backward of the same network, reported only",
+                "ms_per_step": ms, "value": batch / ms * 1e3, "unit": UNIT,
+                "torch": torch.__version__, "cudnn": torch.backends.cudnn.version()}
+    except Exception as exc:  # the side leg must never take the bench line down
+        return {"error": f"{type(exc).__name__}: {exc}"[:200]}
+    finally:
+        (torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32,
+         torch.backends.cudnn.benchmark) = prev
+        torch.cuda.empty_cache()
+
+
+def _timed_steps(torch, step, warmup, steps):
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _cpu_timed(fn, budget_s, max_steps=5):
+    fn()  # warm-up
+    done, t0 = 0, time.perf_counter()
+    while done < max_steps:
+        fn()
+        done += 1
+        if time.perf_counter() - t0 > budget_s:
+            break
+    return (time.perf_counter() - t0) / done, done
+
+
+def other_workloads_leg(torch, peaks, steps=5, warmup=3, cpu_budget_s=5.0):
+    """The four other synthetic configurations at their full sizes (forward + backward step,
+    3 warm-up + 5 timed steps each), each with the whole-step contraction rate against the
+    tensor peak of its arithmetic mode and a bounded CPU stand-in sample (torch-CPU on a
+    reduced slice of the same workload, scaled linearly and labelled so)."""
+    from flashlight_b200 import _lib as L
+    from flashlight_b200 import autograd as A
+    from flashlight_b200 import workloads
+    from oracle import cpu_workloads as CW
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(1234)
+    out = {}
+    tf32_peak, bf16_peak = peaks["bf16_tflops_sustained"] / 2, peaks["bf16_tflops_sustained"]
+
+    def run(name, model, x, t, units, unit, flops, peak, dtype, cpu_fn, cpu_units, cpu_note):
+        xd, td = x.cuda(), t.cuda()
+
+        def step():
+            model.zeroGrad()
+            loss = model.loss(xd, td)
+            loss.backward()
+            return loss
+
+        try:
+            ms = _timed_steps(torch, step, warmup, steps)
+            achieved = flops / (ms * 1e-3) / 1e12
+            entry = {"ms_per_step": ms, "value": units / (ms * 1e-3), "unit": unit, "dtype": dtype,
+                     "steps": steps, "warmup": warmup, "loss": float(step().tensor.float().cpu()),
+                     "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak,
+                                  "unit": "TFLOP/s", "frac": achieved / peak,
+                                  "kernel": "tcgen05 contraction kernels, whole step "
+                                            "(2*M*N*K of every contraction / step time)",
+                                  "peak_source": f"{peaks['source']} bf16 sustained" +
+                                                 ("" if dtype == "bf16" else " / 2 (tf32 rate)")}}
+        except Exception as exc:
+            out[name] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+            return
+        try:
+            sec, done = _cpu_timed(cpu_fn, cpu_budget_s)
+            entry["cpu_baseline"] = {"value": cpu_units / sec, "unit": unit,
+                                     "cores": torch.get_num_threads(), "cpu_model": cpu_model(),
+                                     "kind": "port", "sample": f"{done} steps, {cpu_note}"}
+        except Exception as exc:
+            entry["cpu_baseline"] = {"error": f"{type(exc).__name__}: {exc}"[:200]}
+        out[name] = entry
+        del xd, td
+        torch.cuda.empty_cache()
+
+    def host(model):
+        return [p.tensor.detach().float().cpu() for p in model.parameters()]
+
+    # C1: README MNIST convnet, batch 64, fp32 operands on the tensor cores (TF32)
+    A.set_math_mode(L.MATH_TF32)
+    m = workloads.mnist_convnet()
+    x, t = torch.randn(64, 1, 28, 28, generator=g), torch.randint(0, 10, (64,), generator=g, dtype=torch.int32)
+    mask = (torch.rand(64, 1024, generator=g) > 0.5).float()
+    ps = host(m)
+    run("mnist_convnet_b64", m, x, t, 64, "images/s", 3 * 1.78e9, tf32_peak, "tf32",
+        lambda: CW.mnist_convnet_step(ps, x, t, mask), 64, "full size (batch 64), torch-CPU fp32")
+    # C3: conv-ASR 12 x 1024 channels, T = 1000, batch 16
+    m = workloads.ConvAsr()
+    B, T = 16, 1000
+    x = torch.randn(B, 80, 1, T, generator=g)
+    t = torch.randint(0, 30, (B * T,), generator=g, dtype=torch.int32)
+    ps = host(m)
+    xs, ts = x[:1, :, :, :250].contiguous(), t[:250].contiguous()
+    run("conv_asr_b16_t1000", m, x, t, B * T, "frames/s", 3 * 4833e9, tf32_peak, "tf32",
+        lambda: CW.conv_asr_step(ps, xs, ts), 250,
+        "1 sequence of 250 frames (1/64 of the step), torch-CPU fp32, frames/s of the sample")
+    # C4: 3-layer bidirectional LSTM, H = 1024, T = 500, batch 32
+    m = workloads.BiLstm()
+    T, B = 500, 32
+    x, tgt = torch.randn(T, B, 80, generator=g), torch.randn(T, B, 2048, generator=g)
+    lstm = torch.nn.LSTM(80, 1024, 3, bidirectional=True)
+    xs, tgs = x[:25], tgt[:25]
+
+    def lstm_cpu():
+        lstm.zero_grad()
+        y, _ = lstm(xs)
+        ((y - tgs) ** 2).mean().backward()
+
+    run("bilstm_h1024_t500_b32", m, x, tgt, B, "sequences/s", 3 * 1900e9, tf32_peak, "tf32", lstm_cpu,
+        32 * 25 / 500.0,
+        "25 of 500 time steps at batch 32, torch.nn.LSTM on the CPU: a restatement, not the "
+        "reference (its oneDNN backend has no rnnBackward), scaled to whole sequences")
+    # C5: Transformer LM 12 x 768, T = 512, batch 8, bf16 compute with fp32 master weights
+    m = workloads.TransformerLM(compute_dtype=torch.bfloat16)
+    B, T = 8, 512
+    ids = torch.randint(0, 32000, (B, T), generator=g)
+    t = torch.randint(0, 32000, (B * T,), generator=g, dtype=torch.int32)
+    ps = host(m)
+    ids1, t1 = ids[:1].contiguous(), t[:T].contiguous()
+    run("transformer_lm_12x768_t512_b8_bf16", m, ids, t, B * T, "tokens/s", 3 * 974e9, bf16_peak,
+        "bf16", lambda: CW.transformer_lm_step(ps, ids1, t1, heads=12, layers=12), T,
+        "1 of 8 sequences (512 tokens), torch-CPU fp32, tokens/s of the sample")
+    return out
+
+
 TENSOR_OPS = {"conv2d", "conv2dBackwardData", "conv2dBackwardFilterBias", "linear", "linear_backward"}
 CONV_OPS = ("conv2d", "conv2dBackwardData", "conv2dBackwardFilterBias")
 CONV_KERNEL = "tc_persistent_kernel (conv2d + conv2dBackwardData + conv2dBackwardFilterBias)"
@@ -358,7 +534,7 @@ def run_gpu_arm(args) -> None:
     # ---- the same step captured once as a CUDA graph and replayed: no per-operator events, no
     # host work between kernels.  `value` is timed on the replays when capture works; the
     # eager pass above stays the source of the per-operator and roofline figures.
-    graph, graph_loss, graph_note = None, None, "disabled"
+    graph, graph_loss, graph_note, graph_error = None, None, "disabled", None
     if args.graph:
         try:
             static_x, static_t = x_dev.clone(), t_dev.clone()
@@ -383,7 +559,8 @@ def run_gpu_arm(args) -> None:
             ms_total = g0.elapsed_time(g1)
             graph_note = "value and e2e are timed on replays of the step captured as one CUDA graph"
         except Exception as exc:  # capture refused: keep the eager timing
-            graph, graph_note = None, f"graph capture failed, eager timing kept: {exc}"
+            graph, graph_note = None, "graph capture failed, eager timing kept"
+            graph_error = f"{type(exc).__name__}: {exc}"[:300]
             ms_total = ms_eager
             torch.cuda.synchronize()
     clocks = sampler.stop() if rank == 0 else None
@@ -460,7 +637,8 @@ def run_gpu_arm(args) -> None:
             peak = peaks["bf16_tflops_sustained"] / 2
             src = f"{peaks['source']} bf16 sustained / 2 (tf32 rate)"
             traffic = None
-            if top == CONV_KERNEL and B == 256:
+            # (the capture was taken with fl-order activations; not re-used for channels-last)
+            if top == CONV_KERNEL and B == 256 and not workloads.CHANNELS_LAST:
                 traffic = CONV_DRAM_BYTES_PER_STEP_B256 * args.steps / max(tv["calls"], 1)
         else:
             peak = FP32_FMA_TFLOPS
@@ -489,9 +667,20 @@ def run_gpu_arm(args) -> None:
                      "tflops": v["flops"] / (v["ms"] * 1e-3) / 1e12 if v["flops"] else None,
                      "gbs": v["bytes"] / (v["ms"] * 1e-3) / 1e9}
 
-    cpu_base = None
+    cpu_base = vendor = others = None
+    graph_captured = graph is not None
     if world == 1 and not args.no_cpu_baseline:
         cpu_base, _, _ = cpu_sample(args.cpu_batch, 12, 1, budget_s=25.0)
+    if world == 1 and not args.no_side_legs:
+        # free the step's tensors first: the side legs build their own models
+        del model, graph, timer, bufs
+        torch.cuda.empty_cache()
+        vendor = vendor_library_leg(torch, B)
+        others = other_workloads_leg(torch, peaks)
+        A.set_math_mode(math_mode)
+    # the loss of this very step (seed 1234, rank 0's batch, initial weights) is a fixed
+    # number: 7.0982 in every arithmetic mode to the bound below
+    loss_expected = 7.0982 if (B == 256 and world == 1) else None
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -505,15 +694,24 @@ def run_gpu_arm(args) -> None:
                    "step": "zeroGrad + forward + loss + backward" +
                            (" + bucketed NCCL all-reduce" if world > 1 else ""),
                    "timed_region": graph_note,
+                   "host_layer": "Python mirror of fl::AutogradExtension over the C ABI "
+                                 "(flashlight_b200/extension.py); the C++ class runs the same "
+                                 "entry points behind fl::Tensor in tests/test_fl_harness_gpu.py",
+                   "activation_layout": "channels_last" if workloads.CHANNELS_LAST else "fl order (NCHW)",
                    "gpu_launches_counted": "kernel launches of the eager pass of the same K steps "
                                            "(a replay runs the same kernels as graph nodes)"},
         "value_eager": images / (ms_eager * 1e-3), "ms_per_step_eager": ms_eager / args.steps,
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": int(x_host.numel() * 4 + t_host.numel() * 4),
                 "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
+        "graph_captured": graph_captured, "graph_error": graph_error,
         "gpu_launches": int(launches),
         "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base, "per_op": per_op,
         "loss": last,
+        "loss_check": None if loss_expected is None else {
+            "expected": loss_expected, "tolerance": 2e-3,
+            "ok": abs(last - loss_expected) <= 2e-3 * loss_expected},
+        "vendor_library": vendor, "workloads": others,
     }
     print(json.dumps(line), flush=True)
 
@@ -529,6 +727,8 @@ def main() -> None:
     ap.add_argument("--bucket-mb", type=int, default=32)
     ap.add_argument("--cpu-batch", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-side-legs", action="store_true",
+                    help="skip the reported-only legs (vendor-library step, the other four workloads)")
     ap.add_argument("--no-graph", dest="graph", action="store_false",
                     help="time the eager step only (default: also capture it as a CUDA graph)")
     args = ap.parse_args()
