@@ -83,6 +83,10 @@ SIGNATURES = {
     "flb200_pool2d_output_dims": (C.c_int, [P(Pool2dDesc), P(i32), P(i32)]),
     "flb200_pool2d_forward": (C.c_int, [P(Pool2dDesc), vp, vp, vp, vp]),
     "flb200_pool2d_backward": (C.c_int, [P(Pool2dDesc), vp, vp, vp, vp, vp]),
+    "flb200_layernorm_affine_forward": (C.c_int, [vp, vp, vp, vp, i64, i64, C.c_int, vp]),
+    "flb200_layernorm_affine_workspace_bytes": (sz, [i64, i64]),
+    "flb200_layernorm_affine_backward": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, C.c_int, vp,
+                                                   sz, vp]),
     "flb200_batchnorm_geometry": (C.c_int, [P(i64), C.c_int, P(i32), C.c_int, P(BatchnormDesc)]),
     "flb200_batchnorm_workspace_bytes": (sz, [P(BatchnormDesc)]),
     "flb200_batchnorm_forward": (C.c_int, [P(BatchnormDesc), vp, vp, vp, vp, vp, vp, vp, C.c_int,

@@ -528,19 +528,21 @@ def softmax_rows(x: Variable, scale: float = 1.0, causal_period: int = 0) -> Var
 
 def affine_rows(x: Variable, w: Variable, b: Variable) -> Variable:
     """y = x * tile(w) + tile(b) over rows of features: the affine part of fl::LayerNorm
-    (flashlight/fl/nn/modules/LayerNorm.cpp:99-110).  The products are torch glue; the two
-    parameter gradients are channel sums over the rows (channel_sum kernel)."""
-    xt, wt = x.tensor, w.tensor
-    y = torch.addcmul(b.tensor, xt, wt)
+    (flashlight/fl/nn/modules/LayerNorm.cpp:99-128) as one kernel forward and two backward
+    (parameter gradients from one pass over dy and x, then dx = dy * w).  w and b are the fp32
+    parameters themselves, whatever the activations' dtype."""
+    xt, wt, bt = x.tensor, w.tensor, b.tensor
+    y = F.layernorm_affine(xt, wt, bt)
 
     def grad_func(inputs, gy):
-        rows, feat = gy.numel() // gy.shape[-1], gy.shape[-1]
+        need_p = inputs[1].isCalcGrad() or inputs[2].isCalcGrad()
+        gx, gw, gb = F.layernorm_affine_backward(gy, xt, wt, inputs[0].isCalcGrad(), need_p)
         if inputs[0].isCalcGrad():
-            inputs[0].addGrad(gy * wt)
+            inputs[0].addGrad(gx.reshape(xt.shape))
         if inputs[1].isCalcGrad():
-            inputs[1].addGrad(F.channel_sum((gy * xt).contiguous(), rows, feat, 1).reshape(wt.shape))
+            inputs[1].addGrad(gw.reshape(wt.shape))
         if inputs[2].isCalcGrad():
-            inputs[2].addGrad(F.channel_sum(gy.contiguous(), rows, feat, 1).reshape(wt.shape))
+            inputs[2].addGrad(gb.reshape(bt.shape))
 
     return Variable(y, False, [x, w, b], grad_func)
 

@@ -380,6 +380,30 @@ bn_tail_backward_reduce_cl_kernel(const float* __restrict__ x, const float* __re
   }
 }
 
+// Affine part of fl::LayerNorm over rows of features: y = xhat * gamma + beta, and its gradient
+// chain dgamma = sum_rows dy * xhat, dbeta = sum_rows dy, dxhat = dy * gamma.
+struct AffineFwdF {
+  const float* weight;
+  const float* bias;
+  struct K { float w, b; };
+  __device__ K channel(long long c) const { return K{weight[c], bias ? bias[c] : 0.f}; }
+  __device__ float apply(const K& k, float a, float) const { return __fmaf_rn(a, k.w, k.b); }
+};
+struct AffineBwdReduceF {  // a = dy, b = xhat
+  struct K {};
+  __device__ K channel(long long) const { return K{}; }
+  __device__ void accumulate(const K&, float a, float b, float& s0, float& s1) const {
+    s0 += a;
+    s1 += a * b;
+  }
+};
+struct ScaleF {  // a = dy
+  const float* weight;
+  struct K { float w; };
+  __device__ K channel(long long c) const { return K{weight[c]}; }
+  __device__ float apply(const K& k, float a, float) const { return a * k.w; }
+};
+
 struct BiasAddF {
   const float* bias;
   struct K { float b; };
@@ -449,6 +473,16 @@ __global__ void bn_stats_finalize_kernel(const float2* __restrict__ partial, int
     const double unbiased = count > 1.0 ? var * count / (count - 1.0) : var;
     running_var[c] = (float)((1.0 - momentum) * running_var[c] + momentum * unbiased);
   }
+}
+
+__global__ void affine_bwd_finalize_kernel(const float2* __restrict__ partial, int splits,
+                                           long long channels, float* __restrict__ grad_weight,
+                                           float* __restrict__ grad_bias) {
+  long long c;
+  double s0, s1;
+  if (!fin_sums(partial, splits, channels, &c, &s0, &s1)) return;
+  if (grad_bias) grad_bias[c] = (float)s0;
+  if (grad_weight) grad_weight[c] = (float)s1;
 }
 
 __global__ void bn_infer_prepare_kernel(long long channels, const float* __restrict__ weight,
@@ -667,6 +701,57 @@ int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t o
   FLB200_DISPATCH_DTYPE(dtype, "channel_bias_add",
                         rc = (launch_apply<T, 1>("channel_bias_add", x, nullptr, y, outer, channels,
                                                  inner, BiasAddF{bias}, as_stream(stream))));
+  return rc;
+}
+
+size_t flb200_layernorm_affine_workspace_bytes(int64_t rows, int64_t features) {
+  if (rows < 1 || features < 1) return 0;
+  return channel_partial_bytes(rows, features, 1);
+}
+
+int flb200_layernorm_affine_forward(const void* xhat, const float* weight, const float* bias,
+                                    void* y, int64_t rows, int64_t features, int dtype,
+                                    void* stream) {
+  if (int st = check_geo("layernorm_affine_forward", rows, features, 1)) return st;
+  FLB200_REQUIRE(xhat && weight && y, "layernorm_affine_forward: null pointer");
+  int rc = FLB200_OK;
+  FLB200_DISPATCH_DTYPE(dtype, "layernorm_affine_forward",
+                        rc = (launch_apply<T, 1>("layernorm_affine_forward", xhat, nullptr, y, rows,
+                                                 features, 1, AffineFwdF{weight, bias},
+                                                 as_stream(stream))));
+  return rc;
+}
+
+int flb200_layernorm_affine_backward(const void* grad_y, const void* xhat, const float* weight,
+                                     void* grad_xhat, float* grad_weight, float* grad_bias,
+                                     int64_t rows, int64_t features, int dtype, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  if (int st = check_geo("layernorm_affine_backward", rows, features, 1)) return st;
+  FLB200_REQUIRE(grad_y && xhat && weight, "layernorm_affine_backward: null pointer");
+  cudaStream_t st = as_stream(stream);
+  int rc = FLB200_OK;
+  if (grad_weight || grad_bias) {
+    const size_t need = channel_partial_bytes(rows, features, 1);
+    if (!workspace || workspace_bytes < need)
+      return fail(FLB200_WORKSPACE_TOO_SMALL, "layernorm_affine_backward: workspace %zu < %zu",
+                  workspace_bytes, need);
+    float2* partial = static_cast<float2*>(workspace);
+    int splits = 0;
+    FLB200_DISPATCH_DTYPE(dtype, "layernorm_affine_backward",
+                          rc = (launch_reduce<T, 2>("layernorm_affine_backward_reduce", grad_y, xhat,
+                                                    partial, rows, features, 1, AffineBwdReduceF{},
+                                                    &splits, st)));
+    if (rc) return rc;
+    affine_bwd_finalize_kernel<<<fin_grid(features), kFinThreads, 0, st>>>(
+        partial, splits, features, grad_weight, grad_bias);
+    FLB200_AFTER_LAUNCH("layernorm_affine_backward_finalize");
+  }
+  if (grad_xhat) {
+    FLB200_DISPATCH_DTYPE(dtype, "layernorm_affine_backward",
+                          rc = (launch_apply<T, 1>("layernorm_affine_backward_apply", grad_y, nullptr,
+                                                   grad_xhat, rows, features, 1, ScaleF{weight},
+                                                   st)));
+  }
   return rc;
 }
 

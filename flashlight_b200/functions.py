@@ -139,6 +139,36 @@ def channel_bias_add(x, bias, outer: int, channels: int, inner: int, out=None):
     return out
 
 
+def layernorm_affine(xhat, weight, bias):
+    """y = xhat * weight + bias over rows of features (the affine part of fl::LayerNorm);
+    weight / bias are fp32 parameter vectors of the last dimension's length."""
+    feat = xhat.shape[-1]
+    xh = xhat.contiguous()
+    y = torch.empty_like(xh)
+    L.check(L.lib.flb200_layernorm_affine_forward(ptr(xh), ptr(weight), ptr(bias), ptr(y),
+                                                  xh.numel() // feat, feat, dtype_code(xh),
+                                                  stream_handle()))
+    return y
+
+
+def layernorm_affine_backward(grad_y, xhat, weight, need_input_grad=True, need_param_grads=True):
+    """Returns (grad_xhat, grad_weight, grad_bias); the parameter gradients are fp32."""
+    feat = xhat.shape[-1]
+    rows = xhat.numel() // feat
+    gy, xh = grad_y.contiguous(), xhat.contiguous()
+    gx = torch.empty_like(xh) if need_input_grad else None
+    gw = gb = None
+    if need_param_grads:
+        gw = torch.empty(feat, dtype=torch.float32, device=xh.device)
+        gb = torch.empty(feat, dtype=torch.float32, device=xh.device)
+    nbytes = L.lib.flb200_layernorm_affine_workspace_bytes(rows, feat)
+    ws = workspace(nbytes, xh)
+    L.check(L.lib.flb200_layernorm_affine_backward(ptr(gy), ptr(xh), ptr(weight), ptr(gx), ptr(gw),
+                                                   ptr(gb), rows, feat, dtype_code(xh), ptr(ws),
+                                                   nbytes, stream_handle()))
+    return gx, gw, gb
+
+
 # ------------------------------------------------------------------ linear
 def _linear_dims(weight, x):
     I = x.shape[-1]

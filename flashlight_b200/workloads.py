@@ -231,7 +231,7 @@ class TransformerLM(nn.Module):
     projections, vocabulary projection and all their gradients), LayerNorm statistics, GELU,
     logSoftmax, the loss, the residual adds and the embedding lookup with its scatter-add
     gradient and the scaled causal softmax run on this library's kernels; head split / merge
-    permutations and the LayerNorm affine products are torch glue (autograd.glue and friends)."""
+    permutations are torch data movement (autograd.glue); nothing arithmetic is left to torch."""
 
     def __init__(self, vocab=32000, d=768, heads=12, ffn=3072, layers=12, seed=1234, device="cuda",
                  compute_dtype=torch.float32):
@@ -271,8 +271,7 @@ class TransformerLM(nn.Module):
         return out + list(self.ln_f) + self.head.parameters()
 
     def _ln(self, x, wb):
-        dt = self.compute_dtype
-        return A.affine_rows(self.norm(x), A.cast(wb[0], dt), A.cast(wb[1], dt))
+        return A.affine_rows(self.norm(x), wb[0], wb[1])
 
     def _lin(self, mod, x):
         w = A.cast(mod.params[0], self.compute_dtype)
@@ -284,12 +283,13 @@ class TransformerLM(nn.Module):
         qkv = self._lin(blk["qkv"], x)  # (B*T, 3d)
 
         def split(i, scale):
-            fwd = lambda t: (t.reshape(B, T, 3, h, hd)[:, :, i].permute(0, 2, 1, 3) * scale) \
+            # pure data movement: pick q, k or v and bring the head index forward
+            fwd = lambda t: t.reshape(B, T, 3, h, hd)[:, :, i].permute(0, 2, 1, 3) \
                 .reshape(B * h, T, hd).contiguous()
 
             def bwd(g):
                 full = torch.zeros(B, T, 3, h, hd, device=g.device, dtype=g.dtype)
-                full[:, :, i] = (g.reshape(B, h, T, hd) * scale).permute(0, 2, 1, 3)
+                full[:, :, i] = g.reshape(B, h, T, hd).permute(0, 2, 1, 3)
                 return full.reshape(B * T, 3 * d)
 
             return A.glue(qkv, fwd, bwd)

@@ -332,6 +332,23 @@ int flb200_channel_sum(const void* in, float* out, int64_t outer, int64_t channe
 int flb200_channel_sum_static_scratch(const void* in, float* out, int64_t outer,
                                       int64_t channels, int64_t inner, int dtype, void* stream);
 
+/* The affine part of fl::LayerNorm (flashlight/fl/nn/modules/LayerNorm.cpp:112-128: the
+ * normalised tensor times tileAs(weight) plus tileAs(bias)) on rows of `features` contiguous
+ * elements, as one kernel:  y[r][f] = xhat[r][f] * weight[f] + bias[f]  (bias may be NULL).
+ * weight / bias are fp32 whatever the activations' dtype (fp32 master parameters are used as
+ * they are).  In place allowed. */
+int flb200_layernorm_affine_forward(const void* xhat, const float* weight, const float* bias,
+                                    void* y, int64_t rows, int64_t features, int dtype,
+                                    void* stream);
+/* Its gradient chain (the tileAs / sumAs products of Functions.cpp:27-58, 537-566) in two
+ * kernels: grad_weight[f] = sum_r grad_y * xhat and grad_bias[f] = sum_r grad_y from one pass
+ * over both tensors (fp32, either may be NULL), grad_xhat = grad_y * weight (may be NULL). */
+size_t flb200_layernorm_affine_workspace_bytes(int64_t rows, int64_t features);
+int flb200_layernorm_affine_backward(const void* grad_y, const void* xhat, const float* weight,
+                                     void* grad_xhat, float* grad_weight, float* grad_bias,
+                                     int64_t rows, int64_t features, int dtype, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+
 /* y[o][c][i] = x[o][c][i] + bias[c] (tile + add, Functions.cpp:1270-1275). In place allowed. */
 int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t outer,
                             int64_t channels, int64_t inner, int dtype, void* stream);

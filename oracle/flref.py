@@ -235,6 +235,33 @@ def linear_backward(x, weight, gy, has_bias):
     return gx, gw, gb
 
 
+def embedding(table, ids):
+    """flashlight/fl/autograd/Functions.cpp:1707-1749: column ids[r] of the fl table [dim, vocab]
+    = row ids[r] of the torch view (vocab, dim)."""
+    return table[ids.reshape(-1).long()]
+
+
+def embedding_backward(grad_out, ids, vocab):
+    g = torch.zeros(vocab, grad_out.shape[-1], dtype=grad_out.dtype)
+    g.index_add_(0, ids.reshape(-1).long(), grad_out.reshape(-1, grad_out.shape[-1]))
+    return g
+
+
+def layer_norm(x, fl_axes, eps, weight=None, bias=None):
+    """fl::LayerNorm (flashlight/fl/nn/modules/LayerNorm.cpp:60-131): batchnorm over the
+    complement of the normalised fl axes with momentum 0 (statistics per position of the
+    complement axes, biased variance), then the optional affine over the normalised axes.
+    x is the torch view (reversed fl shape)."""
+    nd = x.dim()
+    comp = [a for a in range(nd) if a not in fl_axes]
+    y = batchnorm(x, None, None, None, None, comp, True, 0.0, eps)[0] if comp else None
+    if y is None:  # every axis normalised: one statistic for the whole tensor
+        y = (x - x.mean()) / torch.sqrt(x.var(unbiased=False) + eps)
+    if weight is not None:
+        y = y * weight + (bias if bias is not None else 0)
+    return y
+
+
 # --------------------------------------------------------- eltwise chains
 def relu(x):
     return torch.clamp_min(x, 0)  # fl::max(x, 0.0), Functions.cpp:1787-1789

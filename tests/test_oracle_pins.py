@@ -47,6 +47,83 @@ def test_rnn_forward_matches_reference_goldens(reference_root, test, mode):
     assert np.abs(got - c["vals"]).max() < 1e-4
 
 
+# ------------------------- reference goldens (Embedding, Linear, LogSoftmax, LayerNorm)
+def _literals(src: str, test: str):
+    """Every Tensor::fromVector<float>({shape}, {values}) literal of one TEST body, in order, as
+    fp64 tensors in torch order (reversed fl shape; the flat value order is the same bytes)."""
+    body = re.search(r"TEST\(ModuleTest, %s\)(.*?)\n}\n" % test, src, re.S).group(1)
+    out = []
+    for m in re.finditer(r"fromVector<float>\(\s*\{([^}]*)\},\s*\{([^}]*)\}\)", body, re.S):
+        names = dict(re.findall(r"(\w+) = (\d+)", body))
+        shape = [int(names.get(t.strip(), t.strip())) for t in m.group(1).split(",")]
+        vals = [float(v) for v in re.findall(r"-?\d+\.?\d*(?:[eE]-?\d+)?", m.group(2))]
+        out.append(torch.tensor(vals, dtype=torch.float64).reshape(list(reversed(shape))))
+    return out
+
+
+def _module_tests(reference_root):
+    return (reference_root / "flashlight/fl/test/nn/ModuleTest.cpp").read_text()
+
+
+def test_embedding_matches_reference_golden(reference_root):
+    """ModuleTest EmbeddingFwd: table [embDim, nEmb], ids [nQuery, batch] -> [embDim, nQuery, batch]."""
+    table, ids, want = _literals(_module_tests(reference_root), "EmbeddingFwd")[:3]
+    got = R.embedding(table, ids.to(torch.int64)).reshape(want.shape)
+    assert torch.equal(got, want)
+
+
+def test_linear_matches_reference_goldens(reference_root):
+    """ModuleTest LinearFwd: fl weight [n_out, n_in] (torch (n_in, n_out)), with and without bias."""
+    w, x, want, bias, want_b = _literals(_module_tests(reference_root), "LinearFwd")[:5]
+    assert torch.equal(R.linear(x, w, None), want)
+    assert torch.equal(R.linear(x, w, bias), want_b)
+
+
+def test_log_softmax_matches_reference_goldens(reference_root):
+    """ModuleTest LogSoftmaxFwd: over fl dim 0 (the oracle's own axis) and over fl dim 1 (the
+    same function on the transposed view); goldens carry 6 digits, the test uses allClose(1e-4)."""
+    x, want0, want1 = _literals(_module_tests(reference_root), "LogSoftmaxFwd")[:3]
+    assert (R.log_softmax(x) - want0).abs().max() < 1e-4
+    assert (R.log_softmax(x.t()).t() - want1).abs().max() < 1e-4
+
+
+def test_layer_norm_matches_reference_closed_form(reference_root):
+    """ModuleTest LayerNormFwd holds no literal output: it compares the module with
+    (x - mean) / sqrt(var_biased + eps) over the normalised axis.  Replayed on the oracle with the
+    reference's shapes, axis and eps (read from the test), for its three module variants."""
+    body = re.search(r"TEST\(ModuleTest, LayerNormFwd\)(.*?)\n}\n", _module_tests(reference_root), re.S).group(1)
+    eps = float(re.search(r"double eps = ([0-9.eE-]+);", body).group(1))
+    axis = int(re.search(r"feat_axes = \{(\d+)\}", body).group(1))
+    feat = int(re.search(r"int F = (\d+);", body).group(1))
+    shape = [int(v) for v in re.search(r"fl::rand\(\{([^}]*)\}\)", body).group(1).replace("F", str(feat)).split(",")]
+    assert (eps, axis, shape) == (1e-5, 3, [4, 4, 3, 10])
+    x = randn(*reversed(shape), seed=7, dtype=torch.float64)   # torch view of fl [4, 4, 3, F]
+    tdim = len(shape) - 1 - axis                               # fl axis 3 = torch dim 0
+    true_out = (x - x.mean(tdim, keepdim=True)) / torch.sqrt(x.var(tdim, unbiased=False, keepdim=True) + eps)
+    assert (R.layer_norm(x, [axis], eps) - true_out).abs().max() < eps
+    ones = torch.ones(feat, dtype=torch.float64).reshape(-1, 1, 1, 1)
+    zeros = torch.zeros(feat, dtype=torch.float64).reshape(-1, 1, 1, 1)
+    assert (R.layer_norm(x, [axis], eps, ones, zeros) - true_out).abs().max() < eps
+    x3 = randn(3, 4, 4, seed=8, dtype=torch.float64)           # fl [4, 4, 3], axes {0}
+    want3 = (x3 - x3.mean(-1, keepdim=True)) / torch.sqrt(x3.var(-1, unbiased=False, keepdim=True) + eps)
+    assert (R.layer_norm(x3, [0], eps) - want3).abs().max() < eps
+
+
+def test_conv_padding_shapes_of_reference_module_test(reference_root):
+    """ModuleTest ConvPadding pins SAME padding and the output-extent formula: the three output
+    shapes are read from the test and reproduced with derive_padding + conv_out_dim."""
+    from flashlight_b200.nn import SAME, derive_padding
+    body = re.search(r"TEST\(ModuleTest, ConvPadding\)(.*?)\n}\n", _module_tests(reference_root), re.S).group(1)
+    shapes = [[int(v) for v in m.split(",")] for m in re.findall(r"Shape\(\{([^}]*)\}\)", body)]
+    assert len(shapes) == 3
+    # Conv2D(30, 100, wx, wy, sx, sy, px, py, [dx, dy]) on a 32 x 32 x 30 x 2 input
+    cases = [(3, 5, 2, 1, SAME, 0, 1, 1), (3, 5, 2, 1, SAME, SAME, 1, 1), (10, 10, 1, 1, SAME, SAME, 4, 4)]
+    for (wx, wy, sx, sy, px, py, dx, dy), want in zip(cases, shapes):
+        pxx, pyy = derive_padding(32, wx, sx, px, dx), derive_padding(32, wy, sy, py, dy)
+        got = [R.conv_out_dim(32, wx, sx, pxx, dx), R.conv_out_dim(32, wy, sy, pyy, dy), 100, 2]
+        assert got == want, (got, want)
+
+
 def test_rnn_param_counts_of_reference_backward_test(reference_root):
     """AutogradRnnTest.cpp pins the flat weight size for 2 layers, H=2, in=2, bidirectional."""
     src = (reference_root / "flashlight/fl/test/autograd/AutogradRnnTest.cpp").read_text()

@@ -257,6 +257,29 @@ def test_batchnorm_errors(ext):
         ext.batchnormBackward(x, None, None, x, None, [2], False, 1e-5)
 
 
+@pytest.mark.parametrize("rows,feat", [(4096, 768), (37, 20), (5, 3), (2000, 1024)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, STRICT_TOL), (torch.bfloat16, 1.6e-2)])
+def test_layernorm_affine(fx, rows, feat, dtype, tol):
+    """The affine part of fl::LayerNorm (y = xhat * gamma + beta over rows of features) and its
+    gradient chain as kernels; fp32 parameters with fp32 or bf16 activations."""
+    xh = randn(rows, feat, seed=41, dtype=dtype)
+    w, b = randn(feat, seed=42) + 1.5, randn(feat, seed=43)
+    gy = randn(rows, feat, seed=44, dtype=dtype)
+    y = fx.layernorm_affine(xh.cuda(), w.cuda(), b.cuda())
+    assert y.dtype == dtype
+    assert_close(y, xh.double() * w.double() + b.double(), tol, "layernorm affine y")
+    gx, gw, gb = fx.layernorm_affine_backward(gy.cuda(), xh.cuda(), w.cuda())
+    assert gw.dtype == torch.float32 and gb.dtype == torch.float32
+    assert_close(gx, gy.double() * w.double(), tol, "layernorm affine dx")
+    assert_close(gw, (gy.double() * xh.double()).sum(0), STRICT_TOL, "layernorm affine dgamma")
+    assert_close(gb, gy.double().sum(0), STRICT_TOL, "layernorm affine dbeta")
+    # only the input gradient / only the parameter gradients
+    gx2, gw2, gb2 = fx.layernorm_affine_backward(gy.cuda(), xh.cuda(), w.cuda(), True, False)
+    assert gw2 is None and gb2 is None and torch.equal(gx2, gx)
+    gx3, gw3, _ = fx.layernorm_affine_backward(gy.cuda(), xh.cuda(), w.cuda(), False, True)
+    assert gx3 is None and torch.equal(gw3, gw)
+
+
 # ------------------------------------------------------------------- pool2d
 POOL_GEOS = [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1), (3, 2, 1, 2, 1, 0), (7, 7, 1, 1, 0, 0),
              (2, 2, 1, 1, 0, 0)]
