@@ -373,9 +373,28 @@ def other_workloads_leg(torch, peaks, steps=5, warmup=3, cpu_budget_s=5.0):
             return loss
 
         try:
-            ms = _timed_steps(torch, step, warmup, steps)
+            ms_eager = _timed_steps(torch, step, warmup, steps)
+            # the same step captured once as a CUDA graph and replayed (as the ResNet-50 line
+            # does): no host work between the kernels
+            ms, captured = ms_eager, False
+            try:
+                side = torch.cuda.Stream()
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    step()
+                torch.cuda.current_stream().wait_stream(side)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step()
+                ms = _timed_steps(torch, graph.replay, warmup, steps)
+                captured = True
+                del graph
+            except Exception:
+                torch.cuda.synchronize()
             achieved = flops / (ms * 1e-3) / 1e12
-            entry = {"ms_per_step": ms, "value": units / (ms * 1e-3), "unit": unit, "dtype": dtype,
+            entry = {"ms_per_step": ms, "ms_per_step_eager": ms_eager, "graph_captured": captured,
+                     "value": units / (ms * 1e-3), "unit": unit, "dtype": dtype,
                      "steps": steps, "warmup": warmup, "loss": float(step().tensor.float().cpu()),
                      "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak,
                                   "unit": "TFLOP/s", "frac": achieved / peak,

@@ -83,6 +83,8 @@ SIGNATURES = {
     "flb200_pool2d_output_dims": (C.c_int, [P(Pool2dDesc), P(i32), P(i32)]),
     "flb200_pool2d_forward": (C.c_int, [P(Pool2dDesc), vp, vp, vp, vp]),
     "flb200_pool2d_backward": (C.c_int, [P(Pool2dDesc), vp, vp, vp, vp, vp]),
+    "flb200_selftest_bounded_wait_workspace_bytes": (sz, []),
+    "flb200_selftest_bounded_wait": (C.c_int, [f64, vp, sz, vp]),
     "flb200_layernorm_affine_forward": (C.c_int, [vp, vp, vp, vp, i64, i64, C.c_int, vp]),
     "flb200_layernorm_affine_workspace_bytes": (sz, [i64, i64]),
     "flb200_layernorm_affine_backward": (C.c_int, [vp, vp, vp, vp, vp, vp, i64, i64, C.c_int, vp,

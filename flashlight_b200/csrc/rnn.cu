@@ -16,6 +16,8 @@
 // time steps for dW_ih, dW_hh and the gradient of the layer input.
 // The reserve space (forward -> backward payload) holds the activated gates,
 // cell states, GRU candidates' recurrent part and the outputs of inner layers.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "rnn_step.cuh"
 
@@ -215,13 +217,14 @@ __global__ void copy_rows_kernel(const float* __restrict__ src, long long src_st
   dst[(long long)b * dst_stride + j] = src ? src[(long long)b * src_stride + j] : 0.f;
 }
 
-struct FwdWs { size_t zero, gh, bias, mm, total; };
+struct FwdWs { size_t zero, gh, bias, sync, mm, total; };
 FwdWs fwd_ws(const RnnDims& r) {
   FwdWs w{};
   size_t off = 0;
   w.zero = off; off += up256((size_t)r.B * r.H * 4);
   w.gh = off; off += up256((size_t)r.B * r.GH * 4);
   w.bias = off; off += up256((size_t)r.GH * 4);
+  w.sync = off; off += 256;  // grid-barrier counter of the persistent recurrence kernel
   w.mm = off;
   size_t m = 0;
   for (int l = 0; l < r.L; ++l) {
@@ -235,7 +238,7 @@ FwdWs fwd_ws(const RnnDims& r) {
   return w;
 }
 
-struct BwdWs { size_t dgx, dgh, dya, dyb, dh, dc, zero, red, mm, mm_bytes, red_bytes, total; };
+struct BwdWs { size_t dgx, dgh, dya, dyb, dh, dc, zero, sync, xbuf, red, mm, mm_bytes, red_bytes, total; };
 BwdWs bwd_ws(const RnnDims& r) {
   BwdWs w{};
   size_t off = 0;
@@ -246,6 +249,10 @@ BwdWs bwd_ws(const RnnDims& r) {
   w.dh = off; off += up256((size_t)r.B * r.H * 4);
   w.dc = off; off += up256((size_t)r.B * r.H * 4);
   w.zero = off; off += up256((size_t)r.B * r.H * 4);
+  w.sync = off; off += 256;  // grid-barrier counter of the persistent recurrence kernel
+  w.xbuf = off;              // its per-step exchange of partial sums
+  if (r.mode == FLB200_RNN_LSTM && (r.H == 256 || r.H == 512 || r.H == 1024))
+    off += up256(lstm_sequence_backward_scratch_bytes(r.H));
   w.red = off;
   w.red_bytes = flb200_channel_sum_workspace_bytes(r.TB, r.GH, 1);
   off += up256(w.red_bytes);
@@ -365,7 +372,25 @@ int flb200_rnn_forward(const flb200_rnn_desc* d, const void* x, const void* hx, 
       CUtensorMap map_whh;
       if (fused)
         if (int rc = lstm_step_weight_map(&map_whh, wf + po.w_hh, H)) return rc;
-      for (int step = 0; step < T; ++step) {
+      // ... or, where the device can hold the whole launch at once, ONE persistent kernel for
+      // all T steps with W_hh resident in shared memory (FLB200_RNN_PERSISTENT=0: per step)
+      static const bool persistent_off = [] {
+        const char* v = getenv("FLB200_RNN_PERSISTENT");
+        return v && v[0] == '0';
+      }();
+      int first_step = 0;
+      if (fused && !persistent_off && lstm_sequence_supported(d->math_mode, B, H)) {
+        if (int rc = lstm_sequence_forward(
+                map_whh, gates, cells, out + (long long)dir * H, out_stride, h_prev, c_prev,
+                reinterpret_cast<unsigned*>(ws + W.sync), T, B, H, dir, 0, -1, st))
+          return rc;
+        const int t_last = dir == 0 ? T - 1 : 0;
+        h_prev = out + (long long)t_last * B * out_stride + (long long)dir * H;
+        hp_stride = out_stride;
+        c_prev = cells + (long long)t_last * BH;
+        first_step = T;
+      }
+      for (int step = first_step; step < T; ++step) {
         const int t = dir == 0 ? step : T - 1 - step;
         float* g_t = gates + (long long)t * B * GH;
         float* h_t = out + (long long)t * B * out_stride + (long long)dir * H;
@@ -469,6 +494,27 @@ int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
       const float* gates = reinterpret_cast<const float*>(rs + RL.per_p * (size_t)p);
       const float* cells = reinterpret_cast<const float*>(rs + RL.per_p * (size_t)p + RL.cell_off);
       const float* qbuf = reinterpret_cast<const float*>(rs + RL.per_p * (size_t)p + RL.q_off);
+      // LSTM in TF32 mode on a device that holds the whole launch at once: the recurrence of
+      // all T steps in ONE persistent kernel (FLB200_RNN_PERSISTENT=0: kernels per step)
+      static const bool persistent_off = [] {
+        const char* v = getenv("FLB200_RNN_PERSISTENT");
+        return v && v[0] == '0';
+      }();
+      const bool persistent = r.mode == FLB200_RNN_LSTM && !persistent_off &&
+                              lstm_sequence_backward_supported(d->math_mode, B, H);
+      if (persistent) {
+        CUtensorMap map_wt;
+        if (int rc = lstm_sequence_weight_map_transposed(&map_wt, wf + po.w_hh, H)) return rc;
+        if (int rc = lstm_sequence_backward(
+                map_wt, gates, cells, cxf ? cxf + (long long)p * BH : zero,
+                dy_l ? dy_l + (long long)dir * H : nullptr, ys,
+                grad_hy ? static_cast<const float*>(grad_hy) + (long long)p * BH : nullptr,
+                grad_cy ? static_cast<const float*>(grad_cy) + (long long)p * BH : nullptr, dgx, dh,
+                dc, reinterpret_cast<float*>(ws + W.xbuf), reinterpret_cast<unsigned*>(ws + W.sync),
+                T, B, H, dir, st))
+          return rc;
+      }
+      if (!persistent) {
       copy_rows_kernel<<<cell_grid, 256, 0, st>>>(
           grad_hy ? static_cast<const float*>(grad_hy) + (long long)p * BH : nullptr, H, dh, H, B,
           H);
@@ -500,6 +546,7 @@ int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
                         1, dh, H, r.mode == FLB200_RNN_GRU ? 1.f : 0.f, mmws, mmws_bytes, stream))
           return rc;
       }
+      }  // !persistent
       if (grad_hx) {
         copy_rows_kernel<<<cell_grid, 256, 0, st>>>(
             dh, H, static_cast<float*>(grad_hx) + (long long)p * BH, H, B, H);
@@ -545,6 +592,38 @@ int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
     }
   }
   return FLB200_OK;
+}
+
+// ---- self-test of the bounded waits -------------------------------------------------------
+size_t flb200_selftest_bounded_wait_workspace_bytes(void) {
+  // W_hh [4H][H], gates [T][B][4H], cells and output [T][B][H], h0 / c0 [B][H], the counter
+  const size_t H = 256, B = 4, T = 3;
+  return (4 * H * H + T * B * 4 * H + 2 * T * B * H + 2 * B * H) * 4 + 256;
+}
+
+int flb200_selftest_bounded_wait(double budget_ms, void* workspace, size_t workspace_bytes,
+                                 void* stream) {
+  const int H = 256, B = 4, T = 3;
+  FLB200_REQUIRE(workspace && workspace_bytes >= flb200_selftest_bounded_wait_workspace_bytes(),
+                 "selftest_bounded_wait: workspace too small");
+  FLB200_REQUIRE(budget_ms > 0.0 && budget_ms <= 1000.0, "selftest_bounded_wait: budget in (0, 1000] ms");
+  if (!lstm_sequence_supported(FLB200_MATH_TF32, B, H))
+    return fail(FLB200_UNSUPPORTED, "selftest_bounded_wait: the persistent kernel cannot run here");
+  cudaStream_t st = as_stream(stream);
+  FLB200_CUDA_CHECK(cudaMemsetAsync(workspace, 0, flb200_selftest_bounded_wait_workspace_bytes(), st));
+  float* w = static_cast<float*>(workspace);
+  float* gates = w + 4 * H * H;
+  float* cells = gates + T * B * 4 * H;
+  float* out = cells + T * B * H;
+  float* h0 = out + T * B * H;
+  float* c0 = h0 + B * H;
+  unsigned* sync = reinterpret_cast<unsigned*>(c0 + B * H);
+  CUtensorMap map;
+  if (int rc = lstm_step_weight_map(&map, w, H)) return rc;
+  // CTA 0 never arrives at the grid barrier: every CTA's wait for step 1 runs out after
+  // budget_ms (at ~2 GHz), raises the status flag and the kernel still ends by itself
+  return lstm_sequence_forward(map, gates, cells, out, H, h0, c0, sync, T, B, H, 0,
+                               (long long)(budget_ms * 2.0e6), 0, st);
 }
 
 }  // extern "C"

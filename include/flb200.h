@@ -495,6 +495,18 @@ int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
                         const void* reserve, size_t reserve_bytes, void* workspace,
                         size_t workspace_bytes, void* stream);
 
+/* ------------------------------------------------------------- diagnostics */
+/* Self-test of the bounded device-side waits (no counterpart in the reference): runs the
+ * persistent LSTM recurrence kernel on a tiny all-zero problem in which one thread block never
+ * arrives at the per-step grid barrier.  Every other block's wait runs out after `budget_ms`,
+ * raises the library's device status flag, and the kernel ends by itself with the context
+ * intact; a following flb200_tc_poll_status() returns FLB200_TIMEOUT and clears the flag.
+ * FLB200_UNSUPPORTED where that kernel cannot run (not sm_100, or the device cannot hold its
+ * blocks at once). */
+size_t flb200_selftest_bounded_wait_workspace_bytes(void);
+int flb200_selftest_bounded_wait(double budget_ms, void* workspace, size_t workspace_bytes,
+                                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif
