@@ -93,6 +93,30 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB
 
 
+DIST_SRC = CSRC / "dist" / "dist.cpp"
+DIST_LIB = CSRC / "dist" / "libflb200_dist.so"
+
+
+def build_dist(force: bool = False) -> Path:
+    """Builds libflb200_dist.so (gradient synchronisation over NCCL; host code only)."""
+    h = hashlib.sha256(DIST_SRC.read_bytes())
+    for hdr in sorted(INCLUDE.glob("*.h")):
+        h.update(hdr.read_bytes())
+    stamp_file = OBJ_DIR / "dist.stamp"
+    OBJ_DIR.mkdir(exist_ok=True)
+    if (not force and DIST_LIB.exists() and stamp_file.exists()
+            and stamp_file.read_text() == h.hexdigest()):
+        return DIST_LIB
+    cmd = [_nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-I", str(INCLUDE),
+           str(DIST_SRC), "-o", str(DIST_LIB), "-lnccl"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"building {DIST_LIB.name} failed:\n{res.stdout}\n{res.stderr}")
+    stamp_file.write_text(h.hexdigest())
+    return DIST_LIB
+
+
 if __name__ == "__main__":
     path = build(force="--force" in sys.argv, verbose="--verbose" in sys.argv)
     print(path)
+    print(build_dist(force="--force" in sys.argv))
