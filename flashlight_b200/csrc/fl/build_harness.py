@@ -4,8 +4,8 @@ the flashlight checkout (FLASHLIGHT_REFERENCE, or a directory `reference` beside
 repository) with the stub tensor backend selected and every other backend off.  No reference
 source is copied; the object files and the shared object stay out of version control.
 
-The shared object links libflb200.so (the kernel library, same directory tree) and the CUDA
-runtime.  Where the checkout is absent nothing is built and the harness test is skipped.
+The shared object links libflb200.so and libflb200_dist.so (the kernel and gradient-
+synchronisation libraries, same directory tree) and the CUDA runtime.  Where the checkout is absent nothing is built and the harness test is skipped.
 Usage: python build_harness.py [--force]
 """
 from __future__ import annotations
@@ -33,7 +33,8 @@ REFERENCE_SOURCES = [
     "runtime/Stream.cpp", "runtime/SynchronousStream.cpp",
     "autograd/tensor/AutogradOps.cpp",
 ]
-OWN_SOURCES = ["B200AutogradExtension.cpp", "B200Tensor.cpp", "harness.cpp"]
+OWN_SOURCES = ["B200AutogradExtension.cpp", "B200Tensor.cpp", "B200DistributedBackend.cpp",
+               "harness.cpp"]
 FLAGS = [
     "-std=c++20", "-O2", "-fPIC", "-DFL_USE_TENSOR_STUB=1", "-DFL_USE_ARRAYFIRE=0",
     "-DFL_USE_ONEDNN=0", "-DFL_USE_JIT=0", "-DFL_USE_CUDNN=0", "-DFL_BACKEND_CUDA=1",
@@ -57,6 +58,7 @@ def build(force: bool = False) -> Path | None:
         return LIB if LIB.exists() else None
     from flashlight_b200.csrc import build as kernel_build
     kernel_build.build()
+    kernel_build.build_dist()
     OUT.mkdir(exist_ok=True)
     cuda = cuda_home()
     inc = ["-I", str(ref), "-I", str(ROOT / "include"), "-I", str(HERE), "-I", str(cuda / "include")]
@@ -82,6 +84,7 @@ def build(force: bool = False) -> Path | None:
     with ThreadPoolExecutor(max_workers=8) as pool:
         objs = list(pool.map(compile_one, jobs))
     cmd = ["g++", "-shared", "-o", str(LIB), *map(str, objs), "-L", str(CSRC), "-lflb200",
+           "-L", str(CSRC / "dist"), "-lflb200_dist", "-Wl,-rpath,$ORIGIN/../dist",
            "-L", str(cuda / "lib64"), "-lcudart", "-Wl,-rpath,$ORIGIN/..",
            "-Wl,-rpath," + str(cuda / "lib64"), "-Wl,--no-undefined"]
     res = subprocess.run(cmd, capture_output=True, text=True)

@@ -20,6 +20,7 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "B200AutogradExtension.h"
@@ -30,6 +31,18 @@
 
 namespace fl {
 FL_REGISTER_TENSOR_EXTENSION(B200AutogradExtension, Stub);
+// The Tensor-level half of fl::distributed, defined in B200DistributedBackend.cpp with the
+// signatures of flashlight/fl/distributed/DistributedApi.h:33-136.
+void distributedInit(
+    DistributedInit initMethod,
+    int worldRank,
+    int worldSize,
+    const std::unordered_map<std::string, std::string>& params);
+int getWorldRank();
+int getWorldSize();
+void allReduce(Tensor& arr, bool async);
+void allReduceMultiple(std::vector<Tensor*> arrs, bool async, bool contiguous);
+void syncDistributed();
 }
 
 namespace {
@@ -249,6 +262,55 @@ int flb200_fl_rnn_backward(
     out(std::get<1>(r), ghx);
     out(std::get<2>(r), gcx);
     out(std::get<3>(r), gw);
+  });
+}
+
+// ---- fl::distributed through fl::Tensor objects (f32 host buffers in, reduced values out) ----
+int flb200_fl_distributed_init(const char* path, int rank, int size, int devices_per_node) {
+  return guarded([&] {
+    fl::distributedInit(
+        fl::DistributedInit::FILE_SYSTEM, rank, size,
+        {{fl::DistributedConstants::kFilePath, path ? path : ""},
+         {fl::DistributedConstants::kMaxDevicePerNode, std::to_string(devices_per_node)},
+         {"RENDEZVOUS_TIMEOUT_S", "60"}});
+  });
+}
+
+int flb200_fl_world_rank(void) {
+  return fl::getWorldRank();
+}
+int flb200_fl_world_size(void) {
+  return fl::getWorldSize();
+}
+
+int flb200_fl_all_reduce(float* data, long long n, int async) {
+  return guarded([&] {
+    auto t = in(data, {static_cast<fl::Dim>(n)});
+    fl::allReduce(t, async != 0);
+    if (async) {
+      fl::syncDistributed();
+    }
+    out(t, data);
+  });
+}
+
+int flb200_fl_all_reduce_multiple(
+    float* const* data, const long long* counts, int n, int async, int contiguous) {
+  return guarded([&] {
+    std::vector<fl::Tensor> held;
+    held.reserve(n);
+    for (int i = 0; i < n; ++i) {
+      held.push_back(in(data[i], {static_cast<fl::Dim>(counts[i])}));
+    }
+    std::vector<fl::Tensor*> ptrs;
+    for (auto& t : held) {
+      ptrs.push_back(&t);
+    }
+    fl::allReduceMultiple(ptrs, async != 0, contiguous != 0);
+    fl::syncDistributed();
+    for (int i = 0; i < n; ++i) {
+      out(held[i], data[i]);
+    }
   });
 }
 

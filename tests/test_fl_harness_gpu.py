@@ -55,7 +55,8 @@ def test_harness_library_exports_the_shim():
     lib = C.CDLL(str(lib_path))
     for name in ("init", "registered", "last_error", "payload_new", "payload_free", "conv2d",
                  "conv2d_backward_data", "conv2d_backward_filter_bias", "pool2d", "pool2d_backward",
-                 "batchnorm", "batchnorm_backward", "rnn", "rnn_backward"):
+                 "batchnorm", "batchnorm_backward", "rnn", "rnn_backward", "distributed_init",
+                 "world_rank", "world_size", "all_reduce", "all_reduce_multiple"):
         assert hasattr(lib, "flb200_fl_" + name), name
 
 
@@ -220,3 +221,42 @@ def test_rnn_through_fl_tensors(H):
                                   ptr(dx), ptr(dhx), ptr(dcx), ptr(dw), I, B, T, Hd, L_, 2, 1,
                                   C.c_float(0.0), None)
     assert rc != 0
+
+
+@pytest.mark.gpu
+def test_distributed_backend_through_fl_tensors(H, tmp_path):
+    """fl::allReduce / allReduceMultiple / syncDistributed on fl::Tensor objects, answered by
+    B200DistributedBackend.cpp over the native NCCL backend.  One process is a communicator of
+    size 1: every collective, copy and stream dependency still runs.  Error behaviour follows
+    flashlight/fl/distributed/backend/cuda/DistributedBackend.cpp:114-175."""
+    ok(H, H.flb200_fl_init())
+    H.flb200_fl_all_reduce.argtypes = [f32p, C.c_longlong, C.c_int]
+    H.flb200_fl_all_reduce_multiple.argtypes = [C.POINTER(f32p), C.POINTER(C.c_longlong), C.c_int,
+                                                C.c_int, C.c_int]
+    x = np.arange(1000, dtype=np.float32)
+    if H.flb200_fl_world_size() == 1 and H.flb200_fl_world_rank() == 0:
+        rc = H.flb200_fl_all_reduce(ptr(x), x.size, 0)
+        if rc != 0:   # not yet initialised in this process
+            assert rc == 2 and b"not initialized" in H.flb200_fl_last_error()
+    assert H.flb200_fl_distributed_init(b"", 0, 1, 8) == 1          # std::invalid_argument
+    assert b"FilePath" in H.flb200_fl_last_error()
+    ok(H, H.flb200_fl_distributed_init(str(tmp_path / "id").encode(), 0, 1, 8))
+    assert (H.flb200_fl_world_rank(), H.flb200_fl_world_size()) == (0, 1)
+    for async_ in (0, 1):
+        y = x.copy()
+        ok(H, H.flb200_fl_all_reduce(ptr(y), y.size, async_))
+        assert np.array_equal(y, x)
+    bufs = [np.full(n, float(i + 1), dtype=np.float32) for i, n in enumerate((5, 4096, 33))]
+    for async_, contiguous in ((0, 0), (1, 0), (0, 1), (1, 1)):
+        work = [b.copy() for b in bufs]
+        ptrs = (f32p * 3)(*[ptr(b) for b in work])
+        counts = (C.c_longlong * 3)(*[b.size for b in work])
+        ok(H, H.flb200_fl_all_reduce_multiple(ptrs, counts, 3, async_, contiguous))
+        for a, b in zip(work, bufs):
+            assert np.array_equal(a, b)
+    big = [np.zeros(3 << 20, dtype=np.float32) for _ in range(2)]   # 24 MB > the 20 MB buffer
+    ptrs = (f32p * 2)(*[ptr(b) for b in big])
+    counts = (C.c_longlong * 2)(*[b.size for b in big])
+    assert H.flb200_fl_all_reduce_multiple(ptrs, counts, 2, 0, 1) == 2
+    assert b"Total coalesce buffer size" in H.flb200_fl_last_error()
+    ok(H, H.flb200_fl_all_reduce_multiple(ptrs, counts, 2, 0, 0))    # fine when not packed
