@@ -129,6 +129,7 @@ SIGNATURES = {
     "flb200_tanh_forward": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "flb200_tanh_backward": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_dropout_apply": (C.c_int, [vp, vp, vp, f32, i64, C.c_int, vp]),
+    "flb200_bernoulli_mask": (C.c_int, [vp, i64, f32, C.c_uint64, C.c_uint64, C.c_int, vp]),
     "flb200_add": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_log_softmax_forward": (C.c_int, [vp, vp, i64, i64, C.c_int, vp]),
     "flb200_log_softmax_backward": (C.c_int, [vp, vp, vp, i64, i64, C.c_int, vp]),
@@ -144,6 +145,12 @@ SIGNATURES = {
     "flb200_rnn_forward": (C.c_int, [P(RnnDesc), vp, vp, vp, vp, vp, vp, vp, vp, sz, vp, sz, vp]),
     "flb200_rnn_backward": (C.c_int, [P(RnnDesc), vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                       vp, sz, vp, sz, vp]),
+    "flb200_rnn_dropout_mask_elements": (i64, [P(RnnDesc)]),
+    "flb200_rnn_reserve_bytes_dropout": (sz, [P(RnnDesc)]),
+    "flb200_rnn_forward_dropout": (C.c_int, [P(RnnDesc), vp, vp, vp, vp, vp, f32, vp, vp, vp, vp,
+                                             sz, vp, sz, vp]),
+    "flb200_rnn_backward_dropout": (C.c_int, [P(RnnDesc), vp, vp, vp, vp, vp, f32, vp, vp, vp, vp,
+                                              vp, vp, vp, vp, vp, sz, vp, sz, vp]),
 }
 
 

@@ -451,3 +451,75 @@ int flb200_add(const void* a, const void* b, void* out, int64_t n, int dtype, vo
 }
 
 }  // extern "C"
+
+// ---- Bernoulli masks -------------------------------------------------------------------------
+// Philox4x32-10 (Salmon et al., "Parallel random numbers: as easy as 1, 2, 3", SC'11), a
+// counter-based generator: element block i of the stream (seed, offset) is a pure function of
+// (seed, offset + i), so a mask is reproducible whatever the grid that wrote it.
+namespace flb200 {
+namespace {
+
+__device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
+  constexpr uint32_t kM0 = 0xD2511F53u, kM1 = 0xCD9E8D57u, kW0 = 0x9E3779B9u, kW1 = 0xBB67AE85u;
+#pragma unroll
+  for (int round = 0; round < 10; ++round) {
+    const uint32_t hi0 = __umulhi(kM0, ctr.x), lo0 = kM0 * ctr.x;
+    const uint32_t hi1 = __umulhi(kM1, ctr.z), lo1 = kM1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += kW0;
+    key.y += kW1;
+  }
+  return ctr;
+}
+
+template <typename T>
+__global__ void bernoulli_mask_kernel(T* out, long long n, float keep, unsigned long long seed,
+                                      unsigned long long offset) {
+  const long long blocks = (n + 3) / 4;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < blocks;
+       i += (long long)gridDim.x * blockDim.x) {
+    const unsigned long long c = offset + (unsigned long long)i;
+    const uint4 r = philox4x32_10(make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u),
+                                  make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const long long e = 4 * i + j;
+      // 24 random bits -> a uniform value in [0, 1) that fp32 holds exactly
+      if (e < n) out[e] = Num<T>::from_f(((w[j] >> 8) * (1.0f / 16777216.0f)) < keep ? 1.f : 0.f);
+    }
+  }
+}
+
+}  // namespace
+}  // namespace flb200
+
+extern "C" int flb200_bernoulli_mask(void* out, int64_t n, float keep_prob, uint64_t seed,
+                                     uint64_t offset, int dtype, void* stream) {
+  using namespace flb200;
+  FLB200_REQUIRE(n >= 0, "bernoulli_mask: negative size");
+  FLB200_REQUIRE(keep_prob >= 0.f && keep_prob <= 1.f, "bernoulli_mask: probability outside [0, 1]");
+  if (n == 0) return FLB200_OK;
+  FLB200_REQUIRE(out, "bernoulli_mask: null tensor");
+  const long long blocks = (n + 3) / 4;
+  const unsigned grid = (unsigned)std::min<long long>((blocks + 255) / 256, 148 * 8);
+  cudaStream_t st = as_stream(stream);
+  switch (dtype) {
+    case FLB200_F32:
+      bernoulli_mask_kernel<float><<<grid, 256, 0, st>>>(static_cast<float*>(out), n, keep_prob,
+                                                         seed, offset);
+      break;
+    case FLB200_F16:
+      bernoulli_mask_kernel<__half><<<grid, 256, 0, st>>>(static_cast<__half*>(out), n, keep_prob,
+                                                          seed, offset);
+      break;
+    case FLB200_BF16:
+      bernoulli_mask_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(
+          static_cast<__nv_bfloat16*>(out), n, keep_prob, seed, offset);
+      break;
+    default:
+      return fail(FLB200_UNSUPPORTED, "bernoulli_mask: unsupported dtype %d", dtype);
+  }
+  FLB200_AFTER_LAUNCH("bernoulli_mask");
+  return FLB200_OK;
+}

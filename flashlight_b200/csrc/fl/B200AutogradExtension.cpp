@@ -6,6 +6,9 @@
  */
 #include "B200AutogradExtension.h"
 
+#include <atomic>
+#include <cstdlib>
+
 #include <algorithm>
 #include <cstdlib>
 #include <stdexcept>
@@ -62,7 +65,22 @@ struct ConvPayload : detail::AutogradPayloadData {
 
 struct RnnPayload : detail::AutogradPayloadData {
   Tensor reserve;
+  Tensor dropoutMask; // [H * dirs, B, T, L - 1] of 0 / 1 when inter-layer dropout is on
 };
+
+// Counter of the dropout-mask stream: every mask continues where the last one ended, so two
+// calls never reuse random numbers (the seed is fixed per process unless FLB200_SEED is set).
+uint64_t nextMaskOffset(int64_t elements) {
+  static std::atomic<uint64_t> offset{0};
+  return offset.fetch_add(static_cast<uint64_t>((elements + 3) / 4));
+}
+uint64_t maskSeed() {
+  static const uint64_t seed = [] {
+    const char* v = std::getenv("FLB200_SEED");
+    return v ? std::strtoull(v, nullptr, 10) : 0x5eed5eedULL;
+  }();
+  return seed;
+}
 
 flb200_conv2d_desc convDesc(
     const Tensor& input,
@@ -493,8 +511,8 @@ std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::rnn(
     const Tensor& weights, const int hiddenSize, const int numLayers, const RnnMode mode,
     const bool bidirectional, const float dropout,
     std::shared_ptr<detail::AutogradPayload> payload) {
-  if (dropout != 0.f) {
-    throw std::invalid_argument("rnn: inter-layer dropout is not built in the B200 extension");
+  if (dropout < 0.f || dropout >= 1.f) {
+    throw std::invalid_argument("rnn: dropout must be in [0, 1)");
   }
   requireF32(input, "rnn");
   requireF32(weights, "rnn");
@@ -514,28 +532,57 @@ std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::rnn(
     cy = Tensor({hiddenSize, d.batch, numLayers * dirs}, input.type());
   }
   Tensor none;
+  // Inter-layer dropout (cudnn/RNN.cpp:83-85): the mask is drawn by the library's counter-based
+  // generator and lives in the payload, where rnnBackward finds it.
+  const bool useDropout = dropout > 0.f && numLayers > 1;
+  const int64_t maskElements = useDropout ? flb200_rnn_dropout_mask_elements(&d) : 0;
   std::shared_ptr<RnnPayload> data;
   size_t reserveBytes = 0;
   if (payload) {  // created inside the payload and used from there (see pool2d)
-    reserveBytes = flb200_rnn_reserve_bytes(&d);
+    reserveBytes = useDropout ? flb200_rnn_reserve_bytes_dropout(&d) : flb200_rnn_reserve_bytes(&d);
     data = std::make_shared<RnnPayload>();
     data->reserve = scratch(reserveBytes);
+    if (useDropout) {
+      data->dropoutMask = Tensor({hiddenSize * dirs, d.batch, d.seq_len, numLayers - 1}, dtype::f32);
+    }
     payload->data = data;
   }
+  Tensor localMask;
+  if (useDropout && !data) {
+    localMask = Tensor({hiddenSize * dirs, d.batch, d.seq_len, numLayers - 1}, dtype::f32);
+  }
   const Tensor& reserve = data ? data->reserve : none;
-  const size_t wsBytes = flb200_rnn_workspace_bytes(&d, payload ? 0 : 2);
+  const Tensor& mask = data ? data->dropoutMask : localMask;
+  size_t wsBytes = flb200_rnn_workspace_bytes(&d, payload ? 0 : 2);
+  if (!payload && useDropout) {
+    wsBytes += flb200_rnn_reserve_bytes_dropout(&d);
+  }
   auto ws = scratch(wsBytes);
   {
-    DevicePtr xPtr(x), wPtr(w), yPtr(y), hyPtr(hy), wsPtr(ws), hxPtr, cxPtr, cyPtr, rsPtr;
+    DevicePtr xPtr(x), wPtr(w), yPtr(y), hyPtr(hy), wsPtr(ws), hxPtr, cxPtr, cyPtr, rsPtr, mkPtr;
     const auto& st = stream();
-    relativeSync(st, {x, hx, cx, w, y, hy, cy, reserve, ws});
-    check(
-        flb200_rnn_forward(
-            &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(), yPtr.get(),
-            hyPtr.get(), ptrOrNull(cy, cyPtr), ptrOrNull(reserve, rsPtr), reserveBytes,
-            wsPtr.get(), wsBytes, st.handle()),
-        "rnn");
-    relativeSync({y, hy, cy, reserve}, st);
+    relativeSync(st, {x, hx, cx, w, y, hy, cy, reserve, ws, mask});
+    if (useDropout) {
+      check(
+          flb200_bernoulli_mask(
+              ptrOrNull(mask, mkPtr), maskElements, 1.f - dropout, maskSeed(),
+              nextMaskOffset(maskElements), FLB200_F32, st.handle()),
+          "rnn");
+      check(
+          flb200_rnn_forward_dropout(
+              &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(), mkPtr.get(),
+              dropout, yPtr.get(), hyPtr.get(), ptrOrNull(cy, cyPtr), ptrOrNull(reserve, rsPtr),
+              reserveBytes, wsPtr.get(), wsBytes, st.handle()),
+          "rnn");
+    } else {
+      check(
+          flb200_rnn_forward(
+              &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(), yPtr.get(),
+              hyPtr.get(), ptrOrNull(cy, cyPtr), ptrOrNull(reserve, rsPtr), reserveBytes,
+              wsPtr.get(), wsBytes, st.handle()),
+          "rnn");
+    }
+    relativeSync({y, hy, cy, reserve, mask}, st);
     if (pollEveryCall_) {
       checkDeviceWaits();
     }
@@ -548,7 +595,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> B200AutogradExtension::rnnBackward(
     const Tensor& input, const Tensor& hiddenState, const Tensor& cellState,
     const Tensor& weights, const std::shared_ptr<detail::RNNGradData> gradData,
     const Tensor& output, const int numLayers, const int hiddenSize, const RnnMode mode,
-    const bool bidirectional, const float /* dropProb */,
+    const bool bidirectional, const float dropProb,
     std::shared_ptr<detail::AutogradPayload> payload) {
   if (!payload || !payload->data) {
     throw std::invalid_argument(
@@ -556,6 +603,7 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> B200AutogradExtension::rnnBackward(
   }
   const auto d = rnnDesc(input, hiddenSize, numLayers, mode, bidirectional, mathMode_);
   const Tensor& reserve = std::static_pointer_cast<RnnPayload>(payload->data)->reserve;
+  const Tensor& mask = std::static_pointer_cast<RnnPayload>(payload->data)->dropoutMask;
   const auto x = input.asContiguousTensor();
   const auto hx = hiddenState.isEmpty() ? hiddenState : hiddenState.asContiguousTensor();
   const auto cx = cellState.isEmpty() ? cellState : cellState.asContiguousTensor();
@@ -577,16 +625,27 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> B200AutogradExtension::rnnBackward(
   auto ws = scratch(wsBytes);
   {
     DevicePtr xPtr(x), wPtr(w), yPtr(y), dxPtr(dx), dhxPtr(dhx), dwPtr(dw), rsPtr(reserve),
-        wsPtr(ws), hxPtr, cxPtr, dyPtr, dhyPtr, dcyPtr, dcxPtr;
+        wsPtr(ws), hxPtr, cxPtr, dyPtr, dhyPtr, dcyPtr, dcxPtr, mkPtr;
     const auto& st = stream();
-    relativeSync(st, {x, hx, cx, w, y, dy, dhy, dcy, dx, dhx, dcx, dw, reserve, ws});
-    check(
-        flb200_rnn_backward(
-            &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(), yPtr.get(),
-            ptrOrNull(dy, dyPtr), ptrOrNull(dhy, dhyPtr), ptrOrNull(dcy, dcyPtr), dxPtr.get(),
-            dhxPtr.get(), ptrOrNull(dcx, dcxPtr), dwPtr.get(), rsPtr.get(),
-            static_cast<size_t>(reserve.elements()), wsPtr.get(), wsBytes, st.handle()),
-        "rnnBackward");
+    relativeSync(st, {x, hx, cx, w, y, dy, dhy, dcy, dx, dhx, dcx, dw, reserve, ws, mask});
+    if (!mask.isEmpty()) {
+      check(
+          flb200_rnn_backward_dropout(
+              &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(),
+              ptrOrNull(mask, mkPtr), dropProb, yPtr.get(), ptrOrNull(dy, dyPtr),
+              ptrOrNull(dhy, dhyPtr), ptrOrNull(dcy, dcyPtr), dxPtr.get(), dhxPtr.get(),
+              ptrOrNull(dcx, dcxPtr), dwPtr.get(), rsPtr.get(),
+              static_cast<size_t>(reserve.elements()), wsPtr.get(), wsBytes, st.handle()),
+          "rnnBackward");
+    } else {
+      check(
+          flb200_rnn_backward(
+              &d, xPtr.get(), ptrOrNull(hx, hxPtr), ptrOrNull(cx, cxPtr), wPtr.get(), yPtr.get(),
+              ptrOrNull(dy, dyPtr), ptrOrNull(dhy, dhyPtr), ptrOrNull(dcy, dcyPtr), dxPtr.get(),
+              dhxPtr.get(), ptrOrNull(dcx, dcxPtr), dwPtr.get(), rsPtr.get(),
+              static_cast<size_t>(reserve.elements()), wsPtr.get(), wsBytes, st.handle()),
+          "rnnBackward");
+    }
     relativeSync({dx, dhx, dcx, dw}, st);
     if (pollEveryCall_) {
       checkDeviceWaits();

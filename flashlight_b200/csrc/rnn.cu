@@ -73,9 +73,11 @@ inline size_t up256(size_t v) { return (v + 255) / 256 * 256; }
 // Reserve space: per pseudo-layer gates [T][B][GH], cells [T][B][H] (LSTM),
 // q [T][B][H] (GRU); per inner layer its output [T][B][H*dirs].
 struct ReserveLayout {
-  size_t gates_stride, cell_off, q_off, per_p, inner_y_off, inner_y_stride, total;
+  size_t gates_stride, cell_off, q_off, per_p, inner_y_off, inner_y_stride, dropped_off, total;
 };
-ReserveLayout reserve_layout(const RnnDims& r) {
+// dropout: the inner layers' outputs are kept twice, as computed (the layer's own backward pass
+// needs its hidden states) and with the dropout mask applied (the input of the layer above).
+ReserveLayout reserve_layout(const RnnDims& r, bool dropout = false) {
   ReserveLayout L{};
   size_t off = up256((size_t)r.TB * r.GH * 4);
   L.cell_off = off;
@@ -85,7 +87,8 @@ ReserveLayout reserve_layout(const RnnDims& r) {
   L.per_p = off;
   L.inner_y_off = L.per_p * (size_t)(r.L * r.dirs);
   L.inner_y_stride = up256((size_t)r.TB * r.H * r.dirs * 4);
-  L.total = L.inner_y_off + L.inner_y_stride * (size_t)(r.L - 1);
+  L.dropped_off = L.inner_y_off + L.inner_y_stride * (size_t)(r.L - 1);
+  L.total = L.dropped_off + (dropout ? L.inner_y_stride * (size_t)(r.L - 1) : 0);
   return L;
 }
 
@@ -303,14 +306,19 @@ size_t flb200_rnn_workspace_bytes(const flb200_rnn_desc* d, int backward) {
   return n;
 }
 
-int flb200_rnn_forward(const flb200_rnn_desc* d, const void* x, const void* hx, const void* cx,
-                       const void* w, void* y, void* hy, void* cy, void* reserve,
-                       size_t reserve_bytes, void* workspace, size_t workspace_bytes,
-                       void* stream) {
+// mask != NULL: inter-layer dropout (backend/cudnn/RNN.cpp:83-85), mask [L-1][T][B][H*dirs] of
+// 0 / 1, applied with scale 1 / (1 - p) to the input of layers 1 .. L-1.
+static int rnn_forward_impl(const flb200_rnn_desc* d, const void* x, const void* hx,
+                            const void* cx, const void* w, const void* mask, float drop_p,
+                            void* y, void* hy, void* cy, void* reserve, size_t reserve_bytes,
+                            void* workspace, size_t workspace_bytes, void* stream) {
   RnnDims r;
   if (int st = make_dims("rnn_forward", d, &r)) return st;
   FLB200_REQUIRE(x && w && y, "rnn_forward: null tensor");
-  const ReserveLayout RL = reserve_layout(r);
+  FLB200_REQUIRE(!mask || (drop_p >= 0.f && drop_p < 1.f), "rnn_forward: dropout outside [0, 1)");
+  const bool dropout = mask != nullptr && r.L > 1;
+  const float drop_scale = dropout ? 1.f / (1.f - drop_p) : 1.f;
+  const ReserveLayout RL = reserve_layout(r, dropout);
   const FwdWs W = fwd_ws(r);
   char* ws = static_cast<char*>(workspace);
   char* rs = static_cast<char*>(reserve);
@@ -343,8 +351,9 @@ int flb200_rnn_forward(const flb200_rnn_desc* d, const void* x, const void* hx, 
   for (int l = 0; l < r.L; ++l) {
     const long long In = in_size(r, l);
     const float* in = l == 0 ? static_cast<const float*>(x)
-                             : reinterpret_cast<const float*>(rs + RL.inner_y_off +
-                                                              RL.inner_y_stride * (size_t)(l - 1));
+                             : reinterpret_cast<const float*>(
+                                   rs + (dropout ? RL.dropped_off : RL.inner_y_off) +
+                                   RL.inner_y_stride * (size_t)(l - 1));
     float* out = l == r.L - 1 ? static_cast<float*>(y)
                               : reinterpret_cast<float*>(rs + RL.inner_y_off +
                                                          RL.inner_y_stride * (size_t)l);
@@ -433,20 +442,32 @@ int flb200_rnn_forward(const flb200_rnn_desc* d, const void* x, const void* hx, 
         FLB200_AFTER_LAUNCH("rnn_copy_cy");
       }
     }
+    if (dropout && l < r.L - 1) {
+      const long long n = r.TB * out_stride;
+      if (int rc = flb200_dropout_apply(
+              out, static_cast<const float*>(mask) + (long long)l * n,
+              rs + RL.dropped_off + RL.inner_y_stride * (size_t)l, drop_scale, n, FLB200_F32,
+              stream))
+        return rc;
+    }
   }
   return FLB200_OK;
 }
 
-int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx, const void* cx,
-                        const void* w, const void* y, const void* grad_y, const void* grad_hy,
-                        const void* grad_cy, void* grad_x, void* grad_hx, void* grad_cx,
-                        void* grad_w, const void* reserve, size_t reserve_bytes, void* workspace,
-                        size_t workspace_bytes, void* stream) {
+static int rnn_backward_impl(const flb200_rnn_desc* d, const void* x, const void* hx,
+                             const void* cx, const void* w, const void* mask, float drop_p,
+                             const void* y, const void* grad_y, const void* grad_hy,
+                             const void* grad_cy, void* grad_x, void* grad_hx, void* grad_cx,
+                             void* grad_w, const void* reserve, size_t reserve_bytes,
+                             void* workspace, size_t workspace_bytes, void* stream) {
   RnnDims r;
   if (int st = make_dims("rnn_backward", d, &r)) return st;
   FLB200_REQUIRE(x && w && y && grad_x && grad_w, "rnn_backward: null tensor");
   FLB200_REQUIRE(reserve, "rnn_backward: the reserve space written by rnn_forward is required");
-  const ReserveLayout RL = reserve_layout(r);
+  FLB200_REQUIRE(!mask || (drop_p >= 0.f && drop_p < 1.f), "rnn_backward: dropout outside [0, 1)");
+  const bool dropout = mask != nullptr && r.L > 1;
+  const float drop_scale = dropout ? 1.f / (1.f - drop_p) : 1.f;
+  const ReserveLayout RL = reserve_layout(r, dropout);
   if (reserve_bytes < RL.total)
     return fail(FLB200_WORKSPACE_TOO_SMALL, "rnn_backward: reserve %zu < %zu", reserve_bytes,
                 RL.total);
@@ -478,9 +499,11 @@ int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
 
   for (int l = r.L - 1; l >= 0; --l) {
     const long long In = in_size(r, l);
+    // the layer's input as the forward pass fed it: with dropout, the masked copy
     const float* in = l == 0 ? static_cast<const float*>(x)
-                             : reinterpret_cast<const float*>(rs + RL.inner_y_off +
-                                                              RL.inner_y_stride * (size_t)(l - 1));
+                             : reinterpret_cast<const float*>(
+                                   rs + (dropout ? RL.dropped_off : RL.inner_y_off) +
+                                   RL.inner_y_stride * (size_t)(l - 1));
     const float* out = l == r.L - 1 ? static_cast<const float*>(y)
                                     : reinterpret_cast<const float*>(rs + RL.inner_y_off +
                                                                      RL.inner_y_stride * (size_t)l);
@@ -590,8 +613,68 @@ int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
                       dir == 0 ? 0.f : 1.f, mmws, mmws_bytes, stream))
         return rc;
     }
+    if (dropout && l > 0) {
+      // din is the gradient of the MASKED output of the layer below
+      const long long n = r.TB * In;
+      if (int rc = flb200_dropout_apply(din, static_cast<const float*>(mask) + (long long)(l - 1) * n,
+                                        din, drop_scale, n, FLB200_F32, stream))
+        return rc;
+    }
   }
   return FLB200_OK;
+}
+
+int flb200_rnn_forward(const flb200_rnn_desc* d, const void* x, const void* hx, const void* cx,
+                       const void* w, void* y, void* hy, void* cy, void* reserve,
+                       size_t reserve_bytes, void* workspace, size_t workspace_bytes,
+                       void* stream) {
+  return rnn_forward_impl(d, x, hx, cx, w, nullptr, 0.f, y, hy, cy, reserve, reserve_bytes,
+                          workspace, workspace_bytes, stream);
+}
+
+int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx, const void* cx,
+                        const void* w, const void* y, const void* grad_y, const void* grad_hy,
+                        const void* grad_cy, void* grad_x, void* grad_hx, void* grad_cx,
+                        void* grad_w, const void* reserve, size_t reserve_bytes, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  return rnn_backward_impl(d, x, hx, cx, w, nullptr, 0.f, y, grad_y, grad_hy, grad_cy, grad_x,
+                           grad_hx, grad_cx, grad_w, reserve, reserve_bytes, workspace,
+                           workspace_bytes, stream);
+}
+
+int64_t flb200_rnn_dropout_mask_elements(const flb200_rnn_desc* d) {
+  RnnDims r;
+  if (make_dims("rnn_dropout_mask_elements", d, &r)) return -1;
+  return (long long)(r.L - 1) * r.TB * r.H * r.dirs;
+}
+
+size_t flb200_rnn_reserve_bytes_dropout(const flb200_rnn_desc* d) {
+  RnnDims r;
+  if (make_dims("rnn_reserve_bytes_dropout", d, &r)) return 0;
+  return reserve_layout(r, r.L > 1).total;
+}
+
+int flb200_rnn_forward_dropout(const flb200_rnn_desc* d, const void* x, const void* hx,
+                               const void* cx, const void* w, const void* mask, float p, void* y,
+                               void* hy, void* cy, void* reserve, size_t reserve_bytes,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+  FLB200_REQUIRE(mask || flb200_rnn_dropout_mask_elements(d) == 0,
+                 "rnn_forward_dropout: null mask");
+  return rnn_forward_impl(d, x, hx, cx, w, mask, p, y, hy, cy, reserve, reserve_bytes, workspace,
+                          workspace_bytes, stream);
+}
+
+int flb200_rnn_backward_dropout(const flb200_rnn_desc* d, const void* x, const void* hx,
+                                const void* cx, const void* w, const void* mask, float p,
+                                const void* y, const void* grad_y, const void* grad_hy,
+                                const void* grad_cy, void* grad_x, void* grad_hx, void* grad_cx,
+                                void* grad_w, const void* reserve, size_t reserve_bytes,
+                                void* workspace, size_t workspace_bytes, void* stream) {
+  FLB200_REQUIRE(mask || flb200_rnn_dropout_mask_elements(d) == 0,
+                 "rnn_backward_dropout: null mask");
+  return rnn_backward_impl(d, x, hx, cx, w, mask, p, y, grad_y, grad_hy, grad_cy, grad_x, grad_hx,
+                           grad_cx, grad_w, reserve, reserve_bytes, workspace, workspace_bytes,
+                           stream);
 }
 
 // ---- self-test of the bounded waits -------------------------------------------------------

@@ -78,6 +78,28 @@ def stream_handle() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+_mask_offset = 0
+
+
+def bernoulli_mask(shape, keep_prob: float, device, dtype=torch.float32, seed: Optional[int] = None,
+                   offset: Optional[int] = None) -> torch.Tensor:
+    """A 0 / 1 mask with P(1) = keep_prob from the library's counter-based generator
+    (flb200_bernoulli_mask).  Without an explicit (seed, offset) the stream continues from the
+    last call, seeded by torch's CUDA generator seed."""
+    global _mask_offset
+    out = torch.empty(shape, dtype=dtype, device=device)
+    n = out.numel()
+    if seed is None:
+        seed = torch.cuda.initial_seed() & ((1 << 64) - 1)
+    if offset is None:
+        offset = _mask_offset
+        _mask_offset += (n + 3) // 4
+    code = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}[dtype]
+    L.check(L.lib.flb200_bernoulli_mask(ptr(out), n, float(keep_prob), seed, offset, code,
+                                        stream_handle()))
+    return out
+
+
 def workspace(nbytes: int, like: torch.Tensor) -> Optional[torch.Tensor]:
     if nbytes <= 0:
         return None
@@ -153,6 +175,7 @@ class _PoolPayload:
 @dataclass
 class _RnnPayload:
     reserve: torch.Tensor
+    dropout_mask: Optional[torch.Tensor] = None
 
 
 def _shape4(t: torch.Tensor):
@@ -443,10 +466,13 @@ class B200AutogradExtension:
                          self.math_mode)
 
     def rnn(self, input, hiddenState, cellState, weights, hiddenSize, numLayers, mode,
-            bidirectional, dropout, payload=None):
-        """Returns (y, hy, cy); cy is None unless mode is LSTM."""
-        if dropout != 0.0:
-            raise NotImplementedError("rnn: inter-layer dropout is not built")
+            bidirectional, dropout, payload=None, dropout_mask=None):
+        """Returns (y, hy, cy); cy is None unless mode is LSTM.  dropout > 0 applies inter-layer
+        dropout (backend/cudnn/RNN.cpp:83-85): the mask [numLayers - 1, T, B, H * dirs] of 0 / 1
+        is drawn here (`bernoulli_mask`, a counter-based generator seeded from torch's) unless the
+        caller supplies one, and is kept in the payload for the backward pass."""
+        if not 0.0 <= dropout < 1.0:
+            raise ValueError("rnn: dropout must be in [0, 1)")
         d = self._rnn_desc(input, hiddenSize, numLayers, mode, bidirectional)
         nparams = L.lib.flb200_rnn_num_params(C.byref(d))
         if weights.numel() != nparams:
@@ -454,20 +480,40 @@ class B200AutogradExtension:
         dirs = 2 if bidirectional else 1
         T, B, _ = input.shape
         dev = input.device
+        use_dropout = (dropout > 0.0 or dropout_mask is not None) and numLayers > 1
+        mask = None
+        if use_dropout:
+            shape = (numLayers - 1, T, B, hiddenSize * dirs)
+            if dropout_mask is not None:
+                mask = dropout_mask
+                if tuple(mask.shape) != shape or mask.dtype != torch.float32 or not mask.is_contiguous():
+                    raise ValueError(f"rnn: dropout mask must be a dense float32 tensor {shape}")
+            else:
+                mask = bernoulli_mask(shape, 1.0 - dropout, dev)
         y = torch.empty((T, B, hiddenSize * dirs), dtype=torch.float32, device=dev)
         hy = torch.empty((numLayers * dirs, B, hiddenSize), dtype=torch.float32, device=dev)
         cy = torch.empty_like(hy) if int(mode) == L.RNN_LSTM else None
         reserve = None
         rbytes = 0
         if payload is not None:
-            rbytes = L.lib.flb200_rnn_reserve_bytes(C.byref(d))
+            rbytes = (L.lib.flb200_rnn_reserve_bytes_dropout(C.byref(d)) if use_dropout
+                      else L.lib.flb200_rnn_reserve_bytes(C.byref(d)))
             reserve = workspace(rbytes, input)
             payload.data = _RnnPayload(reserve)
+            payload.data.dropout_mask = mask
         wbytes = L.lib.flb200_rnn_workspace_bytes(C.byref(d), 0 if reserve is not None else 2)
+        if reserve is None and use_dropout:
+            wbytes += L.lib.flb200_rnn_reserve_bytes_dropout(C.byref(d))
         ws = workspace(wbytes, input)
-        L.check(L.lib.flb200_rnn_forward(
-            C.byref(d), ptr(input), ptr(hiddenState), ptr(cellState), ptr(weights), ptr(y), ptr(hy),
-            ptr(cy), ptr(reserve), rbytes, ptr(ws), wbytes, stream_handle()))
+        if use_dropout:
+            L.check(L.lib.flb200_rnn_forward_dropout(
+                C.byref(d), ptr(input), ptr(hiddenState), ptr(cellState), ptr(weights), ptr(mask),
+                float(dropout), ptr(y), ptr(hy), ptr(cy), ptr(reserve), rbytes, ptr(ws), wbytes,
+                stream_handle()))
+        else:
+            L.check(L.lib.flb200_rnn_forward(
+                C.byref(d), ptr(input), ptr(hiddenState), ptr(cellState), ptr(weights), ptr(y),
+                ptr(hy), ptr(cy), ptr(reserve), rbytes, ptr(ws), wbytes, stream_handle()))
         return y, hy, cy
 
     def rnnBackward(self, input, hiddenState, cellState, weights, gradData: RNNGradData, output,
@@ -477,6 +523,7 @@ class B200AutogradExtension:
             raise ValueError("B200AutogradExtension::rnnBackward given null detail::AutogradPayload")
         d = self._rnn_desc(input, hiddenSize, numLayers, mode, bidirectional)
         reserve = payload.data.reserve
+        mask = getattr(payload.data, "dropout_mask", None)
         dx = torch.empty_like(input)
         dirs = 2 if bidirectional else 1
         B = input.shape[1]
@@ -485,6 +532,13 @@ class B200AutogradExtension:
         dw = torch.empty_like(weights)
         wbytes = L.lib.flb200_rnn_workspace_bytes(C.byref(d), 1)
         ws = workspace(wbytes, input)
+        if mask is not None:
+            L.check(L.lib.flb200_rnn_backward_dropout(
+                C.byref(d), ptr(input), ptr(hiddenState), ptr(cellState), ptr(weights), ptr(mask),
+                float(dropProb), ptr(output), ptr(gradData.dy), ptr(gradData.dhy),
+                ptr(gradData.dcy), ptr(dx), ptr(dhx), ptr(dcx), ptr(dw), ptr(reserve),
+                reserve.numel(), ptr(ws), wbytes, stream_handle()))
+            return dx, dhx, dcx, dw
         L.check(L.lib.flb200_rnn_backward(
             C.byref(d), ptr(input), ptr(hiddenState), ptr(cellState), ptr(weights), ptr(output),
             ptr(gradData.dy), ptr(gradData.dhy), ptr(gradData.dcy), ptr(dx), ptr(dhx), ptr(dcx),

@@ -391,6 +391,12 @@ int flb200_tanh_backward(const void* y, const void* grad_y, void* grad_x, int64_
  * holds 0/1 in the tensor's dtype, as the reference materialises it. */
 int flb200_dropout_apply(const void* in, const void* mask, void* out, float scale,
                          int64_t n, int dtype, void* stream);
+/* The Bernoulli mask the reference draws with `rand(shape) > ratio` (Functions.cpp:1779-1781)
+ * for dropout: out[i] = 1 with probability keep_prob, else 0, from a counter-based generator
+ * (Philox4x32-10): the values depend on (seed, offset, i) only, never on the launch shape;
+ * element i uses counter offset + i / 4, so consecutive masks advance `offset` by (n + 3) / 4. */
+int flb200_bernoulli_mask(void* out, int64_t n, float keep_prob, uint64_t seed, uint64_t offset,
+                          int dtype, void* stream);
 /* out = a + b: Variable::addGrad fan-in accumulation (flashlight/fl/autograd/Variable.cpp:205-211). In place allowed. */
 int flb200_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
 
@@ -494,6 +500,25 @@ int flb200_rnn_backward(const flb200_rnn_desc* d, const void* x, const void* hx,
                         void* grad_x, void* grad_hx, void* grad_cx, void* grad_w,
                         const void* reserve, size_t reserve_bytes, void* workspace,
                         size_t workspace_bytes, void* stream);
+
+/* Inter-layer dropout (the `dropout` argument of AutogradExtension::rnn / rnnBackward,
+ * AutogradExtension.h:96-106,167-179; applied by cuDNN to the input of every layer but the first,
+ * backend/cudnn/RNN.cpp:83-85): the mask is DATA, [num_layers - 1][seq_len][batch][hidden * dirs]
+ * floats of 0 / 1 (flb200_bernoulli_mask draws one), scaled by 1 / (1 - p) when applied, and the
+ * same mask must be passed to the backward call.  The reserve space is larger
+ * (flb200_rnn_reserve_bytes_dropout): inner outputs are kept with and without the mask. */
+int64_t flb200_rnn_dropout_mask_elements(const flb200_rnn_desc* d);
+size_t flb200_rnn_reserve_bytes_dropout(const flb200_rnn_desc* d);
+int flb200_rnn_forward_dropout(const flb200_rnn_desc* d, const void* x, const void* hx,
+                               const void* cx, const void* w, const void* mask, float p, void* y,
+                               void* hy, void* cy, void* reserve, size_t reserve_bytes,
+                               void* workspace, size_t workspace_bytes, void* stream);
+int flb200_rnn_backward_dropout(const flb200_rnn_desc* d, const void* x, const void* hx,
+                                const void* cx, const void* w, const void* mask, float p,
+                                const void* y, const void* grad_y, const void* grad_hy,
+                                const void* grad_cy, void* grad_x, void* grad_hx, void* grad_cx,
+                                void* grad_w, const void* reserve, size_t reserve_bytes,
+                                void* workspace, size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------- diagnostics */
 /* Self-test of the bounded device-side waits (no counterpart in the reference): runs the

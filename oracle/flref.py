@@ -400,9 +400,12 @@ def _cell(mode, gx, h, c, whh, bhh, H):
     return (torch.relu(a) if mode == RNN_RELU else torch.tanh(a)), c
 
 
-def rnn(x, hx, cx, w, hidden, layers, mode, bidirectional):
+def rnn(x, hx, cx, w, hidden, layers, mode, bidirectional, dropout=0.0, dropout_mask=None):
     """x (T,B,I); hx/cx (L*dirs,B,H) or None; returns (y (T,B,H*dirs), hy, cy).
-    Written with differentiable torch ops so that torch.autograd gives rnn_backward()."""
+    Written with differentiable torch ops so that torch.autograd gives rnn_backward().
+    dropout_mask (layers-1, T, B, H*dirs) of 0 / 1: inter-layer dropout as cuDNN applies it
+    (flashlight/fl/autograd/tensor/backend/cudnn/RNN.cpp:83-85): the input of every layer but
+    the first is mask * value / (1 - dropout)."""
     T, B, I = x.shape
     dirs = 2 if bidirectional else 1
     params = rnn_unpack(w, I, hidden, layers, mode, bidirectional)
@@ -425,19 +428,22 @@ def rnn(x, hx, cx, w, hidden, layers, mode, bidirectional):
             hys.append(h)
             cys.append(c)
         inp = torch.cat(outs, dim=-1)
+        if dropout_mask is not None and l < layers - 1:
+            inp = inp * dropout_mask[l].to(inp.dtype) / (1.0 - dropout)
     hy = torch.stack(hys, 0)
     cy = torch.stack(cys, 0) if mode == RNN_LSTM else None
     return inp, hy, cy
 
 
-def rnn_backward(x, hx, cx, w, hidden, layers, mode, bidirectional, gy, ghy, gcy):
+def rnn_backward(x, hx, cx, w, hidden, layers, mode, bidirectional, gy, ghy, gcy, dropout=0.0,
+                 dropout_mask=None):
     """(dx, dhx, dcx, dw) by autograd through rnn(); absent output gradients count as zero
     (flashlight/fl/autograd/tensor/backend/cudnn/RNN.cpp:269-272)."""
     xr = x.detach().clone().requires_grad_(True)
     wr = w.detach().clone().requires_grad_(True)
     hr = hx.detach().clone().requires_grad_(True) if hx is not None else None
     cr = cx.detach().clone().requires_grad_(True) if cx is not None else None
-    y, hy, cy = rnn(xr, hr, cr, wr, hidden, layers, mode, bidirectional)
+    y, hy, cy = rnn(xr, hr, cr, wr, hidden, layers, mode, bidirectional, dropout, dropout_mask)
     total = (y * (gy if gy is not None else 0)).sum()
     if ghy is not None:
         total = total + (hy * ghy).sum()

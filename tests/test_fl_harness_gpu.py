@@ -224,6 +224,41 @@ def test_rnn_through_fl_tensors(H):
 
 
 @pytest.mark.gpu
+def test_rnn_dropout_through_fl_tensors(H):
+    """The C++ extension draws the inter-layer dropout mask itself and keeps it in the payload:
+    the result differs from the run without dropout, a second call draws another mask, and
+    rnnBackward with the same payload is repeatable."""
+    ok(H, H.flb200_fl_init())
+    r = load("rnn_lstm")
+    I, Hd, L_, B, T = (int(v) for v in r["dims"])
+    assert L_ >= 2
+    x, hx, cx, w, gy = (arr(r[k]) for k in ("x", "hx", "cx", "w", "gy"))
+    n = C.c_longlong(w.size)
+    outs = []
+    for _ in range(2):
+        y, hy, cy = np.empty_like(gy), np.empty_like(hx), np.empty_like(cx)
+        pl = H.flb200_fl_payload_new()
+        ok(H, H.flb200_fl_rnn(ptr(x), ptr(hx), ptr(cx), ptr(w), n, ptr(y), ptr(hy), ptr(cy), I, B, T,
+                              Hd, L_, 2, 1, C.c_float(0.5), vp(pl)))
+        grads = []
+        for _ in range(2):
+            dx, dhx, dcx, dw = (np.empty_like(x), np.empty_like(hx), np.empty_like(cx),
+                                np.empty_like(w))
+            ok(H, H.flb200_fl_rnn_backward(ptr(x), ptr(hx), ptr(cx), ptr(w), n, ptr(y), ptr(gy), None,
+                                           None, ptr(dx), ptr(dhx), ptr(dcx), ptr(dw), I, B, T, Hd,
+                                           L_, 2, 1, C.c_float(0.5), vp(pl)))
+            grads.append((dx, dw))
+        assert np.array_equal(grads[0][0], grads[1][0]) and np.array_equal(grads[0][1], grads[1][1])
+        assert np.isfinite(y).all() and np.isfinite(grads[0][1]).all()
+        H.flb200_fl_payload_free(vp(pl))
+        outs.append(y)
+    assert np.abs(outs[0] - r["y"].numpy()).max() > 1e-3      # not the dropout-free result
+    assert np.abs(outs[0] - outs[1]).max() > 1e-4              # a fresh mask per call
+    assert H.flb200_fl_rnn(ptr(x), ptr(hx), ptr(cx), ptr(w), n, ptr(outs[0]), None, None, I, B, T, Hd,
+                           L_, 2, 1, C.c_float(1.0), None) == 1
+
+
+@pytest.mark.gpu
 def test_distributed_backend_through_fl_tensors(H, tmp_path):
     """fl::allReduce / allReduceMultiple / syncDistributed on fl::Tensor objects, answered by
     B200DistributedBackend.cpp over the native NCCL backend.  One process is a communicator of

@@ -527,6 +527,92 @@ def test_rnn_forward_backward(ext, mode, case, with_state):
             assert_close(dcx, wdcx, STRICT_TOL, "rnn dcx")
 
 
+@pytest.mark.parametrize("mode", [R.RNN_TANH, R.RNN_LSTM, R.RNN_GRU])
+@pytest.mark.parametrize("case", [(5, 16, 2, 3, 7, True), (80, 64, 3, 4, 9, True), (6, 8, 3, 2, 5, False)])
+def test_rnn_inter_layer_dropout(ext, mode, case):
+    """Inter-layer dropout (backend/cudnn/RNN.cpp:83-85) with the mask supplied as data: the
+    input of every layer but the first is mask * value / (1 - p), forward and backward."""
+    from flashlight_b200.extension import AutogradPayload, RNNGradData
+    I, H, L_, B, T, bi = case
+    dirs = 2 if bi else 1
+    p = 0.3
+    n = R.rnn_num_params(I, H, L_, mode, bi)
+    w = randn(n, seed=60) * (0.5 / H ** 0.5)
+    x = randn(T, B, I, seed=61)
+    hx = randn(L_ * dirs, B, H, seed=62) * 0.5
+    cx = randn(L_ * dirs, B, H, seed=63) * 0.5 if mode == R.RNN_LSTM else None
+    g = torch.Generator().manual_seed(64)
+    mask = (torch.rand(L_ - 1, T, B, H * dirs, generator=g) >= p).float()
+    payload = AutogradPayload()
+    y, hy, cy = ext.rnn(x.cuda(), hx.cuda(), dev(cx), w.cuda(), H, L_, mode, bi, p, payload,
+                        dropout_mask=mask.cuda())
+    wy, why, wcy = R.rnn(x.double(), hx.double(), f64(cx), w.double(), H, L_, mode, bi, p, mask)
+    assert_close(y, wy, STRICT_TOL, "rnn y (dropout)")
+    assert_close(hy, why, STRICT_TOL, "rnn hy (dropout)")
+    # and it is not the same function as without dropout
+    y0, _, _ = ext.rnn(x.cuda(), hx.cuda(), dev(cx), w.cuda(), H, L_, mode, bi, 0.0, None)
+    assert (y0 - y).abs().max() > 1e-3
+    gy = randn(T, B, H * dirs, seed=65)
+    ghy = randn(L_ * dirs, B, H, seed=66)
+    dx, dhx, dcx, dw = ext.rnnBackward(x.cuda(), hx.cuda(), dev(cx), w.cuda(),
+                                       RNNGradData(gy.cuda(), ghy.cuda(), None), y, L_, H, mode, bi,
+                                       p, payload)
+    wdx, wdhx, wdcx, wdw = R.rnn_backward(x.double(), hx.double(), f64(cx), w.double(), H, L_, mode,
+                                          bi, gy.double(), ghy.double(), None, p, mask)
+    assert_close(dx, wdx, STRICT_TOL, "rnn dx (dropout)")
+    assert_close(dhx, wdhx, STRICT_TOL, "rnn dhx (dropout)")
+    assert_close(dw, wdw, STRICT_TOL, "rnn dw (dropout)")
+    if mode == R.RNN_LSTM:
+        assert_close(dcx, wdcx, STRICT_TOL, "rnn dcx (dropout)")
+
+
+def test_rnn_dropout_draws_its_own_mask(ext):
+    """Without a supplied mask the extension draws one (kept in the payload for the backward
+    pass); two calls use different parts of the random stream."""
+    from flashlight_b200.extension import AutogradPayload, RNNGradData
+    I, H, L_, B, T = 6, 32, 2, 4, 8
+    w = randn(R.rnn_num_params(I, H, L_, R.RNN_LSTM, True), seed=67) * 0.1
+    x = randn(T, B, I, seed=68)
+    pa, pb = AutogradPayload(), AutogradPayload()
+    ya, _, _ = ext.rnn(x.cuda(), None, None, w.cuda(), H, L_, R.RNN_LSTM, True, 0.5, pa)
+    yb, _, _ = ext.rnn(x.cuda(), None, None, w.cuda(), H, L_, R.RNN_LSTM, True, 0.5, pb)
+    ma, mb = pa.data.dropout_mask, pb.data.dropout_mask
+    assert ma.shape == (1, T, B, 2 * H) and set(ma.unique().tolist()) <= {0.0, 1.0}
+    assert 0.35 < ma.mean().item() < 0.65 and not torch.equal(ma, mb)
+    assert (ya - yb).abs().max() > 1e-4
+    wy, _, _ = R.rnn(x.double(), None, None, w.double(), H, L_, R.RNN_LSTM, True, 0.5, ma.cpu())
+    assert_close(ya, wy, STRICT_TOL, "rnn y (own mask)")
+    gy = randn(T, B, 2 * H, seed=69)
+    dx, _, _, dw = ext.rnnBackward(x.cuda(), None, None, w.cuda(), RNNGradData(gy.cuda(), None, None),
+                                   ya, L_, H, R.RNN_LSTM, True, 0.5, pa)
+    wdx, _, _, wdw = R.rnn_backward(x.double(), None, None, w.double(), H, L_, R.RNN_LSTM, True,
+                                    gy.double(), None, None, 0.5, ma.cpu())
+    assert_close(dx, wdx, STRICT_TOL, "rnn dx (own mask)")
+    assert_close(dw, wdw, STRICT_TOL, "rnn dw (own mask)")
+    with pytest.raises(ValueError):
+        ext.rnn(x.cuda(), None, None, w.cuda(), H, L_, R.RNN_LSTM, True, 1.0, None)
+
+
+def test_bernoulli_mask_is_a_pure_function_of_seed_and_counter():
+    from flashlight_b200.extension import bernoulli_mask
+    a = bernoulli_mask((1000003,), 0.8, "cuda", seed=7, offset=100)
+    b = bernoulli_mask((1000003,), 0.8, "cuda", seed=7, offset=100)
+    c = bernoulli_mask((1000003,), 0.8, "cuda", seed=8, offset=100)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    assert abs(a.mean().item() - 0.8) < 2e-3
+    # a mask drawn in two pieces (counter advanced by the elements / 4 of the first) is the same
+    d = bernoulli_mask((400,), 0.8, "cuda", seed=7, offset=100)
+    e = bernoulli_mask((600,), 0.8, "cuda", seed=7, offset=200)
+    assert torch.equal(torch.cat([d, e]), a[:1000])
+    # neighbouring bits are not correlated
+    ac = ((a[1:] - 0.8) * (a[:-1] - 0.8)).mean().item()
+    assert abs(ac) < 1e-3
+    h = bernoulli_mask((4096,), 0.5, "cuda", dtype=torch.bfloat16, seed=1, offset=0)
+    f = bernoulli_mask((4096,), 0.5, "cuda", seed=1, offset=0)
+    assert torch.equal(h.float(), f)
+    assert bernoulli_mask((0,), 0.5, "cuda").numel() == 0
+
+
 def test_rnn_backward_without_output_gradient(ext):
     """dy absent counts as zeros (backend/cudnn/RNN.cpp:269-272): only dhy drives the gradient."""
     from flashlight_b200.extension import AutogradPayload, RNNGradData
