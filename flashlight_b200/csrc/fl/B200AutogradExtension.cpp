@@ -15,6 +15,7 @@
 #include <string>
 
 #include "flashlight/fl/common/DevicePtr.h"
+#include "flashlight/fl/common/DynamicBenchmark.h"
 #include "flashlight/fl/tensor/Compute.h"
 #include "flashlight/fl/tensor/TensorBase.h"
 #include "flb200.h"
@@ -269,12 +270,51 @@ Tensor B200AutogradExtension::conv2d(
   return output;
 }
 
+/**************************** run-time kernel-mode selection ****************************/
+std::shared_ptr<fl::DynamicBenchmark> B200AutogradExtension::createBenchmarkOptions() {
+  return std::make_shared<fl::DynamicBenchmark>(
+      std::make_shared<fl::DynamicBenchmarkOptions<KernelMode>>(
+          std::vector<KernelMode>(
+              {KernelMode::F32, KernelMode::F32_ALLOW_CONVERSION, KernelMode::F32_SPLIT}),
+          fl::kDynamicBenchmarkDefaultCount));
+}
+
+int B200AutogradExtension::modeFor(const std::shared_ptr<DynamicBenchmark>& bench) const {
+  if (!bench || !DynamicBenchmark::getBenchmarkMode()) {
+    return mathMode_;
+  }
+  switch (bench->getOptions<DynamicBenchmarkOptions<KernelMode>>()->currentOption()) {
+    case KernelMode::F32:
+      return FLB200_MATH_STRICT_F32;
+    case KernelMode::F32_ALLOW_CONVERSION:
+      return FLB200_MATH_TF32;
+    case KernelMode::F32_SPLIT:
+      return FLB200_MATH_F32X3;
+  }
+  return mathMode_;
+}
+
+namespace {
+// Times `fn` for the benchmark's current option while tuning is on (DynamicBenchmark::audit
+// synchronises the device around it), else just runs it.
+template <typename F>
+void audited(const std::shared_ptr<DynamicBenchmark>& bench, F&& fn) {
+  if (bench && DynamicBenchmark::getBenchmarkMode()) {
+    bench->audit(fn);
+  } else {
+    fn();
+  }
+}
+} // namespace
+
 Tensor B200AutogradExtension::conv2dBackwardData(
     const Tensor& gradOutput, const Tensor& input, const Tensor& weight, const int sx,
     const int sy, const int px, const int py, const int dx, const int dy, const int groups,
-    std::shared_ptr<DynamicBenchmark>, std::shared_ptr<detail::AutogradPayload> payload) {
+    std::shared_ptr<DynamicBenchmark> dataGradBenchmark,
+    std::shared_ptr<detail::AutogradPayload> payload) {
   requireF32(gradOutput, "conv2dBackwardData");
-  const auto d = convDesc(input, weight, sx, sy, px, py, dx, dy, groups, mathMode_);
+  const auto d =
+      convDesc(input, weight, sx, sy, px, py, dx, dy, groups, modeFor(dataGradBenchmark));
   auto gradInput = Tensor(input.shape(), input.type());
   const size_t wsBytes = flb200_conv2d_workspace_bytes(&d, 1);
   auto ws = scratch(wsBytes);
@@ -290,12 +330,14 @@ Tensor B200AutogradExtension::conv2dBackwardData(
       relativeSync(st, {conv->xCl, conv->gyCl});
     }
     relativeSync(st, {gradOutput, weight, gradInput, ws});
-    check(
-        flb200_conv2d_backward_data_cached(
-            &d, goPtr.get(), wtPtr.get(), giPtr.get(), wsPtr.get(), wsBytes,
-            conv ? &conv->cache : nullptr, st.handle()),
-        "conv2dBackwardData");
-    relativeSync({gradInput}, st);
+    audited(dataGradBenchmark, [&] {
+      check(
+          flb200_conv2d_backward_data_cached(
+              &d, goPtr.get(), wtPtr.get(), giPtr.get(), wsPtr.get(), wsBytes,
+              conv ? &conv->cache : nullptr, st.handle()),
+          "conv2dBackwardData");
+      relativeSync({gradInput}, st);
+    });
     if (pollEveryCall_) {
       checkDeviceWaits();
     }
@@ -306,10 +348,12 @@ Tensor B200AutogradExtension::conv2dBackwardData(
 std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
     const Tensor& gradOutput, const Tensor& input, const Tensor& weights, const Tensor& bias,
     const int sx, const int sy, const int px, const int py, const int dx, const int dy,
-    const int groups, std::shared_ptr<DynamicBenchmark>, std::shared_ptr<DynamicBenchmark>,
+    const int groups, std::shared_ptr<DynamicBenchmark> filterGradBenchmark,
+    std::shared_ptr<DynamicBenchmark> /* biasGradBenchmark: the bias gradient is a reduction */,
     std::shared_ptr<detail::AutogradPayload> payload) {
   requireF32(gradOutput, "conv2dBackwardFilterBias");
-  const auto d = convDesc(input, weights, sx, sy, px, py, dx, dy, groups, mathMode_);
+  const auto d =
+      convDesc(input, weights, sx, sy, px, py, dx, dy, groups, modeFor(filterGradBenchmark));
   auto gradWeights = Tensor(weights.shape(), weights.type());
   // the bias gradient is skipped when there is no bias (cudnn/Conv2D.cpp:753)
   Tensor gradBias;
@@ -338,11 +382,14 @@ std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
       relativeSync(st, {conv->xCl, conv->gyCl});
     }
     relativeSync(st, {gradOutput, input, gradWeights, gradBias, ws});
-    check(
-        flb200_conv2d_backward_filter_bias_cached(
-            &d, goPtr.get(), inPtr.get(), gwPtr.get(), gb, wsPtr.get(), wsBytes,
-            conv ? &conv->cache : nullptr, st.handle()),
-        "conv2dBackwardFilterBias");
+    audited(filterGradBenchmark, [&] {
+      check(
+          flb200_conv2d_backward_filter_bias_cached(
+              &d, goPtr.get(), inPtr.get(), gwPtr.get(), gb, wsPtr.get(), wsBytes,
+              conv ? &conv->cache : nullptr, st.handle()),
+          "conv2dBackwardFilterBias");
+      relativeSync({gradWeights, gradBias}, st);
+    });
     if (conv) {
       conv->gyCl = Tensor(); // dead after this pass; x stays for a later backward
       conv->gyFrom = nullptr;

@@ -26,6 +26,20 @@ class B200AutogradExtension final : public AutogradExtension {
   // fp32 is the built dtype of the dense operators (f16 / bf16 exist for the element-wise ones)
   bool isDataTypeSupported(const fl::dtype& dtype) const override;
 
+  // The arithmetic a convolution gradient may run in, in the order DynamicBenchmark tries them
+  // (the counterpart of CudnnAutogradExtension::KernelMode,
+  // flashlight/fl/autograd/tensor/backend/cudnn/CudnnAutogradExtension.h:24): fp32 FMA, TF32
+  // tensor cores ("allow conversion"), and the three-pass TF32 split with fp32-grade results.
+  enum class KernelMode { F32 = 0, F32_ALLOW_CONVERSION = 1, F32_SPLIT = 2 };
+
+  // Options for a Conv2D module's run-time autotune (flashlight/fl/common/DynamicBenchmark.h:
+  // 196-263): while DynamicBenchmark::getBenchmarkMode() is on, conv2dBackwardData and
+  // conv2dBackwardFilterBias time each mode kDynamicBenchmarkDefaultCount times through
+  // DynamicBenchmark::audit and then keep the fastest, as the cuDNN extension does
+  // (cudnn/Conv2D.cpp:401-405,466-535); with benchmark mode off they run in the extension's
+  // configured mode.
+  std::shared_ptr<fl::DynamicBenchmark> createBenchmarkOptions() override;
+
   // Every wait inside the tensor-core kernels is bounded: one that runs out raises a device
   // flag and the kernel returns with partial results instead of hanging the GPU.  This call
   // synchronises the extension's stream, reads and clears the flag and throws
@@ -89,6 +103,9 @@ class B200AutogradExtension final : public AutogradExtension {
       std::shared_ptr<detail::AutogradPayload> payload) override;
 
  private:
+  // math mode of one audited call: the benchmark's current option while tuning is on
+  int modeFor(const std::shared_ptr<DynamicBenchmark>& bench) const;
+
   // FLB200_MATH_STRICT_F32, _TF32 or _F32X3 (environment FLB200_MATH=strict|tf32|f32x3, or
   // FLB200_TF32=1; read once)
   int mathMode_;

@@ -44,18 +44,36 @@ const CUDAStream& B200Backend::stream() {
 }
 
 /******************************* tensor *******************************/
+// Device memory comes from the CUDA stream-ordered pool on the backend's stream: allocating and
+// freeing a tensor neither synchronises the device nor calls into the driver's allocator in the
+// steady state (the pool keeps what was freed).  Every B200Tensor computes on that one stream
+// and the extension orders its own stream against it with relativeSync before a tensor it used
+// can be freed, so stream order is enough to make reuse safe.
 struct B200Tensor::Buffer {
   void* ptr = nullptr;
   size_t bytes = 0;
   int locks = 0;
   explicit Buffer(size_t n) : bytes(n) {
     if (n > 0) {
-      cudaCheck(cudaMalloc(&ptr, n), "cudaMalloc");
+      static const bool configured = [] {
+        int dev = 0;
+        cudaMemPool_t pool = nullptr;
+        unsigned long long keep = ~0ull;  // never trim the pool at synchronisation points
+        if (cudaGetDevice(&dev) == cudaSuccess &&
+            cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+          cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep);
+        }
+        return true;
+      }();
+      (void)configured;
+      cudaCheck(
+          cudaMallocAsync(&ptr, n, B200Backend::getInstance().stream().handle()),
+          "cudaMallocAsync");
     }
   }
   ~Buffer() {
     if (ptr) {
-      cudaFree(ptr); // synchronises with every stream that may still use the buffer
+      cudaFreeAsync(ptr, B200Backend::getInstance().stream().handle());
     }
   }
   Buffer(const Buffer&) = delete;

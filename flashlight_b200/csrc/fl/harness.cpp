@@ -25,6 +25,7 @@
 
 #include "B200AutogradExtension.h"
 #include "B200Tensor.h"
+#include "flashlight/fl/common/DynamicBenchmark.h"
 #include "flashlight/fl/autograd/tensor/AutogradOps.h"
 #include "flashlight/fl/tensor/TensorBase.h"
 #include "flashlight/fl/tensor/TensorExtension.h"
@@ -262,6 +263,53 @@ int flb200_fl_rnn_backward(
     out(std::get<1>(r), ghx);
     out(std::get<2>(r), gcx);
     out(std::get<3>(r), gw);
+  });
+}
+
+// ---- run-time kernel-mode selection (DynamicBenchmark) ----
+using Bench = std::shared_ptr<fl::DynamicBenchmark>;
+void* flb200_fl_benchmark_new(void) {
+  try {
+    fl::Tensor t({2}, fl::dtype::f32);
+    auto b = t.backend().getExtension<fl::AutogradExtension>().createBenchmarkOptions();
+    return b ? new Bench(b) : nullptr;
+  } catch (const std::exception& e) {
+    g_error = e.what();
+    return nullptr;
+  }
+}
+void flb200_fl_benchmark_free(void* h) {
+  delete static_cast<Bench*>(h);
+}
+void flb200_fl_benchmark_mode(int on) {
+  fl::DynamicBenchmark::setBenchmarkMode(on != 0);
+}
+// index of the option the next audited call will use, and whether tuning has finished
+int flb200_fl_benchmark_state(void* h, int* complete) {
+  auto opts = (*static_cast<Bench*>(h))
+                  ->getOptions<fl::DynamicBenchmarkOptions<fl::B200AutogradExtension::KernelMode>>();
+  if (complete) {
+    *complete = opts->timingsComplete() ? 1 : 0;
+  }
+  return static_cast<int>(opts->currentOption());
+}
+
+int flb200_fl_conv2d_backward_tuned(
+    const float* gy, const float* x, const float* w, float* gx, float* gw, int W, int H, int C,
+    int N, int kW, int kH, int Cout, int Wo, int Ho, int sx, int sy, int px, int py, int dx,
+    int dy, int groups, void* data_bench, void* filter_bench) {
+  return guarded([&] {
+    Bench db = data_bench ? *static_cast<Bench*>(data_bench) : nullptr;
+    Bench fb = filter_bench ? *static_cast<Bench*>(filter_bench) : nullptr;
+    auto tgy = in(gy, {Wo, Ho, Cout, N});
+    auto tx = in(x, {W, H, C, N});
+    auto tw = in(w, {kW, kH, C / groups, Cout});
+    out(fl::detail::conv2dBackwardData(tgy, tx, tw, sx, sy, px, py, dx, dy, groups, db, nullptr),
+        gx);
+    out(fl::detail::conv2dBackwardFilterBias(
+            tgy, tx, tw, fl::Tensor(), sx, sy, px, py, dx, dy, groups, fb, nullptr, nullptr)
+            .first,
+        gw);
   });
 }
 

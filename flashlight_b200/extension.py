@@ -193,6 +193,65 @@ def default_math_mode() -> int:
     return L.MATH_TF32 if os.environ.get("FLB200_TF32", "0") not in ("0", "", "false") else L.MATH_STRICT_F32
 
 
+class DynamicBenchmark:
+    """fl::DynamicBenchmark with DynamicBenchmarkOptions<KernelMode>
+    (flashlight/fl/common/DynamicBenchmark.h:60-263): while the class-wide benchmark mode is on,
+    audit() times the call under the current option (device synchronised on both sides, as
+    fl::sync() does there); every option is timed `count` times, then the fastest is kept."""
+
+    _benchmark_mode = False
+
+    def __init__(self, options: Sequence[int], count: int = 10):
+        if not options:
+            raise ValueError("Options must be passed vector with at least one element")
+        self.options, self.count = list(options), int(count)
+        self.reset()
+
+    def reset(self) -> None:
+        self.times = [0.0] * len(self.options)
+        self.counts = [0] * len(self.options)
+        self._complete, self._idx = False, 0
+
+    @classmethod
+    def setBenchmarkMode(cls, mode: bool) -> None:
+        cls._benchmark_mode = bool(mode)
+
+    @classmethod
+    def getBenchmarkMode(cls) -> bool:
+        return cls._benchmark_mode
+
+    def _update(self) -> None:
+        if self._complete:
+            return
+        for i, c in enumerate(self.counts):
+            if c < self.count:
+                self._idx = i
+                return
+        self._complete = True
+        self._idx = min(range(len(self.options)), key=lambda i: self.times[i])
+
+    def currentOption(self) -> int:
+        self._update()
+        return self.options[self._idx]
+
+    def timingsComplete(self) -> bool:
+        self._update()
+        return self._complete
+
+    def audit(self, function, incrementCount: bool = True):
+        if self.timingsComplete() or not self._benchmark_mode:
+            return function()
+        import time
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = function()
+        torch.cuda.synchronize()
+        self.times[self._idx] += time.perf_counter() - t0
+        if incrementCount:
+            self.counts[self._idx] += 1
+        return out
+
+
 class B200AutogradExtension:
     """sm_100a implementation of the Flashlight autograd extension interface."""
 
@@ -210,9 +269,19 @@ class B200AutogradExtension:
         """TensorExtension::isDataTypeSupported (flashlight/fl/tensor/TensorExtension.h:34)."""
         return dtype in _DTYPES
 
-    def createBenchmarkOptions(self):
-        """Base-class default: no dynamic benchmark (AutogradExtension.h:53-55)."""
-        return None
+    def createBenchmarkOptions(self) -> DynamicBenchmark:
+        """Options of a Conv2D module's run-time autotune: fp32 FMA, TF32 ("allow conversion")
+        and the three-pass split, tried in that order (the counterpart of
+        backend/cudnn/CudnnAutogradExtension.cpp:16-25)."""
+        return DynamicBenchmark([L.MATH_STRICT_F32, L.MATH_TF32, L.MATH_F32X3])
+
+    def _audited(self, bench: Optional[DynamicBenchmark], run):
+        """run(math_mode) under the benchmark's current option while tuning is on, else in the
+        configured mode (backend/cudnn/Conv2D.cpp:401-405,466-535)."""
+        if bench is None or not DynamicBenchmark.getBenchmarkMode():
+            return run(self.math_mode)
+        mode = bench.currentOption()
+        return bench.audit(lambda: run(mode))
 
     # --------------------------------------------------------------- conv2d
     def _conv_desc(self, input, weights, sx, sy, px, py, dx, dy, groups,
@@ -269,36 +338,46 @@ class B200AutogradExtension:
 
     def conv2dBackwardData(self, gradOutput, input, weight, sx, sy, px, py, dx, dy, groups,
                            dataGradBenchmark=None, payload=None):
-        d = self._conv_desc(input, weight, sx, sy, px, py, dx, dy, groups,
-                            is_channels_last(gradOutput) or is_channels_last(input))
         grad_in = torch.empty_like(input)
-        nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 1)
-        ws = workspace(nbytes, input)
-        cache = self._conv_cache(d, payload, input)
-        if cache is not None:
-            cache.bind_gy(gradOutput)
-        L.check(L.lib.flb200_conv2d_backward_data_cached(
-            C.byref(d), ptr(gradOutput), ptr(weight), ptr(grad_in), ptr(ws), nbytes,
-            cache.ref() if cache is not None else None, stream_handle()))
+
+        def run(mode):
+            d = self._conv_desc(input, weight, sx, sy, px, py, dx, dy, groups,
+                                is_channels_last(gradOutput) or is_channels_last(input))
+            d.math_mode = mode
+            nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 1)
+            ws = workspace(nbytes, input)
+            cache = self._conv_cache(d, payload, input)
+            if cache is not None:
+                cache.bind_gy(gradOutput)
+            L.check(L.lib.flb200_conv2d_backward_data_cached(
+                C.byref(d), ptr(gradOutput), ptr(weight), ptr(grad_in), ptr(ws), nbytes,
+                cache.ref() if cache is not None else None, stream_handle()))
+
+        self._audited(dataGradBenchmark, run)
         return grad_in
 
     def conv2dBackwardFilterBias(self, gradOutput, input, weights, bias, sx, sy, px, py, dx, dy,
                                  groups, filterBench=None, biasBench=None, autogradPayload=None):
-        d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups,
-                            is_channels_last(gradOutput) or is_channels_last(input))
         grad_w = torch.empty_like(weights)
         grad_b = torch.empty_like(bias) if bias is not None else None
-        nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 2)
-        ws = workspace(nbytes, input)
-        cache = self._conv_cache(d, autogradPayload, input)
-        if cache is not None:
-            cache.check_x(input)
-            cache.check_gy(gradOutput)
-        L.check(L.lib.flb200_conv2d_backward_filter_bias_cached(
-            C.byref(d), ptr(gradOutput), ptr(input), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes,
-            cache.ref() if cache is not None else None, stream_handle()))
-        if cache is not None:
-            cache.release_gy()
+
+        def run(mode):
+            d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups,
+                                is_channels_last(gradOutput) or is_channels_last(input))
+            d.math_mode = mode
+            nbytes = L.lib.flb200_conv2d_workspace_bytes(C.byref(d), 2)
+            ws = workspace(nbytes, input)
+            cache = self._conv_cache(d, autogradPayload, input)
+            if cache is not None:
+                cache.check_x(input)
+                cache.check_gy(gradOutput)
+            L.check(L.lib.flb200_conv2d_backward_filter_bias_cached(
+                C.byref(d), ptr(gradOutput), ptr(input), ptr(grad_w), ptr(grad_b), ptr(ws), nbytes,
+                cache.ref() if cache is not None else None, stream_handle()))
+            if cache is not None:
+                cache.release_gy()
+
+        self._audited(filterBench, run)   # the bias gradient is a reduction: nothing to choose
         return grad_w, grad_b
 
     # --------------------------------------------------------------- pool2d

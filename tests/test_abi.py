@@ -119,3 +119,29 @@ def test_cpp_extension_compiles_against_reference_headers(reference_root):
                          text=True)
     assert res.returncode == 0, res.stderr
     assert "compiles against the reference headers" in res.stdout
+
+
+def test_dynamic_benchmark_host_logic():
+    """fl::DynamicBenchmarkOptions semantics (flashlight/fl/common/DynamicBenchmark.h:60-194):
+    options are tried in order `count` times each, then the fastest stays."""
+    from flashlight_b200.extension import DynamicBenchmark
+    b = DynamicBenchmark([7, 8, 9], count=2)
+    assert b.currentOption() == 7 and not b.timingsComplete()
+    fake = {7: 3.0, 8: 1.0, 9: 2.0}
+    DynamicBenchmark.setBenchmarkMode(True)
+    try:
+        order = []
+        for _ in range(6):
+            opt = b.currentOption()
+            order.append(opt)
+            b.times[b._idx] += fake[opt]      # what audit() does around the call
+            b.counts[b._idx] += 1
+        assert order == [7, 7, 8, 8, 9, 9]
+        assert b.timingsComplete() and b.currentOption() == 8
+        ran = []
+        assert b.audit(lambda: ran.append(1) or "x") == "x" and ran == [1]   # no more timing
+        assert b.counts == [2, 2, 2]
+    finally:
+        DynamicBenchmark.setBenchmarkMode(False)
+    with pytest.raises(ValueError):
+        DynamicBenchmark([])

@@ -56,7 +56,8 @@ def test_harness_library_exports_the_shim():
     for name in ("init", "registered", "last_error", "payload_new", "payload_free", "conv2d",
                  "conv2d_backward_data", "conv2d_backward_filter_bias", "pool2d", "pool2d_backward",
                  "batchnorm", "batchnorm_backward", "rnn", "rnn_backward", "distributed_init",
-                 "world_rank", "world_size", "all_reduce", "all_reduce_multiple"):
+                 "world_rank", "world_size", "all_reduce", "all_reduce_multiple", "benchmark_new",
+                 "benchmark_free", "benchmark_mode", "benchmark_state", "conv2d_backward_tuned"):
         assert hasattr(lib, "flb200_fl_" + name), name
 
 
@@ -221,6 +222,56 @@ def test_rnn_through_fl_tensors(H):
                                   ptr(dx), ptr(dhx), ptr(dcx), ptr(dw), I, B, T, Hd, L_, 2, 1,
                                   C.c_float(0.0), None)
     assert rc != 0
+
+
+@pytest.mark.gpu
+def test_run_time_kernel_mode_selection(H):
+    """createBenchmarkOptions() + DynamicBenchmark::audit (flashlight/fl/common/DynamicBenchmark.h:
+    196-263): with benchmark mode on, the convolution gradients try fp32 FMA, TF32 and the
+    three-pass split kDynamicBenchmarkDefaultCount (10) times each and then stay on the fastest by
+    wall clock, which on a tensor-core-sized layer is one of the two tensor-core modes (the
+    first timed call of a mode also pays its one-time set-up, so which of the two wins is not
+    asserted); with benchmark mode off the configured mode runs."""
+    from oracle import flref as R
+    from tests.parity import assert_close_scaled
+    ok(H, H.flb200_fl_init())
+    H.flb200_fl_benchmark_new.restype = vp
+    H.flb200_fl_benchmark_free.argtypes = [vp]
+    H.flb200_fl_benchmark_state.argtypes = [vp, i32p]
+    N, Cc, Hh, W, Co, k = 64, 256, 14, 14, 256, 3
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(N, Cc, Hh, W, generator=g)
+    w = torch.randn(Co, Cc, k, k, generator=g) * 0.02
+    gy = torch.randn(N, Co, Hh, W, generator=g)
+    wgx = R.conv2d_backward_data(gy.double(), x.shape, w.double(), 1, 1, 1, 1, 1, 1, 1)
+    wgw, _ = R.conv2d_backward_filter_bias(gy.double(), x.double(), w.shape, False, 1, 1, 1, 1, 1, 1, 1)
+    xa, wa, gya = arr(x), arr(w), arr(gy)
+    gx, gw = np.empty_like(xa), np.empty_like(wa)
+    geo = (W, Hh, Cc, N, k, k, Co, W, Hh, 1, 1, 1, 1, 1, 1, 1)
+    db, fb = H.flb200_fl_benchmark_new(), H.flb200_fl_benchmark_new()
+    assert db and fb, H.flb200_fl_last_error().decode()
+    done = C.c_int(0)
+    assert H.flb200_fl_benchmark_state(vp(db), C.byref(done)) == 0 and done.value == 0
+    H.flb200_fl_benchmark_mode(1)
+    try:
+        seen = set()
+        for _ in range(31):
+            seen.add(H.flb200_fl_benchmark_state(vp(db), C.byref(done)))
+            ok(H, H.flb200_fl_conv2d_backward_tuned(ptr(gya), ptr(xa), ptr(wa), ptr(gx), ptr(gw), *geo,
+                                                    vp(db), vp(fb)))
+            assert_close_scaled(torch.from_numpy(gx), wgx, 2e-3, "tuned conv2dBackwardData")
+            assert_close_scaled(torch.from_numpy(gw), wgw, 2e-3, "tuned conv2dBackwardFilterBias")
+        assert seen == {0, 1, 2}                       # every mode was tried
+        for b in (db, fb):
+            assert H.flb200_fl_benchmark_state(vp(b), C.byref(done)) in (1, 2) and done.value == 1
+    finally:
+        H.flb200_fl_benchmark_mode(0)
+    # benchmark mode off: the benchmark objects are ignored
+    ok(H, H.flb200_fl_conv2d_backward_tuned(ptr(gya), ptr(xa), ptr(wa), ptr(gx), ptr(gw), *geo,
+                                            vp(db), vp(fb)))
+    assert_close_scaled(torch.from_numpy(gx), wgx, 2e-3, "conv2dBackwardData")
+    H.flb200_fl_benchmark_free(vp(db))
+    H.flb200_fl_benchmark_free(vp(fb))
 
 
 @pytest.mark.gpu

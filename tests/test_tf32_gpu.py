@@ -384,3 +384,36 @@ def test_matmul_bf16(L, case):
     assert L.lib.flb200_tc_kernel_launches() > before
     assert_close_scaled(got.float().reshape(want.shape), want, 1e-2, "bf16 matmul")
     assert L.lib.flb200_tc_poll_status(None) == 0  # no bounded wait ran out
+
+
+# ------------------------------------------------------------- run-time mode selection
+def test_conv_gradients_pick_a_tensor_core_mode(L):
+    """createBenchmarkOptions(): with benchmark mode on, a strict-mode extension's convolution
+    gradients try all three modes and settle on a tensor-core one for a tensor-core-sized layer;
+    with it off they stay strict."""
+    from flashlight_b200.extension import B200AutogradExtension, DynamicBenchmark
+    ext = B200AutogradExtension(math_mode=L.MATH_STRICT_F32)
+    x = randn(32, 128, 28, 28, seed=70).cuda()
+    w = (randn(128, 128, 3, 3, seed=71) * 0.03).cuda()
+    gy = randn(32, 128, 28, 28, seed=72).cuda()
+    args = (1, 1, 1, 1, 1, 1, 1)
+    want_gx = R.conv2d_backward_data(gy.double().cpu(), x.shape, w.double().cpu(), *args)
+    want_gw, _ = R.conv2d_backward_filter_bias(gy.double().cpu(), x.double().cpu(), w.shape, False, *args)
+    db, fb = ext.createBenchmarkOptions(), ext.createBenchmarkOptions()
+    _, launched = tc_delta(L, lambda: ext.conv2dBackwardData(gy, x, w, *args, db, None))
+    assert launched == 0 and db.counts == [0, 0, 0]            # benchmark mode is off
+    DynamicBenchmark.setBenchmarkMode(True)
+    try:
+        for _ in range(30):
+            gx = ext.conv2dBackwardData(gy, x, w, *args, db, None)
+            gw, _ = ext.conv2dBackwardFilterBias(gy, x, w, None, *args, fb, None, None)
+            assert_close_scaled(gx, want_gx, 2e-3, "tuned backward data")
+            assert_close_scaled(gw, want_gw, 2e-3, "tuned backward filter")
+        for b in (db, fb):
+            assert b.timingsComplete() and b.counts == [10, 10, 10]
+            assert b.currentOption() in (L.MATH_TF32, L.MATH_F32X3)
+            assert b.times[0] > min(b.times[1], b.times[2])
+        _, launched = tc_delta(L, lambda: ext.conv2dBackwardData(gy, x, w, *args, db, None))
+        assert launched >= 1                                     # now on the tensor cores
+    finally:
+        DynamicBenchmark.setBenchmarkMode(False)
