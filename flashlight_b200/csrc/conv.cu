@@ -29,7 +29,8 @@ int make_conv_geo(const char* name, const flb200_conv2d_desc* d, ConvGeo* g) {
   FLB200_REQUIRE(d->groups >= 1 && d->C % d->groups == 0 && d->Cout % d->groups == 0,
                  "%s: channels (%d in, %d out) not divisible by groups (%d)", name, d->C, d->Cout,
                  d->groups);
-  FLB200_REQUIRE(d->dtype == FLB200_F32, "%s: only f32 is built (dtype %d)", name, d->dtype);
+  FLB200_REQUIRE(d->dtype == FLB200_F32 || d->dtype == FLB200_F16 || d->dtype == FLB200_BF16,
+                 "%s: unknown dtype %d", name, d->dtype);
   FLB200_REQUIRE(d->math_mode >= FLB200_MATH_STRICT_F32 && d->math_mode <= FLB200_MATH_F32X3,
                  "%s: unknown math mode %d", name, d->math_mode);
   const int ekw = 1 + (d->kW - 1) * d->dx, ekh = 1 + (d->kH - 1) * d->dy;
@@ -247,6 +248,84 @@ inline bool tc_operands_aligned(const void* a, const void* b, const void* c, con
   return aligned16(a) && aligned16(b) && aligned16(c) && aligned16(d) && aligned16(ws);
 }
 
+
+// ---- 16-bit tensors ---------------------------------------------------------------------------
+// f16 / bf16 convolutions (the reference accepts f16, backend/cudnn/Conv2D.cpp:231,266,321) run
+// as: widen the operands into fp32 copies at the front of the workspace, run the fp32 operator
+// in the call's math mode (TF32 tensor cores keep 10 mantissa bits, as many as f16 has and more
+// than bf16), round the result once to the 16-bit type.  Accumulation is fp32 throughout.
+template <typename T>
+__global__ void widen_kernel(const T* __restrict__ in, float* __restrict__ out, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    if (i + 8 <= n && (reinterpret_cast<uintptr_t>(in + i) & 15) == 0) {
+      const Vec16<T> v = *reinterpret_cast<const Vec16<T>*>(in + i);
+#pragma unroll
+      for (int j = 0; j < 8; j += 4)
+        *reinterpret_cast<float4*>(out + i + j) =
+            make_float4(Num<T>::to_f(v.v[j]), Num<T>::to_f(v.v[j + 1]), Num<T>::to_f(v.v[j + 2]),
+                        Num<T>::to_f(v.v[j + 3]));
+    } else {
+      for (long long j = i; j < n && j < i + 8; ++j) out[j] = Num<T>::to_f(in[j]);
+    }
+  }
+}
+template <typename T>
+__global__ void narrow_kernel(const float* __restrict__ in, T* __restrict__ out, long long n) {
+  const long long stride = (long long)gridDim.x * blockDim.x * 8;
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+    if (i + 8 <= n && (reinterpret_cast<uintptr_t>(out + i) & 15) == 0) {
+      Vec16<T> v;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v.v[j] = Num<T>::from_f(in[i + j]);
+      *reinterpret_cast<Vec16<T>*>(out + i) = v;
+    } else {
+      for (long long j = i; j < n && j < i + 8; ++j) out[j] = Num<T>::from_f(in[j]);
+    }
+  }
+}
+int widen(const void* in, float* out, long long n, int dtype, cudaStream_t st) {
+  if (n == 0 || !in) return FLB200_OK;
+  const unsigned grid = (unsigned)std::min<long long>((n / 8 + 255) / 256 + 1, 148 * 8);
+  if (dtype == FLB200_F16)
+    widen_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(in), out, n);
+  else
+    widen_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), out, n);
+  FLB200_AFTER_LAUNCH("conv_widen");
+  return FLB200_OK;
+}
+int narrow(const float* in, void* out, long long n, int dtype, cudaStream_t st) {
+  if (n == 0 || !out) return FLB200_OK;
+  const unsigned grid = (unsigned)std::min<long long>((n / 8 + 255) / 256 + 1, 148 * 8);
+  if (dtype == FLB200_F16)
+    narrow_kernel<__half><<<grid, 256, 0, st>>>(in, static_cast<__half*>(out), n);
+  else
+    narrow_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(in, static_cast<__nv_bfloat16*>(out), n);
+  FLB200_AFTER_LAUNCH("conv_narrow");
+  return FLB200_OK;
+}
+// byte offsets of the fp32 copies pass `which` needs, in the order of its tensors:
+// 0: x, w, bias, y | 1: grad_y, w, grad_x | 2: grad_y, x, grad_w, grad_bias
+struct WideCopies {
+  long long n[4];
+  size_t off[4], total;
+};
+inline size_t up256c(size_t v) { return (v + 255) / 256 * 256; }
+WideCopies wide_copies(const ConvGeo& g, int which) {
+  const long long x = (long long)g.N * g.C * g.HW, w = (long long)g.Cout * g.Cg * g.RS,
+                  y = (long long)g.N * g.Cout * g.HoWo, b = g.Cout;
+  const long long n[3][4] = {{x, w, b, y}, {y, w, x, 0}, {y, x, w, b}};
+  WideCopies c{};
+  size_t off = 0;
+  for (int i = 0; i < 4; ++i) {
+    c.n[i] = n[which][i];
+    c.off[i] = off;
+    off += up256c((size_t)c.n[i] * 4);
+  }
+  c.total = off;
+  return c;
+}
+
 }  // namespace
 }  // namespace flb200
 
@@ -279,6 +358,8 @@ size_t flb200_conv2d_workspace_bytes(const flb200_conv2d_desc* d, int which) {
                                : flb200_channel_sum_workspace_bytes(g.N, g.Cout, g.HoWo));
   }
   if (d->math_mode != FLB200_MATH_STRICT_F32) need = max_sz(need, tc_conv_workspace_bytes(g, which));
+  if (d->dtype != FLB200_F32 && which >= 0 && which <= 2)
+    need = up256c(need) + wide_copies(g, which).total;  // fp32 copies of the 16-bit tensors
   return need;
 }
 
@@ -304,6 +385,26 @@ int flb200_conv2d_forward_cached(const flb200_conv2d_desc* d, const void* x, con
   if (int st = make_conv_geo("conv2d_forward", d, &g)) return st;
   FLB200_REQUIRE(x && w && y, "conv2d_forward: null tensor");
   cudaStream_t st = as_stream(stream);
+  if (d->dtype != FLB200_F32) {
+    const WideCopies c = wide_copies(g, 0);
+    if (!workspace || workspace_bytes < c.total)
+      return fail(FLB200_WORKSPACE_TOO_SMALL, "conv2d_forward: workspace %zu < %zu",
+                  workspace_bytes, c.total);
+    char* ws = static_cast<char*>(workspace);
+    float* x32 = reinterpret_cast<float*>(ws + c.off[0]);
+    float* w32 = reinterpret_cast<float*>(ws + c.off[1]);
+    float* b32 = bias ? reinterpret_cast<float*>(ws + c.off[2]) : nullptr;
+    float* y32 = reinterpret_cast<float*>(ws + c.off[3]);
+    if (int rc = widen(x, x32, c.n[0], d->dtype, st)) return rc;
+    if (int rc = widen(w, w32, c.n[1], d->dtype, st)) return rc;
+    if (int rc = widen(bias, b32, c.n[2], d->dtype, st)) return rc;
+    flb200_conv2d_desc d32 = *d;
+    d32.dtype = FLB200_F32;
+    if (int rc = flb200_conv2d_forward_cached(&d32, x32, w32, b32, y32, ws + c.total,
+                                              workspace_bytes - c.total, nullptr, stream))
+      return rc;
+    return narrow(y32, y, c.n[3], d->dtype, st);
+  }
   const float* xf = static_cast<const float*>(x);
   const float* wf = static_cast<const float*>(w);
   const float* bf = static_cast<const float*>(bias);
@@ -337,6 +438,24 @@ int flb200_conv2d_backward_data_cached(const flb200_conv2d_desc* d, const void* 
   if (int st = make_conv_geo("conv2d_backward_data", d, &g)) return st;
   FLB200_REQUIRE(grad_y && w && grad_x, "conv2d_backward_data: null tensor");
   cudaStream_t st = as_stream(stream);
+  if (d->dtype != FLB200_F32) {
+    const WideCopies c = wide_copies(g, 1);
+    if (!workspace || workspace_bytes < c.total)
+      return fail(FLB200_WORKSPACE_TOO_SMALL, "conv2d_backward_data: workspace %zu < %zu",
+                  workspace_bytes, c.total);
+    char* ws = static_cast<char*>(workspace);
+    float* gy32 = reinterpret_cast<float*>(ws + c.off[0]);
+    float* w32 = reinterpret_cast<float*>(ws + c.off[1]);
+    float* gx32 = reinterpret_cast<float*>(ws + c.off[2]);
+    if (int rc = widen(grad_y, gy32, c.n[0], d->dtype, st)) return rc;
+    if (int rc = widen(w, w32, c.n[1], d->dtype, st)) return rc;
+    flb200_conv2d_desc d32 = *d;
+    d32.dtype = FLB200_F32;
+    if (int rc = flb200_conv2d_backward_data_cached(&d32, gy32, w32, gx32, ws + c.total,
+                                                    workspace_bytes - c.total, nullptr, stream))
+      return rc;
+    return narrow(gx32, grad_x, c.n[2], d->dtype, st);
+  }
   const float* gyf = static_cast<const float*>(grad_y);
   const float* wf = static_cast<const float*>(w);
   float* gxf = static_cast<float*>(grad_x);
@@ -369,6 +488,27 @@ int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const
   if (int st = make_conv_geo("conv2d_backward_filter_bias", d, &g)) return st;
   FLB200_REQUIRE(grad_y && x && grad_w, "conv2d_backward_filter_bias: null tensor");
   cudaStream_t st = as_stream(stream);
+  if (d->dtype != FLB200_F32) {
+    const WideCopies c = wide_copies(g, 2);
+    if (!workspace || workspace_bytes < c.total)
+      return fail(FLB200_WORKSPACE_TOO_SMALL, "conv2d_backward_filter_bias: workspace %zu < %zu",
+                  workspace_bytes, c.total);
+    char* ws = static_cast<char*>(workspace);
+    float* gy32 = reinterpret_cast<float*>(ws + c.off[0]);
+    float* x32 = reinterpret_cast<float*>(ws + c.off[1]);
+    float* gw32 = reinterpret_cast<float*>(ws + c.off[2]);
+    float* gb32 = grad_bias ? reinterpret_cast<float*>(ws + c.off[3]) : nullptr;
+    if (int rc = widen(grad_y, gy32, c.n[0], d->dtype, st)) return rc;
+    if (int rc = widen(x, x32, c.n[1], d->dtype, st)) return rc;
+    flb200_conv2d_desc d32 = *d;
+    d32.dtype = FLB200_F32;
+    if (int rc = flb200_conv2d_backward_filter_bias_cached(&d32, gy32, x32, gw32, gb32,
+                                                           ws + c.total, workspace_bytes - c.total,
+                                                           nullptr, stream))
+      return rc;
+    if (int rc = narrow(gw32, grad_w, c.n[2], d->dtype, st)) return rc;
+    return narrow(gb32, grad_bias, c.n[3], d->dtype, st);
+  }
   const float* gyf = static_cast<const float*>(grad_y);
   const float* xf = static_cast<const float*>(x);
   float* gwf = static_cast<float*>(grad_w);

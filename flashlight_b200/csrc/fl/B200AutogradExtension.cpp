@@ -48,6 +48,23 @@ void requireF32(const Tensor& t, const char* what) {
   }
 }
 
+// Activations of the convolution, pooling and batch-norm operators may be f32 or f16 (the
+// types the cuDNN extension takes for them, minus f64): the library's type code.
+int activationType(const Tensor& t, const char* what) {
+  if (t.type() == fl::dtype::f32) {
+    return FLB200_F32;
+  }
+  if (t.type() == fl::dtype::f16) {
+    return FLB200_F16;
+  }
+  throw std::invalid_argument(std::string(what) + ": the B200 extension needs f32 or f16 tensors");
+}
+void requireSameType(const Tensor& t, const Tensor& like, const char* what) {
+  if (!t.isEmpty() && t.type() != like.type()) {
+    throw std::invalid_argument(std::string(what) + ": all tensors of the call must share a type");
+  }
+}
+
 Tensor scratch(size_t bytes) {
   return Tensor({static_cast<long long>(std::max<size_t>(bytes, 1))}, fl::dtype::b8);
 }
@@ -96,7 +113,7 @@ flb200_conv2d_desc convDesc(
   d.kH = static_cast<int>(dimOr1(weights, 1));
   d.Cout = static_cast<int>(dimOr1(weights, 3));
   d.sx = sx; d.sy = sy; d.px = px; d.py = py; d.dx = dx; d.dy = dy; d.groups = groups;
-  d.dtype = FLB200_F32;
+  d.dtype = activationType(input, "conv2d");
   d.math_mode = mathMode;
   d.layout = FLB200_LAYOUT_NCHW;  // fl tensors are [W,H,C,N]
   if (dimOr1(weights, 2) * groups != d.C) {
@@ -114,7 +131,7 @@ flb200_pool2d_desc poolDesc(
   d.N = static_cast<int>(dimOr1(input, 3));
   d.wx = wx; d.wy = wy; d.sx = sx; d.sy = sy; d.px = px; d.py = py;
   d.mode = static_cast<int>(mode);
-  d.dtype = FLB200_F32;
+  d.dtype = activationType(input, "pool2d");
   d.layout = FLB200_LAYOUT_NCHW;
   return d;
 }
@@ -130,6 +147,7 @@ flb200_batchnorm_desc bnDesc(const Tensor& input, const std::vector<int>& axes) 
       flb200_batchnorm_geometry(
           shape.data(), input.ndim(), ax.data(), static_cast<int>(ax.size()), &d),
       "batchnorm");
+  d.dtype = activationType(input, "batchnorm");  // parameters and statistics stay f32
   return d;
 }
 
@@ -228,7 +246,9 @@ const CUDAStream& B200AutogradExtension::stream() {
 }
 
 bool B200AutogradExtension::isDataTypeSupported(const fl::dtype& dtype) const {
-  return dtype == fl::dtype::f32;
+  // f16: convolution, pooling and batch-norm activations (fp32 accumulation; batch-norm
+  // parameters stay f32, as in backend/cudnn/BatchNorm.cpp:92-95).  The rnn operator is f32.
+  return dtype == fl::dtype::f32 || dtype == fl::dtype::f16;
 }
 
 /**************************** conv2d ****************************/
@@ -236,9 +256,8 @@ Tensor B200AutogradExtension::conv2d(
     const Tensor& input, const Tensor& weights, const Tensor& bias, const int sx, const int sy,
     const int px, const int py, const int dx, const int dy, const int groups,
     std::shared_ptr<detail::AutogradPayload> payload) {
-  requireF32(input, "conv2d");
-  requireF32(weights, "conv2d");
-  requireF32(bias, "conv2d");
+  requireSameType(weights, input, "conv2d");
+  requireSameType(bias, input, "conv2d");
   const auto d = convDesc(input, weights, sx, sy, px, py, dx, dy, groups, mathMode_);
   int32_t wo = 0, ho = 0;
   check(flb200_conv2d_output_dims(&d, &wo, &ho), "conv2d");
@@ -312,7 +331,8 @@ Tensor B200AutogradExtension::conv2dBackwardData(
     const int sy, const int px, const int py, const int dx, const int dy, const int groups,
     std::shared_ptr<DynamicBenchmark> dataGradBenchmark,
     std::shared_ptr<detail::AutogradPayload> payload) {
-  requireF32(gradOutput, "conv2dBackwardData");
+  requireSameType(gradOutput, input, "conv2dBackwardData");
+  requireSameType(weight, input, "conv2dBackwardData");
   const auto d =
       convDesc(input, weight, sx, sy, px, py, dx, dy, groups, modeFor(dataGradBenchmark));
   auto gradInput = Tensor(input.shape(), input.type());
@@ -351,7 +371,8 @@ std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
     const int groups, std::shared_ptr<DynamicBenchmark> filterGradBenchmark,
     std::shared_ptr<DynamicBenchmark> /* biasGradBenchmark: the bias gradient is a reduction */,
     std::shared_ptr<detail::AutogradPayload> payload) {
-  requireF32(gradOutput, "conv2dBackwardFilterBias");
+  requireSameType(gradOutput, input, "conv2dBackwardFilterBias");
+  requireSameType(weights, input, "conv2dBackwardFilterBias");
   const auto d =
       convDesc(input, weights, sx, sy, px, py, dx, dy, groups, modeFor(filterGradBenchmark));
   auto gradWeights = Tensor(weights.shape(), weights.type());
@@ -408,7 +429,6 @@ std::pair<Tensor, Tensor> B200AutogradExtension::conv2dBackwardFilterBias(
 Tensor B200AutogradExtension::pool2d(
     const Tensor& input, const int wx, const int wy, const int sx, const int sy, const int px,
     const int py, const PoolingMode mode, std::shared_ptr<detail::AutogradPayload> payload) {
-  requireF32(input, "pool2d");
   const auto d = poolDesc(input, wx, wy, sx, sy, px, py, mode);
   int32_t wo = 0, ho = 0;
   check(flb200_pool2d_output_dims(&d, &wo, &ho), "pool2d");
@@ -446,7 +466,7 @@ Tensor B200AutogradExtension::pool2dBackward(
     const Tensor& gradOutput, const Tensor& input, const Tensor& /* poolOutput */, const int wx,
     const int wy, const int sx, const int sy, const int px, const int py, const PoolingMode mode,
     std::shared_ptr<detail::AutogradPayload> payload) {
-  requireF32(gradOutput, "pool2dBackward");
+  requireSameType(gradOutput, input, "pool2dBackward");
   const auto d = poolDesc(input, wx, wy, sx, sy, px, py, mode);
   auto gradInput = Tensor(input.shape(), input.type());
   Tensor none;
@@ -477,7 +497,6 @@ Tensor B200AutogradExtension::batchnorm(
     const Tensor& bias, Tensor& runningMean, Tensor& runningVar, const std::vector<int>& axes,
     const bool train, const double momentum, const double epsilon,
     std::shared_ptr<detail::AutogradPayload>) {
-  requireF32(input, "batchnorm");
   requireF32(weight, "batchnorm");
   requireF32(bias, "batchnorm");
   auto d = bnDesc(input, axes);
@@ -524,7 +543,8 @@ std::tuple<Tensor, Tensor, Tensor> B200AutogradExtension::batchnormBackward(
   if (!train) {
     throw std::logic_error("can't compute batchnorm grad when train was not specified");
   }
-  requireF32(gradOutput, "batchnormBackward");
+  requireSameType(gradOutput, input, "batchnormBackward");
+  requireF32(weight, "batchnormBackward");
   auto d = bnDesc(input, axes);
   const long long features = d.channels;
   auto gradIn = Tensor(input.shape(), input.type());

@@ -1,10 +1,12 @@
 /* See B200Tensor.h. */
 #include "B200Tensor.h"
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <sstream>
 #include <stdexcept>
+#include <vector>
 
 #include "flashlight/fl/tensor/TensorBase.h"
 
@@ -32,8 +34,8 @@ B200Backend& B200Backend::getInstance() {
 void B200Backend::eval(const Tensor& /* tensor */) {}
 
 bool B200Backend::supportsDataType(const fl::dtype& dtype) const {
-  return dtype == fl::dtype::f32 || dtype == fl::dtype::b8 || dtype == fl::dtype::u8 ||
-      dtype == fl::dtype::s32;
+  return dtype == fl::dtype::f32 || dtype == fl::dtype::f16 || dtype == fl::dtype::b8 ||
+      dtype == fl::dtype::u8 || dtype == fl::dtype::s32;
 }
 
 const CUDAStream& B200Backend::stream() {
@@ -200,11 +202,32 @@ const Stream& B200Tensor::stream() const {
   return B200Backend::getInstance().stream();
 }
 
+// f32 <-> f16 through the host (round to nearest even): this tensor type exists to drive the
+// extension from tests, so the conversion favours being obviously right over being fast.
 Tensor B200Tensor::astype(const dtype type) {
-  if (type != type_) {
-    throw std::invalid_argument("B200Tensor::astype - conversions are not built");
+  if (type == type_) {
+    return copy();
   }
-  return copy();
+  const bool widen = type_ == fl::dtype::f16 && type == fl::dtype::f32;
+  const bool narrow = type_ == fl::dtype::f32 && type == fl::dtype::f16;
+  if (!widen && !narrow) {
+    throw std::invalid_argument("B200Tensor::astype - only f32 <-> f16 conversions are built");
+  }
+  const size_t n = static_cast<size_t>(shape_.elements());
+  std::vector<float> wide(n);
+  std::vector<__half> half(n);
+  if (narrow) {
+    host(wide.data());
+    for (size_t i = 0; i < n; ++i) {
+      half[i] = __float2half_rn(wide[i]);
+    }
+    return toTensor<B200Tensor>(shape_, type, half.data(), Location::Host);
+  }
+  host(half.data());
+  for (size_t i = 0; i < n; ++i) {
+    wide[i] = __half2float(half[i]);
+  }
+  return toTensor<B200Tensor>(shape_, type, wide.data(), Location::Host);
 }
 
 Tensor B200Tensor::flatten() const {

@@ -62,7 +62,7 @@ class B200Tensor : public StubTensor {
   bool isContiguous() override;
   Shape strides() override;
   const Stream& stream() const override;
-  Tensor astype(const dtype type) override; // same type only
+  Tensor astype(const dtype type) override; // same type, or f32 <-> f16
   Tensor flatten() const override;
   Tensor asContiguousTensor() override;
   void setContext(void* context) override;

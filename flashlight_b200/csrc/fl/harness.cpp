@@ -266,6 +266,48 @@ int flb200_fl_rnn_backward(
   });
 }
 
+// ---- f16 activations: one bottleneck-style chain conv2d -> batchnorm -> pool2d and its
+// gradients on f16 fl::Tensor objects (f32 host buffers in and out; batch-norm parameters f32) ----
+int flb200_fl_half_chain(
+    const float* x, const float* w, const float* gamma, const float* beta, const float* gy,
+    float* y, float* gx, float* gw, float* ggamma, float* gbeta, int W, int H, int C, int N,
+    int k, int Cout, int pad) {
+  return guarded([&] {
+    const auto f16 = fl::dtype::f16;
+    auto& ext = fl::Tensor().backend().getExtension<fl::AutogradExtension>();
+    if (!ext.isDataTypeSupported(f16)) {
+      throw std::runtime_error("the extension does not report f16 as supported");
+    }
+    auto tx = in(x, {W, H, C, N}).astype(f16);
+    auto tw = in(w, {k, k, C, Cout}).astype(f16);
+    auto tg = in(gamma, {Cout});
+    auto tb = in(beta, {Cout});
+    auto pc = std::make_shared<fl::detail::AutogradPayload>();
+    auto pp = std::make_shared<fl::detail::AutogradPayload>();
+    auto c = fl::detail::conv2d(tx, tw, fl::Tensor(), 1, 1, pad, pad, 1, 1, 1, pc);
+    fl::Tensor sm, sv, rm, rv;
+    auto b = fl::detail::batchnorm(sm, sv, c, tg, tb, rm, rv, {2}, true, 0.1, 1e-5, nullptr);
+    auto p = fl::detail::pool2d(b, 2, 2, 2, 2, 0, 0, fl::PoolingMode::AVG_INCLUDE_PADDING, pp);
+    if (c.type() != f16 || b.type() != f16 || p.type() != f16 || sm.type() != fl::dtype::f32) {
+      throw std::runtime_error("unexpected result types in the f16 chain");
+    }
+    out(p.astype(fl::dtype::f32), y);
+    auto tgy = in(gy, {p.dim(0), p.dim(1), p.dim(2), p.dim(3)}).astype(f16);
+    auto gb = fl::detail::pool2dBackward(tgy, b, p, 2, 2, 2, 2, 0, 0, fl::PoolingMode::AVG_INCLUDE_PADDING, pp);
+    auto bn = fl::detail::batchnormBackward(gb, sm, sv, c, tg, {2}, true, 1e-5f, nullptr);
+    auto gc = std::get<0>(bn);
+    out(std::get<1>(bn), ggamma);
+    out(std::get<2>(bn), gbeta);
+    out(fl::detail::conv2dBackwardData(gc, tx, tw, 1, 1, pad, pad, 1, 1, 1, nullptr, pc)
+            .astype(fl::dtype::f32),
+        gx);
+    out(fl::detail::conv2dBackwardFilterBias(
+            gc, tx, tw, fl::Tensor(), 1, 1, pad, pad, 1, 1, 1, nullptr, nullptr, pc)
+            .first.astype(fl::dtype::f32),
+        gw);
+  });
+}
+
 // ---- run-time kernel-mode selection (DynamicBenchmark) ----
 using Bench = std::shared_ptr<fl::DynamicBenchmark>;
 void* flb200_fl_benchmark_new(void) {

@@ -287,8 +287,8 @@ class B200AutogradExtension:
     def _conv_desc(self, input, weights, sx, sy, px, py, dx, dy, groups,
                    output_channels_last: Optional[bool] = None) -> L.Conv2dDesc:
         """output_channels_last: layout of y / grad_y; None = that of the input."""
-        if input.dtype != torch.float32 or weights.dtype != torch.float32:
-            raise ValueError("conv2d: only f32 tensors are supported")
+        if input.dtype not in _DTYPES or weights.dtype != input.dtype:
+            raise ValueError("conv2d: input and weights must share one of f32 / f16 / bf16")
         x_cl = is_channels_last(input)
         y_cl = x_cl if output_channels_last is None else bool(output_channels_last)
         if x_cl and not y_cl:
@@ -299,8 +299,8 @@ class B200AutogradExtension:
         if Cg * groups != Cin:
             raise ValueError(
                 f"conv2d: weight has {Cg} input channels per group x {groups} groups, input has {Cin}")
-        return L.Conv2dDesc(W, H, Cin, N, kW, kH, Cout, sx, sy, px, py, dx, dy, groups, L.F32,
-                            self.math_mode, layout)
+        return L.Conv2dDesc(W, H, Cin, N, kW, kH, Cout, sx, sy, px, py, dx, dy, groups,
+                            dtype_code(input), self.math_mode, layout)
 
     def _conv_cache(self, d, payload, like) -> Optional["_ConvLayoutCache"]:
         """The layout cache kept in the payload of one conv2d call site (None when the route

@@ -89,7 +89,8 @@ typedef struct flb200_conv2d_desc {
   int32_t W, H, C, N;
   int32_t kW, kH, Cout;
   int32_t sx, sy, px, py, dx, dy, groups;
-  int32_t dtype;      /* FLB200_F32 only */
+  int32_t dtype;      /* FLB200_F32; FLB200_F16 / FLB200_BF16: every tensor of the call in that
+                       * type, fp32 accumulation (operands are widened into the workspace) */
   int32_t math_mode;  /* FLB200_MATH_* */
   int32_t layout;     /* FLB200_LAYOUT_* of x / grad_x and y / grad_y (0 = fl's own) */
 } flb200_conv2d_desc;
@@ -169,7 +170,7 @@ typedef struct flb200_pool2d_desc {
   int32_t W, H, C, N;
   int32_t wx, wy, sx, sy, px, py;
   int32_t mode;   /* FLB200_POOL_* */
-  int32_t dtype;  /* FLB200_F32 */
+  int32_t dtype;  /* FLB200_F32 / F16 / BF16 */
   int32_t layout; /* FLB200_LAYOUT_NCHW or FLB200_LAYOUT_NHWC (x, y, argmax and gradients alike) */
 } flb200_pool2d_desc;
 
@@ -199,7 +200,9 @@ int flb200_pool2d_backward(const flb200_pool2d_desc* d, const void* grad_y,
  * outer*inner elements.  Per-activation mode (min axis 0) is inner == 1. */
 typedef struct flb200_batchnorm_desc {
   int64_t outer, channels, inner;
-  int32_t dtype;  /* FLB200_F32 */
+  int32_t dtype;  /* of x, y and their gradients: FLB200_F32 / F16 / BF16; weight, bias, the
+                   * statistics and their gradients are fp32 whatever it is (the reference's
+                   * f16 batch-norm, backend/cudnn/BatchNorm.cpp:92-95) */
 } flb200_batchnorm_desc;
 
 /* Turns (shape, axes) into the descriptor; returns FLB200_INVALID_ARG for axes

@@ -57,7 +57,8 @@ def test_harness_library_exports_the_shim():
                  "conv2d_backward_data", "conv2d_backward_filter_bias", "pool2d", "pool2d_backward",
                  "batchnorm", "batchnorm_backward", "rnn", "rnn_backward", "distributed_init",
                  "world_rank", "world_size", "all_reduce", "all_reduce_multiple", "benchmark_new",
-                 "benchmark_free", "benchmark_mode", "benchmark_state", "conv2d_backward_tuned"):
+                 "benchmark_free", "benchmark_mode", "benchmark_state", "conv2d_backward_tuned",
+                 "half_chain"):
         assert hasattr(lib, "flb200_fl_" + name), name
 
 
@@ -272,6 +273,41 @@ def test_run_time_kernel_mode_selection(H):
     assert_close_scaled(torch.from_numpy(gx), wgx, 2e-3, "conv2dBackwardData")
     H.flb200_fl_benchmark_free(vp(db))
     H.flb200_fl_benchmark_free(vp(fb))
+
+
+@pytest.mark.gpu
+def test_f16_activations_through_fl_tensors(H):
+    """isDataTypeSupported(f16): conv2d -> batchnorm (f32 parameters) -> pool2d and all their
+    gradients on f16 fl::Tensor objects.  The oracle runs the same chain in fp64 from the
+    f16-rounded inputs; each stage here rounds its result to f16 once."""
+    from oracle import flref as R
+    from tests.parity import assert_close_scaled
+    ok(H, H.flb200_fl_init())
+    N, Cc, Hh, W, Co, k, pad = 4, 32, 12, 12, 64, 3, 1
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(N, Cc, Hh, W, generator=g).half()
+    w = (torch.randn(Co, Cc, k, k, generator=g) * 0.06).half()
+    gamma = torch.rand(Co, generator=g) + 0.5
+    beta = torch.randn(Co, generator=g)
+    gy = torch.randn(N, Co, Hh // 2, W // 2, generator=g).half()
+    xr = x.double().requires_grad_(True)
+    wr = w.double().requires_grad_(True)
+    gr, br = gamma.double().requires_grad_(True), beta.double().requires_grad_(True)
+    c = torch.nn.functional.conv2d(xr, wr, None, 1, pad)
+    b = torch.nn.functional.batch_norm(c, None, None, gr, br, True, 0.1, 1e-5)
+    p = torch.nn.functional.avg_pool2d(b, 2, 2)
+    p.backward(gy.double())
+    xa, wa, ga, ba, gya = arr(x), arr(w), arr(gamma), arr(beta), arr(gy)
+    y = np.empty(p.shape, dtype=np.float32)
+    gx, gw, gg, gb = np.empty_like(xa), np.empty_like(wa), np.empty_like(ga), np.empty_like(ba)
+    ok(H, H.flb200_fl_half_chain(ptr(xa), ptr(wa), ptr(ga), ptr(ba), ptr(gya), ptr(y), ptr(gx),
+                                 ptr(gw), ptr(gg), ptr(gb), W, Hh, Cc, N, k, Co, pad))
+    tol = 6e-3   # three f16 roundings (2^-11 each) amplified by the normalisation
+    assert_close_scaled(torch.from_numpy(y), p.detach(), tol, "f16 chain output")
+    assert_close_scaled(torch.from_numpy(gx), xr.grad, tol, "f16 chain dx")
+    assert_close_scaled(torch.from_numpy(gw), wr.grad, tol, "f16 chain dw")
+    assert_close_scaled(torch.from_numpy(gg), gr.grad, tol, "f16 chain dgamma")
+    assert_close_scaled(torch.from_numpy(gb), br.grad, tol, "f16 chain dbeta")
 
 
 @pytest.mark.gpu
