@@ -117,6 +117,11 @@ SIGNATURES = {
     "flb200_embedding_backward": (C.c_int, [vp, vp, C.c_int, vp, i64, i64, i64, C.c_int, vp]),
     "flb200_softmax_forward": (C.c_int, [vp, vp, i64, i64, f32, i64, C.c_int, vp]),
     "flb200_softmax_backward": (C.c_int, [vp, vp, vp, i64, i64, f32, C.c_int, vp]),
+    "flb200_softmax_forward_lse": (C.c_int, [vp, vp, vp, i64, i64, f32, i64, C.c_int, vp]),
+    "flb200_attention_backward_supported": (C.c_int, [i64, i64, C.c_int]),
+    "flb200_attention_backward_workspace_bytes": (sz, [i64, i64, i64]),
+    "flb200_attention_backward": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i64, i64, f32,
+                                            C.c_int, C.c_int, vp, sz, vp]),
     "flb200_sgd_step": (C.c_int, [vp, vp, vp, i64, f32, f32, f32, C.c_int, f32, C.c_int, C.c_int, vp]),
     "flb200_relu_forward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_relu_backward_mask": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),

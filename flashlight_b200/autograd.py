@@ -10,6 +10,7 @@ the matching backward kernels.  This file holds no arithmetic of its own.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, List, Optional, Sequence
 
 import torch
@@ -20,6 +21,10 @@ from .extension import (AutogradPayload, B200AutogradExtension, RNNGradData, is_
                         same_layout)
 
 _ext: Optional[B200AutogradExtension] = None
+
+
+# FLB200_FUSED_ATTENTION=0: attention() runs the operator chain (matmul, softmax, matmul)
+FUSED_ATTENTION_OFF = os.environ.get("FLB200_FUSED_ATTENTION", "1") == "0"
 
 
 def extension() -> B200AutogradExtension:
@@ -511,6 +516,35 @@ def bmm(a: Variable, b: Variable, trans_b: bool = False) -> Variable:
             inputs[1].addGrad(gb)
 
     return Variable(y, False, [a, b], grad_func)
+
+
+def attention(q: Variable, k: Variable, v: Variable, scale: float, causal: bool) -> Variable:
+    """softmax(scale * q k^T [+ causal mask]) v for (batch * heads, T, head dim) tensors — the
+    chain matmulNT, softmax, matmul of flashlight/fl/autograd/Functions.cpp:1828-1891.  The
+    forward pass runs that chain on the library's kernels but keeps only q, k, v, the output and
+    the rows' log-sum-exp; the gradient is the fused kernel, which recomputes the probabilities
+    block by block.  Shapes the fused kernel is not built for take the operator chain."""
+    if not F.attention_backward_supported(q.tensor) or FUSED_ATTENTION_OFF:
+        probs = softmax_rows(bmm(q, k, trans_b=True), scale, causal_period=q.tensor.shape[1] if causal else 0)
+        return bmm(probs, v)
+    mode = extension().math_mode
+    qt, kt, vt = q.tensor.contiguous(), k.tensor.contiguous(), v.tensor.contiguous()
+    Z, T, hd = qt.shape
+    scores = F.matmul(qt, kt, m=T, n=T, k=hd, a_strides=(hd, 1), b_strides=(1, hd), batch=Z,
+                      batch_strides=(T * hd, T * hd, 0), math_mode=mode)
+    probs, lse = F.softmax_lse(scores, scale, T if causal else 0)
+    del scores
+    out = F.matmul(probs, vt, m=T, n=hd, k=T, a_strides=(T, 1), b_strides=(hd, 1), batch=Z,
+                   batch_strides=(T * T, T * hd, 0), math_mode=mode)
+    del probs
+
+    def grad_func(inputs, gy):
+        dq, dk, dv = F.attention_backward(qt, kt, vt, out, gy.contiguous(), lse, scale, causal)
+        for inp, g in zip(inputs, (dq, dk, dv)):
+            if inp.isCalcGrad():
+                inp.addGrad(g)
+
+    return Variable(out, False, [q, k, v], grad_func)
 
 
 def softmax_rows(x: Variable, scale: float = 1.0, causal_period: int = 0) -> Variable:

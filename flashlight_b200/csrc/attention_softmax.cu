@@ -20,7 +20,7 @@ constexpr int kPerLane = 64;  // rows of up to 2048 columns
 template <typename T, int PER>
 __global__ void __launch_bounds__(256)
 softmax_forward_kernel(const T* __restrict__ x, T* __restrict__ y, long long rows, int cols,
-                       float scale, int period) {
+                       float scale, int period, float* __restrict__ lse) {
   const int lane = threadIdx.x & 31;
   const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
@@ -44,6 +44,7 @@ softmax_forward_kernel(const T* __restrict__ x, T* __restrict__ y, long long row
   }
   s = warp_sum(s);
   const float inv = 1.f / s;
+  if (lse && lane == 0) lse[r] = m + logf(s);  // log of the sum of exp(scale * x) over the row
   T* yr = y + r * cols;
 #pragma unroll
   for (int j = 0; j < PER; ++j) {
@@ -81,7 +82,7 @@ softmax_backward_kernel(const T* __restrict__ y, const T* __restrict__ dy, T* __
 
 template <typename T>
 int launch(bool backward, const void* a, const void* b, void* out, long long rows, int cols,
-           float scale, int period, cudaStream_t st) {
+           float scale, int period, cudaStream_t st, float* lse) {
   const unsigned grid = (unsigned)((rows + 7) / 8);
 #define FLB200_SOFTMAX_CASE(PER)                                                              \
   if (cols <= 32 * PER) {                                                                     \
@@ -91,7 +92,7 @@ int launch(bool backward, const void* a, const void* b, void* out, long long row
           cols, scale);                                                                       \
     else                                                                                      \
       softmax_forward_kernel<T, PER><<<grid, 256, 0, st>>>(                                   \
-          static_cast<const T*>(a), static_cast<T*>(out), rows, cols, scale, period);         \
+          static_cast<const T*>(a), static_cast<T*>(out), rows, cols, scale, period, lse);    \
     return FLB200_OK;                                                                         \
   }
   FLB200_SOFTMAX_CASE(4)
@@ -103,7 +104,7 @@ int launch(bool backward, const void* a, const void* b, void* out, long long row
 }
 
 int dispatch(bool backward, const void* a, const void* b, void* out, long long rows, long long cols,
-             float scale, long long period, int dtype, void* stream) {
+             float scale, long long period, int dtype, void* stream, float* lse = nullptr) {
   const char* name = backward ? "softmax_backward" : "softmax_forward";
   FLB200_REQUIRE(rows >= 0 && cols >= 1 && period >= 0, "%s: bad extents", name);
   FLB200_REQUIRE(cols <= 32 * kPerLane, "%s: rows of more than %d columns", name, 32 * kPerLane);
@@ -113,10 +114,10 @@ int dispatch(bool backward, const void* a, const void* b, void* out, long long r
   cudaStream_t st = as_stream(stream);
   int rc;
   switch (dtype) {
-    case FLB200_F32: rc = launch<float>(backward, a, b, out, rows, (int)cols, scale, (int)period, st); break;
-    case FLB200_F16: rc = launch<__half>(backward, a, b, out, rows, (int)cols, scale, (int)period, st); break;
+    case FLB200_F32: rc = launch<float>(backward, a, b, out, rows, (int)cols, scale, (int)period, st, lse); break;
+    case FLB200_F16: rc = launch<__half>(backward, a, b, out, rows, (int)cols, scale, (int)period, st, lse); break;
     case FLB200_BF16:
-      rc = launch<__nv_bfloat16>(backward, a, b, out, rows, (int)cols, scale, (int)period, st);
+      rc = launch<__nv_bfloat16>(backward, a, b, out, rows, (int)cols, scale, (int)period, st, lse);
       break;
     default: return fail(FLB200_UNSUPPORTED, "%s: unknown dtype %d", name, dtype);
   }
@@ -133,6 +134,12 @@ extern "C" {
 int flb200_softmax_forward(const void* x, void* y, int64_t cols, int64_t rows, float scale,
                            int64_t causal_period, int dtype, void* stream) {
   return flb200::dispatch(false, x, nullptr, y, rows, cols, scale, causal_period, dtype, stream);
+}
+
+int flb200_softmax_forward_lse(const void* x, void* y, float* lse, int64_t cols, int64_t rows,
+                               float scale, int64_t causal_period, int dtype, void* stream) {
+  return flb200::dispatch(false, x, nullptr, y, rows, cols, scale, causal_period, dtype, stream,
+                          lse);
 }
 
 int flb200_softmax_backward(const void* y, const void* grad_y, void* grad_x, int64_t cols,

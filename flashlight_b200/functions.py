@@ -349,6 +349,38 @@ def softmax(x, scale: float = 1.0, causal_period: int = 0):
     return y
 
 
+def softmax_lse(x, scale: float = 1.0, causal_period: int = 0):
+    """softmax as above plus lse[row] = log sum exp(scale * x[row]) (fp32), the only thing the
+    fused attention gradient keeps of the scores."""
+    Cc, X = _cx(x)
+    y = torch.empty_like(x)
+    lse = torch.empty(X, dtype=torch.float32, device=x.device)
+    L.check(L.lib.flb200_softmax_forward_lse(ptr(x), ptr(y), ptr(lse), Cc, X, scale, causal_period,
+                                             dtype_code(x), stream_handle()))
+    return y, lse
+
+
+def attention_backward_supported(q) -> bool:
+    return bool(L.lib.flb200_attention_backward_supported(q.shape[1], q.shape[2], dtype_code(q)))
+
+
+def attention_backward(q, k, v, o, grad_o, lse, scale: float, causal: bool):
+    """(dq, dk, dv) of o = softmax(scale * q k^T [+ causal mask]) v in one flash-style kernel;
+    q, k, v, o, grad_o (batch * heads, T, head dim) dense, lse (batch * heads * T,) fp32."""
+    Z, T, hd = q.shape
+    for t in (q, k, v, o, grad_o):
+        if tuple(t.shape) != (Z, T, hd) or not t.is_contiguous() or t.dtype != q.dtype:
+            raise ValueError("attention_backward: q, k, v, o and grad_o must be dense and alike")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    nbytes = L.lib.flb200_attention_backward_workspace_bytes(Z, T, hd)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    L.check(L.lib.flb200_attention_backward(ptr(q), ptr(k), ptr(v), ptr(o), ptr(grad_o), ptr(lse),
+                                            ptr(dq), ptr(dk), ptr(dv), Z, T, hd, float(scale),
+                                            1 if causal else 0, dtype_code(q), ptr(ws), nbytes,
+                                            stream_handle()))
+    return dq, dk, dv
+
+
 def softmax_backward(y, grad_y, scale: float = 1.0):
     Cc, X = _cx(y)
     gx = torch.empty_like(y)

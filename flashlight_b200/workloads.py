@@ -295,10 +295,10 @@ class TransformerLM(nn.Module):
             return A.glue(qkv, fwd, bwd)
 
         q, k, v = split(0, 1.0), split(1, 1.0), split(2, 1.0)
-        scores = A.bmm(q, k, trans_b=True)                        # (B*h, T, T)
-        # scale 1/sqrt(head dim) and the causal mask are folded into the softmax kernel
-        probs = A.softmax_rows(scores, 1.0 / math.sqrt(hd), causal_period=T)
-        ctx = A.bmm(probs, v)                                     # (B*h, T, hd)
+        # scores (B*h, T, T) -> softmax with the scale 1/sqrt(head dim) and the causal mask folded
+        # in -> context (B*h, T, hd); the gradient is the fused kernel where it is built (bf16,
+        # head dim 64, T a multiple of 128), which keeps no T x T tensor for the backward pass
+        ctx = A.attention(q, k, v, 1.0 / math.sqrt(hd), causal=True)
         merged = A.glue(
             ctx, lambda t: t.reshape(B, h, T, hd).permute(0, 2, 1, 3).reshape(B * T, d).contiguous(),
             lambda g: g.reshape(B, T, h, hd).permute(0, 2, 1, 3).reshape(B * h, T, hd).contiguous())

@@ -438,6 +438,27 @@ int flb200_softmax_forward(const void* x, void* y, int64_t cols, int64_t rows, f
                            int64_t causal_period, int dtype, void* stream);
 int flb200_softmax_backward(const void* y, const void* grad_y, void* grad_x, int64_t cols,
                             int64_t rows, float scale, int dtype, void* stream);
+/* The forward pass that also keeps lse[row] = log sum_c exp(scale * x[row][c]) over the unmasked
+ * columns (fp32): all that flb200_attention_backward needs of the scores. */
+int flb200_softmax_forward_lse(const void* x, void* y, float* lse, int64_t cols, int64_t rows,
+                               float scale, int64_t causal_period, int dtype, void* stream);
+
+/* Gradient of o = softmax(scale * q k^T [+ causal mask]) v, the chain of
+ * flashlight/fl/autograd/Functions.cpp:1828-1891 (matmulNT, softmax, matmul) as one flash-style
+ * kernel: the T x T scores and probabilities are recomputed block by block in tensor memory from
+ * q, k and lse instead of being kept from the forward pass or written by the backward pass.
+ * q, k, v, o, grad_o, grad_q, grad_k, grad_v: [batch_heads][seq_len][head_dim] row-major;
+ * lse [batch_heads][seq_len] from flb200_softmax_forward_lse; causal: key c of query r is masked
+ * when c > r.  Built for FLB200_BF16, head_dim 64, seq_len a multiple of 128
+ * (flb200_attention_backward_supported); the workspace holds fp32 sums of grad_q. */
+int flb200_attention_backward_supported(int64_t seq_len, int64_t head_dim, int dtype);
+size_t flb200_attention_backward_workspace_bytes(int64_t batch_heads, int64_t seq_len,
+                                                 int64_t head_dim);
+int flb200_attention_backward(const void* q, const void* k, const void* v, const void* o,
+                              const void* grad_o, const float* lse, void* grad_q, void* grad_k,
+                              void* grad_v, int64_t batch_heads, int64_t seq_len,
+                              int64_t head_dim, float scale, int causal, int dtype,
+                              void* workspace, size_t workspace_bytes, void* stream);
 
 /* logSoftmax over fl dim 0: x, y [C, X] column-major (Functions.cpp:1044-1070). */
 int flb200_log_softmax_forward(const void* x, void* y, int64_t C, int64_t X, int dtype,
