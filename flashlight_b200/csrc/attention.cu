@@ -14,8 +14,9 @@
 //     dV_j += P^T dO_i                  (128 x  64, K = 128)  columns 256..319   (kept over i)
 //     dK_j += dS^T Q_i                  (128 x  64, K = 128)  columns 320..383   (kept over i)
 //     dQ_i  = dS K_j                    (128 x  64, K = 128)  columns 384..447
-// with P = exp(scale * S - lse), dS = scale * P * (dP - D), D = rowsum(dO * O), computed by the
-// 128 row threads between the two groups of contractions and written to shared memory as bf16
+// with P = exp(scale * S - lse), dS = scale * P * (dP - D) and D = rowsum(dO * O) from a small
+// pre-pass, computed by the row threads (two per query row, half of the columns each) between
+// the two groups of contractions and written to shared memory as bf16
 // operand tiles.  One storage order serves every role a tile plays: row r of a tile is 128
 // bytes (64 bf16) at r * 128 with its 16-byte chunks XOR-swizzled by r & 7 — read as a K-major
 // operand (rows = m or n, 64 k per row) or as an MN-major operand (rows = k, 64 m or n per
@@ -37,13 +38,13 @@ namespace {
 
 using namespace tc;
 
-constexpr int kAttnThreads = 160;      // warps 0..3: one thread per query row; warp 4: TMA + MMA
+constexpr int kAttnThreads = 288;      // warps 0..7: two threads per query row (each half of the
+                                       // columns); warp 8: TMA + MMA
 constexpr int kTile = 128 * 128;       // bytes of a [128 rows][64 bf16] tile
 constexpr int kAttnSmem = 4 * kTile + 2 * 2 * kTile + 1024 + 256;  // K V Q dO, P dS, align, bars
 
 struct AttnArgs {
-  const __nv_bfloat16* o;
-  const __nv_bfloat16* d_o;
+  const float* dsum;  // rowsum(dO * O), from attention_dsum_kernel
   const float* lse;
   float* dq_acc;
   __nv_bfloat16* dk;
@@ -57,6 +58,39 @@ struct AttnArgs {
 __device__ __forceinline__ uint32_t score_chunk(int r, int key0) {
   return (uint32_t)(key0 >> 6) * kTile + (uint32_t)r * 128 +
          ((((uint32_t)(key0 & 63) >> 3) ^ ((uint32_t)r & 7)) << 4);
+}
+
+// four consecutive fp32 sums in one reduction instruction (16-byte aligned address)
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+// two 32-column loads of this thread's tensor-memory lane in flight together
+__device__ __forceinline__ void tmem_ld32_pair(uint32_t ta, float* a, uint32_t tb, float* b) {
+  uint32_t x[32], y[32];
+#define FLB200_LD32(addr, r)                                                                     \
+  asm volatile(                                                                                  \
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                  \
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                  \
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"  \
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),      \
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),  \
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),            \
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),            \
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])             \
+      : "r"(addr)                                                                                \
+      : "memory")
+  FLB200_LD32(ta, x);
+  FLB200_LD32(tb, y);
+#undef FLB200_LD32
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    a[i] = __uint_as_float(x[i]);
+    b[i] = __uint_as_float(y[i]);
+  }
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -100,14 +134,15 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q,
     *failed = 0;
     fence_barrier_init();
   }
-  if (warp == 4) tmem_alloc(tmem_slot, 512);
+  if (warp == 8) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const bool issuer = warp == 4 && lane == 0;
-  const bool row_thread = warp < 4;
-  const int r = threadIdx.x;  // query row inside the block (row threads)
+  const bool issuer = warp == 8 && lane == 0;
+  const bool row_thread = warp < 8;
+  const int r = (warp & 3) * 32 + lane;  // query row inside the block (row threads)
+  const int half = warp >> 2;            // which half of the columns this row thread handles
 
   // operand descriptors (see the file comment): K-major tiles step 32 bytes per 16 k,
   // MN-major tiles step 16 rows = 2048 bytes per 16 k
@@ -132,6 +167,13 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q,
     tma_load(&map_v, bar_kv, sV, 2, c);
   }
 
+#ifdef FLB200_ATTN_PROFILE
+  long long pc[6] = {0, 0, 0, 0, 0, 0};
+#define ATTN_MARK(k, t) pc[k] += clock64() - t; t = clock64()
+  long long tp = clock64();
+#else
+#define ATTN_MARK(k, t)
+#endif
   const int i_first = a.causal ? j : 0;
   uint32_t it = 0;
   for (int i = i_first; i < nblk; ++i, ++it) {
@@ -157,30 +199,18 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     float lse = 0.f, dsum = 0.f;
     if (row_thread) {
-      // D = rowsum(dO * O) of this thread's query row, while the contractions run
-      const uint4* po = reinterpret_cast<const uint4*>(a.o + (qrow + r) * 64);
-      const uint4* pg = reinterpret_cast<const uint4*>(a.d_o + (qrow + r) * 64);
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const uint4 vo = po[u], vg = pg[u];
-        const __nv_bfloat162* ho = reinterpret_cast<const __nv_bfloat162*>(&vo);
-        const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&vg);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 fo = __bfloat1622float2(ho[e]), fg = __bfloat1622float2(hg[e]);
-          dsum += fo.x * fg.x + fo.y * fg.y;
-        }
-      }
+      dsum = a.dsum[qrow + r];
       lse = a.lse[qrow + r];
+      ATTN_MARK(0, tp);
       if (*failed == 0 && !mbar_wait(bar_s, ph)) *failed = 3;
       tc_fence_after();
-      const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+      ATTN_MARK(1, tp);
+      const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
       const int q_pos = i * 128 + r;
 #pragma unroll 1
-      for (int c0 = 0; c0 < 128; c0 += 32) {
+      for (int c0 = 64 * half; c0 < 64 * half + 64; c0 += 32) {
         float s[32], dp[32];
-        tmem_ld32(lane_addr + (uint32_t)c0, s);
-        tmem_ld32(lane_addr + 128u + (uint32_t)c0, dp);
+        tmem_ld32_pair(lane_addr + (uint32_t)c0, s, lane_addr + 128u + (uint32_t)c0, dp);
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const bool masked = a.causal && (j * 128 + c0 + e > q_pos);
@@ -200,6 +230,7 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q,
         }
       }
       fence_proxy_async();  // the tensor core reads these generic-proxy writes next
+      ATTN_MARK(2, tp);
     }
     tc_fence_before();
     __syncthreads();
@@ -221,47 +252,75 @@ attention_backward_kernel(const __grid_constant__ CUtensorMap map_q,
     if (*failed == 0 && !mbar_wait(bar_o, ph)) *failed = 4;
     tc_fence_after();
     if (row_thread) {
-      float* dst = a.dq_acc + (qrow + r) * 64;
-      const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16) + 384u;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float v[32];
-        tmem_ld32(lane_addr + (uint32_t)c0, v);
+      ATTN_MARK(3, tp);
+      float* dst = a.dq_acc + (qrow + r) * 64 + 32 * half;
+      float v[32];
+      tmem_ld32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + 384u + 32u * half, v);
 #pragma unroll
-        for (int e = 0; e < 32; ++e) atomicAdd(dst + c0 + e, v[e]);
-      }
+      for (int e = 0; e < 32; e += 4) red_add_v4(dst + e, v[e], v[e + 1], v[e + 2], v[e + 3]);
+      ATTN_MARK(4, tp);
     }
     // the next block's loads and contractions overwrite Q_i, dO_i, S, dP, P, dS and dQ
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+#ifdef FLB200_ATTN_PROFILE
+    if (row_thread) { ATTN_MARK(5, tp); }
+#endif
   }
+#ifdef FLB200_ATTN_PROFILE
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    printf("attention profile (CTA 0, %u blocks): D+lse %lld | wait S,dP %lld | softmax %lld | wait dV dK dQ %lld | atomics %lld | sync %lld\n",
+           it, pc[0], pc[1], pc[2], pc[3], pc[4], pc[5]);
+#endif
 
   if (row_thread) {
+    // the first half of the row threads stores dV_j, the second dK_j
     const long long krow = row0 + (long long)j * 128 + r;
-    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + 256u + 64u * half;
+    __nv_bfloat16* out = (half == 0 ? a.dv : a.dk) + krow * 64;
 #pragma unroll 1
-    for (int which = 0; which < 2; ++which) {
-      __nv_bfloat16* out = (which == 0 ? a.dv : a.dk) + krow * 64;
-#pragma unroll 1
-      for (int c0 = 0; c0 < 64; c0 += 32) {
-        float v[32];
-        tmem_ld32(lane_addr + 256u + 64u * which + (uint32_t)c0, v);
+    for (int c0 = 0; c0 < 64; c0 += 32) {
+      float v[32];
+      tmem_ld32(lane_addr + (uint32_t)c0, v);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          *reinterpret_cast<uint4*>(out + c0 + 8 * u) =
-              make_uint4(pack_bf16(v[8 * u], v[8 * u + 1]), pack_bf16(v[8 * u + 2], v[8 * u + 3]),
-                         pack_bf16(v[8 * u + 4], v[8 * u + 5]), pack_bf16(v[8 * u + 6], v[8 * u + 7]));
-      }
+      for (int u = 0; u < 4; ++u)
+        *reinterpret_cast<uint4*>(out + c0 + 8 * u) =
+            make_uint4(pack_bf16(v[8 * u], v[8 * u + 1]), pack_bf16(v[8 * u + 2], v[8 * u + 3]),
+                       pack_bf16(v[8 * u + 4], v[8 * u + 5]), pack_bf16(v[8 * u + 6], v[8 * u + 7]));
     }
   }
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0 && *failed != 0 && a.status) atomicExch(a.status, *failed);
-  if (warp == 4) {
+  if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
   }
+}
+
+// D[row] = sum_d dO[row][d] * O[row][d]: eight lanes per row, one 16-byte load each
+__global__ void attention_dsum_kernel(const __nv_bfloat16* __restrict__ o,
+                                      const __nv_bfloat16* __restrict__ d_o,
+                                      float* __restrict__ dsum, long long rows) {
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long row = t >> 3;
+  float acc = 0.f;
+  if (row < rows) {
+    const uint4 vo = reinterpret_cast<const uint4*>(o)[t];
+    const uint4 vg = reinterpret_cast<const uint4*>(d_o)[t];
+    const __nv_bfloat162* ho = reinterpret_cast<const __nv_bfloat162*>(&vo);
+    const __nv_bfloat162* hg = reinterpret_cast<const __nv_bfloat162*>(&vg);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 fo = __bfloat1622float2(ho[e]), fg = __bfloat1622float2(hg[e]);
+      acc += fo.x * fg.x + fo.y * fg.y;
+    }
+  }
+  acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+  acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+  if (row < rows && (threadIdx.x & 7) == 0) dsum[row] = acc;
 }
 
 __global__ void narrow_dq_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ dq,
@@ -285,7 +344,9 @@ extern "C" {
 size_t flb200_attention_backward_workspace_bytes(int64_t batch_heads, int64_t seq_len,
                                                  int64_t head_dim) {
   if (batch_heads <= 0 || seq_len <= 0 || head_dim <= 0) return 0;
-  return (size_t)batch_heads * seq_len * head_dim * sizeof(float);  // fp32 sums of dq
+  // fp32 sums of dq, then rowsum(dO * O)
+  return (size_t)batch_heads * seq_len * head_dim * sizeof(float) +
+         (size_t)batch_heads * seq_len * sizeof(float);
 }
 
 int flb200_attention_backward_supported(int64_t seq_len, int64_t head_dim, int dtype) {
@@ -334,10 +395,14 @@ int flb200_attention_backward(const void* q, const void* k, const void* v, const
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
     configured[dev] = true;
   }
-  FLB200_CUDA_CHECK(cudaMemsetAsync(workspace, 0, need, st));
+  const size_t acc_bytes = (size_t)rows * 64 * sizeof(float);
+  FLB200_CUDA_CHECK(cudaMemsetAsync(workspace, 0, acc_bytes, st));
+  float* dsum = reinterpret_cast<float*>(static_cast<char*>(workspace) + acc_bytes);
+  attention_dsum_kernel<<<(unsigned)((rows * 8 + 255) / 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(grad_o), dsum, rows);
+  FLB200_AFTER_LAUNCH("attention_dsum");
   AttnArgs a{};
-  a.o = static_cast<const __nv_bfloat16*>(o);
-  a.d_o = static_cast<const __nv_bfloat16*>(grad_o);
+  a.dsum = dsum;
   a.lse = lse;
   a.dq_acc = static_cast<float*>(workspace);
   a.dk = static_cast<__nv_bfloat16*>(grad_k);
