@@ -71,6 +71,12 @@ SIGNATURES = {
     "flb200_conv2d_output_dims": (C.c_int, [P(Conv2dDesc), P(i32), P(i32)]),
     "flb200_conv2d_workspace_bytes": (sz, [P(Conv2dDesc), C.c_int]),
     "flb200_conv2d_forward": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, vp]),
+    "flb200_conv2d_stats_bytes": (sz, [P(Conv2dDesc), P(i64)]),
+    "flb200_conv2d_forward_stats": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, vp, sz, vp, vp]),
+    "flb200_batchnorm_from_stats_workspace_bytes": (sz, [P(BatchnormDesc), i64]),
+    "flb200_batchnorm_forward_from_stats": (C.c_int, [P(BatchnormDesc), vp, vp, C.c_int, vp, i64, vp,
+                                                      vp, vp, vp, vp, vp, f64, f64, vp, vp, vp, sz,
+                                                      vp]),
     "flb200_conv2d_backward_data": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, sz, vp]),
     "flb200_conv2d_backward_filter_bias": (C.c_int, [P(Conv2dDesc), vp, vp, vp, vp, vp, sz, vp]),
     "flb200_conv2d_cache_bytes": (sz, [P(Conv2dDesc), C.c_int]),

@@ -23,6 +23,8 @@ from .extension import (AutogradPayload, B200AutogradExtension, RNNGradData, is_
 _ext: Optional[B200AutogradExtension] = None
 
 
+# FLB200_CONV_STATS=0: batch-norm always runs its own statistics pass
+CONV_STATS_ON = os.environ.get("FLB200_CONV_STATS", "1") != "0"
 # FLB200_FUSED_ATTENTION=0: attention() runs the operator chain (matmul, softmax, matmul)
 FUSED_ATTENTION_OFF = os.environ.get("FLB200_FUSED_ATTENTION", "1") == "0"
 
@@ -135,14 +137,20 @@ class Variable:
 
 # ------------------------------------------------------------------ functions
 def conv2d(x: Variable, w: Variable, b: Optional[Variable], sx=1, sy=1, px=0, py=0, dx=1, dy=1,
-           groups=1, channels_last_out: Optional[bool] = None) -> Variable:
+           groups=1, channels_last_out: Optional[bool] = None, stats: bool = False) -> Variable:
     """fl::conv2d (Functions.cpp:1327-1452).  channels_last_out=True: the output is stored
-    channels-last although the input is in fl's order (a network's first convolution)."""
+    channels-last although the input is in fl's order (a network's first convolution).
+    stats=True (a convolution that feeds a training-mode batch-norm over its channels, the
+    pairing of flashlight/pkg/vision/models/Resnet.cpp:67-121): where the library can, the
+    per-channel sums of the output are taken in the convolution's epilogue and travel with the
+    result (`conv_stats`); batchnorm() / batchnorm_add_relu() then skip their statistics pass."""
     ext = extension()
     args = (sx, sy, px, py, dx, dy, groups)
     payload = AutogradPayload()
     bt = b.tensor if b is not None else None
-    y = ext.conv2d(x.tensor, w.tensor, bt, *args, payload, channels_last_out=channels_last_out)
+    sums: Optional[list] = [] if (stats and CONV_STATS_ON) else None
+    y = ext.conv2d(x.tensor, w.tensor, bt, *args, payload, channels_last_out=channels_last_out,
+                   stats_out=sums)
     xt, wt = x.tensor, w.tensor
 
     def grad_func(inputs, gy):
@@ -157,7 +165,19 @@ def conv2d(x: Variable, w: Variable, b: Optional[Variable], sx=1, sy=1, px=0, py
             if need_b:
                 inputs[2].addGrad(gb.reshape(bt.shape))
 
-    return Variable(y, False, [x, w] + ([b] if b is not None else []), grad_func)
+    out = Variable(y, False, [x, w] + ([b] if b is not None else []), grad_func)
+    if sums:
+        out.conv_stats = sums[0]
+    return out
+
+
+def _conv_stats(x: Variable, axes: Sequence[int], train: bool):
+    """What a producing convolution attached to x, if it is the statistics this batch-norm
+    needs (training mode, per channel of an image batch)."""
+    st = getattr(x, "conv_stats", None)
+    if st is None or not train or list(axes) != [2] or x.tensor.dim() != 4:
+        return None
+    return st
 
 
 def pool2d(x: Variable, wx, wy, sx, sy, px, py, mode=L.POOL_MAX) -> Variable:
@@ -183,7 +203,8 @@ def batchnorm(x: Variable, weight: Optional[Variable], bias: Optional[Variable],
     wt = weight.tensor if weight is not None else None
     bt = bias.tensor if bias is not None else None
     y, save_mean, save_var = ext.batchnorm(x.tensor, wt, bt, running_mean, running_var, axes, train,
-                                           momentum, epsilon, None, relu=relu)
+                                           momentum, epsilon, None, relu=relu,
+                                           conv_stats=_conv_stats(x, axes, train))
     xt = x.tensor
     ins = [x] + ([weight] if weight is not None else []) + ([bias] if bias is not None else [])
 
@@ -218,8 +239,9 @@ def batchnorm_add_relu(x: Variable, addend: Variable, weight: Optional[Variable]
     wt = weight.tensor if weight is not None else None
     bt = bias.tensor if bias is not None else None
     xt = x.tensor
-    y, mask, save_mean, save_var = ext.batchnormAddRelu(xt, addend.tensor, wt, bt, running_mean,
-                                                        running_var, axes, train, momentum, epsilon)
+    y, mask, save_mean, save_var = ext.batchnormAddRelu(
+        xt, addend.tensor, wt, bt, running_mean, running_var, axes, train, momentum, epsilon,
+        conv_stats=_conv_stats(x, axes, train))
     ins = [x, addend] + ([weight] if weight is not None else []) + ([bias] if bias is not None else [])
 
     def grad_func2(inputs, ga, gb):

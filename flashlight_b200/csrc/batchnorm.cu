@@ -475,6 +475,42 @@ __global__ void bn_stats_finalize_kernel(const float2* __restrict__ partial, int
   }
 }
 
+// The same from the statistics matrix a convolution's epilogue wrote for x (EpiStats,
+// tc_kernel.cuh): `partial` holds the column sums of its [groups][2 * channels] rows in the
+// making — sums of x in columns [0, channels), sums of x^2 in [channels, 2 * channels).
+__global__ void bn_stats_finalize_matrix_kernel(const float2* __restrict__ partial, int splits,
+                                                long long channels, double count,
+                                                const float* __restrict__ weight, double eps,
+                                                double momentum, float* __restrict__ running_mean,
+                                                float* __restrict__ running_var,
+                                                float* __restrict__ save_mean,
+                                                float* __restrict__ save_invstd,
+                                                float* __restrict__ scale) {
+  const long long c = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (c >= channels) return;  // whole warps only
+  double s = 0.0, q = 0.0;
+  for (int i = lane; i < splits; i += 32) {
+    s += (double)partial[c * splits + i].x;
+    q += (double)partial[(channels + c) * splits + i].x;
+  }
+  s = warp_sum(s);
+  q = warp_sum(q);
+  if (lane != 0) return;
+  const double mean = s / count;
+  double var = q / count - mean * mean;
+  if (var < 0.0) var = 0.0;
+  const double invstd = 1.0 / sqrt(var + eps);
+  save_mean[c] = (float)mean;
+  save_invstd[c] = (float)invstd;
+  scale[c] = bn_scale((float)invstd, weight, c);
+  if (running_mean) running_mean[c] = (float)((1.0 - momentum) * running_mean[c] + momentum * mean);
+  if (running_var) {
+    const double unbiased = count > 1.0 ? var * count / (count - 1.0) : var;
+    running_var[c] = (float)((1.0 - momentum) * running_var[c] + momentum * unbiased);
+  }
+}
+
 __global__ void affine_bwd_finalize_kernel(const float2* __restrict__ partial, int splits,
                                            long long channels, float* __restrict__ grad_weight,
                                            float* __restrict__ grad_bias) {
@@ -807,11 +843,14 @@ static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
                                   const float* weight, const float* bias, float* running_mean,
                                   float* running_var, float* save_mean, float* save_invstd,
                                   int train, double momentum, double epsilon, void* y,
-                                  void* workspace, size_t workspace_bytes, void* stream) {
+                                  void* workspace, size_t workspace_bytes, void* stream,
+                                  const float* stats = nullptr, long long stat_groups = 0) {
   FLB200_REQUIRE(d, "batchnorm_forward: null descriptor");
   if (int st = check_geo("batchnorm_forward", d->outer, d->channels, d->inner)) return st;
   FLB200_REQUIRE(x && y, "batchnorm_forward: null tensor");
-  const size_t need = flb200_batchnorm_workspace_bytes(d);
+  const size_t base_need = flb200_batchnorm_workspace_bytes(d);
+  const size_t need =
+      base_need + (stats ? channel_partial_bytes(stat_groups, 2 * d->channels, 1) : 0);
   if (!workspace || workspace_bytes < need)
     return fail(FLB200_WORKSPACE_TOO_SMALL, "batchnorm_forward: workspace %zu < %zu",
                 workspace_bytes, need);
@@ -825,16 +864,29 @@ static int batchnorm_forward_impl(bool relu, const void* addend, uint8_t* mask,
   const float* mean_ptr;
   if (train) {
     FLB200_REQUIRE(save_mean && save_invstd, "batchnorm_forward: training needs save_mean/save_invstd");
-    int splits = 0;
-    StatsF sf{static_cast<const float*>(x), d->inner, d->dtype};
-    FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_forward",
-                          rc = (launch_reduce<T, 1>("batchnorm_stats", x, nullptr, partial,
-                                                    d->outer, C, d->inner, sf, &splits, st)));
-    if (rc) return rc;
-    bn_stats_finalize_kernel<<<fin_grid(C), kFinThreads, 0, st>>>(
-        partial, splits, C, (double)d->outer * (double)d->inner, x, d->inner, d->dtype, weight,
-        epsilon, momentum, running_mean, running_var, save_mean, save_invstd, scale);
-    FLB200_AFTER_LAUNCH("batchnorm_stats_finalize");
+    if (stats) {
+      // the producer of x took the sums in its epilogue: reduce its small matrix instead of x
+      float2* p2 = reinterpret_cast<float2*>(ws + base_need);
+      int splits = 0;
+      rc = launch_reduce<float, 1>("batchnorm_stats_matrix", stats, nullptr, p2, stat_groups,
+                                   2 * C, 1, SumF{}, &splits, st);
+      if (rc) return rc;
+      bn_stats_finalize_matrix_kernel<<<fin_grid(C), kFinThreads, 0, st>>>(
+          p2, splits, C, (double)d->outer * (double)d->inner, weight, epsilon, momentum,
+          running_mean, running_var, save_mean, save_invstd, scale);
+      FLB200_AFTER_LAUNCH("batchnorm_stats_finalize_matrix");
+    } else {
+      int splits = 0;
+      StatsF sf{static_cast<const float*>(x), d->inner, d->dtype};
+      FLB200_DISPATCH_DTYPE(d->dtype, "batchnorm_forward",
+                            rc = (launch_reduce<T, 1>("batchnorm_stats", x, nullptr, partial,
+                                                      d->outer, C, d->inner, sf, &splits, st)));
+      if (rc) return rc;
+      bn_stats_finalize_kernel<<<fin_grid(C), kFinThreads, 0, st>>>(
+          partial, splits, C, (double)d->outer * (double)d->inner, x, d->inner, d->dtype, weight,
+          epsilon, momentum, running_mean, running_var, save_mean, save_invstd, scale);
+      FLB200_AFTER_LAUNCH("batchnorm_stats_finalize");
+    }
     mean_ptr = save_mean;
   } else {
     FLB200_REQUIRE(running_mean && running_var,
@@ -921,6 +973,36 @@ int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void
   return batchnorm_forward_impl(true, addend, mask, d, x, weight, bias, running_mean, running_var,
                                 save_mean, save_invstd, train, momentum, epsilon, y, workspace,
                                 workspace_bytes, stream);
+}
+
+size_t flb200_batchnorm_from_stats_workspace_bytes(const flb200_batchnorm_desc* d,
+                                                   int64_t groups) {
+  if (!d || groups < 1) return 0;
+  const size_t base = flb200_batchnorm_workspace_bytes(d);
+  return base == 0 ? 0 : base + channel_partial_bytes(groups, 2 * d->channels, 1);
+}
+
+int flb200_batchnorm_forward_from_stats(const flb200_batchnorm_desc* d, const void* x,
+                                        const void* addend, int relu, const float* stats,
+                                        int64_t groups, const float* weight, const float* bias,
+                                        float* running_mean, float* running_var,
+                                        float* save_mean, float* save_invstd, double momentum,
+                                        double epsilon, void* y, uint8_t* mask, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+  FLB200_REQUIRE(d && stats && groups >= 1, "batchnorm_forward_from_stats: null argument");
+  FLB200_REQUIRE(d->dtype == FLB200_F32 && aligned16(stats) && d->channels % 4 == 0,
+                 "batchnorm_forward_from_stats: f32 tensors, channels a multiple of 4");
+  if (addend) {
+    FLB200_REQUIRE(mask, "batchnorm_forward_from_stats: the add + relu form writes a mask");
+    if ((d->inner < 2 && d->channels % 8 != 0) || !aligned16(x) || !aligned16(addend) ||
+        !aligned16(y))
+      return fail(FLB200_UNSUPPORTED,
+                  "batchnorm_forward_from_stats: the add + relu form needs 16-byte aligned "
+                  "tensors, in a spatial layout or channels-last with a multiple of 8 channels");
+  }
+  return batchnorm_forward_impl(addend != nullptr || relu != 0, addend, mask, d, x, weight, bias,
+                                running_mean, running_var, save_mean, save_invstd, 1, momentum,
+                                epsilon, y, workspace, workspace_bytes, stream, stats, groups);
 }
 
 // tail_mask != null: grad_y / tail_gb are the join's two incoming gradients (tail_gb may be

@@ -423,6 +423,41 @@ int flb200_conv2d_forward_cached(const flb200_conv2d_desc* d, const void* x, con
                           workspace_bytes, st);
 }
 
+size_t flb200_conv2d_stats_bytes(const flb200_conv2d_desc* d, int64_t* groups) {
+  ConvGeo g;
+  if (groups) *groups = 0;
+  if (make_conv_geo("conv2d_stats_bytes", d, &g)) return 0;
+  if (d->math_mode == FLB200_MATH_STRICT_F32 || d->dtype != FLB200_F32) return 0;
+  const long long n = tc_conv_stats_groups(g);
+  if (n == 0 || !tc_conv_supported(g, 0, tc_conv_workspace_bytes(g, 0))) return 0;
+  if (groups) *groups = n;
+  // CTA pairs may write one phantom tile (four all-zero rows) past the last real one
+  return (size_t)(n + 4) * 2 * g.Cout * sizeof(float);
+}
+
+int flb200_conv2d_forward_stats(const flb200_conv2d_desc* d, const void* x, const void* w,
+                                const void* bias, void* y, float* stats, size_t stats_bytes,
+                                void* workspace, size_t workspace_bytes,
+                                flb200_conv2d_cache* cache, void* stream) {
+  ConvGeo g;
+  if (int st = make_conv_geo("conv2d_forward_stats", d, &g)) return st;
+  FLB200_REQUIRE(x && w && y && stats, "conv2d_forward_stats: null tensor");
+  const size_t need = flb200_conv2d_stats_bytes(d, nullptr);
+  if (need == 0 || !tc_operands_aligned(x, w, y, bias, workspace) || !aligned16(stats) ||
+      !tc_conv_supported(g, 0, workspace_bytes))
+    return fail(FLB200_UNSUPPORTED,
+                "conv2d_forward_stats: needs a tensor-core route with a channels-last fp32 output "
+                "of a multiple of 32 channels, 16-byte aligned tensors and the forward workspace");
+  if (stats_bytes < need)
+    return fail(FLB200_WORKSPACE_TOO_SMALL, "conv2d_forward_stats: statistics buffer %zu < %zu",
+                stats_bytes, need);
+  ConvStats cs{stats};
+  tc::X3Scope x3(d->math_mode == FLB200_MATH_F32X3);
+  return tc_conv_forward(g, static_cast<const float*>(x), static_cast<const float*>(w),
+                         static_cast<const float*>(bias), static_cast<float*>(y), workspace,
+                         workspace_bytes, as_stream(stream), cache, &cs);
+}
+
 int flb200_conv2d_backward_data(const flb200_conv2d_desc* d, const void* grad_y, const void* w,
                                 void* grad_x, void* workspace, size_t workspace_bytes,
                                 void* stream) {

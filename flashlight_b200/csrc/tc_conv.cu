@@ -262,9 +262,17 @@ bool tc_conv_supported(const ConvGeo& g, int which, size_t workspace_bytes) {
   return workspace_bytes >= tc_conv_workspace_bytes(g, which);
 }
 
+long long tc_conv_stats_groups(const ConvGeo& g) {
+  if (!g.y_cl || g.Cout % 32 != 0) return 0;
+  if (cl_1x1(g)) return 4 * (((long long)g.N * g.HW + tc::kBM - 1) / tc::kBM);
+  if (direct_1x1(g)) return 0;
+  if (patch_conv_supported(g) || window_conv_supported(g)) return patch_conv_stats_groups(g);
+  return 0;
+}
+
 int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias, float* y,
-                    void* ws, size_t ws_bytes, cudaStream_t st,
-    flb200_conv2d_cache* cache) {
+                    void* ws, size_t ws_bytes, cudaStream_t st, flb200_conv2d_cache* cache,
+                    const ConvStats* stats) {
   CUtensorMap ma, mb;
   tc::EpiloguePlan ep{};
   ep.out = y;
@@ -279,9 +287,12 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
       return rc;
     ep.m_stride = g.Cout;
     ep.n_stride = 1;
+    ep.stats = stats ? stats->matrix : nullptr;
     return tc::run(ma, mb, plan_k_major(2), plan_k_major(2), ep, M, g.Cout, k_iters, 1, nullptr, 0,
                    st);
   }
+  if (stats && tc_conv_stats_groups(g) == 0)
+    return fail(FLB200_UNSUPPORTED, "conv2d_forward: this route takes no output statistics");
   if (direct_1x1(g)) {
     if (int rc = map3d(&ma, x, g.HW, g.C, g.N, g.HW, (long long)g.C * g.HW, 32, true)) return rc;
     // a K-major B tile is one box of all the tile's rows, or of half of them on CTA pairs
@@ -295,8 +306,10 @@ int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const floa
     return tc::run(ma, mb, pa, pb, ep, g.HW, g.Cout, (g.C + tc::kBK - 1) / tc::kBK, g.N, nullptr, 0,
                    st);
   }
-  if (patch_conv_supported(g)) return patch_conv_forward(g, x, w, bias, y, ws, ws_bytes, st, cache);
-  if (window_conv_supported(g)) return window_conv_forward(g, x, w, bias, y, ws, ws_bytes, st, cache);
+  if (patch_conv_supported(g))
+    return patch_conv_forward(g, x, w, bias, y, ws, ws_bytes, st, cache, stats);
+  if (window_conv_supported(g))
+    return window_conv_forward(g, x, w, bias, y, ws, ws_bytes, st, cache, stats);
   const GeneralSizes s = general_sizes(g);
   char* base = static_cast<char*>(ws);
   float* col = reinterpret_cast<float*>(base);

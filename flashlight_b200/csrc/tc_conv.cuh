@@ -26,9 +26,18 @@ size_t tc_conv_workspace_bytes(const ConvGeo& g, int which);
 // Size of the channels-last copy of x (which 0) or grad_y (which 1) that can be kept between
 // the calls of one convolution; 0 for routes that make no such copy.
 size_t tc_conv_cache_bytes(const ConvGeo& g, int which);
+// Per-channel statistics of the output, taken in the forward pass's epilogue (EpiStats,
+// tc_kernel.cuh): `matrix` receives tc_conv_stats_groups(g) rows of 2 * Cout floats whose column
+// sums are, per output channel, the sum and the sum of squares of y.
+struct ConvStats {
+  float* matrix;
+};
+// Number of rows the forward pass of this geometry writes, 0 where it cannot (output not stored
+// channels-last, Cout not a multiple of 32, or a route without the staged epilogue).
+long long tc_conv_stats_groups(const ConvGeo& g);
 int tc_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias, float* y,
                     void* ws, size_t ws_bytes, cudaStream_t st,
-    flb200_conv2d_cache* cache = nullptr);
+                    flb200_conv2d_cache* cache = nullptr, const ConvStats* stats = nullptr);
 int tc_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx, void* ws,
                           size_t ws_bytes, cudaStream_t st,
     flb200_conv2d_cache* cache = nullptr);
@@ -41,9 +50,10 @@ int tc_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, f
 bool patch_conv_supported(const ConvGeo& g);
 size_t patch_conv_workspace_bytes(const ConvGeo& g, int which);
 size_t patch_conv_cache_bytes(const ConvGeo& g, int which);
+long long patch_conv_stats_groups(const ConvGeo& g);
 int patch_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
                        float* y, void* ws, size_t ws_bytes, cudaStream_t st,
-    flb200_conv2d_cache* cache = nullptr);
+                       flb200_conv2d_cache* cache = nullptr, const ConvStats* stats = nullptr);
 int patch_conv_backward_data(const ConvGeo& g, const float* gy, const float* w, float* gx,
                              void* ws, size_t ws_bytes, cudaStream_t st,
     flb200_conv2d_cache* cache = nullptr);
@@ -59,7 +69,7 @@ size_t window_conv_workspace_bytes(const ConvGeo& g, int which);
 size_t window_conv_cache_bytes(const ConvGeo& g, int which);
 int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
                         float* y, void* ws, size_t ws_bytes, cudaStream_t st,
-    flb200_conv2d_cache* cache = nullptr);
+                        flb200_conv2d_cache* cache = nullptr, const ConvStats* stats = nullptr);
 int window_conv_backward_filter(const ConvGeo& g, const float* gy, const float* x, float* gw,
                                 void* ws, size_t ws_bytes, cudaStream_t st,
     flb200_conv2d_cache* cache = nullptr);

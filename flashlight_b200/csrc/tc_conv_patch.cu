@@ -279,6 +279,7 @@ struct PatchArgs {
   float* out;
   const float* bias;
   int out_H, out_W, out_C, oh_mul, ow_mul, fill_cell, out_cl;
+  float* stats;  // EpiStats matrix of the output (forward only) or null
 };
 int filter_box_rows(int bn) { return patch_uses_pairs(bn) ? bn / 2 : bn; }
 
@@ -300,6 +301,7 @@ int run_patch(const CUtensorMap& ma, const CUtensorMap& mb, const PatchArgs& a, 
   p.oh_mul = a.oh_mul; p.ow_mul = a.ow_mul;
   p.fill_cell = a.fill_cell;
   p.out_cl = a.out_cl;
+  p.stats = a.stats;
   p.tiles_n = (p.n_out + BN - 1) / BN;
   const long long m_tiles = (long long)p.tiles_q * p.tiles_p * p.tiles_b;
   FLB200_REQUIRE(a.ncls >= 1 && a.ncls <= tc::kMaxPatchClasses, "patch conv: bad class count");
@@ -509,9 +511,17 @@ size_t patch_conv_cache_bytes(const ConvGeo& g, int which) {
   return g.y_cl ? 0 : up256((size_t)g.N * g.HoWo * up4(g.Cout) * 4);
 }
 
+// rows of the statistics matrix: four per pixel patch (one per 32-row quarter of a tile)
+long long patch_conv_stats_groups(const ConvGeo& g0) {
+  const ConvGeo g = patch_conv_supported(g0) ? sampled_geo(g0) : g0;
+  const Patch pt = pick_patch(g.Wo, g.Ho, g.N);
+  return 4LL * ((g.Wo + pt.QW - 1) / pt.QW) * ((g.Ho + pt.PH - 1) / pt.PH) *
+         ((g.N + pt.NB - 1) / pt.NB);
+}
+
 int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const float* bias,
                        float* y, void* ws, size_t ws_bytes, cudaStream_t st,
-                       flb200_conv2d_cache* cache) {
+                       flb200_conv2d_cache* cache, const ConvStats* stats) {
   (void)ws_bytes;
   const ConvGeo g = sampled_geo(g0);
   const int cp = up4(g.C);
@@ -543,6 +553,7 @@ int patch_conv_forward(const ConvGeo& g0, const float* x, const float* w, const 
   a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
   a.oh_mul = 1; a.ow_mul = 1;
   a.out_cl = g.y_cl;
+  a.stats = stats && g.y_cl ? stats->matrix : nullptr;
   const int bn = tc::pick_bn(g.Cout);
   CUtensorMap ma, mb;
   if (int rc = nhwc_map(&ma, xt, g.C, cp, g.W, g.H, g.N, a.patch.QW, a.patch.PH, a.patch.NB, g.sx,
@@ -747,7 +758,7 @@ size_t window_conv_cache_bytes(const ConvGeo& g, int which) {
 
 int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const float* bias,
                         float* y, void* ws, size_t ws_bytes, cudaStream_t st,
-    flb200_conv2d_cache* cache) {
+                        flb200_conv2d_cache* cache, const ConvStats* stats) {
   (void)ws_bytes;
   const WindowGeo wg = window_geo(g);
   char* base = static_cast<char*>(ws);
@@ -782,6 +793,7 @@ int window_conv_forward(const ConvGeo& g, const float* x, const float* w, const 
   a.out_H = g.Ho; a.out_W = g.Wo; a.out_C = g.Cout;
   a.oh_mul = 1; a.ow_mul = 1;
   a.out_cl = g.y_cl;
+  a.stats = stats && g.y_cl ? stats->matrix : nullptr;
   return run_patch_any(bn, ma, mb, a, st);
 }
 

@@ -232,7 +232,8 @@ int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, con
   // an MN-major bf16 B tile is made of 64-column boxes: no narrower tile than one box
   if (bf16 && pb.mn_major && L.bn < 64) L.bn = 64;
   // split-K partials are written with 16-byte vectors: an unaligned workspace is not used
-  if (L.splits > 1 && (!ws || !aligned16(ws) || ws_bytes < L.workspace_bytes)) {
+  // (nor are the column statistics of the output taken from partial sums)
+  if (L.splits > 1 && (!ws || !aligned16(ws) || ws_bytes < L.workspace_bytes || ep.stats)) {
     L.splits = 1;
     L.iters_per_split = (int)k_iters;
   }

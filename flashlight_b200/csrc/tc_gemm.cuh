@@ -70,6 +70,8 @@ struct EpiloguePlan {
   const float* bias_n;  // added per column (may be null)
   float alpha, beta;
   int out_bf16;         // `out` points at __nv_bfloat16 (offsets are in elements either way)
+  float* stats;         // EpiStats matrix [ceil(M / 128) * 4][2 * N] (tc_kernel.cuh) or null:
+                        // per-column sums and sums of squares of a row-major fp32 output
 };
 
 struct Launch {

@@ -70,6 +70,36 @@ __device__ __forceinline__ float4 epi_stage_read(const float* stage, int lane, i
   return reinterpret_cast<const float4*>(stage)[r * 8 + (q ^ (r & 7))];
 }
 
+// Batch-norm statistics of a convolution's output taken from its accumulators: while a warp
+// stores its 32 x 32 chunk through the staging tile, every lane adds up the values (and their
+// squares) it holds — 4 channels of 8 rows — and two shuffles complete the sums over the
+// chunk's 32 rows; lanes 0..7 then write them, 128 contiguous bytes each for sums and squares,
+// into row `group` of a [groups][2 * channels] matrix (sums first, then squares).  Its column
+// sums are the per-channel totals; no atomics, so the result does not depend on timing.
+struct EpiStats {
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = make_float4(0.f, 0.f, 0.f, 0.f);
+  __device__ __forceinline__ void add(const float4& v) {
+    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    q.x = fmaf(v.x, v.x, q.x); q.y = fmaf(v.y, v.y, q.y);
+    q.z = fmaf(v.z, v.z, q.z); q.w = fmaf(v.w, v.w, q.w);
+  }
+  __device__ __forceinline__ void flush(float* stats, long long group, int channels, int c0,
+                                        int lane) {
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+      s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
+      s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
+      q.x += __shfl_xor_sync(0xffffffffu, q.x, o); q.y += __shfl_xor_sync(0xffffffffu, q.y, o);
+      q.z += __shfl_xor_sync(0xffffffffu, q.z, o); q.w += __shfl_xor_sync(0xffffffffu, q.w, o);
+    }
+    if (lane < 8) {
+      float* row = stats + group * (2LL * channels) + c0 + 4 * lane;
+      *reinterpret_cast<float4*>(row) = s;
+      *reinterpret_cast<float4*>(row + channels) = q;
+    }
+  }
+};
+
 // X3 = 1: every stage also holds the low-order tiles of the 3xTF32 split (see the kernel).
 template <int BN, int STAGES, int X3 = 0>
 struct SmemLayout {
@@ -568,12 +598,18 @@ struct GemmProblem {
         for (int j = 0; j < 32; ++j) w[j] = scale * v[j];
         epi_stage_write(stage, lane, w);
         const int m_first = m - lane;  // first row of this warp
+        EpiStats acc;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const int mr = m_first + 4 * k + (lane >> 3);
           const float4 val = epi_stage_read(stage, lane, k);
-          if (mr < M) *reinterpret_cast<float4*>(base + (long long)mr * ld + nb + 4 * (lane & 7)) = val;
+          if (mr < M) {
+            *reinterpret_cast<float4*>(base + (long long)mr * ld + nb + 4 * (lane & 7)) = val;
+            if (ep.stats) acc.add(val);
+          }
         }
+        if (ep.stats && splits == 1)
+          acc.flush(ep.stats, (long long)(t.m0 >> 7) * 4 + (row >> 5), N, nb, lane);
         __syncwarp();  // the tile is rewritten by the next chunk
         return;
       }

@@ -72,6 +72,7 @@ struct PatchConvProblem {
   int oh_mul, ow_mul;
   int fill_cell;  // see store()
   int out_cl;     // output stored channels-last: out[img][oh][ow][co]
+  float* stats;   // EpiStats matrix [pixel tiles * 4][2 * n_out] (tc_kernel.cuh), or null
 
   struct Tile { int q0, p0, b0, n0, c; };
   struct LoadState { int i, j, cc, aw, ah, wtap, c; };
@@ -177,12 +178,21 @@ struct PatchConvProblem {
       float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
       if (bias) bq = *reinterpret_cast<const float4*>(bias + nb + 4 * (lane & 7));
       const int r_first = row - lane;
+      EpiStats acc;
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
         float* dst = cl_row(t, r_first + 4 * k + (lane >> 3));
         float4 val = epi_stage_read(stage, lane, k);
         val.x += bq.x; val.y += bq.y; val.z += bq.z; val.w += bq.w;
-        if (dst) *reinterpret_cast<float4*>(dst + nb + 4 * (lane & 7)) = val;
+        if (dst) {
+          *reinterpret_cast<float4*>(dst + nb + 4 * (lane & 7)) = val;
+          if (stats) acc.add(val);
+        }
+      }
+      if (stats) {
+        const long long tile_m = ((long long)(t.b0 >> (7 - qw_shift - ph_shift)) * tiles_p +
+                                  (t.p0 >> ph_shift)) * tiles_q + (t.q0 >> qw_shift);
+        acc.flush(stats, tile_m * 4 + (row >> 5), n_out, nb, lane);
       }
       __syncwarp();
       return;

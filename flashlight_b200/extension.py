@@ -317,9 +317,12 @@ class B200AutogradExtension:
         return payload.data
 
     def conv2d(self, input, weights, bias, sx, sy, px, py, dx, dy, groups, payload=None,
-               channels_last_out: Optional[bool] = None):
+               channels_last_out: Optional[bool] = None, stats_out: Optional[list] = None):
         """channels_last_out=True on an input in fl's order: the output (and from there the whole
-        network) is stored channels-last; a channels-last input always gives such an output."""
+        network) is stored channels-last; a channels-last input always gives such an output.
+        stats_out: a list that receives (matrix, groups) — the batch-norm statistics of the result,
+        taken in the convolution's epilogue (flb200_conv2d_forward_stats), for
+        batchnorm(..., conv_stats=...) — where the library can do that; it stays empty otherwise."""
         d = self._conv_desc(input, weights, sx, sy, px, py, dx, dy, groups, channels_last_out)
         wo, ho = L.i32(), L.i32()
         L.check(L.lib.flb200_conv2d_output_dims(C.byref(d), C.byref(wo), C.byref(ho)))
@@ -331,6 +334,17 @@ class B200AutogradExtension:
         cache = self._conv_cache(d, payload, input)
         if cache is not None:
             cache.bind_x(input)
+        if stats_out is not None:
+            groups = L.i64()
+            sbytes = L.lib.flb200_conv2d_stats_bytes(C.byref(d), C.byref(groups))
+            if sbytes and all(t is None or t.data_ptr() % 16 == 0
+                              for t in (input, weights, bias, out, ws)):
+                stats = torch.empty(sbytes // 4, dtype=torch.float32, device=input.device)
+                L.check(L.lib.flb200_conv2d_forward_stats(
+                    C.byref(d), ptr(input), ptr(weights), ptr(bias), ptr(out), ptr(stats), sbytes,
+                    ptr(ws), nbytes, cache.ref() if cache is not None else None, stream_handle()))
+                stats_out.append((stats, groups.value))
+                return out
         L.check(L.lib.flb200_conv2d_forward_cached(
             C.byref(d), ptr(input), ptr(weights), ptr(bias), ptr(out), ptr(ws), nbytes,
             cache.ref() if cache is not None else None, stream_handle()))
@@ -427,7 +441,7 @@ class B200AutogradExtension:
         return d
 
     def batchnorm(self, input, weight, bias, runningMean, runningVar, axes, train, momentum,
-                  epsilon, payload=None, relu=False):
+                  epsilon, payload=None, relu=False, conv_stats=None):
         """Returns (output, saveMean, saveVar).  saveVar holds 1/sqrt(var + eps).
         runningMean / runningVar are updated in place when given.  relu=True returns
         relu(batchnorm(x)) from the same two passes (pair it with batchnormReluBackward)."""
@@ -446,6 +460,16 @@ class B200AutogradExtension:
             save_var = torch.empty(d.channels, dtype=torch.float32, device=input.device)
         nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
         ws = workspace(nbytes, input)
+        if conv_stats is not None and train:
+            # statistics from what the producing convolution took: no pass over x for them
+            stats, groups = conv_stats
+            nbytes = L.lib.flb200_batchnorm_from_stats_workspace_bytes(C.byref(d), groups)
+            ws = workspace(nbytes, input)
+            L.check(L.lib.flb200_batchnorm_forward_from_stats(
+                C.byref(d), ptr(input), None, 1 if relu else 0, ptr(stats), groups, ptr(weight),
+                ptr(bias), ptr(runningMean), ptr(runningVar), ptr(save_mean), ptr(save_var),
+                float(momentum), float(epsilon), ptr(out), None, ptr(ws), nbytes, stream_handle()))
+            return out, save_mean, save_var
         forward = L.lib.flb200_batchnorm_relu_forward if relu else L.lib.flb200_batchnorm_forward
         L.check(forward(
             C.byref(d), ptr(input), ptr(weight), ptr(bias), ptr(runningMean), ptr(runningVar),
@@ -477,7 +501,7 @@ class B200AutogradExtension:
                 and input.data_ptr() % 16 == 0 and addend.data_ptr() % 16 == 0)
 
     def batchnormAddRelu(self, input, addend, weight, bias, runningMean, runningVar, axes, train,
-                         momentum, epsilon, payload=None):
+                         momentum, epsilon, payload=None, conv_stats=None):
         """relu(batchnorm(input) + addend) with the predicate's bit mask: returns
         (output, mask, saveMean, saveVar).  Check batchnormAddReluSupported first."""
         d = self._bn_desc(input, axes)
@@ -492,6 +516,15 @@ class B200AutogradExtension:
             save_var = torch.empty(d.channels, dtype=torch.float32, device=input.device)
         nbytes = L.lib.flb200_batchnorm_workspace_bytes(C.byref(d))
         ws = workspace(nbytes, input)
+        if conv_stats is not None and train:
+            stats, groups = conv_stats
+            nbytes = L.lib.flb200_batchnorm_from_stats_workspace_bytes(C.byref(d), groups)
+            ws = workspace(nbytes, input)
+            L.check(L.lib.flb200_batchnorm_forward_from_stats(
+                C.byref(d), ptr(input), ptr(addend), 1, ptr(stats), groups, ptr(weight), ptr(bias),
+                ptr(runningMean), ptr(runningVar), ptr(save_mean), ptr(save_var), float(momentum),
+                float(epsilon), ptr(out), ptr(mask), ptr(ws), nbytes, stream_handle()))
+            return out, mask, save_mean, save_var
         L.check(L.lib.flb200_batchnorm_add_relu_forward(
             C.byref(d), ptr(input), ptr(addend), ptr(weight), ptr(bias), ptr(runningMean),
             ptr(runningVar), ptr(save_mean), ptr(save_var), 1 if train else 0, float(momentum),

@@ -79,9 +79,12 @@ class Conv2D(Module):
     fan-in kW*kH*Cin/groups, bias U(+-sqrt(1/fan_in))."""
 
     def __init__(self, n_in, n_out, wx, wy, sx=1, sy=1, px=0, py=0, dx=1, dy=1, bias=True, groups=1,
-                 gen=None, device="cuda", channels_last_out=None):
+                 gen=None, device="cuda", channels_last_out=None, stats=False):
         super().__init__()
         self.cfg = (n_in, n_out, wx, wy, sx, sy, px, py, dx, dy, groups)
+        # True where a batch-norm over the channels follows: the convolution's epilogue takes
+        # the batch-norm's statistics (autograd.conv2d)
+        self.stats = stats
         # True on a network's first convolution: its output, and with it every activation
         # downstream, is stored channels-last (see extension.py)
         self.channels_last_out = channels_last_out
@@ -98,7 +101,7 @@ class Conv2D(Module):
         py = derive_padding(H, wy, sy, py, dy)
         b = self.params[1] if len(self.params) > 1 else None
         return A.conv2d(x, self.params[0], b, sx, sy, px, py, dx, dy, groups,
-                        channels_last_out=self.channels_last_out)
+                        channels_last_out=self.channels_last_out, stats=self.stats)
 
 
 class Linear(Module):

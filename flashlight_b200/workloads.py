@@ -45,7 +45,8 @@ class Bottleneck(nn.Module):
     def __init__(self, in_c, planes, stride, gen, device):
         super().__init__()
         out_c = planes * 4
-        mk = lambda i, o, k, s: nn.Conv2D(i, o, k, k, s, s, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device)
+        mk = lambda i, o, k, s: nn.Conv2D(i, o, k, k, s, s, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device,
+                                         stats=True)  # every convolution here feeds a batch-norm
         self.c1, self.b1 = mk(in_c, planes, 1, 1), nn.BatchNorm(2, planes, gen=gen, device=device)
         self.c2, self.b2 = mk(planes, planes, 3, stride), nn.BatchNorm(2, planes, gen=gen, device=device)
         self.c3, self.b3 = mk(planes, out_c, 1, 1), nn.BatchNorm(2, out_c, gen=gen, device=device)
@@ -102,7 +103,7 @@ def resnet50(seed: int = 1234, device: str = "cuda", blocks=(3, 4, 6, 3), classe
         channels_last = CHANNELS_LAST
     m = nn.Sequential()
     m.add(nn.Conv2D(3, width, 7, 7, 2, 2, nn.SAME, nn.SAME, 1, 1, False, 1, gen, device,
-                    channels_last_out=True if channels_last else None))
+                    channels_last_out=True if channels_last else None, stats=True))
     if FUSE_BATCHNORM_RELU:
         m.add(nn.BatchNormReLU(2, width, gen=gen, device=device))
     else:

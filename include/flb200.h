@@ -166,6 +166,21 @@ int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const
                                               flb200_conv2d_cache* cache, void* stream);
 
 /* ------------------------------------------------------- pool2d (a5, a8) */
+/* Forward convolution that also takes the batch-norm statistics of its output while the
+ * accumulators are stored — the conv + batch-norm pairing of
+ * flashlight/pkg/vision/models/Resnet.cpp:67-121: `stats` receives a matrix of `groups` rows of
+ * 2 * Cout floats (flb200_conv2d_stats_bytes gives its size and the row count) whose column sums
+ * are, per output channel, the sum of y ([0, Cout)) and the sum of y^2 ([Cout, 2 Cout)) — one row
+ * per 32 output pixels, written without atomics, so results do not depend on timing.
+ * flb200_batchnorm_forward_from_stats reduces that small matrix instead of reading y again.
+ * Tensor-core modes, fp32, channels-last output, Cout a multiple of 32; elsewhere
+ * flb200_conv2d_stats_bytes returns 0.  The workspace is that of flb200_conv2d_forward. */
+size_t flb200_conv2d_stats_bytes(const flb200_conv2d_desc* d, int64_t* groups);
+int flb200_conv2d_forward_stats(const flb200_conv2d_desc* d, const void* x, const void* w,
+                                const void* bias, void* y, float* stats, size_t stats_bytes,
+                                void* workspace, size_t workspace_bytes,
+                                flb200_conv2d_cache* cache, void* stream);
+
 typedef struct flb200_pool2d_desc {
   int32_t W, H, C, N;
   int32_t wx, wy, sx, sy, px, py;
@@ -258,6 +273,19 @@ int flb200_batchnorm_add_relu_forward(const flb200_batchnorm_desc* d, const void
                                       float* save_invstd, int train, double momentum,
                                       double epsilon, void* y, uint8_t* mask, void* workspace,
                                       size_t workspace_bytes, void* stream);
+/* Training-mode batch-norm forward whose statistics come from the matrix a convolution wrote for
+ * x (flb200_conv2d_forward_stats: `groups` rows of 2 * channels floats) instead of a pass over x.
+ * addend != NULL: the relu(batchnorm(x) + addend) form (mask required); else relu != 0:
+ * relu(batchnorm(x)); else the plain operator.  Everything else as in the functions above;
+ * workspace: flb200_batchnorm_from_stats_workspace_bytes. */
+size_t flb200_batchnorm_from_stats_workspace_bytes(const flb200_batchnorm_desc* d, int64_t groups);
+int flb200_batchnorm_forward_from_stats(const flb200_batchnorm_desc* d, const void* x,
+                                        const void* addend, int relu, const float* stats,
+                                        int64_t groups, const float* weight, const float* bias,
+                                        float* running_mean, float* running_var,
+                                        float* save_mean, float* save_invstd, double momentum,
+                                        double epsilon, void* y, uint8_t* mask, void* workspace,
+                                        size_t workspace_bytes, void* stream);
 /* Gradient of flb200_batchnorm_add_relu_forward given the gradients of its output's consumers
  * (grad_y_b may be NULL): grad_sum = mask ? grad_y_a + grad_y_b : 0 is written (the addend's
  * gradient) while the first batch-norm pass reduces it, then grad_x / grad_weight / grad_bias

@@ -268,3 +268,71 @@ def test_resnet_step_both_layouts(L, mode, loss_tol, grad_tol, channels_last):
             assert err <= grad_tol, f"parameter {i} {tuple(wg.shape)}: gradient error {err:.3e}"
     finally:
         A.set_math_mode(L.MATH_STRICT_F32)
+
+
+# ------------------------------------------------------------- statistics in the conv epilogue
+@pytest.mark.parametrize("case", [
+    (8, 64, 14, 14, 256, 1, 1, 0),      # channels-last 1 x 1 (GEMM route), expand
+    (5, 256, 7, 7, 64, 1, 1, 0),        # ragged last row tile
+    (8, 64, 14, 14, 64, 3, 1, 1),       # patch route
+    (6, 128, 15, 15, 128, 3, 2, 1),     # strided, patches that overhang the image
+    (4, 3, 32, 32, 64, 7, 2, 3),        # first layer: row-window route, fl-order input
+    (33, 128, 7, 7, 512, 1, 1, 0),      # wide output on CTA pairs, odd tile count
+])
+def test_conv_forward_statistics_match_the_output(case):
+    """flb200_conv2d_forward_stats: the column sums of the matrix written in the epilogue are the
+    per-channel sums of the tensor the same call wrote, and the batch-norm built on them equals the stand-alone one."""
+    from flashlight_b200 import _lib as L
+    from flashlight_b200.extension import B200AutogradExtension
+    N, Cc, H, W, Co, k, s, p = case
+    ext = B200AutogradExtension(math_mode=L.MATH_TF32)
+    x = randn(N, Cc, H, W, seed=110).cuda()
+    first = Cc <= 4
+    if not first:
+        x = x.contiguous(memory_format=torch.channels_last)
+    w = (randn(Co, Cc, k, k, seed=111) * (1.0 / (Cc * k * k) ** 0.5)).cuda()
+    args = (s, s, p, p, 1, 1, 1)
+    sums = []
+    y = ext.conv2d(x, w, None, *args, None, channels_last_out=True if first else None, stats_out=sums)
+    assert len(sums) == 1
+    matrix, groups = sums[0]
+    assert matrix.numel() >= groups * 2 * Co
+    totals = matrix[:groups * 2 * Co].view(groups, 2 * Co).double().sum(0)
+    y_plain = ext.conv2d(x, w, None, *args, None, channels_last_out=True if first else None)
+    assert torch.equal(y, y_plain)                       # same kernels, same result
+    want_s = y.double().sum(dim=(0, 2, 3))
+    want_q = (y.double() ** 2).sum(dim=(0, 2, 3))
+    assert_close_scaled(totals[:Co], want_s, 2e-6, "sum of y")
+    assert_close_scaled(totals[Co:], want_q, 2e-6, "sum of y^2")
+    # batch-norm (+ relu) from the totals against the one that takes its own statistics
+    g, b = (randn(Co, seed=112) * 0.3 + 1.0).cuda(), randn(Co, seed=113).cuda()
+    rm0, rv0 = torch.zeros(Co).cuda(), torch.ones(Co).cuda()
+    rm1, rv1 = rm0.clone(), rv0.clone()
+    o0, m0, v0 = ext.batchnorm(y, g, b, rm0, rv0, [2], True, 0.1, 1e-5, relu=True)
+    o1, m1, v1 = ext.batchnorm(y, g, b, rm1, rv1, [2], True, 0.1, 1e-5, relu=True,
+                               conv_stats=sums[0])
+    assert_close_scaled(m1, m0, 2e-5, "mean from sums")  # means are ~1e-2 of the values summed
+    assert_close_scaled(v1, v0, 2e-5, "inverse std from sums")
+    assert_close_scaled(rv1, rv0, 2e-5, "running variance from sums")
+    assert_close_scaled(o1, o0, 5e-5, "batch-norm + relu from sums")
+    if Co % 8 == 0:
+        short = randn(*y.shape, seed=114).cuda().contiguous(memory_format=torch.channels_last)
+        a0 = ext.batchnormAddRelu(y, short, g, b, None, None, [2], True, 0.1, 1e-5)
+        a1 = ext.batchnormAddRelu(y, short, g, b, None, None, [2], True, 0.1, 1e-5,
+                                  conv_stats=sums[0])
+        assert_close_scaled(a1[0], a0[0], 5e-5, "batch-norm + add + relu from sums")
+
+
+def test_conv_statistics_are_declined_where_not_built():
+    from flashlight_b200 import _lib as L
+    from flashlight_b200.extension import B200AutogradExtension
+    x = randn(2, 32, 8, 8, seed=115).cuda()
+    w = randn(48, 32, 3, 3, seed=116).cuda()
+    for ext, xin in ((B200AutogradExtension(math_mode=L.MATH_TF32), x),                       # fl order
+                     (B200AutogradExtension(math_mode=L.MATH_STRICT_F32),
+                      x.contiguous(memory_format=torch.channels_last)),                        # fp32 FMA
+                     (B200AutogradExtension(math_mode=L.MATH_TF32),
+                      x.contiguous(memory_format=torch.channels_last))):                       # Cout % 32
+        sums = []
+        y = ext.conv2d(xin, w, None, 1, 1, 1, 1, 1, 1, 1, None, stats_out=sums)
+        assert sums == [] and y.shape == (2, 48, 8, 8)
