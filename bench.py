@@ -502,8 +502,10 @@ def run_gpu_arm(args) -> None:
     reducer = None
     if world > 1:
         D.allReduceParameters(model)
-        reducer = D.BucketReducer(model.parameters(), 1.0 / world, args.bucket_mb << 20)
-        D.distributeModuleGrads(model, reducer)
+        if args.sync != "none":  # "none": a diagnostic without gradient synchronisation
+            reducer = D.BucketReducer(model.parameters(), 1.0 / world, args.bucket_mb << 20,
+                                      overlap=args.sync == "overlap")
+            D.distributeModuleGrads(model, reducer)
 
     B = args.batch
     g = torch.Generator().manual_seed(1000 + rank)
@@ -709,6 +711,7 @@ def run_gpu_arm(args) -> None:
             math_mode, "f32"), "data": "synthetic",
         "config": {"workload": WORKLOAD, "batch_per_gpu": B, "global_batch": B * world,
                    "parallelism": f"dp{world}", "math_mode": args.math,
+                   "gradient_sync": args.sync if world > 1 else "none",
                    "l2": "inputs and activations larger than L2 (no flush needed)",
                    "step": "zeroGrad + forward + loss + backward" +
                            (" + bucketed NCCL all-reduce" if world > 1 else ""),
@@ -744,6 +747,10 @@ def main() -> None:
     ap.add_argument("--batch", type=int, default=256, help="images per GPU per step")
     ap.add_argument("--math", default=os.environ.get("FLB200_MATH", "tf32"), choices=["tf32", "strict", "f32x3"])
     ap.add_argument("--bucket-mb", type=int, default=32)
+    ap.add_argument("--sync", default="overlap", choices=["overlap", "end", "none"],
+                    help="N > 1: gradient all-reduce overlapped with backward (the product), "
+                         "all at the end of backward, or none (the last two are diagnostics of "
+                         "what the overlap hides and costs)")
     ap.add_argument("--cpu-batch", type=int, default=32)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-side-legs", action="store_true",

@@ -223,8 +223,12 @@ class BucketReducer(Reducer):
     averaged gradient for every parameter of a reduced bucket."""
 
     def __init__(self, params: Sequence, scale: Optional[float] = None,
-                 bucket_bytes: int = DEFAULT_BUCKET_BYTES):
+                 bucket_bytes: int = DEFAULT_BUCKET_BYTES, overlap: bool = True):
         self.params = list(params)
+        # overlap=False: nothing is reduced before finalize() (same collectives, same order, no
+        # overlap with the backward pass) — the comparison point for what the overlap costs the
+        # compute kernels and what it hides
+        self.overlap = overlap
         self.scale = (1.0 / getWorldSize()) if scale is None else scale
         self.slot = {}
         self.buckets: List[torch.Tensor] = []
@@ -263,6 +267,8 @@ class BucketReducer(Reducer):
         return self.buckets[bi][off:off + n].view(p.tensor.shape)
 
     def _fire_ready(self) -> None:
+        if not self.overlap:
+            return
         while self.next_bucket < len(self.buckets) and self.remaining[self.next_bucket] == 0:
             allReduce(self.buckets[self.next_bucket], self.scale, True)
             self.next_bucket += 1
