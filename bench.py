@@ -472,8 +472,12 @@ CONV_KERNEL = "tc_persistent_kernel (conv2d + conv2dBackwardData + conv2dBackwar
 # dram__bytes_read.sum + dram__bytes_write.sum of every convolution kernel of one step at
 # batch 256 in TF32 mode, from one ncu capture of
 # `python -m flashlight_b200.opbench --suite resnet50_step_convs --batch 256 --math tf32`
-# (summary under profiles/); algorithmic bytes of the same calls: 66.2e9.
+# (summary under profiles/); algorithmic bytes of the same calls: 66.2e9.  With activations in
+# fl's order the layout copies add to it; stored channels-last (`--channels-last`, the default of
+# the workload) the kernels move less than the algorithmic figure (consecutive calls of one
+# layer find part of their operands in L2).
 CONV_DRAM_BYTES_PER_STEP_B256 = 75.2e9
+CONV_DRAM_BYTES_PER_STEP_B256_CHANNELS_LAST = 63.8e9
 FP32_FMA_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12
 
 
@@ -658,9 +662,10 @@ def run_gpu_arm(args) -> None:
             peak = peaks["bf16_tflops_sustained"] / 2
             src = f"{peaks['source']} bf16 sustained / 2 (tf32 rate)"
             traffic = None
-            # (the capture was taken with fl-order activations; not re-used for channels-last)
-            if top == CONV_KERNEL and B == 256 and not workloads.CHANNELS_LAST:
-                traffic = CONV_DRAM_BYTES_PER_STEP_B256 * args.steps / max(tv["calls"], 1)
+            if top == CONV_KERNEL and B == 256:
+                per_step = (CONV_DRAM_BYTES_PER_STEP_B256_CHANNELS_LAST if workloads.CHANNELS_LAST
+                            else CONV_DRAM_BYTES_PER_STEP_B256)
+                traffic = per_step * args.steps / max(tv["calls"], 1)
         else:
             peak = FP32_FMA_TFLOPS
             src = "nominal fp32 FMA rate (148 SMs x 128 lanes x 2 x 1.965 GHz): strict mode uses no tensor cores"

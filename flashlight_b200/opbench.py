@@ -232,11 +232,14 @@ def suite_resnet50_step_convs(batch, math):
     algo_bytes = 0
     for (ci, hw, co, k, s, p), count in zip(RESNET50_CONVS, RESNET50_COUNTS):
         x = torch.randn(batch, ci, hw, hw, device="cuda")
+        first = CHANNELS_LAST and ci <= 4  # the network's first layer: x in fl's order
+        if not first:
+            x = images(x)
         w = torch.randn(co, ci, k, k, device="cuda") * (1.0 / (ci * k * k) ** 0.5)
         args = (s, s, p, p, 1, 1, 1)
         for _ in range(count):
             payload = AutogradPayload()
-            y = ext.conv2d(x, w, None, *args, payload)
+            y = ext.conv2d(x, w, None, *args, payload, True if first else None)
             g = torch.ones_like(y)
             n_pass = 2
             if ci != 3:
@@ -249,6 +252,7 @@ def suite_resnet50_step_convs(batch, math):
             del y, g, payload
         torch.cuda.synchronize()
     print(json.dumps({"suite": "resnet50_step_convs", "batch": batch, "math": math,
+                      "layout": "channels_last" if CHANNELS_LAST else "fl",
                       "conv_calls": int(sum(RESNET50_COUNTS) * 3 - 1), "flops": flops,
                       "algorithmic_bytes": algo_bytes}), flush=True)
 
