@@ -140,6 +140,10 @@ SIGNATURES = {
     "flb200_tanh_forward": (C.c_int, [vp, vp, i64, C.c_int, vp]),
     "flb200_tanh_backward": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_dropout_apply": (C.c_int, [vp, vp, vp, f32, i64, C.c_int, vp]),
+    "flb200_layernorm_forward": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, f64, C.c_int, vp]),
+    "flb200_layernorm_backward_workspace_bytes": (sz, [i64, i64]),
+    "flb200_layernorm_backward": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, i64, i64, C.c_int, vp, sz,
+                                            vp]),
     "flb200_bernoulli_mask": (C.c_int, [vp, i64, f32, C.c_uint64, C.c_uint64, C.c_int, vp]),
     "flb200_add": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
     "flb200_log_softmax_forward": (C.c_int, [vp, vp, i64, i64, C.c_int, vp]),

@@ -25,6 +25,8 @@ _ext: Optional[B200AutogradExtension] = None
 
 # FLB200_CONV_STATS=0: batch-norm always runs its own statistics pass
 CONV_STATS_ON = os.environ.get("FLB200_CONV_STATS", "1") != "0"
+# FLB200_FUSED_LAYERNORM=0: layernorm() declines, callers run normalisation + affine_rows
+LAYERNORM_FUSED_OFF = os.environ.get("FLB200_FUSED_LAYERNORM", "1") == "0"
 # FLB200_FUSED_ATTENTION=0: attention() runs the operator chain (matmul, softmax, matmul)
 FUSED_ATTENTION_OFF = os.environ.get("FLB200_FUSED_ATTENTION", "1") == "0"
 
@@ -601,6 +603,29 @@ def affine_rows(x: Variable, w: Variable, b: Variable) -> Variable:
             inputs[2].addGrad(gb.reshape(bt.shape))
 
     return Variable(y, False, [x, w, b], grad_func)
+
+
+def layernorm(x: Variable, w: Variable, b: Variable, eps: float = 1e-5) -> Variable:
+    """fl::LayerNorm over the last dimension (flashlight/fl/nn/modules/LayerNorm.cpp:66-128) as
+    one operator: a single forward kernel (a warp per row) that keeps x_hat and the rows' inverse
+    standard deviation, and a gradient of two kernels.  w and b are the fp32 parameters whatever
+    the activations' dtype.  Rows of more than 2048 features take the operator chain."""
+    xt, wt, bt = x.tensor, w.tensor, b.tensor
+    if xt.shape[-1] > 2048 or LAYERNORM_FUSED_OFF:
+        return None
+    y, xhat, invstd = F.layernorm(xt, wt, bt, eps)
+
+    def grad_func(inputs, gy):
+        need_p = inputs[1].isCalcGrad() or inputs[2].isCalcGrad()
+        gx, gw, gb = F.layernorm_backward(gy, xhat, wt, invstd, inputs[0].isCalcGrad(), need_p)
+        if inputs[0].isCalcGrad():
+            inputs[0].addGrad(gx.reshape(xt.shape))
+        if inputs[1].isCalcGrad():
+            inputs[1].addGrad(gw.reshape(wt.shape))
+        if inputs[2].isCalcGrad():
+            inputs[2].addGrad(gb.reshape(bt.shape))
+
+    return Variable(y.reshape(xt.shape), False, [x, w, b], grad_func)
 
 
 def embedding(table: Variable, ids: torch.Tensor) -> Variable:

@@ -763,7 +763,7 @@ int flb200_layernorm_affine_backward(const void* grad_y, const void* xhat, const
                                      int64_t rows, int64_t features, int dtype, void* workspace,
                                      size_t workspace_bytes, void* stream) {
   if (int st = check_geo("layernorm_affine_backward", rows, features, 1)) return st;
-  FLB200_REQUIRE(grad_y && xhat && weight, "layernorm_affine_backward: null pointer");
+  FLB200_REQUIRE(grad_y && xhat && (weight || !grad_xhat), "layernorm_affine_backward: null pointer");
   cudaStream_t st = as_stream(stream);
   int rc = FLB200_OK;
   if (grad_weight || grad_bias) {

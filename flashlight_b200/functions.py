@@ -151,6 +151,37 @@ def layernorm_affine(xhat, weight, bias):
     return y
 
 
+def layernorm(x, weight, bias, eps: float):
+    """fl::LayerNorm over the last dimension in one kernel: returns (y, xhat, invstd)."""
+    feat = x.shape[-1]
+    xc = x.contiguous()
+    rows = xc.numel() // feat
+    y, xhat = torch.empty_like(xc), torch.empty_like(xc)
+    invstd = torch.empty(rows, dtype=torch.float32, device=xc.device)
+    L.check(L.lib.flb200_layernorm_forward(ptr(xc), ptr(weight), ptr(bias), ptr(y), ptr(xhat), None,
+                                           ptr(invstd), rows, feat, float(eps), dtype_code(xc),
+                                           stream_handle()))
+    return y, xhat, invstd
+
+
+def layernorm_backward(grad_y, xhat, weight, invstd, need_input_grad=True, need_param_grads=True):
+    """Returns (grad_x, grad_weight, grad_bias); the parameter gradients are fp32."""
+    feat = xhat.shape[-1]
+    rows = xhat.numel() // feat
+    gy = grad_y.contiguous()
+    gx = torch.empty_like(xhat) if need_input_grad else None
+    gw = gb = None
+    if need_param_grads:
+        gw = torch.empty(feat, dtype=torch.float32, device=xhat.device)
+        gb = torch.empty(feat, dtype=torch.float32, device=xhat.device)
+    nbytes = L.lib.flb200_layernorm_backward_workspace_bytes(rows, feat)
+    ws = workspace(nbytes, xhat)
+    L.check(L.lib.flb200_layernorm_backward(ptr(gy), ptr(xhat), ptr(weight), ptr(invstd), ptr(gx),
+                                            ptr(gw), ptr(gb), rows, feat, dtype_code(xhat), ptr(ws),
+                                            nbytes, stream_handle()))
+    return gx, gw, gb
+
+
 def layernorm_affine_backward(grad_y, xhat, weight, need_input_grad=True, need_param_grads=True):
     """Returns (grad_xhat, grad_weight, grad_bias); the parameter gradients are fp32."""
     feat = xhat.shape[-1]

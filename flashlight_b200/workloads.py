@@ -272,7 +272,10 @@ class TransformerLM(nn.Module):
         return out + list(self.ln_f) + self.head.parameters()
 
     def _ln(self, x, wb):
-        return A.affine_rows(self.norm(x), wb[0], wb[1])
+        # one kernel forward, two backward; the operator chain (normalisation, then the affine
+        # part) where the fused operator declines
+        y = A.layernorm(x, wb[0], wb[1], 1e-6)
+        return y if y is not None else A.affine_rows(self.norm(x), wb[0], wb[1])
 
     def _lin(self, mod, x):
         w = A.cast(mod.params[0], self.compute_dtype)

@@ -380,6 +380,23 @@ int flb200_layernorm_affine_backward(const void* grad_y, const void* xhat, const
                                      int64_t rows, int64_t features, int dtype, void* workspace,
                                      size_t workspace_bytes, void* stream);
 
+/* fl::LayerNorm over rows of `features` elements as one operator each way
+ * (flashlight/fl/nn/modules/LayerNorm.cpp:66-128: batchnorm over the normalised axes, then
+ * tileAs(weight) * x_hat + tileAs(bias)): forward reads x once and writes y = x_hat * weight +
+ * bias and x_hat (kept for the gradient; NULL: not written) plus the rows' mean and inverse
+ * standard deviation (fp32, either may be NULL); weight / bias fp32 or NULL; features <= 2048.
+ * Backward: grad_x = invstd * (g - mean(g) - x_hat * mean(g * x_hat)) with g = grad_y * weight
+ * from one pass over grad_y and x_hat, and grad_weight = sum_rows grad_y * x_hat, grad_bias =
+ * sum_rows grad_y from a second one (any of the three outputs may be NULL). */
+int flb200_layernorm_forward(const void* x, const float* weight, const float* bias, void* y,
+                             void* xhat, float* mean, float* invstd, int64_t rows,
+                             int64_t features, double epsilon, int dtype, void* stream);
+size_t flb200_layernorm_backward_workspace_bytes(int64_t rows, int64_t features);
+int flb200_layernorm_backward(const void* grad_y, const void* xhat, const float* weight,
+                              const float* invstd, void* grad_x, float* grad_weight,
+                              float* grad_bias, int64_t rows, int64_t features, int dtype,
+                              void* workspace, size_t workspace_bytes, void* stream);
+
 /* y[o][c][i] = x[o][c][i] + bias[c] (tile + add, Functions.cpp:1270-1275). In place allowed. */
 int flb200_channel_bias_add(const void* x, const float* bias, void* y, int64_t outer,
                             int64_t channels, int64_t inner, int dtype, void* stream);

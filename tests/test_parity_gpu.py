@@ -280,6 +280,45 @@ def test_layernorm_affine(fx, rows, feat, dtype, tol):
     assert gx3 is None and torch.equal(gw3, gw)
 
 
+@pytest.mark.parametrize("rows,feat", [(7, 5), (33, 96), (64, 768), (5, 2048), (3, 1000)])
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, STRICT_TOL), (torch.bfloat16, 1.6e-2)])
+@pytest.mark.parametrize("affine", [True, False])
+def test_layernorm_fused(fx, rows, feat, dtype, tol, affine):
+    """fl::LayerNorm over the last dimension as one operator (flb200_layernorm_forward /
+    _backward) against the fp64 restatement of the reference's chain (oracle layer_norm) and its
+    autograd gradient."""
+    from tests.parity import assert_close_scaled
+    x = (randn(rows, feat, seed=50) * 1.7 + 0.4).to(dtype)
+    w = (randn(feat, seed=51) * 0.5 + 1.0) if affine else None
+    b = randn(feat, seed=52) if affine else None
+    gy = randn(rows, feat, seed=53).to(dtype)
+    xr = x.double().requires_grad_(True)
+    wr = w.double().requires_grad_(True) if affine else None
+    br = b.double().requires_grad_(True) if affine else None
+    want = R.layer_norm(xr, [0], 1e-5, wr, br)
+    want.backward(gy.double())
+    y, xhat, invstd = fx.layernorm(x.cuda(), w.cuda() if affine else None,
+                                   b.cuda() if affine else None, 1e-5)
+    assert y.dtype == dtype and invstd.dtype == torch.float32
+    check = assert_close if dtype == torch.float32 else assert_close_scaled
+    check(y.float() if dtype != torch.float32 else y, want.detach(), tol, "layernorm y")
+    gx, gw, gb = fx.layernorm_backward(gy.cuda(), xhat, w.cuda() if affine else None, invstd,
+                                       True, affine)
+    check(gx.float() if dtype != torch.float32 else gx, xr.grad, tol, "layernorm dx")
+    if affine:
+        ptol = STRICT_TOL if dtype == torch.float32 else 1.6e-2
+        assert_close_scaled(gw, wr.grad, ptol, "layernorm dgamma")
+        assert_close_scaled(gb, br.grad, ptol, "layernorm dbeta")
+
+
+def test_layernorm_fused_rejects_long_rows():
+    from flashlight_b200 import _lib as L
+    assert L.lib.flb200_layernorm_forward(None, None, None, None, None, None, None, 4, 4096, 1e-5,
+                                          L.F32, None) == L.INVALID_ARG
+    assert L.lib.flb200_layernorm_forward(None, None, None, None, None, None, None, 0, 16, 1e-5,
+                                          L.F32, None) == L.OK
+
+
 # ------------------------------------------------------------------- pool2d
 POOL_GEOS = [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1), (3, 2, 1, 2, 1, 0), (7, 7, 1, 1, 0, 0),
              (2, 2, 1, 1, 0, 0)]
