@@ -20,6 +20,7 @@ MATH_STRICT_F32, MATH_TF32, MATH_F32X3 = 0, 1, 2
 LAYOUT_NCHW, LAYOUT_NCHW_IN_NHWC_OUT, LAYOUT_NHWC = 0, 2, 3
 MATH_BY_NAME = {"strict": MATH_STRICT_F32, "tf32": MATH_TF32, "f32x3": MATH_F32X3}
 REDUCE_NONE, REDUCE_MEAN, REDUCE_SUM = 0, 1, 2
+ACT_NONE, ACT_GELU = 0, 1
 IDS_I32, IDS_I64 = 0, 1
 
 i32, i64, f32, f64, vp, sz = C.c_int32, C.c_int64, C.c_float, C.c_double, C.c_void_p, C.c_size_t
@@ -113,6 +114,8 @@ SIGNATURES = {
     "flb200_matmul": (C.c_int, [P(MatmulDesc), vp, vp, vp, vp, sz, vp]),
     "flb200_linear_workspace_bytes": (sz, [i64, i64, i64, C.c_int]),
     "flb200_linear_forward": (C.c_int, [i64, i64, i64, vp, vp, vp, vp, C.c_int, vp, sz, vp]),
+    "flb200_linear_bias_act_forward": (C.c_int, [i64, i64, i64, vp, vp, vp, vp, vp, C.c_int, C.c_int,
+                                                 C.c_int, vp, sz, vp]),
     "flb200_linear_backward_input": (C.c_int, [i64, i64, i64, vp, vp, vp, C.c_int, vp, sz, vp]),
     "flb200_linear_backward_weight": (C.c_int, [i64, i64, i64, vp, vp, vp, C.c_int, vp, sz, vp]),
     "flb200_channel_sum_workspace_bytes": (sz, [i64, i64, i64]),

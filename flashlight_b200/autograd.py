@@ -27,6 +27,8 @@ _ext: Optional[B200AutogradExtension] = None
 CONV_STATS_ON = os.environ.get("FLB200_CONV_STATS", "1") != "0"
 # FLB200_FUSED_LAYERNORM=0: layernorm() declines, callers run normalisation + affine_rows
 LAYERNORM_FUSED_OFF = os.environ.get("FLB200_FUSED_LAYERNORM", "1") == "0"
+# FLB200_FUSED_LINEAR=0: linear() runs contraction, bias and activation as separate kernels
+LINEAR_FUSED_ON = os.environ.get("FLB200_FUSED_LINEAR", "1") != "0"
 # FLB200_FUSED_ATTENTION=0: attention() runs the operator chain (matmul, softmax, matmul)
 FUSED_ATTENTION_OFF = os.environ.get("FLB200_FUSED_ATTENTION", "1") == "0"
 
@@ -316,19 +318,31 @@ def cast(x: Variable, dtype) -> Variable:
     return glue(x, lambda t: t.to(dtype), lambda g: g.to(src))
 
 
-def _linear_bf16(x: Variable, w: Variable, b: Optional[Variable]) -> Variable:
+def _linear_bf16(x: Variable, w: Variable, b: Optional[Variable], gelu: bool = False) -> Variable:
     """fl::linear on bf16 tensors: the three contractions go to flb200_matmul as strided views
-    (bf16 operands, fp32 accumulation); bias (fp32) through the channel kernels."""
+    (bf16 operands, fp32 accumulation); bias (fp32) and an optional gelu in the forward
+    contraction's epilogue where the library fuses them, else through the channel kernels."""
     xt, wt = x.tensor.contiguous(), w.tensor.contiguous()
     I, O = wt.shape
     rows = xt.numel() // I
-    y = F.matmul(xt, wt, m=rows, n=O, k=I, a_strides=(I, 1), b_strides=(O, 1))
-    y = y.reshape(tuple(xt.shape[:-1]) + (O,))
-    if b is not None:
-        F.channel_bias_add(y, b.tensor, rows, O, 1, out=y)
+    fused = None
+    if (b is not None or gelu) and LINEAR_FUSED_ON:
+        fused = F.linear_bias_act(xt, wt, b.tensor if b is not None else None, gelu)
+    if fused is not None:
+        y, pre = fused
+    else:
+        y = F.matmul(xt, wt, m=rows, n=O, k=I, a_strides=(I, 1), b_strides=(O, 1))
+        y = y.reshape(tuple(xt.shape[:-1]) + (O,))
+        if b is not None:
+            F.channel_bias_add(y, b.tensor, rows, O, 1, out=y)
+        pre = y
+        if gelu:
+            y = F.gelu(pre)
 
     def grad_func(inputs, gy):
         gy = gy.contiguous()
+        if gelu:
+            gy = F.gelu_backward(pre, gy)
         if inputs[0].isCalcGrad():   # dX (rows, I) = dY (rows, O) @ W^T (O, I)
             gx = F.matmul(gy, wt, m=rows, n=I, k=O, a_strides=(O, 1), b_strides=(1, O))
             inputs[0].addGrad(gx.reshape(xt.shape))
@@ -341,16 +355,27 @@ def _linear_bf16(x: Variable, w: Variable, b: Optional[Variable]) -> Variable:
     return Variable(y, False, [x, w] + ([b] if b is not None else []), grad_func)
 
 
-def linear(x: Variable, w: Variable, b: Optional[Variable]) -> Variable:
-    """fl::linear (Functions.cpp:1255-1309)."""
+def linear(x: Variable, w: Variable, b: Optional[Variable], gelu: bool = False) -> Variable:
+    """fl::linear (Functions.cpp:1255-1309).  gelu=True: gelu(linear(x)) as one operator (the
+    Linear + bias + GELU of a Transformer feed-forward block): bias and activation are applied
+    where the contraction stores its result, and the pre-activation is kept for the gradient."""
     if x.tensor.dtype == torch.bfloat16:
-        return _linear_bf16(x, w, b)
+        return _linear_bf16(x, w, b, gelu)
     mode = extension().math_mode
     bt = b.tensor if b is not None else None
-    y = F.linear(x.tensor, w.tensor, bt, math_mode=mode)
     xt, wt = x.tensor, w.tensor
+    fused = None
+    if (b is not None or gelu) and LINEAR_FUSED_ON and xt.dtype == torch.float32:
+        fused = F.linear_bias_act(xt, wt, bt, gelu, math_mode=mode)
+    if fused is not None:
+        y, pre = fused
+    else:
+        pre = F.linear(xt, wt, bt, math_mode=mode)
+        y = F.gelu(pre) if gelu else pre
 
     def grad_func(inputs, gy):
+        if gelu:
+            gy = F.gelu_backward(pre, gy)
         need_b = b is not None and inputs[2].isCalcGrad()
         gx, gw, gb = F.linear_backward(xt, wt, gy, need_b, inputs[0].isCalcGrad(),
                                        inputs[1].isCalcGrad(), math_mode=mode)

@@ -111,6 +111,33 @@ int flb200_linear_forward(int64_t O, int64_t I, int64_t cols, const void* weight
   return FLB200_OK;
 }
 
+int flb200_linear_bias_act_forward(int64_t O, int64_t I, int64_t cols, const void* weight,
+                                   const void* x, const float* bias, void* y, void* pre, int act,
+                                   int dtype, int math_mode, void* workspace,
+                                   size_t workspace_bytes, void* stream) {
+  FLB200_REQUIRE(act == FLB200_ACT_NONE || act == FLB200_ACT_GELU,
+                 "linear_bias_act_forward: unknown activation %d", act);
+  FLB200_REQUIRE(act != FLB200_ACT_NONE || pre == nullptr,
+                 "linear_bias_act_forward: a pre-activation copy needs an activation");
+  flb200_matmul_desc d = {};
+  d.m = cols; d.n = O; d.k = I; d.batch = 1;
+  d.a_row = I; d.a_col = 1;
+  d.b_row = O; d.b_col = 1;
+  d.c_row = O; d.c_col = 1;
+  d.alpha = 1.f; d.beta = 0.f;
+  d.dtype = dtype; d.math_mode = math_mode;
+  if (int st = check_desc(&d, x, weight, y)) return st;
+  if (cols == 0 || O == 0) return FLB200_OK;
+  if ((dtype != FLB200_BF16 && math_mode == FLB200_MATH_STRICT_F32) ||
+      !tc_gemm_supported(&d, x, weight, y) || (bias && !aligned16(bias)))
+    return fail(FLB200_UNSUPPORTED,
+                "linear_bias_act_forward: needs the tensor-core path (run linear, bias and "
+                "activation one by one)");
+  tc::X3Scope x3(dtype == FLB200_F32 && math_mode == FLB200_MATH_F32X3);
+  return tc_gemm_run(&d, x, weight, y, workspace, workspace_bytes, as_stream(stream), bias, act,
+                     pre);
+}
+
 int flb200_linear_backward_input(int64_t O, int64_t I, int64_t cols, const void* weight,
                                  const void* grad_y, void* grad_x, int math_mode, void* workspace,
                                  size_t workspace_bytes, void* stream) {

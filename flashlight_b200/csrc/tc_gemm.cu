@@ -233,7 +233,8 @@ int run(const CUtensorMap& ma, const CUtensorMap& mb, const OperandPlan& pa, con
   if (bf16 && pb.mn_major && L.bn < 64) L.bn = 64;
   // split-K partials are written with 16-byte vectors: an unaligned workspace is not used
   // (nor are the column statistics of the output taken from partial sums)
-  if (L.splits > 1 && (!ws || !aligned16(ws) || ws_bytes < L.workspace_bytes || ep.stats)) {
+  if (L.splits > 1 && (!ws || !aligned16(ws) || ws_bytes < L.workspace_bytes || ep.stats || ep.act ||
+                       ep.pre)) {
     L.splits = 1;
     L.iters_per_split = (int)k_iters;
   }
@@ -357,9 +358,15 @@ size_t tc_gemm_workspace_bytes(const flb200_matmul_desc* d) {
 }
 
 int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void* c, void* ws,
-                size_t ws_bytes, cudaStream_t st) {
+                size_t ws_bytes, cudaStream_t st, const float* bias_n, int act, void* pre) {
   const Prepared p = prepare(d, a, b, c);
   if (!p.ok) return fail(FLB200_UNSUPPORTED, "tc_gemm: layout not covered");
+  const bool fused = bias_n != nullptr || act != 0 || pre != nullptr;
+  if (fused && (p.swap || d->c_col != 1 || d->beta != 0.f || d->n % 32 != 0 || d->batch != 1 ||
+                (d->c_row & 7) != 0 || !aligned16(c) || (pre && !aligned16(pre))))
+    return fail(FLB200_UNSUPPORTED,
+                "tc_gemm: bias / activation are fused only into a row-major, 16-byte aligned "
+                "result of a multiple of 32 columns");
   const bool bf16 = d->dtype == FLB200_BF16;
   const long long kstage = bf16 ? 64 : tc::kBK;
   const long long k_iters = (d->k + kstage - 1) / kstage;
@@ -371,6 +378,9 @@ int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void*
   ep.alpha = d->alpha;
   ep.beta = d->beta;
   ep.z_stride = d->c_batch;
+  ep.bias_n = bias_n;
+  ep.act = act;
+  ep.pre = pre;
   long long M, N;
   if (!p.swap) {
     M = d->m; N = d->n;

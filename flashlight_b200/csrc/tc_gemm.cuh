@@ -12,8 +12,12 @@ namespace flb200 {
 // True when the tensor-core kernel covers this problem (layout, alignment, size).
 bool tc_gemm_supported(const flb200_matmul_desc* d, const void* a, const void* b, const void* c);
 size_t tc_gemm_workspace_bytes(const flb200_matmul_desc* d);
+// bias_n / act / pre: per-column bias, activation and pre-activation copy fused into the store
+// (EpiloguePlan); only for products whose result is stored row-major as the caller's C
+// (FLB200_UNSUPPORTED otherwise, so that the caller can run the operators one by one).
 int tc_gemm_run(const flb200_matmul_desc* d, const void* a, const void* b, void* c, void* ws,
-                size_t ws_bytes, cudaStream_t st);
+                size_t ws_bytes, cudaStream_t st, const float* bias_n = nullptr, int act = 0,
+                void* pre = nullptr);
 
 namespace tc {
 
@@ -70,6 +74,10 @@ struct EpiloguePlan {
   const float* bias_n;  // added per column (may be null)
   float alpha, beta;
   int out_bf16;         // `out` points at __nv_bfloat16 (offsets are in elements either way)
+  int act;              // 0 none, 1 GELU (tanh form): applied after alpha and the biases, on the
+                        // row-major fp32 (staged) and bf16 (vector) store paths only
+  void* pre;            // with act: where the value BEFORE the activation goes too (same type
+                        // and layout as `out`; what the activation's gradient needs), or null
   float* stats;         // EpiStats matrix [ceil(M / 128) * 4][2 * N] (tc_kernel.cuh) or null:
                         // per-column sums and sums of squares of a row-major fp32 output
 };

@@ -100,6 +100,12 @@ struct EpiStats {
   }
 };
 
+// gelu in the tanh form of flashlight/fl/autograd/Functions.cpp:1791-1796 (the constants of
+// flb200_gelu_forward)
+__device__ __forceinline__ float epi_gelu(float x) {
+  return 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
+}
+
 // X3 = 1: every stage also holds the low-order tiles of the 3xTF32 split (see the kernel).
 template <int BN, int STAGES, int X3 = 0>
 struct SmemLayout {
@@ -585,7 +591,7 @@ struct GemmProblem {
           ld = N;
         }
       } else if (!ep.out_bf16 && ep.beta == 0.f && ep.n_div == 0 && ep.m_div == 0 &&
-                 ep.n_stride == 1 && ep.bias_m == nullptr && ep.bias_n == nullptr &&
+                 ep.n_stride == 1 && ep.bias_m == nullptr &&
                  (ep.m_stride & 3) == 0 && ((ep.z_stride * t.z) & 3) == 0 &&
                  (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) {
         base = ep.out + (long long)t.z * ep.z_stride;
@@ -599,12 +605,25 @@ struct GemmProblem {
         epi_stage_write(stage, lane, w);
         const int m_first = m - lane;  // first row of this warp
         EpiStats acc;
+        const bool fused = splits == 1 && (ep.bias_n != nullptr || ep.act != 0);
+        float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (fused && ep.bias_n)
+          bq = *reinterpret_cast<const float4*>(ep.bias_n + nb + 4 * (lane & 7));
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const int mr = m_first + 4 * k + (lane >> 3);
-          const float4 val = epi_stage_read(stage, lane, k);
+          float4 val = epi_stage_read(stage, lane, k);
           if (mr < M) {
-            *reinterpret_cast<float4*>(base + (long long)mr * ld + nb + 4 * (lane & 7)) = val;
+            const long long off = (long long)mr * ld + nb + 4 * (lane & 7);
+            if (fused) {
+              val.x += bq.x; val.y += bq.y; val.z += bq.z; val.w += bq.w;
+              if (ep.act) {
+                if (ep.pre) *reinterpret_cast<float4*>(static_cast<float*>(ep.pre) + off) = val;
+                val = make_float4(epi_gelu(val.x), epi_gelu(val.y), epi_gelu(val.z),
+                                  epi_gelu(val.w));
+              }
+            }
+            *reinterpret_cast<float4*>(base + off) = val;
             if (ep.stats) acc.add(val);
           }
         }
@@ -635,16 +654,31 @@ struct GemmProblem {
     if (ep.out_bf16) {
       __nv_bfloat16* outb = reinterpret_cast<__nv_bfloat16*>(ep.out);
       if (ep.beta == 0.f && ep.n_div == 0 && ep.n_stride == 1 && nb + 32 <= N &&
-          ep.bias_n == nullptr && ((m_off + nb) & 7) == 0 &&
-          (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) {
+          ((m_off + nb) & 7) == 0 && (reinterpret_cast<uintptr_t>(ep.out) & 15) == 0) {
         uint4* dst = reinterpret_cast<uint4*>(outb + m_off + nb);
+        uint4* dpre = ep.act && ep.pre
+                          ? reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(ep.pre) + m_off + nb)
+                          : nullptr;
+        const float* bn = ep.bias_n ? ep.bias_n + nb : nullptr;
 #pragma unroll
         for (int j = 0; j < 32; j += 8) {
-          __nv_bfloat162 h[4];
+          float r[8];
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            h[q] = __floats2bfloat162_rn(ep.alpha * v[j + 2 * q] + bm,
-                                         ep.alpha * v[j + 2 * q + 1] + bm);
+          for (int q = 0; q < 8; ++q) r[q] = ep.alpha * v[j + q] + bm + (bn ? bn[j + q] : 0.f);
+          __nv_bfloat162 h[4];
+          if (ep.act) {
+            if (dpre) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(r[2 * q], r[2 * q + 1]);
+              dpre[j >> 3] = *reinterpret_cast<uint4*>(h);
+            }
+            // the activation sees the value the pre-activation tensor holds (rounded to bf16),
+            // as the unfused chain does
+#pragma unroll
+            for (int q = 0; q < 8; ++q) r[q] = epi_gelu(__bfloat162float(__float2bfloat16(r[q])));
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(r[2 * q], r[2 * q + 1]);
           dst[j >> 3] = *reinterpret_cast<uint4*>(h);
         }
         return;

@@ -222,6 +222,28 @@ def linear(x, weight, bias=None, math_mode: Optional[int] = None):
     return y
 
 
+def linear_bias_act(x, weight, bias, gelu: bool = False, math_mode: Optional[int] = None):
+    """y = act(x W + bias) in one kernel (flb200_linear_bias_act_forward): returns (y, pre) with
+    pre = x W + bias when gelu is on (None otherwise), or None where the tensor-core path does
+    not cover the call and the operators have to run one by one."""
+    mode = default_math_mode() if math_mode is None else math_mode
+    O, I, cols = _linear_dims(weight, x)
+    if O % 32 or not x.is_contiguous() or not weight.is_contiguous() or (
+            x.dtype == torch.float32 and mode == L.MATH_STRICT_F32):
+        return None
+    y = torch.empty(tuple(x.shape[:-1]) + (O,), dtype=x.dtype, device=x.device)
+    pre = torch.empty_like(y) if gelu else None
+    nbytes = L.lib.flb200_linear_workspace_bytes(O, I, cols, 0)
+    ws = workspace(nbytes, x)
+    st = L.lib.flb200_linear_bias_act_forward(O, I, cols, ptr(weight), ptr(x), ptr(bias), ptr(y),
+                                              ptr(pre), L.ACT_GELU if gelu else L.ACT_NONE,
+                                              dtype_code(x), mode, ptr(ws), nbytes, stream_handle())
+    if st == L.UNSUPPORTED:
+        return None
+    L.check(st)
+    return y, pre
+
+
 def linear_backward(x, weight, grad_y, has_bias: bool, need_input_grad=True, need_weight_grad=True,
                     math_mode: Optional[int] = None):
     """The linear gradFunc (Functions.cpp:1277-1305): returns (grad_x, grad_weight, grad_bias)."""

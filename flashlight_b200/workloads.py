@@ -277,9 +277,9 @@ class TransformerLM(nn.Module):
         y = A.layernorm(x, wb[0], wb[1], 1e-6)
         return y if y is not None else A.affine_rows(self.norm(x), wb[0], wb[1])
 
-    def _lin(self, mod, x):
+    def _lin(self, mod, x, gelu=False):
         w = A.cast(mod.params[0], self.compute_dtype)
-        return A.linear(x, w, mod.params[1])
+        return A.linear(x, w, mod.params[1], gelu=gelu)
 
     def _attention(self, x, blk, B, T, mask):
         d, h = self.d, self.heads
@@ -315,7 +315,7 @@ class TransformerLM(nn.Module):
         mask = None
         for blk in self.blocks:
             x = A.add(x, self._attention(self._ln(x, blk["ln1"]), blk, B, T, mask))
-            h = A.gelu(self._lin(blk["w1"], self._ln(x, blk["ln2"])))
+            h = self._lin(blk["w1"], self._ln(x, blk["ln2"]), gelu=True)  # Linear + bias + GELU
             x = A.add(x, self._lin(blk["w2"], h))
         scores = A.cast(self._lin(self.head, self._ln(x, self.ln_f)), torch.float32)
         return A.log_softmax_cross_entropy(scores, targets)

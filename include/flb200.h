@@ -332,6 +332,18 @@ size_t flb200_linear_workspace_bytes(int64_t O, int64_t I, int64_t cols, int whi
 int flb200_linear_forward(int64_t O, int64_t I, int64_t cols, const void* weight,
                           const void* x, const void* bias, void* y, int math_mode,
                           void* workspace, size_t workspace_bytes, void* stream);
+/* Linear + bias + activation in one kernel (Linear + bias + GELU of
+ * flashlight/pkg/vision/nn/VisionTransformer.cpp:101-110 and of the Transformer feed-forward
+ * block): y = act(x W + bias) with bias (fp32, may be NULL) and the activation applied where the
+ * accumulators are stored; `pre` (may be NULL) also receives x W + bias, which the activation's
+ * gradient needs.  dtype FLB200_F32 (tensor-core math modes) or FLB200_BF16; O a multiple of 32.
+ * FLB200_UNSUPPORTED where the tensor-core path does not cover the call: run flb200_linear_forward
+ * / flb200_matmul, the bias and the activation one by one. */
+enum { FLB200_ACT_NONE = 0, FLB200_ACT_GELU = 1 };
+int flb200_linear_bias_act_forward(int64_t O, int64_t I, int64_t cols, const void* weight,
+                                   const void* x, const float* bias, void* y, void* pre, int act,
+                                   int dtype, int math_mode, void* workspace,
+                                   size_t workspace_bytes, void* stream);
 int flb200_linear_backward_input(int64_t O, int64_t I, int64_t cols, const void* weight,
                                  const void* grad_y, void* grad_x, int math_mode,
                                  void* workspace, size_t workspace_bytes, void* stream);

@@ -417,3 +417,55 @@ def test_conv_gradients_pick_a_tensor_core_mode(L):
         assert launched >= 1                                     # now on the tensor cores
     finally:
         DynamicBenchmark.setBenchmarkMode(False)
+
+
+# ------------------------------------------------------------- Linear + bias + GELU
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-3), (torch.bfloat16, 1.6e-2)])
+@pytest.mark.parametrize("dims", [(96, 64, 200), (768, 3072, 512), (256, 160, 33)])
+@pytest.mark.parametrize("gelu", [False, True])
+def test_linear_bias_activation_fused(L, fx, dtype, tol, dims, gelu):
+    """flb200_linear_bias_act_forward: bias and gelu applied in the contraction's epilogue, the
+    pre-activation kept; against fp64 (the bf16 case from bf16-rounded operands), and the tape
+    operator's gradients against autograd of the same chain."""
+    from flashlight_b200 import autograd as A
+    I, O, rows = dims
+    x = randn(rows, I, seed=120).to(dtype)
+    w = (randn(I, O, seed=121) * (1.0 / I ** 0.5)).to(dtype)
+    b = randn(O, seed=122)
+    out = fx.linear_bias_act(x.cuda(), w.cuda(), b.cuda(), gelu, math_mode=L.MATH_TF32)
+    z = x.double() @ w.double() + b.double()
+    want = torch.nn.functional.gelu(z, approximate="tanh") if gelu else z
+    if out is None:
+        # few rows: the contraction runs transposed (C^T = B^T A^T), where nothing is fused;
+        # the tape operator below then takes the operators one by one
+        assert rows < 64
+    else:
+        y, pre = out
+        assert y.dtype == dtype
+        assert_close_scaled(y.float(), want, tol, "linear + bias (+ gelu)")
+        if gelu:
+            assert_close_scaled(pre.float(), z, tol, "pre-activation")
+        else:
+            assert pre is None
+    # the tape operator: fused forward, chain gradient
+    prev = A.extension().math_mode
+    A.set_math_mode(L.MATH_TF32)
+    try:
+        xv, wv, bv = (A.Variable(t.cuda(), True) for t in (x, w, b))
+        gy = randn(rows, O, seed=123).to(dtype)
+        A.linear(xv, wv, bv, gelu=gelu).backward(gy.cuda())
+    finally:
+        A.set_math_mode(prev)
+    xr, wr, br = (t.double().requires_grad_(True) for t in (x, w, b))
+    zz = xr @ wr + br
+    (torch.nn.functional.gelu(zz, approximate="tanh") if gelu else zz).backward(gy.double())
+    assert_close_scaled(xv.grad.float(), xr.grad, 2 * tol, "linear dx")
+    assert_close_scaled(wv.grad.float(), wr.grad, 2 * tol, "linear dw")
+    assert_close_scaled(bv.grad.float(), br.grad, 2 * tol, "linear db")
+
+
+def test_linear_bias_activation_declines_gracefully(L, fx):
+    x, w, b = randn(8, 16, seed=124).cuda(), randn(16, 24, seed=125).cuda(), randn(24, seed=126).cuda()
+    assert fx.linear_bias_act(x, w, b, True, math_mode=L.MATH_TF32) is None      # O % 32 != 0
+    x2, w2, b2 = randn(8, 16, seed=127).cuda(), randn(16, 32, seed=128).cuda(), randn(32, seed=129).cuda()
+    assert fx.linear_bias_act(x2, w2, b2, True, math_mode=L.MATH_STRICT_F32) is None  # fp32 FMA mode
