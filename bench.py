@@ -631,6 +631,29 @@ def run_gpu_arm(args) -> None:
     barrier()
     ms_e2e = f0.elapsed_time(f1)
 
+    # The product configuration takes the batch-norm statistics inside the forward convolutions'
+    # epilogues, so their time (and the roofline line below) includes that work.  One more short
+    # eager pass with the hand-over switched off times the contraction kernels on their own.
+    conv_alone = None
+    if world == 1 and A.CONV_STATS_ON and math_mode != L.MATH_STRICT_F32:
+        main_records, timer.records = timer.records, []
+        A.CONV_STATS_ON = False
+        try:
+            for _ in range(2):
+                step(x_dev, t_dev)
+            barrier()
+            timer.enabled = True
+            for _ in range(min(args.steps, 5)):
+                step(x_dev, t_dev)
+            barrier()
+            timer.enabled = False
+            alone = timer.summary()
+            conv_alone = {key: sum(alone[k][key] for k in CONV_OPS if k in alone)
+                          for key in ("ms", "flops")}
+        finally:
+            A.CONV_STATS_ON = True
+            timer.records = main_records
+
     if world > 1:
         tt = torch.tensor([ms_total, ms_e2e, ms_eager], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(tt, op=torch.distributed.ReduceOp.MAX)
@@ -679,6 +702,14 @@ def run_gpu_arm(args) -> None:
             floor = timer.floor_ms(CONV_OPS, peak, peaks["hbm_gbs"])
             roof["per_call_floor_ms"] = floor / args.steps
             roof["frac_of_per_call_floor"] = floor / tv["ms"]
+            if conv_alone and conv_alone["ms"] > 0:
+                a2 = conv_alone["flops"] / (conv_alone["ms"] * 1e-3) / 1e12
+                roof["includes"] = ("the batch-norm statistics of the forward convolutions' outputs, "
+                                    "taken in their epilogues (conv + batch-norm-statistics fusion)")
+                roof["contraction_only"] = {
+                    "achieved": a2, "frac": a2 / peak,
+                    "what": "the same convolution calls in a short extra eager pass with the "
+                            "statistics hand-over off (FLB200_CONV_STATS=0)"}
     else:
         achieved = tv["bytes"] / (tv["ms"] * 1e-3) / 1e9
         peak = peaks["hbm_gbs"]
