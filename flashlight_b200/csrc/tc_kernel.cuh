@@ -72,38 +72,48 @@ __device__ __forceinline__ float4 epi_stage_read(const float* stage, int lane, i
 
 // Batch-norm statistics of a convolution's output taken from its accumulators: while a warp
 // stores its 32 x 32 chunk through the staging tile, every lane adds up the values (and their
-// squares) it holds — 4 channels of 8 rows — and two shuffles complete the sums over the
-// chunk's 32 rows; lanes 0..7 then write them, 128 contiguous bytes each for sums and squares,
+// squares) it holds — 4 channels of 8 rows — and the four row groups are added through the
+// staging tile; lanes 0..7 then write them, 128 contiguous bytes each for sums and squares,
 // into row `group` of a [groups][2 * channels] matrix (sums first, then squares).  Its column
 // sums are the per-channel totals; no atomics, so the result does not depend on timing.
 struct EpiStats {
-  float4 s = make_float4(0.f, 0.f, 0.f, 0.f), q = make_float4(0.f, 0.f, 0.f, 0.f);
-  __device__ __forceinline__ void add(const float4& v) {
-    s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
-    q.x = fmaf(v.x, v.x, q.x); q.y = fmaf(v.y, v.y, q.y);
-    q.z = fmaf(v.z, v.z, q.z); q.w = fmaf(v.w, v.w, q.w);
+  float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f, q0 = 0.f, q1 = 0.f, q2 = 0.f, q3 = 0.f;
+  __device__ __forceinline__ void add(float4 v) {
+    s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
+    q0 = fmaf(v.x, v.x, q0); q1 = fmaf(v.y, v.y, q1);
+    q2 = fmaf(v.z, v.z, q2); q3 = fmaf(v.w, v.w, q3);
   }
+  // `stage`: the warp's staging tile, free again once every lane has read its values out of
+  // it (the caller's loop is done); the four row groups of a chunk (lane / 8) meet through it.
   __device__ __forceinline__ void flush(float* stats, long long group, int channels, int c0,
-                                        int lane) {
-#pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
-      s.x += __shfl_xor_sync(0xffffffffu, s.x, o); s.y += __shfl_xor_sync(0xffffffffu, s.y, o);
-      s.z += __shfl_xor_sync(0xffffffffu, s.z, o); s.w += __shfl_xor_sync(0xffffffffu, s.w, o);
-      q.x += __shfl_xor_sync(0xffffffffu, q.x, o); q.y += __shfl_xor_sync(0xffffffffu, q.y, o);
-      q.z += __shfl_xor_sync(0xffffffffu, q.z, o); q.w += __shfl_xor_sync(0xffffffffu, q.w, o);
-    }
+                                        int lane, float* stage) {
+    __syncwarp();
+    float4* slot = reinterpret_cast<float4*>(stage);
+    slot[2 * lane] = make_float4(s0, s1, s2, s3);
+    slot[2 * lane + 1] = make_float4(q0, q1, q2, q3);
+    __syncwarp();
     if (lane < 8) {
+#pragma unroll
+      for (int g = 1; g < 4; ++g) {
+        const float4 a = slot[2 * (lane + 8 * g)], b = slot[2 * (lane + 8 * g) + 1];
+        s0 += a.x; s1 += a.y; s2 += a.z; s3 += a.w;
+        q0 += b.x; q1 += b.y; q2 += b.z; q3 += b.w;
+      }
       float* row = stats + group * (2LL * channels) + c0 + 4 * lane;
-      *reinterpret_cast<float4*>(row) = s;
-      *reinterpret_cast<float4*>(row + channels) = q;
+      *reinterpret_cast<float4*>(row) = make_float4(s0, s1, s2, s3);
+      *reinterpret_cast<float4*>(row + channels) = make_float4(q0, q1, q2, q3);
     }
   }
 };
 
 // gelu in the tanh form of flashlight/fl/autograd/Functions.cpp:1791-1796 (the constants of
 // flb200_gelu_forward)
+// tanh(u) = 1 - 2 / (1 + exp(2u)) from the fast exponential: branch-free (no library call inside
+// the store loop of the contraction kernels), absolute error below 1e-6
 __device__ __forceinline__ float epi_gelu(float x) {
-  return 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x)));
+  const float u = 0.7978845608f * (x + 0.044715f * x * x * x);
+  const float t = 1.f - __fdividef(2.f, 1.f + __expf(2.f * u));
+  return 0.5f * x * (1.f + t);
 }
 
 // X3 = 1: every stage also holds the low-order tiles of the 3xTF32 split (see the kernel).
@@ -574,6 +584,38 @@ struct GemmProblem {
     return t.n0 + c0 < N;
   }
 
+  // Rows 4k + lane / 8 (k = 0..7) of the warp's staged 32 x 32 chunk to a row-major output,
+  // 16 bytes per lane.  MODE 0: the values as staged; 1: + bias_n; 2: + bias_n, then gelu, the
+  // pre-activation kept in ep.pre when that is set.  STATS: per-channel sums of the stored
+  // values into row `group` of ep.stats.
+  template <int MODE, bool STATS>
+  __device__ __forceinline__ void staged_rows(float* stage, int lane, int m_first, float* out_row,
+                                              long long ld, int nb, long long group) const {
+    float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (MODE != 0 && ep.bias_n)
+      bq = *reinterpret_cast<const float4*>(ep.bias_n + nb + 4 * (lane & 7));
+    float* pre_row = nullptr;
+    if (MODE == 2 && ep.pre)
+      pre_row = static_cast<float*>(ep.pre) + (out_row - ep.out);
+    EpiStats acc;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int mr = m_first + 4 * k + (lane >> 3);
+      float4 val = epi_stage_read(stage, lane, k);
+      if (MODE != 0) { val.x += bq.x; val.y += bq.y; val.z += bq.z; val.w += bq.w; }
+      if (mr < M) {
+        const long long off = (long long)mr * ld;
+        if (MODE == 2) {
+          if (pre_row) *reinterpret_cast<float4*>(pre_row + off) = val;
+          val = make_float4(epi_gelu(val.x), epi_gelu(val.y), epi_gelu(val.z), epi_gelu(val.w));
+        }
+        *reinterpret_cast<float4*>(out_row + off) = val;
+        if (STATS) acc.add(val);
+      }
+    }
+    if (STATS) acc.flush(ep.stats, group, N, nb, lane, stage);
+  }
+
   __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v,
                                         float* stage, int lane) const {
     const int m = t.m0 + row;
@@ -604,31 +646,22 @@ struct GemmProblem {
         for (int j = 0; j < 32; ++j) w[j] = scale * v[j];
         epi_stage_write(stage, lane, w);
         const int m_first = m - lane;  // first row of this warp
-        EpiStats acc;
+        // The flags are uniform across the grid: each combination has its own copy of the
+        // store loop, so the plain one stays eight loads followed by eight stores.
         const bool fused = splits == 1 && (ep.bias_n != nullptr || ep.act != 0);
-        float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (fused && ep.bias_n)
-          bq = *reinterpret_cast<const float4*>(ep.bias_n + nb + 4 * (lane & 7));
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const int mr = m_first + 4 * k + (lane >> 3);
-          float4 val = epi_stage_read(stage, lane, k);
-          if (mr < M) {
-            const long long off = (long long)mr * ld + nb + 4 * (lane & 7);
-            if (fused) {
-              val.x += bq.x; val.y += bq.y; val.z += bq.z; val.w += bq.w;
-              if (ep.act) {
-                if (ep.pre) *reinterpret_cast<float4*>(static_cast<float*>(ep.pre) + off) = val;
-                val = make_float4(epi_gelu(val.x), epi_gelu(val.y), epi_gelu(val.z),
-                                  epi_gelu(val.w));
-              }
-            }
-            *reinterpret_cast<float4*>(base + off) = val;
-            if (ep.stats) acc.add(val);
-          }
+        const bool stats = splits == 1 && ep.stats != nullptr;
+        float* out_row = base + nb + 4 * (lane & 7);
+        const long long group = (long long)(t.m0 >> 7) * 4 + (row >> 5);
+        if (!fused) {
+          if (!stats) staged_rows<0, false>(stage, lane, m_first, out_row, ld, nb, group);
+          else staged_rows<0, true>(stage, lane, m_first, out_row, ld, nb, group);
+        } else if (ep.act == 0) {
+          if (!stats) staged_rows<1, false>(stage, lane, m_first, out_row, ld, nb, group);
+          else staged_rows<1, true>(stage, lane, m_first, out_row, ld, nb, group);
+        } else {
+          if (!stats) staged_rows<2, false>(stage, lane, m_first, out_row, ld, nb, group);
+          else staged_rows<2, true>(stage, lane, m_first, out_row, ld, nb, group);
         }
-        if (ep.stats && splits == 1)
-          acc.flush(ep.stats, (long long)(t.m0 >> 7) * 4 + (row >> 5), N, nb, lane);
         __syncwarp();  // the tile is rewritten by the next chunk
         return;
       }

@@ -168,6 +168,32 @@ struct PatchConvProblem {
     return out + (((long long)img * out_H + p * oh_mul + cls[t.c].oh_add) * out_W + q * ow_mul +
                   cls[t.c].ow_add) * out_C;
   }
+  // Pixel rows 4k + lane / 8 (k = 0..7) of the warp's staged chunk, 16 bytes per lane, bias
+  // added; STATS (uniform across the grid, so a copy of the loop each): per-channel sums of
+  // the stored values into the statistics matrix.
+  template <bool STATS>
+  __device__ __forceinline__ void staged_pixels(const Tile& t, int row, int nb, float* stage,
+                                                int lane) const {
+    float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (bias) bq = *reinterpret_cast<const float4*>(bias + nb + 4 * (lane & 7));
+    const int r_first = row - lane;
+    EpiStats acc;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float* dst = cl_row(t, r_first + 4 * k + (lane >> 3));
+      float4 val = epi_stage_read(stage, lane, k);
+      val.x += bq.x; val.y += bq.y; val.z += bq.z; val.w += bq.w;
+      if (dst) {
+        *reinterpret_cast<float4*>(dst + nb + 4 * (lane & 7)) = val;
+        if (STATS) acc.add(val);
+      }
+    }
+    if (STATS) {
+      const long long tile_m = ((long long)(t.b0 >> (7 - qw_shift - ph_shift)) * tiles_p +
+                                (t.p0 >> ph_shift)) * tiles_q + (t.q0 >> qw_shift);
+      acc.flush(stats, tile_m * 4 + (row >> 5), n_out, nb, lane, stage);
+    }
+  }
   __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v,
                                         float* stage, int lane) const {
     const int nb = t.n0 + c0;
@@ -175,25 +201,8 @@ struct PatchConvProblem {
       // channels-last output: through the warp's staging tile, 4 whole 128-byte pixel rows per
       // store instruction (see tc_kernel.cuh)
       epi_stage_write(stage, lane, v);
-      float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (bias) bq = *reinterpret_cast<const float4*>(bias + nb + 4 * (lane & 7));
-      const int r_first = row - lane;
-      EpiStats acc;
-#pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        float* dst = cl_row(t, r_first + 4 * k + (lane >> 3));
-        float4 val = epi_stage_read(stage, lane, k);
-        val.x += bq.x; val.y += bq.y; val.z += bq.z; val.w += bq.w;
-        if (dst) {
-          *reinterpret_cast<float4*>(dst + nb + 4 * (lane & 7)) = val;
-          if (stats) acc.add(val);
-        }
-      }
-      if (stats) {
-        const long long tile_m = ((long long)(t.b0 >> (7 - qw_shift - ph_shift)) * tiles_p +
-                                  (t.p0 >> ph_shift)) * tiles_q + (t.q0 >> qw_shift);
-        acc.flush(stats, tile_m * 4 + (row >> 5), n_out, nb, lane);
-      }
+      if (stats) staged_pixels<true>(t, row, nb, stage, lane);
+      else staged_pixels<false>(t, row, nb, stage, lane);
       __syncwarp();
       return;
     }
