@@ -27,6 +27,9 @@
 // A problem policy P tells the skeleton what a tile is:
 //   int  a_mn_major, b_mn_major;
 //   static constexpr bool kWarpProducer;  // load() is called by the whole warp (else lane 0)
+//   static constexpr int kMinBlocks;      // second argument of tc_persistent_kernel's launch
+//                                         // bounds: 1 = the register allocator may use the whole
+//                                         // file for the one resident CTA, 0 = its own choice
 //   struct Tile;  struct LoadState;
 //   __device__ int  num_tiles() const;
 //   __device__ void decode(int tile, Tile&) const;
@@ -176,7 +179,7 @@ static __device__ long long g_tc_profile[256 * 8];
 #endif
 
 template <class P, int BN, int STAGES, int X3 = 0, int KSUB = 1>
-__global__ void __launch_bounds__(threads_for<P, X3, BN>())
+__global__ void __launch_bounds__(threads_for<P, X3, BN>(), P::kMinBlocks)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                      const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
   using SL = SmemLayout<BN, STAGES, X3>;
@@ -489,6 +492,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 template <int BN>
 struct GemmProblem {
   static constexpr bool kWarpProducer = true;
+  static constexpr int kMinBlocks = 0;
   static constexpr bool kBf16Capable = true;
   int bf16;  // operands are bf16 (64 elements per stage), else fp32 read as TF32
   OperandCoords a, b;

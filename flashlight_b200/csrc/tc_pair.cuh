@@ -56,7 +56,7 @@ template <class P>
 constexpr int pair_threads_for() { return (pair_second_epilogue_first_warp<P>() + 4) * 32; }
 
 template <class P, int BN, int STAGES, int KSUB = 2>
-__global__ void __launch_bounds__(pair_threads_for<P>())
+__global__ void __launch_bounds__(pair_threads_for<P>(), 1)
 tc_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                const __grid_constant__ CUtensorMap map_b, const P prob, int* status) {
   using SL = PairSmemLayout<BN, STAGES>;

@@ -50,6 +50,7 @@ constexpr int kMaxPatchClasses = 4;
 template <int BN>
 struct PatchConvProblem {
   static constexpr bool kWarpProducer = false;
+  static constexpr int kMinBlocks = 1;
   static constexpr bool kBf16Capable = false;
   int a_mn_major, b_mn_major;  // 0, 0
   // patch geometry (all powers of two, NB * PH * QW == 128)
@@ -165,13 +166,16 @@ struct PatchConvProblem {
     const int p = t.p0 + ((r >> qw_shift) & (PH - 1));
     const int img = t.b0 + (r >> (qw_shift + ph_shift));
     if (q >= pix_w || p >= pix_h || img >= images) return nullptr;
-    return out + (((long long)img * out_H + p * oh_mul + cls[t.c].oh_add) * out_W + q * ow_mul +
-                  cls[t.c].ow_add) * out_C;
+    const int oh_add = fill_cell ? 0 : cls[t.c].oh_add, ow_add = fill_cell ? 0 : cls[t.c].ow_add;
+    return out + (((long long)img * out_H + p * oh_mul + oh_add) * out_W + q * ow_mul + ow_add) *
+                     out_C;
   }
   // Pixel rows 4k + lane / 8 (k = 0..7) of the warp's staged chunk, 16 bytes per lane, bias
   // added; STATS (uniform across the grid, so a copy of the loop each): per-channel sums of
-  // the stored values into the statistics matrix.
-  template <bool STATS>
+  // the stored values into the statistics matrix.  FILL: the strided backward-data whose only
+  // class with taps is (0, 0) — every pixel also writes the zeros of its cell, whole 128-byte
+  // rows like its own values, so the tensor needs no clearing pass.
+  template <bool STATS, bool FILL>
   __device__ __forceinline__ void staged_pixels(const Tile& t, int row, int nb, float* stage,
                                                 int lane) const {
     float4 bq = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -186,6 +190,16 @@ struct PatchConvProblem {
       if (dst) {
         *reinterpret_cast<float4*>(dst + nb + 4 * (lane & 7)) = val;
         if (STATS) acc.add(val);
+        if (FILL) {
+          // this pixel owns its whole oh_mul x ow_mul cell: the other pixels receive zeros
+          const int r = r_first + 4 * k + (lane >> 3);
+          const int ow0 = (t.q0 + (r & (QW - 1))) * ow_mul;
+          const int oh0 = (t.p0 + ((r >> qw_shift) & (PH - 1))) * oh_mul;
+          for (int a = 0; a < oh_mul && oh0 + a < out_H; ++a)
+            for (int b = a == 0 ? 1 : 0; b < ow_mul && ow0 + b < out_W; ++b)
+              *reinterpret_cast<float4*>(dst + ((long long)a * out_W + b) * out_C + nb +
+                                         4 * (lane & 7)) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
       }
     }
     if (STATS) {
@@ -197,12 +211,13 @@ struct PatchConvProblem {
   __device__ __forceinline__ void store(const Tile& t, int row, int c0, const float* v,
                                         float* stage, int lane) const {
     const int nb = t.n0 + c0;
-    if (out_cl && !fill_cell && nb + 32 <= n_out && (out_C & 3) == 0) {
+    if (out_cl && nb + 32 <= n_out && (out_C & 3) == 0) {
       // channels-last output: through the warp's staging tile, 4 whole 128-byte pixel rows per
       // store instruction (see tc_kernel.cuh)
       epi_stage_write(stage, lane, v);
-      if (stats) staged_pixels<true>(t, row, nb, stage, lane);
-      else staged_pixels<false>(t, row, nb, stage, lane);
+      if (fill_cell) staged_pixels<false, true>(t, row, nb, stage, lane);
+      else if (stats) staged_pixels<true, false>(t, row, nb, stage, lane);
+      else staged_pixels<false, false>(t, row, nb, stage, lane);
       __syncwarp();
       return;
     }
@@ -291,6 +306,7 @@ struct PatchConvProblem {
 template <int BN>
 struct PatchWgradProblem {
   static constexpr bool kWarpProducer = true;
+  static constexpr int kMinBlocks = 1;
   static constexpr bool kBf16Capable = false;
   int a_mn_major, b_mn_major;  // 1, 1
   int QW, PH;                  // 32-pixel patch: QW * PH == 32
