@@ -592,13 +592,19 @@ def run_gpu_arm(args) -> None:
 
     # ---- timed region 2: end to end (pinned host batch -> device, loss -> host).  Every step's
     # batch is copied from pinned host memory inside the timed region; the copy of step i + 1
-    # runs on a second stream into the other of two device buffers while step i computes (its
-    # previous reader, step i - 1, ended with the loss read-back).
+    # runs on a second stream into the other of two device buffers while step i computes.  The
+    # loss of step i goes to pinned host memory right behind the step and is read on the host
+    # after step i + 1 has been submitted (every loss is read inside the timed region; the
+    # host never idles the device while it waits for a number).
     copy_stream = torch.cuda.Stream(device=dev)
     bufs = [(torch.empty_like(x_dev), torch.empty_like(t_dev)) for _ in range(2)]
+    consumed = [None, None]  # main-stream event: the last reader of the slot has taken its batch
+    loss_host = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
 
     def fetch(slot):
         with torch.cuda.stream(copy_stream):
+            if consumed[slot] is not None:
+                copy_stream.wait_event(consumed[slot])
             bufs[slot][0].copy_(x_host, non_blocking=True)
             bufs[slot][1].copy_(t_host, non_blocking=True)
             ev = torch.cuda.Event()
@@ -606,21 +612,38 @@ def run_gpu_arm(args) -> None:
         return ev
 
     def run_e2e(n):
-        out = 0.0
         ev = fetch(0)
+        pending = None  # (event, slot) of the previous step's loss copy
+        main = torch.cuda.current_stream()
         for i in range(n):
-            torch.cuda.current_stream().wait_event(ev)
+            main.wait_event(ev)
             xb, tb = bufs[i % 2]
-            if i + 1 < n:
-                ev = fetch((i + 1) % 2)
             if graph is not None:
                 static_x.copy_(xb)
                 static_t.copy_(tb)
+                taken = torch.cuda.Event()
+                taken.record(main)
+                consumed[i % 2] = taken
+                if i + 1 < n:
+                    ev = fetch((i + 1) % 2)
                 graph.replay()
-                out = graph_loss.tensor.item()
+                loss_dev = graph_loss.tensor
             else:
-                out = step(xb, tb).tensor.item()
-        return out
+                if i + 1 < n:
+                    ev = fetch((i + 1) % 2)
+                loss_dev = step(xb, tb).tensor
+                taken = torch.cuda.Event()
+                taken.record(main)
+                consumed[i % 2] = taken
+            loss_host[i % 2].copy_(loss_dev.reshape(1), non_blocking=True)
+            done = torch.cuda.Event()
+            done.record(main)
+            if pending is not None:  # the previous step's loss, now that this one is queued
+                pending[0].synchronize()
+                _ = float(loss_host[pending[1]][0])
+            pending = (done, i % 2)
+        pending[0].synchronize()
+        return float(loss_host[pending[1]][0])
 
     run_e2e(1)
     barrier()
@@ -761,7 +784,10 @@ def run_gpu_arm(args) -> None:
         "value_eager": images / (ms_eager * 1e-3), "ms_per_step_eager": ms_eager / args.steps,
         "e2e": {"value": e2e_value, "unit": UNIT,
                 "h2d_bytes_per_step": int(x_host.numel() * 4 + t_host.numel() * 4),
-                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps},
+                "d2h_bytes_per_step": 4, "ms_per_step": ms_e2e / args.steps,
+                "pipeline": "batch i + 1 is copied host -> device on a second stream while step i "
+                            "runs; the loss of step i is copied to pinned host memory behind the "
+                            "step and read on the host after step i + 1 has been submitted"},
         "graph_captured": graph_captured, "graph_error": graph_error,
         "gpu_launches": int(launches),
         "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base, "per_op": per_op,
