@@ -532,6 +532,32 @@ def glue(x: Variable, fwd, bwd) -> Variable:
     return Variable(y, False, [x], grad_func)
 
 
+def unbind(x: Variable, fwd, bwd, n: int) -> List[Variable]:
+    """One copy that brings `x` into n stacked parts (`fwd` maps its tensor to [n, ...]) and
+    hands each part out as a Variable of its own — the q, k, v of a packed projection.  The
+    reference indexes the packed tensor three times, and each index gradient is a zero tensor
+    of the full size with one slice filled, summed by addGrad
+    (flashlight/fl/autograd/Functions.cpp:1233-1263 `index`); here the parts' gradients are
+    written into one buffer and `bwd` maps it back once, when the last of them has arrived.
+    Every part must take part in the loss (a part without a gradient would leave the buffer
+    waiting).  Data movement only: torch glue."""
+    stacked = fwd(x.tensor)
+    state = {"buf": None, "seen": 0}
+
+    def part_grad(i):
+        def grad_func(inputs, gy):
+            if state["buf"] is None:
+                state["buf"] = torch.empty_like(stacked)
+            state["buf"][i].copy_(gy)
+            state["seen"] += 1
+            if state["seen"] == n:
+                full, state["buf"], state["seen"] = state["buf"], None, 0
+                inputs[0].addGrad(bwd(full))
+        return grad_func
+
+    return [Variable(stacked[i], False, [x], part_grad(i)) for i in range(n)]
+
+
 def bmm(a: Variable, b: Variable, trans_b: bool = False) -> Variable:
     """Batched matmul (Functions.cpp:827-946): a (Z, M, K); b (Z, K, N), or (Z, N, K) when
     trans_b.  The three contractions of forward and backward are strided views of the same

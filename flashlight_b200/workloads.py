@@ -286,19 +286,14 @@ class TransformerLM(nn.Module):
         hd = d // h
         qkv = self._lin(blk["qkv"], x)  # (B*T, 3d)
 
-        def split(i, scale):
-            # pure data movement: pick q, k or v and bring the head index forward
-            fwd = lambda t: t.reshape(B, T, 3, h, hd)[:, :, i].permute(0, 2, 1, 3) \
-                .reshape(B * h, T, hd).contiguous()
-
-            def bwd(g):
-                full = torch.zeros(B, T, 3, h, hd, device=g.device, dtype=g.dtype)
-                full[:, :, i] = g.reshape(B, h, T, hd).permute(0, 2, 1, 3)
-                return full.reshape(B * T, 3 * d)
-
-            return A.glue(qkv, fwd, bwd)
-
-        q, k, v = split(0, 1.0), split(1, 1.0), split(2, 1.0)
+        # pure data movement: one copy brings the head index forward for q, k and v together,
+        # (B*T, 3d) -> (3, B*h, T, hd); their gradients travel back the same way in one copy
+        q, k, v = A.unbind(
+            qkv,
+            lambda t: t.reshape(B, T, 3, h, hd).permute(2, 0, 3, 1, 4).reshape(3, B * h, T, hd)
+            .contiguous(),
+            lambda g: g.reshape(3, B, h, T, hd).permute(1, 3, 0, 2, 4).reshape(B * T, 3 * d)
+            .contiguous(), 3)
         # scores (B*h, T, T) -> softmax with the scale 1/sqrt(head dim) and the causal mask folded
         # in -> context (B*h, T, hd); the gradient is the fused kernel where it is built (bf16,
         # head dim 64, T a multiple of 128), which keeps no T x T tensor for the backward pass
