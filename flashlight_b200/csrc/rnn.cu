@@ -254,7 +254,8 @@ BwdWs bwd_ws(const RnnDims& r) {
   w.zero = off; off += up256((size_t)r.B * r.H * 4);
   w.sync = off; off += 256;  // grid-barrier counter of the persistent recurrence kernel
   w.xbuf = off;              // its per-step exchange of partial sums
-  if (r.mode == FLB200_RNN_LSTM && (r.H == 256 || r.H == 512 || r.H == 1024))
+  if ((r.mode == FLB200_RNN_LSTM || r.mode == FLB200_RNN_GRU) &&
+      (r.H == 256 || r.H == 512 || r.H == 1024))
     off += up256(lstm_sequence_backward_scratch_bytes(r.H));
   w.red = off;
   w.red_bytes = flb200_channel_sum_workspace_bytes(r.TB, r.GH, 1);
@@ -388,6 +389,21 @@ static int rnn_forward_impl(const flb200_rnn_desc* d, const void* x, const void*
         return v && v[0] == '0';
       }();
       int first_step = 0;
+      if (r.mode == FLB200_RNN_GRU && !persistent_off &&
+          lstm_sequence_supported(d->math_mode, B, H, 3)) {
+        // GRU: the same persistent kernel with three gates; its reserve tensor q takes the
+        // place of the cell states
+        if (int rc = lstm_step_weight_map(&map_whh, wf + po.w_hh, H, 3)) return rc;
+        if (int rc = lstm_sequence_forward(
+                map_whh, gates, qbuf, out + (long long)dir * H, out_stride, h_prev, nullptr,
+                reinterpret_cast<unsigned*>(ws + W.sync), T, B, H, dir, 0, -1, st, 3,
+                wf + po.b_hh + 2 * H))
+          return rc;
+        const int t_last = dir == 0 ? T - 1 : 0;
+        h_prev = out + (long long)t_last * B * out_stride + (long long)dir * H;
+        hp_stride = out_stride;
+        first_step = T;
+      }
       if (fused && !persistent_off && lstm_sequence_supported(d->math_mode, B, H)) {
         if (int rc = lstm_sequence_forward(
                 map_whh, gates, cells, out + (long long)dir * H, out_stride, h_prev, c_prev,
@@ -523,18 +539,24 @@ static int rnn_backward_impl(const flb200_rnn_desc* d, const void* x, const void
         const char* v = getenv("FLB200_RNN_PERSISTENT");
         return v && v[0] == '0';
       }();
-      const bool persistent = r.mode == FLB200_RNN_LSTM && !persistent_off &&
-                              lstm_sequence_backward_supported(d->math_mode, B, H);
+      const bool lstm = r.mode == FLB200_RNN_LSTM, gru = r.mode == FLB200_RNN_GRU;
+      const bool persistent = (lstm || gru) && !persistent_off &&
+                              lstm_sequence_backward_supported(d->math_mode, B, H, r.G);
       if (persistent) {
+        // (GRU: q in the place of the cell states, h0 in the place of c0, no cell-state
+        // gradients, the recurrent side's gate gradients in dgh)
         CUtensorMap map_wt;
-        if (int rc = lstm_sequence_weight_map_transposed(&map_wt, wf + po.w_hh, H)) return rc;
+        if (int rc = lstm_sequence_weight_map_transposed(&map_wt, wf + po.w_hh, H, r.G)) return rc;
+        const float* first_state = lstm ? (cxf ? cxf + (long long)p * BH : zero)
+                                        : (hxf ? hxf + (long long)p * BH : zero);
         if (int rc = lstm_sequence_backward(
-                map_wt, gates, cells, cxf ? cxf + (long long)p * BH : zero,
+                map_wt, gates, lstm ? cells : qbuf, first_state,
                 dy_l ? dy_l + (long long)dir * H : nullptr, ys,
                 grad_hy ? static_cast<const float*>(grad_hy) + (long long)p * BH : nullptr,
-                grad_cy ? static_cast<const float*>(grad_cy) + (long long)p * BH : nullptr, dgx, dh,
-                dc, reinterpret_cast<float*>(ws + W.xbuf), reinterpret_cast<unsigned*>(ws + W.sync),
-                T, B, H, dir, st))
+                lstm && grad_cy ? static_cast<const float*>(grad_cy) + (long long)p * BH : nullptr,
+                dgx, dh, dc, reinterpret_cast<float*>(ws + W.xbuf),
+                reinterpret_cast<unsigned*>(ws + W.sync), T, B, H, dir, st, r.G, dgh,
+                out + (long long)dir * H, ys))
           return rc;
       }
       if (!persistent) {

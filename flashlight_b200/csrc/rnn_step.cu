@@ -1,3 +1,5 @@
+// (The sequence kernels further down run the LSTM and the GRU; this first part is the LSTM's
+// single-step kernel.)
 // One LSTM time step as ONE kernel: the recurrent GEMM on the tensor cores, its split-K
 // reduction inside a thread-block cluster, and the cell update as the epilogue.
 //
@@ -181,12 +183,13 @@ lstm_step_kernel(const __grid_constant__ CUtensorMap map_w,
 // anybody) a CTA stops waiting, still walks through the remaining steps and their cluster
 // barriers without blocking, and the host reports FLB200_TIMEOUT.
 struct SeqArgs {
-  float* gates;          // [T][B][4H]: input projections + biases in, activated gates out
-  float* cells;          // [T][B][H]
+  float* gates;          // [T][B][G*H]: input projections + biases in, activated gates out
+  float* cells;          // [T][B][H] (LSTM); GRU: q = U_n h + b_hn, the candidate's recurrent part
+  const float* b_hn;     // GRU: the recurrent bias of the candidate gate [H]
   float* out;            // layer output [T][B][out_stride]; this direction's columns start at 0
   long long out_stride;
   const float* h0;       // [B][H] initial state (or zeros)
-  const float* c0;
+  const float* c0;       // (LSTM)
   unsigned* sync;        // grid barrier counter, zero at launch
   int* status;
   long long wait_budget; // clocks per wait
@@ -226,9 +229,12 @@ static __device__ long long g_rnn_profile[8];
 constexpr int kSeqThreads = 256;  // warp 0 loads W_hh, warp 1 issues MMAs, warps 2-5 copy the
                                   // accumulator; all eight warps load h and update cells
 
-template <int KS>
+// G = 4: LSTM (gates i, f, g, o; the running state of a thread's pairs is c).  G = 3: GRU (gates
+// r, z, n with n = tanh(x_n + r * (U_n h + b_hn)); the running state is h itself): the
+// cluster's UMMA tile holds 96 live rows, the fourth gate's rows are zeros.
+template <int KS, int G>
 __global__ void __launch_bounds__(kSeqThreads)
-lstm_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a) {
+rnn_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a) {
   constexpr int kUnits = 32 / KS;                       // hidden units this CTA updates
   constexpr int kItems = (kUnits * 32 + kSeqThreads - 1) / kSeqThreads;  // (unit, batch) per thread
   constexpr int kLoads = 32 * (kSliceK / 4) / kSeqThreads;               // float4 of h per thread
@@ -261,12 +267,22 @@ lstm_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {  // the resident slice of W_hh: 32 boxes, one barrier
-    if (lane == 0) mbar_expect_tx(w_bar, kStagesK * kABytes);
+  if (warp == 0) {  // the resident slice of W_hh: 8 * G boxes, one barrier
+    if (lane == 0) mbar_expect_tx(w_bar, kStagesK * G * (32 * 128));
     __syncwarp();
     const int s = lane >> 2, g = lane & 3;
-    int c[2] = {rank * kSliceK + s * kBK, g * H + group * 32};
-    tma_load(&map_w, w_bar, a_tiles + s * kABytes + g * (32 * 128), 2, c);
+    if (g < G) {
+      int c[2] = {rank * kSliceK + s * kBK, g * H + group * 32};
+      tma_load(&map_w, w_bar, a_tiles + s * kABytes + g * (32 * 128), 2, c);
+    }
+  }
+  if (G < 4) {  // rows 32 G .. 127 of every k tile belong to no gate
+    constexpr int kPerStage = (4 - G) * (32 * 128 / 16);
+    for (int i = threadIdx.x; i < kStagesK * kPerStage; i += kSeqThreads) {
+      const int s = i / kPerStage, rem = i - s * kPerStage;
+      *reinterpret_cast<float4*>(a_tiles + s * kABytes + G * (32 * 128) + rem * 16) =
+          make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
   if (threadIdx.x == 0 && !mbar_wait(w_bar, 0)) *failed = 1;
   __syncthreads();
@@ -287,7 +303,9 @@ lstm_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a)
     item_b[it] = idx / kUnits;
     item_ul[it] = rank * kUnits + (idx - item_b[it] * kUnits);
     item_live[it] = idx < kUnits * 32 && item_b[it] < B;
-    c_reg[it] = item_live[it] ? a.c0[(long long)item_b[it] * H + group * 32 + item_ul[it]] : 0.f;
+    c_reg[it] = item_live[it] ? (G == 4 ? a.c0 : a.h0)[(long long)item_b[it] * H + group * 32 +
+                                                          item_ul[it]]
+                              : 0.f;
   }
 
 #ifdef FLB200_RNN_PROFILE
@@ -298,14 +316,14 @@ lstm_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a)
     const int t = a.reverse ? a.T - 1 - step : step;
     const int t_prev = a.reverse ? t + 1 : t - 1;
     // input projections of this step (written before the launch): in flight during the wait
-    float* g_t = a.gates + (long long)t * B * 4 * H;
-    float gin[kItems][4];
+    float* g_t = a.gates + (long long)t * B * G * H;
+    float gin[kItems][G];
 #pragma unroll
     for (int it = 0; it < kItems; ++it) {
       if (!item_live[it]) continue;
-      const float* gp = g_t + (long long)item_b[it] * 4 * H + group * 32 + item_ul[it];
+      const float* gp = g_t + (long long)item_b[it] * G * H + group * 32 + item_ul[it];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) gin[it][g] = __ldcg(gp + (long long)g * H);
+      for (int g = 0; g < G; ++g) gin[it][g] = __ldcg(gp + (long long)g * H);
     }
     // ---- wait until every CTA has published h of the previous step
     if (step > 0) {
@@ -379,28 +397,41 @@ lstm_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a)
       for (int it = 0; it < kItems; ++it) {
         if (!item_live[it]) continue;
         const int b = item_b[it], ul = item_ul[it];
-        float pr[KS][4];
+        float pr[KS][G];
 #pragma unroll
         for (int q = 0; q < KS; ++q) {
           const uint32_t base = mapa_u32(part_local, (uint32_t)q);
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
+          for (int g = 0; g < G; ++g)
             pr[q][g] = ld_cluster_f32(base + (uint32_t)(((g * 32 + ul) * kPartStride + b) * 4));
         }
-        float pre[4] = {0.f, 0.f, 0.f, 0.f};
+        float pre[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) pre[g] = 0.f;
 #pragma unroll
         for (int q = 0; q < KS; ++q)  // same order as lstm_step_kernel: bit-identical sums
 #pragma unroll
-          for (int g = 0; g < 4; ++g) pre[g] += pr[q][g];
+          for (int g = 0; g < G; ++g) pre[g] += pr[q][g];
         const int j = group * 32 + ul;
-        float* gp = g_t + (long long)b * 4 * H + j;
-        const float i = sigmoid_(pre[0] + gin[it][0]), f = sigmoid_(pre[1] + gin[it][1]);
-        const float gg = tanhf(pre[2] + gin[it][2]), o = sigmoid_(pre[3] + gin[it][3]);
-        const float c = f * c_reg[it] + i * gg;
-        c_reg[it] = c;
-        gp[0] = i; gp[H] = f; gp[2 * H] = gg; gp[3 * H] = o;
-        a.cells[((long long)t * B + b) * H + j] = c;
-        a.out[((long long)t * B + b) * a.out_stride + j] = o * tanhf(c);
+        float* gp = g_t + (long long)b * G * H + j;
+        if constexpr (G == 4) {
+          const float i = sigmoid_(pre[0] + gin[it][0]), f = sigmoid_(pre[1] + gin[it][1]);
+          const float gg = tanhf(pre[2] + gin[it][2]), o = sigmoid_(pre[3] + gin[it][3]);
+          const float c = f * c_reg[it] + i * gg;
+          c_reg[it] = c;
+          gp[0] = i; gp[H] = f; gp[2 * H] = gg; gp[3 * H] = o;
+          a.cells[((long long)t * B + b) * H + j] = c;
+          a.out[((long long)t * B + b) * a.out_stride + j] = o * tanhf(c);
+        } else {
+          const float r = sigmoid_(pre[0] + gin[it][0]), z = sigmoid_(pre[1] + gin[it][1]);
+          const float q = pre[2] + a.b_hn[j];
+          const float n = tanhf(gin[it][2] + r * q);
+          const float h = (1.f - z) * n + z * c_reg[it];
+          c_reg[it] = h;
+          gp[0] = r; gp[H] = z; gp[2 * H] = n;
+          a.cells[((long long)t * B + b) * H + j] = q;
+          a.out[((long long)t * B + b) * a.out_stride + j] = h;
+        }
       }
     }
     RNN_PROF_MARK(4)
@@ -444,14 +475,18 @@ lstm_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a)
 // have to be 16 CTAs large and the device holds only 7 such clusters at a time.)
 // Barrier, bounded waits and residency rule as in lstm_sequence_kernel.
 struct SeqBwdArgs {
-  const float* gates;    // [T][B][4H] activated gates of the forward pass
-  const float* cells;    // [T][B][H]
-  const float* c0;       // [B][H]
+  const float* gates;    // [T][B][G*H] activated gates of the forward pass
+  const float* cells;    // [T][B][H]; GRU: q, the candidate's recurrent part
+  const float* c0;       // [B][H]; GRU: h0
+  const float* out;      // GRU: the forward output (h of every step), this direction's columns
+  long long out_stride;
   const float* dy;       // gradient of the layer output, this direction's first column, or null
   long long dy_stride;
   const float* dh0;      // [B][H] gradient of the final hidden / cell state, or null
   const float* dc0;
-  float* dgates;         // [T][B][4H] out: gate gradients (also the operand of the weight GEMMs)
+  float* dgates;         // [T][B][G*H] out: gate gradients (also the operand of the weight GEMMs)
+  float* dgh;            // GRU: the gate gradients as the recurrent side sees them (dn * r for
+                         // the candidate); LSTM: == dgates
   float* dh_out;         // [B][H] out: gradient of the initial hidden / cell state
   float* dc_out;
   float* xbuf;           // [SL][H][32] partial sums of one step
@@ -485,10 +520,12 @@ __device__ __forceinline__ void grid_barrier(unsigned* sync, unsigned index, uns
   __syncthreads();
 }
 
-template <int SL>
+// G as in rnn_sequence_kernel; SL = G * H / 256 slices of the gate rows.  GRU: the running dc
+// of a pair is the direct part dh * z of its next dh.
+template <int SL, int G>
 __global__ void __launch_bounds__(kSeqThreads)
-lstm_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const SeqBwdArgs a) {
-  constexpr int kUnits = kBM / SL;                                        // outputs per CTA
+rnn_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const SeqBwdArgs a) {
+  constexpr int kUnits = (kBM + SL - 1) / SL;                             // outputs per CTA
   constexpr int kItems = (kUnits * 32 + kSeqThreads - 1) / kSeqThreads;
   constexpr int kLoads = 32 * (kSliceK / 4) / kSeqThreads;
   extern __shared__ char smem_raw[];
@@ -543,11 +580,12 @@ lstm_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const S
   for (int it = 0; it < kItems; ++it) {
     const int idx = threadIdx.x + it * kSeqThreads;
     item_b[it] = idx / kUnits;
-    item_k[it] = mt * kBM + rank * kUnits + (idx - item_b[it] * kUnits);  // output (hidden unit)
-    item_live[it] = idx < kUnits * 32 && item_b[it] < B;
+    const int unit = rank * kUnits + (idx - item_b[it] * kUnits);  // within the 128-output tile
+    item_k[it] = mt * kBM + unit;                                  // output (hidden unit)
+    item_live[it] = idx < kUnits * 32 && unit < kBM && item_b[it] < B;
     const long long at = (long long)item_b[it] * H + item_k[it];
     dh[it] = item_live[it] && a.dh0 ? a.dh0[at] : 0.f;
-    dc[it] = item_live[it] && a.dc0 ? a.dc0[at] : 0.f;
+    dc[it] = G == 4 && item_live[it] && a.dc0 ? a.dc0[at] : 0.f;
   }
 
   unsigned barrier_index = 0;
@@ -561,35 +599,50 @@ lstm_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const S
       for (int it = 0; it < kItems; ++it) {
         if (!item_live[it]) continue;
         const int b = item_b[it], j = item_k[it];
-        const float* g = a.gates + ((long long)t * B + b) * 4 * H + j;
-        const float gi = __ldcg(g), gf = __ldcg(g + H), gg = __ldcg(g + 2 * H), go = __ldcg(g + 3 * H);
-        const float c = __ldcg(a.cells + ((long long)t * B + b) * H + j);
-        const float cp = step == 0 ? __ldcg(a.c0 + (long long)b * H + j)
-                                   : __ldcg(a.cells + ((long long)t_prev * B + b) * H + j);
+        const float* g = a.gates + ((long long)t * B + b) * G * H + j;
         float d = dh[it];
         if (a.dy) d += __ldcg(a.dy + ((long long)t * B + b) * a.dy_stride + j);
-        const float tc = tanhf(c);
-        const float dct = dc[it] + d * go * (1.f - tc * tc);
-        float* o = a.dgates + ((long long)t * B + b) * 4 * H + j;
-        o[0] = dct * gg * gi * (1.f - gi);
-        o[H] = dct * cp * gf * (1.f - gf);
-        o[2 * H] = dct * gi * (1.f - gg * gg);
-        o[3 * H] = d * tc * go * (1.f - go);
-        dc[it] = dct * gf;
+        float* o = a.dgates + ((long long)t * B + b) * G * H + j;
+        if constexpr (G == 4) {
+          const float gi = __ldcg(g), gf = __ldcg(g + H), gg = __ldcg(g + 2 * H), go = __ldcg(g + 3 * H);
+          const float c = __ldcg(a.cells + ((long long)t * B + b) * H + j);
+          const float cp = step == 0 ? __ldcg(a.c0 + (long long)b * H + j)
+                                     : __ldcg(a.cells + ((long long)t_prev * B + b) * H + j);
+          const float tc = tanhf(c);
+          const float dct = dc[it] + d * go * (1.f - tc * tc);
+          o[0] = dct * gg * gi * (1.f - gi);
+          o[H] = dct * cp * gf * (1.f - gf);
+          o[2 * H] = dct * gi * (1.f - gg * gg);
+          o[3 * H] = d * tc * go * (1.f - go);
+          dc[it] = dct * gf;
+        } else {
+          const float r = __ldcg(g), z = __ldcg(g + H), n = __ldcg(g + 2 * H);
+          const float q = __ldcg(a.cells + ((long long)t * B + b) * H + j);
+          const float hp = step == 0 ? __ldcg(a.c0 + (long long)b * H + j)
+                                     : __ldcg(a.out + ((long long)t_prev * B + b) * a.out_stride + j);
+          const float dn = d * (1.f - z) * (1.f - n * n);
+          const float dz = d * (hp - n) * z * (1.f - z);
+          const float dr = dn * q * r * (1.f - r);
+          float* oh = a.dgh + ((long long)t * B + b) * G * H + j;
+          o[0] = dr; o[H] = dz; o[2 * H] = dn;
+          oh[0] = dr; oh[H] = dz; oh[2 * H] = dn * r;
+          dc[it] = d * z;
+        }
       }
     }
     // ---- every CTA's dgates_t must be complete before anybody contracts over them
     grid_barrier(a.sync, barrier_index++, n_ctas, a.wait_budget, a.status, failed, 14);
     const bool dead = *failed != 0;
     {
-      const float* src = a.dgates + (long long)t * B * 4 * H + rank * kSliceK;
+      const float* src = a.dgh + (long long)t * B * G * H + rank * kSliceK;
       float4 v[kLoads];
 #pragma unroll
       for (int u = 0; u < kLoads; ++u) {
         const int i = threadIdx.x + u * kSeqThreads;
         const int b = i / (kSliceK / 4), q = i - b * (kSliceK / 4);
         v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (b < B && !dead) v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)b * 4 * H) + q);
+        if (b < B && !dead)
+          v[u] = __ldcg(reinterpret_cast<const float4*>(src + (long long)b * G * H) + q);
       }
 #pragma unroll
       for (int u = 0; u < kLoads; ++u) {
@@ -637,7 +690,7 @@ lstm_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const S
         float sum = 0.f;
 #pragma unroll
         for (int q = 0; q < SL; ++q) sum += pr[q];
-        dh[it] = sum;
+        dh[it] = G == 4 ? sum : dc[it] + sum;
       }
     }
     // (the exchange buffer is rewritten only after the next step's first barrier, which every
@@ -649,7 +702,7 @@ lstm_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const S
       if (!item_live[it]) continue;
       const long long at = (long long)item_b[it] * H + item_k[it];
       a.dh_out[at] = dh[it];
-      a.dc_out[at] = dc[it];
+      if (G == 4) a.dc_out[at] = dc[it];
     }
   }
   __syncthreads();
@@ -660,21 +713,36 @@ lstm_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const S
 }
 
 typedef void (*SeqBwdKernel)(const CUtensorMap, const SeqBwdArgs);
-SeqBwdKernel sequence_backward_kernel_for(int sl) {
+SeqBwdKernel sequence_backward_kernel_for(int sl, int G) {
+  if (G == 3) {
+    switch (sl) {
+      case 3: return rnn_sequence_backward_kernel<3, 3>;
+      case 6: return rnn_sequence_backward_kernel<6, 3>;
+      default: return rnn_sequence_backward_kernel<12, 3>;
+    }
+  }
   switch (sl) {
-    case 4: return lstm_sequence_backward_kernel<4>;
-    case 8: return lstm_sequence_backward_kernel<8>;
-    default: return lstm_sequence_backward_kernel<16>;
+    case 4: return rnn_sequence_backward_kernel<4, 4>;
+    case 8: return rnn_sequence_backward_kernel<8, 4>;
+    default: return rnn_sequence_backward_kernel<16, 4>;
   }
 }
 
 typedef void (*SeqKernel)(const CUtensorMap, const SeqArgs);
-SeqKernel sequence_kernel_for(int ks) {
+SeqKernel sequence_kernel_for(int ks, int G) {
+  if (G == 3) {
+    switch (ks) {
+      case 1: return rnn_sequence_kernel<1, 3>;
+      case 2: return rnn_sequence_kernel<2, 3>;
+      case 4: return rnn_sequence_kernel<4, 3>;
+      default: return rnn_sequence_kernel<8, 3>;
+    }
+  }
   switch (ks) {
-    case 1: return lstm_sequence_kernel<1>;
-    case 2: return lstm_sequence_kernel<2>;
-    case 4: return lstm_sequence_kernel<4>;
-    default: return lstm_sequence_kernel<8>;
+    case 1: return rnn_sequence_kernel<1, 4>;
+    case 2: return rnn_sequence_kernel<2, 4>;
+    case 4: return rnn_sequence_kernel<4, 4>;
+    default: return rnn_sequence_kernel<8, 4>;
   }
 }
 
@@ -687,8 +755,8 @@ bool lstm_step_supported(int math_mode, int B, int H) {
   return ks == 1 || ks == 2 || ks == 4 || ks == 8;
 }
 
-int lstm_step_weight_map(CUtensorMap* map, const float* w_hh, int H) {
-  const uint64_t dims[2] = {(uint64_t)H, (uint64_t)4 * H};
+int lstm_step_weight_map(CUtensorMap* map, const float* w_hh, int H, int G) {
+  const uint64_t dims[2] = {(uint64_t)H, (uint64_t)G * H};
   const uint64_t strides[1] = {(uint64_t)H * 4};
   const uint32_t box[2] = {32, 32};
   return tc::make_tensor_map(map, w_hh, 2, dims, strides, box, tc::kMapKMajor);
@@ -744,18 +812,18 @@ int lstm_step_forward(const CUtensorMap& map_w, const float* h_prev, long long h
                         st);
 }
 
-bool lstm_sequence_supported(int math_mode, int B, int H) {
-  if (!lstm_step_supported(math_mode, B, H)) return false;
+bool lstm_sequence_supported(int math_mode, int B, int H, int G) {
+  if (!lstm_step_supported(math_mode, B, H) || (G != 3 && G != 4)) return false;
   // every CTA of the kernel has to be resident at the same time (grid-wide barrier per step)
   // (one answer per device and cluster size 1, 2, 4 or 8)
-  static int max_clusters[64][4];
-  static bool known[64][4] = {{false}};
+  static int max_clusters[64][8];
+  static bool known[64][8] = {{false}};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
   const int ks = H / kSliceK;
-  const int slot = ks == 1 ? 0 : (ks == 2 ? 1 : (ks == 4 ? 2 : 3));
+  const int slot = (ks == 1 ? 0 : (ks == 2 ? 1 : (ks == 4 ? 2 : 3))) + (G == 3 ? 4 : 0);
   if (!known[dev][slot]) {
-    if (cudaFuncSetAttribute(sequence_kernel_for(ks), cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (cudaFuncSetAttribute(sequence_kernel_for(ks, G), cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBytes) != cudaSuccess) {
       (void)cudaGetLastError();
       return false;
@@ -772,7 +840,7 @@ bool lstm_sequence_supported(int math_mode, int B, int H) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, sequence_kernel_for(ks), &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&n, sequence_kernel_for(ks, G), &cfg) != cudaSuccess) {
       (void)cudaGetLastError();
       return false;
     }
@@ -785,8 +853,10 @@ bool lstm_sequence_supported(int math_mode, int B, int H) {
 int lstm_sequence_forward(const CUtensorMap& map_w, float* gates, float* cells, float* out,
                           long long out_stride, const float* h0, const float* c0, unsigned* sync,
                           int T, int B, int H, int reverse, long long wait_budget, int absent_cta,
-                          cudaStream_t st) {
+                          cudaStream_t st, int G, const float* b_hn) {
+  FLB200_REQUIRE(G == 4 || (G == 3 && b_hn), "rnn_sequence_forward: LSTM, or GRU with its bias");
   SeqArgs a{};
+  a.b_hn = b_hn;
   a.gates = gates; a.cells = cells; a.out = out; a.out_stride = out_stride;
   a.h0 = h0; a.c0 = c0; a.sync = sync; a.status = tc::status_ptr();
   a.wait_budget = wait_budget > 0 ? wait_budget : tc::kWaitBudget;
@@ -795,7 +865,7 @@ int lstm_sequence_forward(const CUtensorMap& map_w, float* gates, float* cells, 
                      (reinterpret_cast<uintptr_t>(h0) & 15) == 0,
                  "lstm_sequence_forward: rows must be 16-byte aligned");
   FLB200_CUDA_CHECK(cudaMemsetAsync(sync, 0, sizeof(unsigned), st));
-  SeqKernel kernel = sequence_kernel_for(a.KS);
+  SeqKernel kernel = sequence_kernel_for(a.KS, G);
   FLB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
   cudaLaunchConfig_t cfg{};
@@ -828,17 +898,17 @@ int lstm_sequence_forward(const CUtensorMap& map_w, float* gates, float* cells, 
   return FLB200_OK;
 }
 
-bool lstm_sequence_backward_supported(int math_mode, int B, int H) {
+bool lstm_sequence_backward_supported(int math_mode, int B, int H, int G) {
   if (math_mode != FLB200_MATH_TF32 || !flb200_has_tensor_core_path()) return false;
-  if (B < 1 || B > 32 || (H != 256 && H != 512 && H != 1024)) return false;
+  if (B < 1 || B > 32 || (H != 256 && H != 512 && H != 1024) || (G != 3 && G != 4)) return false;
   // every CTA resident at once: one per SM (the resident weights fill its shared memory)
-  static int per_sm[64][3];
-  static bool known[64][3] = {{false}};
+  static int per_sm[64][6];
+  static bool known[64][6] = {{false}};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-  const int slot = H == 256 ? 0 : (H == 512 ? 1 : 2);
+  const int slot = (H == 256 ? 0 : (H == 512 ? 1 : 2)) + (G == 3 ? 3 : 0);
   if (!known[dev][slot]) {
-    SeqBwdKernel kernel = sequence_backward_kernel_for(H / 64);
+    SeqBwdKernel kernel = sequence_backward_kernel_for(G * H / kSliceK, G);
     int n = 0;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) !=
             cudaSuccess ||
@@ -850,16 +920,17 @@ bool lstm_sequence_backward_supported(int math_mode, int B, int H) {
     per_sm[dev][slot] = n;
     known[dev][slot] = true;
   }
-  return (long long)per_sm[dev][slot] * device_info().sm_count >= (long long)(H / kBM) * (H / 64);
+  return (long long)per_sm[dev][slot] * device_info().sm_count >=
+         (long long)(H / kBM) * (G * H / kSliceK);
 }
 
 size_t lstm_sequence_backward_scratch_bytes(int H) {
-  return (size_t)(H / 64) * H * 32 * sizeof(float);
+  return (size_t)(H / 64) * H * 32 * sizeof(float);  // the LSTM's 4H / 256 slices: the larger
 }
 
-int lstm_sequence_weight_map_transposed(CUtensorMap* map, const float* w_hh, int H) {
-  // W_hh [4H][H] read as an MN-major operand: the output index (column of W_hh) is contiguous
-  const uint64_t dims[2] = {(uint64_t)H, (uint64_t)4 * H};
+int lstm_sequence_weight_map_transposed(CUtensorMap* map, const float* w_hh, int H, int G) {
+  // W_hh [G*H][H] read as an MN-major operand: the output index (column of W_hh) is contiguous
+  const uint64_t dims[2] = {(uint64_t)H, (uint64_t)G * H};
   const uint64_t strides[1] = {(uint64_t)H * 4};
   const uint32_t box[2] = {32, 32};
   return tc::make_tensor_map(map, w_hh, 2, dims, strides, box, tc::kMapMnMajor);
@@ -869,8 +940,13 @@ int lstm_sequence_backward(const CUtensorMap& map_wt, const float* gates, const 
                            const float* c0, const float* dy, long long dy_stride,
                            const float* dh0, const float* dc0, float* dgates, float* dh_out,
                            float* dc_out, float* xbuf, unsigned* sync, int T, int B, int H,
-                           int reverse, cudaStream_t st) {
+                           int reverse, cudaStream_t st, int G, float* dgh, const float* out,
+                           long long out_stride) {
+  FLB200_REQUIRE(G == 4 || (G == 3 && dgh && out && c0),
+                 "rnn_sequence_backward: LSTM, or GRU with its second gradient buffer, the "
+                 "forward output and h0");
   SeqBwdArgs a{};
+  a.dgh = G == 4 ? dgates : dgh; a.out = out; a.out_stride = out_stride;
   a.gates = gates; a.cells = cells; a.c0 = c0; a.dy = dy; a.dy_stride = dy_stride;
   a.dh0 = dh0; a.dc0 = dc0; a.dgates = dgates; a.dh_out = dh_out; a.dc_out = dc_out;
   a.xbuf = xbuf; a.sync = sync; a.status = tc::status_ptr(); a.wait_budget = tc::kWaitBudget;
@@ -879,8 +955,8 @@ int lstm_sequence_backward(const CUtensorMap& map_wt, const float* gates, const 
                      (reinterpret_cast<uintptr_t>(xbuf) & 15) == 0,
                  "lstm_sequence_backward: buffers must be 16-byte aligned");
   FLB200_CUDA_CHECK(cudaMemsetAsync(sync, 0, sizeof(unsigned), st));
-  const int sl = H / 64;
-  SeqBwdKernel kernel = sequence_backward_kernel_for(sl);
+  const int sl = G * H / kSliceK;
+  SeqBwdKernel kernel = sequence_backward_kernel_for(sl, G);
   FLB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kSmemBytes));
   kernel<<<(unsigned)(H / kBM * sl), kSeqThreads, kSmemBytes, st>>>(map_wt, a);

@@ -1,4 +1,4 @@
-"""The persistent LSTM recurrence (one kernel for all time steps of a layer and direction, the
+"""The persistent LSTM / GRU recurrence (one kernel for all time steps of a layer and direction, the
 recurrent weights resident in shared memory, a grid-wide barrier per step) against the fp64
 oracle and against the one-kernel-per-step path, and the bounded wait of its barrier."""
 import ctypes as C
@@ -66,6 +66,52 @@ def test_persistent_lstm_matches_oracle(L, dims, with_state):
     if with_state:
         assert_close_scaled(dhx, wdhx, 5e-3, "persistent lstm dhx")
         assert_close_scaled(dcx, wdcx, 5e-3, "persistent lstm dcx")
+
+
+@pytest.mark.parametrize("dims", [
+    (40, 256, 1, 8, 7, False),     # forward: one CTA per cluster; backward: 6 CTAs, 43 units each
+    (48, 512, 2, 7, 9, True),      # clusters of 2, ragged batch, two layers, both directions
+    (80, 1024, 1, 32, 12, True),   # 128 CTAs forward, 96 backward
+])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_persistent_gru_matches_oracle(L, dims, with_state):
+    """The GRU on the same persistent kernels (three gates; q = U_n h + b_hn kept for the
+    gradient; two gate-gradient tensors, the recurrent side's with dn * r)."""
+    from flashlight_b200.extension import AutogradPayload, B200AutogradExtension, RNNGradData
+    I, H, layers, B, T, bidir = dims
+    dirs = 2 if bidir else 1
+    ext = B200AutogradExtension(math_mode=L.MATH_TF32)
+    n = R.rnn_num_params(I, H, layers, R.RNN_GRU, bidir)
+    w = randn(n, seed=50) * (0.5 / H ** 0.5)
+    x = randn(T, B, I, seed=51)
+    hx = randn(layers * dirs, B, H, seed=52) * 0.5 if with_state else None
+    dev = lambda t: None if t is None else t.cuda()
+    f64 = lambda t: None if t is None else t.double()
+    payload = AutogradPayload()
+    before = L.kernel_launches()
+    y, hy, _ = ext.rnn(x.cuda(), dev(hx), None, w.cuda(), H, layers, R.RNN_GRU, bidir, 0.0,
+                       payload)
+    torch.cuda.synchronize()
+    launches = L.kernel_launches() - before
+    assert launches <= 8 * layers * dirs, f"{launches} launches for {T} steps"
+    wy, why, _ = R.rnn(x.double(), f64(hx), None, w.double(), H, layers, R.RNN_GRU, bidir)
+    assert_close_scaled(y, wy, 5e-3, "persistent gru y")
+    assert_close_scaled(hy, why, 5e-3, "persistent gru hy")
+    gy = randn(T, B, dirs * H, seed=54)
+    ghy = randn(layers * dirs, B, H, seed=55) if with_state else None
+    before = L.kernel_launches()
+    dx, dhx, _, dw = ext.rnnBackward(x.cuda(), dev(hx), None, w.cuda(),
+                                     RNNGradData(gy.cuda(), dev(ghy), None), y, layers, H,
+                                     R.RNN_GRU, bidir, 0.0, payload)
+    torch.cuda.synchronize()
+    launches = L.kernel_launches() - before
+    assert launches <= 40 * layers * dirs, f"{launches} backward launches for {T} steps"
+    wdx, wdhx, _, wdw = R.rnn_backward(x.double(), f64(hx), None, w.double(), H, layers,
+                                       R.RNN_GRU, bidir, gy.double(), f64(ghy), None)
+    assert_close_scaled(dx, wdx, 5e-3, "persistent gru dx")
+    assert_close_scaled(dw, wdw, 5e-3, "persistent gru dw")
+    if with_state:
+        assert_close_scaled(dhx, wdhx, 5e-3, "persistent gru dhx")
 
 
 def test_persistent_equals_per_step_path(L):
