@@ -254,8 +254,7 @@ BwdWs bwd_ws(const RnnDims& r) {
   w.zero = off; off += up256((size_t)r.B * r.H * 4);
   w.sync = off; off += 256;  // grid-barrier counter of the persistent recurrence kernel
   w.xbuf = off;              // its per-step exchange of partial sums
-  if ((r.mode == FLB200_RNN_LSTM || r.mode == FLB200_RNN_GRU) &&
-      (r.H == 256 || r.H == 512 || r.H == 1024))
+  if (r.H == 256 || r.H == 512 || r.H == 1024)
     off += up256(lstm_sequence_backward_scratch_bytes(r.H));
   w.red = off;
   w.red_bytes = flb200_channel_sum_workspace_bytes(r.TB, r.GH, 1);
@@ -389,15 +388,16 @@ static int rnn_forward_impl(const flb200_rnn_desc* d, const void* x, const void*
         return v && v[0] == '0';
       }();
       int first_step = 0;
-      if (r.mode == FLB200_RNN_GRU && !persistent_off &&
-          lstm_sequence_supported(d->math_mode, B, H, 3)) {
-        // GRU: the same persistent kernel with three gates; its reserve tensor q takes the
-        // place of the cell states
-        if (int rc = lstm_step_weight_map(&map_whh, wf + po.w_hh, H, 3)) return rc;
+      if (r.mode != FLB200_RNN_LSTM && !persistent_off &&
+          lstm_sequence_supported(d->math_mode, B, H, r.G)) {
+        // GRU and the plain cells: the same persistent kernel with three gates / one; the
+        // GRU's reserve tensor q takes the place of the cell states
+        const bool gru = r.mode == FLB200_RNN_GRU;
+        if (int rc = lstm_step_weight_map(&map_whh, wf + po.w_hh, H, r.G)) return rc;
         if (int rc = lstm_sequence_forward(
-                map_whh, gates, qbuf, out + (long long)dir * H, out_stride, h_prev, nullptr,
-                reinterpret_cast<unsigned*>(ws + W.sync), T, B, H, dir, 0, -1, st, 3,
-                wf + po.b_hh + 2 * H))
+                map_whh, gates, gru ? qbuf : nullptr, out + (long long)dir * H, out_stride, h_prev,
+                nullptr, reinterpret_cast<unsigned*>(ws + W.sync), T, B, H, dir, 0, -1, st, r.G,
+                gru ? wf + po.b_hh + 2 * H : nullptr, r.mode == FLB200_RNN_RELU ? 0 : 1))
           return rc;
         const int t_last = dir == 0 ? T - 1 : 0;
         h_prev = out + (long long)t_last * B * out_stride + (long long)dir * H;
@@ -540,11 +540,11 @@ static int rnn_backward_impl(const flb200_rnn_desc* d, const void* x, const void
         return v && v[0] == '0';
       }();
       const bool lstm = r.mode == FLB200_RNN_LSTM, gru = r.mode == FLB200_RNN_GRU;
-      const bool persistent = (lstm || gru) && !persistent_off &&
+      const bool persistent = !persistent_off &&
                               lstm_sequence_backward_supported(d->math_mode, B, H, r.G);
       if (persistent) {
         // (GRU: q in the place of the cell states, h0 in the place of c0, no cell-state
-        // gradients, the recurrent side's gate gradients in dgh)
+        // gradients, the recurrent side's gate gradients in dgh; plain cells: gates only)
         CUtensorMap map_wt;
         if (int rc = lstm_sequence_weight_map_transposed(&map_wt, wf + po.w_hh, H, r.G)) return rc;
         const float* first_state = lstm ? (cxf ? cxf + (long long)p * BH : zero)
@@ -556,7 +556,7 @@ static int rnn_backward_impl(const flb200_rnn_desc* d, const void* x, const void
                 lstm && grad_cy ? static_cast<const float*>(grad_cy) + (long long)p * BH : nullptr,
                 dgx, dh, dc, reinterpret_cast<float*>(ws + W.xbuf),
                 reinterpret_cast<unsigned*>(ws + W.sync), T, B, H, dir, st, r.G, dgh,
-                out + (long long)dir * H, ys))
+                out + (long long)dir * H, ys, r.mode == FLB200_RNN_RELU ? 0 : 1))
           return rc;
       }
       if (!persistent) {

@@ -186,6 +186,7 @@ struct SeqArgs {
   float* gates;          // [T][B][G*H]: input projections + biases in, activated gates out
   float* cells;          // [T][B][H] (LSTM); GRU: q = U_n h + b_hn, the candidate's recurrent part
   const float* b_hn;     // GRU: the recurrent bias of the candidate gate [H]
+  int act;               // G = 1: 0 relu, 1 tanh
   float* out;            // layer output [T][B][out_stride]; this direction's columns start at 0
   long long out_stride;
   const float* h0;       // [B][H] initial state (or zeros)
@@ -231,7 +232,8 @@ constexpr int kSeqThreads = 256;  // warp 0 loads W_hh, warp 1 issues MMAs, warp
 
 // G = 4: LSTM (gates i, f, g, o; the running state of a thread's pairs is c).  G = 3: GRU (gates
 // r, z, n with n = tanh(x_n + r * (U_n h + b_hn)); the running state is h itself): the
-// cluster's UMMA tile holds 96 live rows, the fourth gate's rows are zeros.
+// cluster's UMMA tile holds 96 live rows, the fourth gate's rows are zeros.  G = 1: the plain
+// cells h = relu / tanh(x + U h): 32 live rows.
 template <int KS, int G>
 __global__ void __launch_bounds__(kSeqThreads)
 rnn_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a) {
@@ -422,6 +424,11 @@ rnn_sequence_kernel(const __grid_constant__ CUtensorMap map_w, const SeqArgs a) 
           gp[0] = i; gp[H] = f; gp[2 * H] = gg; gp[3 * H] = o;
           a.cells[((long long)t * B + b) * H + j] = c;
           a.out[((long long)t * B + b) * a.out_stride + j] = o * tanhf(c);
+        } else if constexpr (G == 1) {
+          const float v = pre[0] + gin[it][0];
+          const float h = a.act == 0 ? fmaxf(v, 0.f) : tanhf(v);
+          gp[0] = h;
+          a.out[((long long)t * B + b) * a.out_stride + j] = h;
         } else {
           const float r = sigmoid_(pre[0] + gin[it][0]), z = sigmoid_(pre[1] + gin[it][1]);
           const float q = pre[2] + a.b_hn[j];
@@ -485,6 +492,7 @@ struct SeqBwdArgs {
   const float* dh0;      // [B][H] gradient of the final hidden / cell state, or null
   const float* dc0;
   float* dgates;         // [T][B][G*H] out: gate gradients (also the operand of the weight GEMMs)
+  int act;               // G = 1: 0 relu, 1 tanh
   float* dgh;            // GRU: the gate gradients as the recurrent side sees them (dn * r for
                          // the candidate); LSTM: == dgates
   float* dh_out;         // [B][H] out: gradient of the initial hidden / cell state
@@ -615,6 +623,9 @@ rnn_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const Se
           o[2 * H] = dct * gi * (1.f - gg * gg);
           o[3 * H] = d * tc * go * (1.f - go);
           dc[it] = dct * gf;
+        } else if constexpr (G == 1) {
+          const float h = __ldcg(g);
+          o[0] = a.act == 0 ? (h > 0.f ? d : 0.f) : d * (1.f - h * h);
         } else {
           const float r = __ldcg(g), z = __ldcg(g + H), n = __ldcg(g + 2 * H);
           const float q = __ldcg(a.cells + ((long long)t * B + b) * H + j);
@@ -690,7 +701,7 @@ rnn_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const Se
         float sum = 0.f;
 #pragma unroll
         for (int q = 0; q < SL; ++q) sum += pr[q];
-        dh[it] = G == 4 ? sum : dc[it] + sum;
+        dh[it] = G == 3 ? dc[it] + sum : sum;
       }
     }
     // (the exchange buffer is rewritten only after the next step's first barrier, which every
@@ -714,6 +725,13 @@ rnn_sequence_backward_kernel(const __grid_constant__ CUtensorMap map_w, const Se
 
 typedef void (*SeqBwdKernel)(const CUtensorMap, const SeqBwdArgs);
 SeqBwdKernel sequence_backward_kernel_for(int sl, int G) {
+  if (G == 1) {
+    switch (sl) {
+      case 1: return rnn_sequence_backward_kernel<1, 1>;
+      case 2: return rnn_sequence_backward_kernel<2, 1>;
+      default: return rnn_sequence_backward_kernel<4, 1>;
+    }
+  }
   if (G == 3) {
     switch (sl) {
       case 3: return rnn_sequence_backward_kernel<3, 3>;
@@ -730,6 +748,14 @@ SeqBwdKernel sequence_backward_kernel_for(int sl, int G) {
 
 typedef void (*SeqKernel)(const CUtensorMap, const SeqArgs);
 SeqKernel sequence_kernel_for(int ks, int G) {
+  if (G == 1) {
+    switch (ks) {
+      case 1: return rnn_sequence_kernel<1, 1>;
+      case 2: return rnn_sequence_kernel<2, 1>;
+      case 4: return rnn_sequence_kernel<4, 1>;
+      default: return rnn_sequence_kernel<8, 1>;
+    }
+  }
   if (G == 3) {
     switch (ks) {
       case 1: return rnn_sequence_kernel<1, 3>;
@@ -813,15 +839,15 @@ int lstm_step_forward(const CUtensorMap& map_w, const float* h_prev, long long h
 }
 
 bool lstm_sequence_supported(int math_mode, int B, int H, int G) {
-  if (!lstm_step_supported(math_mode, B, H) || (G != 3 && G != 4)) return false;
+  if (!lstm_step_supported(math_mode, B, H) || (G != 1 && G != 3 && G != 4)) return false;
   // every CTA of the kernel has to be resident at the same time (grid-wide barrier per step)
   // (one answer per device and cluster size 1, 2, 4 or 8)
-  static int max_clusters[64][8];
-  static bool known[64][8] = {{false}};
+  static int max_clusters[64][12];
+  static bool known[64][12] = {{false}};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
   const int ks = H / kSliceK;
-  const int slot = (ks == 1 ? 0 : (ks == 2 ? 1 : (ks == 4 ? 2 : 3))) + (G == 3 ? 4 : 0);
+  const int slot = (ks == 1 ? 0 : (ks == 2 ? 1 : (ks == 4 ? 2 : 3))) + (G == 3 ? 4 : (G == 1 ? 8 : 0));
   if (!known[dev][slot]) {
     if (cudaFuncSetAttribute(sequence_kernel_for(ks, G), cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kSmemBytes) != cudaSuccess) {
@@ -853,10 +879,12 @@ bool lstm_sequence_supported(int math_mode, int B, int H, int G) {
 int lstm_sequence_forward(const CUtensorMap& map_w, float* gates, float* cells, float* out,
                           long long out_stride, const float* h0, const float* c0, unsigned* sync,
                           int T, int B, int H, int reverse, long long wait_budget, int absent_cta,
-                          cudaStream_t st, int G, const float* b_hn) {
-  FLB200_REQUIRE(G == 4 || (G == 3 && b_hn), "rnn_sequence_forward: LSTM, or GRU with its bias");
+                          cudaStream_t st, int G, const float* b_hn, int act) {
+  FLB200_REQUIRE(G == 4 || G == 1 || (G == 3 && b_hn),
+                 "rnn_sequence_forward: LSTM, a plain cell, or GRU with its bias");
   SeqArgs a{};
   a.b_hn = b_hn;
+  a.act = act;
   a.gates = gates; a.cells = cells; a.out = out; a.out_stride = out_stride;
   a.h0 = h0; a.c0 = c0; a.sync = sync; a.status = tc::status_ptr();
   a.wait_budget = wait_budget > 0 ? wait_budget : tc::kWaitBudget;
@@ -900,13 +928,14 @@ int lstm_sequence_forward(const CUtensorMap& map_w, float* gates, float* cells, 
 
 bool lstm_sequence_backward_supported(int math_mode, int B, int H, int G) {
   if (math_mode != FLB200_MATH_TF32 || !flb200_has_tensor_core_path()) return false;
-  if (B < 1 || B > 32 || (H != 256 && H != 512 && H != 1024) || (G != 3 && G != 4)) return false;
+  if (B < 1 || B > 32 || (H != 256 && H != 512 && H != 1024) || (G != 1 && G != 3 && G != 4))
+    return false;
   // every CTA resident at once: one per SM (the resident weights fill its shared memory)
-  static int per_sm[64][6];
-  static bool known[64][6] = {{false}};
+  static int per_sm[64][9];
+  static bool known[64][9] = {{false}};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-  const int slot = (H == 256 ? 0 : (H == 512 ? 1 : 2)) + (G == 3 ? 3 : 0);
+  const int slot = (H == 256 ? 0 : (H == 512 ? 1 : 2)) + (G == 3 ? 3 : (G == 1 ? 6 : 0));
   if (!known[dev][slot]) {
     SeqBwdKernel kernel = sequence_backward_kernel_for(G * H / kSliceK, G);
     int n = 0;
@@ -941,12 +970,12 @@ int lstm_sequence_backward(const CUtensorMap& map_wt, const float* gates, const 
                            const float* dh0, const float* dc0, float* dgates, float* dh_out,
                            float* dc_out, float* xbuf, unsigned* sync, int T, int B, int H,
                            int reverse, cudaStream_t st, int G, float* dgh, const float* out,
-                           long long out_stride) {
-  FLB200_REQUIRE(G == 4 || (G == 3 && dgh && out && c0),
+                           long long out_stride, int act) {
+  FLB200_REQUIRE(G == 4 || G == 1 || (G == 3 && dgh && out && c0),
                  "rnn_sequence_backward: LSTM, or GRU with its second gradient buffer, the "
                  "forward output and h0");
   SeqBwdArgs a{};
-  a.dgh = G == 4 ? dgates : dgh; a.out = out; a.out_stride = out_stride;
+  a.dgh = G == 3 ? dgh : dgates; a.out = out; a.out_stride = out_stride; a.act = act;
   a.gates = gates; a.cells = cells; a.c0 = c0; a.dy = dy; a.dy_stride = dy_stride;
   a.dh0 = dh0; a.dc0 = dc0; a.dgates = dgates; a.dh_out = dh_out; a.dc_out = dc_out;
   a.xbuf = xbuf; a.sync = sync; a.status = tc::status_ptr(); a.wait_budget = tc::kWaitBudget;

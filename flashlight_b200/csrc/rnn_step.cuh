@@ -21,7 +21,7 @@ int lstm_step_forward(const CUtensorMap& map_w, const float* h_prev, long long h
 // G = 4: LSTM.  G = 3: GRU — `cells` then holds q = U_n h + b_hn per step (what its gradient
 // needs), c0 is unused, b_hn is the candidate gate's recurrent bias; backward: c0 = h0, `out` =
 // the forward output, dgh = the second gate-gradient tensor (the recurrent side's), dc0 / dc_out
-// unused.
+// unused.  G = 1: the plain cells (act 0 relu, 1 tanh): gates holds h, no cell tensors.
 // The whole recurrence of one (layer, direction) in one persistent kernel (W_hh resident in
 // shared memory, a grid-wide barrier per step).  Supported where lstm_step_forward is and the
 // device can hold every cluster of the launch at once.  gates [T][B][4H] (input projections
@@ -34,7 +34,7 @@ bool lstm_sequence_supported(int math_mode, int B, int H, int G = 4);
 int lstm_sequence_forward(const CUtensorMap& map_w, float* gates, float* cells, float* out,
                           long long out_stride, const float* h0, const float* c0, unsigned* sync,
                           int T, int B, int H, int reverse, long long wait_budget, int absent_cta,
-                          cudaStream_t st, int G = 4, const float* b_hn = nullptr);
+                          cudaStream_t st, int G = 4, const float* b_hn = nullptr, int act = 0);
 
 // The backward recurrence of one (layer, direction) in one persistent kernel: cell gradients
 // and dh_{t-1} = dgates_t * W_hh for all T steps, W_hh resident in shared memory (read from the
@@ -50,7 +50,7 @@ int lstm_sequence_backward(const CUtensorMap& map_wt, const float* gates, const 
                            const float* dh0, const float* dc0, float* dgates, float* dh_out,
                            float* dc_out, float* xbuf, unsigned* sync, int T, int B, int H,
                            int reverse, cudaStream_t st, int G = 4, float* dgh = nullptr,
-                           const float* out = nullptr, long long out_stride = 0);
+                           const float* out = nullptr, long long out_stride = 0, int act = 0);
 size_t lstm_sequence_backward_scratch_bytes(int H);
 
 }  // namespace flb200
