@@ -376,7 +376,7 @@ def other_workloads_leg(torch, peaks, steps=5, warmup=3, cpu_budget_s=5.0):
             ms_eager = _timed_steps(torch, step, warmup, steps)
             # the same step captured once as a CUDA graph and replayed (as the ResNet-50 line
             # does): no host work between the kernels
-            ms, captured = ms_eager, False
+            ms, captured, capture_error = ms_eager, False, None
             try:
                 side = torch.cuda.Stream()
                 side.wait_stream(torch.cuda.current_stream())
@@ -390,10 +390,12 @@ def other_workloads_leg(torch, peaks, steps=5, warmup=3, cpu_budget_s=5.0):
                 ms = _timed_steps(torch, graph.replay, warmup, steps)
                 captured = True
                 del graph
-            except Exception:
+            except Exception as exc:  # capture refused: the eager time stands, the reason is kept
+                capture_error = f"{type(exc).__name__}: {exc}"[:300]
                 torch.cuda.synchronize()
             achieved = flops / (ms * 1e-3) / 1e12
             entry = {"ms_per_step": ms, "ms_per_step_eager": ms_eager, "graph_captured": captured,
+                     "graph_error": capture_error,
                      "value": units / (ms * 1e-3), "unit": unit, "dtype": dtype,
                      "steps": steps, "warmup": warmup, "loss": float(step().tensor.float().cpu()),
                      "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak,
@@ -421,7 +423,7 @@ def other_workloads_leg(torch, peaks, steps=5, warmup=3, cpu_budget_s=5.0):
 
     # C1: README MNIST convnet, batch 64, fp32 operands on the tensor cores (TF32)
     A.set_math_mode(L.MATH_TF32)
-    m = workloads.mnist_convnet()
+    m = workloads.mnist_convnet(device_dropout=True)  # masks from the device generator
     x, t = torch.randn(64, 1, 28, 28, generator=g), torch.randint(0, 10, (64,), generator=g, dtype=torch.int32)
     mask = (torch.rand(64, 1024, generator=g) > 0.5).float()
     ps = host(m)

@@ -203,7 +203,11 @@ class View(Module):
 
 
 class Dropout(Module):
-    """fl::Dropout with the mask supplied as data, so that runs are reproducible on both sides."""
+    """fl::Dropout with the mask supplied as data.  With a host generator the mask is drawn on
+    the host, so that a run is reproducible on both sides of a parity test; without one it comes
+    from the library's counter-based device generator (flb200_bernoulli_mask): nothing crosses
+    the bus and the step can be captured as a CUDA graph (every replay of one captured graph
+    then applies the mask of the captured offsets)."""
 
     def __init__(self, p, gen=None):
         super().__init__()
@@ -212,6 +216,11 @@ class Dropout(Module):
     def forward(self, x):
         if not self.train_mode or self.p == 0:
             return x
+        if self.gen is None:
+            from .extension import bernoulli_mask
+            mask = bernoulli_mask(tuple(x.tensor.shape), 1.0 - self.p, x.tensor.device,
+                                  x.tensor.dtype)
+            return A.dropout(x, self.p, mask)
         mask = (torch.rand(x.tensor.shape, generator=self.gen) > self.p).to(x.tensor.dtype)
         return A.dropout(x, self.p, mask.to(x.tensor.device))
 

@@ -122,9 +122,11 @@ def resnet50(seed: int = 1234, device: str = "cuda", blocks=(3, 4, 6, 3), classe
     return ClassifierModel(m)
 
 
-def mnist_convnet(seed: int = 1234, device: str = "cuda") -> ClassifierModel:
+def mnist_convnet(seed: int = 1234, device: str = "cuda",
+                  device_dropout: bool = False) -> ClassifierModel:
     """Conv 1->32 5x5 SAME, ReLU, MaxPool 2x2/2, Conv 32->64 5x5 SAME, ReLU, MaxPool 2x2/2,
-    View 3136, Linear 3136->1024, ReLU, Dropout(0.5), Linear 1024->10, LogSoftmax."""
+    View 3136, Linear 3136->1024, ReLU, Dropout(0.5), Linear 1024->10, LogSoftmax.
+    device_dropout: draw the dropout masks on the device (no host generator, see nn.Dropout)."""
     gen = torch.Generator().manual_seed(seed)
     m = nn.Sequential(
         nn.Conv2D(1, 32, 5, 5, 1, 1, nn.SAME, nn.SAME, 1, 1, True, 1, gen, device), nn.ReLU(),
@@ -132,7 +134,8 @@ def mnist_convnet(seed: int = 1234, device: str = "cuda") -> ClassifierModel:
         nn.Conv2D(32, 64, 5, 5, 1, 1, nn.SAME, nn.SAME, 1, 1, True, 1, gen, device), nn.ReLU(),
         nn.Pool2D(2, 2, 2, 2, 0, 0, L.POOL_MAX),
         nn.View((-1, 7 * 7 * 64)),
-        nn.Linear(7 * 7 * 64, 1024, True, gen, device), nn.ReLU(), nn.Dropout(0.5, gen),
+        nn.Linear(7 * 7 * 64, 1024, True, gen, device), nn.ReLU(),
+        nn.Dropout(0.5, None if device_dropout else gen),
         nn.Linear(1024, 10, True, gen, device))
     return ClassifierModel(m, fused_loss=False)
 
