@@ -500,6 +500,7 @@ struct GemmProblem {
   int a_mn_major, b_mn_major;
   int M, N, k_iters, splits, iters_per_split;
   int tiles_m, tiles_n, Z;
+  int pair_n_fast;  // order of the pair tiles: column tiles of one row pair next to each other
   float* partial;  // split-K scratch [z*splits + s][M][N]
 
   struct Tile { int m0, n0, z, split, k0, k1; };
@@ -558,9 +559,15 @@ struct GemmProblem {
   __device__ __forceinline__ void decode_pair(int tile, int rank, Tile& t) const {
     const int pairs_m = (tiles_m + 1) >> 1;
     int r = tile;
-    t.m0 = (2 * (r % pairs_m) + rank) * kBM; r /= pairs_m;
-    t.split = r % splits; r /= splits;
-    t.n0 = (r % tiles_n) * BN; r /= tiles_n;
+    if (pair_n_fast) {
+      t.n0 = (r % tiles_n) * BN; r /= tiles_n;
+      t.split = r % splits; r /= splits;
+      t.m0 = (2 * (r % pairs_m) + rank) * kBM; r /= pairs_m;
+    } else {
+      t.m0 = (2 * (r % pairs_m) + rank) * kBM; r /= pairs_m;
+      t.split = r % splits; r /= splits;
+      t.n0 = (r % tiles_n) * BN; r /= tiles_n;
+    }
     t.z = r;
     t.k0 = t.split * iters_per_split;
     t.k1 = min(t.k0 + iters_per_split, k_iters);
