@@ -65,6 +65,22 @@ def _module_tests(reference_root):
     return (reference_root / "flashlight/fl/test/nn/ModuleTest.cpp").read_text()
 
 
+def test_committed_fixture_equals_the_checkout(reference_root):
+    """tests/golden/reference_module_goldens.npz (what the GPU tests read) holds exactly what a
+    fresh parse of the checkout gives."""
+    import importlib.util
+    from pathlib import Path
+    path = Path(__file__).resolve().parent / "golden" / "make_reference_goldens.py"
+    spec = importlib.util.spec_from_file_location("make_reference_goldens", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    fresh = mod.collect(reference_root)
+    stored = np.load(mod.OUT)
+    assert sorted(stored.files) == sorted(fresh)
+    for k, v in fresh.items():
+        assert np.array_equal(stored[k], v), k
+
+
 def test_embedding_matches_reference_golden(reference_root):
     """ModuleTest EmbeddingFwd: table [embDim, nEmb], ids [nQuery, batch] -> [embDim, nQuery, batch]."""
     table, ids, want = _literals(_module_tests(reference_root), "EmbeddingFwd")[:3]
