@@ -145,3 +145,30 @@ def test_dynamic_benchmark_host_logic():
         DynamicBenchmark.setBenchmarkMode(False)
     with pytest.raises(ValueError):
         DynamicBenchmark([])
+
+
+def test_unbind_returns_one_gradient_for_all_parts():
+    """Host logic of the tape's unbind(): the parts' gradients meet in one buffer and reach the
+    packed tensor once, mapped back by the inverse of the forward copy, whatever order they
+    arrive in; a second backward pass through a fresh call starts from a clean state."""
+    import torch
+    from flashlight_b200 import autograd as A
+    B, T, h, hd = 2, 3, 2, 4
+    d = h * hd
+    fwd = lambda t: t.reshape(B, T, 3, h, hd).permute(2, 0, 3, 1, 4).reshape(3, B * h, T, hd).contiguous()
+    bwd = lambda g: g.reshape(3, B, h, T, hd).permute(1, 3, 0, 2, 4).reshape(B * T, 3 * d).contiguous()
+    for order in ((0, 1, 2), (2, 0, 1)):
+        x = A.Variable(torch.arange(B * T * 3 * d, dtype=torch.float32).reshape(B * T, 3 * d), True)
+        parts = A.unbind(x, fwd, bwd, 3)
+        ref = x.tensor.reshape(B, T, 3, h, hd)
+        for i, p in enumerate(parts):
+            assert torch.equal(p.tensor, ref[:, :, i].permute(0, 2, 1, 3).reshape(B * h, T, hd))
+        grads = [torch.full((B * h, T, hd), float(i + 1)) for i in range(3)]
+        for i in order:
+            parts[i].grad_func(parts[i].inputs, grads[i])
+            if i != order[-1]:
+                assert x.grad is None  # nothing is handed on before the last part has arrived
+        want = torch.empty(B, T, 3, h, hd)
+        for i in range(3):
+            want[:, :, i] = float(i + 1)
+        assert torch.equal(x.grad, want.reshape(B * T, 3 * d))
