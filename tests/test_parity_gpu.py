@@ -652,6 +652,37 @@ def test_bernoulli_mask_is_a_pure_function_of_seed_and_counter():
     assert bernoulli_mask((0,), 0.5, "cuda").numel() == 0
 
 
+def test_dropout_module_with_device_masks():
+    """nn.Dropout without a host generator draws its mask on the device: outputs are 0 or
+    x / (1 - p), about 1 - p of them kept, the gradient passes through the same mask, eval mode
+    is the identity, and the step can be captured as a CUDA graph (no host-to-device copy)."""
+    from flashlight_b200 import autograd as A, nn
+    m = nn.Dropout(0.25)
+    x = A.Variable(torch.full((64, 1024), 2.0, device="cuda"), True)
+    y = m.forward(x)
+    kept = y.tensor != 0
+    assert torch.allclose(y.tensor[kept], torch.full_like(y.tensor[kept], 2.0 / 0.75))
+    assert abs(kept.float().mean().item() - 0.75) < 0.01
+    y.backward(torch.ones_like(y.tensor))
+    assert torch.equal(x.grad != 0, kept)
+    assert torch.allclose(x.grad[kept], torch.full_like(x.grad[kept], 1.0 / 0.75))
+    m.train(False)
+    assert m.forward(x) is x
+    m.train(True)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        m.forward(x)
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(g):
+        z = m.forward(x)
+    g.replay()
+    torch.cuda.synchronize()
+    assert abs((z.tensor != 0).float().mean().item() - 0.75) < 0.01
+
+
 def test_rnn_backward_without_output_gradient(ext):
     """dy absent counts as zeros (backend/cudnn/RNN.cpp:269-272): only dhy drives the gradient."""
     from flashlight_b200.extension import AutogradPayload, RNNGradData
