@@ -541,6 +541,56 @@ pool_backward_cl_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   }
 }
 
+// The hot forward case with everything known at compile time: fp32, max pooling, square
+// WIN x WIN window, stride S both ways, four channels per thread.  All WIN * WIN vectors of the
+// window are requested before the first comparison (the general kernel's loops have run-time
+// bounds, so its loads go out one after the other); the selection then walks them in the same
+// order with the same rule, so values and argmax bytes are identical.
+template <int WIN, int S>
+__global__ void __launch_bounds__(256)
+pool_forward_max_cl_fixed_kernel(const float* __restrict__ x, float* __restrict__ y,
+                                 uint8_t* __restrict__ argmax, PoolGeo g, int C, int cv_shift,
+                                 int per_image) {
+  const long long n = blockIdx.y;
+  const unsigned cv = (unsigned)C >> 2;
+  for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < (unsigned)per_image;
+       t += gridDim.x * blockDim.x) {
+    const unsigned pix = cv_shift >= 0 ? t >> cv_shift : t / cv;
+    const int c = (int)(t - pix * cv) * 4;
+    const int p = (int)(pix / (unsigned)g.Wo);
+    const int q = (int)(pix - (unsigned)p * (unsigned)g.Wo);
+    const int h0 = p * S - g.py, w0 = q * S - g.px;
+    const float* xn = x + n * (long long)g.H * g.W * C + c;
+    float4 v[WIN * WIN];
+    bool in[WIN * WIN];
+#pragma unroll
+    for (int ky = 0; ky < WIN; ++ky)
+#pragma unroll
+      for (int kx = 0; kx < WIN; ++kx) {
+        const int h = h0 + ky, w = w0 + kx;
+        const int i = ky * WIN + kx;
+        in[i] = h >= 0 && h < g.H && w >= 0 && w < g.W;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in[i]) v[i] = *reinterpret_cast<const float4*>(xn + ((long long)h * g.W + w) * C);
+      }
+    float acc[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    int arg[4] = {255, 255, 255, 255};
+#pragma unroll
+    for (int i = 0; i < WIN * WIN; ++i) {
+      if (!in[i]) continue;
+      const float e[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (arg[j] == 255 || e[j] > acc[j] || e[j] != e[j]) { acc[j] = e[j]; arg[j] = i; }
+    }
+    const long long o = ((n * g.Ho + p) * g.Wo + q) * (long long)C + c;
+    *reinterpret_cast<float4*>(y + o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if (argmax)
+      *reinterpret_cast<uint32_t*>(argmax + o) = (uint32_t)arg[0] | ((uint32_t)arg[1] << 8) |
+                                                 ((uint32_t)arg[2] << 16) | ((uint32_t)arg[3] << 24);
+  }
+}
+
 // The hot case of the above with everything known at compile time: fp32, max pooling with the
 // argmax payload, square WIN x WIN window, stride S both ways (3x3 / 2 and 2x2 / 2), four
 // channels per thread.  An input pixel lies in at most ceil(WIN / S)^2 windows; their
@@ -599,6 +649,22 @@ int launch_pool_cl(bool backward, const PoolGeo& g, int C, int N, const void* a,
   const dim3 grid((unsigned)bx, (unsigned)N);
   const int pi = (int)per_image;
   if (!backward) {
+    if constexpr (std::is_same<T, float>::value) {
+      if (vec && g.mode == FLB200_POOL_MAX && g.wx == g.wy && g.sx == g.sy && g.sx == 2 &&
+          (g.wx == 3 || g.wx == 2)) {
+        const unsigned cvv = (unsigned)C / 4;
+        int shift = -1;
+        if ((cvv & (cvv - 1)) == 0) { shift = 0; while ((1u << shift) < cvv) ++shift; }
+        if (g.wx == 3)
+          pool_forward_max_cl_fixed_kernel<3, 2><<<grid, 256, 0, st>>>(
+              static_cast<const float*>(a), static_cast<float*>(out), argmax_out, g, C, shift, pi);
+        else
+          pool_forward_max_cl_fixed_kernel<2, 2><<<grid, 256, 0, st>>>(
+              static_cast<const float*>(a), static_cast<float*>(out), argmax_out, g, C, shift, pi);
+        FLB200_AFTER_LAUNCH("pool2d_forward_max_channels_last");
+        return FLB200_OK;
+      }
+    }
     if (vec)
       pool_forward_cl_kernel<T, V><<<grid, 256, 0, st>>>(static_cast<const T*>(a),
                                                          static_cast<T*>(out), argmax_out, g, C, pi);
