@@ -634,6 +634,71 @@ pool_backward_max_cl_fixed_kernel(const float* __restrict__ dy, const uint8_t* _
   }
 }
 
+// The same gradient with a thread per 2 x 2 cell of input pixels (stride 2 both ways): the four
+// pixels of a cell lie in the same (at most) 2 x 2 windows, so a thread reads four dy vectors
+// and argmax words for four results instead of nine.  Candidates are added in the order of the
+// kernel above (nearer window first, rows before columns): identical sums.
+template <int WIN>
+__global__ void __launch_bounds__(256)
+pool_backward_max_cl_cell_kernel(const float* __restrict__ dy, const uint8_t* __restrict__ argmax,
+                                 float* __restrict__ dx, PoolGeo g, int C, int cv_shift,
+                                 int cells_w, int per_image) {
+  const long long n = blockIdx.y;
+  const unsigned cv = (unsigned)C >> 2;
+  for (unsigned t = blockIdx.x * blockDim.x + threadIdx.x; t < (unsigned)per_image;
+       t += gridDim.x * blockDim.x) {
+    const unsigned cell = cv_shift >= 0 ? t >> cv_shift : t / cv;
+    const int c = (int)(t - cell * cv) * 4;
+    const int ca = (int)(cell / (unsigned)cells_w);          // cell row: padded rows 2 ca, 2 ca + 1
+    const int cb = (int)(cell - (unsigned)ca * (unsigned)cells_w);
+    float4 gv[2][2];
+    uint32_t sel[2][2];
+    bool live[2][2];
+#pragma unroll
+    for (int pa = 0; pa < 2; ++pa)
+#pragma unroll
+      for (int qb = 0; qb < 2; ++qb) {
+        const int p = ca - pa, q = cb - qb;
+        live[pa][qb] = p >= 0 && p < g.Ho && q >= 0 && q < g.Wo;
+        gv[pa][qb] = make_float4(0.f, 0.f, 0.f, 0.f);
+        sel[pa][qb] = 0xffffffffu;
+        if (live[pa][qb]) {
+          const long long o = ((n * g.Ho + p) * g.Wo + q) * (long long)C + c;
+          sel[pa][qb] = *reinterpret_cast<const uint32_t*>(argmax + o);
+          gv[pa][qb] = *reinterpret_cast<const float4*>(dy + o);
+        }
+      }
+#pragma unroll
+    for (int dh = 0; dh < 2; ++dh) {
+      const int h = 2 * ca + dh - g.py;
+      if (h < 0 || h >= g.H) continue;
+#pragma unroll
+      for (int dw = 0; dw < 2; ++dw) {
+        const int w = 2 * cb + dw - g.px;
+        if (w < 0 || w >= g.W) continue;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int pa = 0; pa < 2; ++pa) {
+          const int ky = dh + 2 * pa;
+          if (ky >= WIN) continue;
+#pragma unroll
+          for (int qb = 0; qb < 2; ++qb) {
+            const int kx = dw + 2 * qb;
+            if (kx >= WIN || !live[pa][qb]) continue;
+            const uint32_t mine = (uint32_t)(ky * WIN + kx), s4 = sel[pa][qb];
+            const float4 v = gv[pa][qb];
+            if ((s4 & 0xffu) == mine) acc.x += v.x;
+            if (((s4 >> 8) & 0xffu) == mine) acc.y += v.y;
+            if (((s4 >> 16) & 0xffu) == mine) acc.z += v.z;
+            if ((s4 >> 24) == mine) acc.w += v.w;
+          }
+        }
+        *reinterpret_cast<float4*>(dx + ((n * g.H + h) * g.W + w) * (long long)C + c) = acc;
+      }
+    }
+  }
+}
+
 template <typename T>
 int launch_pool_cl(bool backward, const PoolGeo& g, int C, int N, const void* a, const void* x,
                    const uint8_t* argmax_in, uint8_t* argmax_out, void* out, cudaStream_t st) {
@@ -679,6 +744,24 @@ int launch_pool_cl(bool backward, const PoolGeo& g, int C, int N, const void* a,
         const unsigned cvv = (unsigned)C / 4;
         int shift = -1;
         if ((cvv & (cvv - 1)) == 0) { shift = 0; while ((1u << shift) < cvv) ++shift; }
+        // cells of 2 x 2 input pixels in padded coordinates
+        const long long cells_h = (g.H + g.py + 1) / 2, cells_w = (g.W + g.px + 1) / 2;
+        const long long per_cells = cells_h * cells_w * cvv;
+        if (per_cells < 0x7fffffffLL) {
+          long long cbx = (per_cells + 255) / 256;
+          if (cbx > 4096) cbx = 4096;
+          const dim3 cgrid((unsigned)cbx, (unsigned)N);
+          if (g.wx == 3)
+            pool_backward_max_cl_cell_kernel<3><<<cgrid, 256, 0, st>>>(
+                static_cast<const float*>(a), argmax_in, static_cast<float*>(out), g, C, shift,
+                (int)cells_w, (int)per_cells);
+          else
+            pool_backward_max_cl_cell_kernel<2><<<cgrid, 256, 0, st>>>(
+                static_cast<const float*>(a), argmax_in, static_cast<float*>(out), g, C, shift,
+                (int)cells_w, (int)per_cells);
+          FLB200_AFTER_LAUNCH("pool2d_backward_max_channels_last");
+          return FLB200_OK;
+        }
         if (g.wx == 3)
           pool_backward_max_cl_fixed_kernel<3, 2><<<grid, 256, 0, st>>>(
               static_cast<const float*>(a), argmax_in, static_cast<float*>(out), g, C, shift, pi);

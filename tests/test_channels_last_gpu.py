@@ -117,7 +117,8 @@ def test_first_convolution_fl_order_in_channels_last_out(L, case, mode):
         assert L.lib.flb200_tc_kernel_launches() - before >= 2
 
 
-POOL_GEOS = [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1), (3, 2, 1, 2, 1, 0), (7, 7, 1, 1, 0, 0)]
+POOL_GEOS = [(2, 2, 2, 2, 0, 0), (3, 3, 2, 2, 1, 1), (3, 2, 1, 2, 1, 0), (7, 7, 1, 1, 0, 0),
+             (3, 3, 2, 2, 0, 0), (2, 2, 2, 2, 1, 1)]  # the last two: the 2 x 2 cell kernels' other paddings
 
 
 @pytest.mark.parametrize("mode", [R.POOL_MAX, R.POOL_AVG_INCLUDE_PAD, R.POOL_AVG_EXCLUDE_PAD])
