@@ -8,6 +8,8 @@
 // 1024 classes are owned by one warp (8 rows per CTA), longer rows by a CTA.
 // Algorithmic bytes per element: forward 8, logSoftmax gradient 12, fused
 // gradient 8, crossEntropy gradient 4.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace flb200 {
@@ -60,6 +62,40 @@ log_softmax_forward_kernel(const T* __restrict__ x, T* __restrict__ y, long long
     if (live) {
       T* yr = y + row * C;
       for (long long c = lane; c < C; c += GROUP) yr[c] = Num<T>::from_f(Num<T>::to_f(xr[c]) - lse);
+    }
+  }
+}
+
+// Long fp32 rows (C a multiple of 4, 16-byte aligned): a CTA per row, 16-byte accesses, the
+// maximum and the sum of exponentials taken in ONE sweep (a running maximum, the sum rescaled
+// whenever it moves), then the sweep that writes y: two reads of the row instead of three, the
+// second one out of cache.
+__global__ void __launch_bounds__(kRowThreads)
+log_softmax_forward_vec_kernel(const float* __restrict__ x, float* __restrict__ y, long long C4,
+                               long long X) {
+  __shared__ float scratch[32];
+  for (long long row = blockIdx.x; row < X; row += gridDim.x) {
+    const float4* xr = reinterpret_cast<const float4*>(x) + row * C4;
+    float m = -INFINITY, s = 0.f;
+    for (long long c = threadIdx.x; c < C4; c += kRowThreads) {
+      const float4 v = xr[c];
+      const float vm = fmaxf(fmaxf(v.x, v.y), fmaxf(v.z, v.w));
+      if (vm > m) {
+        s *= expf(m - vm);  // m = -inf: s is 0 and stays 0
+        m = vm;
+      }
+      s += expf(v.x - m) + expf(v.y - m) + expf(v.z - m) + expf(v.w - m);
+    }
+    const float row_max = group_max<kRowThreads>(m, scratch);
+    // a thread that saw nothing (m = -inf) contributes 0; rows whose maximum is -inf or NaN
+    // give NaN, as the three-sweep kernel does
+    const float mine = m == -INFINITY ? 0.f : s * expf(m - row_max);
+    const float total = group_sum<kRowThreads>(mine, scratch);
+    const float lse = row_max + logf(total);
+    float4* yr = reinterpret_cast<float4*>(y) + row * C4;
+    for (long long c = threadIdx.x; c < C4; c += kRowThreads) {
+      const float4 v = xr[c];
+      yr[c] = make_float4(v.x - lse, v.y - lse, v.z - lse, v.w - lse);
     }
   }
 }
@@ -180,6 +216,36 @@ lsm_cce_backward_kernel(const T* __restrict__ y, const float* __restrict__ grad_
   }
 }
 
+// The same for fp32 rows of a multiple of 4 classes (16-byte aligned): blockIdx.y = row, four
+// classes per thread, the row's target and weight read once per thread, no division.
+__global__ void __launch_bounds__(256)
+lsm_cce_backward_vec_kernel(const float* __restrict__ y, const float* __restrict__ grad_loss,
+                            const int32_t* __restrict__ targets,
+                            const int32_t* __restrict__ count, float* __restrict__ dx,
+                            long long C4, int reduction, int ignore_index) {
+  const long long row = blockIdx.y;
+  const int t = targets[row];
+  const bool live = t != ignore_index && t >= 0 && t < 4 * C4;
+  const float g = live ? cce_weight(grad_loss, count, row, reduction) : 0.f;
+  const float4* yr = reinterpret_cast<const float4*>(y) + row * C4;
+  float4* dr = reinterpret_cast<float4*>(dx) + row * C4;
+  for (long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x; c < C4;
+       c += (long long)gridDim.x * blockDim.x) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (live) {
+      const float4 l = yr[c];
+      v = make_float4(g * expf(l.x), g * expf(l.y), g * expf(l.z), g * expf(l.w));
+      if ((t >> 2) == c) {  // the one class that also gets the -1 of the one-hot target
+        const int k = t & 3;
+        const float e = k == 0 ? l.x : (k == 1 ? l.y : (k == 2 ? l.z : l.w));
+        const float fixed = g * (expf(e) - 1.f);
+        if (k == 0) v.x = fixed; else if (k == 1) v.y = fixed; else if (k == 2) v.z = fixed; else v.w = fixed;
+      }
+    }
+    dr[c] = v;
+  }
+}
+
 constexpr int kCceParts = 1024;
 
 template <typename T>
@@ -195,6 +261,14 @@ int lsm_launch(bool backward, const void* a, const void* b, void* out, long long
           static_cast<const T*>(a), static_cast<T*>(out), C, X);
   } else {
     const int grid = grid_for(X, 1);
+    if constexpr (std::is_same<T, float>::value) {
+      if (!backward && C % 4 == 0 && aligned16(a) && aligned16(out)) {
+        log_softmax_forward_vec_kernel<<<grid, kRowThreads, 0, st>>>(
+            static_cast<const float*>(a), static_cast<float*>(out), C / 4, X);
+        FLB200_AFTER_LAUNCH("log_softmax_forward");
+        return FLB200_OK;
+      }
+    }
     if (backward)
       log_softmax_backward_kernel<T, kRowThreads><<<grid, kRowThreads, 0, st>>>(
           static_cast<const T*>(a), static_cast<const T*>(b), static_cast<T*>(out), C, X);
@@ -331,6 +405,15 @@ int flb200_log_softmax_cce_backward(const void* y, const float* grad_loss, const
                  "log_softmax_cce_backward: MEAN needs count");
   cudaStream_t st = as_stream(stream);
   const int grid = grid_for(C * X, 256 * 4);
+  if (dtype == FLB200_F32 && C % 4 == 0 && X <= 65535 && aligned16(y) && aligned16(grad_x)) {
+    long long bx = (C / 4 + 255) / 256;
+    if (bx > 64) bx = 64;
+    lsm_cce_backward_vec_kernel<<<dim3((unsigned)bx, (unsigned)X), 256, 0, st>>>(
+        static_cast<const float*>(y), grad_loss, targets, count, static_cast<float*>(grad_x),
+        C / 4, reduction, ignore_index);
+    FLB200_AFTER_LAUNCH("log_softmax_cce_backward");
+    return FLB200_OK;
+  }
   switch (dtype) {
     case FLB200_F32:
       lsm_cce_backward_kernel<float><<<grid, 256, 0, st>>>(
