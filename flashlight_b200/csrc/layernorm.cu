@@ -102,10 +102,159 @@ layernorm_backward_kernel(const T* __restrict__ dy, const T* __restrict__ xhat,
   }
 }
 
+// 16-byte variants for rows of a multiple of V = 16 / sizeof(T) features (row starts are then
+// 16-byte aligned with the tensors): lane l owns vectors l, l + 32, ... of the row, PERV of them.
+template <typename T, int V>
+__device__ __forceinline__ void ln_load(const T* p, float* f) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int k = 0; k < V; ++k) f[k] = Num<T>::to_f(e[k]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void ln_store(T* p, const float* f) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int k = 0; k < V; ++k) e[k] = Num<T>::from_f(f[k]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
+template <typename T, int PERV>
+__global__ void __launch_bounds__(256)
+layernorm_forward_vec_kernel(const T* __restrict__ x, const float* __restrict__ weight,
+                             const float* __restrict__ bias, T* __restrict__ y,
+                             T* __restrict__ xhat, float* __restrict__ mean_out,
+                             float* __restrict__ invstd_out, long long rows, int features,
+                             float eps) {
+  constexpr int V = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const T* xr = x + r * features;
+  float v[PERV][V];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < PERV; ++j) {
+    const int c = (j * 32 + lane) * V;
+    if (c < features) {
+      ln_load<T, V>(xr + c, v[j]);
+#pragma unroll
+      for (int k = 0; k < V; ++k) s += v[j][k];
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) v[j][k] = 0.f;
+    }
+  }
+  const float mean = warp_sum(s) / (float)features;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < PERV; ++j) {
+    const int c = (j * 32 + lane) * V;
+    if (c < features) {
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float d = v[j][k] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float invstd = rsqrtf(warp_sum(q) / (float)features + eps);
+  if (lane == 0) {
+    if (mean_out) mean_out[r] = mean;
+    if (invstd_out) invstd_out[r] = invstd;
+  }
+  T* yr = y + r * features;
+  T* hr = xhat ? xhat + r * features : nullptr;
+#pragma unroll
+  for (int j = 0; j < PERV; ++j) {
+    const int c = (j * 32 + lane) * V;
+    if (c >= features) continue;
+    float h[V], o[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      h[k] = (v[j][k] - mean) * invstd;
+      const float b = bias ? bias[c + k] : 0.f;
+      o[k] = weight ? fmaf(h[k], weight[c + k], b) : h[k] + b;
+    }
+    if (hr) ln_store<T, V>(hr + c, h);
+    ln_store<T, V>(yr + c, o);
+  }
+}
+
+template <typename T, int PERV>
+__global__ void __launch_bounds__(256)
+layernorm_backward_vec_kernel(const T* __restrict__ dy, const T* __restrict__ xhat,
+                              const float* __restrict__ weight, const float* __restrict__ invstd,
+                              T* __restrict__ dx, long long rows, int features) {
+  constexpr int V = 16 / sizeof(T);
+  const int lane = threadIdx.x & 31;
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const T* gr = dy + r * features;
+  const T* hr = xhat + r * features;
+  float g[PERV][V], h[PERV][V];
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int j = 0; j < PERV; ++j) {
+    const int c = (j * 32 + lane) * V;
+    if (c < features) {
+      ln_load<T, V>(gr + c, g[j]);
+      ln_load<T, V>(hr + c, h[j]);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        g[j][k] *= weight ? weight[c + k] : 1.f;
+        s0 += g[j][k];
+        s1 += g[j][k] * h[j][k];
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < V; ++k) g[j][k] = h[j][k] = 0.f;
+    }
+  }
+  const float m0 = warp_sum(s0) / (float)features;
+  const float m1 = warp_sum(s1) / (float)features;
+  const float is = invstd[r];
+  T* xr = dx + r * features;
+#pragma unroll
+  for (int j = 0; j < PERV; ++j) {
+    const int c = (j * 32 + lane) * V;
+    if (c >= features) continue;
+    float o[V];
+#pragma unroll
+    for (int k = 0; k < V; ++k) o[k] = is * (g[j][k] - m0 - h[j][k] * m1);
+    ln_store<T, V>(xr + c, o);
+  }
+}
+
+template <typename T>
+bool ln_vec_ok(const void* a, const void* b, const void* c, int features) {
+  constexpr int V = 16 / sizeof(T);
+  return features % V == 0 && features <= 32 * V * 8 && aligned16(a) && aligned16(b) &&
+         (!c || aligned16(c));
+}
+
 template <typename T>
 int launch_forward(const void* x, const float* w, const float* b, void* y, void* xhat, float* mean,
                    float* invstd, long long rows, int features, float eps, cudaStream_t st) {
   const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (ln_vec_ok<T>(x, y, xhat, features)) {
+    constexpr int V = 16 / sizeof(T);
+#define FLB200_LN_VEC(PERV)                                                                       \
+  if (features <= 32 * V * PERV) {                                                                \
+    layernorm_forward_vec_kernel<T, PERV><<<grid, 256, 0, st>>>(                                  \
+        static_cast<const T*>(x), w, b, static_cast<T*>(y), static_cast<T*>(xhat), mean, invstd,  \
+        rows, features, eps);                                                                     \
+    return FLB200_OK;                                                                             \
+  }
+    FLB200_LN_VEC(1)
+    FLB200_LN_VEC(2)
+    FLB200_LN_VEC(3)
+    FLB200_LN_VEC(4)
+    FLB200_LN_VEC(6)
+    FLB200_LN_VEC(8)
+#undef FLB200_LN_VEC
+  }
 #define FLB200_LN_CASE(PER)                                                                       \
   if (features <= 32 * PER) {                                                                     \
     layernorm_forward_kernel<T, PER><<<grid, 256, 0, st>>>(                                       \
@@ -127,6 +276,23 @@ template <typename T>
 int launch_backward(const void* dy, const void* xhat, const float* w, const float* invstd,
                     void* dx, long long rows, int features, cudaStream_t st) {
   const unsigned grid = (unsigned)((rows + 7) / 8);
+  if (ln_vec_ok<T>(dy, xhat, dx, features)) {
+    constexpr int V = 16 / sizeof(T);
+#define FLB200_LN_VEC(PERV)                                                                   \
+  if (features <= 32 * V * PERV) {                                                            \
+    layernorm_backward_vec_kernel<T, PERV><<<grid, 256, 0, st>>>(                             \
+        static_cast<const T*>(dy), static_cast<const T*>(xhat), w, invstd, static_cast<T*>(dx), \
+        rows, features);                                                                      \
+    return FLB200_OK;                                                                         \
+  }
+    FLB200_LN_VEC(1)
+    FLB200_LN_VEC(2)
+    FLB200_LN_VEC(3)
+    FLB200_LN_VEC(4)
+    FLB200_LN_VEC(6)
+    FLB200_LN_VEC(8)
+#undef FLB200_LN_VEC
+  }
 #define FLB200_LN_CASE(PER)                                                                   \
   if (features <= 32 * PER) {                                                                 \
     layernorm_backward_kernel<T, PER><<<grid, 256, 0, st>>>(                                  \
