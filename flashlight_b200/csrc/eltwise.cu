@@ -523,3 +523,70 @@ extern "C" int flb200_bernoulli_mask(void* out, int64_t n, float keep_prob, uint
   FLB200_AFTER_LAUNCH("bernoulli_mask");
   return FLB200_OK;
 }
+
+// ---- reorder -----------------------------------------------------------------------------------
+// fl::reorder (flashlight/fl/autograd/Functions.cpp:513-535) for the case every head split / merge
+// of an attention block is: up to four outer indices permuted, the innermost run of `inner`
+// elements contiguous on both sides.  A group of lanes copies one run with 16-byte accesses.
+namespace flb200 {
+namespace {
+
+struct ReorderGeo {
+  long long d[4];   // outer extents in OUTPUT order (the output is contiguous)
+  long long is[4];  // input strides of those indices, in 16-byte units
+  int lanes_shift;  // log2 of the lanes per run
+  int vecs;         // 16-byte vectors per run
+};
+
+__global__ void __launch_bounds__(256)
+reorder_runs_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, ReorderGeo g,
+                    long long runs) {
+  const int lanes = 1 << g.lanes_shift;
+  const int sub = threadIdx.x & (lanes - 1);
+  const long long per_cta = 256 >> g.lanes_shift;
+  for (long long r = (long long)blockIdx.x * per_cta + (threadIdx.x >> g.lanes_shift); r < runs;
+       r += (long long)gridDim.x * per_cta) {
+    long long t = r;
+    const long long i3 = t % g.d[3]; t /= g.d[3];
+    const long long i2 = t % g.d[2]; t /= g.d[2];
+    const long long i1 = t % g.d[1]; t /= g.d[1];
+    const uint4* src = in + t * g.is[0] + i1 * g.is[1] + i2 * g.is[2] + i3 * g.is[3];
+    uint4* dst = out + r * g.vecs;
+    for (int v = sub; v < g.vecs; v += lanes) dst[v] = src[v];
+  }
+}
+
+}  // namespace
+}  // namespace flb200
+
+extern "C" int flb200_reorder(const void* in, void* out, const int64_t* dims,
+                              const int64_t* in_strides, int64_t inner, int dtype, void* stream) {
+  using namespace flb200;
+  FLB200_REQUIRE(in && out && dims && in_strides, "reorder: null argument");
+  const size_t es = dtype == FLB200_F32 ? 4 : ((dtype == FLB200_F16 || dtype == FLB200_BF16) ? 2 : 0);
+  FLB200_REQUIRE(es != 0, "reorder: unknown dtype %d", dtype);
+  FLB200_REQUIRE(inner >= 1 && (inner * (int64_t)es) % 16 == 0 && aligned16(in) && aligned16(out),
+                 "reorder: runs must be whole 16-byte vectors of 16-byte aligned tensors");
+  ReorderGeo g{};
+  long long runs = 1;
+  const long long per_vec = (long long)(16 / es);
+  for (int k = 0; k < 4; ++k) {
+    FLB200_REQUIRE(dims[k] >= 0 && in_strides[k] >= 0 && in_strides[k] % per_vec == 0,
+                   "reorder: input strides must be whole 16-byte vectors");
+    g.d[k] = dims[k];
+    g.is[k] = in_strides[k] / per_vec;
+    runs *= dims[k];
+  }
+  if (runs == 0) return FLB200_OK;
+  g.vecs = (int)(inner / per_vec);
+  g.lanes_shift = 0;
+  while ((1 << g.lanes_shift) < g.vecs && g.lanes_shift < 5) ++g.lanes_shift;
+  const long long per_cta = 256 >> g.lanes_shift;
+  long long grid = (runs + per_cta - 1) / per_cta;
+  const long long cap = 32LL * device_info().sm_count;
+  if (grid > cap) grid = cap;
+  reorder_runs_kernel<<<(unsigned)grid, 256, 0, as_stream(stream)>>>(
+      static_cast<const uint4*>(in), static_cast<uint4*>(out), g, runs);
+  FLB200_AFTER_LAUNCH("reorder");
+  return FLB200_OK;
+}

@@ -119,6 +119,35 @@ def add(a, b, out=None):
     return out
 
 
+def reorder(x, shape, perm):
+    """`x.reshape(shape).permute(perm).contiguous()` through flb200_reorder: `shape` has up to five
+    extents, `perm` keeps the last one in place (the contiguous run).  Returns the permuted,
+    contiguous tensor; None where the kernel's 16-byte rules do not hold (the caller then uses
+    the torch copy)."""
+    import ctypes as C
+    n = len(shape)
+    if n < 2 or n > 5 or perm[-1] != n - 1 or not x.is_contiguous():
+        return None
+    es = x.element_size()
+    inner = shape[-1]
+    strides = [1] * n
+    for k in range(n - 2, -1, -1):
+        strides[k] = strides[k + 1] * shape[k + 1]
+    outer = [shape[p] for p in perm[:-1]]
+    ostr = [strides[p] for p in perm[:-1]]
+    while len(outer) < 4:
+        outer.insert(0, 1)
+        ostr.insert(0, 0)
+    vec = 16 // es
+    if (inner * es) % 16 or any(s % vec for s in ostr) or x.data_ptr() % 16:
+        return None
+    out = torch.empty([shape[p] for p in perm], dtype=x.dtype, device=x.device)
+    d = (C.c_int64 * 4)(*outer)
+    st = (C.c_int64 * 4)(*ostr)
+    L.check(L.lib.flb200_reorder(ptr(x), ptr(out), d, st, inner, dtype_code(x), stream_handle()))
+    return out
+
+
 def channel_sum(x, outer: int, channels: int, inner: int):
     """out[c] = sum_{o,i} x[o][c][i] (conv bias gradient; detail::sumAs onto a bias)."""
     if x.numel() != outer * channels * inner:

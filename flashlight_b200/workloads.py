@@ -221,6 +221,14 @@ def mse(y: Variable, target: torch.Tensor) -> Variable:
     return loss
 
 
+def _reorder(t: torch.Tensor, shape, perm) -> torch.Tensor:
+    """t.reshape(shape).permute(perm), contiguous: the library's reorder kernel where its
+    16-byte rules hold, a torch copy otherwise."""
+    t = t.contiguous()
+    out = F.reorder(t, tuple(shape), tuple(perm))
+    return out if out is not None else t.reshape(shape).permute(perm).contiguous()
+
+
 class TransformerLM(nn.Module):
     """Decoder-only language model of the fifth benchmark configuration: token embedding,
     `layers` pre-LayerNorm blocks (x += attn(LN1(x)); x += mlp(LN2(x)), the block of
@@ -289,21 +297,20 @@ class TransformerLM(nn.Module):
         hd = d // h
         qkv = self._lin(blk["qkv"], x)  # (B*T, 3d)
 
-        # pure data movement: one copy brings the head index forward for q, k and v together,
-        # (B*T, 3d) -> (3, B*h, T, hd); their gradients travel back the same way in one copy
+        # pure data movement (fl::reorder with the head vectors kept whole): one copy brings the
+        # head index forward for q, k and v together, (B*T, 3d) -> (3, B*h, T, hd); their
+        # gradients travel back the same way in one copy
         q, k, v = A.unbind(
             qkv,
-            lambda t: t.reshape(B, T, 3, h, hd).permute(2, 0, 3, 1, 4).reshape(3, B * h, T, hd)
-            .contiguous(),
-            lambda g: g.reshape(3, B, h, T, hd).permute(1, 3, 0, 2, 4).reshape(B * T, 3 * d)
-            .contiguous(), 3)
+            lambda t: _reorder(t, (B, T, 3, h, hd), (2, 0, 3, 1, 4)).reshape(3, B * h, T, hd),
+            lambda g: _reorder(g, (3, B, h, T, hd), (1, 3, 0, 2, 4)).reshape(B * T, 3 * d), 3)
         # scores (B*h, T, T) -> softmax with the scale 1/sqrt(head dim) and the causal mask folded
         # in -> context (B*h, T, hd); the gradient is the fused kernel where it is built (bf16,
         # head dim 64, T a multiple of 128), which keeps no T x T tensor for the backward pass
         ctx = A.attention(q, k, v, 1.0 / math.sqrt(hd), causal=True)
         merged = A.glue(
-            ctx, lambda t: t.reshape(B, h, T, hd).permute(0, 2, 1, 3).reshape(B * T, d).contiguous(),
-            lambda g: g.reshape(B, T, h, hd).permute(0, 2, 1, 3).reshape(B * h, T, hd).contiguous())
+            ctx, lambda t: _reorder(t, (B, h, T, hd), (0, 2, 1, 3)).reshape(B * T, d),
+            lambda g: _reorder(g, (B, T, h, hd), (0, 2, 1, 3)).reshape(B * h, T, hd))
         return self._lin(blk["proj"], merged)
 
     def loss(self, ids: torch.Tensor, targets: torch.Tensor) -> Variable:

@@ -459,6 +459,13 @@ int flb200_bernoulli_mask(void* out, int64_t n, float keep_prob, uint64_t seed, 
                           int dtype, void* stream);
 /* out = a + b: Variable::addGrad fan-in accumulation (flashlight/fl/autograd/Variable.cpp:205-211). In place allowed. */
 int flb200_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
+/* fl::reorder (Functions.cpp:513-535) where the innermost run stays contiguous (the head split
+ * and merge of an attention block: [B,T,3,h,hd] <-> [3,B,h,T,hd], [B,h,T,hd] <-> [B,T,h,hd]):
+ * out is contiguous with outer extents dims[0..3] (slowest first) and runs of `inner` elements;
+ * in_strides[k] = input stride, in elements, of output index k.  inner * element size and every
+ * stride must be multiples of 16 bytes, both tensors 16-byte aligned (else INVALID_ARG). */
+int flb200_reorder(const void* in, void* out, const int64_t* dims, const int64_t* in_strides,
+                   int64_t inner, int dtype, void* stream);
 
 /* fl::SGDOptimizer::step for one parameter in one pass
  * (flashlight/fl/optim/SGDOptimizer.cpp:38-68):

@@ -683,6 +683,26 @@ def test_dropout_module_with_device_masks():
     assert abs((z.tensor != 0).float().mean().item() - 0.75) < 0.01
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("case", [
+    ((2, 5, 3, 4, 64), (2, 0, 3, 1, 4)),    # packed q, k, v to heads-first
+    ((3, 2, 4, 5, 64), (1, 3, 0, 2, 4)),    # and back
+    ((3, 4, 7, 32), (0, 2, 1, 3)),          # head merge
+    ((6, 9, 8), (1, 0, 2)),                 # three indices, the shortest run (fp32: two vectors)
+    ((5, 40), (0, 1)),                      # identity
+])
+def test_reorder_matches_permute(fx, case, dtype):
+    """flb200_reorder against torch's permute copy: bit-exact data movement."""
+    shape, perm = case
+    x = randn(*shape, seed=91).to(dtype).cuda()
+    got = fx.reorder(x, shape, perm)
+    assert got is not None and got.is_contiguous()
+    assert torch.equal(got, x.permute(perm).contiguous())
+    # what the kernel is not built for is declined, not mis-copied
+    odd = randn(4, 6, 3, seed=92).to(dtype).cuda()
+    assert fx.reorder(odd, (4, 6, 3), (1, 0, 2)) is None  # runs of 3 elements: not whole vectors
+
+
 def test_rnn_backward_without_output_gradient(ext):
     """dy absent counts as zeros (backend/cudnn/RNN.cpp:269-272): only dhy drives the gradient."""
     from flashlight_b200.extension import AutogradPayload, RNNGradData
