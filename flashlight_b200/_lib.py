@@ -149,6 +149,7 @@ SIGNATURES = {
                                             vp]),
     "flb200_bernoulli_mask": (C.c_int, [vp, i64, f32, C.c_uint64, C.c_uint64, C.c_int, vp]),
     "flb200_add": (C.c_int, [vp, vp, vp, i64, C.c_int, vp]),
+    "flb200_astype": (C.c_int, [vp, C.c_int, vp, C.c_int, i64, vp]),
     "flb200_reorder": (C.c_int, [vp, vp, C.POINTER(C.c_int64), C.POINTER(C.c_int64), i64, C.c_int, vp]),
     "flb200_log_softmax_forward": (C.c_int, [vp, vp, i64, i64, C.c_int, vp]),
     "flb200_log_softmax_backward": (C.c_int, [vp, vp, vp, i64, i64, C.c_int, vp]),

@@ -311,11 +311,17 @@ def rnn(x: Variable, hx: Optional[Variable], cx: Optional[Variable], w: Variable
 def cast(x: Variable, dtype) -> Variable:
     """Variable::astype (flashlight/fl/autograd/Variable.cpp:160-175): the gradient is cast back
     to the input's type, which is how fp32 master weights receive the gradients of their bf16
-    copies.  torch glue."""
+    copies.  The conversions run on the library's kernel (flb200_astype) for f32 <-> f16 / bf16
+    and fall back to torch for other types."""
     src = x.tensor.dtype
     if src == dtype:
         return x
-    return glue(x, lambda t: t.to(dtype), lambda g: g.to(src))
+
+    def to(t, d):
+        out = F.astype(t, d) if t.is_cuda else None
+        return out if out is not None else t.to(d)
+
+    return glue(x, lambda t: to(t, dtype), lambda g: to(g, src))
 
 
 def _linear_bf16(x: Variable, w: Variable, b: Optional[Variable], gelu: bool = False) -> Variable:

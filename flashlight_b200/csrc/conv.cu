@@ -574,4 +574,25 @@ int flb200_conv2d_backward_filter_bias_cached(const flb200_conv2d_desc* d, const
   return FLB200_OK;
 }
 
+
+int flb200_astype(const void* in, int in_dtype, void* out, int out_dtype, int64_t n,
+                  void* stream) {
+  FLB200_REQUIRE(n >= 0, "astype: negative length");
+  if (n == 0) return FLB200_OK;
+  FLB200_REQUIRE(in && out, "astype: null tensor");
+  cudaStream_t st = as_stream(stream);
+  const bool in16 = in_dtype == FLB200_F16 || in_dtype == FLB200_BF16;
+  const bool out16 = out_dtype == FLB200_F16 || out_dtype == FLB200_BF16;
+  if (in_dtype == out_dtype) {
+    const size_t es = in_dtype == FLB200_F32 ? 4 : 2;
+    FLB200_REQUIRE(in_dtype == FLB200_F32 || in16, "astype: unknown dtype %d", in_dtype);
+    FLB200_CUDA_CHECK(cudaMemcpyAsync(out, in, (size_t)n * es, cudaMemcpyDeviceToDevice, st));
+    return FLB200_OK;
+  }
+  if (in_dtype == FLB200_F32 && out16) return narrow(static_cast<const float*>(in), out, n, out_dtype, st);
+  if (in16 && out_dtype == FLB200_F32) return widen(in, static_cast<float*>(out), n, in_dtype, st);
+  return fail(FLB200_UNSUPPORTED, "astype: %d -> %d is not built (f32 <-> f16 / bf16 only)",
+              in_dtype, out_dtype);
+}
+
 }  // extern "C"

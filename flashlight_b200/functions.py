@@ -119,6 +119,20 @@ def add(a, b, out=None):
     return out
 
 
+def astype(x, dtype):
+    """x.to(dtype) between float32 and float16 / bfloat16 through flb200_astype (contiguous
+    tensors); None for anything else (the caller then lets torch convert)."""
+    codes = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
+    if x.dtype not in codes or dtype not in codes or not x.is_contiguous():
+        return None
+    if x.dtype != dtype and torch.float32 not in (x.dtype, dtype):
+        return None
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    L.check(L.lib.flb200_astype(ptr(x), codes[x.dtype], ptr(out), codes[dtype], x.numel(),
+                                stream_handle()))
+    return out
+
+
 def reorder(x, shape, perm):
     """`x.reshape(shape).permute(perm).contiguous()` through flb200_reorder: `shape` has up to five
     extents, `perm` keeps the last one in place (the contiguous run).  Returns the permuted,

@@ -459,6 +459,10 @@ int flb200_bernoulli_mask(void* out, int64_t n, float keep_prob, uint64_t seed, 
                           int dtype, void* stream);
 /* out = a + b: Variable::addGrad fan-in accumulation (flashlight/fl/autograd/Variable.cpp:205-211). In place allowed. */
 int flb200_add(const void* a, const void* b, void* out, int64_t n, int dtype, void* stream);
+/* Variable::astype (flashlight/fl/autograd/Variable.cpp:91-100) between f32 and f16 / bf16
+ * (round to nearest even), 16 bytes per thread; the same type on both sides is a copy. */
+int flb200_astype(const void* in, int in_dtype, void* out, int out_dtype, int64_t n,
+                  void* stream);
 /* fl::reorder (Functions.cpp:513-535) where the innermost run stays contiguous (the head split
  * and merge of an attention block: [B,T,3,h,hd] <-> [3,B,h,T,hd], [B,h,T,hd] <-> [B,T,h,hd]):
  * out is contiguous with outer extents dims[0..3] (slowest first) and runs of `inner` elements;

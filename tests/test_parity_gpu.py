@@ -703,6 +703,21 @@ def test_reorder_matches_permute(fx, case, dtype):
     assert fx.reorder(odd, (4, 6, 3), (1, 0, 2)) is None  # runs of 3 elements: not whole vectors
 
 
+@pytest.mark.parametrize("n", [1, 7, 4096, 1000003])
+@pytest.mark.parametrize("half", [torch.bfloat16, torch.float16])
+def test_astype_matches_torch(fx, n, half):
+    """flb200_astype against torch's conversion (round to nearest even), both directions, lengths
+    that are not multiples of the vector width, and a view that starts off a 16-byte boundary."""
+    x = (randn(n + 3, seed=93) * 3).cuda()
+    for src in (x[:n], x[3:3 + n].contiguous(), x[1:1 + n]):
+        down = fx.astype(src, half)
+        assert down is not None and torch.equal(down, src.to(half))
+        up = fx.astype(down, torch.float32)
+        assert torch.equal(up, down.float())
+    assert torch.equal(fx.astype(x, torch.float32), x)
+    assert fx.astype(x.to(half), torch.float16 if half == torch.bfloat16 else torch.bfloat16) is None
+
+
 def test_rnn_backward_without_output_gradient(ext):
     """dy absent counts as zeros (backend/cudnn/RNN.cpp:269-272): only dhy drives the gradient."""
     from flashlight_b200.extension import AutogradPayload, RNNGradData
