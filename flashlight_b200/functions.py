@@ -119,16 +119,19 @@ def add(a, b, out=None):
     return out
 
 
+_ASTYPE_CODES = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
+
+
 def astype(x, dtype):
     """x.to(dtype) between float32 and float16 / bfloat16 through flb200_astype (contiguous
     tensors); None for anything else (the caller then lets torch convert)."""
-    codes = {torch.float32: L.F32, torch.float16: L.F16, torch.bfloat16: L.BF16}
-    if x.dtype not in codes or dtype not in codes or not x.is_contiguous():
+    src, dst = _ASTYPE_CODES.get(x.dtype), _ASTYPE_CODES.get(dtype)
+    if src is None or dst is None or not x.is_cuda or not x.is_contiguous():
         return None
-    if x.dtype != dtype and torch.float32 not in (x.dtype, dtype):
+    if src != dst and L.F32 not in (src, dst):
         return None
     out = torch.empty(x.shape, dtype=dtype, device=x.device)
-    L.check(L.lib.flb200_astype(ptr(x), codes[x.dtype], ptr(out), codes[dtype], x.numel(),
+    L.check(L.lib.flb200_astype(x.data_ptr(), src, out.data_ptr(), dst, x.numel(),
                                 stream_handle()))
     return out
 
